@@ -1,0 +1,174 @@
+// GatedDeltaNet (KDA) linear attention: fused decode / verify / serial-prefill kernel.
+//
+// One CTA per (head, sequence group) walks the group's rows in order with the head's
+// [dk, dv] f32 state held in registers (4*dk threads, dk/4 state rows each).  Per row it
+// does everything between the input projections and o_proj:
+//   causal depthwise conv (k=4, rolling tail) -> SiLU -> split q,k,v -> L2-norm q,k ->
+//   q *= dk^-0.5 -> beta = sigmoid(b) -> decay = exp(lb * sigmoid(exp(A_log)(fb + dt_bias)))
+//   S *= decay (rows); u = S^T k; S += beta k (v - u)^T; o = S^T q
+//   -> gated RMSNorm with sigmoid(gb) and o_norm.
+// State and conv tails live in `nbuf` rotating buffers per sequence slot: with snapshots on
+// (MTP verify) the state after row i goes to buffer (cur+1+i) % nbuf, so accepting k rows is
+// just cur += k (see fb_mtp_commit) -- no state copy, where the reference restores from
+// per-token snapshots with a commit kernel (kernels/cuda/ferrite_kernels.cu:10415,10580).
+// Math: crates/ferrite-kernel/src/cpu.rs:207-351, crates/ferrite-exec/src/lib.rs:531-713.
+// Replaces gdn_step_v2/v2p, gdn_chunk_batched, gdn_chunk_fused, gdn_prep, conv1d*,
+// conv_prep_fused, gated_rmsnorm (ferrite_kernels.cu:345-1042,2743-2850,10123-10415).
+#include "common.cuh"
+
+namespace {
+
+template <int DK>
+__global__ void __launch_bounds__(4 * DK)
+gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __restrict__ fb,
+                 const float* __restrict__ gb, int ld_fg, const float* __restrict__ conv_w,
+                 const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                 const float* __restrict__ o_norm_w, float* __restrict__ state,
+                 float* __restrict__ conv_state, const int* __restrict__ cur,
+                 const RowMeta* __restrict__ meta, const int* __restrict__ group_first,
+                 float* __restrict__ out, int ld_out, int H, int b_off, int nbuf, int snapshots, float lb, float eps) {
+    constexpr int RPT = DK / 4;  // state rows per thread
+    __shared__ float qs[DK], ks[DK], vs[DK], dec[DK];
+    __shared__ float part[4][DK];
+    __shared__ float red[32];
+    __shared__ float s_beta;
+
+    const int h = blockIdx.x;
+    const int row0 = group_first[blockIdx.y];
+    const RowMeta m0 = meta[row0];
+    const int slot = m0.slot, gsize = m0.gsize;
+    const int P = H * DK;
+    const int tid = threadIdx.x;
+    const int c = tid % DK, rg = tid / DK;
+    const int cbuf = (nbuf > 1) ? cur[slot] % nbuf : 0;
+
+    const size_t head_elems = (size_t)DK * DK;
+    const size_t st_slot = (size_t)nbuf * H * head_elems;
+    float* st_base = state + (size_t)slot * st_slot;
+    const size_t cv_buf = (size_t)3 * P * 3;
+    float* cv_base = conv_state + (size_t)slot * nbuf * cv_buf;
+
+    float s[RPT];
+    {
+        const float* src = st_base + ((size_t)cbuf * H + h) * head_elems;
+#pragma unroll
+        for (int ii = 0; ii < RPT; ++ii) s[ii] = src[(size_t)(rg * RPT + ii) * DK + c];
+    }
+    // conv ownership: tid < 3*DK owns channel (part = tid / DK in {q,k,v}, elem = tid % DK)
+    const bool conv_owner = tid < 3 * DK;
+    const int ch = conv_owner ? (tid / DK) * P + h * DK + (tid % DK) : 0;
+    float hist[3] = {0.f, 0.f, 0.f}, cw[4] = {0.f, 0.f, 0.f, 0.f};
+    if (conv_owner) {
+        const float* t = cv_base + (size_t)cbuf * cv_buf + (size_t)ch * 3;
+        hist[0] = t[0]; hist[1] = t[1]; hist[2] = t[2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cw[i] = conv_w[(size_t)ch * 4 + i];
+    }
+    const float a_exp = __expf(a_log[h]);
+    const float qscale = rsqrtf((float)DK);
+
+    for (int i = 0; i < gsize; ++i) {
+        const int r = row0 + i;
+        const float* prow = proj + (size_t)r * ld_proj;
+        float val = 0.f;
+        if (conv_owner) {
+            const float xin = prow[ch];
+            val = cw[0] * hist[0] + cw[1] * hist[1] + cw[2] * hist[2] + cw[3] * xin;
+            hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = xin;
+            val = siluf_(val);
+        } else {
+            const int e = tid - 3 * DK;
+            const float g = fb[(size_t)r * ld_fg + h * DK + e] + dt_bias[h * DK + e];
+            dec[e] = __expf(lb * sigmoidf_(a_exp * g));
+            if (e == 0) s_beta = sigmoidf_(prow[b_off + h]);
+        }
+        // L2 norms of q (threads [0,DK)) and k (threads [DK,2DK)): warp partials -> red
+        float sq = (tid < 2 * DK) ? val * val : 0.f;
+        sq = warp_sum(sq);
+        __syncthreads();  // previous iteration's readers of qs/ks/vs/part are done
+        if ((tid & 31) == 0) red[tid >> 5] = sq;
+        __syncthreads();
+        if (conv_owner) {
+            const int prt = tid / DK;
+            if (prt < 2) {
+                float tot = 0.f;
+                constexpr int WPP = DK / 32;  // warps per part
+#pragma unroll
+                for (int w = 0; w < WPP; ++w) tot += red[prt * WPP + w];
+                const float nrm = sqrtf(tot);
+                const float inv = nrm > 0.f ? 1.f / nrm : 0.f;
+                if (prt == 0) qs[c] = val * inv * qscale; else ks[c] = val * inv;
+            } else {
+                vs[c] = val;
+            }
+        }
+        __syncthreads();
+        const float beta = s_beta;
+        float up = 0.f;
+#pragma unroll
+        for (int ii = 0; ii < RPT; ++ii) {
+            const int row = rg * RPT + ii;
+            s[ii] *= dec[row];
+            up = fmaf(ks[row], s[ii], up);
+        }
+        part[rg][c] = up;
+        __syncthreads();
+        const float u = part[0][c] + part[1][c] + part[2][c] + part[3][c];
+        const float delta = beta * (vs[c] - u);
+        float op = 0.f;
+#pragma unroll
+        for (int ii = 0; ii < RPT; ++ii) {
+            const int row = rg * RPT + ii;
+            s[ii] = fmaf(ks[row], delta, s[ii]);
+            op = fmaf(qs[row], s[ii], op);
+        }
+        __syncthreads();  // everyone has read part[] (u) before it is reused for o
+        part[rg][c] = op;
+        __syncthreads();
+        float o = 0.f, o2 = 0.f;
+        if (rg == 0) {
+            o = part[0][c] + part[1][c] + part[2][c] + part[3][c];
+            o2 = o * o;
+        }
+        const float tot = block_sum(o2, red);
+        if (rg == 0) {
+            const float inv = rsqrtf(tot / DK + eps);
+            const float gate = sigmoidf_(gb[(size_t)r * ld_fg + h * DK + c]);
+            out[(size_t)r * ld_out + h * DK + c] = o * inv * o_norm_w[c] * gate;
+        }
+        const bool last = (i == gsize - 1);
+        if ((snapshots && nbuf > 1) || last) {
+            const int wb = (snapshots && nbuf > 1) ? (cbuf + 1 + i) % nbuf : cbuf;
+            float* dst = st_base + ((size_t)wb * H + h) * head_elems;
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) dst[(size_t)(rg * RPT + ii) * DK + c] = s[ii];
+            if (conv_owner) {
+                float* t = cv_base + (size_t)wb * cv_buf + (size_t)ch * 3;
+                t[0] = hist[0]; t[1] = hist[1]; t[2] = hist[2];
+            }
+        }
+    }
+}
+
+}  // namespace
+
+// proj [n, ld_proj] holds q|k|v (3P) per row and b (H heads) at column b_off; fb/gb [n, ld_fg] hold the
+// decay and output-gate pre-activations (P each).  state [slots][nbuf][H][dk][dk],
+// conv_state [slots][nbuf][3P][3].  group_first[g] = first row of group g; rows of a group
+// are contiguous and ordered.  snapshots=1 requires gsize < nbuf.
+FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, const float* gb, int64_t ld_fg,
+                        const float* conv_w, const float* a_log, const float* dt_bias,
+                        const float* o_norm_w, float* state, float* conv_state, const int* cur,
+                        const void* meta, const int* group_first, int64_t n_groups, float* out,
+                        int64_t ld_out, int64_t H, int64_t dk, int64_t b_off, int64_t nbuf, int64_t snapshots, float lb,
+                        float eps, cudaStream_t st) {
+    dim3 grid((unsigned)H, (unsigned)n_groups);
+#define GDN_ARGS proj, (int)ld_proj, fb, gb, (int)ld_fg, conv_w, a_log, dt_bias, o_norm_w, state, conv_state, cur, \
+        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps
+    if (dk == 128) gdn_fused_kernel<128><<<grid, 512, 0, st>>>(GDN_ARGS);
+    else if (dk == 64) gdn_fused_kernel<64><<<grid, 256, 0, st>>>(GDN_ARGS);
+    else if (dk == 32) gdn_fused_kernel<32><<<grid, 128, 0, st>>>(GDN_ARGS);
+    else return (int)cudaErrorInvalidValue;
+#undef GDN_ARGS
+    return FB_LAUNCH_CHECK();
+}

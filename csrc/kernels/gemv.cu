@@ -1,0 +1,146 @@
+// Weight-stationary multi-row GEMV family for decode (1..8 activation rows).
+//
+//   out[m, n] (+)= sum_k x[m, k] * W[n, k]        W bf16 or fp8-e4m3 with 128x128 block scales
+//
+// Decode at 1..8 rows is bound by streaming W from HBM once; every activation row rides on
+// the same weight stream (the reference measured 4.45x for 6 verify rows because its forms
+// re-stream per row: AGENTS.md:110-120).  One warp owns R consecutive weight rows so that an
+// x fragment fetched from L1 is reused R times (L1/shared bandwidth, not HBM, is what a
+// naive multi-row GEMV runs out of on B200), lanes stride over K with 16-byte loads, and the
+// weight loads bypass L1 so the activations stay resident there.
+//
+// Replaces the reference's gemv_bf16_v2/_mrows/_nt, gemv_tri, gemv_fp8_v2 and the DSV41
+// gemm_fp8_gemv/mrows families (kernels/cuda/ferrite_kernels.cu:3016-3785,10650-11275).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+
+template <int M, int R, bool FP8>
+__global__ void __launch_bounds__(kWarps * 32)
+gemv_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
+            const float* __restrict__ x, int ldx, float* __restrict__ out, int ldo,
+            int mrows, int N, int K, int group_rows, int accumulate) {
+    constexpr int VEC = FP8 ? 16 : 8;          // elements per 16-byte load
+    constexpr int ESZ = FP8 ? 1 : 2;
+    const int lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * kWarps + (threadIdx.x >> 5);
+    const int n0 = gw * R;
+    if (n0 >= N) return;
+    const float* xg = x + (group_rows > 0 ? (size_t)(n0 / group_rows) * K : 0);
+    const int kblocks = (K + 127) >> 7;
+
+    float acc[M][R];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
+
+    const uint8_t* wrow[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        int n = min(n0 + r, N - 1);
+        wrow[r] = W + (size_t)n * K * ESZ;
+    }
+
+#pragma unroll 2
+    for (int k = lane * VEC; k < K; k += 32 * VEC) {
+        uint4 wv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) wv[r] = ldg_nc_v4(wrow[r] + (size_t)k * ESZ);
+        float xv[M][VEC];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (m < mrows) {
+#pragma unroll
+                for (int v = 0; v < VEC; v += 4) {
+                    float4 t = __ldg(reinterpret_cast<const float4*>(xg + (size_t)m * ldx + k + v));
+                    xv[m][v] = t.x; xv[m][v + 1] = t.y; xv[m][v + 2] = t.z; xv[m][v + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) xv[m][v] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float wf[VEC];
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv[r]);
+            if (FP8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) e4m3x4_to_f32(pw[i], &wf[4 * i]);
+                const float sc = __ldg(scales + (size_t)(min(n0 + r, N - 1) >> 7) * kblocks + (k >> 7));
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    float p = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) p = fmaf(wf[v], xv[m][v], p);
+                    acc[m][r] = fmaf(p, sc, acc[m][r]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { wf[2 * i] = bf16lo(pw[i]); wf[2 * i + 1] = bf16hi(pw[i]); }
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[m][r] = fmaf(wf[v], xv[m][v], acc[m][r]);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float v = warp_sum(acc[m][r]);
+            if (lane == 0 && m < mrows && n0 + r < N) {
+                float* o = out + (size_t)m * ldo + n0 + r;
+                *o = accumulate ? (*o + v) : v;
+            }
+        }
+}
+
+template <int M, bool FP8>
+int launch_r(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo,
+             int mrows, int N, int K, int group_rows, int accumulate, cudaStream_t st) {
+    // Pick R so that there are enough warps to fill 148 SMs; large matrices amortise x reads.
+    int R = (N >= 9472) ? 4 : (N >= 4736 ? 2 : 1);
+    if (group_rows > 0) while (R > 1 && (group_rows % R)) R >>= 1;
+    const int warps = (N + R - 1) / R;
+    dim3 grid((warps + kWarps - 1) / kWarps), block(kWarps * 32);
+    const uint8_t* w8 = static_cast<const uint8_t*>(W);
+    if (R == 4) gemv_kernel<M, 4, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    else if (R == 2) gemv_kernel<M, 2, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    else gemv_kernel<M, 1, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    return FB_LAUNCH_CHECK();
+}
+
+template <bool FP8>
+int launch_m(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo,
+             int mrows, int N, int K, int group_rows, int accumulate, cudaStream_t st) {
+    if (mrows <= 1) return launch_r<1, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
+    if (mrows <= 2) return launch_r<2, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
+    if (mrows <= 4) return launch_r<4, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
+    return launch_r<8, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
+}
+
+}  // namespace
+
+// W [N,K] bf16; x [m,K] f32 (row stride ldx); out [m,N] f32 (row stride ldo); m <= 8.
+// K % 8 == 0, ldx % 4 == 0.  group_rows > 0 makes it block-diagonal: weight rows
+// [g*group_rows, (g+1)*group_rows) read x[:, g*K : (g+1)*K].
+FB_API int fb_gemv_bf16(const void* W, const float* x, int64_t ldx, float* out, int64_t ldo,
+                        int64_t m, int64_t N, int64_t K, int64_t group_rows, int64_t accumulate,
+                        cudaStream_t st) {
+    if (m < 1 || m > 8 || (K % 8) || (ldx % 4)) return (int)cudaErrorInvalidValue;
+    return launch_m<false>(W, nullptr, x, (int)ldx, out, (int)ldo, (int)m, (int)N, (int)K, (int)group_rows, (int)accumulate, st);
+}
+
+// W [N,K] e4m3 with scales [ceil(N/128), ceil(K/128)] f32; K % 16 == 0.
+FB_API int fb_gemv_fp8(const void* W, const float* scales, const float* x, int64_t ldx, float* out,
+                       int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t group_rows,
+                       int64_t accumulate, cudaStream_t st) {
+    if (m < 1 || m > 8 || (K % 16) || (ldx % 4)) return (int)cudaErrorInvalidValue;
+    return launch_m<true>(W, scales, x, (int)ldx, out, (int)ldo, (int)m, (int)N, (int)K, (int)group_rows, (int)accumulate, st);
+}

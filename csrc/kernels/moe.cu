@@ -1,0 +1,256 @@
+// MoE decode path: sigmoid noaux-tc routing and W8A16 fp8 expert GEMVs.
+//
+//   s = sigmoid(logits); choose top-k of (s + bias), ties to the lower index;
+//   w = s_sel / (sum s_sel + eps_f32) * scaling                      (cpu.rs:528-572)
+//   y = sum_slot w_slot * down_e(silu(min(gate_e x, L)) * clamp(up_e x, +-L))
+// Expert weights stay e4m3 with 128x128 block scales in HBM and are dequantised in
+// registers; activations are f32.  gate/up of an expert are one [2I, H] matrix (gate rows
+// first) so a warp streams the two rows of an output pair together and applies SwiGLU in
+// its epilogue; the down kernel folds the routing weights and the sum over slots, so no
+// per-slot buffer is reduced afterwards.  Replaces moe_route, router_gemm_route_fused,
+// moe_fused_act(_fp8), moe_fused_down_sum(_fp8), moe_weighted_sum, swiglu/swiglu2
+// (kernels/cuda/ferrite_kernels.cu:392-421,1207-1300,2977,4021-4499).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t okey(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One block (256 threads) per row; E <= 1024.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                 float* __restrict__ wts, int E, int topk, float scaling) {
+    __shared__ unsigned long long wbest[8];
+    __shared__ unsigned long long s_pick;
+    __shared__ float s_sig[1024];
+    __shared__ float s_sel[32];
+    const int r = blockIdx.x;
+    unsigned long long key[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x + i * 256;
+        key[i] = 0ull;
+        if (e < E) {
+            const float s = 1.f / (1.f + expf(-logits[(size_t)r * E + e]));
+            s_sig[e] = s;
+            key[i] = ((unsigned long long)okey(s + bias[e]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)e);
+        }
+    }
+    __syncthreads();
+    for (int k = 0; k < topk; ++k) {
+        unsigned long long best = 0ull;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) best = key[i] > best ? key[i] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
+            best = t > best ? t : best;
+        }
+        if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned long long b = 0ull;
+            for (int w = 0; w < 8; ++w) b = wbest[w] > b ? wbest[w] : b;
+            s_pick = b;
+            const int e = (int)(0xffffffffu - (uint32_t)(b & 0xffffffffull));
+            ids[(size_t)r * topk + k] = e;
+            s_sel[k] = s_sig[e];
+        }
+        __syncthreads();
+        const unsigned long long pick = s_pick;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) if (key[i] == pick) key[i] = 0ull;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        float sum = 0.f;
+        for (int k = 0; k < topk; ++k) sum += s_sel[k];
+        const float inv = scaling / (sum + 1.1920929e-07f);
+        for (int k = 0; k < topk; ++k) wts[(size_t)r * topk + k] = s_sel[k] * inv;
+    }
+}
+
+// act[r][s][i] = swiglu(gate_i . x_r, up_i . x_r) for expert ids[r][s]; one warp owns IPW pairs.
+template <int IPW>
+__global__ void __launch_bounds__(256)
+moe_gate_up_fp8_kernel(const uint8_t* __restrict__ W13, const float* __restrict__ S13,
+                       const float* __restrict__ x, int ldx, const int* __restrict__ ids,
+                       float* __restrict__ act, int topk, int I, int H, int e_lo, int e_cnt, float limit) {
+    const int pair = blockIdx.y;  // r * topk + s
+    const int r = pair / topk;
+    const int le = ids[pair] - e_lo;
+    const int lane = threadIdx.x & 31;
+    const int i0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * IPW;
+    if (i0 >= I) return;
+    float* dst = act + (size_t)pair * I;
+    if (le < 0 || le >= e_cnt) {  // expert lives on another rank: contributes nothing here
+        if (lane == 0) for (int j = 0; j < IPW && i0 + j < I; ++j) dst[i0 + j] = 0.f;
+        return;
+    }
+    const int kb = (H + 127) >> 7;
+    const int nb = (2 * I + 127) >> 7;
+    const uint8_t* W = W13 + (size_t)le * 2 * I * H;
+    const float* S = S13 + (size_t)le * nb * kb;
+    const float* xr = x + (size_t)r * ldx;
+    float ag[IPW], au[IPW];
+#pragma unroll
+    for (int j = 0; j < IPW; ++j) { ag[j] = 0.f; au[j] = 0.f; }
+#pragma unroll 2
+    for (int k = lane * 16; k < H; k += 512) {
+        uint4 wg[IPW], wu[IPW];
+#pragma unroll
+        for (int j = 0; j < IPW; ++j) {
+            const int i = min(i0 + j, I - 1);
+            wg[j] = ldg_nc_v4(W + (size_t)i * H + k);
+            wu[j] = ldg_nc_v4(W + (size_t)(I + i) * H + k);
+        }
+        float xv[16];
+#pragma unroll
+        for (int v = 0; v < 16; v += 4) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(xr + k + v));
+            xv[v] = t.x; xv[v + 1] = t.y; xv[v + 2] = t.z; xv[v + 3] = t.w;
+        }
+#pragma unroll
+        for (int j = 0; j < IPW; ++j) {
+            const int i = min(i0 + j, I - 1);
+            float wf[16];
+            const uint32_t* pg = reinterpret_cast<const uint32_t*>(&wg[j]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) e4m3x4_to_f32(pg[q], &wf[4 * q]);
+            float p = 0.f;
+#pragma unroll
+            for (int v = 0; v < 16; ++v) p = fmaf(wf[v], xv[v], p);
+            ag[j] = fmaf(p, __ldg(S + (size_t)(i >> 7) * kb + (k >> 7)), ag[j]);
+            const uint32_t* pu = reinterpret_cast<const uint32_t*>(&wu[j]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) e4m3x4_to_f32(pu[q], &wf[4 * q]);
+            p = 0.f;
+#pragma unroll
+            for (int v = 0; v < 16; ++v) p = fmaf(wf[v], xv[v], p);
+            au[j] = fmaf(p, __ldg(S + (size_t)((I + i) >> 7) * kb + (k >> 7)), au[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < IPW; ++j) {
+        const float g = warp_sum(ag[j]), u = warp_sum(au[j]);
+        if (lane == 0 && i0 + j < I) {
+            const float gc = fminf(g, limit);
+            const float uc = fminf(fmaxf(u, -limit), limit);
+            dst[i0 + j] = siluf_(gc) * uc;
+        }
+    }
+}
+
+// out[r][c] (+)= sum_s wts[r][s] * (W2[e_s][c][:] . act[r][s][:]); one warp owns CPW columns,
+// lanes stride over the flattened (slot, 16-element chunk) space.
+template <int CPW>
+__global__ void __launch_bounds__(256)
+moe_down_fp8_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2,
+                    const float* __restrict__ act, const int* __restrict__ ids,
+                    const float* __restrict__ wts, float* __restrict__ out, int ldo, int topk, int I, int H,
+                    int e_lo, int e_cnt, int accumulate) {
+    const int r = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const int c0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * CPW;
+    if (c0 >= H) return;
+    const int cpr = I >> 4;  // 16-element chunks per weight row
+    const int kb = (I + 127) >> 7;
+    const int nb = (H + 127) >> 7;
+    float acc[CPW];
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) acc[j] = 0.f;
+    const int items = topk * cpr;
+#pragma unroll 2
+    for (int it = lane; it < items; it += 32) {
+        const int s = it / cpr, ck = it % cpr;
+        const int le = ids[(size_t)r * topk + s] - e_lo;
+        if (le < 0 || le >= e_cnt) continue;
+        const float wt = wts[(size_t)r * topk + s];
+        const uint8_t* W = W2 + (size_t)le * H * I;
+        const float* S = S2 + (size_t)le * nb * kb;
+        const int k = ck * 16;
+        uint4 wv[CPW];
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) wv[j] = ldg_nc_v4(W + (size_t)min(c0 + j, H - 1) * I + k);
+        const float* a = act + ((size_t)r * topk + s) * I + k;
+        float xv[16];
+#pragma unroll
+        for (int v = 0; v < 16; v += 4) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(a + v));
+            xv[v] = t.x; xv[v + 1] = t.y; xv[v + 2] = t.z; xv[v + 3] = t.w;
+        }
+#pragma unroll
+        for (int j = 0; j < CPW; ++j) {
+            float wf[16];
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv[j]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) e4m3x4_to_f32(pw[q], &wf[4 * q]);
+            float p = 0.f;
+#pragma unroll
+            for (int v = 0; v < 16; ++v) p = fmaf(wf[v], xv[v], p);
+            acc[j] = fmaf(p * wt, __ldg(S + (size_t)(min(c0 + j, H - 1) >> 7) * kb + (k >> 7)), acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CPW; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0 && c0 + j < H) {
+            float* o = out + (size_t)r * ldo + c0 + j;
+            *o = accumulate ? (*o + v) : v;
+        }
+    }
+}
+
+__global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __restrict__ act, int I, float limit) {
+    const int r = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float g = fminf(gu[(size_t)r * ld + i], limit);
+    const float u = fminf(fmaxf(gu[(size_t)r * ld + I + i], -limit), limit);
+    act[(size_t)r * I + i] = siluf_(g) * u;
+}
+
+}  // namespace
+
+FB_API int fb_moe_route(const float* logits, const float* bias, int* ids, float* wts, int64_t n, int64_t E,
+                        int64_t topk, float scaling, cudaStream_t st) {
+    if (E > 1024 || topk > 32) return (int)cudaErrorInvalidValue;
+    moe_route_kernel<<<n, 256, 0, st>>>(logits, bias, ids, wts, (int)E, (int)topk, scaling);
+    return FB_LAUNCH_CHECK();
+}
+
+// W13 [E_loc, 2I, H] e4m3 (gate rows then up rows), S13 [E_loc, ceil(2I/128), ceil(H/128)];
+// act [n, topk, I].  Experts outside [e_lo, e_lo+e_cnt) produce zeros.
+FB_API int fb_moe_gate_up_fp8(const void* W13, const float* S13, const float* x, int64_t ldx, const int* ids,
+                              float* act, int64_t n, int64_t topk, int64_t I, int64_t H, int64_t e_lo,
+                              int64_t e_cnt, float limit, cudaStream_t st) {
+    if (H % 16) return (int)cudaErrorInvalidValue;
+    const int64_t pairs = n * topk;
+    const int ipw = (I * pairs >= 148 * 8 * 8) ? 4 : ((I * pairs >= 148 * 8 * 4) ? 2 : 1);
+    dim3 grid((unsigned)((I + 8 * ipw - 1) / (8 * ipw)), (unsigned)pairs);
+#define GU_ARGS (const uint8_t*)W13, S13, x, (int)ldx, ids, act, (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, limit
+    if (ipw == 4) moe_gate_up_fp8_kernel<4><<<grid, 256, 0, st>>>(GU_ARGS);
+    else if (ipw == 2) moe_gate_up_fp8_kernel<2><<<grid, 256, 0, st>>>(GU_ARGS);
+    else moe_gate_up_fp8_kernel<1><<<grid, 256, 0, st>>>(GU_ARGS);
+#undef GU_ARGS
+    return FB_LAUNCH_CHECK();
+}
+
+// W2 [E_loc, H, I] e4m3, S2 [E_loc, ceil(H/128), ceil(I/128)]; out [n, H].
+FB_API int fb_moe_down_fp8(const void* W2, const float* S2, const float* act, const int* ids, const float* wts,
+                           float* out, int64_t ldo, int64_t n, int64_t topk, int64_t I, int64_t H,
+                           int64_t e_lo, int64_t e_cnt, int64_t accumulate, cudaStream_t st) {
+    if (I % 16) return (int)cudaErrorInvalidValue;
+    dim3 grid((unsigned)((H + 15) / 16), (unsigned)n);
+    moe_down_fp8_kernel<2><<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, act, ids, wts, out, (int)ldo, (int)topk,
+                                                  (int)I, (int)H, (int)e_lo, (int)e_cnt, (int)accumulate);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_swiglu(const float* gu, int64_t ld, float* act, int64_t n, int64_t I, float limit, cudaStream_t st) {
+    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit);
+    return FB_LAUNCH_CHECK();
+}

@@ -1,0 +1,334 @@
+// Row metadata, embedding, RMSNorm family and the manifold-hyper-connection (MHC) chain.
+//
+// MHC per site (reference crates/ferrite-exec/src/mhc.rs:58-213):
+//   r = rsqrt(mean(R_flat^2) + rms_eps);  mixes = (fn . R_flat) * r              (24 values)
+//   pre_i = sigmoid(mix_i*s0 + b_i) + eps;  post_i = 2 sigmoid(mix_{4+i}*s1 + b_{4+i})
+//   comb = Sinkhorn_20(softmax_rows(mix_{8..}*s2 + b_{8..}) + eps)
+//   x = sum_i pre_i R_i  -> rmsnorm -> sublayer -> y;   R'_i = post_i*y + sum_k comb[k][i] R_k
+// Here the site is three launches: hc_mix (split-K partial dots with atomics),
+// hc_pre_apply (coefficients by one warp, contraction and the following RMSNorm fused), and
+// hc_post.  Replaces hc_pre_fuse/hc_pre/hc_post/hc_pre_mix_split/hc_pre_rest345/hc_contract
+// (kernels/cuda/ferrite_kernels.cu:2370-2679,8001-8451).
+#include "common.cuh"
+
+namespace {
+
+__global__ void prep_rows_kernel(const int* __restrict__ row_slot, const int* __restrict__ row_off,
+                                 const int* __restrict__ row_gsize, const int* __restrict__ seq_len,
+                                 RowMeta* __restrict__ meta, int n) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    RowMeta m;
+    m.slot = row_slot[r];
+    m.off = row_off[r];
+    m.gsize = row_gsize[r];
+    m.ctx0 = seq_len[m.slot];
+    m.pos = m.ctx0 + m.off;
+    m.total = m.ctx0 + m.gsize;
+    m.first = (m.off == 0);
+    m.pad = 0;
+    meta[r] = m;
+}
+
+// seq_len[slot] += (accept ? accept[slot] : gsize) for the first row of each group.
+__global__ void advance_rows_kernel(const RowMeta* __restrict__ meta, const int* __restrict__ accept,
+                                    int* __restrict__ seq_len, int n) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n) return;
+    RowMeta m = meta[r];
+    if (!m.first) return;
+    seq_len[m.slot] = m.ctx0 + (accept ? accept[m.slot] : m.gsize);
+}
+
+__global__ void embed_expand_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ emb,
+                                    float* __restrict__ out, int H, int mult, int vocab) {
+    const int r = blockIdx.x;
+    int id = ids[r];
+    id = min(max(id, 0), vocab - 1);
+    const __nv_bfloat16* e = emb + (size_t)id * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = __bfloat162float(e[j]);
+        for (int c = 0; c < mult; ++c) out[((size_t)r * mult + c) * H + j] = v;
+    }
+}
+
+// out = rmsnorm(a (+ b)) * w; optionally stores the sum.
+__global__ void rmsnorm_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                               float* __restrict__ sum_out, const float* __restrict__ w,
+                               float* __restrict__ out, int d, int lda, int ldo, float eps) {
+    extern __shared__ float sh[];
+    float* red = sh;
+    float* buf = sh + 32;
+    const int r = blockIdx.x;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = a[(size_t)r * lda + j];
+        if (b) v += b[(size_t)r * lda + j];
+        buf[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / d + eps);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = buf[j];
+        if (sum_out) sum_out[(size_t)r * lda + j] = v;
+        out[(size_t)r * ldo + j] = v * inv * w[j];
+    }
+}
+
+// cat(rmsnorm(embed[id], enorm), rmsnorm(h_prev, hnorm)) -> out [n, 2H]
+__global__ void mtp_prep_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ emb,
+                                const float* __restrict__ h_prev, const float* __restrict__ enorm,
+                                const float* __restrict__ hnorm, float* __restrict__ out, int H,
+                                int vocab, float eps) {
+    extern __shared__ float sh[];
+    float* red = sh;
+    float* buf = sh + 32;
+    const int r = blockIdx.x, half = blockIdx.y;
+    float ss = 0.f;
+    int id = min(max(ids[r], 0), vocab - 1);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = half == 0 ? __bfloat162float(emb[(size_t)id * H + j]) : h_prev[(size_t)r * H + j];
+        buf[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / H + eps);
+    const float* w = half == 0 ? enorm : hnorm;
+    for (int j = threadIdx.x; j < H; j += blockDim.x)
+        out[(size_t)r * 2 * H + (size_t)half * H + j] = buf[j] * inv * w[j];
+}
+
+constexpr int kMixSplit = 16;
+constexpr int kMaxMix = 24;
+
+// acc[r][0..mix) += fn[:, slice] . R[r][slice];  acc[r][mix] += sum(R[r][slice]^2)
+__global__ void __launch_bounds__(256)
+hc_mix_kernel(const float* __restrict__ R, const float* __restrict__ fn, float* __restrict__ acc,
+              int D, int mix) {
+    __shared__ float red[8][kMaxMix + 1];
+    const int r = blockIdx.x / kMixSplit, s = blockIdx.x % kMixSplit;
+    const int per = (D + kMixSplit - 1) / kMixSplit;
+    const int lo = s * per, hi = min(D, lo + per);
+    const float* row = R + (size_t)r * D;
+    float part[kMaxMix + 1];
+#pragma unroll
+    for (int j = 0; j <= kMaxMix; ++j) part[j] = 0.f;
+    for (int k = lo + threadIdx.x * 4; k < hi; k += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(row + k);
+        part[kMaxMix] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+        for (int j = 0; j < kMaxMix; ++j) {
+            if (j < mix) {
+                float4 f = __ldg(reinterpret_cast<const float4*>(fn + (size_t)j * D + k));
+                part[j] += v.x * f.x + v.y * f.y + v.z * f.z + v.w * f.w;
+            }
+        }
+    }
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j <= kMaxMix; ++j) {
+        float v = warp_sum(part[j]);
+        if (lane == 0) red[wid][j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x <= kMaxMix) {
+        const int j = threadIdx.x;
+        if (j < mix || j == kMaxMix) {
+            float v = 0.f;
+            for (int w = 0; w < 8; ++w) v += red[w][j];
+            atomicAdd(acc + (size_t)r * (kMaxMix + 1) + j, v);
+        }
+    }
+}
+
+// One block per row.  Warp 0 turns the accumulated mixes into (pre, post, comb); all threads
+// then form x = sum_i pre_i R_i and the fused RMSNorm.  The accumulator is cleared for reuse.
+__global__ void __launch_bounds__(512)
+hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
+                    const float* __restrict__ base, const float* __restrict__ ln_w,
+                    float* __restrict__ x_out, float* __restrict__ xn_out, float* __restrict__ post_out,
+                    float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters) {
+    extern __shared__ float sh[];
+    float* red = sh;        // 32
+    float* pre = sh + 32;   // 8
+    float* xb = sh + 40;    // H
+    const int r = blockIdx.x;
+    float* a = acc + (size_t)r * (kMaxMix + 1);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        const float rr = rsqrtf(a[kMaxMix] / (float)(n * H) + rms_eps);
+        if (lane < n) {
+            pre[lane] = sigmoidf_(a[lane] * rr * scale[0] + base[lane]) + hc_eps;
+            post_out[(size_t)r * n + lane] = 2.f * sigmoidf_(a[n + lane] * rr * scale[1] + base[n + lane]);
+        }
+        // comb element (i = lane / n, k = lane % n); n == 4 so rows are 4-lane groups
+        float c = 0.f;
+        const bool act = lane < n * n;
+        if (act) c = a[2 * n + lane] * rr * scale[2] + base[2 * n + lane];
+        float mx = act ? c : -INFINITY;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float e = act ? __expf(c - mx) : 0.f;
+        float den = e + __shfl_xor_sync(0xffffffffu, e, 1);
+        den += __shfl_xor_sync(0xffffffffu, den, 2);
+        c = act ? e / den + hc_eps : 0.f;
+        float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        c = c / (cs + hc_eps);
+        for (int it = 1; it < iters; ++it) {
+            float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            c = c / (rs + hc_eps);
+            cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            c = c / (cs + hc_eps);
+        }
+        if (act) comb_out[(size_t)r * n * n + lane] = c;
+        __syncwarp();
+        if (lane <= kMaxMix) a[lane] = 0.f;
+    }
+    __syncthreads();
+    const float* row = R + (size_t)r * n * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = 0.f;
+        for (int i = 0; i < n; ++i) v += pre[i] * row[(size_t)i * H + j];
+        xb[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / H + rms_eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = xb[j];
+        if (x_out) x_out[(size_t)r * H + j] = v;
+        xn_out[(size_t)r * H + j] = v * inv * ln_w[j];
+    }
+}
+
+// In place: R[r][i][j] = post[r][i]*y[r][j] + sum_k comb[r][k][i] R[r][k][j]   (n == 4)
+__global__ void hc_post_kernel(float* __restrict__ R, const float* __restrict__ y,
+                               const float* __restrict__ post, const float* __restrict__ comb, int H) {
+    const int r = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= H) return;
+    float p[4], c[16], v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = post[r * 4 + i];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) c[i] = comb[r * 16 + i];
+    float* row = R + (size_t)r * 4 * H;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = row[(size_t)k * H + j];
+    const float yy = y[(size_t)r * H + j];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float o = p[i] * yy;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o += c[k * 4 + i] * v[k];
+        row[(size_t)i * H + j] = o;
+    }
+}
+
+// h_final = mean_i R_i ; xn = rmsnorm(h_final) * w
+__global__ void hc_head_kernel(const float* __restrict__ R, const float* __restrict__ w,
+                               float* __restrict__ h_final, float* __restrict__ xn, int H, int n, float eps) {
+    extern __shared__ float sh[];
+    float* red = sh;
+    float* buf = sh + 32;
+    const int r = blockIdx.x;
+    const float* row = R + (size_t)r * n * H;
+    float ss = 0.f;
+    const float invn = 1.f / n;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = 0.f;
+        for (int i = 0; i < n; ++i) v += row[(size_t)i * H + j];
+        v *= invn;
+        buf[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / H + eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        h_final[(size_t)r * H + j] = buf[j];
+        xn[(size_t)r * H + j] = buf[j] * inv * w[j];
+    }
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) o[i] = a[i] + b[i];
+}
+
+}  // namespace
+
+FB_API int fb_prep_rows(const int* row_slot, const int* row_off, const int* row_gsize, const int* seq_len,
+                        void* meta, int64_t n, cudaStream_t st) {
+    prep_rows_kernel<<<(n + 127) / 128, 128, 0, st>>>(row_slot, row_off, row_gsize, seq_len, (RowMeta*)meta, (int)n);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_advance_rows(const void* meta, const int* accept, int* seq_len, int64_t n, cudaStream_t st) {
+    advance_rows_kernel<<<(n + 127) / 128, 128, 0, st>>>((const RowMeta*)meta, accept, seq_len, (int)n);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_embed_expand(const int* ids, const void* emb, float* out, int64_t n, int64_t H, int64_t mult,
+                           int64_t vocab, cudaStream_t st) {
+    embed_expand_kernel<<<n, 256, 0, st>>>(ids, (const __nv_bfloat16*)emb, out, (int)H, (int)mult, (int)vocab);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_rmsnorm(const float* a, const float* b, float* sum_out, const float* w, float* out, int64_t n,
+                      int64_t d, int64_t lda, int64_t ldo, float eps, cudaStream_t st) {
+    size_t sm = (32 + d) * sizeof(float);
+    if (sm > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    rmsnorm_kernel<<<n, 512, sm, st>>>(a, b, sum_out, w, out, (int)d, (int)lda, (int)ldo, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_mtp_prep(const int* ids, const void* emb, const float* h_prev, const float* enorm,
+                       const float* hnorm, float* out, int64_t n, int64_t H, int64_t vocab, float eps,
+                       cudaStream_t st) {
+    size_t sm = (32 + H) * sizeof(float);
+    mtp_prep_kernel<<<dim3(n, 2), 512, sm, st>>>(ids, (const __nv_bfloat16*)emb, h_prev, enorm, hnorm, out,
+                                                  (int)H, (int)vocab, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+// acc is [n, 25] f32 and must be zero on entry; fb_hc_pre_apply clears it again.
+FB_API int fb_hc_mix(const float* R, const float* fn, float* acc, int64_t n, int64_t D, int64_t mix,
+                     cudaStream_t st) {
+    if (mix > kMaxMix || (D % (4 * kMixSplit))) return (int)cudaErrorInvalidValue;
+    hc_mix_kernel<<<n * kMixSplit, 256, 0, st>>>(R, fn, acc, (int)D, (int)mix);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const float* base,
+                           const float* ln_w, float* x_out, float* xn_out, float* post_out, float* comb_out,
+                           int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
+                           cudaStream_t st) {
+    if (mult != 4) return (int)cudaErrorInvalidValue;
+    size_t sm = (40 + H) * sizeof(float);
+    hc_pre_apply_kernel<<<n, 512, sm, st>>>(R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
+                                            (int)H, (int)mult, rms_eps, hc_eps, (int)iters);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_hc_post(float* R, const float* y, const float* post, const float* comb, int64_t n, int64_t H,
+                      cudaStream_t st) {
+    hc_post_kernel<<<dim3((H + 255) / 256, n), 256, 0, st>>>(R, y, post, comb, (int)H);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_hc_head(const float* R, const float* w, float* h_final, float* xn, int64_t n, int64_t H,
+                      int64_t mult, float eps, cudaStream_t st) {
+    size_t sm = (32 + H) * sizeof(float);
+    hc_head_kernel<<<n, 512, sm, st>>>(R, w, h_final, xn, (int)H, (int)mult, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_add(const float* a, const float* b, float* o, int64_t n, cudaStream_t st) {
+    add_kernel<<<(n + 255) / 256, 256, 0, st>>>(a, b, o, (size_t)n);
+    return FB_LAUNCH_CHECK();
+}

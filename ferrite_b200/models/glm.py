@@ -1,0 +1,510 @@
+"""GLM-5.3-Flash on one B200 rank: device weight packing, state pools and the kernel chain.
+
+The chain is the device twin of :class:`ferrite_b200.models.glm_ref.GlmReference` and of
+the reference's per-layer device chains (``crates/ferrite-kernel/src/cuda.rs:3836-6298``,
+``crates/ferrite-exec/src/tp.rs:2870-3393,5320-5500``), built from the hand-written
+sm_100a kernels in ``csrc/kernels``.  Every buffer a kernel touches is allocated once, so a
+forward pass can be captured in a CUDA graph and replayed; all per-step scalars (sequence
+lengths, snapshot cursor, token ids) live in device memory and are advanced by graph nodes.
+"""
+from __future__ import annotations
+
+import math
+import zlib
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import _lib
+from ..config import EngineConfig, GlmConfig
+from ..ops.reference import quant_fp8_block
+from .glm_weights import init_kind, shard_weight, weight_layout
+
+ROWMETA_BYTES = 32
+HC_ACC = 25
+
+
+# ---------------------------------------------------------------------------------------
+# weight sources
+# ---------------------------------------------------------------------------------------
+class DictSource:
+    """Weights from a name -> tensor dict (checkpoint or small random model)."""
+
+    def __init__(self, weights: Dict[str, torch.Tensor], device):
+        self.w, self.device = weights, device
+
+    def get(self, name: str) -> torch.Tensor:
+        return self.w[name].to(self.device)
+
+
+class SyntheticSource:
+    """Random-init weights generated on the device, tensor by tensor (no host copy).
+    Matrices N(0, std); norm weights / HC scales 1; biases, A_log, dt_bias, HC bases 0."""
+
+    def __init__(self, cfg: GlmConfig, device, seed: int = 0, std: float = 0.02):
+        self.layout = weight_layout(cfg)
+        self.device, self.seed, self.std = device, seed, std
+
+    def get(self, name: str) -> torch.Tensor:
+        shape = self.layout[name]
+        kind = init_kind(name)
+        if kind == "zeros":
+            return torch.zeros(shape, device=self.device)
+        if kind == "ones":
+            return torch.ones(shape, device=self.device)
+        g = torch.Generator(device=self.device).manual_seed((self.seed << 32) ^ zlib.crc32(name.encode()))
+        dt = torch.bfloat16 if len(shape) > 1 and shape[0] * shape[1] > (1 << 22) else torch.float32
+        return torch.randn(shape, generator=g, device=self.device, dtype=dt) * self.std
+
+    def expert_chunk(self, pfx: str, e0: int, e1: int, Il: int, H: int):
+        """Routed experts e0..e1 of one layer, already at the shard's width: (gate|up
+        [n, 2*Il, H], down [n, H, Il]) in bf16."""
+        g = torch.Generator(device=self.device).manual_seed((self.seed << 32) ^ zlib.crc32(f"{pfx}.{e0}".encode()))
+        a13 = torch.randn(e1 - e0, 2 * Il, H, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+        a2 = torch.randn(e1 - e0, H, Il, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+        return a13, a2
+
+
+@dataclass
+class RowSet:
+    """Static description of the rows of one forward pass: rows are grouped by sequence,
+    groups are contiguous, row r of a group sits at position seq_len[slot] + off."""
+    n: int
+    n_groups: int
+    row_slot: torch.Tensor
+    row_off: torch.Tensor
+    row_gsize: torch.Tensor
+    group_first: torch.Tensor
+    group_slot: torch.Tensor
+    meta: torch.Tensor
+    gsize_max: int
+
+
+class GlmDeviceModel:
+    def __init__(self, cfg: GlmConfig, ecfg: EngineConfig, src, rank: int = 0, world: int = 1,
+                 device="cuda", allreduce=None, max_rows: int = 8, n_slots: int = 1):
+        self.cfg, self.ecfg = cfg, ecfg
+        self.rank, self.world = rank, world
+        self.dev = torch.device(device)
+        self.K = _lib.lib()
+        self.allreduce = allreduce  # callable(tensor_view[n,H]) summing across ranks, in place
+        self.max_rows = max_rows
+        self.n_slots = n_slots
+        la, ds = cfg.linear_attn, cfg.dsa
+        assert la.num_heads % world == 0 and ds.num_heads % world == 0
+        self.h_gdn = la.num_heads // world
+        self.P = self.h_gdn * la.head_dim
+        self.h_dsa = ds.num_heads // world
+        self.kv_f32 = ecfg.kv_dtype == "f32"
+        self.nbuf = (ecfg.mtp_n + 1) if ecfg.mtp_n > 1 else 1
+        self.E_res = ecfg.experts_resident or cfg.n_routed_experts
+        self.layers: List[dict] = []
+        self.debug_hook = None  # callable(layer_index, site, ws, n) after each sublayer (eager runs only)
+        self._pack(src)
+        self._alloc_ws()
+        self._alloc_state()
+
+    # ------------------------------------------------------------------ packing
+    def _sh(self, src, name):
+        return shard_weight(name, src.get(name), self.rank, self.world)
+
+    def _bf(self, t):
+        return t.to(torch.bfloat16).contiguous()
+
+    def _f(self, t):
+        return t.float().contiguous()
+
+    def _fp8(self, t):
+        q, s = quant_fp8_block(t.float())
+        return q.contiguous(), s.contiguous()
+
+    def _pack_attn_linear(self, src, pfx, L):
+        a = f"{pfx}.self_attn"
+        cat = torch.cat([self._sh(src, f"{a}.qkv_proj.weight").float(), src.get(f"{a}.f_a_proj.weight").float(),
+                         src.get(f"{a}.g_a_proj.weight").float(), self._sh(src, f"{a}.b_proj.weight").float()], 0)
+        L["w_in"] = self._bf(cat)
+        L["f_b"] = self._bf(self._sh(src, f"{a}.f_b_proj.weight"))
+        L["g_b"] = self._bf(self._sh(src, f"{a}.g_b_proj.weight"))
+        L["conv_w"] = self._f(self._sh(src, f"{a}.qkv_conv1d.weight"))
+        L["a_log"] = self._f(self._sh(src, f"{a}.A_log"))
+        L["dt_bias"] = self._f(self._sh(src, f"{a}.dt_bias"))
+        L["o_norm"] = self._f(src.get(f"{a}.o_norm.weight"))
+        L["o_proj"] = self._bf(self._sh(src, f"{a}.o_proj.weight"))
+
+    def _pack_attn_dsa(self, src, pfx, L):
+        ds = self.cfg.dsa
+        a = f"{pfx}.self_attn"
+        cat = torch.cat([src.get(f"{a}.q_a_proj.weight").float(), src.get(f"{a}.kv_a_proj_with_mqa.weight").float(),
+                         src.get(f"{a}.indexer.wk.weight").float(), src.get(f"{a}.indexer.weights_proj.weight").float(),
+                         src.get(f"{a}.indexer.index_kpool_compress_gate").float()], 0)
+        L["w_in"] = self._bf(cat)
+        L["qa_ln"] = self._f(src.get(f"{a}.q_a_layernorm.weight"))
+        L["kv_ln"] = self._f(src.get(f"{a}.kv_a_layernorm.weight"))
+        L["kn_w"] = self._f(src.get(f"{a}.indexer.k_norm.weight"))
+        L["kn_b"] = self._f(src.get(f"{a}.indexer.k_norm.bias"))
+        L["ape"] = self._f(src.get(f"{a}.indexer.index_kpool_compress_ape"))
+        L["w_q"] = self._bf(torch.cat([self._sh(src, f"{a}.q_b_proj.weight").float(),
+                                       src.get(f"{a}.indexer.wq_b.weight").float()], 0))
+        kvb = self._sh(src, f"{a}.kv_b_proj.weight").float()
+        dk, dv, DL = ds.qk_nope_head_dim, ds.v_head_dim, ds.kv_lora_rank
+        kvb = kvb.view(self.h_dsa, dk + dv, DL)
+        # absorbed forms: q_abs[h] = Wk_h^T q_h (rows = latent dim), o_h = Wv_h ctx_h
+        L["wk_abs"] = self._bf(kvb[:, :dk, :].transpose(1, 2).reshape(self.h_dsa * DL, dk))
+        L["wv_abs"] = self._bf(kvb[:, dk:, :].reshape(self.h_dsa * dv, DL))
+        L["o_proj"] = self._bf(self._sh(src, f"{a}.o_proj.weight"))
+
+    def _pack_mlp_dense(self, src, pfx, L):
+        g = self._sh(src, f"{pfx}.mlp.gate_proj.weight").float()
+        u = self._sh(src, f"{pfx}.mlp.up_proj.weight").float()
+        d = self._sh(src, f"{pfx}.mlp.down_proj.weight").float()
+        if self.ecfg.fp8_experts:
+            L["d13"], L["d13s"] = self._fp8(torch.cat([g, u], 0))
+            L["d2"], L["d2s"] = self._fp8(d)
+        else:
+            L["d13"], L["d2"] = self._bf(torch.cat([g, u], 0)), self._bf(d)
+        L["I_dense"] = g.shape[0]
+
+    def _pack_mlp_moe(self, src, pfx, L):
+        cfg = self.cfg
+        E, Er = cfg.n_routed_experts, self.E_res
+        L["gate"] = self._bf(src.get(f"{pfx}.mlp.gate.weight"))
+        bias = self._f(src.get(f"{pfx}.mlp.gate.e_score_correction_bias")).clone()
+        if Er < E:
+            bias[Er:] = -1e30  # experts that are not resident can never be routed to
+        L["gate_bias"] = bias
+        sg = self._sh(src, f"{pfx}.mlp.shared_expert.gate_proj.weight").float()
+        su = self._sh(src, f"{pfx}.mlp.shared_expert.up_proj.weight").float()
+        L["s13"] = self._bf(torch.cat([sg, su], 0))
+        L["s2"] = self._bf(self._sh(src, f"{pfx}.mlp.shared_expert.down_proj.weight"))
+        L["I_shared"] = sg.shape[0]
+        Il = cfg.moe_intermediate_size // self.world
+        H = cfg.hidden_size
+        w13 = torch.empty(Er, 2 * Il, H, dtype=torch.float8_e4m3fn, device=self.dev)
+        s13 = torch.empty(Er, (2 * Il + 127) // 128, (H + 127) // 128, device=self.dev)
+        w2 = torch.empty(Er, H, Il, dtype=torch.float8_e4m3fn, device=self.dev)
+        s2 = torch.empty(Er, (H + 127) // 128, (Il + 127) // 128, device=self.dev)
+        chunk = getattr(src, "expert_chunk", None)
+        if chunk is not None and (2 * Il) % 128 == 0 and H % 128 == 0:
+            step = 16
+            for e0 in range(0, Er, step):
+                e1 = min(Er, e0 + step)
+                a13, a2 = chunk(pfx, e0, e1, Il, H)
+                q, s = quant_fp8_block(a13.view(-1, H))
+                w13[e0:e1], s13[e0:e1] = q.view(e1 - e0, 2 * Il, H), s.view(e1 - e0, -1, s.shape[1])
+                q, s = quant_fp8_block(a2.view(-1, Il))
+                w2[e0:e1], s2[e0:e1] = q.view(e1 - e0, H, Il), s.view(e1 - e0, -1, s.shape[1])
+        else:
+            for e in range(Er):
+                g = self._sh(src, f"{pfx}.mlp.experts.{e}.gate_proj.weight").float()
+                u = self._sh(src, f"{pfx}.mlp.experts.{e}.up_proj.weight").float()
+                d = self._sh(src, f"{pfx}.mlp.experts.{e}.down_proj.weight").float()
+                w13[e], s13[e] = quant_fp8_block(torch.cat([g, u], 0))
+                w2[e], s2[e] = quant_fp8_block(d)
+        L["w13"], L["s13s"], L["w2"], L["s2s"] = w13, s13, w2, s2
+        L["I_moe"] = Il
+
+    def _pack(self, src):
+        cfg = self.cfg
+        self.embed = self._bf(src.get("model.embed_tokens.weight"))
+        self.lm_head = self._bf(src.get("lm_head.weight"))
+        self.final_norm = self._f(src.get("model.norm.weight"))
+        n_total = cfg.num_layers + cfg.num_nextn_predict_layers
+        for i in range(n_total):
+            pfx = f"model.layers.{i}"
+            L = {"idx": i, "dsa": cfg.is_dsa(i), "moe": cfg.is_moe(i), "mtp": i >= cfg.num_layers}
+            L["ln1"] = self._f(src.get(f"{pfx}.input_layernorm.weight"))
+            L["ln2"] = self._f(src.get(f"{pfx}.post_attention_layernorm.weight"))
+            if not L["mtp"] and cfg.mhc:
+                for site in ("attn", "ffn"):
+                    L[f"hc_{site}_fn"] = self._f(src.get(f"{pfx}.hc_{site}_fn"))
+                    L[f"hc_{site}_scale"] = self._f(src.get(f"{pfx}.hc_{site}_scale"))
+                    L[f"hc_{site}_base"] = self._f(src.get(f"{pfx}.hc_{site}_base"))
+            if L["mtp"]:
+                L["enorm"] = self._f(src.get(f"{pfx}.enorm.weight"))
+                L["hnorm"] = self._f(src.get(f"{pfx}.hnorm.weight"))
+                L["eh_proj"] = self._bf(src.get(f"{pfx}.eh_proj.weight"))
+                L["head_norm"] = self._f(src.get(f"{pfx}.shared_head.norm.weight"))
+            (self._pack_attn_dsa if L["dsa"] else self._pack_attn_linear)(src, pfx, L)
+            (self._pack_mlp_moe if L["moe"] else self._pack_mlp_dense)(src, pfx, L)
+            if L["dsa"]:
+                L["family"] = cfg.dsa_family(i)
+            else:
+                L["gdn_index"] = cfg.linear_layers.index(i)
+            self.layers.append(L)
+
+    # ------------------------------------------------------------------ buffers
+    def _z(self, *shape, dtype=torch.float32):
+        return torch.zeros(*shape, dtype=dtype, device=self.dev)
+
+    def _alloc_ws(self):
+        cfg, la, ds, M = self.cfg, self.cfg.linear_attn, self.cfg.dsa, self.max_rows
+        H = cfg.hidden_size
+        ws = {}
+        ws["R"] = self._z(M, cfg.hc_mult, H)
+        ws["x"] = self._z(M, H)        # sublayer input (normed)
+        ws["y"] = self._z(M, H)        # sublayer output
+        ws["res"] = self._z(M, H)      # plain residual (MTP layer)
+        ws["post"] = self._z(M, cfg.hc_mult)
+        ws["comb"] = self._z(M, cfg.hc_mult * cfg.hc_mult)
+        ws["hc_acc"] = self._z(M, HC_ACC)
+        self.ld_gdn = 3 * self.P + 2 * la.low_rank + self.h_gdn
+        self.ld_gdn += (-self.ld_gdn) % 4
+        ws["gdn_proj"] = self._z(M, self.ld_gdn)
+        ws["gdn_fb"] = self._z(M, self.P)
+        ws["gdn_gb"] = self._z(M, self.P)
+        ws["gdn_core"] = self._z(M, self.P)
+        self.ld_dsa = ds.q_lora_rank + ds.kv_lora_rank + 2 * ds.index_head_dim + ds.index_n_heads
+        ws["dsa_proj"] = self._z(M, self.ld_dsa + (-self.ld_dsa) % 4)
+        ws["dsa_qa"] = self._z(M, ds.q_lora_rank)
+        ws["dsa_wi"] = self._z(M, ds.index_n_heads)
+        self.ld_qq = self.h_dsa * ds.qk_nope_head_dim + ds.index_n_heads * ds.index_head_dim
+        ws["dsa_qq"] = self._z(M, self.ld_qq)
+        ws["dsa_qabs"] = self._z(M, self.h_dsa * ds.kv_lora_rank)
+        self.max_pools = (self.ecfg.max_ctx + ds.index_kpool - 1) // ds.index_kpool + 1
+        ws["dsa_scores"] = self._z(M, self.max_pools)
+        ws["dsa_idx"] = self._z(M, ds.idx_width + ds.index_kpool, dtype=torch.int32)
+        ws["dsa_cnt"] = self._z(M, dtype=torch.int32)
+        self.nsplit = 8 if self.h_dsa * ds.kv_lora_rank >= 4096 else 2
+        ws["dsa_opart"] = self._z(M, self.nsplit, self.h_dsa, ds.kv_lora_rank)
+        ws["dsa_ml"] = self._z(M, self.nsplit, self.h_dsa, 2)
+        ws["dsa_ctx"] = self._z(M, self.h_dsa * ds.kv_lora_rank)
+        ws["dsa_ov"] = self._z(M, self.h_dsa * ds.v_head_dim)
+        Imax = max([L.get("I_dense", 0) for L in self.layers] + [L.get("I_shared", 0) for L in self.layers] + [1])
+        ws["gu"] = self._z(M, 2 * Imax)
+        ws["act"] = self._z(M, Imax)
+        ws["moe_logits"] = self._z(M, cfg.n_routed_experts)
+        ws["moe_ids"] = self._z(M, cfg.num_experts_per_tok, dtype=torch.int32)
+        ws["moe_wts"] = self._z(M, cfg.num_experts_per_tok)
+        Il = max([L.get("I_moe", 0) for L in self.layers] + [1])
+        ws["moe_act"] = self._z(M, cfg.num_experts_per_tok, Il)
+        ws["h_final"] = self._z(M, H)
+        ws["xh"] = self._z(M, H)
+        ws["logits"] = self._z(M, self.lm_head.shape[0])
+        ws["amax_part"] = self._z(M * 64, dtype=torch.int64)
+        ws["mtp_in"] = self._z(M, 2 * H)
+        ws["mtp_hout"] = self._z(M, H)
+        self.ws = ws
+
+    def _alloc_state(self):
+        cfg, la, ds = self.cfg, self.cfg.linear_attn, self.cfg.dsa
+        S, nb = self.n_slots, self.nbuf
+        ng = len(cfg.linear_layers)
+        self.gdn_state = self._z(ng, S, nb, self.h_gdn, la.head_dim, la.head_dim)
+        self.conv_state = self._z(ng, S, nb, 3 * self.P, la.conv_kernel - 1)
+        ps = ds.page_size
+        self.max_pages = (self.ecfg.max_ctx + ps - 1) // ps
+        self.num_pages = S * self.max_pages
+        nf = cfg.n_dsa_families
+        kvdt = torch.float32 if self.kv_f32 else torch.bfloat16
+        self.lat_cache = torch.zeros(nf, self.num_pages, ps, ds.kv_lora_rank, dtype=kvdt, device=self.dev)
+        self.kidx_cache = self._z(nf, self.num_pages, ps, ds.index_head_dim)
+        self.kgate_cache = self._z(nf, self.num_pages, ps, ds.index_head_dim)
+        self.pool_cache = self._z(nf, self.num_pages, ps // ds.index_kpool, ds.index_head_dim)
+        # static identity paging: slot s owns pages [s*max_pages, (s+1)*max_pages)
+        self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=self.dev).view(S, self.max_pages).contiguous()
+        self.main_len = self._z(S, dtype=torch.int32)
+        self.mtp_len = self._z(S, dtype=torch.int32)
+        self.cur = self._z(S, dtype=torch.int32)
+
+    def reset_slot(self, slot: int):
+        self.gdn_state[:, slot].zero_()
+        self.conv_state[:, slot].zero_()
+        self.main_len[slot] = 0
+        self.mtp_len[slot] = 0
+        self.cur[slot] = 0
+
+    def make_rows(self, slots: List[int], gsizes: List[int]) -> RowSet:
+        rs, ro, rg, gf = [], [], [], []
+        for s, g in zip(slots, gsizes):
+            gf.append(len(rs))
+            for o in range(g):
+                rs.append(s); ro.append(o); rg.append(g)
+        n = len(rs)
+        assert n <= self.max_rows, (n, self.max_rows)
+        t = lambda v: torch.tensor(v, dtype=torch.int32, device=self.dev)
+        return RowSet(n, len(slots), t(rs), t(ro), t(rg), t(gf), t(list(slots)),
+                      torch.zeros(n * ROWMETA_BYTES, dtype=torch.uint8, device=self.dev), max(gsizes))
+
+    # ------------------------------------------------------------------ op helpers
+    def gemv(self, w, x, out, m, N, K, ldx=None, ldo=None, group_rows=0, accumulate=False, scales=None):
+        """Rows are processed eight at a time; every chunk re-streams the weights once."""
+        ldx = ldx if ldx is not None else K
+        ldo = ldo if ldo is not None else N
+        xe = x.element_size()
+        for r0 in range(0, m, 8):
+            mm = min(8, m - r0)
+            xp = _lib.ctypes.c_void_p(_ptr(x) + r0 * ldx * xe)
+            op = _lib.ctypes.c_void_p(_ptr(out) + r0 * ldo * 4)
+            if scales is None:
+                self.K.call("fb_gemv_bf16", w, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
+            else:
+                self.K.call("fb_gemv_fp8", w, scales, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
+
+    def _reduce(self, y, n):
+        if self.world > 1:
+            self.allreduce(y[:n])
+
+    # ------------------------------------------------------------------ sublayers
+    def _attn_linear(self, L, rs: RowSet, snapshots: bool):
+        cfg, la, ws, n = self.cfg, self.cfg.linear_attn, self.ws, rs.n
+        H, P, r = cfg.hidden_size, self.P, la.low_rank
+        proj = ws["gdn_proj"]
+        self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, ldo=self.ld_gdn)
+        self.gemv(L["f_b"], View(proj, 3 * P), ws["gdn_fb"], n, P, r, ldx=self.ld_gdn)
+        self.gemv(L["g_b"], View(proj, 3 * P + r), ws["gdn_gb"], n, P, r, ldx=self.ld_gdn)
+        gi = L["gdn_index"]
+        self.K.call("fb_gdn_fused", proj, self.ld_gdn, ws["gdn_fb"], ws["gdn_gb"], P, L["conv_w"], L["a_log"],
+                    L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
+                    rs.group_first, rs.n_groups, ws["gdn_core"], P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
+                    self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps))
+        self.gemv(L["o_proj"], ws["gdn_core"], ws["y"], n, H, P)
+        self._reduce(ws["y"], n)
+
+    def _attn_dsa(self, L, rs: RowSet):
+        cfg, ds, ws, n = self.cfg, self.cfg.dsa, self.ws, rs.n
+        H = cfg.hidden_size
+        f = L["family"]
+        QL, DL, ID, IH = ds.q_lora_rank, ds.kv_lora_rank, ds.index_head_dim, ds.index_n_heads
+        dk, dv, hl = ds.qk_nope_head_dim, ds.v_head_dim, self.h_dsa
+        ldp = ws["dsa_proj"].shape[1]
+        self.gemv(L["w_in"], ws["x"], ws["dsa_proj"], n, self.ld_dsa, H, ldo=ldp)
+        pt, mp, ps = self.page_table, self.max_pages, ds.page_size
+        self.K.call("fb_dsa_prep", ws["dsa_proj"], ldp, L["qa_ln"], L["kv_ln"], L["kn_w"], L["kn_b"], ws["dsa_qa"],
+                    ws["dsa_wi"], self.lat_cache[f], self.kidx_cache[f], self.kgate_cache[f], rs.meta, pt, mp, ps,
+                    n, QL, DL, ID, IH, float(cfg.rms_norm_eps), int(self.kv_f32))
+        self.K.call("fb_dsa_pool", self.kidx_cache[f], self.kgate_cache[f], L["ape"], self.pool_cache[f], rs.meta,
+                    pt, mp, ps, n, ID, ds.index_kpool)
+        self.gemv(L["w_q"], ws["dsa_qa"], ws["dsa_qq"], n, self.ld_qq, QL)
+        self.K.call("fb_dsa_scores", View(ws["dsa_qq"], hl * dk), self.ld_qq, ws["dsa_wi"], self.pool_cache[f],
+                    ws["dsa_scores"], self.max_pools, rs.meta, pt, mp, ps, n, IH, ID, ds.index_kpool, self.max_pools)
+        ldi = ws["dsa_idx"].shape[1]
+        self.K.call("fb_dsa_select", ws["dsa_scores"], self.max_pools, ws["dsa_idx"], ldi, ws["dsa_cnt"], rs.meta,
+                    n, ds.index_kpool, ds.select_pools)
+        self.gemv(L["wk_abs"], ws["dsa_qq"], ws["dsa_qabs"], n, hl * DL, dk, ldx=self.ld_qq, group_rows=DL)
+        self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
+                    ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, 0, 1,
+                    float(dk ** -0.5), int(self.kv_f32))
+        self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ws["dsa_ctx"], None, n, hl, DL, self.nsplit, 1)
+        self.gemv(L["wv_abs"], ws["dsa_ctx"], ws["dsa_ov"], n, hl * dv, DL, ldx=hl * DL, group_rows=dv)
+        self.gemv(L["o_proj"], ws["dsa_ov"], ws["y"], n, H, hl * dv)
+        self._reduce(ws["y"], n)
+
+    def _ffn_dense(self, L, n):
+        cfg, ws = self.cfg, self.ws
+        H, I = cfg.hidden_size, L["I_dense"]
+        ldg = ws["gu"].shape[1]
+        self.gemv(L["d13"], ws["x"], ws["gu"], n, 2 * I, H, ldo=ldg, scales=L.get("d13s"))
+        self.K.call("fb_swiglu", ws["gu"], ldg, ws["act"], n, I, float(cfg.swiglu_limit))
+        # act rows are packed with stride I by fb_swiglu
+        self.gemv(L["d2"], ws["act"], ws["y"], n, H, I, scales=L.get("d2s"))
+        self._reduce(ws["y"], n)
+
+    def _ffn_moe(self, L, n):
+        cfg, ws = self.cfg, self.ws
+        H, E, topk = cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok
+        Il, Is = L["I_moe"], L["I_shared"]
+        self.gemv(L["gate"], ws["x"], ws["moe_logits"], n, E, H)
+        self.K.call("fb_moe_route", ws["moe_logits"], L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
+                    float(cfg.routed_scaling_factor))
+        ldg = ws["gu"].shape[1]
+        self.gemv(L["s13"], ws["x"], ws["gu"], n, 2 * Is, H, ldo=ldg)
+        self.K.call("fb_swiglu", ws["gu"], ldg, ws["act"], n, Is, float(cfg.swiglu_limit))
+        self.gemv(L["s2"], ws["act"], ws["y"], n, H, Is)
+        self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], ws["x"], H, ws["moe_ids"], ws["moe_act"], n, topk, Il,
+                    H, 0, self.E_res, float(cfg.swiglu_limit))
+        self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"], H, n,
+                    topk, Il, H, 0, self.E_res, 1)
+        self._reduce(ws["y"], n)
+
+    def _attn(self, L, rs, snapshots):
+        if L["dsa"]:
+            self._attn_dsa(L, rs)
+        else:
+            self._attn_linear(L, rs, snapshots)
+
+    def _ffn(self, L, n):
+        if L["moe"]:
+            self._ffn_moe(L, n)
+        else:
+            self._ffn_dense(L, n)
+
+    def _hc_site(self, L, site, ln, n):
+        cfg, ws = self.cfg, self.ws
+        H, m = cfg.hidden_size, cfg.hc_mult
+        self.K.call("fb_hc_mix", ws["R"], L[f"hc_{site}_fn"], ws["hc_acc"], n, m * H, cfg.hc_mix)
+        self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
+                    ws["x"], ws["post"], ws["comb"], n, H, m, float(cfg.rms_norm_eps), float(cfg.hc_eps),
+                    cfg.hc_sinkhorn_iters)
+
+    # ------------------------------------------------------------------ passes
+    def main_forward(self, rs: RowSet, ids: torch.Tensor, snapshots: bool = False, advance: bool = True,
+                     judges: Optional[torch.Tensor] = None, head_from: int = 0):
+        """Main model over the rows of ``rs`` (token ids on the device).  Leaves logits in
+        ws['logits'][:n], the pre-norm contracted residual in ws['h_final'][:n] and, when
+        ``judges`` is given, the greedy token of every row there."""
+        cfg, ws, n, K = self.cfg, self.ws, rs.n, self.K
+        H = cfg.hidden_size
+        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.main_len, rs.meta, n)
+        K.call("fb_embed_expand", ids, self.embed, ws["R"], n, H, cfg.hc_mult, cfg.vocab_size)
+        for L in self.layers[:cfg.num_layers]:
+            self._hc_site(L, "attn", L["ln1"], n)
+            self._attn(L, rs, snapshots)
+            K.call("fb_hc_post", ws["R"], ws["y"], ws["post"], ws["comb"], n, H)
+            if self.debug_hook:
+                self.debug_hook(L["idx"], "attn", ws, n)
+            self._hc_site(L, "ffn", L["ln2"], n)
+            self._ffn(L, n)
+            K.call("fb_hc_post", ws["R"], ws["y"], ws["post"], ws["comb"], n, H)
+            if self.debug_hook:
+                self.debug_hook(L["idx"], "ffn", ws, n)
+        K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], ws["xh"], n, H, cfg.hc_mult, float(cfg.rms_norm_eps))
+        V = self.lm_head.shape[0]
+        nh = n - head_from  # the head runs on rows [head_from, n); their logits land in rows [0, nh)
+        if nh > 0:
+            self.gemv(self.lm_head, View(ws["xh"], head_from * H), ws["logits"], nh, V, H)
+            if judges is not None:
+                K.call("fb_argmax", ws["logits"], V, ws["amax_part"], View(judges, head_from), None, nh, V, 1, 0)
+        if advance:
+            K.call("fb_advance_rows", rs.meta, None, self.main_len, n)
+
+    def mtp_forward(self, rs: RowSet, ids: torch.Tensor, h_prev: torch.Tensor, out_ids: Optional[torch.Tensor],
+                    head_from: int = 0, advance: bool = True):
+        """The MTP layer over rows (token, h_prev).  ws['mtp_hout'][:n] = its residual output;
+        out_ids[r - head_from] = greedy draft token of row r >= head_from."""
+        cfg, ws, n, K = self.cfg, self.ws, rs.n, self.K
+        H = cfg.hidden_size
+        L = self.layers[cfg.num_layers]
+        eps = float(cfg.rms_norm_eps)
+        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.mtp_len, rs.meta, n)
+        K.call("fb_mtp_prep", ids, self.embed, h_prev, L["enorm"], L["hnorm"], ws["mtp_in"], n, H, cfg.vocab_size, eps)
+        self.gemv(L["eh_proj"], ws["mtp_in"], ws["res"], n, H, 2 * H)
+        K.call("fb_rmsnorm", ws["res"], None, None, L["ln1"], ws["x"], n, H, H, H, eps)
+        self._attn_dsa(L, rs)
+        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["res"], L["ln2"], ws["x"], n, H, H, H, eps)
+        self._ffn_moe(L, n)
+        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["mtp_hout"], L["head_norm"], ws["xh"], n, H, H, H, eps)
+        nh = n - head_from
+        if out_ids is not None and nh > 0:
+            V = self.lm_head.shape[0]
+            self.gemv(self.lm_head, View(ws["xh"], head_from * H), ws["logits"], nh, V, H)
+            K.call("fb_argmax", ws["logits"], V, ws["amax_part"], out_ids, None, nh, V, 1, 0)
+        if advance:
+            K.call("fb_advance_rows", rs.meta, None, self.mtp_len, n)
+
+
+class View:
+    """A column-offset view of a 2-D f32 buffer, passed to kernels as a raw pointer."""
+
+    def __init__(self, t: torch.Tensor, col: int):
+        self.t, self.col = t, col
+
+    def data_ptr(self):
+        return self.t.data_ptr() + self.col * self.t.element_size()
+
+    def element_size(self):
+        return self.t.element_size()
+
+
+def _ptr(x):
+    return x.data_ptr()

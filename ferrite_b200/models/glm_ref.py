@@ -56,6 +56,7 @@ class GlmReference:
         self.cfg = cfg
         self.world = world
         self.use_wy = use_wy
+        self.trace = None  # set to a list to record (layer, site, R, y) after every sublayer
         self.shards = [shard_weights_tp({k: v.float() for k, v in weights.items()}, r, world)
                        for r in range(world)]
         self.full = self.shards[0]  # replicated tensors are read from shard 0
@@ -207,10 +208,14 @@ class GlmReference:
                                          w[f"{pfx}.hc_attn_base"], eps, cfg.hc_eps, cfg.hc_sinkhorn_iters)
                 y = self._attn(st, i, pfx, R.rmsnorm(x, w[f"{pfx}.input_layernorm.weight"], eps))
                 Rs = R.hc_post(y, Rs, post, comb)
+                if self.trace is not None:
+                    self.trace.append((i, "attn", Rs.clone(), y.clone()))
                 x, post, comb = R.hc_pre(Rs, w[f"{pfx}.hc_ffn_fn"], w[f"{pfx}.hc_ffn_scale"],
                                          w[f"{pfx}.hc_ffn_base"], eps, cfg.hc_eps, cfg.hc_sinkhorn_iters)
                 y = self._ffn(i, pfx, R.rmsnorm(x, w[f"{pfx}.post_attention_layernorm.weight"], eps))
                 Rs = R.hc_post(y, Rs, post, comb)
+                if self.trace is not None:
+                    self.trace.append((i, "ffn", Rs.clone(), y.clone()))
             else:
                 Rs = Rs + self._attn(st, i, pfx, R.rmsnorm(Rs, w[f"{pfx}.input_layernorm.weight"], eps))
                 Rs = Rs + self._ffn(i, pfx, R.rmsnorm(Rs, w[f"{pfx}.post_attention_layernorm.weight"], eps))

@@ -252,3 +252,37 @@ def fp8_row_blocks(rows: int, rank: int, world: int, block: int = 128) -> Tuple[
     k = rows // world
     assert k % block == 0, f"fp8 row shard {k} is not a multiple of {block}"
     return rank * k // block, (rank + 1) * k // block
+
+
+def quantize_like_device(cfg: GlmConfig, w: Weights) -> Weights:
+    """The weights as a single-rank device model sees them, returned in fp32: matrices are
+    rounded to bf16, routed-expert and dense-MLP matrices go through the e4m3 128x128
+    block quantiser (gate and up jointly, as they are stored as one [2I, H] matrix).  An
+    oracle run on these values differs from the device only by accumulation order."""
+    from ..ops.reference import dequant_fp8_block, quant_fp8_block
+    out: Weights = {}
+    keep_f32 = ("hc_attn_", "hc_ffn_", "A_log", "dt_bias", "conv1d", "e_score_correction_bias", "compress_ape")
+
+    def is_fp8(name: str) -> bool:
+        if ".mlp.experts." in name:
+            return True
+        return ".mlp." in name and ".shared_expert." not in name and ".mlp.gate." not in name \
+            and name.endswith(("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+
+    for name, t in w.items():
+        t = t.float()
+        if t.dim() < 2 or any(k in name for k in keep_f32):
+            out[name] = t.clone()
+        elif is_fp8(name):
+            if name.endswith("up_proj.weight"):
+                continue  # handled with its gate
+            if name.endswith("gate_proj.weight"):
+                up = name.replace("gate_proj", "up_proj")
+                both = torch.cat([t, w[up].float()], 0)
+                dq = dequant_fp8_block(*quant_fp8_block(both))
+                out[name], out[up] = dq[: t.shape[0]].clone(), dq[t.shape[0]:].clone()
+            else:
+                out[name] = dequant_fp8_block(*quant_fp8_block(t))
+        else:
+            out[name] = t.to(torch.bfloat16).float()
+    return out

@@ -1,0 +1,22 @@
+"""All-reduce providers for the tensor-parallel chain.
+
+``make_allreduce`` returns a callable ``f(view)`` that sums a [n, H] f32 buffer across the
+ranks in place on the current stream.  ``nccl`` is the library baseline; ``p2p`` is the
+one-shot peer-memory all-reduce of :mod:`ferrite_b200.parallel.symm` (bounded waits, status
+word), the counterpart of the reference's AR v5 (``kernels/cuda/ferrite_kernels.cu:8968-9524``).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def make_allreduce(device, rank: int, world: int, max_elems: int, kind: str = "nccl"):
+    if kind == "p2p":
+        from .symm import P2PAllReduce
+        return P2PAllReduce(device, rank, world, max_elems)
+
+    def nccl_allreduce(view: torch.Tensor):
+        dist.all_reduce(view)
+
+    return nccl_allreduce

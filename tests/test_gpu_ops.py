@@ -1,0 +1,386 @@
+"""GPU: every CUDA op against the plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+from ferrite_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ferrite_b200 import _lib
+    return _lib.lib()
+
+
+def dev(t):
+    return t.cuda()
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def check(name, got, want, atol, rtol=1e-3):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item()
+    assert torch.allclose(got, want, atol=atol, rtol=rtol), f"{name}: max err {err:.3e} (ref max {ref:.3e})"
+
+
+def make_meta(K, slots, gsizes, seq_len):
+    """Row tables + RowMeta for groups (slot, size); seq_len: per-slot start positions."""
+    rs, ro, rg, gf = [], [], [], []
+    for s, g in zip(slots, gsizes):
+        gf.append(len(rs))
+        for o in range(g):
+            rs.append(s); ro.append(o); rg.append(g)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    n = len(rs)
+    meta = torch.zeros(n * 32, dtype=torch.uint8, device="cuda")
+    sl = t(seq_len)
+    K.call("fb_prep_rows", t(rs), t(ro), t(rg), sl, meta, n)
+    return meta, t(gf), n, sl
+
+
+@pytest.mark.parametrize("m,N,K_,group", [(1, 300, 256, 0), (3, 4100, 512, 0), (8, 9600, 128, 0),
+                                          (2, 16 * 64, 32, 64), (5, 777, 4096, 0)])
+def test_gemv_bf16(K, m, N, K_, group):
+    G = N // group if group else 1
+    w = rnd(N, K_, seed=1, scale=0.1).bfloat16()
+    x = rnd(m, G * K_, seed=2)
+    out = torch.full((m, N), 7.0)
+    wd, xd, od = dev(w), dev(x), dev(out)
+    K.call("fb_gemv_bf16", wd, xd, G * K_, od, N, m, N, K_, group, 0)
+    if group:
+        want = torch.einsum("mgk,gnk->mgn", x.view(m, G, K_), w.float().view(G, group, K_)).reshape(m, N)
+    else:
+        want = x @ w.float().t()
+    check("gemv", od, want, 2e-3)
+    K.call("fb_gemv_bf16", wd, xd, G * K_, od, N, m, N, K_, group, 1)
+    check("gemv-acc", od, 2 * want, 4e-3)
+
+
+@pytest.mark.parametrize("m,N,K_", [(1, 256, 256), (3, 512, 4096), (8, 10240, 384), (2, 200, 128)])
+def test_gemv_fp8(K, m, N, K_):
+    w = rnd(N, K_, seed=3, scale=0.05)
+    q, s = R.quant_fp8_block(w)
+    x = rnd(m, K_, seed=4)
+    od = torch.zeros(m, N, device="cuda")
+    K.call("fb_gemv_fp8", dev(q), dev(s), dev(x), K_, od, N, m, N, K_, 0, 0)
+    want = x @ R.dequant_fp8_block(q, s).t()
+    check("gemv_fp8", od, want, 2e-3)
+
+
+def test_rmsnorm_and_add(K):
+    n, d = 5, 384
+    a, b, w = rnd(n, d, seed=1), rnd(n, d, seed=2), rnd(d, seed=3)
+    out, s = torch.zeros(n, d, device="cuda"), torch.zeros(n, d, device="cuda")
+    K.call("fb_rmsnorm", dev(a), dev(b), s, dev(w), out, n, d, d, d, 1e-5)
+    check("sum", s, a + b, 1e-6)
+    check("rmsnorm", out, R.rmsnorm(a + b, w, 1e-5), 1e-5)
+    K.call("fb_rmsnorm", dev(a), None, None, dev(w), out, n, d, d, d, 1e-5)
+    check("rmsnorm1", out, R.rmsnorm(a, w, 1e-5), 1e-5)
+
+
+@pytest.mark.parametrize("H", [128, 4096])
+def test_hc_chain(K, H):
+    n, mult, mix = 3, 4, 24
+    Rr = rnd(n, mult, H, seed=1)
+    fn = rnd(mix, mult * H, seed=2, scale=0.05)
+    scale = torch.tensor([0.7, 1.3, 0.9])
+    base = rnd(mix, seed=3, scale=0.3)
+    ln = rnd(H, seed=4).abs() + 0.5
+    y = rnd(n, H, seed=5)
+    Rd = dev(Rr.clone())
+    acc = torch.zeros(n, 25, device="cuda")
+    x, xn = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
+    post, comb = torch.zeros(n, 4, device="cuda"), torch.zeros(n, 16, device="cuda")
+    K.call("fb_hc_mix", Rd, dev(fn), acc, n, mult * H, mix)
+    K.call("fb_hc_pre_apply", Rd, acc, dev(scale), dev(base), dev(ln), x, xn, post, comb, n, H, mult, 1e-5, 1e-6, 20)
+    xr, pr, cr = R.hc_pre(Rr, fn, scale, base, 1e-5, 1e-6, 20)
+    check("hc x", x, xr, 1e-4)
+    check("hc post", post, pr, 1e-5)
+    check("hc comb", comb.view(n, 4, 4), cr, 1e-5)
+    check("hc xn", xn, R.rmsnorm(xr, ln, 1e-5), 1e-4)
+    assert acc.abs().max().item() == 0.0, "accumulator must be cleared for reuse"
+    K.call("fb_hc_post", Rd, dev(y), post, comb, n, H)
+    check("hc_post", Rd, R.hc_post(y, Rr, pr, cr), 1e-4)
+    hf, xh = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
+    K.call("fb_hc_head", dev(Rr), dev(ln), hf, xh, n, H, mult, 1e-5)
+    check("hc_head", hf, Rr.mean(1), 1e-5)
+    check("hc_head norm", xh, R.rmsnorm(Rr.mean(1), ln, 1e-5), 1e-5)
+
+
+def test_embed_and_mtp_prep(K):
+    V, H, n = 50, 96, 4
+    emb = rnd(V, H, seed=1).bfloat16()
+    ids = torch.tensor([3, 49, 0, 7], dtype=torch.int32)
+    out = torch.zeros(n, 4, H, device="cuda")
+    K.call("fb_embed_expand", dev(ids), dev(emb), out, n, H, 4, V)
+    check("embed", out, emb.float()[ids.long()].unsqueeze(1).repeat(1, 4, 1), 0)
+    hp, en, hn = rnd(n, H, seed=2), rnd(H, seed=3), rnd(H, seed=4)
+    o2 = torch.zeros(n, 2 * H, device="cuda")
+    K.call("fb_mtp_prep", dev(ids), dev(emb), dev(hp), dev(en), dev(hn), o2, n, H, V, 1e-5)
+    want = torch.cat([R.rmsnorm(emb.float()[ids.long()], en, 1e-5), R.rmsnorm(hp, hn, 1e-5)], -1)
+    check("mtp_prep", o2, want, 1e-5)
+
+
+@pytest.mark.parametrize("dk,H,groups,nbuf,snap", [(32, 2, [3], 4, 1), (64, 3, [1, 2], 1, 0), (128, 2, [5], 4, 0),
+                                                   (128, 1, [3, 3], 4, 1)])
+def test_gdn_fused(K, dk, H, groups, nbuf, snap):
+    r_lr, P = 16, H * dk
+    slots = list(range(len(groups)))
+    S = len(groups)
+    n = sum(groups)
+    ld = 3 * P + 2 * r_lr + H
+    ld += (-ld) % 4
+    b_off = 3 * P + 2 * r_lr
+    proj = rnd(n, ld, seed=1)
+    fb, gb = rnd(n, P, seed=2), rnd(n, P, seed=3)
+    conv_w = rnd(3 * P, 4, seed=4, scale=0.5)
+    a_log, dt_bias, o_norm = rnd(H, seed=5, scale=0.3), rnd(P, seed=6, scale=0.3), rnd(dk, seed=7).abs() + 0.5
+    state = rnd(S, nbuf, H, dk, dk, seed=8, scale=0.2)
+    conv_state = rnd(S, nbuf, 3 * P, 3, seed=9)
+    cur = torch.tensor([1 % nbuf] * S, dtype=torch.int32)
+    meta, gf, n_, _ = make_meta(K, slots, groups, [10] * S)
+    sd, cd = dev(state.clone()), dev(conv_state.clone())
+    out = torch.zeros(n, P, device="cuda")
+    K.call("fb_gdn_fused", dev(proj), ld, dev(fb), dev(gb), P, dev(conv_w), dev(a_log), dev(dt_bias), dev(o_norm),
+           sd, cd, dev(cur), meta, gf, len(groups), out, P, H, dk, b_off, nbuf, snap, -5.0, 1e-5)
+    r0 = 0
+    for gi, g in enumerate(groups):
+        c = int(cur[gi])
+        rows = slice(r0, r0 + g)
+        co, tail = R.causal_conv1d(proj[rows, :3 * P], conv_w, conv_state[gi, c])
+        co = torch.nn.functional.silu(co)
+        q, k, v = (co[:, i * P:(i + 1) * P].reshape(g, H, dk) for i in range(3))
+        q, k = R.l2norm_heads(q) * dk ** -0.5, R.l2norm_heads(k)
+        beta = torch.sigmoid(proj[rows, b_off:b_off + H])
+        gl = R.gdn_log_decay(fb[rows], dt_bias, a_log, -5.0, H)
+        core, s_new = R.gdn_recurrent(q, k, v, beta, gl, state[gi, c])
+        want = R.gated_rmsnorm(core, gb[rows].view(g, H, dk), o_norm, 1e-5).reshape(g, P)
+        check(f"gdn out g{gi}", out[rows], want, 2e-4)
+        wb = (c + g) % nbuf if (snap and nbuf > 1) else c
+        check(f"gdn state g{gi}", sd[gi, wb], s_new, 2e-4)
+        check(f"gdn conv g{gi}", cd[gi, wb], tail, 1e-6)
+        if snap and nbuf > 1:
+            _, s1 = R.gdn_recurrent(q[:1], k[:1], v[:1], beta[:1], gl[:1], state[gi, c])
+            check(f"gdn snap0 g{gi}", sd[gi, (c + 1) % nbuf], s1, 2e-4)
+            check(f"gdn untouched g{gi}", sd[gi, c], state[gi, c], 0)
+        r0 += g
+
+
+@pytest.mark.parametrize("E,topk", [(8, 2), (288, 8)])
+def test_moe_route(K, E, topk):
+    n = 6
+    logits = rnd(n, E, seed=1)
+    logits[0, 3] = logits[0, 5]  # a tie resolves to the lower index
+    bias = rnd(E, seed=2, scale=0.1)
+    ids = torch.zeros(n, topk, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n, topk, device="cuda")
+    K.call("fb_moe_route", dev(logits), dev(bias), ids, wts, n, E, topk, 2.5)
+    w_ref, i_ref = R.moe_route(logits, bias, topk, 2.5)
+    assert torch.equal(ids.cpu().long(), i_ref), (ids.cpu(), i_ref)
+    check("route w", wts, w_ref, 1e-5)
+
+
+@pytest.mark.parametrize("n,E,topk,I,H", [(1, 8, 2, 128, 256), (3, 16, 8, 256, 4096), (2, 6, 3, 2048, 512)])
+def test_moe_experts_fp8(K, n, E, topk, I, H):
+    g = torch.Generator().manual_seed(7)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    q13, s13 = zip(*[R.quant_fp8_block(w13[e]) for e in range(E)])
+    q2, s2 = zip(*[R.quant_fp8_block(w2[e]) for e in range(E)])
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+    x = torch.randn(n, H, generator=g)
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(n)]).int()
+    wts = torch.rand(n, topk, generator=g)
+    act = torch.zeros(n, topk, I, device="cuda")
+    out = torch.ones(n, H, device="cuda")
+    K.call("fb_moe_gate_up_fp8", dev(q13), dev(s13), dev(x), H, dev(ids), act, n, topk, I, H, 0, E, 10.0)
+    K.call("fb_moe_down_fp8", dev(q2), dev(s2), act, dev(ids), dev(wts), out, H, n, topk, I, H, 0, E, 1)
+    want = torch.ones(n, H)
+    act_ref = torch.zeros(n, topk, I)
+    for r in range(n):
+        for s in range(topk):
+            e = int(ids[r, s])
+            W13 = R.dequant_fp8_block(q13[e], s13[e])
+            a = R.swiglu_limited(x[r] @ W13[:I].t(), x[r] @ W13[I:].t(), 10.0)
+            act_ref[r, s] = a
+            want[r] += wts[r, s] * (a @ R.dequant_fp8_block(q2[e], s2[e]).t())
+    check("moe act", act, act_ref, 2e-3)
+    check("moe out", out, want, 5e-3)
+    # expert-parallel masking: experts outside [e_lo, e_lo+cnt) contribute nothing
+    lo, cnt = E // 2, E - E // 2
+    out2 = torch.zeros(n, H, device="cuda")
+    K.call("fb_moe_gate_up_fp8", dev(q13[lo:]), dev(s13[lo:]), dev(x), H, dev(ids), act, n, topk, I, H, lo, cnt, 10.0)
+    K.call("fb_moe_down_fp8", dev(q2[lo:]), dev(s2[lo:]), act, dev(ids), dev(wts), out2, H, n, topk, I, H, lo, cnt, 0)
+    want2 = torch.zeros(n, H)
+    for r in range(n):
+        for s in range(topk):
+            e = int(ids[r, s])
+            if e >= lo:
+                want2[r] += wts[r, s] * (act_ref[r, s] @ R.dequant_fp8_block(q2[e], s2[e]).t())
+    check("moe ep", out2, want2, 5e-3)
+
+
+def test_swiglu(K):
+    n, I = 3, 300
+    gu = rnd(n, 2 * I, seed=1, scale=8.0)
+    act = torch.zeros(n, I, device="cuda")
+    K.call("fb_swiglu", dev(gu), 2 * I, act, n, I, 10.0)
+    check("swiglu", act, R.swiglu_limited(gu[:, :I], gu[:, I:], 10.0), 1e-5)
+
+
+def test_argmax_and_accept(K):
+    n, V = 4, 154880
+    logits = rnd(n, V, seed=1)
+    logits[1, 77] = logits[1, 9000] = 50.0
+    ids = torch.zeros(n, dtype=torch.int32, device="cuda")
+    vals = torch.zeros(n, device="cuda")
+    part = torch.zeros(n * 64, dtype=torch.int64, device="cuda")
+    K.call("fb_argmax", dev(logits), V, part, ids, vals, n, V, 1, 0)
+    assert ids.cpu().tolist() == R.argmax_first(logits).tolist()
+    check("argmax vals", vals, logits.max(-1).values, 0)
+    H, nv, nbuf = 64, 3, 4
+    for drafts, judges, k in (([5, 6], [5, 6, 7], 3), ([5, 6], [5, 9, 7], 2), ([5, 6], [1, 6, 7], 1)):
+        blk = torch.tensor([11] + drafts, dtype=torch.int32, device="cuda")
+        jd = torch.tensor(judges, dtype=torch.int32, device="cuda")
+        out = torch.zeros(nv + 1, dtype=torch.int32, device="cuda")
+        hf = dev(rnd(nv, H, seed=2))
+        mtp_ids = torch.zeros(2, dtype=torch.int32, device="cuda")
+        mtp_h = dev(rnd(2, H, seed=3))
+        old1 = mtp_h[1].clone()
+        gslot = torch.zeros(1, dtype=torch.int32, device="cuda")
+        main_len = torch.tensor([100], dtype=torch.int32, device="cuda")
+        mtp_len = torch.tensor([101], dtype=torch.int32, device="cuda")
+        cur = torch.tensor([3], dtype=torch.int32, device="cuda")
+        K.call("fb_mtp_accept", blk, jd, out, hf, mtp_ids, mtp_h, gslot, main_len, mtp_len, cur, 1, nv, H, nbuf)
+        torch.cuda.synchronize()
+        assert out.tolist() == [k] + judges[:k] + [-1] * (nv - k)
+        assert main_len.item() == 100 + k and mtp_len.item() == 98 + k and cur.item() == (3 + k) % nbuf
+        assert blk[0].item() == judges[k - 1]
+        assert mtp_ids.tolist() == [([11] + drafts)[k - 1], judges[k - 1]]
+        check("mtp_h1", mtp_h[1], hf[k - 1], 0)
+        check("mtp_h0", mtp_h[0], old1 if k == 1 else hf[k - 2], 0)
+
+
+def _dsa_setup(K, n_groups_rows, ctx0, kpool, page, ID, IH, DL, max_pages, kv_f32, seed=0):
+    """Fill a paged cache for one slot with `ctx0` tokens then append the group's rows."""
+    g = torch.Generator().manual_seed(seed)
+    total = ctx0 + n_groups_rows
+    lat = torch.randn(total, DL, generator=g)
+    kidx = torch.randn(total, ID, generator=g)
+    kgate = torch.randn(total, ID, generator=g)
+    num_pages = max_pages
+    perm = torch.randperm(num_pages, generator=g).int()  # scattered physical pages
+    pt = perm.view(1, max_pages).contiguous()
+    return lat, kidx, kgate, pt, total
+
+
+@pytest.mark.parametrize("ctx0,n,kpool,select_max", [(0, 7, 4, 8), (37, 3, 4, 4), (200, 1, 4, 16), (41, 2, 2, 64),
+                                                      (5000, 3, 4, 512)])
+def test_dsa_pool_scores_select(K, ctx0, n, kpool, select_max):
+    page, ID, IH, DL = 16, 32, 4, 64
+    total = ctx0 + n
+    max_pages = (total + page - 1) // page + 2
+    lat, kidx, kgate, pt, _ = _dsa_setup(K, n, ctx0, kpool, page, ID, IH, DL, max_pages, True, seed=ctx0 + n)
+    g = torch.Generator().manual_seed(99)
+    ape = torch.randn(kpool, ID, generator=g)
+    qi = torch.randn(n, IH, ID, generator=g)
+    wi = torch.rand(n, IH, generator=g)
+    # physical caches
+    kidx_c = torch.zeros(max_pages, page, ID)
+    kgate_c = torch.zeros(max_pages, page, ID)
+    for t in range(total):
+        pg = int(pt[0, t // page])
+        kidx_c[pg, t % page] = kidx[t]
+        kgate_c[pg, t % page] = kgate[t]
+    pool_c = torch.zeros(max_pages, page // kpool, ID, device="cuda")
+    ptd = dev(pt)
+    # pools of the cached prefix are filled by "prefill" rows: one forward over all tokens
+    meta_all, _, _, _ = make_meta(K, [0], [total], [0])
+    K.call("fb_dsa_pool", dev(kidx_c), dev(kgate_c), dev(ape), pool_c, meta_all, ptd, max_pages, page, total, ID, kpool)
+    want_pools = R.kpool_compress(kidx, kgate, ape, kpool)
+    npools = want_pools.shape[0]
+    got_pools = torch.stack([pool_c[int(pt[0, p // (page // kpool)]), p % (page // kpool)] for p in range(npools)])
+    check("pool keys", got_pools, want_pools, 1e-5)
+    meta, gf, n_, _ = make_meta(K, [0], [n], [ctx0])
+    max_pools = npools + 3
+    scores = torch.zeros(n, max_pools, device="cuda")
+    K.call("fb_dsa_scores", dev(qi.reshape(n, -1)), IH * ID, dev(wi), pool_c, scores, max_pools, meta, ptd, max_pages,
+           page, n, IH, ID, kpool, max_pools)
+    s_ref = R.indexer_scores(qi, want_pools, wi)
+    for i in range(n):
+        nvis = min(npools, ctx0 // kpool + i + 1)
+        check(f"scores row {i}", scores[i, :nvis], s_ref[i, :nvis], 1e-4)
+    # selection is exact on the device's own scores
+    W = select_max * kpool + kpool + 3
+    idx = torch.full((n, W), -7, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(n, dtype=torch.int32, device="cuda")
+    K.call("fb_dsa_select", scores, max_pools, idx, W, cnt, meta, n, kpool, select_max)
+    sc = scores.cpu()
+    for i in range(n):
+        nvis = min(npools, ctx0 // kpool + i + 1)
+        select_k = min(select_max, npools)
+        s = torch.full((npools,), float("-inf"))
+        s[:nvis] = sc[i, :nvis]
+        order = torch.sort(s, descending=True, stable=True).indices[:select_k]
+        pools = torch.tensor([int(p) if s[p] != float("-inf") else -1 for p in order]).view(1, -1)
+        # expand_pool_indices takes ctx0 of row 0; a single row at offset i is ctx0 + i
+        ref = R.expand_pool_indices(pools, kpool, ctx0 + i, total, select_k * kpool + kpool - 1)
+        want = sorted(set(int(t) for t in ref[0] if t >= 0))
+        got = idx[i, :int(cnt[i])].cpu().tolist()
+        assert got == want, f"row {i}: got {got[:12]}... ({len(got)}) want {want[:12]}... ({len(want)})"
+
+
+@pytest.mark.parametrize("hl,DL,kv_f32,ntok,nshard", [(4, 64, 1, 37, 1), (3, 64, 0, 5, 1), (64, 512, 0, 300, 1),
+                                                      (8, 512, 1, 70, 1), (4, 64, 1, 90, 2), (16, 512, 0, 130, 4)])
+def test_dsa_attention(K, hl, DL, kv_f32, ntok, nshard):
+    page, n = 16, 2
+    T = 400
+    max_pages = T // page
+    g = torch.Generator().manual_seed(hl + DL + ntok)
+    lat = torch.randn(T, DL, generator=g)
+    if not kv_f32:
+        lat = lat.bfloat16().float()
+    pt = torch.randperm(max_pages, generator=g).int().view(1, max_pages)
+    cache = torch.zeros(max_pages, page, DL)
+    for t in range(T):
+        cache[int(pt[0, t // page]), t % page] = lat[t]
+    cache_d = dev(cache if kv_f32 else cache.bfloat16())
+    qabs = torch.randn(n, hl, DL, generator=g) * 0.3
+    W = ntok + 8
+    idx = torch.full((n, W), -1, dtype=torch.int32)
+    cnt = torch.tensor([ntok, max(1, ntok // 2)], dtype=torch.int32)
+    for i in range(n):
+        idx[i, :int(cnt[i])] = torch.randperm(T, generator=g)[:int(cnt[i])].int()
+    meta, _, _, _ = make_meta(K, [0], [n], [T - n])
+    scale = 0.11
+    nsplit = 4
+    parts_o, parts_ml = [], []
+    for sh in range(nshard):
+        o_part = torch.zeros(n, nsplit, hl, DL, device="cuda")
+        ml = torch.zeros(n, nsplit, hl, 2, device="cuda")
+        K.call("fb_dsa_attn_partial", dev(qabs.reshape(n, -1)), cache_d, dev(idx), W, dev(cnt), o_part, ml, meta,
+               dev(pt), max_pages, page, n, hl, DL, nsplit, sh, nshard, scale, kv_f32)
+        ctx = torch.zeros(n, hl, DL, device="cuda")
+        lse = torch.zeros(n, hl, 2, device="cuda")
+        K.call("fb_dsa_attn_merge", o_part, ml, ctx, lse, n, hl, DL, nsplit, 1 if nshard == 1 else 0)
+        parts_o.append(ctx)
+        parts_ml.append(lse)
+    if nshard > 1:  # cross-shard merge is the same merge over [n, nshard, hl, *]
+        o_all = torch.stack(parts_o, 1).contiguous()
+        ml_all = torch.stack(parts_ml, 1).contiguous()
+        ctx = torch.zeros(n, hl, DL, device="cuda")
+        K.call("fb_dsa_attn_merge", o_all, ml_all, ctx, None, n, hl, DL, nshard, 1)
+    want = torch.zeros(n, hl, DL)
+    for i in range(n):
+        ids = idx[i, :int(cnt[i])].long()
+        s = torch.einsum("hd,td->ht", qabs[i], lat[ids]) * scale
+        p = torch.softmax(s, -1)
+        want[i] = p @ lat[ids]
+    check("dsa attn", ctx, want, 2e-4)
