@@ -92,6 +92,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--profile", action="store_true",
+                    help="open the CUDA profiler window around the timed device loop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -156,9 +158,14 @@ def main():
         time.sleep(0.3)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profile:
+        torch.cuda.profiler.start()
     e0.record()
     run_device_loop(args.steps)
     e1.record()
+    if args.profile:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     barrier()
     ms = e0.elapsed_time(e1)
     tokens = int(m.main_len[0].item()) - len0

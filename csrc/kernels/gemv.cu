@@ -101,6 +101,114 @@ gemv_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
         }
 }
 
+
+// Split-K form for K >= 1024: a CTA owns RB consecutive weight rows, its 8 warps take
+// interleaved 512-byte slabs of K, and an x fragment is reused for all RB rows.  There are
+// N/RB CTAs whatever K is, so mid-size matrices (N = 4096) still fill 148 SMs, and every lane
+// keeps RB 16-byte weight loads in flight per step.
+template <int M, int RB, bool FP8>
+__global__ void __launch_bounds__(kWarps * 32)
+gemv_splitk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
+                   const float* __restrict__ x, int ldx, float* __restrict__ out, int ldo,
+                   int mrows, int N, int K, int accumulate) {
+    constexpr int VEC = FP8 ? 16 : 8;
+    constexpr int ESZ = FP8 ? 1 : 2;
+    __shared__ float red[kWarps][M * RB];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = blockIdx.x * RB;
+    const int kblocks = (K + 127) >> 7;
+    float acc[M][RB];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < RB; ++r) acc[m][r] = 0.f;
+    const uint8_t* wrow[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) wrow[r] = W + (size_t)min(n0 + r, N - 1) * K * ESZ;
+    const float* srow = FP8 ? scales + (size_t)(n0 >> 7) * kblocks : nullptr;
+
+#pragma unroll 2
+    for (int k = (warp * 32 + lane) * VEC; k < K; k += kWarps * 32 * VEC) {
+        uint4 wv[RB];
+#pragma unroll
+        for (int r = 0; r < RB; ++r) wv[r] = ldg_nc_v4(wrow[r] + (size_t)k * ESZ);
+        float xv[M][VEC];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (m < mrows) {
+#pragma unroll
+                for (int v = 0; v < VEC; v += 4) {
+                    float4 t = __ldg(reinterpret_cast<const float4*>(x + (size_t)m * ldx + k + v));
+                    xv[m][v] = t.x; xv[m][v + 1] = t.y; xv[m][v + 2] = t.z; xv[m][v + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) xv[m][v] = 0.f;
+            }
+        }
+        float sc = 1.f;
+        if (FP8) sc = __ldg(srow + (k >> 7));
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            float wf[VEC];
+            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv[r]);
+            if (FP8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) e4m3x4_to_f32(pw[i], &wf[4 * i]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    float p = 0.f;
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) p = fmaf(wf[v], xv[m][v], p);
+                    acc[m][r] = fmaf(p, sc, acc[m][r]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { wf[2 * i] = bf16lo(pw[i]); wf[2 * i + 1] = bf16hi(pw[i]); }
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[m][r] = fmaf(wf[v], xv[m][v], acc[m][r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            const float v = warp_sum(acc[m][r]);
+            if (lane == 0) red[warp][m * RB + r] = v;
+        }
+    __syncthreads();
+    if (threadIdx.x < M * RB) {
+        const int m = threadIdx.x / RB, r = threadIdx.x % RB;
+        if (m < mrows && n0 + r < N) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) v += red[w][threadIdx.x];
+            float* o = out + (size_t)m * ldo + n0 + r;
+            *o = accumulate ? (*o + v) : v;
+        }
+    }
+}
+
+template <int M, int RB, bool FP8>
+int launch_sk(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo, int mrows,
+              int N, int K, int accumulate, cudaStream_t st) {
+    dim3 grid((N + RB - 1) / RB), block(kWarps * 32);
+    gemv_splitk_kernel<M, RB, FP8><<<grid, block, 0, st>>>(static_cast<const uint8_t*>(W), scales, x, ldx, out, ldo,
+                                                            mrows, N, K, accumulate);
+    return FB_LAUNCH_CHECK();
+}
+
+template <int M, bool FP8>
+int launch_sk_rb(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo, int mrows,
+                 int N, int K, int accumulate, cudaStream_t st) {
+    if (N >= 2368) return launch_sk<M, 8, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+    if (N >= 592) return launch_sk<M, 4, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+    return launch_sk<M, 2, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+}
+
 template <int M, bool FP8>
 int launch_r(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo,
              int mrows, int N, int K, int group_rows, int accumulate, cudaStream_t st) {
@@ -119,6 +227,15 @@ int launch_r(const void* W, const float* scales, const float* x, int ldx, float*
 template <bool FP8>
 int launch_m(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo,
              int mrows, int N, int K, int group_rows, int accumulate, cudaStream_t st) {
+    if (group_rows == 0 && K >= 1024) {
+        switch (mrows) {
+            case 1: return launch_sk_rb<1, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+            case 2: return launch_sk_rb<2, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+            case 3: return launch_sk_rb<3, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+            case 4: return launch_sk_rb<4, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+            default: return launch_sk<8, 4, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
+        }
+    }
     if (mrows <= 1) return launch_r<1, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
     if (mrows <= 2) return launch_r<2, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);
     if (mrows <= 4) return launch_r<4, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate, st);

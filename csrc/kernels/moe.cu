@@ -21,7 +21,7 @@ __device__ __forceinline__ uint32_t okey(float f) {
 
 // One block (256 threads) per row; E <= 1024.
 __global__ void __launch_bounds__(256)
-moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int* __restrict__ ids,
                  float* __restrict__ wts, int E, int topk, float scaling) {
     __shared__ unsigned long long wbest[8];
     __shared__ unsigned long long s_pick;
@@ -34,7 +34,7 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
         const int e = threadIdx.x + i * 256;
         key[i] = 0ull;
         if (e < E) {
-            const float s = 1.f / (1.f + expf(-logits[(size_t)r * E + e]));
+            const float s = 1.f / (1.f + expf(-logits[(size_t)r * ld + e]));
             s_sig[e] = s;
             key[i] = ((unsigned long long)okey(s + bias[e]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)e);
         }
@@ -215,10 +215,10 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __res
 
 }  // namespace
 
-FB_API int fb_moe_route(const float* logits, const float* bias, int* ids, float* wts, int64_t n, int64_t E,
-                        int64_t topk, float scaling, cudaStream_t st) {
+FB_API int fb_moe_route(const float* logits, int64_t ld, const float* bias, int* ids, float* wts, int64_t n,
+                        int64_t E, int64_t topk, float scaling, cudaStream_t st) {
     if (E > 1024 || topk > 32) return (int)cudaErrorInvalidValue;
-    moe_route_kernel<<<n, 256, 0, st>>>(logits, bias, ids, wts, (int)E, (int)topk, scaling);
+    moe_route_kernel<<<n, 256, 0, st>>>(logits, (int)ld, bias, ids, wts, (int)E, (int)topk, scaling);
     return FB_LAUNCH_CHECK();
 }
 
@@ -244,8 +244,8 @@ FB_API int fb_moe_down_fp8(const void* W2, const float* S2, const float* act, co
                            float* out, int64_t ldo, int64_t n, int64_t topk, int64_t I, int64_t H,
                            int64_t e_lo, int64_t e_cnt, int64_t accumulate, cudaStream_t st) {
     if (I % 16) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned)((H + 15) / 16), (unsigned)n);
-    moe_down_fp8_kernel<2><<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, act, ids, wts, out, (int)ldo, (int)topk,
+    dim3 grid((unsigned)((H + 31) / 32), (unsigned)n);
+    moe_down_fp8_kernel<4><<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, act, ids, wts, out, (int)ldo, (int)topk,
                                                   (int)I, (int)H, (int)e_lo, (int)e_cnt, (int)accumulate);
     return FB_LAUNCH_CHECK();
 }

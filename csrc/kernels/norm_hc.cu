@@ -5,9 +5,9 @@
 //   pre_i = sigmoid(mix_i*s0 + b_i) + eps;  post_i = 2 sigmoid(mix_{4+i}*s1 + b_{4+i})
 //   comb = Sinkhorn_20(softmax_rows(mix_{8..}*s2 + b_{8..}) + eps)
 //   x = sum_i pre_i R_i  -> rmsnorm -> sublayer -> y;   R'_i = post_i*y + sum_k comb[k][i] R_k
-// Here the site is three launches: hc_mix (split-K partial dots with atomics),
-// hc_pre_apply (coefficients by one warp, contraction and the following RMSNorm fused), and
-// hc_post.  Replaces hc_pre_fuse/hc_pre/hc_post/hc_pre_mix_split/hc_pre_rest345/hc_contract
+// Here a site is two launches: hc_post_mix (the previous site's hc_post fused with this
+// site's split-K mix dots, accumulated with atomics) and hc_pre_apply (coefficients by one
+// warp, contraction and the following RMSNorm fused).  Replaces hc_pre_fuse/hc_pre/hc_post/hc_pre_mix_split/hc_pre_rest345/hc_contract
 // (kernels/cuda/ferrite_kernels.cu:2370-2679,8001-8451).
 #include "common.cuh"
 
@@ -99,61 +99,110 @@ __global__ void mtp_prep_kernel(const int* __restrict__ ids, const __nv_bfloat16
         out[(size_t)r * 2 * H + (size_t)half * H + j] = buf[j] * inv * w[j];
 }
 
-constexpr int kMixSplit = 16;
 constexpr int kMaxMix = 24;
+constexpr int kMixGroups = 4;   // the mix rows are split over blockIdx.z
+constexpr int kPmThreads = 128; // one float4 column of R per thread -> 512 columns per CTA
 
-// acc[r][0..mix) += fn[:, slice] . R[r][slice];  acc[r][mix] += sum(R[r][slice]^2)
-__global__ void __launch_bounds__(256)
-hc_mix_kernel(const float* __restrict__ R, const float* __restrict__ fn, float* __restrict__ acc,
-              int D, int mix) {
-    __shared__ float red[8][kMaxMix + 1];
-    const int r = blockIdx.x / kMixSplit, s = blockIdx.x % kMixSplit;
-    const int per = (D + kMixSplit - 1) / kMixSplit;
-    const int lo = s * per, hi = min(D, lo + per);
-    const float* row = R + (size_t)r * D;
-    float part[kMaxMix + 1];
+// Fused hc_post of one site and hc_mix of the next (n == 4 residual copies):
+//   if y:  Rout[r][i][j] = post[r][i]*y[r][j] + sum_k comb[r][k][i] Rin[r][k][j]
+//   if fn: acc[r][m] += sum_{i,j} fn[m][i*H + j] * R'[r][i][j];  acc[r][24] += sum R'^2
+// grid = (ceil(H/512), n, kMixGroups); every z recomputes R' for its columns (cheap), z == 0
+// writes it and owns the sum of squares.  With a mix (several z) Rout must not alias Rin:
+// the other z blocks still read Rin.
+__global__ void __launch_bounds__(kPmThreads)
+hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, const float* __restrict__ post,
+                   const float* __restrict__ comb, const float* __restrict__ fn, float* __restrict__ acc,
+                   int H, int mix) {
+    __shared__ float red[kPmThreads / 32][8];
+    const int r = blockIdx.y, z = blockIdx.z;
+    const int j = (blockIdx.x * kPmThreads + threadIdx.x) * 4;
+    const bool act = j < H;
+    const float* row = Rin + (size_t)r * 4 * H;
+    float* orow = Rout + (size_t)r * 4 * H;
+    float4 v[4];
 #pragma unroll
-    for (int j = 0; j <= kMaxMix; ++j) part[j] = 0.f;
-    for (int k = lo + threadIdx.x * 4; k < hi; k += blockDim.x * 4) {
-        float4 v = *reinterpret_cast<const float4*>(row + k);
-        part[kMaxMix] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    for (int k = 0; k < 4; ++k) v[k] = act ? *reinterpret_cast<const float4*>(row + (size_t)k * H + j) : make_float4(0, 0, 0, 0);
+    if (y) {
+        const float4 yy = act ? *reinterpret_cast<const float4*>(y + (size_t)r * H + j) : make_float4(0, 0, 0, 0);
+        float p[4], c[16];
 #pragma unroll
-        for (int j = 0; j < kMaxMix; ++j) {
-            if (j < mix) {
-                float4 f = __ldg(reinterpret_cast<const float4*>(fn + (size_t)j * D + k));
-                part[j] += v.x * f.x + v.y * f.y + v.z * f.z + v.w * f.w;
+        for (int i = 0; i < 4; ++i) p[i] = post[r * 4 + i];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) c[i] = comb[r * 16 + i];
+        float4 o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[i].x = p[i] * yy.x; o[i].y = p[i] * yy.y; o[i].z = p[i] * yy.z; o[i].w = p[i] * yy.w;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float ck = c[k * 4 + i];
+                o[i].x += ck * v[k].x; o[i].y += ck * v[k].y; o[i].z += ck * v[k].z; o[i].w += ck * v[k].w;
             }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = o[i];
+            if (act && z == 0) *reinterpret_cast<float4*>(orow + (size_t)i * H + j) = o[i];
+        }
+    }
+    if (!fn) return;
+    const int per = (mix + kMixGroups - 1) / kMixGroups;  // <= 6
+    const int m0 = z * per;
+    float part[7];
+#pragma unroll
+    for (int q = 0; q < 7; ++q) part[q] = 0.f;
+    if (act) {
+#pragma unroll
+        for (int q = 0; q < 6; ++q) {
+            const int m = m0 + q;
+            if (q < per && m < mix) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 f = __ldg(reinterpret_cast<const float4*>(fn + (size_t)m * 4 * H + (size_t)i * H + j));
+                    part[q] += v[i].x * f.x + v[i].y * f.y + v[i].z * f.z + v[i].w * f.w;
+                }
+            }
+        }
+        if (z == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) part[6] += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
         }
     }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int j = 0; j <= kMaxMix; ++j) {
-        float v = warp_sum(part[j]);
-        if (lane == 0) red[wid][j] = v;
+    for (int q = 0; q < 7; ++q) {
+        const float s = warp_sum(part[q]);
+        if (lane == 0) red[wid][q] = s;
     }
     __syncthreads();
-    if (threadIdx.x <= kMaxMix) {
-        const int j = threadIdx.x;
-        if (j < mix || j == kMaxMix) {
-            float v = 0.f;
-            for (int w = 0; w < 8; ++w) v += red[w][j];
-            atomicAdd(acc + (size_t)r * (kMaxMix + 1) + j, v);
-        }
+    if (threadIdx.x < 7) {
+        const int q = threadIdx.x;
+        float s = 0.f;
+        for (int w = 0; w < kPmThreads / 32; ++w) s += red[w][q];
+        float* a = acc + (size_t)r * (kMaxMix + 1);
+        if (q == 6) { if (z == 0) atomicAdd(a + kMaxMix, s); }
+        else if (q < per && m0 + q < mix) atomicAdd(a + m0 + q, s);
     }
 }
 
-// One block per row.  Warp 0 turns the accumulated mixes into (pre, post, comb); all threads
-// then form x = sum_i pre_i R_i and the fused RMSNorm.  The accumulator is cleared for reuse.
-__global__ void __launch_bounds__(512)
+// One block per row, one float4 column per thread (H/4 <= 1024 threads).  The residual
+// loads are issued before the barrier so they overlap warp 0's coefficient math; the
+// accumulator is cleared for reuse.
+__global__ void __launch_bounds__(1024)
 hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
                     const float* __restrict__ base, const float* __restrict__ ln_w,
                     float* __restrict__ x_out, float* __restrict__ xn_out, float* __restrict__ post_out,
                     float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters) {
-    extern __shared__ float sh[];
-    float* red = sh;        // 32
-    float* pre = sh + 32;   // 8
-    float* xb = sh + 40;    // H
+    __shared__ float red[32];
+    __shared__ float pre[8];
     const int r = blockIdx.x;
+    const float* row = R + (size_t)r * n * H;
+    const int j = threadIdx.x * 4;
+    const bool act = j < H;
+    float4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = act ? *reinterpret_cast<const float4*>(row + (size_t)k * H + j) : make_float4(0, 0, 0, 0);
+    const float4 lw = act ? *reinterpret_cast<const float4*>(ln_w + j) : make_float4(0, 0, 0, 0);
     float* a = acc + (size_t)r * (kMaxMix + 1);
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
@@ -164,69 +213,44 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
         }
         // comb element (i = lane / n, k = lane % n); n == 4 so rows are 4-lane groups
         float c = 0.f;
-        const bool act = lane < n * n;
-        if (act) c = a[2 * n + lane] * rr * scale[2] + base[2 * n + lane];
-        float mx = act ? c : -INFINITY;
+        const bool on = lane < n * n;
+        if (on) c = a[2 * n + lane] * rr * scale[2] + base[2 * n + lane];
+        float mx = on ? c : -INFINITY;
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        float e = act ? __expf(c - mx) : 0.f;
+        float e = on ? __expf(c - mx) : 0.f;
         float den = e + __shfl_xor_sync(0xffffffffu, e, 1);
         den += __shfl_xor_sync(0xffffffffu, den, 2);
-        c = act ? e / den + hc_eps : 0.f;
+        c = on ? e / den + hc_eps : 0.f;
         float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
         cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-        c = c / (cs + hc_eps);
+        c = __fdividef(c, cs + hc_eps);
         for (int it = 1; it < iters; ++it) {
             float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
             rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-            c = c / (rs + hc_eps);
+            c = __fdividef(c, rs + hc_eps);
             cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
             cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-            c = c / (cs + hc_eps);
+            c = __fdividef(c, cs + hc_eps);
         }
-        if (act) comb_out[(size_t)r * n * n + lane] = c;
+        if (on) comb_out[(size_t)r * n * n + lane] = c;
         __syncwarp();
         if (lane <= kMaxMix) a[lane] = 0.f;
     }
     __syncthreads();
-    const float* row = R + (size_t)r * n * H;
-    float ss = 0.f;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        float v = 0.f;
-        for (int i = 0; i < n; ++i) v += pre[i] * row[(size_t)i * H + j];
-        xb[j] = v;
-        ss += v * v;
-    }
+    float4 x;
+    x.x = pre[0] * v[0].x + pre[1] * v[1].x + pre[2] * v[2].x + pre[3] * v[3].x;
+    x.y = pre[0] * v[0].y + pre[1] * v[1].y + pre[2] * v[2].y + pre[3] * v[3].y;
+    x.z = pre[0] * v[0].z + pre[1] * v[1].z + pre[2] * v[2].z + pre[3] * v[3].z;
+    x.w = pre[0] * v[0].w + pre[1] * v[1].w + pre[2] * v[2].w + pre[3] * v[3].w;
+    float ss = act ? x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w : 0.f;
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / H + rms_eps);
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        float v = xb[j];
-        if (x_out) x_out[(size_t)r * H + j] = v;
-        xn_out[(size_t)r * H + j] = v * inv * ln_w[j];
-    }
-}
-
-// In place: R[r][i][j] = post[r][i]*y[r][j] + sum_k comb[r][k][i] R[r][k][j]   (n == 4)
-__global__ void hc_post_kernel(float* __restrict__ R, const float* __restrict__ y,
-                               const float* __restrict__ post, const float* __restrict__ comb, int H) {
-    const int r = blockIdx.y;
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= H) return;
-    float p[4], c[16], v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) p[i] = post[r * 4 + i];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) c[i] = comb[r * 16 + i];
-    float* row = R + (size_t)r * 4 * H;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = row[(size_t)k * H + j];
-    const float yy = y[(size_t)r * H + j];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float o = p[i] * yy;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) o += c[k * 4 + i] * v[k];
-        row[(size_t)i * H + j] = o;
+    if (act) {
+        if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)r * H + j) = x;
+        float4 o;
+        o.x = x.x * inv * lw.x; o.y = x.y * inv * lw.y; o.z = x.z * inv * lw.z; o.w = x.w * inv * lw.w;
+        *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
     }
 }
 
@@ -297,28 +321,34 @@ FB_API int fb_mtp_prep(const int* ids, const void* emb, const float* h_prev, con
 }
 
 // acc is [n, 25] f32 and must be zero on entry; fb_hc_pre_apply clears it again.
+// y == nullptr skips the post update, fn == nullptr skips the mix.
+FB_API int fb_hc_post_mix(const float* Rin, float* Rout, const float* y, const float* post, const float* comb,
+                          const float* fn, float* acc, int64_t n, int64_t H, int64_t mix, cudaStream_t st) {
+    if (mix > kMaxMix || (H % 4) || (y && fn && Rin == Rout)) return (int)cudaErrorInvalidValue;
+    dim3 grid((unsigned)((H / 4 + kPmThreads - 1) / kPmThreads), (unsigned)n, fn ? kMixGroups : 1);
+    hc_post_mix_kernel<<<grid, kPmThreads, 0, st>>>(Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
+    return FB_LAUNCH_CHECK();
+}
+
 FB_API int fb_hc_mix(const float* R, const float* fn, float* acc, int64_t n, int64_t D, int64_t mix,
                      cudaStream_t st) {
-    if (mix > kMaxMix || (D % (4 * kMixSplit))) return (int)cudaErrorInvalidValue;
-    hc_mix_kernel<<<n * kMixSplit, 256, 0, st>>>(R, fn, acc, (int)D, (int)mix);
-    return FB_LAUNCH_CHECK();
+    return fb_hc_post_mix(R, nullptr, nullptr, nullptr, nullptr, fn, acc, n, D / 4, mix, st);
 }
 
 FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const float* base,
                            const float* ln_w, float* x_out, float* xn_out, float* post_out, float* comb_out,
                            int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
                            cudaStream_t st) {
-    if (mult != 4) return (int)cudaErrorInvalidValue;
-    size_t sm = (40 + H) * sizeof(float);
-    hc_pre_apply_kernel<<<n, 512, sm, st>>>(R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
-                                            (int)H, (int)mult, rms_eps, hc_eps, (int)iters);
+    if (mult != 4 || (H % 4) || H / 4 > 1024) return (int)cudaErrorInvalidValue;
+    const int threads = (int)(((H / 4) + 31) / 32 * 32);
+    hc_pre_apply_kernel<<<n, threads, 0, st>>>(R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
+                                               (int)H, (int)mult, rms_eps, hc_eps, (int)iters);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_hc_post(float* R, const float* y, const float* post, const float* comb, int64_t n, int64_t H,
                       cudaStream_t st) {
-    hc_post_kernel<<<dim3((H + 255) / 256, n), 256, 0, st>>>(R, y, post, comb, (int)H);
-    return FB_LAUNCH_CHECK();
+    return fb_hc_post_mix(R, R, y, post, comb, nullptr, nullptr, n, H, 0, st);
 }
 
 FB_API int fb_hc_head(const float* R, const float* w, float* h_final, float* xn, int64_t n, int64_t H,

@@ -124,8 +124,8 @@ class GlmDeviceModel:
         cat = torch.cat([self._sh(src, f"{a}.qkv_proj.weight").float(), src.get(f"{a}.f_a_proj.weight").float(),
                          src.get(f"{a}.g_a_proj.weight").float(), self._sh(src, f"{a}.b_proj.weight").float()], 0)
         L["w_in"] = self._bf(cat)
-        L["f_b"] = self._bf(self._sh(src, f"{a}.f_b_proj.weight"))
-        L["g_b"] = self._bf(self._sh(src, f"{a}.g_b_proj.weight"))
+        L["fg_b"] = self._bf(torch.cat([self._sh(src, f"{a}.f_b_proj.weight").float(),
+                                        self._sh(src, f"{a}.g_b_proj.weight").float()], 0))
         L["conv_w"] = self._f(self._sh(src, f"{a}.qkv_conv1d.weight"))
         L["a_log"] = self._f(self._sh(src, f"{a}.A_log"))
         L["dt_bias"] = self._f(self._sh(src, f"{a}.dt_bias"))
@@ -168,14 +168,13 @@ class GlmDeviceModel:
     def _pack_mlp_moe(self, src, pfx, L):
         cfg = self.cfg
         E, Er = cfg.n_routed_experts, self.E_res
-        L["gate"] = self._bf(src.get(f"{pfx}.mlp.gate.weight"))
         bias = self._f(src.get(f"{pfx}.mlp.gate.e_score_correction_bias")).clone()
         if Er < E:
             bias[Er:] = -1e30  # experts that are not resident can never be routed to
         L["gate_bias"] = bias
         sg = self._sh(src, f"{pfx}.mlp.shared_expert.gate_proj.weight").float()
         su = self._sh(src, f"{pfx}.mlp.shared_expert.up_proj.weight").float()
-        L["s13"] = self._bf(torch.cat([sg, su], 0))
+        L["gate_s13"] = self._bf(torch.cat([src.get(f"{pfx}.mlp.gate.weight").float(), sg, su], 0))
         L["s2"] = self._bf(self._sh(src, f"{pfx}.mlp.shared_expert.down_proj.weight"))
         L["I_shared"] = sg.shape[0]
         Il = cfg.moe_intermediate_size // self.world
@@ -241,7 +240,9 @@ class GlmDeviceModel:
         cfg, la, ds, M = self.cfg, self.cfg.linear_attn, self.cfg.dsa, self.max_rows
         H = cfg.hidden_size
         ws = {}
-        ws["R"] = self._z(M, cfg.hc_mult, H)
+        ws["R0"] = self._z(M, cfg.hc_mult, H)
+        ws["R1"] = self._z(M, cfg.hc_mult, H)
+        ws["R"] = ws["R0"]
         ws["x"] = self._z(M, H)        # sublayer input (normed)
         ws["y"] = self._z(M, H)        # sublayer output
         ws["res"] = self._z(M, H)      # plain residual (MTP layer)
@@ -251,8 +252,7 @@ class GlmDeviceModel:
         self.ld_gdn = 3 * self.P + 2 * la.low_rank + self.h_gdn
         self.ld_gdn += (-self.ld_gdn) % 4
         ws["gdn_proj"] = self._z(M, self.ld_gdn)
-        ws["gdn_fb"] = self._z(M, self.P)
-        ws["gdn_gb"] = self._z(M, self.P)
+        ws["gdn_fg"] = self._z(M, 2 * self.P)
         ws["gdn_core"] = self._z(M, self.P)
         self.ld_dsa = ds.q_lora_rank + ds.kv_lora_rank + 2 * ds.index_head_dim + ds.index_n_heads
         ws["dsa_proj"] = self._z(M, self.ld_dsa + (-self.ld_dsa) % 4)
@@ -265,7 +265,7 @@ class GlmDeviceModel:
         ws["dsa_scores"] = self._z(M, self.max_pools)
         ws["dsa_idx"] = self._z(M, ds.idx_width + ds.index_kpool, dtype=torch.int32)
         ws["dsa_cnt"] = self._z(M, dtype=torch.int32)
-        self.nsplit = 8 if self.h_dsa * ds.kv_lora_rank >= 4096 else 2
+        self.nsplit = 32 if self.h_dsa * ds.kv_lora_rank >= 4096 else 2
         ws["dsa_opart"] = self._z(M, self.nsplit, self.h_dsa, ds.kv_lora_rank)
         ws["dsa_ml"] = self._z(M, self.nsplit, self.h_dsa, 2)
         ws["dsa_ctx"] = self._z(M, self.h_dsa * ds.kv_lora_rank)
@@ -273,7 +273,8 @@ class GlmDeviceModel:
         Imax = max([L.get("I_dense", 0) for L in self.layers] + [L.get("I_shared", 0) for L in self.layers] + [1])
         ws["gu"] = self._z(M, 2 * Imax)
         ws["act"] = self._z(M, Imax)
-        ws["moe_logits"] = self._z(M, cfg.n_routed_experts)
+        Ismax = max([L.get("I_shared", 0) for L in self.layers] + [1])
+        ws["moe_lg"] = self._z(M, cfg.n_routed_experts + 2 * Ismax)
         ws["moe_ids"] = self._z(M, cfg.num_experts_per_tok, dtype=torch.int32)
         ws["moe_wts"] = self._z(M, cfg.num_experts_per_tok)
         Il = max([L.get("I_moe", 0) for L in self.layers] + [1])
@@ -351,10 +352,9 @@ class GlmDeviceModel:
         H, P, r = cfg.hidden_size, self.P, la.low_rank
         proj = ws["gdn_proj"]
         self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, ldo=self.ld_gdn)
-        self.gemv(L["f_b"], View(proj, 3 * P), ws["gdn_fb"], n, P, r, ldx=self.ld_gdn)
-        self.gemv(L["g_b"], View(proj, 3 * P + r), ws["gdn_gb"], n, P, r, ldx=self.ld_gdn)
+        self.gemv(L["fg_b"], View(proj, 3 * P), ws["gdn_fg"], n, 2 * P, r, ldx=self.ld_gdn, group_rows=P)
         gi = L["gdn_index"]
-        self.K.call("fb_gdn_fused", proj, self.ld_gdn, ws["gdn_fb"], ws["gdn_gb"], P, L["conv_w"], L["a_log"],
+        self.K.call("fb_gdn_fused", proj, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"], L["a_log"],
                     L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
                     rs.group_first, rs.n_groups, ws["gdn_core"], P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
                     self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps))
@@ -404,12 +404,11 @@ class GlmDeviceModel:
         cfg, ws = self.cfg, self.ws
         H, E, topk = cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok
         Il, Is = L["I_moe"], L["I_shared"]
-        self.gemv(L["gate"], ws["x"], ws["moe_logits"], n, E, H)
-        self.K.call("fb_moe_route", ws["moe_logits"], L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
+        ldl = ws["moe_lg"].shape[1]
+        self.gemv(L["gate_s13"], ws["x"], ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
+        self.K.call("fb_moe_route", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
                     float(cfg.routed_scaling_factor))
-        ldg = ws["gu"].shape[1]
-        self.gemv(L["s13"], ws["x"], ws["gu"], n, 2 * Is, H, ldo=ldg)
-        self.K.call("fb_swiglu", ws["gu"], ldg, ws["act"], n, Is, float(cfg.swiglu_limit))
+        self.K.call("fb_swiglu", View(ws["moe_lg"], E), ldl, ws["act"], n, Is, float(cfg.swiglu_limit))
         self.gemv(L["s2"], ws["act"], ws["y"], n, H, Is)
         self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], ws["x"], H, ws["moe_ids"], ws["moe_act"], n, topk, Il,
                     H, 0, self.E_res, float(cfg.swiglu_limit))
@@ -429,13 +428,25 @@ class GlmDeviceModel:
         else:
             self._ffn_dense(L, n)
 
-    def _hc_site(self, L, site, ln, n):
+    def _hc_pre(self, L, site, ln, n):
+        """Coefficients + contraction + RMSNorm of one site; its mix dots are already in hc_acc."""
         cfg, ws = self.cfg, self.ws
-        H, m = cfg.hidden_size, cfg.hc_mult
-        self.K.call("fb_hc_mix", ws["R"], L[f"hc_{site}_fn"], ws["hc_acc"], n, m * H, cfg.hc_mix)
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
-                    ws["x"], ws["post"], ws["comb"], n, H, m, float(cfg.rms_norm_eps), float(cfg.hc_eps),
-                    cfg.hc_sinkhorn_iters)
+                    ws["x"], ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
+                    float(cfg.hc_eps), cfg.hc_sinkhorn_iters)
+
+    def _hc_post_mix(self, fn_next, n, first=False):
+        """hc_post of the finished site fused with the mix dots of the next one; the residual
+        stream ping-pongs between two buffers because the mix blocks re-read the old one."""
+        cfg, ws = self.cfg, self.ws
+        rin = ws["R"]
+        rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
+        if first:
+            self.K.call("fb_hc_post_mix", rin, rin, None, None, None, fn_next, ws["hc_acc"], n, cfg.hidden_size, cfg.hc_mix)
+            return
+        self.K.call("fb_hc_post_mix", rin, rout, ws["y"], ws["post"], ws["comb"], fn_next, ws["hc_acc"], n,
+                    cfg.hidden_size, cfg.hc_mix)
+        ws["R"] = rout
 
     # ------------------------------------------------------------------ passes
     def main_forward(self, rs: RowSet, ids: torch.Tensor, snapshots: bool = False, advance: bool = True,
@@ -446,16 +457,20 @@ class GlmDeviceModel:
         cfg, ws, n, K = self.cfg, self.ws, rs.n, self.K
         H = cfg.hidden_size
         K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.main_len, rs.meta, n)
+        ws["R"] = ws["R0"]
         K.call("fb_embed_expand", ids, self.embed, ws["R"], n, H, cfg.hc_mult, cfg.vocab_size)
-        for L in self.layers[:cfg.num_layers]:
-            self._hc_site(L, "attn", L["ln1"], n)
+        ws["R"] = ws["R0"]
+        main = self.layers[:cfg.num_layers]
+        self._hc_post_mix(main[0]["hc_attn_fn"], n, first=True)
+        for li, L in enumerate(main):
+            self._hc_pre(L, "attn", L["ln1"], n)
             self._attn(L, rs, snapshots)
-            K.call("fb_hc_post", ws["R"], ws["y"], ws["post"], ws["comb"], n, H)
+            self._hc_post_mix(L["hc_ffn_fn"], n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "attn", ws, n)
-            self._hc_site(L, "ffn", L["ln2"], n)
+            self._hc_pre(L, "ffn", L["ln2"], n)
             self._ffn(L, n)
-            K.call("fb_hc_post", ws["R"], ws["y"], ws["post"], ws["comb"], n, H)
+            self._hc_post_mix(main[li + 1]["hc_attn_fn"] if li + 1 < len(main) else None, n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "ffn", ws, n)
         K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], ws["xh"], n, H, cfg.hc_mult, float(cfg.rms_norm_eps))

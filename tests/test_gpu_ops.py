@@ -106,8 +106,18 @@ def test_hc_chain(K, H):
     check("hc comb", comb.view(n, 4, 4), cr, 1e-5)
     check("hc xn", xn, R.rmsnorm(xr, ln, 1e-5), 1e-4)
     assert acc.abs().max().item() == 0.0, "accumulator must be cleared for reuse"
+    # fused hc_post + next-site mix into a second buffer, then the in-place stand-alone form
+    R2 = torch.zeros_like(Rd)
+    fn2 = rnd(mix, mult * H, seed=12, scale=0.05)
+    K.call("fb_hc_post_mix", Rd, R2, dev(y), post, comb, dev(fn2), acc, n, H, mix)
+    Rn = R.hc_post(y, Rr, pr, cr)
+    check("hc_post fused", R2, Rn, 1e-4)
+    flat = Rn.reshape(n, -1)
+    check("mix fused", acc[:, :mix], flat @ fn2.t(), 2e-3)
+    check("sumsq fused", acc[:, 24], flat.pow(2).sum(-1), 1e-2, rtol=1e-4)
+    acc.zero_()
     K.call("fb_hc_post", Rd, dev(y), post, comb, n, H)
-    check("hc_post", Rd, R.hc_post(y, Rr, pr, cr), 1e-4)
+    check("hc_post", Rd, Rn, 1e-4)
     hf, xh = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
     K.call("fb_hc_head", dev(Rr), dev(ln), hf, xh, n, H, mult, 1e-5)
     check("hc_head", hf, Rr.mean(1), 1e-5)
@@ -181,7 +191,7 @@ def test_moe_route(K, E, topk):
     bias = rnd(E, seed=2, scale=0.1)
     ids = torch.zeros(n, topk, dtype=torch.int32, device="cuda")
     wts = torch.zeros(n, topk, device="cuda")
-    K.call("fb_moe_route", dev(logits), dev(bias), ids, wts, n, E, topk, 2.5)
+    K.call("fb_moe_route", dev(logits), E, dev(bias), ids, wts, n, E, topk, 2.5)
     w_ref, i_ref = R.moe_route(logits, bias, topk, 2.5)
     assert torch.equal(ids.cpu().long(), i_ref), (ids.cpu(), i_ref)
     check("route w", wts, w_ref, 1e-5)
