@@ -1,0 +1,198 @@
+#!/usr/bin/env python
+"""Per-kernel micro-benchmarks at GLM-5.3-Flash decode shapes, against the HBM roofline.
+
+Each case runs one kernel entry point on weights that rotate through enough distinct
+copies to exceed the 126 MB L2, is timed with CUDA events after warm-up, and is reported as
+algorithmic bytes / time and as a fraction of the measured copy bandwidth
+(MEASURED_PEAKS.json `hbm_gbs`, fallback 6650 GB/s).
+
+  python bench_kernels.py                 # all cases, one table
+  python bench_kernels.py --only moe_down # one case (the form used under ncu)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch  # noqa: E402
+
+from ferrite_b200 import _lib  # noqa: E402
+
+
+def hbm_peak_gbs() -> tuple:
+    p = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "of measured"
+    return 6650.0, "of fallback"
+
+
+def split_buf(x: torch.Tensor) -> torch.Tensor:
+    M, K = x.shape
+    sp = torch.zeros(4, M, K, dtype=torch.int16, device=x.device)
+    bh = x.bfloat16(); bl = (x - bh.float()).bfloat16()
+    hh = x.half(); hl = (x - hh.float()).half()
+    for i, t in enumerate((bh, bl, hh, hl)):
+        sp[i] = t.view(torch.int16)
+    return sp
+
+
+def fp8_rand(*shape):
+    return (torch.randn(*shape, device="cuda", dtype=torch.bfloat16) * 100).to(torch.float8_e4m3fn)
+
+
+class Case:
+    def __init__(self, name, nbytes, fn, note=""):
+        self.name, self.nbytes, self.fn, self.note = name, nbytes, fn, note
+
+
+def make_cases(K, only):
+    cases = []
+    dev = "cuda"
+
+    def want(name):
+        return only is None or only in name
+
+    def gemv_case(name, N, Kd, m, fp8=False, mma=True):
+        if not want(name):
+            return
+        esz = 1 if fp8 else 2
+        reps = max(2, int(300e6 // (N * Kd * esz)) + 1)
+        x = torch.randn(m, Kd, device=dev)
+        xs = split_buf(x)
+        out = torch.zeros(m, N, device=dev)
+        if fp8:
+            ws = [fp8_rand(N, Kd) for _ in range(reps)]
+            sc = torch.rand((N + 127) // 128, (Kd + 127) // 128, device=dev) * 1e-3
+        else:
+            ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) for _ in range(reps)]
+        state = {"i": 0}
+
+        def fn():
+            w = ws[state["i"] % reps]
+            state["i"] += 1
+            if mma:
+                if fp8:
+                    K.call("fb_gemv_mma_fp8", w, sc, xs, Kd, m * Kd, out, N, m, N, Kd, 0, None, 0, 0, 0)
+                else:
+                    K.call("fb_gemv_mma_bf16", w, xs, Kd, m * Kd, out, N, m, N, Kd, 0, 0, None, 0, 0, 0)
+            else:
+                if fp8:
+                    K.call("fb_gemv_fp8", w, sc, x, Kd, out, N, m, N, Kd, 0, 0)
+                else:
+                    K.call("fb_gemv_bf16", w, x, Kd, out, N, m, N, Kd, 0, 0)
+        cases.append(Case(name, N * Kd * esz, fn, f"N={N} K={Kd} m={m}"))
+
+    gemv_case("gemv_mma_bf16.lm_head.m1", 154880, 4096, 1)
+    gemv_case("gemv_mma_bf16.lm_head.m3", 154880, 4096, 3)
+    gemv_case("gemv_simt_bf16.lm_head.m3", 154880, 4096, 3, mma=False)
+    gemv_case("gemv_mma_bf16.gdn_in.m3", 24896, 4096, 3)
+    gemv_case("gemv_mma_bf16.gdn_o_proj.m3", 4096, 8192, 3)
+    gemv_case("gemv_simt_bf16.gdn_o_proj.m3", 4096, 8192, 3, mma=False)
+    gemv_case("gemv_mma_bf16.dsa_o_proj.m3", 4096, 16384, 3)
+    gemv_case("gemv_mma_bf16.dsa_q.m3", 20480, 1536, 3)
+    gemv_case("gemv_mma_bf16.router_shared.m3", 4384, 4096, 3)
+    gemv_case("gemv_mma_bf16.shared_down.m3", 4096, 2048, 3)
+    gemv_case("gemv_mma_fp8.dense_gate_up.m3", 24576, 4096, 3, fp8=True)
+    gemv_case("gemv_mma_fp8.dense_down.m3", 4096, 12288, 3, fp8=True)
+    gemv_case("gemv_simt_fp8.dense_down.m3", 4096, 12288, 3, fp8=True, mma=False)
+
+    # ---- MoE experts: 3 rows x 8 slots, experts drawn from a pool larger than L2 ----------
+    for tag, I, H in (("tp1", 2048, 4096), ("tp8", 256, 4096)):
+        if not (want("moe_gate_up") or want("moe_down")):
+            break
+        E, n, topk = (40 if I == 2048 else 320), 3, 8
+        w13 = fp8_rand(E, 2 * I, H)
+        s13 = torch.rand(E, 2 * I // 128, H // 128, device=dev) * 1e-3
+        w2 = fp8_rand(E, H, I)
+        s2 = torch.rand(E, H // 128, I // 128, device=dev) * 1e-3
+        x = torch.randn(n, H, device=dev)
+        xs = split_buf(x)
+        asp = torch.zeros(4, n * topk, I, dtype=torch.int16, device=dev)
+        act = torch.zeros(n, topk, I, device=dev)
+        out = torch.zeros(n, H, device=dev)
+        wts = torch.rand(n, topk, device=dev)
+        idsets = [torch.randperm(E, device=dev)[:n * topk].int().view(n, topk).contiguous() for _ in range(8)]
+        st = {"i": 0}
+
+        def gu(I=I, H=H, w13=w13, s13=s13, xs=xs, asp=asp, idsets=idsets, st=st, wts=wts):
+            ids = idsets[st["i"] % 8]; st["i"] += 1
+            K.call("fb_moe_gate_up_mma", w13, s13, xs, H, n * H, ids, wts, asp, I, n * topk * I, n, topk, I, H, 0, E, 10.0)
+
+        def dn(I=I, H=H, w2=w2, s2=s2, asp=asp, idsets=idsets, st=st, out=out):
+            ids = idsets[st["i"] % 8]; st["i"] += 1
+            K.call("fb_moe_down_mma", w2, s2, asp, I, n * topk * I, ids, out, H, n, topk, I, H, 0, E, 0, None, 0, 0, 0)
+
+        def gu_simt(I=I, H=H, w13=w13, s13=s13, x=x, act=act, idsets=idsets, st=st):
+            ids = idsets[st["i"] % 8]; st["i"] += 1
+            K.call("fb_moe_gate_up_fp8", w13, s13, x, H, ids, act, n, topk, I, H, 0, E, 10.0)
+
+        def dn_simt(I=I, H=H, w2=w2, s2=s2, act=act, idsets=idsets, st=st, out=out, wts=wts):
+            ids = idsets[st["i"] % 8]; st["i"] += 1
+            K.call("fb_moe_down_fp8", w2, s2, act, ids, wts, out, H, n, topk, I, H, 0, E, 0)
+
+        if want("moe_gate_up"):
+            cases.append(Case(f"moe_gate_up_mma.{tag}", n * topk * 2 * I * H, gu, f"24 experts I={I}"))
+            cases.append(Case(f"moe_gate_up_simt.{tag}", n * topk * 2 * I * H, gu_simt, f"24 experts I={I}"))
+        if want("moe_down"):
+            cases.append(Case(f"moe_down_mma.{tag}", n * topk * I * H, dn, f"24 experts I={I}"))
+            cases.append(Case(f"moe_down_simt.{tag}", n * topk * I * H, dn_simt, f"24 experts I={I}"))
+
+    # ---- MHC site -----------------------------------------------------------------------
+    if want("hc_"):
+        n, H, mix = 3, 4096, 24
+        R0, R1 = torch.randn(n, 4, H, device=dev), torch.zeros(n, 4, H, device=dev)
+        fns = [torch.randn(mix, 4 * H, device=dev) * 0.02 for _ in range(100)]
+        acc = torch.zeros(n, 25, device=dev)
+        y = torch.randn(n, H, device=dev)
+        post, comb = torch.rand(n, 4, device=dev), torch.rand(n, 16, device=dev)
+        scale, base, ln = torch.ones(3, device=dev), torch.zeros(mix, device=dev), torch.ones(H, device=dev)
+        xn = torch.zeros(n, H, device=dev)
+        sp = torch.zeros(4, n, H, dtype=torch.int16, device=dev)
+        st = {"i": 0}
+
+        def pm():
+            f = fns[st["i"] % 100]; st["i"] += 1
+            K.call("fb_hc_post_mix", R0, R1, y, post, comb, f, acc, n, H, mix)
+
+        def pa():
+            K.call("fb_hc_pre_apply", R1, acc, scale, base, ln, None, xn, post, comb, n, H, 4, 1e-5, 1e-6, 20, sp, H, n * H, 3)
+        cases.append(Case("hc_post_mix.m3", mix * 4 * H * 4 + 2 * n * 4 * H * 4, pm, "fn 1.5 MB f32"))
+        cases.append(Case("hc_pre_apply.m3", n * 4 * H * 4, pa, "latency-bound"))
+    return cases
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--json", default=None)
+    args = ap.parse_args()
+    K = _lib.lib()
+    peak, tag = hbm_peak_gbs()
+    rows = []
+    for c in make_cases(K, args.only):
+        for _ in range(args.warmup):
+            c.fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            c.fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.iters
+        gbs = c.nbytes / us / 1e3
+        rows.append({"kernel": c.name, "us": round(us, 2), "MB": round(c.nbytes / 1e6, 1), "GB/s": round(gbs, 0),
+                     "frac": round(gbs / peak, 3), "note": c.note})
+        print(f"{c.name:38s} {us:9.2f} us  {c.nbytes / 1e6:8.1f} MB  {gbs:7.0f} GB/s  {gbs / peak:5.2f} {tag}  {c.note}")
+    if args.json:
+        json.dump({"hbm_peak_gbs": peak, "peak_kind": tag, "rows": rows}, open(args.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -78,7 +78,7 @@ __device__ __forceinline__ void e4m3x4_to_f32(uint32_t w, float* o) {
 
 __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
     uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
     return r;
 }

@@ -10,6 +10,7 @@
 // layernorm_affine, sparse_attn_v2*, sparse_attn_*_split, sparse_attn_merge
 // (kernels/cuda/ferrite_kernels.cu:1557-2296,6465-7871).
 #include "common.cuh"
+#include "mma_gemv.cuh"
 
 namespace {
 
@@ -35,7 +36,8 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
                 const float* __restrict__ kv_ln, const float* __restrict__ kn_w,
                 const float* __restrict__ kn_b, float* __restrict__ qa_out, float* __restrict__ wi_out,
                 KVT* __restrict__ lat_cache, float* __restrict__ kidx_cache, float* __restrict__ kgate_cache,
-                const RowMeta* __restrict__ meta, PageView pv, int QL, int DL, int ID, int IH, float eps) {
+                const RowMeta* __restrict__ meta, PageView pv, int QL, int DL, int ID, int IH, float eps,
+                SplitBuf osp) {
     __shared__ float red[32];
     const int r = blockIdx.x;
     const RowMeta m = meta[r];
@@ -46,7 +48,11 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
     for (int j = threadIdx.x; j < QL; j += blockDim.x) ss += p[j] * p[j];
     ss = block_sum(ss, red);
     float inv = rsqrtf(ss / QL + eps);
-    for (int j = threadIdx.x; j < QL; j += blockDim.x) qa_out[(size_t)r * QL + j] = p[j] * inv * qa_ln[j];
+    for (int j = threadIdx.x; j < QL; j += blockDim.x) {
+        const float o = p[j] * inv * qa_ln[j];
+        qa_out[(size_t)r * QL + j] = o;
+        split_store(osp, r, j, o);
+    }
     // latent RMSNorm -> cache
     const float* pl = p + QL;
     ss = 0.f;
@@ -296,9 +302,13 @@ dsa_attn_partial_kernel(const float* __restrict__ qabs, const KVT* __restrict__ 
     const int lo = sp * per, hi = min(n_tok, lo + per);
     const int tid = threadIdx.x;
 
-    for (int i = tid; i < hl * DL; i += 256) {
-        const int h = i / DL, d = i % DL;
-        q_s[h * QS + d] = qabs[((size_t)r * hl + h) * DL + d];
+    {
+        const float4* q4 = reinterpret_cast<const float4*>(qabs + (size_t)r * hl * DL);
+#pragma unroll 8
+        for (int i = tid; i < hl * DL / 4; i += 256) {
+            const int h = (i * 4) / DL, d = (i * 4) % DL;
+            *reinterpret_cast<float4*>(q_s + h * QS + d) = __ldg(q4 + i);
+        }
     }
     const int t_l = tid % kTT, hg = tid / kTT;  // score phase: token lane, head group
     float mrun[HPT], lrun[HPT];
@@ -424,7 +434,7 @@ dsa_attn_partial_kernel(const float* __restrict__ qabs, const KVT* __restrict__ 
 // ctx[r][h][:] = sum_s o_s e^{m_s - M} / (sum_s l_s e^{m_s - M} + eps_f32); optional lse out.
 __global__ void dsa_attn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                       float* __restrict__ ctx, float* __restrict__ lse_out, int hl, int DL,
-                                      int nsplit, int normalise) {
+                                      int nsplit, int normalise, SplitBuf osp) {
     const int r = blockIdx.y, h = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(((size_t)r * nsplit + s) * hl + h) * 2]);
@@ -441,6 +451,7 @@ __global__ void dsa_attn_merge_kernel(const float* __restrict__ o_part, const fl
             if (ms != -INFINITY) o += o_part[(((size_t)r * nsplit + s) * hl + h) * DL + d] * __expf(ms - M);
         }
         ctx[((size_t)r * hl + h) * DL + d] = o * inv;
+        split_store(osp, r, h * DL + d, o * inv);
     }
     if (lse_out && threadIdx.x == 0) {
         lse_out[((size_t)r * hl + h) * 2] = M;
@@ -460,14 +471,16 @@ FB_API int fb_dsa_prep(const float* proj, int64_t ld, const float* qa_ln, const 
                        const float* kn_w, const float* kn_b, float* qa_out, float* wi_out, void* lat_cache,
                        float* kidx_cache, float* kgate_cache, const void* meta, const int* page_table,
                        int64_t max_pages, int64_t page_size, int64_t n, int64_t QL, int64_t DL, int64_t ID,
-                       int64_t IH, float eps, int64_t kv_f32, cudaStream_t st) {
+                       int64_t IH, float eps, int64_t kv_f32, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
+                       cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     PageView pv = make_pv(page_table, max_pages, page_size);
     if (kv_f32)
         dsa_prep_kernel<float><<<n, 512, 0, st>>>(proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
-            (float*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps);
+            (float*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     else
         dsa_prep_kernel<__nv_bfloat16><<<n, 512, 0, st>>>(proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
-            (__nv_bfloat16*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps);
+            (__nv_bfloat16*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 
@@ -542,8 +555,10 @@ FB_API int fb_dsa_attn_partial(const float* qabs, const void* lat_cache, const i
 }
 
 FB_API int fb_dsa_attn_merge(const float* o_part, const float* ml_part, float* ctx, float* lse_out, int64_t n,
-                             int64_t hl, int64_t DL, int64_t nsplit, int64_t normalise, cudaStream_t st) {
+                             int64_t hl, int64_t DL, int64_t nsplit, int64_t normalise, void* s_base, int64_t s_ld,
+                             int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     dsa_attn_merge_kernel<<<dim3((unsigned)hl, (unsigned)n), 128, 0, st>>>(o_part, ml_part, ctx, lse_out, (int)hl,
-                                                                           (int)DL, (int)nsplit, (int)normalise);
+                                                                           (int)DL, (int)nsplit, (int)normalise, osp);
     return FB_LAUNCH_CHECK();
 }

@@ -15,6 +15,7 @@
 // Replaces gdn_step_v2/v2p, gdn_chunk_batched, gdn_chunk_fused, gdn_prep, conv1d*,
 // conv_prep_fused, gated_rmsnorm (ferrite_kernels.cu:345-1042,2743-2850,10123-10415).
 #include "common.cuh"
+#include "mma_gemv.cuh"
 
 namespace {
 
@@ -26,7 +27,8 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
                  const float* __restrict__ o_norm_w, float* __restrict__ state,
                  float* __restrict__ conv_state, const int* __restrict__ cur,
                  const RowMeta* __restrict__ meta, const int* __restrict__ group_first,
-                 float* __restrict__ out, int ld_out, int H, int b_off, int nbuf, int snapshots, float lb, float eps) {
+                 float* __restrict__ out, int ld_out, int H, int b_off, int nbuf, int snapshots, float lb, float eps,
+                 SplitBuf osp) {
     constexpr int RPT = DK / 4;  // state rows per thread
     __shared__ float qs[DK], ks[DK], vs[DK], dec[DK];
     __shared__ float part[4][DK];
@@ -134,7 +136,9 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
         if (rg == 0) {
             const float inv = rsqrtf(tot / DK + eps);
             const float gate = sigmoidf_(gb[(size_t)r * ld_fg + h * DK + c]);
-            out[(size_t)r * ld_out + h * DK + c] = o * inv * o_norm_w[c] * gate;
+            const float ov = o * inv * o_norm_w[c] * gate;
+            out[(size_t)r * ld_out + h * DK + c] = ov;
+            split_store(osp, r, h * DK + c, ov);
         }
         const bool last = (i == gsize - 1);
         if ((snapshots && nbuf > 1) || last) {
@@ -161,10 +165,11 @@ FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, con
                         const float* o_norm_w, float* state, float* conv_state, const int* cur,
                         const void* meta, const int* group_first, int64_t n_groups, float* out,
                         int64_t ld_out, int64_t H, int64_t dk, int64_t b_off, int64_t nbuf, int64_t snapshots, float lb,
-                        float eps, cudaStream_t st) {
+                        float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     dim3 grid((unsigned)H, (unsigned)n_groups);
 #define GDN_ARGS proj, (int)ld_proj, fb, gb, (int)ld_fg, conv_w, a_log, dt_bias, o_norm_w, state, conv_state, cur, \
-        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps
+        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps, osp
     if (dk == 128) gdn_fused_kernel<128><<<grid, 512, 0, st>>>(GDN_ARGS);
     else if (dk == 64) gdn_fused_kernel<64><<<grid, 256, 0, st>>>(GDN_ARGS);
     else if (dk == 32) gdn_fused_kernel<32><<<grid, 128, 0, st>>>(GDN_ARGS);

@@ -12,6 +12,7 @@
 // Replaces the reference's gemv_bf16_v2/_mrows/_nt, gemv_tri, gemv_fp8_v2 and the DSV41
 // gemm_fp8_gemv/mrows families (kernels/cuda/ferrite_kernels.cu:3016-3785,10650-11275).
 #include "common.cuh"
+#include "mma_gemv.cuh"
 
 namespace {
 
@@ -209,6 +210,108 @@ int launch_sk_rb(const void* W, const float* scales, const float* x, int ldx, fl
     return launch_sk<M, 2, FP8>(W, scales, x, ldx, out, ldo, mrows, N, K, accumulate, st);
 }
 
+
+// ---- tensor-core form (see mma_gemv.cuh) ---------------------------------------------------
+// A CTA owns 16*RT weight rows; its NW warps take interleaved k-blocks (64 bf16 / 128 e4m3
+// elements) with the next block's weight loads in flight while the current block is
+// multiplied; partial D tiles are summed across warps through shared memory.
+template <int RT, int NW, bool FP8>
+__global__ void __launch_bounds__(NW * 32)
+gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
+                const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
+                float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,
+                SplitBuf osplit) {
+    constexpr int KB = FP8 ? 128 : 64;
+    constexpr int XW = FP8 ? 16 : 8;
+    __shared__ float red[NW][RT][32][4];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16 * RT;
+    const int nkb = K / KB;
+    const int kblocks = (K + 127) >> 7;
+    if (group_rows > 0) { const size_t go = (size_t)(n0 / group_rows) * K; xhi += go; xlo += go; }
+    float acc[RT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) { acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f; }
+    const uint8_t* wa[RT];
+    const uint8_t* wb[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        const size_t esz = FP8 ? 1 : 2;
+        wa[r] = W + (size_t)min(n0 + r * 16 + g, N - 1) * K * esz + (size_t)t * 32;
+        wb[r] = W + (size_t)min(n0 + r * 16 + g + 8, N - 1) * K * esz + (size_t)t * 32;
+    }
+    WFrag cur[RT], nxt[RT];
+    if (warp < nkb) {
+#pragma unroll
+        for (int r = 0; r < RT; ++r) cur[r] = load_wfrag(wa[r] + (size_t)warp * 128, wb[r] + (size_t)warp * 128);
+    }
+    for (int kb = warp; kb < nkb; kb += NW) {
+        const int kn = kb + NW;
+        if (kn < nkb) {
+#pragma unroll
+            for (int r = 0; r < RT; ++r) nxt[r] = load_wfrag(wa[r] + (size_t)kn * 128, wb[r] + (size_t)kn * 128);
+        }
+        uint32_t xh[XW], xl[XW];
+        load_xfrag<XW>(xhi, xlo, ldx, g, mrows, kb * KB + t * (KB / 4), xh, xl);
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+            if (FP8) {
+                float d[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_wfrag_fp8(d, cur[r], reinterpret_cast<const uint32_t(&)[16]>(xh), reinterpret_cast<const uint32_t(&)[16]>(xl));
+                const float sc = __ldg(scales + (size_t)((n0 + r * 16) >> 7) * kblocks + kb);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(d[c], sc, acc[r][c]);
+            } else {
+                mma_wfrag_bf16(acc[r], cur[r], reinterpret_cast<const uint32_t(&)[8]>(xh), reinterpret_cast<const uint32_t(&)[8]>(xl));
+            }
+        }
+        if (kn < nkb) {
+#pragma unroll
+            for (int r = 0; r < RT; ++r) cur[r] = nxt[r];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) red[warp][r][lane][c] = acc[r][c];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < RT * 128; idx += NW * 32) {
+        const int r = idx >> 7, l = (idx & 127) >> 2, c = idx & 3;
+        const int row = n0 + r * 16 + (l >> 2) + 8 * (c >> 1);
+        const int col = 2 * (l & 3) + (c & 1);
+        if (col < mrows && row < N) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) v += red[w][r][l][c];
+            float* o = out + (size_t)col * ldo + row;
+            if (accumulate) v += *o;
+            *o = v;
+            split_store(osplit, col, row, v);
+        }
+    }
+}
+
+template <bool FP8>
+int launch_mma(const void* W, const float* scales, const uint16_t* xs, int ldx, int plane, float* out, int ldo,
+               int mrows, int N, int K, int group_rows, int accumulate, SplitBuf osplit, cudaStream_t st) {
+    const uint16_t* hi = xs + (FP8 ? 2 * (size_t)plane : 0);
+    const uint16_t* lo = hi + plane;
+    const uint8_t* w8 = static_cast<const uint8_t*>(W);
+    constexpr int KB = FP8 ? 128 : 64;
+    const int nkb = K / KB;
+    if (N >= 9472 && (group_rows == 0 || group_rows % 32 == 0)) {
+        gemv_mma_kernel<2, 8, FP8><<<(N + 31) / 32, 256, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+    } else if (nkb >= 64 && N <= 8192) {  // few row tiles, long rows: split K over 16 warps
+        gemv_mma_kernel<1, 16, FP8><<<(N + 15) / 16, 512, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+    } else if (nkb >= 8) {
+        gemv_mma_kernel<1, 8, FP8><<<(N + 15) / 16, 256, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+    } else {
+        gemv_mma_kernel<1, 2, FP8><<<(N + 15) / 16, 64, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+    }
+    return FB_LAUNCH_CHECK();
+}
+
 template <int M, bool FP8>
 int launch_r(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo,
              int mrows, int N, int K, int group_rows, int accumulate, cudaStream_t st) {
@@ -260,4 +363,42 @@ FB_API int fb_gemv_fp8(const void* W, const float* scales, const float* x, int64
                        int64_t accumulate, cudaStream_t st) {
     if (m < 1 || m > 8 || (K % 16) || (ldx % 4)) return (int)cudaErrorInvalidValue;
     return launch_m<true>(W, scales, x, (int)ldx, out, (int)ldo, (int)m, (int)N, (int)K, (int)group_rows, (int)accumulate, st);
+}
+
+// Tensor-core forms.  xs is a split-activation buffer (planes bf16 hi/lo, f16 hi/lo of
+// `xs_plane` elements, row stride xs_ld); bf16 weights read planes 0/1, e4m3 weights read
+// planes 2/3.  K must be a multiple of 64 (bf16) / 128 (e4m3); m <= 8.  When os_base is
+// given the result is also written in split form (os_mask picks the plane pairs).
+FB_API int fb_gemv_mma_bf16(const void* W, const void* xs, int64_t xs_ld, int64_t xs_plane, float* out,
+                            int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t group_rows, int64_t accumulate,
+                            void* os_base, int64_t os_ld, int64_t os_plane, int64_t os_mask, cudaStream_t st) {
+    if (m < 1 || m > 8 || (K % 64) || (xs_ld % 8) || (group_rows % 16)) return (int)cudaErrorInvalidValue;
+    SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
+    return launch_mma<false>(W, nullptr, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
+                             (int)K, (int)group_rows, (int)accumulate, os, st);
+}
+
+FB_API int fb_gemv_mma_fp8(const void* W, const float* scales, const void* xs, int64_t xs_ld, int64_t xs_plane,
+                           float* out, int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t accumulate,
+                           void* os_base, int64_t os_ld, int64_t os_plane, int64_t os_mask, cudaStream_t st) {
+    if (m < 1 || m > 8 || (K % 128) || (xs_ld % 8)) return (int)cudaErrorInvalidValue;
+    SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
+    return launch_mma<true>(W, scales, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
+                            (int)K, 0, (int)accumulate, os, st);
+}
+
+namespace {
+__global__ void split_rows_kernel(const float* __restrict__ x, int ldx, SplitBuf s, int K) {
+    const int r = blockIdx.y;
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < K) split_store(s, r, k, x[(size_t)r * ldx + k]);
+}
+}  // namespace
+
+// Stand-alone f32 -> split conversion (producers normally emit the split form themselves).
+FB_API int fb_split_rows(const float* x, int64_t ldx, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
+                         int64_t m, int64_t K, cudaStream_t st) {
+    SplitBuf s{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    split_rows_kernel<<<dim3((unsigned)((K + 255) / 256), (unsigned)m), 256, 0, st>>>(x, (int)ldx, s, (int)K);
+    return FB_LAUNCH_CHECK();
 }

@@ -11,6 +11,7 @@
 // moe_fused_act(_fp8), moe_fused_down_sum(_fp8), moe_weighted_sum, swiglu/swiglu2
 // (kernels/cuda/ferrite_kernels.cu:392-421,1207-1300,2977,4021-4499).
 #include "common.cuh"
+#include "mma_gemv.cuh"
 
 namespace {
 
@@ -204,13 +205,157 @@ moe_down_fp8_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
     }
 }
 
-__global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __restrict__ act, int I, float limit) {
+
+// ---- tensor-core forms (see mma_gemv.cuh) --------------------------------------------------
+// gate/up: a CTA owns 16 gate rows and the matching 16 up rows of one (row, slot) pair's
+// expert; activations sit in MMA column 0.  The epilogue applies SwiGLU, multiplies by the
+// routing weight (so the down kernel is a plain sum over slots) and writes the result in
+// f16 split form for the down kernel.
+constexpr int kGuWarps = 4;
+__global__ void __launch_bounds__(kGuWarps * 32)
+moe_gate_up_mma_kernel(const uint8_t* __restrict__ W13, const float* __restrict__ S13,
+                       const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
+                       const int* __restrict__ ids, const float* __restrict__ wts, SplitBuf asplit,
+                       int topk, int I, int H, int e_lo, int e_cnt, float limit) {
+    __shared__ float red[kGuWarps][2][32][4];
+    const int pair = blockIdx.y;
+    const int r = pair / topk;
+    const int le = ids[pair] - e_lo;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int i0 = blockIdx.x * 16;
+    if (le < 0 || le >= e_cnt) {
+        if (threadIdx.x < 16 && i0 + threadIdx.x < I) split_store(asplit, pair, i0 + threadIdx.x, 0.f);
+        return;
+    }
+    const int kb_n = H >> 7;
+    const int nb = (2 * I + 127) >> 7;
+    const uint8_t* W = W13 + (size_t)le * 2 * I * H;
+    const float* S = S13 + (size_t)le * nb * kb_n;
+    const uint8_t* wa[2];
+    const uint8_t* wb[2];
+    int rowblk[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int base = q * I;
+        wa[q] = W + (size_t)(base + min(i0 + g, I - 1)) * H + t * 32;
+        wb[q] = W + (size_t)(base + min(i0 + g + 8, I - 1)) * H + t * 32;
+        rowblk[q] = (base + i0) >> 7;
+    }
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const uint16_t* xh_row = xhi + (size_t)r * ldx;
+    const uint16_t* xl_row = xlo + (size_t)r * ldx;
+    WFrag cur[2], nxt[2];
+    if (warp < kb_n) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) cur[q] = load_wfrag(wa[q] + (size_t)warp * 128, wb[q] + (size_t)warp * 128);
+    }
+    for (int kb = warp; kb < kb_n; kb += kGuWarps) {
+        const int kn = kb + kGuWarps;
+        if (kn < kb_n) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) nxt[q] = load_wfrag(wa[q] + (size_t)kn * 128, wb[q] + (size_t)kn * 128);
+        }
+        uint32_t xh[16], xl[16];
+        load_xfrag<16>(xh_row, xl_row, 0, g, 1, kb * 128 + t * 32, xh, xl);  // column 0 only
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_wfrag_fp8(d, cur[q], xh, xl);
+            const float sc = __ldg(S + (size_t)rowblk[q] * kb_n + kb);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[q][c] = fmaf(d[c], sc, acc[q][c]);
+        }
+        if (kn < kb_n) { cur[0] = nxt[0]; cur[1] = nxt[1]; }
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) red[warp][q][lane][c] = acc[q][c];
+    __syncthreads();
+    if (threadIdx.x < 16 && i0 + threadIdx.x < I) {
+        const int j = threadIdx.x;           // row of the tile
+        const int l = (j & 7) * 4, c = (j >> 3) * 2;  // lane with t == 0, column 0
+        float gsum = 0.f, usum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kGuWarps; ++w) { gsum += red[w][0][l][c]; usum += red[w][1][l][c]; }
+        const float gc = fminf(gsum, limit);
+        const float uc = fminf(fmaxf(usum, -limit), limit);
+        split_store(asplit, pair, i0 + j, siluf_(gc) * uc * wts[pair]);
+    }
+}
+
+// down: a CTA owns 16 output columns of one row; warps walk the (slot, k-block) items.
+// act comes pre-multiplied by the routing weights, in f16 split form.
+__global__ void __launch_bounds__(256)
+moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2,
+                    const uint16_t* __restrict__ ahi, const uint16_t* __restrict__ alo, int lda,
+                    const int* __restrict__ ids, float* __restrict__ out, int ldo, int topk, int I, int H,
+                    int e_lo, int e_cnt, int accumulate, SplitBuf osplit) {
+    __shared__ float red[8][32][4];
+    const int r = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int c0 = blockIdx.x * 16;
+    const int kb_n = I >> 7;
+    const int nb = (H + 127) >> 7;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int items = topk * kb_n;
+    const size_t ra = (size_t)min(c0 + g, H - 1) * I + t * 32, rb = (size_t)min(c0 + g + 8, H - 1) * I + t * 32;
+    auto item_frag = [&](int it, WFrag& f) -> int {  // loads the item's weights; returns its local expert or -1
+        const int s = it / kb_n, kb = it % kb_n;
+        const int le = ids[r * topk + s] - e_lo;
+        if (le < 0 || le >= e_cnt) return -1;
+        const uint8_t* W = W2 + (size_t)le * H * I + (size_t)kb * 128;
+        f = load_wfrag(W + ra, W + rb);
+        return le;
+    };
+    WFrag cur, nxt;
+    int le_cur = -1, le_nxt = -1;
+    if (warp < items) le_cur = item_frag(warp, cur);
+    for (int it = warp; it < items; it += 8) {
+        const int in = it + 8;
+        if (in < items) le_nxt = item_frag(in, nxt);
+        if (le_cur >= 0) {  // warp-uniform
+            const int s = it / kb_n, kb = it % kb_n;
+            const int pair = r * topk + s;
+            uint32_t xh[16], xl[16];
+            load_xfrag<16>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, kb * 128 + t * 32, xh, xl);
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_wfrag_fp8(d, cur, xh, xl);
+            const float sc = __ldg(S2 + (size_t)le_cur * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc, acc[c]);
+        }
+        cur = nxt;
+        le_cur = le_nxt;
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[warp][lane][c] = acc[c];
+    __syncthreads();
+    if (threadIdx.x < 16 && c0 + threadIdx.x < H) {
+        const int j = threadIdx.x;
+        const int l = (j & 7) * 4, c = (j >> 3) * 2;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += red[w][l][c];
+        float* o = out + (size_t)r * ldo + c0 + j;
+        if (accumulate) v += *o;
+        *o = v;
+        split_store(osplit, r, c0 + j, v);
+    }
+}
+
+__global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __restrict__ act, int I, float limit,
+                              SplitBuf asplit) {
     const int r = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= I) return;
     const float g = fminf(gu[(size_t)r * ld + i], limit);
     const float u = fminf(fmaxf(gu[(size_t)r * ld + I + i], -limit), limit);
-    act[(size_t)r * I + i] = siluf_(g) * u;
+    const float v = siluf_(g) * u;
+    if (act) act[(size_t)r * I + i] = v;
+    split_store(asplit, r, i, v);
 }
 
 }  // namespace
@@ -251,6 +396,44 @@ FB_API int fb_moe_down_fp8(const void* W2, const float* S2, const float* act, co
 }
 
 FB_API int fb_swiglu(const float* gu, int64_t ld, float* act, int64_t n, int64_t I, float limit, cudaStream_t st) {
-    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit);
+    SplitBuf none{nullptr, 0, 0, 0};
+    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit, none);
+    return FB_LAUNCH_CHECK();
+}
+
+// act (f32, optional) and/or its split form (row stride s_ld).
+FB_API int fb_swiglu_split(const float* gu, int64_t ld, float* act, void* s_base, int64_t s_ld, int64_t s_plane,
+                           int64_t s_mask, int64_t n, int64_t I, float limit, cudaStream_t st) {
+    SplitBuf sp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit, sp);
+    return FB_LAUNCH_CHECK();
+}
+
+// Tensor-core expert kernels.  xs: split activations (f16 planes 2/3 are read), one row per
+// token.  as: split buffer of n*topk rows x I (f16 planes) that carries
+// swiglu(gate, up) * routing weight from gate_up to down.  H % 128 == 0 and I % 128 == 0.
+FB_API int fb_moe_gate_up_mma(const void* W13, const float* S13, const void* xs, int64_t xs_ld, int64_t xs_plane,
+                              const int* ids, const float* wts, void* as_base, int64_t as_ld, int64_t as_plane,
+                              int64_t n, int64_t topk, int64_t I, int64_t H, int64_t e_lo, int64_t e_cnt,
+                              float limit, cudaStream_t st) {
+    if ((H % 128) || (xs_ld % 8)) return (int)cudaErrorInvalidValue;
+    const uint16_t* hi = (const uint16_t*)xs + 2 * xs_plane;
+    SplitBuf asp{(uint16_t*)as_base, (int)as_ld, (int)as_plane, 2};
+    dim3 grid((unsigned)((I + 15) / 16), (unsigned)(n * topk));
+    moe_gate_up_mma_kernel<<<grid, kGuWarps * 32, 0, st>>>((const uint8_t*)W13, S13, hi, hi + xs_plane, (int)xs_ld, ids, wts, asp,
+                                                 (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, limit);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_moe_down_mma(const void* W2, const float* S2, const void* as_base, int64_t as_ld, int64_t as_plane,
+                           const int* ids, float* out, int64_t ldo, int64_t n, int64_t topk, int64_t I, int64_t H,
+                           int64_t e_lo, int64_t e_cnt, int64_t accumulate, void* os_base, int64_t os_ld,
+                           int64_t os_plane, int64_t os_mask, cudaStream_t st) {
+    if ((I % 128) || (as_ld % 8)) return (int)cudaErrorInvalidValue;
+    const uint16_t* hi = (const uint16_t*)as_base + 2 * as_plane;
+    SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
+    dim3 grid((unsigned)((H + 15) / 16), (unsigned)n);
+    moe_down_mma_kernel<<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, hi, hi + as_plane, (int)as_ld, ids, out, (int)ldo,
+                                              (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, (int)accumulate, os);
     return FB_LAUNCH_CHECK();
 }

@@ -10,6 +10,7 @@
 // warp, contraction and the following RMSNorm fused).  Replaces hc_pre_fuse/hc_pre/hc_post/hc_pre_mix_split/hc_pre_rest345/hc_contract
 // (kernels/cuda/ferrite_kernels.cu:2370-2679,8001-8451).
 #include "common.cuh"
+#include "mma_gemv.cuh"
 
 namespace {
 
@@ -55,7 +56,7 @@ __global__ void embed_expand_kernel(const int* __restrict__ ids, const __nv_bflo
 // out = rmsnorm(a (+ b)) * w; optionally stores the sum.
 __global__ void rmsnorm_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                float* __restrict__ sum_out, const float* __restrict__ w,
-                               float* __restrict__ out, int d, int lda, int ldo, float eps) {
+                               float* __restrict__ out, int d, int lda, int ldo, float eps, SplitBuf osp) {
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -72,7 +73,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ a, const float* __restr
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float v = buf[j];
         if (sum_out) sum_out[(size_t)r * lda + j] = v;
-        out[(size_t)r * ldo + j] = v * inv * w[j];
+        const float o = v * inv * w[j];
+        out[(size_t)r * ldo + j] = o;
+        split_store(osp, r, j, o);
     }
 }
 
@@ -80,7 +83,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ a, const float* __restr
 __global__ void mtp_prep_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ emb,
                                 const float* __restrict__ h_prev, const float* __restrict__ enorm,
                                 const float* __restrict__ hnorm, float* __restrict__ out, int H,
-                                int vocab, float eps) {
+                                int vocab, float eps, SplitBuf osp) {
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -95,8 +98,11 @@ __global__ void mtp_prep_kernel(const int* __restrict__ ids, const __nv_bfloat16
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / H + eps);
     const float* w = half == 0 ? enorm : hnorm;
-    for (int j = threadIdx.x; j < H; j += blockDim.x)
-        out[(size_t)r * 2 * H + (size_t)half * H + j] = buf[j] * inv * w[j];
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float o = buf[j] * inv * w[j];
+        out[(size_t)r * 2 * H + (size_t)half * H + j] = o;
+        split_store(osp, r, half * H + j, o);
+    }
 }
 
 constexpr int kMaxMix = 24;
@@ -192,7 +198,8 @@ __global__ void __launch_bounds__(1024)
 hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
                     const float* __restrict__ base, const float* __restrict__ ln_w,
                     float* __restrict__ x_out, float* __restrict__ xn_out, float* __restrict__ post_out,
-                    float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters) {
+                    float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters,
+                    SplitBuf osp) {
     __shared__ float red[32];
     __shared__ float pre[8];
     const int r = blockIdx.x;
@@ -251,12 +258,15 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
         float4 o;
         o.x = x.x * inv * lw.x; o.y = x.y * inv * lw.y; o.z = x.z * inv * lw.z; o.w = x.w * inv * lw.w;
         *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
+        split_store(osp, r, j, o.x); split_store(osp, r, j + 1, o.y);
+        split_store(osp, r, j + 2, o.z); split_store(osp, r, j + 3, o.w);
     }
 }
 
 // h_final = mean_i R_i ; xn = rmsnorm(h_final) * w
 __global__ void hc_head_kernel(const float* __restrict__ R, const float* __restrict__ w,
-                               float* __restrict__ h_final, float* __restrict__ xn, int H, int n, float eps) {
+                               float* __restrict__ h_final, float* __restrict__ xn, int H, int n, float eps,
+                               SplitBuf osp) {
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -275,7 +285,9 @@ __global__ void hc_head_kernel(const float* __restrict__ R, const float* __restr
     const float inv = rsqrtf(ss / H + eps);
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
         h_final[(size_t)r * H + j] = buf[j];
-        xn[(size_t)r * H + j] = buf[j] * inv * w[j];
+        const float o = buf[j] * inv * w[j];
+        xn[(size_t)r * H + j] = o;
+        split_store(osp, r, j, o);
     }
 }
 
@@ -304,19 +316,21 @@ FB_API int fb_embed_expand(const int* ids, const void* emb, float* out, int64_t 
 }
 
 FB_API int fb_rmsnorm(const float* a, const float* b, float* sum_out, const float* w, float* out, int64_t n,
-                      int64_t d, int64_t lda, int64_t ldo, float eps, cudaStream_t st) {
+                      int64_t d, int64_t lda, int64_t ldo, float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + d) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    rmsnorm_kernel<<<n, 512, sm, st>>>(a, b, sum_out, w, out, (int)d, (int)lda, (int)ldo, eps);
+    rmsnorm_kernel<<<n, 512, sm, st>>>(a, b, sum_out, w, out, (int)d, (int)lda, (int)ldo, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_mtp_prep(const int* ids, const void* emb, const float* h_prev, const float* enorm,
-                       const float* hnorm, float* out, int64_t n, int64_t H, int64_t vocab, float eps,
+                       const float* hnorm, float* out, int64_t n, int64_t H, int64_t vocab, float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
                        cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + H) * sizeof(float);
     mtp_prep_kernel<<<dim3(n, 2), 512, sm, st>>>(ids, (const __nv_bfloat16*)emb, h_prev, enorm, hnorm, out,
-                                                  (int)H, (int)vocab, eps);
+                                                  (int)H, (int)vocab, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 
@@ -337,12 +351,13 @@ FB_API int fb_hc_mix(const float* R, const float* fn, float* acc, int64_t n, int
 
 FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const float* base,
                            const float* ln_w, float* x_out, float* xn_out, float* post_out, float* comb_out,
-                           int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
+                           int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
                            cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     if (mult != 4 || (H % 4) || H / 4 > 1024) return (int)cudaErrorInvalidValue;
     const int threads = (int)(((H / 4) + 31) / 32 * 32);
     hc_pre_apply_kernel<<<n, threads, 0, st>>>(R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
-                                               (int)H, (int)mult, rms_eps, hc_eps, (int)iters);
+                                               (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp);
     return FB_LAUNCH_CHECK();
 }
 
@@ -352,9 +367,10 @@ FB_API int fb_hc_post(float* R, const float* y, const float* post, const float* 
 }
 
 FB_API int fb_hc_head(const float* R, const float* w, float* h_final, float* xn, int64_t n, int64_t H,
-                      int64_t mult, float eps, cudaStream_t st) {
+                      int64_t mult, float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + H) * sizeof(float);
-    hc_head_kernel<<<n, 512, sm, st>>>(R, w, h_final, xn, (int)H, (int)mult, eps);
+    hc_head_kernel<<<n, 512, sm, st>>>(R, w, h_final, xn, (int)H, (int)mult, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 

@@ -236,6 +236,9 @@ class GlmDeviceModel:
     def _z(self, *shape, dtype=torch.float32):
         return torch.zeros(*shape, dtype=dtype, device=self.dev)
 
+    def _act(self, ld, split=True):
+        return Act(self.dev, self.max_rows, ld, split)
+
     def _alloc_ws(self):
         cfg, la, ds, M = self.cfg, self.cfg.linear_attn, self.cfg.dsa, self.max_rows
         H = cfg.hidden_size
@@ -243,23 +246,23 @@ class GlmDeviceModel:
         ws["R0"] = self._z(M, cfg.hc_mult, H)
         ws["R1"] = self._z(M, cfg.hc_mult, H)
         ws["R"] = ws["R0"]
-        ws["x"] = self._z(M, H)        # sublayer input (normed)
+        ws["x"] = self._act(H)         # sublayer input (normed), f32 + split planes
         ws["y"] = self._z(M, H)        # sublayer output
         ws["res"] = self._z(M, H)      # plain residual (MTP layer)
         ws["post"] = self._z(M, cfg.hc_mult)
         ws["comb"] = self._z(M, cfg.hc_mult * cfg.hc_mult)
         ws["hc_acc"] = self._z(M, HC_ACC)
         self.ld_gdn = 3 * self.P + 2 * la.low_rank + self.h_gdn
-        self.ld_gdn += (-self.ld_gdn) % 4
-        ws["gdn_proj"] = self._z(M, self.ld_gdn)
+        self.ld_gdn += (-self.ld_gdn) % 8
+        ws["gdn_proj"] = self._act(self.ld_gdn)
         ws["gdn_fg"] = self._z(M, 2 * self.P)
-        ws["gdn_core"] = self._z(M, self.P)
+        ws["gdn_core"] = self._act(self.P)
         self.ld_dsa = ds.q_lora_rank + ds.kv_lora_rank + 2 * ds.index_head_dim + ds.index_n_heads
         ws["dsa_proj"] = self._z(M, self.ld_dsa + (-self.ld_dsa) % 4)
-        ws["dsa_qa"] = self._z(M, ds.q_lora_rank)
+        ws["dsa_qa"] = self._act(ds.q_lora_rank)
         ws["dsa_wi"] = self._z(M, ds.index_n_heads)
         self.ld_qq = self.h_dsa * ds.qk_nope_head_dim + ds.index_n_heads * ds.index_head_dim
-        ws["dsa_qq"] = self._z(M, self.ld_qq)
+        ws["dsa_qq"] = self._act(self.ld_qq)
         ws["dsa_qabs"] = self._z(M, self.h_dsa * ds.kv_lora_rank)
         self.max_pools = (self.ecfg.max_ctx + ds.index_kpool - 1) // ds.index_kpool + 1
         ws["dsa_scores"] = self._z(M, self.max_pools)
@@ -268,22 +271,25 @@ class GlmDeviceModel:
         self.nsplit = 32 if self.h_dsa * ds.kv_lora_rank >= 4096 else 2
         ws["dsa_opart"] = self._z(M, self.nsplit, self.h_dsa, ds.kv_lora_rank)
         ws["dsa_ml"] = self._z(M, self.nsplit, self.h_dsa, 2)
-        ws["dsa_ctx"] = self._z(M, self.h_dsa * ds.kv_lora_rank)
-        ws["dsa_ov"] = self._z(M, self.h_dsa * ds.v_head_dim)
-        Imax = max([L.get("I_dense", 0) for L in self.layers] + [L.get("I_shared", 0) for L in self.layers] + [1])
+        ws["dsa_ctx"] = self._act(self.h_dsa * ds.kv_lora_rank)
+        ws["dsa_ov"] = self._act(self.h_dsa * ds.v_head_dim)
+        Imax = max([L.get("I_dense", 0) for L in self.layers] + [L.get("I_shared", 0) for L in self.layers] + [8])
+        Imax += (-Imax) % 8
         ws["gu"] = self._z(M, 2 * Imax)
-        ws["act"] = self._z(M, Imax)
+        ws["act"] = self._act(Imax)
         Ismax = max([L.get("I_shared", 0) for L in self.layers] + [1])
         ws["moe_lg"] = self._z(M, cfg.n_routed_experts + 2 * Ismax)
         ws["moe_ids"] = self._z(M, cfg.num_experts_per_tok, dtype=torch.int32)
         ws["moe_wts"] = self._z(M, cfg.num_experts_per_tok)
-        Il = max([L.get("I_moe", 0) for L in self.layers] + [1])
+        Il = max([L.get("I_moe", 0) for L in self.layers] + [8])
+        Il += (-Il) % 8
         ws["moe_act"] = self._z(M, cfg.num_experts_per_tok, Il)
+        ws["moe_act_s"] = torch.zeros(4, M * cfg.num_experts_per_tok, Il, dtype=torch.int16, device=self.dev)
         ws["h_final"] = self._z(M, H)
-        ws["xh"] = self._z(M, H)
+        ws["xh"] = self._act(H)
         ws["logits"] = self._z(M, self.lm_head.shape[0])
         ws["amax_part"] = self._z(M * 64, dtype=torch.int64)
-        ws["mtp_in"] = self._z(M, 2 * H)
+        ws["mtp_in"] = self._act(2 * H)
         ws["mtp_hout"] = self._z(M, H)
         self.ws = ws
 
@@ -328,19 +334,42 @@ class GlmDeviceModel:
                       torch.zeros(n * ROWMETA_BYTES, dtype=torch.uint8, device=self.dev), max(gsizes))
 
     # ------------------------------------------------------------------ op helpers
-    def gemv(self, w, x, out, m, N, K, ldx=None, ldo=None, group_rows=0, accumulate=False, scales=None):
-        """Rows are processed eight at a time; every chunk re-streams the weights once."""
-        ldx = ldx if ldx is not None else K
-        ldo = ldo if ldo is not None else N
-        xe = x.element_size()
+    def gemv(self, w, x, out, m, N, K, ldx=None, ldo=None, group_rows=0, accumulate=False, scales=None,
+             xcol=0, ocol=0, omask=0):
+        """out[:m, ocol:ocol+N] (+)= x[:m, xcol:...] . w^T.  x / out may be :class:`Act` buffers
+        (f32 + split planes) or plain f32 tensors.  Rows go eight at a time; each chunk streams
+        the weights once.  The tensor-core kernel runs when the input has split planes and K
+        fits its k-block; otherwise the SIMT kernel reads the f32 copy."""
+        xa = x if isinstance(x, Act) else None
+        oa = out if isinstance(out, Act) else None
+        xf = xa.f if xa else x
+        of = oa.f if oa else out
+        ldx = ldx if ldx is not None else (xa.ld if xa else K)
+        ldo = ldo if ldo is not None else (oa.ld if oa else N)
+        fp8 = scales is not None
+        kb = 128 if fp8 else 64
+        use_mma = xa is not None and xa.s is not None and K % kb == 0 and group_rows % 16 == 0 and ldx % 8 == 0
         for r0 in range(0, m, 8):
             mm = min(8, m - r0)
-            xp = _lib.ctypes.c_void_p(_ptr(x) + r0 * ldx * xe)
-            op = _lib.ctypes.c_void_p(_ptr(out) + r0 * ldo * 4)
-            if scales is None:
-                self.K.call("fb_gemv_bf16", w, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
+            op = _lib.ctypes.c_void_p(of.data_ptr() + (r0 * ldo + ocol) * 4)
+            if oa is not None and omask:
+                osb = (_lib.ctypes.c_void_p(oa.s.data_ptr() + (r0 * ldo + ocol) * 2), ldo, oa.plane, omask)
             else:
+                osb = (None, 0, 0, 0)
+            if use_mma:
+                xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + (r0 * ldx + xcol) * 2)
+                if fp8:
+                    self.K.call("fb_gemv_mma_fp8", w, scales, xp, ldx, xa.plane, op, ldo, mm, N, K, accumulate, *osb)
+                else:
+                    self.K.call("fb_gemv_mma_bf16", w, xp, ldx, xa.plane, op, ldo, mm, N, K, group_rows, accumulate, *osb)
+                continue
+            xp = _lib.ctypes.c_void_p(xf.data_ptr() + (r0 * ldx + xcol) * 4)
+            if fp8:
                 self.K.call("fb_gemv_fp8", w, scales, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
+            else:
+                self.K.call("fb_gemv_bf16", w, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
+            if osb[0] is not None:
+                self.K.call("fb_split_rows", op, ldo, *osb, mm, N)
 
     def _reduce(self, y, n):
         if self.world > 1:
@@ -351,14 +380,15 @@ class GlmDeviceModel:
         cfg, la, ws, n = self.cfg, self.cfg.linear_attn, self.ws, rs.n
         H, P, r = cfg.hidden_size, self.P, la.low_rank
         proj = ws["gdn_proj"]
-        self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, ldo=self.ld_gdn)
-        self.gemv(L["fg_b"], View(proj, 3 * P), ws["gdn_fg"], n, 2 * P, r, ldx=self.ld_gdn, group_rows=P)
+        self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, omask=1)
+        self.gemv(L["fg_b"], proj, ws["gdn_fg"], n, 2 * P, r, group_rows=P, xcol=3 * P)
         gi = L["gdn_index"]
-        self.K.call("fb_gdn_fused", proj, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"], L["a_log"],
-                    L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
-                    rs.group_first, rs.n_groups, ws["gdn_core"], P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
-                    self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps))
-        self.gemv(L["o_proj"], ws["gdn_core"], ws["y"], n, H, P)
+        core = ws["gdn_core"]
+        self.K.call("fb_gdn_fused", proj.f, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"],
+                    L["a_log"], L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
+                    rs.group_first, rs.n_groups, core.f, P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
+                    self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps), *core.sp(1))
+        self.gemv(L["o_proj"], core, ws["y"], n, H, P)
         self._reduce(ws["y"], n)
 
     def _attn_dsa(self, L, rs: RowSet):
@@ -370,34 +400,37 @@ class GlmDeviceModel:
         ldp = ws["dsa_proj"].shape[1]
         self.gemv(L["w_in"], ws["x"], ws["dsa_proj"], n, self.ld_dsa, H, ldo=ldp)
         pt, mp, ps = self.page_table, self.max_pages, ds.page_size
-        self.K.call("fb_dsa_prep", ws["dsa_proj"], ldp, L["qa_ln"], L["kv_ln"], L["kn_w"], L["kn_b"], ws["dsa_qa"],
+        qa, qq, ctx, ov = ws["dsa_qa"], ws["dsa_qq"], ws["dsa_ctx"], ws["dsa_ov"]
+        self.K.call("fb_dsa_prep", ws["dsa_proj"], ldp, L["qa_ln"], L["kv_ln"], L["kn_w"], L["kn_b"], qa.f,
                     ws["dsa_wi"], self.lat_cache[f], self.kidx_cache[f], self.kgate_cache[f], rs.meta, pt, mp, ps,
-                    n, QL, DL, ID, IH, float(cfg.rms_norm_eps), int(self.kv_f32))
+                    n, QL, DL, ID, IH, float(cfg.rms_norm_eps), int(self.kv_f32), *qa.sp(1))
         self.K.call("fb_dsa_pool", self.kidx_cache[f], self.kgate_cache[f], L["ape"], self.pool_cache[f], rs.meta,
                     pt, mp, ps, n, ID, ds.index_kpool)
-        self.gemv(L["w_q"], ws["dsa_qa"], ws["dsa_qq"], n, self.ld_qq, QL)
-        self.K.call("fb_dsa_scores", View(ws["dsa_qq"], hl * dk), self.ld_qq, ws["dsa_wi"], self.pool_cache[f],
+        self.gemv(L["w_q"], qa, qq, n, self.ld_qq, QL, omask=1)
+        self.K.call("fb_dsa_scores", View(qq.f, hl * dk), self.ld_qq, ws["dsa_wi"], self.pool_cache[f],
                     ws["dsa_scores"], self.max_pools, rs.meta, pt, mp, ps, n, IH, ID, ds.index_kpool, self.max_pools)
         ldi = ws["dsa_idx"].shape[1]
         self.K.call("fb_dsa_select", ws["dsa_scores"], self.max_pools, ws["dsa_idx"], ldi, ws["dsa_cnt"], rs.meta,
                     n, ds.index_kpool, ds.select_pools)
-        self.gemv(L["wk_abs"], ws["dsa_qq"], ws["dsa_qabs"], n, hl * DL, dk, ldx=self.ld_qq, group_rows=DL)
+        self.gemv(L["wk_abs"], qq, ws["dsa_qabs"], n, hl * DL, dk, group_rows=DL)
         self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
                     ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, 0, 1,
                     float(dk ** -0.5), int(self.kv_f32))
-        self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ws["dsa_ctx"], None, n, hl, DL, self.nsplit, 1)
-        self.gemv(L["wv_abs"], ws["dsa_ctx"], ws["dsa_ov"], n, hl * dv, DL, ldx=hl * DL, group_rows=dv)
-        self.gemv(L["o_proj"], ws["dsa_ov"], ws["y"], n, H, hl * dv)
+        self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, self.nsplit, 1,
+                    *ctx.sp(1))
+        self.gemv(L["wv_abs"], ctx, ov, n, hl * dv, DL, group_rows=dv, omask=1)
+        self.gemv(L["o_proj"], ov, ws["y"], n, H, hl * dv)
         self._reduce(ws["y"], n)
 
     def _ffn_dense(self, L, n):
         cfg, ws = self.cfg, self.ws
         H, I = cfg.hidden_size, L["I_dense"]
         ldg = ws["gu"].shape[1]
+        act = ws["act"]
         self.gemv(L["d13"], ws["x"], ws["gu"], n, 2 * I, H, ldo=ldg, scales=L.get("d13s"))
-        self.K.call("fb_swiglu", ws["gu"], ldg, ws["act"], n, I, float(cfg.swiglu_limit))
-        # act rows are packed with stride I by fb_swiglu
-        self.gemv(L["d2"], ws["act"], ws["y"], n, H, I, scales=L.get("d2s"))
+        self.K.call("fb_swiglu_split", ws["gu"], ldg, act.f, *act.sp(3, ld=I), n, I, float(cfg.swiglu_limit))
+        # fb_swiglu packs rows with stride I in both the f32 and the split form
+        self.gemv(L["d2"], act, ws["y"], n, H, I, ldx=I, scales=L.get("d2s"))
         self._reduce(ws["y"], n)
 
     def _ffn_moe(self, L, n):
@@ -405,15 +438,25 @@ class GlmDeviceModel:
         H, E, topk = cfg.hidden_size, cfg.n_routed_experts, cfg.num_experts_per_tok
         Il, Is = L["I_moe"], L["I_shared"]
         ldl = ws["moe_lg"].shape[1]
-        self.gemv(L["gate_s13"], ws["x"], ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
+        act, x = ws["act"], ws["x"]
+        self.gemv(L["gate_s13"], x, ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
         self.K.call("fb_moe_route", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
                     float(cfg.routed_scaling_factor))
-        self.K.call("fb_swiglu", View(ws["moe_lg"], E), ldl, ws["act"], n, Is, float(cfg.swiglu_limit))
-        self.gemv(L["s2"], ws["act"], ws["y"], n, H, Is)
-        self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], ws["x"], H, ws["moe_ids"], ws["moe_act"], n, topk, Il,
-                    H, 0, self.E_res, float(cfg.swiglu_limit))
-        self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"], H, n,
-                    topk, Il, H, 0, self.E_res, 1)
+        self.K.call("fb_swiglu_split", View(ws["moe_lg"], E), ldl, act.f, *act.sp(1, ld=Is), n, Is,
+                    float(cfg.swiglu_limit))
+        self.gemv(L["s2"], act, ws["y"], n, H, Is, ldx=Is)
+        if H % 128 == 0 and Il % 128 == 0:
+            mas = ws["moe_act_s"]
+            ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
+            self.K.call("fb_moe_gate_up_mma", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_ids"], ws["moe_wts"],
+                        mas, ld_as, plane_as, n, topk, Il, H, 0, self.E_res, float(cfg.swiglu_limit))
+            self.K.call("fb_moe_down_mma", L["w2"], L["s2s"], mas, ld_as, plane_as, ws["moe_ids"], ws["y"], H, n,
+                        topk, Il, H, 0, self.E_res, 1, None, 0, 0, 0)
+        else:
+            self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], x.f, H, ws["moe_ids"], ws["moe_act"], n, topk,
+                        Il, H, 0, self.E_res, float(cfg.swiglu_limit))
+            self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"],
+                        H, n, topk, Il, H, 0, self.E_res, 1)
         self._reduce(ws["y"], n)
 
     def _attn(self, L, rs, snapshots):
@@ -431,9 +474,10 @@ class GlmDeviceModel:
     def _hc_pre(self, L, site, ln, n):
         """Coefficients + contraction + RMSNorm of one site; its mix dots are already in hc_acc."""
         cfg, ws = self.cfg, self.ws
+        x = ws["x"]
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
-                    ws["x"], ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
-                    float(cfg.hc_eps), cfg.hc_sinkhorn_iters)
+                    x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
+                    float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3))
 
     def _hc_post_mix(self, fn_next, n, first=False):
         """hc_post of the finished site fused with the mix dots of the next one; the residual
@@ -473,11 +517,13 @@ class GlmDeviceModel:
             self._hc_post_mix(main[li + 1]["hc_attn_fn"] if li + 1 < len(main) else None, n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "ffn", ws, n)
-        K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], ws["xh"], n, H, cfg.hc_mult, float(cfg.rms_norm_eps))
+        xh = ws["xh"]
+        K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], xh.f, n, H, cfg.hc_mult,
+               float(cfg.rms_norm_eps), *xh.sp(1))
         V = self.lm_head.shape[0]
         nh = n - head_from  # the head runs on rows [head_from, n); their logits land in rows [0, nh)
         if nh > 0:
-            self.gemv(self.lm_head, View(ws["xh"], head_from * H), ws["logits"], nh, V, H)
+            self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
             if judges is not None:
                 K.call("fb_argmax", ws["logits"], V, ws["amax_part"], View(judges, head_from), None, nh, V, 1, 0)
         if advance:
@@ -492,20 +538,37 @@ class GlmDeviceModel:
         L = self.layers[cfg.num_layers]
         eps = float(cfg.rms_norm_eps)
         K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.mtp_len, rs.meta, n)
-        K.call("fb_mtp_prep", ids, self.embed, h_prev, L["enorm"], L["hnorm"], ws["mtp_in"], n, H, cfg.vocab_size, eps)
-        self.gemv(L["eh_proj"], ws["mtp_in"], ws["res"], n, H, 2 * H)
-        K.call("fb_rmsnorm", ws["res"], None, None, L["ln1"], ws["x"], n, H, H, H, eps)
+        mi, x, xh = ws["mtp_in"], ws["x"], ws["xh"]
+        K.call("fb_mtp_prep", ids, self.embed, h_prev, L["enorm"], L["hnorm"], mi.f, n, H, cfg.vocab_size, eps, *mi.sp(1))
+        self.gemv(L["eh_proj"], mi, ws["res"], n, H, 2 * H)
+        K.call("fb_rmsnorm", ws["res"], None, None, L["ln1"], x.f, n, H, H, H, eps, *x.sp(3))
         self._attn_dsa(L, rs)
-        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["res"], L["ln2"], ws["x"], n, H, H, H, eps)
+        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["res"], L["ln2"], x.f, n, H, H, H, eps, *x.sp(3))
         self._ffn_moe(L, n)
-        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["mtp_hout"], L["head_norm"], ws["xh"], n, H, H, H, eps)
+        K.call("fb_rmsnorm", ws["res"], ws["y"], ws["mtp_hout"], L["head_norm"], xh.f, n, H, H, H, eps, *xh.sp(1))
         nh = n - head_from
         if out_ids is not None and nh > 0:
             V = self.lm_head.shape[0]
-            self.gemv(self.lm_head, View(ws["xh"], head_from * H), ws["logits"], nh, V, H)
+            self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
             K.call("fb_argmax", ws["logits"], V, ws["amax_part"], out_ids, None, nh, V, 1, 0)
         if advance:
             K.call("fb_advance_rows", rs.meta, None, self.mtp_len, n)
+
+
+class Act:
+    """An activation buffer [M, ld]: an f32 copy plus the four 16-bit split planes
+    (bf16 hi/lo, f16 hi/lo) that the tensor-core GEMVs read."""
+
+    def __init__(self, dev, M: int, ld: int, split: bool = True):
+        self.M, self.ld, self.plane = M, ld, M * ld
+        self.f = torch.zeros(M, ld, dtype=torch.float32, device=dev)
+        self.s = torch.zeros(4, M, ld, dtype=torch.int16, device=dev) if split else None
+
+    def sp(self, mask: int, ld: Optional[int] = None):
+        """(base, ld, plane, mask) arguments for a producer kernel's split output."""
+        if self.s is None or not mask:
+            return (None, 0, 0, 0)
+        return (self.s, ld if ld is not None else self.ld, self.plane, mask)
 
 
 class View:

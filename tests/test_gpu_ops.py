@@ -30,6 +30,36 @@ def check(name, got, want, atol, rtol=1e-3):
     assert torch.allclose(got, want, atol=atol, rtol=rtol), f"{name}: max err {err:.3e} (ref max {ref:.3e})"
 
 
+def unsplit(sp, kind):
+    """Rebuild f32 values from a [4, M, ld] int16 split buffer (kind 0 = bf16 pair, 1 = f16 pair)."""
+    dt = torch.bfloat16 if kind == 0 else torch.float16
+    hi = sp[2 * kind].view(dt).float()
+    lo = sp[2 * kind + 1].view(dt).float()
+    return hi + lo
+
+
+def check_split(name, sp, want, n, K_):
+    for kind in (0, 1):
+        got = unsplit(sp.cpu(), kind)[:n, :K_]
+        err = (got - want.float().cpu()).abs().max().item()
+        ref = want.abs().max().item() + 1e-9
+        assert err / ref < 2e-4, f"{name} kind {kind}: rel err {err / ref:.2e}"
+
+
+def to_split(x, ld=None):
+    """Host-side split of an f32 [M, K] tensor into the [4, M, ld] int16 layout."""
+    M, K_ = x.shape
+    ld = ld or K_
+    sp = torch.zeros(4, M, ld, dtype=torch.int16)
+    bh = x.bfloat16()
+    bl = (x - bh.float()).bfloat16()
+    hh = x.half()
+    hl = (x - hh.float()).half()
+    for i, t in enumerate((bh, bl, hh, hl)):
+        sp[i, :, :K_] = t.view(torch.int16)
+    return sp
+
+
 def make_meta(K, slots, gsizes, seq_len):
     """Row tables + RowMeta for groups (slot, size); seq_len: per-slot start positions."""
     rs, ro, rg, gf = [], [], [], []
@@ -78,10 +108,10 @@ def test_rmsnorm_and_add(K):
     n, d = 5, 384
     a, b, w = rnd(n, d, seed=1), rnd(n, d, seed=2), rnd(d, seed=3)
     out, s = torch.zeros(n, d, device="cuda"), torch.zeros(n, d, device="cuda")
-    K.call("fb_rmsnorm", dev(a), dev(b), s, dev(w), out, n, d, d, d, 1e-5)
+    K.call("fb_rmsnorm", dev(a), dev(b), s, dev(w), out, n, d, d, d, 1e-5, None, 0, 0, 0)
     check("sum", s, a + b, 1e-6)
     check("rmsnorm", out, R.rmsnorm(a + b, w, 1e-5), 1e-5)
-    K.call("fb_rmsnorm", dev(a), None, None, dev(w), out, n, d, d, d, 1e-5)
+    K.call("fb_rmsnorm", dev(a), None, None, dev(w), out, n, d, d, d, 1e-5, None, 0, 0, 0)
     check("rmsnorm1", out, R.rmsnorm(a, w, 1e-5), 1e-5)
 
 
@@ -97,9 +127,11 @@ def test_hc_chain(K, H):
     Rd = dev(Rr.clone())
     acc = torch.zeros(n, 25, device="cuda")
     x, xn = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
+    sp = torch.zeros(4, n, H, dtype=torch.int16, device="cuda")
     post, comb = torch.zeros(n, 4, device="cuda"), torch.zeros(n, 16, device="cuda")
     K.call("fb_hc_mix", Rd, dev(fn), acc, n, mult * H, mix)
-    K.call("fb_hc_pre_apply", Rd, acc, dev(scale), dev(base), dev(ln), x, xn, post, comb, n, H, mult, 1e-5, 1e-6, 20)
+    K.call("fb_hc_pre_apply", Rd, acc, dev(scale), dev(base), dev(ln), x, xn, post, comb, n, H, mult, 1e-5, 1e-6, 20, sp, H, n * H, 3)
+    check_split("hc xn split", sp, xn, n, H)
     xr, pr, cr = R.hc_pre(Rr, fn, scale, base, 1e-5, 1e-6, 20)
     check("hc x", x, xr, 1e-4)
     check("hc post", post, pr, 1e-5)
@@ -119,7 +151,7 @@ def test_hc_chain(K, H):
     K.call("fb_hc_post", Rd, dev(y), post, comb, n, H)
     check("hc_post", Rd, Rn, 1e-4)
     hf, xh = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
-    K.call("fb_hc_head", dev(Rr), dev(ln), hf, xh, n, H, mult, 1e-5)
+    K.call("fb_hc_head", dev(Rr), dev(ln), hf, xh, n, H, mult, 1e-5, None, 0, 0, 0)
     check("hc_head", hf, Rr.mean(1), 1e-5)
     check("hc_head norm", xh, R.rmsnorm(Rr.mean(1), ln, 1e-5), 1e-5)
 
@@ -133,7 +165,7 @@ def test_embed_and_mtp_prep(K):
     check("embed", out, emb.float()[ids.long()].unsqueeze(1).repeat(1, 4, 1), 0)
     hp, en, hn = rnd(n, H, seed=2), rnd(H, seed=3), rnd(H, seed=4)
     o2 = torch.zeros(n, 2 * H, device="cuda")
-    K.call("fb_mtp_prep", dev(ids), dev(emb), dev(hp), dev(en), dev(hn), o2, n, H, V, 1e-5)
+    K.call("fb_mtp_prep", dev(ids), dev(emb), dev(hp), dev(en), dev(hn), o2, n, H, V, 1e-5, None, 0, 0, 0)
     want = torch.cat([R.rmsnorm(emb.float()[ids.long()], en, 1e-5), R.rmsnorm(hp, hn, 1e-5)], -1)
     check("mtp_prep", o2, want, 1e-5)
 
@@ -159,7 +191,7 @@ def test_gdn_fused(K, dk, H, groups, nbuf, snap):
     sd, cd = dev(state.clone()), dev(conv_state.clone())
     out = torch.zeros(n, P, device="cuda")
     K.call("fb_gdn_fused", dev(proj), ld, dev(fb), dev(gb), P, dev(conv_w), dev(a_log), dev(dt_bias), dev(o_norm),
-           sd, cd, dev(cur), meta, gf, len(groups), out, P, H, dk, b_off, nbuf, snap, -5.0, 1e-5)
+           sd, cd, dev(cur), meta, gf, len(groups), out, P, H, dk, b_off, nbuf, snap, -5.0, 1e-5, None, 0, 0, 0)
     r0 = 0
     for gi, g in enumerate(groups):
         c = int(cur[gi])
@@ -379,14 +411,14 @@ def test_dsa_attention(K, hl, DL, kv_f32, ntok, nshard):
                dev(pt), max_pages, page, n, hl, DL, nsplit, sh, nshard, scale, kv_f32)
         ctx = torch.zeros(n, hl, DL, device="cuda")
         lse = torch.zeros(n, hl, 2, device="cuda")
-        K.call("fb_dsa_attn_merge", o_part, ml, ctx, lse, n, hl, DL, nsplit, 1 if nshard == 1 else 0)
+        K.call("fb_dsa_attn_merge", o_part, ml, ctx, lse, n, hl, DL, nsplit, 1 if nshard == 1 else 0, None, 0, 0, 0)
         parts_o.append(ctx)
         parts_ml.append(lse)
     if nshard > 1:  # cross-shard merge is the same merge over [n, nshard, hl, *]
         o_all = torch.stack(parts_o, 1).contiguous()
         ml_all = torch.stack(parts_ml, 1).contiguous()
         ctx = torch.zeros(n, hl, DL, device="cuda")
-        K.call("fb_dsa_attn_merge", o_all, ml_all, ctx, None, n, hl, DL, nshard, 1)
+        K.call("fb_dsa_attn_merge", o_all, ml_all, ctx, None, n, hl, DL, nshard, 1, None, 0, 0, 0)
     want = torch.zeros(n, hl, DL)
     for i in range(n):
         ids = idx[i, :int(cnt[i])].long()
@@ -394,3 +426,82 @@ def test_dsa_attention(K, hl, DL, kv_f32, ntok, nshard):
         p = torch.softmax(s, -1)
         want[i] = p @ lat[ids]
     check("dsa attn", ctx, want, 2e-4)
+
+
+@pytest.mark.parametrize("m,N,K_,group", [(1, 48, 64, 0), (3, 4100, 512, 0), (8, 9600, 128, 0), (2, 16 * 64, 64, 64),
+                                          (5, 777, 4096, 0), (3, 24896, 4096, 0)])
+def test_gemv_mma_bf16(K, m, N, K_, group):
+    G = N // group if group else 1
+    w = rnd(N, K_, seed=1, scale=0.1).bfloat16()
+    x = rnd(m, G * K_, seed=2)
+    xs = dev(to_split(x))
+    od = torch.full((m, N), 7.0, device="cuda")
+    osp = torch.zeros(4, m, N, dtype=torch.int16, device="cuda")
+    K.call("fb_gemv_mma_bf16", dev(w), xs, G * K_, m * G * K_, od, N, m, N, K_, group, 0, osp, N, m * N, 3)
+    if group:
+        want = torch.einsum("mgk,gnk->mgn", x.view(m, G, K_), w.float().view(G, group, K_)).reshape(m, N)
+    else:
+        want = x @ w.float().t()
+    check("gemv mma", od, want, 2e-3)
+    check_split("gemv mma split out", osp, od, m, N)
+    K.call("fb_gemv_mma_bf16", dev(w), xs, G * K_, m * G * K_, od, N, m, N, K_, group, 1, None, 0, 0, 0)
+    check("gemv mma acc", od, 2 * want, 4e-3)
+    # the split conversion kernel agrees with the host-side split
+    sp2 = torch.zeros(4, m, G * K_, dtype=torch.int16, device="cuda")
+    K.call("fb_split_rows", dev(x), G * K_, sp2, G * K_, m * G * K_, 3, m, G * K_)
+    assert torch.equal(sp2.cpu(), to_split(x))
+
+
+@pytest.mark.parametrize("m,N,K_", [(1, 256, 256), (3, 512, 4096), (8, 10240, 384), (2, 200, 128)])
+def test_gemv_mma_fp8(K, m, N, K_):
+    w = rnd(N, K_, seed=3, scale=0.05)
+    q, s = R.quant_fp8_block(w)
+    x = rnd(m, K_, seed=4)
+    od = torch.zeros(m, N, device="cuda")
+    K.call("fb_gemv_mma_fp8", dev(q), dev(s), dev(to_split(x)), K_, m * K_, od, N, m, N, K_, 0, None, 0, 0, 0)
+    check("gemv mma fp8", od, x @ R.dequant_fp8_block(q, s).t(), 2e-3)
+
+
+@pytest.mark.parametrize("n,E,topk,I,H", [(1, 8, 2, 128, 256), (3, 16, 8, 256, 4096), (2, 6, 3, 2048, 512)])
+def test_moe_experts_mma(K, n, E, topk, I, H):
+    g = torch.Generator().manual_seed(7)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    q13, s13 = zip(*[R.quant_fp8_block(w13[e]) for e in range(E)])
+    q2, s2 = zip(*[R.quant_fp8_block(w2[e]) for e in range(E)])
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+    x = torch.randn(n, H, generator=g)
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(n)]).int()
+    wts = torch.rand(n, topk, generator=g)
+    asp = torch.zeros(4, n * topk, I, dtype=torch.int16, device="cuda")
+    out = torch.ones(n, H, device="cuda")
+    lo, cnt = 0, E
+    K.call("fb_moe_gate_up_mma", dev(q13), dev(s13), dev(to_split(x)), H, n * H, dev(ids), dev(wts), asp, I, n * topk * I,
+           n, topk, I, H, lo, cnt, 10.0)
+    K.call("fb_moe_down_mma", dev(q2), dev(s2), asp, I, n * topk * I, dev(ids), out, H, n, topk, I, H, lo, cnt, 1,
+           None, 0, 0, 0)
+    want = torch.ones(n, H)
+    act_ref = torch.zeros(n * topk, I)
+    for r in range(n):
+        for s in range(topk):
+            e = int(ids[r, s])
+            W13 = R.dequant_fp8_block(q13[e], s13[e])
+            a = R.swiglu_limited(x[r] @ W13[:I].t(), x[r] @ W13[I:].t(), 10.0) * wts[r, s]
+            act_ref[r * topk + s] = a
+            want[r] += a @ R.dequant_fp8_block(q2[e], s2[e]).t()
+    check("moe mma act", unsplit(asp.cpu(), 1), act_ref, 2e-3)
+    check("moe mma out", out, want, 5e-3)
+    # expert-parallel masking
+    lo, cnt = E // 2, E - E // 2
+    out2 = torch.zeros(n, H, device="cuda")
+    K.call("fb_moe_gate_up_mma", dev(q13[lo:]), dev(s13[lo:]), dev(to_split(x)), H, n * H, dev(ids), dev(wts), asp, I,
+           n * topk * I, n, topk, I, H, lo, cnt, 10.0)
+    K.call("fb_moe_down_mma", dev(q2[lo:]), dev(s2[lo:]), asp, I, n * topk * I, dev(ids), out2, H, n, topk, I, H, lo,
+           cnt, 0, None, 0, 0, 0)
+    want2 = torch.zeros(n, H)
+    for r in range(n):
+        for s in range(topk):
+            e = int(ids[r, s])
+            if e >= lo:
+                want2[r] += act_ref[r * topk + s] @ R.dequant_fp8_block(q2[e], s2[e]).t()
+    check("moe mma ep", out2, want2, 5e-3)
