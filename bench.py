@@ -92,6 +92,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
+                    help="all-reduce used by the tensor-parallel chain: peer-memory one-shot kernel or NCCL")
     ap.add_argument("--profile", action="store_true",
                     help="open the CUDA profiler window around the timed device loop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -114,7 +116,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from ferrite_b200.parallel.collective import make_allreduce
-        allreduce = make_allreduce(dev, rank, world, max_elems=8 * 4096)
+        allreduce = make_allreduce(dev, rank, world, max_elems=64 * 4096, kind=args.collective)
 
     cfg = GlmConfig.production() if args.layers == 0 else GlmConfig.scaled(args.layers)
     # 288 experts x 43 MoE layers are 312 GB in fp8: one 180 GB GPU cannot hold them, so at
@@ -198,7 +200,7 @@ def main():
             "impl": "ours",
             "config": {"model": "GLM-5.3-Flash (45 layers: 34 GatedDeltaNet + 11 DSA, 3 dense + 42 MoE, 1 MTP layer)"
                                 if args.layers == 0 else f"DEBUG {args.layers}-layer slice (invalid as a result)",
-                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}",
+                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none",
                        "weights": "random-init; bf16, routed experts + dense FFN fp8 e4m3 128x128 block-scaled (W8A16)",
                        "mtp": "draft 2 / verify 3" if mtp else "off",
                        "accept_tokens_per_step": round(tokens / args.steps, 3),

@@ -171,6 +171,7 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--no-graph", action="store_true", help="eager launches (use under ncu)")
     args = ap.parse_args()
     K = _lib.lib()
     peak, tag = hbm_peak_gbs()
@@ -180,10 +181,21 @@ def main():
             c.fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.iters):
-            c.fn()
-        e1.record()
+        if args.no_graph:
+            e0.record()
+            for _ in range(args.iters):
+                c.fn()
+            e1.record()
+        else:  # one graph of `iters` launches: no per-launch host time in the measurement
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(args.iters):
+                    c.fn()
+            g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / args.iters
         gbs = c.nbytes / us / 1e3

@@ -1,0 +1,169 @@
+// One-shot all-reduce over NVLink peer memory, with bounded waits and a status word.
+//
+// Every rank owns a symmetric region: staging[2 parity][world][max_elems] f32 and
+// flags[2][world][kMaxChunks] u32, mapped into every peer through CUDA IPC.  One launch does
+// the whole collective for payloads of a few rows of the hidden size (16-48 KB):
+//   1. push: each CTA owns a 4096-element chunk and stores its part of the local vector
+//      into slot `rank` of EVERY peer's staging (16-byte peer stores over NVLink);
+//   2. publish: bar.sync, then one thread fences at system scope and release-stores the
+//      epoch stamp of that chunk into every peer's flag word;
+//   3. wait: the CTA polls its OWN flag words (peers write them into local memory, so a
+//      poll never crosses NVLink) until all peers carry the epoch -- at most `max_spins`
+//      polls, after which the kernel records {TIMEOUT, peer, epoch, chunk} in the status
+//      buffer and leaves the vector unreduced instead of spinning, trapping or parking;
+//   4. reduce: slots are summed in rank order, so every rank gets bit-identical sums.
+// Epochs advance only inside this kernel, chunk by chunk, so warm-up, capture and replay
+// keep all ranks in lockstep; staging is double-buffered by epoch parity, which is enough
+// because a rank publishes epoch e+1 only after it finished reducing epoch e.
+// This is the counterpart of the reference's AR v5 (kernels/cuda/ferrite_kernels.cu:8968-9524),
+// whose waiter parks forever or traps on timeout (:9180-9229).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxChunks = 64;
+constexpr int kChunk = 4096;  // elements per CTA (1024 threads x float4)
+constexpr int kMaxWorld = 8;
+
+struct ArTables {
+    float* staging[kMaxWorld];
+    uint32_t* flags[kMaxWorld];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+// Shared by the stand-alone all-reduce and the fused epilogues: push `v`, publish, wait,
+// and return the rank-ordered sum of the chunk element owned by this thread.  `ok` is false
+// after a timeout (v is then returned unchanged).
+__device__ __forceinline__ float4 ar_chunk(const ArTables& t, uint32_t* epoch, int* status, int rank, int world,
+                                           int max_elems, int max_spins, int chunk, float4 v, bool valid, bool* ok) {
+    __shared__ int s_fail;
+    const uint32_t e = epoch[chunk] + 1u;
+    const int par = e & 1u;
+    const size_t off = (size_t)chunk * kChunk + threadIdx.x * 4;
+    if (threadIdx.x == 0) s_fail = 0;
+    if (valid) {
+        for (int p = 0; p < world; ++p) {
+            float* dst = t.staging[p] + ((size_t)par * world + rank) * max_elems + off;
+            *reinterpret_cast<float4*>(dst) = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int p = 0; p < world; ++p) st_release_sys(t.flags[p] + ((size_t)par * world + rank) * kMaxChunks + chunk, e);
+    }
+    if (threadIdx.x < world) {
+        const uint32_t* f = t.flags[rank] + ((size_t)par * world + threadIdx.x) * kMaxChunks + chunk;
+        int spins = 0;
+        // stamps only grow; a stamp ahead of e cannot occur (see the parity argument above)
+        while (ld_acquire_sys(f) < e) {
+            if (++spins > max_spins) {
+                if (atomicCAS(&s_fail, 0, 1) == 0) {
+                    status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = chunk;
+                }
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    const bool good = (s_fail == 0);
+    *ok = good;
+    float4 acc = v;
+    if (good && valid) {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int src = 0; src < world; ++src) {
+            const float4 a = ld_cg_f4(t.staging[rank] + ((size_t)par * world + src) * max_elems + off);
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) epoch[chunk] = e;  // stay in step with the peers even after a timeout
+    return acc;
+}
+
+__global__ void __launch_bounds__(1024)
+ar_oneshot_kernel(ArTables t, uint32_t* epoch, int* status, float* y, int n_elems, int rank, int world,
+                  int max_elems, int max_spins) {
+    const int chunk = blockIdx.x;
+    const int i = chunk * kChunk + threadIdx.x * 4;
+    const bool valid = i < n_elems;
+    float4 v = valid ? *reinterpret_cast<const float4*>(y + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bool ok;
+    const float4 r = ar_chunk(t, epoch, status, rank, world, max_elems, max_spins, chunk, v, valid, &ok);
+    if (ok && valid) *reinterpret_cast<float4*>(y + i) = r;
+}
+
+// A wait that nothing satisfies: used by the failure-detection test to check that a bounded
+// wait gives up with a status word and leaves the context usable.
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, int max_spins, int* status) {
+    int spins = 0;
+    while (ld_acquire_sys(flag) < want) {
+        if (++spins > max_spins) {
+            status[0] = FB_TIMEOUT; status[1] = -1; status[2] = (int)want; status[3] = spins;
+            return;
+        }
+        __nanosleep(64);
+    }
+    status[0] = FB_OK;
+}
+
+}  // namespace
+
+// ---- symmetric memory plumbing (cudaMalloc + CUDA IPC) ----------------------------------------
+FB_API int fb_symm_alloc(int64_t bytes, void** out) {
+    cudaError_t e = cudaMalloc(out, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaMemset(*out, 0, (size_t)bytes);
+    return (int)e;
+}
+FB_API int fb_symm_free(void* p) { return (int)cudaFree(p); }
+FB_API int fb_ipc_get_handle(void* p, void* handle64) {
+    return (int)cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64), p);
+}
+FB_API int fb_ipc_open(const void* handle64, void** out) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+FB_API int fb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+FB_API int fb_memcpy_d2h(void* dst, const void* src, int64_t bytes) {
+    return (int)cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost);
+}
+FB_API int fb_ar_limits(int* max_chunks, int* chunk_elems) {
+    *max_chunks = kMaxChunks; *chunk_elems = kChunk;
+    return 0;
+}
+
+// staging_ptrs / flag_ptrs: host arrays of `world` device pointers (index = rank; the own
+// entry is the local allocation).  y [n_elems] f32 is reduced in place; n_elems % 4 == 0 and
+// n_elems <= min(max_elems, 64 * 4096).
+FB_API int fb_ar_oneshot(const void* const* staging_ptrs, const void* const* flag_ptrs, void* epoch, int* status,
+                         float* y, int64_t n_elems, int64_t rank, int64_t world, int64_t max_elems,
+                         int64_t max_spins, cudaStream_t st) {
+    if (world > kMaxWorld || n_elems > max_elems || (n_elems % 4) || n_elems > (int64_t)kMaxChunks * kChunk)
+        return (int)cudaErrorInvalidValue;
+    ArTables t;
+    for (int i = 0; i < world; ++i) { t.staging[i] = (float*)staging_ptrs[i]; t.flags[i] = (uint32_t*)flag_ptrs[i]; }
+    const int chunks = (int)((n_elems + kChunk - 1) / kChunk);
+    ar_oneshot_kernel<<<chunks, 1024, 0, st>>>(t, (uint32_t*)epoch, status, y, (int)n_elems, (int)rank, (int)world,
+                                               (int)max_elems, (int)max_spins);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_wait_flag(const void* flag, int64_t want, int64_t max_spins, int* status, cudaStream_t st) {
+    wait_flag_kernel<<<1, 1, 0, st>>>((const uint32_t*)flag, (uint32_t)want, (int)max_spins, status);
+    return FB_LAUNCH_CHECK();
+}

@@ -253,12 +253,12 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
             for (int r = 0; r < RT; ++r) nxt[r] = load_wfrag(wa[r] + (size_t)kn * 128, wb[r] + (size_t)kn * 128);
         }
         uint32_t xh[XW], xl[XW];
-        load_xfrag<XW>(xhi, xlo, ldx, g, mrows, kb * KB + t * (KB / 4), xh, xl);
+        load_xfrag<XW, !FP8>(xhi, xlo, ldx, g, mrows, kb * KB + t * (KB / 4), xh, xl);
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
             if (FP8) {
                 float d[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_wfrag_fp8(d, cur[r], reinterpret_cast<const uint32_t(&)[16]>(xh), reinterpret_cast<const uint32_t(&)[16]>(xl));
+                mma_wfrag_fp8<false>(d, cur[r], reinterpret_cast<const uint32_t(&)[16]>(xh), reinterpret_cast<const uint32_t(&)[16]>(xl));
                 const float sc = __ldg(scales + (size_t)((n0 + r * 16) >> 7) * kblocks + kb);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(d[c], sc, acc[r][c]);

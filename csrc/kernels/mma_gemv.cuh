@@ -61,7 +61,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
 // Activation fragment of one lane for a k-block: WORDS 32-bit words of hi and of lo
 // (2 elements per word), taken from activation row g = lane >> 2 at element offset k0.
 // Rows >= mrows read as zero.
-template <int WORDS>
+template <int WORDS, bool LO = true>
 __device__ __forceinline__ void load_xfrag(const uint16_t* __restrict__ hi, const uint16_t* __restrict__ lo, int ld,
                                            int g, int mrows, int k0, uint32_t (&xh)[WORDS], uint32_t (&xl)[WORDS]) {
     if (g < mrows) {
@@ -69,9 +69,12 @@ __device__ __forceinline__ void load_xfrag(const uint16_t* __restrict__ hi, cons
         const uint4* pl = reinterpret_cast<const uint4*>(lo + (size_t)g * ld + k0);
 #pragma unroll
         for (int i = 0; i < WORDS / 4; ++i) {
-            const uint4 a = __ldg(ph + i), b = __ldg(pl + i);
+            const uint4 a = __ldg(ph + i);
             xh[4 * i] = a.x; xh[4 * i + 1] = a.y; xh[4 * i + 2] = a.z; xh[4 * i + 3] = a.w;
-            xl[4 * i] = b.x; xl[4 * i + 1] = b.y; xl[4 * i + 2] = b.z; xl[4 * i + 3] = b.w;
+            if (LO) {
+                const uint4 b = __ldg(pl + i);
+                xl[4 * i] = b.x; xl[4 * i + 1] = b.y; xl[4 * i + 2] = b.z; xl[4 * i + 3] = b.w;
+            }
         }
     } else {
 #pragma unroll
@@ -105,7 +108,10 @@ __device__ __forceinline__ void mma_wfrag_bf16(float (&d)[4], const WFrag& f, co
 }
 
 // e4m3 weights, k-block = 128 elements (one scale block): the lane's 32 bytes of each row
-// feed 8 MMAs (x2).  d receives the UNSCALED block sum.
+// feed 8 MMAs.  d receives the UNSCALED block sum.  LO adds the low activation half (8 more
+// MMAs); the f16 high half alone keeps 11 mantissa bits, and the legacy tensor pipe is the
+// co-bottleneck of the fp8 kernels, so the expert and dense-FFN kernels run hi-only.
+template <bool LO>
 __device__ __forceinline__ void mma_wfrag_fp8(float (&d)[4], const WFrag& f, const uint32_t (&xh)[16],
                                               const uint32_t (&xl)[16]) {
     const uint32_t A[8] = {f.a0.x, f.a0.y, f.a0.z, f.a0.w, f.a1.x, f.a1.y, f.a1.z, f.a1.w};
@@ -116,6 +122,6 @@ __device__ __forceinline__ void mma_wfrag_fp8(float (&d)[4], const WFrag& f, con
         const uint32_t a_lo = e4m3x2_to_f16x2((uint16_t)(A[j] & 0xffffu)), a_hi = e4m3x2_to_f16x2((uint16_t)(A[j] >> 16));
         const uint32_t b_lo = e4m3x2_to_f16x2((uint16_t)(B[j] & 0xffffu)), b_hi = e4m3x2_to_f16x2((uint16_t)(B[j] >> 16));
         mma_f16_16816(d, a_lo, b_lo, a_hi, b_hi, xh[2 * j], xh[2 * j + 1]);
-        mma_f16_16816(d, a_lo, b_lo, a_hi, b_hi, xl[2 * j], xl[2 * j + 1]);
+        if (LO) mma_f16_16816(d, a_lo, b_lo, a_hi, b_hi, xl[2 * j], xl[2 * j + 1]);
     }
 }

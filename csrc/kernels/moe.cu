@@ -257,11 +257,11 @@ moe_gate_up_mma_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
             for (int q = 0; q < 2; ++q) nxt[q] = load_wfrag(wa[q] + (size_t)kn * 128, wb[q] + (size_t)kn * 128);
         }
         uint32_t xh[16], xl[16];
-        load_xfrag<16>(xh_row, xl_row, 0, g, 1, kb * 128 + t * 32, xh, xl);  // column 0 only
+        load_xfrag<16, false>(xh_row, xl_row, 0, g, 1, kb * 128 + t * 32, xh, xl);  // column 0 only
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_wfrag_fp8(d, cur[q], xh, xl);
+            mma_wfrag_fp8<false>(d, cur[q], xh, xl);
             const float sc = __ldg(S + (size_t)rowblk[q] * kb_n + kb);
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[q][c] = fmaf(d[c], sc, acc[q][c]);
@@ -320,9 +320,9 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
             const int s = it / kb_n, kb = it % kb_n;
             const int pair = r * topk + s;
             uint32_t xh[16], xl[16];
-            load_xfrag<16>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, kb * 128 + t * 32, xh, xl);
+            load_xfrag<16, false>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, kb * 128 + t * 32, xh, xl);
             float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_wfrag_fp8(d, cur, xh, xl);
+            mma_wfrag_fp8<false>(d, cur, xh, xl);
             const float sc = __ldg(S2 + (size_t)le_cur * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc, acc[c]);

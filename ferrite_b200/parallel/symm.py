@@ -1,0 +1,104 @@
+"""Symmetric peer memory over CUDA IPC and the one-shot all-reduce built on it.
+
+One process per GPU: every rank allocates its region with ``cudaMalloc``, exports it with
+``cudaIpcGetMemHandle``, and opens the peers' handles, so that kernels can store straight
+into a peer's HBM over NVLink.  Handles travel through ``torch.distributed`` (any backend).
+The reference keeps its ranks as threads of one process and enables peer access directly
+(``crates/ferrite-kernel/src/cuda.rs:6607-6762``); the collective itself is described in
+``csrc/kernels/collective.cu``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+
+FB_OK, FB_TIMEOUT, FB_BAD_CANARY, FB_BAD_ARG = 0, 1, 2, 3
+
+
+class CollectiveTimeout(RuntimeError):
+    def __init__(self, peer: int, epoch: int, chunk: int):
+        super().__init__(f"all-reduce wait ran out: peer {peer}, epoch {epoch}, chunk {chunk}")
+        self.peer, self.epoch, self.chunk = peer, epoch, chunk
+
+
+class SymmetricRegion:
+    """``nbytes`` of zeroed device memory on every rank, each rank holding pointers to all."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
+        self.K = _lib.lib()
+        self.nbytes, self.rank, self.world = nbytes, rank, world
+        p = ctypes.c_void_p()
+        self._check(self.K.lib.fb_symm_alloc(ctypes.c_int64(nbytes), ctypes.byref(p)), "fb_symm_alloc")
+        self.local = p.value
+        handle = ctypes.create_string_buffer(64)
+        self._check(self.K.lib.fb_ipc_get_handle(ctypes.c_void_p(self.local), handle), "fb_ipc_get_handle")
+        handles: List[Optional[bytes]] = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for r in range(world):
+            if r == rank:
+                self.ptrs.append(self.local)
+                continue
+            q = ctypes.c_void_p()
+            self._check(self.K.lib.fb_ipc_open(ctypes.c_char_p(handles[r]), ctypes.byref(q)), "fb_ipc_open")
+            self.ptrs.append(q.value)
+            self._opened.append(q.value)
+        dist.barrier(group=group)
+
+    @staticmethod
+    def _check(rc: int, what: str):
+        if rc != 0:
+            raise _lib.KernelError(f"{what} failed with CUDA error {rc}")
+
+    def close(self):
+        for q in self._opened:
+            self.K.lib.fb_ipc_close(ctypes.c_void_p(q))
+        self._opened = []
+        if self.local:
+            self.K.lib.fb_symm_free(ctypes.c_void_p(self.local))
+            self.local = 0
+
+
+class P2PAllReduce:
+    """Callable ``f(view)``: in-place sum of a contiguous f32 view across the ranks, one
+    kernel launch on the current stream.  ``check()`` reads the status word on the host."""
+
+    def __init__(self, device, rank: int, world: int, max_elems: int, max_spins: int = 2_000_000, group=None):
+        self.K = _lib.lib()
+        self.rank, self.world, self.max_spins = rank, world, max_spins
+        mc, ce = ctypes.c_int(), ctypes.c_int()
+        self.K.lib.fb_ar_limits(ctypes.byref(mc), ctypes.byref(ce))
+        self.max_chunks, self.chunk = mc.value, ce.value
+        self.max_elems = min((max_elems + self.chunk - 1) // self.chunk, self.max_chunks) * self.chunk
+        self.staging = SymmetricRegion(2 * world * self.max_elems * 4, rank, world, group)
+        self.flags = SymmetricRegion(2 * world * self.max_chunks * 4, rank, world, group)
+        self.epoch = torch.zeros(self.max_chunks, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        arr = ctypes.c_void_p * world
+        self._sp = arr(*self.staging.ptrs)
+        self._fp = arr(*self.flags.ptrs)
+        self.calls = 0
+
+    def __call__(self, view: torch.Tensor):
+        n = view.numel()
+        assert view.is_contiguous() and view.dtype == torch.float32 and n <= self.max_elems and n % 4 == 0
+        self.K.call("fb_ar_oneshot", self._sp, self._fp, self.epoch, self.status, view, n, self.rank, self.world,
+                    self.max_elems, self.max_spins)
+        self.calls += 1
+
+    def check(self):
+        """Host-side read of the status word (synchronises the device)."""
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3])
+
+    def close(self):
+        self.staging.close()
+        self.flags.close()

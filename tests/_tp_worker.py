@@ -1,0 +1,85 @@
+"""Worker run under torch.distributed.run by test_gpu_multi.py (one process per GPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from ferrite_b200.config import EngineConfig, GlmConfig  # noqa: E402
+from ferrite_b200.engine.glm_engine import GlmEngine  # noqa: E402
+from ferrite_b200.models.glm import DictSource  # noqa: E402
+from ferrite_b200.models.glm_weights import random_weights  # noqa: E402
+from ferrite_b200.parallel.symm import P2PAllReduce  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ar = P2PAllReduce(dev, rank, world, max_elems=64 * 4096)
+    # 1. one-shot all-reduce == NCCL all-reduce, bit-identical across ranks, eager and in a graph
+    for n in (4096, 3 * 4096, 16 * 4096 + 8, 64 * 4096):
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for it in range(3):
+            x = torch.randn(n, device=dev, generator=g)
+            want = x.clone()
+            dist.all_reduce(want)
+            got = x.clone()
+            ar(got)
+            torch.cuda.synchronize()
+            ar.check()
+            assert torch.allclose(got, want, atol=1e-4, rtol=1e-5), (n, it, (got - want).abs().max().item())
+            ref = got.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, got), "ranks disagree bitwise"
+    buf = torch.ones(4096, device=dev) * (rank + 1)
+    ar(buf)  # warm-up outside capture
+    buf.fill_(rank + 1)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ar(buf)
+    total = world * (world + 1) / 2
+    for it in range(4):
+        buf.fill_(rank + 1)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.all(buf == total), (it, buf[:4])
+    ar.check()
+    # 2. tensor-parallel engine == single-rank engine, token for token (greedy and MTP)
+    for name in ("tiny", "golden4"):
+        cfg = getattr(GlmConfig, name)()
+        w = random_weights(cfg, 0, std=0.05)
+        prompt = torch.randint(0, cfg.vocab_size, (29,), generator=torch.Generator().manual_seed(1)).tolist()
+        outs = {}
+        for mtp_n in (1, 3):
+            ecfg = EngineConfig(max_ctx=256, mtp_n=mtp_n, kv_dtype="f32", tp=world)
+            eng = GlmEngine(cfg, ecfg, DictSource(w, dev), rank=rank, world=world, device=dev, allreduce=ar,
+                            prefill_rows=16)
+            outs[mtp_n], _ = eng.generate(prompt, 14)
+            ar.check()
+        assert outs[1] == outs[3], (name, outs)
+        t = torch.tensor(outs[1], device=dev)
+        t0 = t.clone()
+        dist.broadcast(t0, 0)
+        assert torch.equal(t, t0), "ranks emitted different tokens"
+        if rank == 0:
+            e1 = GlmEngine(cfg, EngineConfig(max_ctx=256, mtp_n=1, kv_dtype="f32"), DictSource(w, dev), device=dev,
+                           prefill_rows=16)
+            single, _ = e1.generate(prompt, 14)
+            # shards quantise their own fp8 blocks, so a rare late divergence is tolerated:
+            same = sum(a == b for a, b in zip(single, outs[1]))
+            assert same >= 10, (name, single, outs[1])
+            print(f"{name}: tp{world} tokens {outs[1]} (tp1 agreement {same}/14)")
+    dist.barrier()
+    ar.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("TP_WORKER_OK")
+
+
+if __name__ == "__main__":
+    main()

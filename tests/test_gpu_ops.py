@@ -459,7 +459,9 @@ def test_gemv_mma_fp8(K, m, N, K_):
     x = rnd(m, K_, seed=4)
     od = torch.zeros(m, N, device="cuda")
     K.call("fb_gemv_mma_fp8", dev(q), dev(s), dev(to_split(x)), K_, m * K_, od, N, m, N, K_, 0, None, 0, 0, 0)
-    check("gemv mma fp8", od, x @ R.dequant_fp8_block(q, s).t(), 2e-3)
+    # e4m3 weights run with f16 (11-bit) activations: tolerance is relative to the output scale
+    want = x @ R.dequant_fp8_block(q, s).t()
+    check("gemv mma fp8", od, want, 2e-3 * want.abs().max().item())
 
 
 @pytest.mark.parametrize("n,E,topk,I,H", [(1, 8, 2, 128, 256), (3, 16, 8, 256, 4096), (2, 6, 3, 2048, 512)])
@@ -489,8 +491,8 @@ def test_moe_experts_mma(K, n, E, topk, I, H):
             a = R.swiglu_limited(x[r] @ W13[:I].t(), x[r] @ W13[I:].t(), 10.0) * wts[r, s]
             act_ref[r * topk + s] = a
             want[r] += a @ R.dequant_fp8_block(q2[e], s2[e]).t()
-    check("moe mma act", unsplit(asp.cpu(), 1), act_ref, 2e-3)
-    check("moe mma out", out, want, 5e-3)
+    check("moe mma act", unsplit(asp.cpu(), 1), act_ref, 2e-3 * act_ref.abs().max().item())
+    check("moe mma out", out, want, 3e-3 * want.abs().max().item())
     # expert-parallel masking
     lo, cnt = E // 2, E - E // 2
     out2 = torch.zeros(n, H, device="cuda")
@@ -504,4 +506,4 @@ def test_moe_experts_mma(K, n, E, topk, I, H):
             e = int(ids[r, s])
             if e >= lo:
                 want2[r] += act_ref[r * topk + s] @ R.dequant_fp8_block(q2[e], s2[e]).t()
-    check("moe mma ep", out2, want2, 5e-3)
+    check("moe mma ep", out2, want2, 3e-3 * want2.abs().max().item())
