@@ -1,0 +1,167 @@
+"""OpenAI-compatible HTTP API (FastAPI): chat completions with SSE streaming, models,
+health, stats and shutdown.
+
+Routes and payloads follow the reference server (``crates/ferrite-http/src/api.rs:68-393``,
+``sse.rs:1-193``): ``POST /v1/chat/completions`` (``messages`` required and non-empty, else
+400 ``invalid_request_error``; ``max_completion_tokens`` wins over ``max_tokens``, default 256;
+``temperature`` accepted and ignored -- decoding is greedy; unknown fields ignored),
+``GET /v1/models``, ``GET /health``, ``GET /v1/stats``, ``POST /shutdown``.  A stream sends an
+optional comment line with the admission result, one ``chat.completion.chunk`` per engine
+event (bytes of an incomplete UTF-8 character are held back), a final frame with
+``finish_reason`` (and ``usage`` if asked), then ``data: [DONE]``; closing the connection
+cancels the request.
+"""
+
+import asyncio
+import json
+import os
+import queue as _queue
+import threading
+import time
+import uuid
+from typing import List, Optional
+
+from .engine import EngineDriver, RequestSpec, Usage
+from .tokenizer import ChatTokenizer, utf8_holdback
+
+
+def _err(msg: str, status: int = 400):
+    from fastapi.responses import JSONResponse
+    return JSONResponse({"error": {"message": msg, "type": "invalid_request_error"}}, status_code=status)
+
+
+def _usage(u: Optional[Usage]) -> dict:
+    u = u or Usage()
+    return {"prompt_tokens": u.prompt_tokens, "completion_tokens": u.completion_tokens,
+            "total_tokens": u.total_tokens, "cached_tokens": u.cached_tokens}
+
+
+def finish_reason(reason: str) -> str:
+    return reason if reason in ("stop", "length") else ("stop" if reason == "cancelled" else reason)
+
+
+def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str = "glm-5.3-flash",
+               on_shutdown=None):
+    from fastapi import FastAPI, Request
+    from fastapi.responses import JSONResponse, StreamingResponse
+
+    app = FastAPI(title="ferrite_b200")
+
+    async def _next_event(sink):
+        loop = asyncio.get_running_loop()
+        while True:
+            try:
+                return sink.get_nowait()
+            except _queue.Empty:
+                await asyncio.sleep(0.001)
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        try:
+            body = await request.json()
+        except Exception:
+            return _err("request body is not valid JSON")
+        msgs = body.get("messages") if isinstance(body, dict) else None
+        if not isinstance(msgs, list) or not msgs:
+            return _err("`messages` must be a non-empty array")
+        for m in msgs:
+            if not isinstance(m, dict) or "role" not in m or not isinstance(m.get("content", ""), str):
+                return _err("each message needs a `role` and a string `content`")
+        max_new = body.get("max_completion_tokens", body.get("max_tokens", 256))
+        if not isinstance(max_new, int) or max_new < 1:
+            return _err("`max_tokens` must be a positive integer")
+        model = body.get("model") or model_name
+        stream = bool(body.get("stream", False))
+        include_usage = bool(body.get("include_usage", False)) or bool((body.get("stream_options") or {}).get("include_usage"))
+        prompt = tokenizer.encode_chat(msgs)
+        spec = RequestSpec(prompt, max_new, tuple(tokenizer.stop_ids()))
+        rid, sink = driver.submit(spec)
+        cid = "chatcmpl-" + uuid.uuid4().hex[:24]
+        created = int(time.time())
+
+        if not stream:
+            ids: List[int] = []
+            usage, reason = None, "stop"
+            while True:
+                ev = await _next_event(sink)
+                if ev.kind == "tokens":
+                    ids.extend(ev.ids)
+                elif ev.kind == "finished":
+                    usage, reason = ev.usage, ev.reason
+                    break
+            return JSONResponse({
+                "id": cid, "object": "chat.completion", "created": created, "model": model,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": tokenizer.decode(ids)},
+                             "finish_reason": finish_reason(reason)}],
+                "usage": _usage(usage)})
+
+        def frame(delta: dict, fin=None, usage=None) -> str:
+            obj = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": model,
+                   "choices": [{"index": 0, "delta": delta, "finish_reason": fin}]}
+            if usage is not None:
+                obj["usage"] = usage
+            return "data: " + json.dumps(obj, ensure_ascii=False) + "\n\n"
+
+        async def gen():
+            held = b""
+            done = False
+            try:
+                while True:
+                    ev = await _next_event(sink)
+                    if ev.kind == "admitted":
+                        yield f": ferrite: admitted prefix_hit={str(ev.prefix_hit).lower()} prompt_tokens={ev.prompt_tokens}\n\n"
+                    elif ev.kind == "tokens":
+                        data = held + tokenizer.decode_bytes(ev.ids)
+                        hb = utf8_holdback(data)
+                        held = data[len(data) - hb:] if hb else b""
+                        text = data[:len(data) - hb].decode("utf-8", errors="replace")
+                        if text:
+                            yield frame({"content": text})
+                    else:
+                        tail = held.decode("utf-8", errors="replace")
+                        yield frame({"content": tail} if tail else {}, fin=finish_reason(ev.reason),
+                                    usage=_usage(ev.usage) if include_usage else None)
+                        yield "data: [DONE]\n\n"
+                        done = True
+                        return
+            finally:
+                if not done:  # the client went away: stop generating for it
+                    driver.cancel(rid)
+
+        return StreamingResponse(gen(), media_type="text/event-stream",
+                                 headers={"Cache-Control": "no-cache", "Connection": "keep-alive"})
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "created": 0, "owned_by": "ferrite"}]}
+
+    @app.get("/health")
+    async def health():
+        e = driver.stats().get("engine", {})
+        return {"status": "ok", "engine": {"ticks": e.get("ticks", 0), "tokens_committed": e.get("tokens_committed", 0)}}
+
+    @app.get("/v1/stats")
+    async def stats():
+        return driver.stats()
+
+    @app.post("/shutdown")
+    async def shutdown():
+        def later():
+            time.sleep(0.3)  # let the reply (and any profiler) flush first
+            if on_shutdown:
+                on_shutdown()
+            else:
+                os._exit(0)
+        threading.Thread(target=later, daemon=True).start()
+        return {"status": "shutting_down"}
+
+    return app
+
+
+def serve(engine, tokenizer: ChatTokenizer, host: str = "127.0.0.1", port: int = 8000,
+          model_name: str = "glm-5.3-flash"):
+    """Blocking: run the HTTP server over ``engine`` until /shutdown."""
+    import uvicorn
+    driver = EngineDriver(engine)
+    app = create_app(driver, tokenizer, model_name)
+    uvicorn.run(app, host=host, port=port, log_level="warning")
