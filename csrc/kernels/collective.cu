@@ -18,6 +18,9 @@
 // This is the counterpart of the reference's AR v5 (kernels/cuda/ferrite_kernels.cu:8968-9524),
 // whose waiter parks forever or traps on timeout (:9180-9229).
 #include "common.cuh"
+#include <string.h>
+
+int g_fb_pdl = 0;  // measured neutral on the decode chain (kernel time, not launch gaps, dominates); opt-in
 
 namespace {
 
@@ -98,6 +101,7 @@ __device__ __forceinline__ float4 ar_chunk(const ArTables& t, uint32_t* epoch, i
 __global__ void __launch_bounds__(1024)
 ar_oneshot_kernel(ArTables t, uint32_t* epoch, int* status, float* y, int n_elems, int rank, int world,
                   int max_elems, int max_spins) {
+    PDL_PROLOGUE();
     const int chunk = blockIdx.x;
     const int i = chunk * kChunk + threadIdx.x * 4;
     const bool valid = i < n_elems;
@@ -110,6 +114,7 @@ ar_oneshot_kernel(ArTables t, uint32_t* epoch, int* status, float* y, int n_elem
 // A wait that nothing satisfies: used by the failure-detection test to check that a bounded
 // wait gives up with a status word and leaves the context usable.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, int max_spins, int* status) {
+    PDL_PROLOGUE();
     int spins = 0;
     while (ld_acquire_sys(flag) < want) {
         if (++spins > max_spins) {
@@ -142,6 +147,9 @@ FB_API int fb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 FB_API int fb_memcpy_d2h(void* dst, const void* src, int64_t bytes) {
     return (int)cudaMemcpy(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost);
 }
+// 1 = launch every kernel with programmatic dependent launch allowed, 0 = plain (default).
+FB_API int fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; return 0; }
+
 FB_API int fb_ar_limits(int* max_chunks, int* chunk_elems) {
     *max_chunks = kMaxChunks; *chunk_elems = kChunk;
     return 0;
@@ -158,12 +166,12 @@ FB_API int fb_ar_oneshot(const void* const* staging_ptrs, const void* const* fla
     ArTables t;
     for (int i = 0; i < world; ++i) { t.staging[i] = (float*)staging_ptrs[i]; t.flags[i] = (uint32_t*)flag_ptrs[i]; }
     const int chunks = (int)((n_elems + kChunk - 1) / kChunk);
-    ar_oneshot_kernel<<<chunks, 1024, 0, st>>>(t, (uint32_t*)epoch, status, y, (int)n_elems, (int)rank, (int)world,
+    FB_LAUNCH((ar_oneshot_kernel), chunks, 1024, 0, st, t, (uint32_t*)epoch, status, y, (int)n_elems, (int)rank, (int)world,
                                                (int)max_elems, (int)max_spins);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_wait_flag(const void* flag, int64_t want, int64_t max_spins, int* status, cudaStream_t st) {
-    wait_flag_kernel<<<1, 1, 0, st>>>((const uint32_t*)flag, (uint32_t)want, (int)max_spins, status);
+    FB_LAUNCH((wait_flag_kernel), 1, 1, 0, st, (const uint32_t*)flag, (uint32_t)want, (int)max_spins, status);
     return FB_LAUNCH_CHECK();
 }

@@ -25,6 +25,37 @@ enum FbStatus : int {
 
 #define FB_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+// ---- programmatic dependent launch (PDL) ---------------------------------------------------
+// Every kernel is launched with programmatic stream serialization allowed and starts with
+// PDL_PROLOGUE(): it lets the NEXT kernel in the stream be scheduled right away and then
+// waits until the PREVIOUS kernel has completed and flushed its memory.  Launch latency and
+// the ramp-up of a kernel therefore overlap the tail of its predecessor; because every
+// kernel waits before it touches any buffer, completion is transitive along the stream.
+// Only data that no kernel of the step writes (weights) may be read before pdl_wait().
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define PDL_PROLOGUE() do { pdl_launch(); pdl_wait(); } while (0)
+
+extern int g_fb_pdl;  // 1 = launch with the PDL attribute, 0 = plain launches (default)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_fb_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#define FB_LAUNCH(kernel, grid, block, smem, st, ...) \
+    (void)fb_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), st, __VA_ARGS__)
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -38,6 +38,7 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
                 KVT* __restrict__ lat_cache, float* __restrict__ kidx_cache, float* __restrict__ kgate_cache,
                 const RowMeta* __restrict__ meta, PageView pv, int QL, int DL, int ID, int IH, float eps,
                 SplitBuf osp) {
+    PDL_PROLOGUE();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const RowMeta m = meta[r];
@@ -85,6 +86,7 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
 __global__ void dsa_pool_kernel(const float* __restrict__ kidx_cache, const float* __restrict__ kgate_cache,
                                 const float* __restrict__ ape, float* __restrict__ pool_cache,
                                 const RowMeta* __restrict__ meta, PageView pv, int ID, int kpool) {
+    PDL_PROLOGUE();
     const RowMeta m = meta[blockIdx.x];
     const int p = m.pos / kpool;
     const int ppp = pv.page_size / kpool;  // pools per page
@@ -116,6 +118,7 @@ __global__ void __launch_bounds__(128)
 dsa_score_kernel(const float* __restrict__ qi, int ld_qi, const float* __restrict__ wi,
                  const float* __restrict__ pool_cache, float* __restrict__ scores, int ld_sc,
                  const RowMeta* __restrict__ meta, PageView pv, int IH, int kpool) {
+    PDL_PROLOGUE();
     extern __shared__ float sq[];  // [IH][ID] then [IH]
     float* sw = sq + IH * ID;
     const int r = blockIdx.y;
@@ -186,6 +189,7 @@ __device__ __forceinline__ uint32_t block_scan_excl(uint32_t v, uint32_t* wsum, 
 __global__ void __launch_bounds__(1024)
 dsa_select_kernel(const float* __restrict__ scores, int ld_sc, int* __restrict__ idx, int ld_idx,
                   int* __restrict__ cnt, const RowMeta* __restrict__ meta, int kpool, int select_max) {
+    PDL_PROLOGUE();
     __shared__ uint32_t hist[256];
     __shared__ uint32_t wsum[32];
     __shared__ uint32_t s_total, s_prefix, s_need, s_below;
@@ -283,6 +287,7 @@ dsa_attn_partial_kernel(const float* __restrict__ qabs, const KVT* __restrict__ 
                         float* __restrict__ o_part, float* __restrict__ ml_part,
                         const RowMeta* __restrict__ meta, PageView pv, int hl, int nsplit,
                         int shard, int nshard, float scale) {
+    PDL_PROLOGUE();
     constexpr int QS = DL + 4;                 // padded row stride (floats)
     constexpr int HPT = (HLMAX + 15) / 16;     // heads per thread in the score phase
     constexpr int CPT = (DL >= 256) ? DL / 256 : 1;
@@ -435,6 +440,7 @@ dsa_attn_partial_kernel(const float* __restrict__ qabs, const KVT* __restrict__ 
 __global__ void dsa_attn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                       float* __restrict__ ctx, float* __restrict__ lse_out, int hl, int DL,
                                       int nsplit, int normalise, SplitBuf osp) {
+    PDL_PROLOGUE();
     const int r = blockIdx.y, h = blockIdx.x;
     float M = -INFINITY;
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(((size_t)r * nsplit + s) * hl + h) * 2]);
@@ -476,10 +482,10 @@ FB_API int fb_dsa_prep(const float* proj, int64_t ld, const float* qa_ln, const 
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     PageView pv = make_pv(page_table, max_pages, page_size);
     if (kv_f32)
-        dsa_prep_kernel<float><<<n, 512, 0, st>>>(proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
+        FB_LAUNCH((dsa_prep_kernel<float>), n, 512, 0, st, proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
             (float*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     else
-        dsa_prep_kernel<__nv_bfloat16><<<n, 512, 0, st>>>(proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
+        FB_LAUNCH((dsa_prep_kernel<__nv_bfloat16>), n, 512, 0, st, proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
             (__nv_bfloat16*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     return FB_LAUNCH_CHECK();
 }
@@ -488,7 +494,7 @@ FB_API int fb_dsa_pool(const float* kidx_cache, const float* kgate_cache, const 
                        const void* meta, const int* page_table, int64_t max_pages, int64_t page_size,
                        int64_t n, int64_t ID, int64_t kpool, cudaStream_t st) {
     PageView pv = make_pv(page_table, max_pages, page_size);
-    dsa_pool_kernel<<<n, 128, 0, st>>>(kidx_cache, kgate_cache, ape, pool_cache, (const RowMeta*)meta, pv, (int)ID, (int)kpool);
+    FB_LAUNCH((dsa_pool_kernel), n, 128, 0, st, kidx_cache, kgate_cache, ape, pool_cache, (const RowMeta*)meta, pv, (int)ID, (int)kpool);
     return FB_LAUNCH_CHECK();
 }
 
@@ -501,9 +507,9 @@ FB_API int fb_dsa_scores(const float* qi, int64_t ld_qi, const float* wi, const 
     dim3 grid((unsigned)((max_pools + 127) / 128), (unsigned)n);
     size_t sm = (size_t)(IH * ID + IH) * sizeof(float);
 #define SC_ARGS qi, (int)ld_qi, wi, pool_cache, scores, (int)ld_sc, (const RowMeta*)meta, pv, (int)IH, (int)kpool
-    if (ID == 128) dsa_score_kernel<128><<<grid, 128, sm, st>>>(SC_ARGS);
-    else if (ID == 32) dsa_score_kernel<32><<<grid, 128, sm, st>>>(SC_ARGS);
-    else if (ID == 16) dsa_score_kernel<16><<<grid, 128, sm, st>>>(SC_ARGS);
+    if (ID == 128) FB_LAUNCH((dsa_score_kernel<128>), grid, 128, sm, st, SC_ARGS);
+    else if (ID == 32) FB_LAUNCH((dsa_score_kernel<32>), grid, 128, sm, st, SC_ARGS);
+    else if (ID == 16) FB_LAUNCH((dsa_score_kernel<16>), grid, 128, sm, st, SC_ARGS);
     else return (int)cudaErrorInvalidValue;
 #undef SC_ARGS
     return FB_LAUNCH_CHECK();
@@ -511,7 +517,7 @@ FB_API int fb_dsa_scores(const float* qi, int64_t ld_qi, const float* wi, const 
 
 FB_API int fb_dsa_select(const float* scores, int64_t ld_sc, int* idx, int64_t ld_idx, int* cnt,
                          const void* meta, int64_t n, int64_t kpool, int64_t select_max, cudaStream_t st) {
-    dsa_select_kernel<<<n, 1024, 0, st>>>(scores, (int)ld_sc, idx, (int)ld_idx, cnt, (const RowMeta*)meta,
+    FB_LAUNCH((dsa_select_kernel), n, 1024, 0, st, scores, (int)ld_sc, idx, (int)ld_idx, cnt, (const RowMeta*)meta,
                                           (int)kpool, (int)select_max);
     return FB_LAUNCH_CHECK();
 }
@@ -527,7 +533,7 @@ static int launch_attn(const float* qabs, const void* lat, const int* idx, int64
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
         if (e != cudaSuccess) return (int)e;
     }
-    k<<<dim3((unsigned)nsplit, (unsigned)n), 256, sm, st>>>(qabs, (const KVT*)lat, idx, (int)ld_idx, cnt, o_part,
+    FB_LAUNCH((k), dim3((unsigned)nsplit, (unsigned)n), 256, sm, st, qabs, (const KVT*)lat, idx, (int)ld_idx, cnt, o_part,
         ml_part, (const RowMeta*)meta, pv, (int)hl, (int)nsplit, (int)shard, (int)nshard, scale);
     return FB_LAUNCH_CHECK();
 }
@@ -558,7 +564,7 @@ FB_API int fb_dsa_attn_merge(const float* o_part, const float* ml_part, float* c
                              int64_t hl, int64_t DL, int64_t nsplit, int64_t normalise, void* s_base, int64_t s_ld,
                              int64_t s_plane, int64_t s_mask, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    dsa_attn_merge_kernel<<<dim3((unsigned)hl, (unsigned)n), 128, 0, st>>>(o_part, ml_part, ctx, lse_out, (int)hl,
+    FB_LAUNCH((dsa_attn_merge_kernel), dim3((unsigned)hl, (unsigned)n), 128, 0, st, o_part, ml_part, ctx, lse_out, (int)hl,
                                                                            (int)DL, (int)nsplit, (int)normalise, osp);
     return FB_LAUNCH_CHECK();
 }

@@ -29,6 +29,7 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
                  const RowMeta* __restrict__ meta, const int* __restrict__ group_first,
                  float* __restrict__ out, int ld_out, int H, int b_off, int nbuf, int snapshots, float lb, float eps,
                  SplitBuf osp) {
+    PDL_PROLOGUE();
     constexpr int RPT = DK / 4;  // state rows per thread
     __shared__ float qs[DK], ks[DK], vs[DK], dec[DK];
     __shared__ float part[4][DK];
@@ -170,9 +171,9 @@ FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, con
     dim3 grid((unsigned)H, (unsigned)n_groups);
 #define GDN_ARGS proj, (int)ld_proj, fb, gb, (int)ld_fg, conv_w, a_log, dt_bias, o_norm_w, state, conv_state, cur, \
         (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps, osp
-    if (dk == 128) gdn_fused_kernel<128><<<grid, 512, 0, st>>>(GDN_ARGS);
-    else if (dk == 64) gdn_fused_kernel<64><<<grid, 256, 0, st>>>(GDN_ARGS);
-    else if (dk == 32) gdn_fused_kernel<32><<<grid, 128, 0, st>>>(GDN_ARGS);
+    if (dk == 128) FB_LAUNCH((gdn_fused_kernel<128>), grid, 512, 0, st, GDN_ARGS);
+    else if (dk == 64) FB_LAUNCH((gdn_fused_kernel<64>), grid, 256, 0, st, GDN_ARGS);
+    else if (dk == 32) FB_LAUNCH((gdn_fused_kernel<32>), grid, 128, 0, st, GDN_ARGS);
     else return (int)cudaErrorInvalidValue;
 #undef GDN_ARGS
     return FB_LAUNCH_CHECK();

@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 gemv_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
             const float* __restrict__ x, int ldx, float* __restrict__ out, int ldo,
             int mrows, int N, int K, int group_rows, int accumulate) {
+    PDL_PROLOGUE();
     constexpr int VEC = FP8 ? 16 : 8;          // elements per 16-byte load
     constexpr int ESZ = FP8 ? 1 : 2;
     const int lane = threadIdx.x & 31;
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 gemv_splitk_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
                    const float* __restrict__ x, int ldx, float* __restrict__ out, int ldo,
                    int mrows, int N, int K, int accumulate) {
+    PDL_PROLOGUE();
     constexpr int VEC = FP8 ? 16 : 8;
     constexpr int ESZ = FP8 ? 1 : 2;
     __shared__ float red[kWarps][M * RB];
@@ -197,7 +199,7 @@ template <int M, int RB, bool FP8>
 int launch_sk(const void* W, const float* scales, const float* x, int ldx, float* out, int ldo, int mrows,
               int N, int K, int accumulate, cudaStream_t st) {
     dim3 grid((N + RB - 1) / RB), block(kWarps * 32);
-    gemv_splitk_kernel<M, RB, FP8><<<grid, block, 0, st>>>(static_cast<const uint8_t*>(W), scales, x, ldx, out, ldo,
+    FB_LAUNCH((gemv_splitk_kernel<M, RB, FP8>), grid, block, 0, st, static_cast<const uint8_t*>(W), scales, x, ldx, out, ldo,
                                                             mrows, N, K, accumulate);
     return FB_LAUNCH_CHECK();
 }
@@ -221,6 +223,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
                 const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
                 float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,
                 SplitBuf osplit) {
+    pdl_launch();  // weights are constant: the first k-block is fetched before pdl_wait()
     constexpr int KB = FP8 ? 128 : 64;
     constexpr int XW = FP8 ? 16 : 8;
     __shared__ float red[NW][RT][32][4];
@@ -246,6 +249,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
 #pragma unroll
         for (int r = 0; r < RT; ++r) cur[r] = load_wfrag(wa[r] + (size_t)warp * 128, wb[r] + (size_t)warp * 128);
     }
+    pdl_wait();
     for (int kb = warp; kb < nkb; kb += NW) {
         const int kn = kb + NW;
         if (kn < nkb) {
@@ -301,13 +305,13 @@ int launch_mma(const void* W, const float* scales, const uint16_t* xs, int ldx, 
     constexpr int KB = FP8 ? 128 : 64;
     const int nkb = K / KB;
     if (N >= 9472 && (group_rows == 0 || group_rows % 32 == 0)) {
-        gemv_mma_kernel<2, 8, FP8><<<(N + 31) / 32, 256, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+        FB_LAUNCH((gemv_mma_kernel<2, 8, FP8>), (N + 31) / 32, 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
     } else if (nkb >= 64 && N <= 8192) {  // few row tiles, long rows: split K over 16 warps
-        gemv_mma_kernel<1, 16, FP8><<<(N + 15) / 16, 512, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+        FB_LAUNCH((gemv_mma_kernel<1, 16, FP8>), (N + 15) / 16, 512, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
     } else if (nkb >= 8) {
-        gemv_mma_kernel<1, 8, FP8><<<(N + 15) / 16, 256, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+        FB_LAUNCH((gemv_mma_kernel<1, 8, FP8>), (N + 15) / 16, 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
     } else {
-        gemv_mma_kernel<1, 2, FP8><<<(N + 15) / 16, 64, 0, st>>>(w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
+        FB_LAUNCH((gemv_mma_kernel<1, 2, FP8>), (N + 15) / 16, 64, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit);
     }
     return FB_LAUNCH_CHECK();
 }
@@ -321,9 +325,9 @@ int launch_r(const void* W, const float* scales, const float* x, int ldx, float*
     const int warps = (N + R - 1) / R;
     dim3 grid((warps + kWarps - 1) / kWarps), block(kWarps * 32);
     const uint8_t* w8 = static_cast<const uint8_t*>(W);
-    if (R == 4) gemv_kernel<M, 4, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
-    else if (R == 2) gemv_kernel<M, 2, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
-    else gemv_kernel<M, 1, FP8><<<grid, block, 0, st>>>(w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    if (R == 4) FB_LAUNCH((gemv_kernel<M, 4, FP8>), grid, block, 0, st, w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    else if (R == 2) FB_LAUNCH((gemv_kernel<M, 2, FP8>), grid, block, 0, st, w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
+    else FB_LAUNCH((gemv_kernel<M, 1, FP8>), grid, block, 0, st, w8, scales, x, ldx, out, ldo, mrows, N, K, group_rows, accumulate);
     return FB_LAUNCH_CHECK();
 }
 
@@ -389,6 +393,7 @@ FB_API int fb_gemv_mma_fp8(const void* W, const float* scales, const void* xs, i
 
 namespace {
 __global__ void split_rows_kernel(const float* __restrict__ x, int ldx, SplitBuf s, int K) {
+    PDL_PROLOGUE();
     const int r = blockIdx.y;
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k < K) split_store(s, r, k, x[(size_t)r * ldx + k]);
@@ -399,6 +404,6 @@ __global__ void split_rows_kernel(const float* __restrict__ x, int ldx, SplitBuf
 FB_API int fb_split_rows(const float* x, int64_t ldx, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
                          int64_t m, int64_t K, cudaStream_t st) {
     SplitBuf s{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    split_rows_kernel<<<dim3((unsigned)((K + 255) / 256), (unsigned)m), 256, 0, st>>>(x, (int)ldx, s, (int)K);
+    FB_LAUNCH((split_rows_kernel), dim3((unsigned)((K + 255) / 256), (unsigned)m), 256, 0, st, x, (int)ldx, s, (int)K);
     return FB_LAUNCH_CHECK();
 }

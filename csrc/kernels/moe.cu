@@ -24,6 +24,7 @@ __device__ __forceinline__ uint32_t okey(float f) {
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int* __restrict__ ids,
                  float* __restrict__ wts, int E, int topk, float scaling) {
+    PDL_PROLOGUE();
     __shared__ unsigned long long wbest[8];
     __shared__ unsigned long long s_pick;
     __shared__ float s_sig[1024];
@@ -80,6 +81,7 @@ __global__ void __launch_bounds__(256)
 moe_gate_up_fp8_kernel(const uint8_t* __restrict__ W13, const float* __restrict__ S13,
                        const float* __restrict__ x, int ldx, const int* __restrict__ ids,
                        float* __restrict__ act, int topk, int I, int H, int e_lo, int e_cnt, float limit) {
+    PDL_PROLOGUE();
     const int pair = blockIdx.y;  // r * topk + s
     const int r = pair / topk;
     const int le = ids[pair] - e_lo;
@@ -153,6 +155,7 @@ moe_down_fp8_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
                     const float* __restrict__ act, const int* __restrict__ ids,
                     const float* __restrict__ wts, float* __restrict__ out, int ldo, int topk, int I, int H,
                     int e_lo, int e_cnt, int accumulate) {
+    PDL_PROLOGUE();
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const int c0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * CPW;
@@ -217,6 +220,7 @@ moe_gate_up_mma_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
                        const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
                        const int* __restrict__ ids, const float* __restrict__ wts, SplitBuf asplit,
                        int topk, int I, int H, int e_lo, int e_cnt, float limit) {
+    PDL_PROLOGUE();
     __shared__ float red[kGuWarps][2][32][4];
     const int pair = blockIdx.y;
     const int r = pair / topk;
@@ -292,6 +296,7 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
                     const uint16_t* __restrict__ ahi, const uint16_t* __restrict__ alo, int lda,
                     const int* __restrict__ ids, float* __restrict__ out, int ldo, int topk, int I, int H,
                     int e_lo, int e_cnt, int accumulate, SplitBuf osplit) {
+    PDL_PROLOGUE();
     __shared__ float red[8][32][4];
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -348,6 +353,7 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
 
 __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __restrict__ act, int I, float limit,
                               SplitBuf asplit) {
+    PDL_PROLOGUE();
     const int r = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= I) return;
@@ -363,7 +369,7 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __res
 FB_API int fb_moe_route(const float* logits, int64_t ld, const float* bias, int* ids, float* wts, int64_t n,
                         int64_t E, int64_t topk, float scaling, cudaStream_t st) {
     if (E > 1024 || topk > 32) return (int)cudaErrorInvalidValue;
-    moe_route_kernel<<<n, 256, 0, st>>>(logits, (int)ld, bias, ids, wts, (int)E, (int)topk, scaling);
+    FB_LAUNCH((moe_route_kernel), n, 256, 0, st, logits, (int)ld, bias, ids, wts, (int)E, (int)topk, scaling);
     return FB_LAUNCH_CHECK();
 }
 
@@ -377,9 +383,9 @@ FB_API int fb_moe_gate_up_fp8(const void* W13, const float* S13, const float* x,
     const int ipw = (I * pairs >= 148 * 8 * 8) ? 4 : ((I * pairs >= 148 * 8 * 4) ? 2 : 1);
     dim3 grid((unsigned)((I + 8 * ipw - 1) / (8 * ipw)), (unsigned)pairs);
 #define GU_ARGS (const uint8_t*)W13, S13, x, (int)ldx, ids, act, (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, limit
-    if (ipw == 4) moe_gate_up_fp8_kernel<4><<<grid, 256, 0, st>>>(GU_ARGS);
-    else if (ipw == 2) moe_gate_up_fp8_kernel<2><<<grid, 256, 0, st>>>(GU_ARGS);
-    else moe_gate_up_fp8_kernel<1><<<grid, 256, 0, st>>>(GU_ARGS);
+    if (ipw == 4) FB_LAUNCH((moe_gate_up_fp8_kernel<4>), grid, 256, 0, st, GU_ARGS);
+    else if (ipw == 2) FB_LAUNCH((moe_gate_up_fp8_kernel<2>), grid, 256, 0, st, GU_ARGS);
+    else FB_LAUNCH((moe_gate_up_fp8_kernel<1>), grid, 256, 0, st, GU_ARGS);
 #undef GU_ARGS
     return FB_LAUNCH_CHECK();
 }
@@ -390,14 +396,14 @@ FB_API int fb_moe_down_fp8(const void* W2, const float* S2, const float* act, co
                            int64_t e_lo, int64_t e_cnt, int64_t accumulate, cudaStream_t st) {
     if (I % 16) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)((H + 31) / 32), (unsigned)n);
-    moe_down_fp8_kernel<4><<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, act, ids, wts, out, (int)ldo, (int)topk,
+    FB_LAUNCH((moe_down_fp8_kernel<4>), grid, 256, 0, st, (const uint8_t*)W2, S2, act, ids, wts, out, (int)ldo, (int)topk,
                                                   (int)I, (int)H, (int)e_lo, (int)e_cnt, (int)accumulate);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_swiglu(const float* gu, int64_t ld, float* act, int64_t n, int64_t I, float limit, cudaStream_t st) {
     SplitBuf none{nullptr, 0, 0, 0};
-    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit, none);
+    FB_LAUNCH((swiglu_kernel), dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st, gu, (int)ld, act, (int)I, limit, none);
     return FB_LAUNCH_CHECK();
 }
 
@@ -405,7 +411,7 @@ FB_API int fb_swiglu(const float* gu, int64_t ld, float* act, int64_t n, int64_t
 FB_API int fb_swiglu_split(const float* gu, int64_t ld, float* act, void* s_base, int64_t s_ld, int64_t s_plane,
                            int64_t s_mask, int64_t n, int64_t I, float limit, cudaStream_t st) {
     SplitBuf sp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    swiglu_kernel<<<dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st>>>(gu, (int)ld, act, (int)I, limit, sp);
+    FB_LAUNCH((swiglu_kernel), dim3((unsigned)((I + 255) / 256), (unsigned)n), 256, 0, st, gu, (int)ld, act, (int)I, limit, sp);
     return FB_LAUNCH_CHECK();
 }
 
@@ -420,7 +426,7 @@ FB_API int fb_moe_gate_up_mma(const void* W13, const float* S13, const void* xs,
     const uint16_t* hi = (const uint16_t*)xs + 2 * xs_plane;
     SplitBuf asp{(uint16_t*)as_base, (int)as_ld, (int)as_plane, 2};
     dim3 grid((unsigned)((I + 15) / 16), (unsigned)(n * topk));
-    moe_gate_up_mma_kernel<<<grid, kGuWarps * 32, 0, st>>>((const uint8_t*)W13, S13, hi, hi + xs_plane, (int)xs_ld, ids, wts, asp,
+    FB_LAUNCH((moe_gate_up_mma_kernel), grid, kGuWarps * 32, 0, st, (const uint8_t*)W13, S13, hi, hi + xs_plane, (int)xs_ld, ids, wts, asp,
                                                  (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, limit);
     return FB_LAUNCH_CHECK();
 }
@@ -433,7 +439,7 @@ FB_API int fb_moe_down_mma(const void* W2, const float* S2, const void* as_base,
     const uint16_t* hi = (const uint16_t*)as_base + 2 * as_plane;
     SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
     dim3 grid((unsigned)((H + 15) / 16), (unsigned)n);
-    moe_down_mma_kernel<<<grid, 256, 0, st>>>((const uint8_t*)W2, S2, hi, hi + as_plane, (int)as_ld, ids, out, (int)ldo,
+    FB_LAUNCH((moe_down_mma_kernel), grid, 256, 0, st, (const uint8_t*)W2, S2, hi, hi + as_plane, (int)as_ld, ids, out, (int)ldo,
                                               (int)topk, (int)I, (int)H, (int)e_lo, (int)e_cnt, (int)accumulate, os);
     return FB_LAUNCH_CHECK();
 }

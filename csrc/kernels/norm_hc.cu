@@ -17,6 +17,7 @@ namespace {
 __global__ void prep_rows_kernel(const int* __restrict__ row_slot, const int* __restrict__ row_off,
                                  const int* __restrict__ row_gsize, const int* __restrict__ seq_len,
                                  RowMeta* __restrict__ meta, int n) {
+    PDL_PROLOGUE();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     RowMeta m;
@@ -34,6 +35,7 @@ __global__ void prep_rows_kernel(const int* __restrict__ row_slot, const int* __
 // seq_len[slot] += (accept ? accept[slot] : gsize) for the first row of each group.
 __global__ void advance_rows_kernel(const RowMeta* __restrict__ meta, const int* __restrict__ accept,
                                     int* __restrict__ seq_len, int n) {
+    PDL_PROLOGUE();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     RowMeta m = meta[r];
@@ -43,6 +45,7 @@ __global__ void advance_rows_kernel(const RowMeta* __restrict__ meta, const int*
 
 __global__ void embed_expand_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ emb,
                                     float* __restrict__ out, int H, int mult, int vocab) {
+    PDL_PROLOGUE();
     const int r = blockIdx.x;
     int id = ids[r];
     id = min(max(id, 0), vocab - 1);
@@ -57,6 +60,7 @@ __global__ void embed_expand_kernel(const int* __restrict__ ids, const __nv_bflo
 __global__ void rmsnorm_kernel(const float* __restrict__ a, const float* __restrict__ b,
                                float* __restrict__ sum_out, const float* __restrict__ w,
                                float* __restrict__ out, int d, int lda, int ldo, float eps, SplitBuf osp) {
+    PDL_PROLOGUE();
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -84,6 +88,7 @@ __global__ void mtp_prep_kernel(const int* __restrict__ ids, const __nv_bfloat16
                                 const float* __restrict__ h_prev, const float* __restrict__ enorm,
                                 const float* __restrict__ hnorm, float* __restrict__ out, int H,
                                 int vocab, float eps, SplitBuf osp) {
+    PDL_PROLOGUE();
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -119,6 +124,7 @@ __global__ void __launch_bounds__(kPmThreads)
 hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, const float* __restrict__ post,
                    const float* __restrict__ comb, const float* __restrict__ fn, float* __restrict__ acc,
                    int H, int mix) {
+    PDL_PROLOGUE();
     __shared__ float red[kPmThreads / 32][8];
     const int r = blockIdx.y, z = blockIdx.z;
     const int j = (blockIdx.x * kPmThreads + threadIdx.x) * 4;
@@ -200,6 +206,7 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
                     float* __restrict__ x_out, float* __restrict__ xn_out, float* __restrict__ post_out,
                     float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters,
                     SplitBuf osp) {
+    PDL_PROLOGUE();
     __shared__ float red[32];
     __shared__ float pre[8];
     const int r = blockIdx.x;
@@ -267,6 +274,7 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
 __global__ void hc_head_kernel(const float* __restrict__ R, const float* __restrict__ w,
                                float* __restrict__ h_final, float* __restrict__ xn, int H, int n, float eps,
                                SplitBuf osp) {
+    PDL_PROLOGUE();
     extern __shared__ float sh[];
     float* red = sh;
     float* buf = sh + 32;
@@ -292,6 +300,7 @@ __global__ void hc_head_kernel(const float* __restrict__ R, const float* __restr
 }
 
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, size_t n) {
+    PDL_PROLOGUE();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) o[i] = a[i] + b[i];
 }
@@ -300,18 +309,18 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
 
 FB_API int fb_prep_rows(const int* row_slot, const int* row_off, const int* row_gsize, const int* seq_len,
                         void* meta, int64_t n, cudaStream_t st) {
-    prep_rows_kernel<<<(n + 127) / 128, 128, 0, st>>>(row_slot, row_off, row_gsize, seq_len, (RowMeta*)meta, (int)n);
+    FB_LAUNCH((prep_rows_kernel), (n + 127) / 128, 128, 0, st, row_slot, row_off, row_gsize, seq_len, (RowMeta*)meta, (int)n);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_advance_rows(const void* meta, const int* accept, int* seq_len, int64_t n, cudaStream_t st) {
-    advance_rows_kernel<<<(n + 127) / 128, 128, 0, st>>>((const RowMeta*)meta, accept, seq_len, (int)n);
+    FB_LAUNCH((advance_rows_kernel), (n + 127) / 128, 128, 0, st, (const RowMeta*)meta, accept, seq_len, (int)n);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_embed_expand(const int* ids, const void* emb, float* out, int64_t n, int64_t H, int64_t mult,
                            int64_t vocab, cudaStream_t st) {
-    embed_expand_kernel<<<n, 256, 0, st>>>(ids, (const __nv_bfloat16*)emb, out, (int)H, (int)mult, (int)vocab);
+    FB_LAUNCH((embed_expand_kernel), n, 256, 0, st, ids, (const __nv_bfloat16*)emb, out, (int)H, (int)mult, (int)vocab);
     return FB_LAUNCH_CHECK();
 }
 
@@ -320,7 +329,7 @@ FB_API int fb_rmsnorm(const float* a, const float* b, float* sum_out, const floa
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + d) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    rmsnorm_kernel<<<n, 512, sm, st>>>(a, b, sum_out, w, out, (int)d, (int)lda, (int)ldo, eps, osp);
+    FB_LAUNCH((rmsnorm_kernel), n, 512, sm, st, a, b, sum_out, w, out, (int)d, (int)lda, (int)ldo, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 
@@ -329,7 +338,7 @@ FB_API int fb_mtp_prep(const int* ids, const void* emb, const float* h_prev, con
                        cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + H) * sizeof(float);
-    mtp_prep_kernel<<<dim3(n, 2), 512, sm, st>>>(ids, (const __nv_bfloat16*)emb, h_prev, enorm, hnorm, out,
+    FB_LAUNCH((mtp_prep_kernel), dim3(n, 2), 512, sm, st, ids, (const __nv_bfloat16*)emb, h_prev, enorm, hnorm, out,
                                                   (int)H, (int)vocab, eps, osp);
     return FB_LAUNCH_CHECK();
 }
@@ -340,7 +349,7 @@ FB_API int fb_hc_post_mix(const float* Rin, float* Rout, const float* y, const f
                           const float* fn, float* acc, int64_t n, int64_t H, int64_t mix, cudaStream_t st) {
     if (mix > kMaxMix || (H % 4) || (y && fn && Rin == Rout)) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)((H / 4 + kPmThreads - 1) / kPmThreads), (unsigned)n, fn ? kMixGroups : 1);
-    hc_post_mix_kernel<<<grid, kPmThreads, 0, st>>>(Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
+    FB_LAUNCH((hc_post_mix_kernel), grid, kPmThreads, 0, st, Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
     return FB_LAUNCH_CHECK();
 }
 
@@ -356,7 +365,7 @@ FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     if (mult != 4 || (H % 4) || H / 4 > 1024) return (int)cudaErrorInvalidValue;
     const int threads = (int)(((H / 4) + 31) / 32 * 32);
-    hc_pre_apply_kernel<<<n, threads, 0, st>>>(R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
+    FB_LAUNCH((hc_pre_apply_kernel), n, threads, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
                                                (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp);
     return FB_LAUNCH_CHECK();
 }
@@ -370,11 +379,11 @@ FB_API int fb_hc_head(const float* R, const float* w, float* h_final, float* xn,
                       int64_t mult, float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     size_t sm = (32 + H) * sizeof(float);
-    hc_head_kernel<<<n, 512, sm, st>>>(R, w, h_final, xn, (int)H, (int)mult, eps, osp);
+    FB_LAUNCH((hc_head_kernel), n, 512, sm, st, R, w, h_final, xn, (int)H, (int)mult, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_add(const float* a, const float* b, float* o, int64_t n, cudaStream_t st) {
-    add_kernel<<<(n + 255) / 256, 256, 0, st>>>(a, b, o, (size_t)n);
+    FB_LAUNCH((add_kernel), (n + 255) / 256, 256, 0, st, a, b, o, (size_t)n);
     return FB_LAUNCH_CHECK();
 }

@@ -21,6 +21,7 @@ constexpr int kSlices = 64;
 
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long long* __restrict__ part, int V) {
+    PDL_PROLOGUE();
     __shared__ unsigned long long wb[8];
     const int r = blockIdx.y;
     const int per = (V + kSlices - 1) / kSlices;
@@ -48,6 +49,7 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long lo
 
 __global__ void argmax_final_kernel(const unsigned long long* __restrict__ part, int* __restrict__ ids,
                                     float* __restrict__ vals, int id_stride, int vocab_offset) {
+    PDL_PROLOGUE();
     const int r = blockIdx.x;
     unsigned long long best = part[(size_t)r * kSlices + threadIdx.x];
     if (threadIdx.x + 32 < kSlices) {
@@ -82,6 +84,7 @@ mtp_accept_kernel(int* __restrict__ block_ids, const int* __restrict__ judges, i
                   const float* __restrict__ h_final, int* __restrict__ mtp_ids, float* __restrict__ mtp_h,
                   const int* __restrict__ group_slot, int* __restrict__ main_len, int* __restrict__ mtp_len,
                   int* __restrict__ cur, int nv, int H, int nbuf) {
+    PDL_PROLOGUE();
     __shared__ int s_k;
     const int g = blockIdx.x;
     int* blk = block_ids + (size_t)g * nv;
@@ -121,6 +124,7 @@ mtp_accept_kernel(int* __restrict__ block_ids, const int* __restrict__ judges, i
 
 __global__ void copy_i32_kernel(const int* __restrict__ src, int* __restrict__ dst, int n, int src_stride,
                                 int dst_stride) {
+    PDL_PROLOGUE();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[(size_t)i * dst_stride] = src[(size_t)i * src_stride];
 }
@@ -130,20 +134,20 @@ __global__ void copy_i32_kernel(const int* __restrict__ src, int* __restrict__ d
 // part: scratch of n*64 u64.  ids[r*id_stride] = argmax (+ vocab_offset); vals (optional) = max.
 FB_API int fb_argmax(const float* logits, int64_t ld, void* part, int* ids, float* vals, int64_t n, int64_t V,
                      int64_t id_stride, int64_t vocab_offset, cudaStream_t st) {
-    argmax_partial_kernel<<<dim3(kSlices, (unsigned)n), 256, 0, st>>>(logits, (int)ld, (unsigned long long*)part, (int)V);
-    argmax_final_kernel<<<n, 32, 0, st>>>((const unsigned long long*)part, ids, vals, (int)id_stride, (int)vocab_offset);
+    FB_LAUNCH((argmax_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V);
+    FB_LAUNCH((argmax_final_kernel), n, 32, 0, st, (const unsigned long long*)part, ids, vals, (int)id_stride, (int)vocab_offset);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_mtp_accept(int* block_ids, const int* judges, int* out_tokens, const float* h_final, int* mtp_ids,
                          float* mtp_h, const int* group_slot, int* main_len, int* mtp_len, int* cur,
                          int64_t n_groups, int64_t nv, int64_t H, int64_t nbuf, cudaStream_t st) {
-    mtp_accept_kernel<<<n_groups, 256, 0, st>>>(block_ids, judges, out_tokens, h_final, mtp_ids, mtp_h, group_slot,
+    FB_LAUNCH((mtp_accept_kernel), n_groups, 256, 0, st, block_ids, judges, out_tokens, h_final, mtp_ids, mtp_h, group_slot,
                                                 main_len, mtp_len, cur, (int)nv, (int)H, (int)nbuf);
     return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_copy_i32(const int* src, int* dst, int64_t n, int64_t src_stride, int64_t dst_stride, cudaStream_t st) {
-    copy_i32_kernel<<<(n + 127) / 128, 128, 0, st>>>(src, dst, (int)n, (int)src_stride, (int)dst_stride);
+    FB_LAUNCH((copy_i32_kernel), (n + 127) / 128, 128, 0, st, src, dst, (int)n, (int)src_stride, (int)dst_stride);
     return FB_LAUNCH_CHECK();
 }
