@@ -3,6 +3,9 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <pybind11/numpy.h>
+
+#include "safetensors_file.h"
 #include "tick_planner.h"
 
 namespace py = pybind11;
@@ -19,6 +22,30 @@ PYBIND11_MODULE(_runtime, m) {
     m.attr("build_id") = FB_RUNTIME_BUILD_ID;
     py::module_ g = m.def_submodule("golden", "f32 CPU golden ops");
     bind_golden(g);
+
+    py::class_<SafetensorsFile>(m, "SafetensorsFile")
+        .def(py::init<const std::string&>())
+        .def("header", [](const SafetensorsFile& f) { return py::bytes(f.header()); })
+        .def_property_readonly("data_offset", &SafetensorsFile::data_offset)
+        .def_property_readonly("data_size", &SafetensorsFile::data_size)
+        .def("view", [](py::object self, size_t begin, size_t end) {
+            // zero-copy uint8 view of data bytes [begin, end); keeps the file alive
+            auto& f = self.cast<SafetensorsFile&>();
+            if (end > f.data_size() || begin > end) throw std::out_of_range("view range");
+            return py::array_t<uint8_t>({(py::ssize_t)(end - begin)}, {1}, f.data() + begin, self);
+        })
+        .def("copy_rows", [](const SafetensorsFile& f, size_t begin, size_t row_bytes, size_t r0, size_t r1, size_t c0,
+                             size_t c1, py::array_t<uint8_t, py::array::c_style> dst) {
+            if ((size_t)dst.size() < (r1 - r0) * (c1 - c0)) throw std::out_of_range("dst too small");
+            f.copy_rows(begin, row_bytes, r0, r1, c0, c1, dst.mutable_data());
+        })
+        .def("dequant_e4m3_block", [](const SafetensorsFile& f, size_t begin, size_t scale_begin, size_t rows, size_t cols,
+                                      size_t blk, size_t r0, size_t r1) {
+            py::array_t<float> out({(py::ssize_t)(r1 - r0), (py::ssize_t)cols});
+            f.dequant_e4m3_block(begin, scale_begin, rows, cols, blk, r0, r1, out.mutable_data());
+            return out;
+        });
+    m.def("e4m3_to_f32", &e4m3_to_f32);
 
     m.def("cp_layer_range", &cp_layer_range);
     m.def("bucket_for", &bucket_for);
