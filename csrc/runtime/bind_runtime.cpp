@@ -164,6 +164,7 @@ PYBIND11_MODULE(_runtime, m) {
         }, py::arg("req"), py::arg("len"), py::arg("first_token") = -1, py::arg("snapshot_captured") = false)
         .def("ingest_decode", &BatchScheduler::ingest_decode)
         .def("get", &BatchScheduler::get, py::return_value_policy::reference_internal)
+        .def("reserve_pages", [](BatchScheduler& s, int n) { return s.pages().alloc(n); })
         .def("forget", &BatchScheduler::forget).def("idle", &BatchScheduler::idle).def("stats", &BatchScheduler::stats);
 
     m.attr("EV_ADMITTED") = (int)EV_ADMITTED; m.attr("EV_TOKENS") = (int)EV_TOKENS; m.attr("EV_FINISHED") = (int)EV_FINISHED;

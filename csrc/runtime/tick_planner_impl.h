@@ -59,7 +59,8 @@ public:
             Request& r = reqs_[id];
             if (r.state != RS_PREFILL) continue;
             const int n = (int)r.prompt.size();
-            const int boundary = (n / cfg_.page_size) * cfg_.page_size;  // last block boundary
+            // last block boundary strictly inside the prompt: a later identical prompt can resume there
+            const int boundary = ((n - 1) / cfg_.page_size) * cfg_.page_size;
             int start = r.prefilled;
             while (start < n && budget > 0) {
                 int len = std::min(budget, n - start);
@@ -207,7 +208,9 @@ private:
             const int nblk = (int)r.prompt.size() / ps;
             std::vector<int> pg(r.pages.begin(), r.pages.begin() + std::min<int>(nblk, (int)r.pages.size()));
             std::vector<int> snaps(pg.size(), -1);
-            if (!snaps.empty() && r.boundary_snapshot >= 0) snaps.back() = r.boundary_snapshot;
+            const int sb = ((int)r.prompt.size() - 1) / ps - 1;  // block that ends on the snapshot boundary
+            if (sb >= 0 && sb < (int)snaps.size() && r.boundary_snapshot >= 0) snaps[sb] = r.boundary_snapshot;
+            else if (r.boundary_snapshot >= 0) store_.release(r.boundary_snapshot);
             std::vector<int> dup_pages, dup_snaps;
             for (int p : pg) pages_.retain(p);  // the tree's own reference
             radix_.insert(r.prompt, pg, snaps, &dup_pages, &dup_snaps);

@@ -83,7 +83,8 @@ class RowSet:
 
 class GlmDeviceModel:
     def __init__(self, cfg: GlmConfig, ecfg: EngineConfig, src, rank: int = 0, world: int = 1,
-                 device="cuda", allreduce=None, max_rows: int = 8, n_slots: int = 1):
+                 device="cuda", allreduce=None, max_rows: int = 8, n_slots: int = 1,
+                 num_pages: Optional[int] = None):
         self.cfg, self.ecfg = cfg, ecfg
         self.rank, self.world = rank, world
         self.dev = torch.device(device)
@@ -91,6 +92,7 @@ class GlmDeviceModel:
         self.allreduce = allreduce  # callable(tensor_view[n,H]) summing across ranks, in place
         self.max_rows = max_rows
         self.n_slots = n_slots
+        self.num_pages_arg = num_pages
         la, ds = cfg.linear_attn, cfg.dsa
         assert la.num_heads % world == 0 and ds.num_heads % world == 0
         self.h_gdn = la.num_heads // world
@@ -301,7 +303,9 @@ class GlmDeviceModel:
         self.conv_state = self._z(ng, S, nb, 3 * self.P, la.conv_kernel - 1)
         ps = ds.page_size
         self.max_pages = (self.ecfg.max_ctx + ps - 1) // ps
-        self.num_pages = S * self.max_pages
+        # default: static identity paging (slot s owns its own range); with an explicit page
+        # count the table is filled by the caller's page allocator (page 0 = scratch page)
+        self.num_pages = self.num_pages_arg or S * self.max_pages
         nf = cfg.n_dsa_families
         kvdt = torch.float32 if self.kv_f32 else torch.bfloat16
         self.lat_cache = torch.zeros(nf, self.num_pages, ps, ds.kv_lora_rank, dtype=kvdt, device=self.dev)
@@ -309,7 +313,10 @@ class GlmDeviceModel:
         self.kgate_cache = self._z(nf, self.num_pages, ps, ds.index_head_dim)
         self.pool_cache = self._z(nf, self.num_pages, ps // ds.index_kpool, ds.index_head_dim)
         # static identity paging: slot s owns pages [s*max_pages, (s+1)*max_pages)
-        self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=self.dev).view(S, self.max_pages).contiguous()
+        if self.num_pages_arg:
+            self.page_table = torch.zeros(S, self.max_pages, dtype=torch.int32, device=self.dev)
+        else:
+            self.page_table = torch.arange(self.num_pages, dtype=torch.int32, device=self.dev).view(S, self.max_pages).contiguous()
         self.main_len = self._z(S, dtype=torch.int32)
         self.mtp_len = self._z(S, dtype=torch.int32)
         self.cur = self._z(S, dtype=torch.int32)
