@@ -1,0 +1,160 @@
+"""Command line: one-shot generation or the HTTP server.
+
+  python -m ferrite_b200.serve --model mock --serve --port 8000
+  python -m ferrite_b200.serve --model glm53 --model-dir /ckpt --prompt "hi" --max-tokens 64
+  python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 -m ferrite_b200.serve \
+      --model glm53 --synthetic --tp 4 --serve --max-seqs 16
+
+Flags follow the reference binary (``crates/ferrite-serve/src/main.rs:39-68``): ``--model``,
+``--model-dir``, ``--backend cpu|cuda``, ``--tp``, ``--prompt``, ``--serve``, ``--port``,
+``--max-seqs``, ``--model-name``, ``--max-tokens``; ``--mtp N`` selects the verify width of the
+single-sequence speculative engine (``--max-seqs 1``).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+
+def build_engine(args):
+    """Returns (ServeEngine, tokenizer, rank, world)."""
+    from .engine import HostEngine, SingleFlight
+    from .tokenizer import ChatTokenizer
+    tok = ChatTokenizer.load(args.model_dir)
+    if args.model == "mock":
+        return HostEngine(vocab=tok.vocab_size, max_rows=args.max_seqs), tok, 0, 1
+    import torch
+    from ..config import EngineConfig, GlmConfig
+    cfgs = {"glm53": GlmConfig.production, "glm-tiny": GlmConfig.tiny, "glm-golden4": GlmConfig.golden4}
+    if args.model not in cfgs:
+        raise SystemExit(f"unknown --model {args.model} (mock, {', '.join(cfgs)})")
+    cfg = GlmConfig.from_hf(os.path.join(args.model_dir, "config.json")) \
+        if args.model_dir and os.path.exists(os.path.join(args.model_dir, "config.json")) else cfgs[args.model]()
+    if args.backend == "cpu":
+        from ..models.checkpoint import CheckpointSource
+        from ..models.glm_ref import GlmReference
+        from ..models.glm_weights import random_weights
+        from ..models.glm_weights import weight_layout
+        if args.model_dir and not args.synthetic:
+            src = CheckpointSource(args.model_dir, cfg)
+            w = {k: src.get(k) for k in weight_layout(cfg)}
+        else:
+            w = random_weights(cfg, 0)
+        return SingleFlight(_RefStep(GlmReference(cfg, w))), tok, 0, 1
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.tp, f"--tp {args.tp} needs {args.tp} processes (torch.distributed.run), got {world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    allreduce = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from ..parallel.collective import make_allreduce
+        allreduce = make_allreduce(dev, rank, world, max_elems=64 * cfg.hidden_size, kind="p2p")
+    from ..models.glm import SyntheticSource
+    if args.model_dir and not args.synthetic:
+        from ..models.checkpoint import CheckpointSource
+        src = CheckpointSource(args.model_dir, cfg, dev)
+    else:
+        src = SyntheticSource(cfg, dev)
+    mtp = args.mtp if args.max_seqs == 1 else 1
+    ecfg = EngineConfig(tp=world, max_ctx=args.max_ctx, mtp_n=mtp, experts_resident=args.experts_resident or None)
+    if args.max_seqs == 1:
+        from ..engine.glm_engine import GlmEngine
+        eng = SingleFlight(_GlmStep(GlmEngine(cfg, ecfg, src, rank, world, dev, allreduce), mtp > 1))
+    else:
+        from ..engine.gpu_engine import GpuEngine
+        eng = GpuEngine(cfg, ecfg, src, rank, world, dev, allreduce, max_rows=args.max_seqs)
+    if world > 1:
+        from .tp_pool import ReplicatedEngine, make_control_group
+        eng = ReplicatedEngine(eng, rank, world, make_control_group())
+    return eng, tok, rank, world
+
+
+class _GlmStep:
+    """StepEngine over the single-sequence GLM engine."""
+
+    def __init__(self, eng, mtp: bool):
+        self.eng, self.mtp = eng, mtp
+
+    def start(self, prompt):
+        first = self.eng.prefill(prompt if len(prompt) >= 2 else [prompt[0]] * 2)
+        self.eng.build_graphs(self.mtp)
+        return first, 0
+
+    def step(self):
+        return self.eng.spec_step() if self.mtp else [self.eng.step_plain()]
+
+
+class _RefStep:
+    """StepEngine over the fp32 CPU reference engine."""
+
+    def __init__(self, ref):
+        self.ref = ref
+
+    def start(self, prompt):
+        self.st = self.ref.new_seq()
+        self.last = self.ref.prefill(self.st, prompt)
+        return self.last, 0
+
+    def step(self):
+        self.last = self.ref.decode_greedy(self.st, self.last, 2)[-1]
+        return [self.last]
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="ferrite_b200.serve")
+    ap.add_argument("--model", default="mock")
+    ap.add_argument("--model-dir", default=None)
+    ap.add_argument("--backend", default="cuda", choices=["cpu", "cuda"])
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--prompt", default=None)
+    ap.add_argument("--serve", action="store_true")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--max-seqs", type=int, default=1)
+    ap.add_argument("--model-name", default=None)
+    ap.add_argument("--max-tokens", type=int, default=64)
+    ap.add_argument("--max-ctx", type=int, default=8192)
+    ap.add_argument("--mtp", type=int, default=3)
+    ap.add_argument("--synthetic", action="store_true", help="random-init weights instead of a checkpoint")
+    ap.add_argument("--experts-resident", type=int, default=0)
+    args = ap.parse_args(argv)
+    eng, tok, rank, world = build_engine(args)
+    if rank != 0:
+        eng.follow()
+        return 0
+    name = args.model_name or args.model
+    if args.serve:
+        from .api import serve
+        serve(eng, tok, args.host, args.port, name)
+        return 0
+    from .engine import RequestSpec
+    prompt = tok.encode_chat([{"role": "user", "content": args.prompt or "Hello"}])
+    rid = eng.submit(RequestSpec(prompt, args.max_tokens, tuple(tok.stop_ids())))
+    t0, ids, t_first = time.time(), [], None
+    while True:
+        done = False
+        for r, ev in eng.tick():
+            if ev.kind == "tokens":
+                t_first = t_first or time.time()
+                ids += ev.ids
+            elif ev.kind == "finished":
+                done = True
+        if done:
+            break
+    dt = time.time() - (t_first or t0)
+    print(tok.decode(ids))
+    print(f"[stats] prompt {len(prompt)} tok, ttft {((t_first or t0) - t0) * 1e3:.1f} ms, "
+          f"{len(ids)} tok in {dt:.3f} s = {len(ids) / max(dt, 1e-9):.1f} tok/s", file=sys.stderr)
+    if hasattr(eng, "stop"):
+        eng.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
