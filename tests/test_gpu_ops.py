@@ -507,3 +507,22 @@ def test_moe_experts_mma(K, n, E, topk, I, H):
             if e >= lo:
                 want2[r] += act_ref[r * topk + s] @ R.dequant_fp8_block(q2[e], s2[e]).t()
     check("moe mma ep", out2, want2, 3e-3 * want2.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K_", [(5, 300, 256), (16, 128, 64), (64, 4096, 4096), (300, 1000, 512), (1, 129, 1536),
+                                    (130, 256, 8192)])
+def test_gemm_tcgen05_bf16(K, M, N, K_):
+    """TMA + tcgen05 GEMM (weights as the A operand) against fp32 matmul of the same bf16 inputs."""
+    w = rnd(N, K_, seed=1, scale=0.1).bfloat16()
+    x = rnd(M, K_, seed=2).bfloat16()
+    out = torch.full((M, N), 3.0, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    K.call("fb_gemm_tc_bf16", dev(w), dev(x), K_, out, N, M, N, K_, 0, status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, f"kernel reported {status.tolist()}"
+    want = x.float() @ w.float().t()
+    check("gemm tc", out, want, 2e-3 * max(1.0, want.abs().max().item()))
+    K.call("fb_gemm_tc_bf16", dev(w), dev(x), K_, out, N, M, N, K_, 1, status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    check("gemm tc acc", out, 2 * want, 4e-3 * max(1.0, want.abs().max().item()))
