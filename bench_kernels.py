@@ -141,6 +141,21 @@ def make_cases(K, only):
             cases.append(Case(f"moe_down_mma.{tag}", n * topk * I * H, dn, f"24 experts I={I}"))
             cases.append(Case(f"moe_down_simt.{tag}", n * topk * I * H, dn_simt, f"24 experts I={I}"))
 
+    # ---- tcgen05 prefill GEMM (reported in TFLOP/s through the note; bytes = weights once) -------
+    for tag, M, N, Kd in (("qkv_in.m1024", 1024, 24896, 4096), ("o_proj.m1024", 1024, 4096, 8192), ("lm_head.m256", 256, 154880, 4096),
+                          ("o_proj.m64", 64, 4096, 8192)):
+        name = f"gemm_tc_bf16.{tag}"
+        if not want(name):
+            continue
+        w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+        x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(M, N, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+        def tcfn(w=w, x=x, out=out, status=status, M=M, N=N, Kd=Kd):
+            K.call("fb_gemm_tc_bf16", w, x, Kd, out, N, M, N, Kd, 0, status)
+        cases.append(Case(name, N * Kd * 2, tcfn, f"M={M} N={N} K={Kd} FLOP={2 * M * N * Kd}"))
+
     # ---- MHC site -----------------------------------------------------------------------
     if want("hc_"):
         n, H, mix = 3, 4096, 24
@@ -201,7 +216,12 @@ def main():
         gbs = c.nbytes / us / 1e3
         rows.append({"kernel": c.name, "us": round(us, 2), "MB": round(c.nbytes / 1e6, 1), "GB/s": round(gbs, 0),
                      "frac": round(gbs / peak, 3), "note": c.note})
-        print(f"{c.name:38s} {us:9.2f} us  {c.nbytes / 1e6:8.1f} MB  {gbs:7.0f} GB/s  {gbs / peak:5.2f} {tag}  {c.note}")
+        extra = ""
+        if "FLOP=" in c.note:
+            tf = float(c.note.split("FLOP=")[1]) / us / 1e6
+            rows[-1]["TFLOPs"] = round(tf, 1)
+            extra = f"  {tf:7.1f} TFLOP/s"
+        print(f"{c.name:38s} {us:9.2f} us  {c.nbytes / 1e6:8.1f} MB  {gbs:7.0f} GB/s  {gbs / peak:5.2f} {tag}  {c.note}{extra}")
     if args.json:
         json.dump({"hbm_peak_gbs": peak, "peak_kind": tag, "rows": rows}, open(args.json, "w"), indent=1)
 

@@ -101,6 +101,8 @@ class GlmDeviceModel:
         self.kv_f32 = ecfg.kv_dtype == "f32"
         self.nbuf = (ecfg.mtp_n + 1) if ecfg.mtp_n > 1 else 1
         self.E_res = ecfg.experts_resident or cfg.n_routed_experts
+        self.tc_min_rows = 16  # row count from which dense bf16 projections use the tcgen05 GEMM
+        self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
         self.layers: List[dict] = []
         self.debug_hook = None  # callable(layer_index, site, ws, n) after each sublayer (eager runs only)
         self._pack(src)
@@ -356,6 +358,15 @@ class GlmDeviceModel:
         fp8 = scales is not None
         kb = 128 if fp8 else 64
         use_mma = xa is not None and xa.s is not None and K % kb == 0 and group_rows % 16 == 0 and ldx % 8 == 0
+        if use_mma and not fp8 and group_rows == 0 and m >= self.tc_min_rows:
+            # prefill-sized row counts: TMA + tcgen05 GEMM over the bf16 high plane of the activations
+            xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
+            op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
+            self.K.call("fb_gemm_tc_bf16", w, xp, ldx, op, ldo, m, N, K, int(accumulate), self.tc_status)
+            if oa is not None and omask:
+                self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
+                            omask, m, N)
+            return
         for r0 in range(0, m, 8):
             mm = min(8, m - r0)
             op = _lib.ctypes.c_void_p(of.data_ptr() + (r0 * ldo + ocol) * 4)
