@@ -54,7 +54,7 @@ def make_cases(K, only):
     dev = "cuda"
 
     def want(name):
-        return only is None or only in name
+        return only is None or only in name or name in only
 
     def gemv_case(name, N, Kd, m, fp8=False, mma=True):
         if not want(name):

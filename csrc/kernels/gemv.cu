@@ -218,7 +218,7 @@ int launch_sk_rb(const void* W, const float* scales, const float* x, int ldx, fl
 // elements) with the next block's weight loads in flight while the current block is
 // multiplied; partial D tiles are summed across warps through shared memory.
 template <int RT, int NW, bool FP8>
-__global__ void __launch_bounds__(NW * 32)
+__global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
 gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
                 const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
                 float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,

@@ -291,7 +291,7 @@ moe_gate_up_mma_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
 
 // down: a CTA owns 16 output columns of one row; warps walk the (slot, k-block) items.
 // act comes pre-multiplied by the routing weights, in f16 split form.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2,
                     const uint16_t* __restrict__ ahi, const uint16_t* __restrict__ alo, int lda,
                     const int* __restrict__ ids, float* __restrict__ out, int ldo, int topk, int I, int H,
