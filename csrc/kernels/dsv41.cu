@@ -1,0 +1,1187 @@
+// Kernels of the DSV41 family (sliding-window + compressed-KV latent attention with an indexer,
+// sqrt-softplus MoE with fp4 experts, offset hyper-connections, engram n-gram memory).
+//
+// Storage choices (all device-side, the golden model only defines values):
+//   * window KV: ring of `cap` rows per slot, row of position p at p % cap, cap >= window +
+//     rows of one forward, so that a multi-row forward (verify, chunked prefill) never
+//     overwrites a row that an earlier row of the same forward still sees, and rejected rows
+//     are simply overwritten later; values are e4m3-per-32 round trips held as bf16 (exact);
+//   * compressor input ring: the raw (kv, score) rows of the last `depth` positions, so a
+//     group is pooled from positions, not from a mutable partial state (no rollback needed);
+//   * compressed KV / index keys: one row per group j at index j, e2m1 round trips held as
+//     bf16 (exact: 1 + 3 mantissa bits).
+// Reference kernels replaced: kernels/cuda/dsv41/*.cu (`rmsnorm_*`, `apply_rope*`, `ring_*`,
+// `win_kv_quant_rt`, `compress_*`, `indexer_score*`, `candidate_blocks`, `indexer_topk`,
+// `sparse_attn_pf`, `route_*`, `expert_gemv_fp4_*`, `engram_*`, `hc_*`), semantics of
+// ref_inference/model.py and ref_inference/kernel.py.
+#include <cuda_fp4.h>
+
+#include "common.cuh"
+#include "mma_gemv.cuh"
+
+namespace {
+
+constexpr int kMaxMixD4 = 24;  // (2 + hc) * hc for hc = 4; accumulator rows are kMaxMixD4 + 1 wide
+
+// ---- codecs ------------------------------------------------------------------------------------
+__device__ __forceinline__ float pow2_ceil(float x) {  // 2^ceil(log2 x), x > 0 normal
+    const uint32_t b = __float_as_uint(x);
+    const int e = (int)((b >> 23) & 0xff) + ((b & 0x7fffffu) ? 1 : 0);
+    return __uint_as_float((uint32_t)min(max(e, 0), 254) << 23);
+}
+__device__ __forceinline__ float e4m3_rt(float v) {  // nearest e4m3 (saturating), as f32
+    const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(q, __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+__device__ __forceinline__ float e2m1_rt(float v) {  // nearest e2m1 (ties to even code, saturating), as f32
+    const float a = fminf(fabsf(v), 6.f);
+    float r;
+    if (a <= 0.25f) r = 0.f;
+    else if (a < 0.75f) r = 0.5f;
+    else if (a <= 1.25f) r = 1.f;
+    else if (a < 1.75f) r = 1.5f;
+    else if (a <= 2.5f) r = 2.f;
+    else if (a < 3.5f) r = 3.f;
+    else if (a <= 5.f) r = 4.f;
+    else r = 6.f;
+    return copysignf(r, v);
+}
+// Scale of one 32-value block whose |max| is amax: e4m3 values with a power-of-two scale.
+__device__ __forceinline__ float fp8_block_scale(float amax) { return pow2_ceil(fmaxf(amax, 1e-4f) * (1.f / 448.f)); }
+
+// ---- activation quantisation: e4m3 per 32 with power-of-two scales, round trip ----------------
+// One warp per 32-value block.  xq may alias x.
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const float* __restrict__ x, int ldx, float* __restrict__ xq, int ldq, SplitBuf osp, int n, int K) {
+    PDL_PROLOGUE();
+    const int lane = threadIdx.x & 31;
+    const int nb = K / 32;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n * nb) return;
+    const int r = w / nb, b = w % nb;
+    const float v = x[(size_t)r * ldx + b * 32 + lane];
+    const float s = fp8_block_scale(warp_max(fabsf(v)));
+    const float q = e4m3_rt(v / s) * s;
+    if (xq) xq[(size_t)r * ldq + b * 32 + lane] = q;
+    split_store(osp, r, b * 32 + lane, q);
+}
+
+// ---- offset hyper-connection front -------------------------------------------------------------
+// acc [n][25]: the 24 mix dots of the CURRENT stream R plus its sum of squares (cleared here).
+// Computes this site's (pre, post, comb); `pre` is only stored (the NEXT site contracts with
+// it), the contraction uses pre_in, the coefficients of the previous site.
+//   xn = rmsnorm(sum_i pre_in[i] R_i) * ln_w
+__global__ void __launch_bounds__(512)
+hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
+                     const float* __restrict__ base, const float* __restrict__ ln_w, const float* __restrict__ pre_in,
+                     float* __restrict__ pre_out, float* __restrict__ post_out, float* __restrict__ comb_out,
+                     float* __restrict__ xn_out, float* __restrict__ xc_out, int H, float rms_eps, float hc_eps, int iters,
+                     SplitBuf osp) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* red = sh;       // 32
+    float* xs = sh + 32;   // H
+    const int n = 4;
+    const int r = blockIdx.x;
+    const float* row = R + (size_t)r * n * H;
+    if (acc && threadIdx.x < 32) {
+        float* a = acc + (size_t)r * (kMaxMixD4 + 1);
+        const int lane = threadIdx.x;
+        const float rr = rsqrtf(a[kMaxMixD4] / (float)(n * H) + rms_eps);
+        if (lane < n) {
+            pre_out[(size_t)r * n + lane] = sigmoidf_(a[lane] * rr * scale[0] + base[lane]) + hc_eps;
+            post_out[(size_t)r * n + lane] = 2.f * sigmoidf_(a[n + lane] * rr * scale[1] + base[n + lane]);
+        }
+        float c = 0.f;
+        const bool on = lane < n * n;
+        if (on) c = a[2 * n + lane] * rr * scale[2] + base[2 * n + lane];
+        float mx = on ? c : -INFINITY;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float e = on ? __expf(c - mx) : 0.f;
+        float den = e + __shfl_xor_sync(0xffffffffu, e, 1);
+        den += __shfl_xor_sync(0xffffffffu, den, 2);
+        c = on ? e / den + hc_eps : 0.f;
+        float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        c = c / (cs + hc_eps);
+        for (int it = 1; it < iters; ++it) {
+            float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            c = c / (rs + hc_eps);
+            cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            c = c / (cs + hc_eps);
+        }
+        if (on) comb_out[(size_t)r * n * n + lane] = c;
+        __syncwarp();
+        if (lane <= kMaxMixD4) a[lane] = 0.f;
+    }
+    const float p0 = pre_in[r * n + 0], p1 = pre_in[r * n + 1], p2 = pre_in[r * n + 2], p3 = pre_in[r * n + 3];
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = p0 * row[j] + p1 * row[H + j] + p2 * row[2 * H + j] + p3 * row[3 * H + j];
+        xs[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / H + rms_eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = xs[j];
+        if (xc_out) xc_out[(size_t)r * H + j] = v;
+        const float o = v * inv * ln_w[j];
+        xn_out[(size_t)r * H + j] = o;
+        split_store(osp, r, j, o);
+    }
+}
+
+// ---- RoPE on the last `rd` dims of each head (adjacent pairs), in place -------------------------
+// position of row r = meta[r].pos (+ pos_off); optional fp4-per-32 round trip of the whole head
+// afterwards (the indexer's q).
+__global__ void __launch_bounds__(128)
+rope_heads_kernel(float* __restrict__ x, int ld, int heads, int hd, int rd, const float* __restrict__ freqs,
+                  const RowMeta* __restrict__ meta, int pos_off, int inverse, int fp4_rt, SplitBuf osp) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y, h = blockIdx.x;
+    float* v = x + (size_t)r * ld + (size_t)h * hd;
+    const float pos = (float)(meta[r].pos + pos_off);
+    for (int i = threadIdx.x; i < rd / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * freqs[i], &sn, &cs);
+        if (inverse) sn = -sn;
+        float* p = v + (hd - rd) + 2 * i;
+        const float a = p[0], b = p[1];
+        p[0] = a * cs - b * sn;
+        p[1] = a * sn + b * cs;
+    }
+    if (fp4_rt) {
+        __syncthreads();
+        const int lane = threadIdx.x & 31;
+        for (int b = threadIdx.x >> 5; b < hd / 32; b += blockDim.x >> 5) {
+            const float t = v[b * 32 + lane];
+            const float s = pow2_ceil(fmaxf(warp_max(fabsf(t)), 6.f * 1.17549435e-38f) * (1.f / 6.f));
+            const float q = e2m1_rt(t / s) * s;
+            v[b * 32 + lane] = q;
+            split_store(osp, r, h * hd + b * 32 + lane, q);
+        }
+    }
+}
+
+// ---- KV row: rmsnorm -> rope -> e4m3/32 round trip -> ring (bf16) and/or plain rows --------------
+__global__ void __launch_bounds__(128)
+kv_append_kernel(const float* __restrict__ kv, int ld, const float* __restrict__ norm_w, const float* __restrict__ freqs,
+                 const RowMeta* __restrict__ meta, __nv_bfloat16* __restrict__ ring, int cap, float* __restrict__ rows_out,
+                 int hd, int rd, float eps, int pos_off) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* red = sh;
+    float* v = sh + 32;
+    const int r = blockIdx.x;
+    const RowMeta m = meta[r];
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+        const float t = kv[(size_t)r * ld + j];
+        v[j] = t;
+        ss += t * t;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / hd + eps);
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) v[j] = v[j] * inv * norm_w[j];
+    __syncthreads();
+    const int p = m.pos + pos_off;
+    for (int i = threadIdx.x; i < rd / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)p * freqs[i], &sn, &cs);
+        float* q = v + (hd - rd) + 2 * i;
+        const float a = q[0], b = q[1];
+        q[0] = a * cs - b * sn;
+        q[1] = a * sn + b * cs;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    for (int b = threadIdx.x >> 5; b < hd / 32; b += blockDim.x >> 5) {
+        const float t = v[b * 32 + lane];
+        const float s = fp8_block_scale(warp_max(fabsf(t)));
+        const float q = e4m3_rt(t / s) * s;
+        if (ring) ring[((size_t)m.slot * cap + (p % cap)) * hd + b * 32 + lane] = __float2bfloat16_rn(q);
+        if (rows_out) rows_out[(size_t)r * hd + b * 32 + lane] = q;
+    }
+}
+
+// ---- compressor ------------------------------------------------------------------------------------
+// Phase 1: every row stores its raw (kv, score) at position % depth of the input ring.
+// Phase 2: a row whose position completes a group pools the group's `ratio` positions with a
+// per-channel softmax over the scores, RMS-normalises, and writes lat[r] (pre-RoPE) with
+// flag[r] = 1; other rows get flag 0.  ratio == 1: lat = rmsnorm(kv), no ring.
+__global__ void __launch_bounds__(512)
+compress_kernel(const float* __restrict__ kv, const float* __restrict__ sc, int ld, const RowMeta* __restrict__ meta,
+                float* __restrict__ ring_kv, float* __restrict__ ring_sc, int depth, const float* __restrict__ norm_w,
+                float* __restrict__ lat, int* __restrict__ flag, int n, int hd, int ratio, float eps) {
+    PDL_PROLOGUE();
+    __shared__ float red[32];
+    if (ratio > 1) {
+        for (int r = 0; r < n; ++r) {
+            const RowMeta m = meta[r];
+            const size_t o = ((size_t)m.slot * depth + (m.pos % depth)) * hd;
+            for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+                ring_kv[o + j] = kv[(size_t)r * ld + j];
+                ring_sc[o + j] = sc[(size_t)r * ld + j];
+            }
+        }
+        __syncthreads();
+    }
+    for (int r = 0; r < n; ++r) {
+        const RowMeta m = meta[r];
+        const bool done = ((m.pos + 1) % ratio) == 0;
+        if (threadIdx.x == 0) flag[r] = done ? 1 : 0;
+        if (!done) continue;  // block-uniform
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+            float v;
+            if (ratio == 1) {
+                v = kv[(size_t)r * ld + j];
+            } else {
+                float mx = -INFINITY;
+                for (int i = 0; i < ratio; ++i)
+                    mx = fmaxf(mx, ring_sc[((size_t)m.slot * depth + ((m.pos - i) % depth)) * hd + j]);
+                float den = 0.f, num = 0.f;
+                for (int i = ratio - 1; i >= 0; --i) {
+                    const size_t o = ((size_t)m.slot * depth + ((m.pos - i) % depth)) * hd + j;
+                    const float e = __expf(ring_sc[o] - mx);
+                    den += e;
+                    num += e * ring_kv[o];
+                }
+                v = num / den;
+            }
+            lat[(size_t)r * hd + j] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / hd + eps);
+        for (int j = threadIdx.x; j < hd; j += blockDim.x) lat[(size_t)r * hd + j] *= inv * norm_w[j];
+        __syncthreads();
+    }
+}
+
+// Finished latents -> compressed-KV cache: rope at position (group * ratio), e2m1 per 16 with an
+// e4m3 scale, row j = pos / ratio of the slot's cache.  Rows with flag 0 are skipped.
+__global__ void __launch_bounds__(128)
+latent_store_kernel(const float* __restrict__ lat, const int* __restrict__ flag, const RowMeta* __restrict__ meta,
+                    const float* __restrict__ freqs, __nv_bfloat16* __restrict__ cache, int cap, int hd, int rd, int ratio) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* v = sh;
+    const int r = blockIdx.x;
+    if (!flag[r]) return;
+    const RowMeta m = meta[r];
+    const int j = m.pos / ratio;
+    if (j >= cap) return;
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) v[i] = lat[(size_t)r * hd + i];
+    __syncthreads();
+    const float p = (float)(j * ratio);
+    for (int i = threadIdx.x; i < rd / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf(p * freqs[i], &sn, &cs);
+        float* q = v + (hd - rd) + 2 * i;
+        const float a = q[0], b = q[1];
+        q[0] = a * cs - b * sn;
+        q[1] = a * sn + b * cs;
+    }
+    __syncthreads();
+    // 16-value groups: half-warps
+    const int lane = threadIdx.x & 31, half = lane >> 4;
+    for (int g = (threadIdx.x >> 5) * 2 + half; g < hd / 16; g += (blockDim.x >> 5) * 2) {
+        const float t = v[g * 16 + (lane & 15)];
+        float am = fabsf(t);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        const float s = e4m3_rt(fmaxf(am, 6.f * 0.001953125f) * (1.f / 6.f));
+        cache[((size_t)m.slot * cap + j) * hd + g * 16 + (lane & 15)] = __float2bfloat16_rn(e2m1_rt(t / s) * s);
+    }
+}
+
+// Index keys: kraw [n, id] = wk . latent (pre-RoPE latent) -> rmsnorm -> rope(group * ratio) ->
+// e2m1 per 32 with power-of-two scales -> k cache row pos / ratio.
+__global__ void __launch_bounds__(128)
+index_k_store_kernel(const float* __restrict__ kraw, int ld, const int* __restrict__ flag, const RowMeta* __restrict__ meta,
+                     const float* __restrict__ norm_w, const float* __restrict__ freqs, __nv_bfloat16* __restrict__ cache,
+                     int cap, int id, int rd, int ratio, float eps) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* red = sh;
+    float* v = sh + 32;
+    const int r = blockIdx.x;
+    if (!flag[r]) return;
+    const RowMeta m = meta[r];
+    const int j = m.pos / ratio;
+    if (j >= cap) return;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < id; i += blockDim.x) {
+        const float t = kraw[(size_t)r * ld + i];
+        v[i] = t;
+        ss += t * t;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / id + eps);
+    for (int i = threadIdx.x; i < id; i += blockDim.x) v[i] = v[i] * inv * norm_w[i];
+    __syncthreads();
+    const float p = (float)(j * ratio);
+    for (int i = threadIdx.x; i < rd / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf(p * freqs[i], &sn, &cs);
+        float* q = v + (id - rd) + 2 * i;
+        const float a = q[0], b = q[1];
+        q[0] = a * cs - b * sn;
+        q[1] = a * sn + b * cs;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    for (int b = threadIdx.x >> 5; b < id / 32; b += blockDim.x >> 5) {
+        const float t = v[b * 32 + lane];
+        const float s = pow2_ceil(fmaxf(warp_max(fabsf(t)), 6.f * 1.17549435e-38f) * (1.f / 6.f));
+        cache[((size_t)m.slot * cap + j) * id + b * 32 + lane] = __float2bfloat16_rn(e2m1_rt(t / s) * s);
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// ---- indexer ------------------------------------------------------------------------------------
+// score[r][j] = sum_h relu(q[r][h] . k[j]) * w[r][h] for j < clen(r) = (pos + 1) / ratio, -inf beyond,
+// over this rank's heads (the caller all-reduces across ranks).  One lane per head, keys
+// broadcast from shared memory; q rows padded by one float against bank conflicts.
+__global__ void __launch_bounds__(256)
+index_score_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ w, int ldw,
+                   const __nv_bfloat16* __restrict__ kc, int cap, const RowMeta* __restrict__ meta,
+                   float* __restrict__ score, int lds, int heads, int id, int ratio, float wscale) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* qs = sh;                          // [heads][id + 1]
+    float* ks = sh + heads * (id + 1);       // [8 warps][id]
+    const int r = blockIdx.y;
+    const RowMeta m = meta[r];
+    const int clen = (m.pos + 1) / ratio;
+    const int per = (blockDim.x >> 5) * 4;
+    const int j0 = blockIdx.x * per;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (j0 >= min(cap, lds)) return;
+    if (j0 >= clen) {  // whole block beyond the visible range
+        for (int j = j0 + threadIdx.x; j < min(j0 + per, lds); j += blockDim.x) score[(size_t)r * lds + j] = -INFINITY;
+        return;
+    }
+    for (int i = threadIdx.x; i < heads * id; i += blockDim.x) qs[(i / id) * (id + 1) + (i % id)] = q[(size_t)r * ldq + i];
+    __syncthreads();
+    const float wh = lane < heads ? w[(size_t)r * ldw + lane] * wscale : 0.f;
+    float* kw = ks + warp * id;
+    for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + warp * 4 + jj;
+        if (j >= lds) break;
+        if (j >= clen) { if (lane == 0) score[(size_t)r * lds + j] = -INFINITY; continue; }
+        __syncwarp();
+        for (int e = lane; e < id; e += 32) kw[e] = __bfloat162float(kc[((size_t)m.slot * cap + j) * id + e]);
+        __syncwarp();
+        float acc = 0.f;
+        for (int h = lane; h < heads; h += 32) {   // heads <= 32 in every shipped config; loop keeps it general
+            float d = 0.f;
+            const float* qh = qs + h * (id + 1);
+            for (int e = 0; e < id; ++e) d = fmaf(qh[e], kw[e], d);
+            const float whh = (h == lane) ? wh : w[(size_t)r * ldw + h] * wscale;
+            acc += fmaxf(d, 0.f) * whh;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) score[(size_t)r * lds + j] = acc;
+    }
+}
+
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Block-wide exclusive scan of one int per thread (blockDim.x <= 1024); returns the exclusive
+// prefix and writes the block total to *total.
+__device__ __forceinline__ int block_excl_scan(int v, int* wsum, int* total) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += t;
+    }
+    __syncthreads();
+    if (lane == 31) wsum[wid] = x;
+    __syncthreads();
+    if (wid == 0) {
+        int s = lane < nw ? wsum[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, s, o);
+            if (lane >= o) s += t;
+        }
+        wsum[lane] = s;  // inclusive warp totals
+    }
+    __syncthreads();
+    const int base = wid ? wsum[wid - 1] : 0;
+    *total = wsum[nw - 1];
+    return base + x - v;
+}
+
+// Top-k of each row by (score descending, index ascending), emitted in index order, -1 padded.
+// len(r) = ceil(((pos + 1) / ratio) / div); entries whose mask byte is 0 count as -inf.
+// Four 8-bit radix passes find the k-th key, one ordered pass emits.
+__global__ void __launch_bounds__(1024)
+topk_sorted_kernel(const float* __restrict__ score, int lds, const uint8_t* __restrict__ mask, int ldm,
+                   const RowMeta* __restrict__ meta, int ratio, int div, int k, int* __restrict__ out, int ldo) {
+    PDL_PROLOGUE();
+    __shared__ int hist[256];
+    __shared__ int wsum[32];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need, s_written, s_eq_taken;
+    const int r = blockIdx.x;
+    const int clen = (meta[r].pos + 1) / ratio;
+    const int len = min((clen + div - 1) / div, lds);
+    const float* sc = score + (size_t)r * lds;
+    const uint8_t* mk = mask ? mask + (size_t)r * ldm : nullptr;
+    int* o = out + (size_t)r * ldo;
+    const int kk = min(k, len);
+    auto key_at = [&](int j) -> uint32_t {
+        const float v = (mk && !mk[j]) ? -INFINITY : sc[j];
+        return ordered_key(v);
+    };
+    uint32_t T = 0;
+    int need_eq = 0;
+    if (kk < len) {
+        // k-th largest key: walk the digits from the top
+        if (threadIdx.x == 0) { s_prefix = 0; s_need = kk; }
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+            __syncthreads();
+            const uint32_t prefix = s_prefix;
+            const uint32_t pmask = pass ? (0xffffffffu << (shift + 8)) : 0u;
+            for (int j = threadIdx.x; j < len; j += blockDim.x) {
+                const uint32_t key = key_at(j);
+                if ((key & pmask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int need = s_need, d = 255;
+                for (; d > 0; --d) {
+                    if (hist[d] >= need) break;
+                    need -= hist[d];
+                }
+                s_need = need;
+                s_prefix = prefix | ((uint32_t)d << shift);
+            }
+            __syncthreads();
+        }
+        T = s_prefix;
+        need_eq = s_need;  // how many entries equal to T are taken (the lowest indices)
+    }
+    if (threadIdx.x == 0) { s_written = 0; s_eq_taken = 0; }
+    __syncthreads();
+    for (int j0 = 0; j0 < len; j0 += blockDim.x) {
+        const int j = j0 + threadIdx.x;
+        int gt = 0, eq = 0;
+        if (j < len) {
+            if (kk >= len) gt = 1;
+            else {
+                const uint32_t key = key_at(j);
+                gt = key > T;
+                eq = key == T;
+            }
+        }
+        int tot_eq, tot_sel;
+        const int eq_before = block_excl_scan(eq, wsum, &tot_eq) + s_eq_taken;
+        const int sel = gt || (eq && eq_before < need_eq);
+        __syncthreads();
+        const int pos = block_excl_scan(sel, wsum, &tot_sel) + s_written;
+        if (sel && pos < ldo) o[pos] = j;
+        __syncthreads();
+        if (threadIdx.x == 0) { s_written += tot_sel; s_eq_taken += tot_eq; }
+        __syncthreads();
+    }
+    for (int i = s_written + threadIdx.x; i < min(k, ldo); i += blockDim.x) o[i] = -1;
+}
+
+// Block scores for the candidate level: max over each `bs` positions below clen, the block
+// holding the newest visible position pinned to +inf.
+__global__ void __launch_bounds__(256)
+block_max_kernel(const float* __restrict__ score, int lds, const RowMeta* __restrict__ meta, int ratio, int bs,
+                 float* __restrict__ out, int ldo) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y;
+    const int clen = (meta[r].pos + 1) / ratio;
+    const int nb = (clen + bs - 1) / bs;
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= ldo) return;
+    float v = -INFINITY;
+    if (b < nb) {
+        for (int i = 0; i < bs; ++i) {
+            const int j = b * bs + i;
+            if (j < clen && j < lds) v = fmaxf(v, score[(size_t)r * lds + j]);
+        }
+        if (b == (clen - 1) / bs) v = INFINITY;
+    }
+    out[(size_t)r * ldo + b] = v;
+}
+
+// mask[r][j] = 1 for positions inside the selected blocks (mask is cleared by the caller).
+__global__ void __launch_bounds__(256)
+cand_mask_kernel(const int* __restrict__ blk, int ldb, int kb, int bs, uint8_t* __restrict__ mask, int ldm) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= kb * bs) return;
+    const int b = blk[(size_t)r * ldb + t / bs];
+    if (b < 0) return;
+    const int j = b * bs + t % bs;
+    if (j < ldm) mask[(size_t)r * ldm + j] = 1;
+}
+
+// ---- sparse attention with a sink ----------------------------------------------------------------
+// One CTA per (row, tile of 8 heads), one warp per head.  Keys: the row's window positions from
+// the ring, the selected compressed rows, then `n_extra` plain rows (a draft block's own KV).
+// Lane i of a warp owns elements {2i + 64j, 2i + 1 + 64j}: adjacent pairs (the RoPE pairs) and
+// conflict-free 4-byte reads of a staged bf16 key.  q is rotated on load, the output gets the
+// inverse rotation; softmax runs online with max over the real keys only, the sink logit
+// joins the denominator at the end, a row without keys yields zeros.
+constexpr int kAttnTile = 16;
+template <int NJ>  // head_dim / 64
+__global__ void __launch_bounds__(256)
+sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ ring, int cap, int window,
+                   const __nv_bfloat16* __restrict__ comp, int ccap, const int* __restrict__ idx, int ldi, int ktop,
+                   const float* __restrict__ extra, int n_extra, const float* __restrict__ sink,
+                   const float* __restrict__ freqs, int rd, const RowMeta* __restrict__ meta, int pos_off, int win_mode,
+                   float scale, int heads, float* __restrict__ out, int ldo, SplitBuf osp) {
+    PDL_PROLOGUE();
+    constexpr int HD = NJ * 64;
+    __shared__ __align__(16) uint32_t ktile[kAttnTile][HD / 2];
+    __shared__ int kvalid[kAttnTile];
+    const int r = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x * 8 + warp;
+    const bool hv = h < heads;
+    const RowMeta m = meta[r];
+    const int pos = m.pos + pos_off;          // position of the query (RoPE)
+    const int wpos = win_mode ? m.ctx0 - 1 : m.pos;  // newest window position visible to the query (mode 1: the
+                                                     // rows of a draft block all see the window up to the block's start)
+    const int nw = min(wpos + 1, window);
+    const int L = max(nw, 0) + ktop + n_extra;
+    // rotation factors of this lane's pairs
+    float cs[NJ], sn[NJ];
+    float qv[NJ][2];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int e = 2 * lane + 64 * j;
+        cs[j] = 1.f; sn[j] = 0.f;
+        if (e >= HD - rd) sincosf((float)pos * freqs[(e - (HD - rd)) >> 1], &sn[j], &cs[j]);
+        const float a = hv ? q[(size_t)r * ldq + (size_t)h * HD + e] : 0.f;
+        const float b = hv ? q[(size_t)r * ldq + (size_t)h * HD + e + 1] : 0.f;
+        qv[j][0] = (a * cs[j] - b * sn[j]) * scale;
+        qv[j][1] = (a * sn[j] + b * cs[j]) * scale;
+    }
+    float mx = -1e30f, den = 0.f;
+    float ov[NJ][2];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) ov[j][0] = ov[j][1] = 0.f;
+    for (int t0 = 0; t0 < L; t0 += kAttnTile) {
+        __syncthreads();
+        // stage up to kAttnTile keys
+        for (int t = warp; t < kAttnTile; t += 8) {
+            const int i = t0 + t;
+            const __nv_bfloat16* src = nullptr;
+            const float* srcf = nullptr;
+            if (i < nw) {
+                const int p = wpos - nw + 1 + i;
+                src = ring + ((size_t)m.slot * cap + (p % cap)) * HD;
+            } else if (i < nw + ktop) {
+                const int c = idx[(size_t)r * ldi + (i - nw)];
+                if (c >= 0 && c < ccap) src = comp + ((size_t)m.slot * ccap + c) * HD;
+            } else if (i < L) {
+                srcf = extra + (size_t)(i - nw - ktop) * HD;
+            }
+            if (lane == 0) kvalid[t] = (src || srcf) ? 1 : 0;
+            if (!src && !srcf) {
+                for (int e = lane; e < HD / 2; e += 32) ktile[t][e] = 0u;  // a masked key must not feed NaN into 0 * k
+            } else if (src) {
+                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+                for (int e = lane; e < HD / 2; e += 32) ktile[t][e] = s32[e];
+            } else if (srcf) {
+                for (int e = lane; e < HD / 2; e += 32) {
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(srcf[2 * e], srcf[2 * e + 1]);
+                    ktile[t][e] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+            }
+        }
+        __syncthreads();
+        float sc[kAttnTile];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int t = 0; t < kAttnTile; ++t) {
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const uint32_t kw = ktile[t][lane + 32 * j];
+                d = fmaf(qv[j][0], bf16lo(kw), d);
+                d = fmaf(qv[j][1], bf16hi(kw), d);
+            }
+            sc[t] = d;
+        }
+#pragma unroll
+        for (int t = 0; t < kAttnTile; ++t) {
+            sc[t] = warp_sum(sc[t]);
+            if (!kvalid[t] || t0 + t >= L) sc[t] = -INFINITY;
+            tmax = fmaxf(tmax, sc[t]);
+        }
+        const float mnew = fmaxf(mx, tmax);
+        const float resc = __expf(mx - mnew);
+        den *= resc;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) { ov[j][0] *= resc; ov[j][1] *= resc; }
+#pragma unroll
+        for (int t = 0; t < kAttnTile; ++t) {
+            const float p = __expf(sc[t] - mnew);  // exp(-inf) = 0 for masked keys
+            den += p;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const uint32_t kw = ktile[t][lane + 32 * j];
+                ov[j][0] = fmaf(p, bf16lo(kw), ov[j][0]);
+                ov[j][1] = fmaf(p, bf16hi(kw), ov[j][1]);
+            }
+        }
+        mx = mnew;
+    }
+    if (!hv) return;
+    den += __expf(sink[h] - mx);
+    const float inv = 1.f / den;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int e = 2 * lane + 64 * j;
+        const float a = ov[j][0] * inv, b = ov[j][1] * inv;
+        const float x0 = a * cs[j] + b * sn[j];   // inverse rotation
+        const float x1 = -a * sn[j] + b * cs[j];
+        float* o = out + (size_t)r * ldo + (size_t)h * HD + e;
+        o[0] = x0;
+        o[1] = x1;
+        split_store(osp, r, h * HD + e, x0);
+        split_store(osp, r, h * HD + e + 1, x1);
+    }
+}
+
+}  // namespace
+
+namespace {
+
+// ---- MoE route: sqrt(softplus) scores, bias only for selection, normalised, scaled -------------
+__global__ void __launch_bounds__(128)
+route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, const float* __restrict__ bias_vl,
+             const uint8_t* __restrict__ is_image, int E, int topk, float route_scale, int* __restrict__ idx,
+             float* __restrict__ wts) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    float* sc = sh;        // E scores
+    float* sel = sh + E;   // E selection values
+    __shared__ float red[32];
+    __shared__ int s_best;
+    const int r = blockIdx.x;
+    const float* b = (bias_vl && is_image && is_image[r]) ? bias_vl : bias;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const float x = logits[(size_t)r * ld + e];
+        const float sp = x > 20.f ? x : log1pf(expf(x));
+        const float s = sqrtf(sp);
+        sc[e] = s;
+        sel[e] = s + b[e];
+    }
+    __syncthreads();
+    float wsum = 0.f;
+    for (int k = 0; k < topk; ++k) {
+        float best = -INFINITY;
+        int bi = E;
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            const float v = sel[e];
+            if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+        }
+        // block argmax with the lower index winning ties
+        const float bm = block_max(best, red);
+        int cand = (best == bm) ? bi : E;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+        __syncthreads();
+        if (threadIdx.x == 0) s_best = E;
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) atomicMin(&s_best, cand);
+        __syncthreads();
+        const int e = s_best;
+        if (threadIdx.x == 0) {
+            idx[(size_t)r * topk + k] = e;
+            wts[(size_t)r * topk + k] = sc[e];
+            sel[e] = -INFINITY;
+        }
+        wsum += sc[e];
+        __syncthreads();
+    }
+    if (threadIdx.x < topk) {
+        float w = wts[(size_t)r * topk + threadIdx.x];
+        if (topk > 1) w = w / (wsum + 1e-20f);
+        wts[(size_t)r * topk + threadIdx.x] = w * route_scale;
+    }
+}
+
+// ---- fp4 experts ---------------------------------------------------------------------------------
+// Weights: e2m1 packed two per byte (even k in the low nibble) with one ue8m0 byte per 32 values
+// of K, per row.  Activations arrive already e4m3-per-32 round-tripped (f32).
+__device__ __forceinline__ void fp4x8_to_f32(uint32_t p, float* o) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((p >> (8 * i)) & 0xffu), __NV_E2M1);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        o[2 * i] = f.x;
+        o[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ float ue8m0_f32(uint8_t b) { return __uint_as_float((uint32_t)b << 23); }
+
+// dot of one packed fp4 row (K values, scales per 32) with x (shared memory, f32); whole warp.
+__device__ __forceinline__ float fp4_row_dot(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ srow,
+                                             const float* __restrict__ xs, int K, int lane) {
+    float acc = 0.f;
+    for (int c = lane; c < K / 16; c += 32) {  // 16 values = 8 bytes per lane step
+        const uint2 p = *reinterpret_cast<const uint2*>(wrow + (size_t)c * 8);
+        float v[16];
+        fp4x8_to_f32(p.x, v);
+        fp4x8_to_f32(p.y, v + 8);
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) d = fmaf(v[i], xs[c * 16 + i], d);
+        acc = fmaf(d, ue8m0_f32(srow[c >> 1]), acc);
+    }
+    return warp_sum(acc);
+}
+
+// h[r][s][i] = silu(min(gate, lim)) * clamp(up, +-lim) * w[r][s]; gate/up rows i of expert idx[r][s].
+// w13 [E][2][I][K/2], s13 [E][2][I][K/32].  grid (ceil(I/8), topk, rows), 8 warps = 8 rows i.
+__global__ void __launch_bounds__(256)
+expert_gate_up_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ idx, const float* __restrict__ wts,
+                      const uint8_t* __restrict__ w13, const uint8_t* __restrict__ s13, float* __restrict__ h,
+                      int topk, int I, int K, float lim) {
+    PDL_PROLOGUE();
+    extern __shared__ float xs[];
+    const int r = blockIdx.z, s = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = x[(size_t)r * ldx + k];
+    __syncthreads();
+    const int i = blockIdx.x * 8 + warp;
+    if (i >= I) return;
+    const int e = idx[(size_t)r * topk + s];
+    const size_t wrow = (size_t)K / 2, srow = (size_t)K / 32;
+    const uint8_t* wg = w13 + ((size_t)e * 2 * I + i) * wrow;
+    const uint8_t* wu = w13 + ((size_t)e * 2 * I + I + i) * wrow;
+    const uint8_t* sg = s13 + ((size_t)e * 2 * I + i) * srow;
+    const uint8_t* su = s13 + ((size_t)e * 2 * I + I + i) * srow;
+    float g = fp4_row_dot(wg, sg, xs, K, lane);
+    float u = fp4_row_dot(wu, su, xs, K, lane);
+    if (lane == 0) {
+        if (lim > 0.f) { u = fminf(fmaxf(u, -lim), lim); g = fminf(g, lim); }
+        h[((size_t)r * topk + s) * I + i] = siluf_(g) * u * wts[(size_t)r * topk + s];
+    }
+}
+
+// y[r][c] (+)= sum_s w2[idx[r][s]][c] . hq[r][s]   (hq already e4m3 round-tripped).
+// w2 [E][D][I/2], s2 [E][D][I/32].  grid (ceil(D/8), rows).
+__global__ void __launch_bounds__(256)
+expert_down_kernel(const float* __restrict__ hq, const int* __restrict__ idx, const uint8_t* __restrict__ w2,
+                   const uint8_t* __restrict__ s2, float* __restrict__ y, int ldy, int topk, int I, int D, int accumulate) {
+    PDL_PROLOGUE();
+    extern __shared__ float hs[];  // [topk][I]
+    const int r = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = threadIdx.x; k < topk * I; k += blockDim.x) hs[k] = hq[(size_t)r * topk * I + k];
+    __syncthreads();
+    const int c = blockIdx.x * 8 + warp;
+    if (c >= D) return;
+    float acc = 0.f;
+    for (int s = 0; s < topk; ++s) {
+        const int e = idx[(size_t)r * topk + s];
+        const uint8_t* wr = w2 + ((size_t)e * D + c) * (I / 2);
+        const uint8_t* sr = s2 + ((size_t)e * D + c) * (I / 32);
+        acc += fp4_row_dot(wr, sr, hs + (size_t)s * I, I, lane);
+    }
+    if (lane == 0) {
+        float* o = y + (size_t)r * ldy + c;
+        *o = accumulate ? *o + acc : acc;
+    }
+}
+
+// SwiGLU with clamps on a fused [gate | up] row (shared expert): out = silu(min(g, lim)) * clamp(u).
+__global__ void __launch_bounds__(256)
+swiglu_clamp_kernel(const float* __restrict__ gu, int ld, float* __restrict__ out, int ldo, int n, int I, float lim) {
+    PDL_PROLOGUE();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n * I) return;
+    const int r = t / I, i = t % I;
+    float g = gu[(size_t)r * ld + i], u = gu[(size_t)r * ld + I + i];
+    if (lim > 0.f) { u = fminf(fmaxf(u, -lim), lim); g = fminf(g, lim); }
+    out[(size_t)r * ldo + i] = siluf_(g) * u;
+}
+
+// ---- engram --------------------------------------------------------------------------------------
+// Phase 1 stores each row's compressed token id (DEAD = -1 for masked rows) at its position of
+// the slot's history; phase 2 hashes the 2..G-grams ending at each row.
+__global__ void __launch_bounds__(256)
+engram_hash_kernel(const int* __restrict__ ids, const uint8_t* __restrict__ dead, const RowMeta* __restrict__ meta,
+                   const int* __restrict__ token_map, int* __restrict__ hist, int hist_cap,
+                   const long long* __restrict__ mult, const long long* __restrict__ primes,
+                   const long long* __restrict__ offs, int pad_id, int n, int L, int G, int heads,
+                   long long* __restrict__ out) {
+    PDL_PROLOGUE();
+    for (int r = threadIdx.x; r < n; r += blockDim.x) {
+        const RowMeta m = meta[r];
+        if (m.pos < hist_cap) hist[(size_t)m.slot * hist_cap + m.pos] = (dead && dead[r]) ? -1 : token_map[ids[r]];
+    }
+    __syncthreads();
+    const int cols = (G - 1) * heads;
+    for (int t = threadIdx.x; t < n * L * cols; t += blockDim.x) {
+        const int r = t / (L * cols), l = (t / cols) % L, c = t % cols;
+        const int g = c / heads;  // uses look-backs 0 .. g + 1
+        const RowMeta m = meta[r];
+        long long rolling = 0;
+        bool blocked = false;
+        for (int shift = 0; shift <= g + 1; ++shift) {
+            const int p = m.pos - shift;
+            int tok = pad_id;
+            if (p < 0) blocked = true;
+            else {
+                const int src = hist[(size_t)m.slot * hist_cap + min(p, hist_cap - 1)];
+                if (src < 0) blocked = true;
+                if (!blocked) tok = src;
+            }
+            const long long prod = (long long)tok * mult[l * G + shift];
+            rolling = shift == 0 ? prod : (rolling ^ prod);
+        }
+        long long md = rolling % primes[l * cols + c];
+        out[((size_t)r * L + l) * cols + c] = md + offs[l * cols + c];
+    }
+}
+
+// Gather `cols` table rows (e4m3 with ue8m0 per 32) of layer index l; rows outside
+// [row_lo, row_hi) contribute zeros (another rank owns them).  out [n][cols * hd] f32.
+__global__ void __launch_bounds__(256)
+engram_gather_kernel(const long long* __restrict__ hash, int L, int l, int cols, const uint8_t* __restrict__ table,
+                     const uint8_t* __restrict__ scale, long long row_lo, long long row_hi, int hd,
+                     float* __restrict__ out) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y, c = blockIdx.x;
+    const long long id = hash[((size_t)r * L + l) * cols + c];
+    float* o = out + ((size_t)r * cols + c) * hd;
+    const bool mine = id >= row_lo && id < row_hi;
+    const size_t loc = (size_t)(id - row_lo);
+    for (int j = threadIdx.x; j < hd; j += blockDim.x) {
+        float v = 0.f;
+        if (mine) {
+            const __half_raw hr = __nv_cvt_fp8_to_halfraw(table[loc * hd + j], __NV_E4M3);
+            v = __half2float(*reinterpret_cast<const __half*>(&hr)) * ue8m0_f32(scale[loc * (hd / 32) + j / 32]);
+        }
+        o[j] = v;
+    }
+}
+
+// R[r][i] += gate_i * value; gate_i = sigmoid(sign(d) sqrt(max(|d|, 1e-6))),
+// d = sum(R_i * qk_i * key_i) * rstd(R_i) * rstd(key_i) / sqrt(D).  kv [n][(hc + 1) * D].
+__global__ void __launch_bounds__(256)
+engram_apply_kernel(float* __restrict__ R, const float* __restrict__ kv, const float* __restrict__ qk,
+                    const uint8_t* __restrict__ dead, int hc, int D, float eps) {
+    PDL_PROLOGUE();
+    __shared__ float red[32];
+    const int r = blockIdx.y, i = blockIdx.x;
+    if (dead && dead[r]) return;
+    float* h = R + ((size_t)r * hc + i) * D;
+    const float* key = kv + (size_t)r * (hc + 1) * D + (size_t)i * D;
+    const float* val = kv + (size_t)r * (hc + 1) * D + (size_t)hc * D;
+    const float* w = qk + (size_t)i * D;
+    float hh = 0.f, kk = 0.f, dt = 0.f;
+    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+        const float a = h[j], b = key[j];
+        hh += a * a;
+        kk += b * b;
+        dt += a * w[j] * b;
+    }
+    hh = block_sum(hh, red);
+    kk = block_sum(kk, red);
+    dt = block_sum(dt, red);
+    const float d = dt * rsqrtf(hh / D + eps) * rsqrtf(kk / D + eps) * rsqrtf((float)D);
+    const float g = sigmoidf_(copysignf(sqrtf(fmaxf(fabsf(d), 1e-6f)), d));
+    for (int j = threadIdx.x; j < D; j += blockDim.x) h[j] += g * val[j];
+}
+
+// ---- small helpers -------------------------------------------------------------------------------
+// out[r][col0 + j] = mean_i R[r][i][j]
+__global__ void __launch_bounds__(256)
+copy_mean_kernel(const float* __restrict__ R, float* __restrict__ out, int ldo, int col0, int hc, int D) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= D) return;
+    float s = 0.f;
+    for (int i = 0; i < hc; ++i) s += R[((size_t)r * hc + i) * D + j];
+    out[(size_t)r * ldo + col0 + j] = s / hc;
+}
+
+// x[j] = table[id][j] (bf16 table), id read from device memory.
+__global__ void __launch_bounds__(256)
+gather_row_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ id, int D, int vocab,
+                  float* __restrict__ out, SplitBuf osp) {
+    PDL_PROLOGUE();
+    const int t = min(max(id[0], 0), vocab - 1);
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < D; j += gridDim.x * blockDim.x) {
+        const float v = __bfloat162float(table[(size_t)t * D + j]);
+        out[j] = v;
+        split_store(osp, 0, j, v);
+    }
+}
+
+// plain f32-weight GEMV (compressor projections): out[r][n] = sum_k x[r][k] W[n][k]; warp per n.
+__global__ void __launch_bounds__(256)
+gemv_f32w_kernel(const float* __restrict__ W, const float* __restrict__ x, int ldx, float* __restrict__ out, int ldo,
+                 int m, int N, int K) {
+    PDL_PROLOGUE();
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    for (int k = lane * 4; k < K; k += 128) {
+        const float4 w = *reinterpret_cast<const float4*>(W + (size_t)n * K + k);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < m) {
+                const float4 v = *reinterpret_cast<const float4*>(x + (size_t)r * ldx + k);
+                acc[r] += w.x * v.x + w.y * v.y + w.z * v.z + w.w * v.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < m) out[(size_t)r * ldo + n] = v;
+    }
+}
+
+}  // namespace
+
+// ---- C ABI ------------------------------------------------------------------------------------------
+static inline SplitBuf mk_split(void* base, int64_t ld, int64_t plane, int64_t mask) {
+    return SplitBuf{(uint16_t*)base, (int)ld, (int)plane, (int)mask};
+}
+
+FB_API int fb_d4_quant_rows(const float* x, int64_t ldx, float* xq, int64_t ldq, int64_t n, int64_t K, void* s_base,
+                            int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (K % 32) return (int)cudaErrorInvalidValue;
+    const int64_t warps = n * (K / 32);
+    FB_LAUNCH((quant_rows_kernel), (warps + 7) / 8, 256, 0, st, x, (int)ldx, xq, (int)ldq,
+              mk_split(s_base, s_ld, s_plane, s_mask), (int)n, (int)K);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_hc_pre(const float* R, float* acc, const float* scale, const float* base, const float* ln_w,
+                        const float* pre_in, float* pre_out, float* post_out, float* comb_out, float* xn_out,
+                        float* xc_out, int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
+                        void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (mult != 4) return (int)cudaErrorInvalidValue;
+    const size_t sm = (32 + H) * sizeof(float);
+    if (sm > 48 * 1024) cudaFuncSetAttribute(hc_pre_offset_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    FB_LAUNCH((hc_pre_offset_kernel), n, 512, sm, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,
+              xn_out, xc_out, (int)H, rms_eps, hc_eps, (int)iters, mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_rope_heads(float* x, int64_t ld, int64_t n, int64_t heads, int64_t hd, int64_t rd, const float* freqs,
+                            const void* meta, int64_t pos_off, int64_t inverse, int64_t fp4_rt, void* s_base,
+                            int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (hd % 32 || rd % 2) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((rope_heads_kernel), dim3((unsigned)heads, (unsigned)n), 128, 0, st, x, (int)ld, (int)heads, (int)hd, (int)rd,
+              freqs, (const RowMeta*)meta, (int)pos_off, (int)inverse, (int)fp4_rt, mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_kv_append(const float* kv, int64_t ld, const float* norm_w, const float* freqs, const void* meta,
+                           void* ring, int64_t cap, float* rows_out, int64_t n, int64_t hd, int64_t rd, float eps,
+                           int64_t pos_off, cudaStream_t st) {
+    if (hd % 32) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((kv_append_kernel), n, 128, (32 + hd) * sizeof(float), st, kv, (int)ld, norm_w, freqs, (const RowMeta*)meta,
+              (__nv_bfloat16*)ring, (int)cap, rows_out, (int)hd, (int)rd, eps, (int)pos_off);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_compress(const float* kv, const float* sc, int64_t ld, const void* meta, float* ring_kv, float* ring_sc,
+                          int64_t depth, const float* norm_w, float* lat, int* flag, int64_t n, int64_t hd,
+                          int64_t ratio, float eps, cudaStream_t st) {
+    if (ratio > 1 && depth < ratio + n) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((compress_kernel), 1, 512, 0, st, kv, sc, (int)ld, (const RowMeta*)meta, ring_kv, ring_sc, (int)depth, norm_w,
+              lat, flag, (int)n, (int)hd, (int)ratio, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_latent_store(const float* lat, const int* flag, const void* meta, const float* freqs, void* cache,
+                              int64_t cap, int64_t n, int64_t hd, int64_t rd, int64_t ratio, cudaStream_t st) {
+    if (hd % 16) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((latent_store_kernel), n, 128, hd * sizeof(float), st, lat, flag, (const RowMeta*)meta, freqs,
+              (__nv_bfloat16*)cache, (int)cap, (int)hd, (int)rd, (int)ratio);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_index_k_store(const float* kraw, int64_t ld, const int* flag, const void* meta, const float* norm_w,
+                               const float* freqs, void* cache, int64_t cap, int64_t n, int64_t id, int64_t rd,
+                               int64_t ratio, float eps, cudaStream_t st) {
+    if (id % 32) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((index_k_store_kernel), n, 128, (32 + id) * sizeof(float), st, kraw, (int)ld, flag, (const RowMeta*)meta,
+              norm_w, freqs, (__nv_bfloat16*)cache, (int)cap, (int)id, (int)rd, (int)ratio, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_index_score(const float* q, int64_t ldq, const float* w, int64_t ldw, const void* kc, int64_t cap,
+                             const void* meta, float* score, int64_t lds, int64_t n, int64_t heads, int64_t id,
+                             int64_t ratio, float wscale, cudaStream_t st) {
+    const size_t sm = ((size_t)heads * (id + 1) + 8 * id) * sizeof(float);
+    if (sm > 48 * 1024) cudaFuncSetAttribute(index_score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    const int64_t len = lds < cap ? lds : cap;
+    FB_LAUNCH((index_score_kernel), dim3((unsigned)((len + 31) / 32), (unsigned)n), 256, sm, st, q, (int)ldq, w, (int)ldw,
+              (const __nv_bfloat16*)kc, (int)cap, (const RowMeta*)meta, score, (int)lds, (int)heads, (int)id, (int)ratio, wscale);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_topk_sorted(const float* score, int64_t lds, const uint8_t* mask, int64_t ldm, const void* meta,
+                             int64_t ratio, int64_t div, int64_t k, int* out, int64_t ldo, int64_t n, cudaStream_t st) {
+    FB_LAUNCH((topk_sorted_kernel), n, 1024, 0, st, score, (int)lds, mask, (int)ldm, (const RowMeta*)meta, (int)ratio,
+              (int)div, (int)k, out, (int)ldo);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_block_max(const float* score, int64_t lds, const void* meta, int64_t ratio, int64_t bs, float* out,
+                           int64_t ldo, int64_t n, cudaStream_t st) {
+    FB_LAUNCH((block_max_kernel), dim3((unsigned)((ldo + 255) / 256), (unsigned)n), 256, 0, st, score, (int)lds,
+              (const RowMeta*)meta, (int)ratio, (int)bs, out, (int)ldo);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_cand_mask(const int* blk, int64_t ldb, int64_t kb, int64_t bs, uint8_t* mask, int64_t ldm, int64_t n,
+                           cudaStream_t st) {
+    cudaError_t e = cudaMemsetAsync(mask, 0, (size_t)n * ldm, st);
+    if (e != cudaSuccess) return (int)e;
+    FB_LAUNCH((cand_mask_kernel), dim3((unsigned)((kb * bs + 255) / 256), (unsigned)n), 256, 0, st, blk, (int)ldb, (int)kb,
+              (int)bs, mask, (int)ldm);
+    return FB_LAUNCH_CHECK();
+}
+
+template <int NJ>
+static int launch_attn(const float* q, int ldq, const void* ring, int cap, int window, const void* comp, int ccap,
+                       const int* idx, int ldi, int ktop, const float* extra, int n_extra, const float* sink,
+                       const float* freqs, int rd, const void* meta, int pos_off, int win_mode, float scale, int heads,
+                       float* out, int ldo, SplitBuf osp, int n, cudaStream_t st) {
+    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n), 256, 0, st, q, ldq,
+              (const __nv_bfloat16*)ring, cap, window, (const __nv_bfloat16*)comp, ccap, idx, ldi, ktop, extra, n_extra, sink,
+              freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, out, ldo, osp);
+    return FB_LAUNCH_CHECK();
+}
+
+// q [n][heads*hd] un-rotated; out gets the inverse rotation.  idx may be null (ktop = 0), extra may be null.
+FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int64_t cap, int64_t window, const void* comp,
+                             int64_t ccap, const int* idx, int64_t ldi, int64_t ktop, const float* extra, int64_t n_extra,
+                             const float* sink, const float* freqs, int64_t rd, const void* meta, int64_t pos_off,
+                             int64_t win_mode, float scale, int64_t heads, int64_t hd, float* out, int64_t ldo, int64_t n,
+                             void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    const SplitBuf osp = mk_split(s_base, s_ld, s_plane, s_mask);
+    if (!idx) ktop = 0;
+    if (!extra) n_extra = 0;
+#define D4_ATTN(NJ) launch_attn<NJ>(q, (int)ldq, ring, (int)cap, (int)window, comp, (int)ccap, idx, (int)ldi, (int)ktop, extra, \
+                                    (int)n_extra, sink, freqs, (int)rd, meta, (int)pos_off, (int)win_mode, scale, (int)heads, out, \
+                                    (int)ldo, osp, (int)n, st)
+    switch (hd) {
+        case 64: return D4_ATTN(1);
+        case 128: return D4_ATTN(2);
+        case 256: return D4_ATTN(4);
+        case 512: return D4_ATTN(8);
+        default: return (int)cudaErrorInvalidValue;
+    }
+#undef D4_ATTN
+}
+
+FB_API int fb_d4_route(const float* logits, int64_t ld, const float* bias, const float* bias_vl, const uint8_t* is_image,
+                       int64_t n, int64_t E, int64_t topk, float route_scale, int* idx, float* wts, cudaStream_t st) {
+    if (topk > 32) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((route_kernel), n, 128, 2 * E * sizeof(float), st, logits, (int)ld, bias, bias_vl, is_image, (int)E, (int)topk,
+              route_scale, idx, wts);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_expert_gate_up(const float* x, int64_t ldx, const int* idx, const float* wts, const void* w13,
+                                const void* s13, float* h, int64_t n, int64_t topk, int64_t I, int64_t K, float lim,
+                                cudaStream_t st) {
+    if (K % 32) return (int)cudaErrorInvalidValue;
+    const size_t sm = K * sizeof(float);
+    if (sm > 48 * 1024) cudaFuncSetAttribute(expert_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    FB_LAUNCH((expert_gate_up_kernel), dim3((unsigned)((I + 7) / 8), (unsigned)topk, (unsigned)n), 256, sm, st, x, (int)ldx, idx,
+              wts, (const uint8_t*)w13, (const uint8_t*)s13, h, (int)topk, (int)I, (int)K, lim);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_expert_down(const float* hq, const int* idx, const void* w2, const void* s2, float* y, int64_t ldy,
+                             int64_t n, int64_t topk, int64_t I, int64_t D, int64_t accumulate, cudaStream_t st) {
+    if (I % 32) return (int)cudaErrorInvalidValue;
+    const size_t sm = (size_t)topk * I * sizeof(float);
+    if (sm > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    FB_LAUNCH((expert_down_kernel), dim3((unsigned)((D + 7) / 8), (unsigned)n), 256, sm, st, hq, idx, (const uint8_t*)w2,
+              (const uint8_t*)s2, y, (int)ldy, (int)topk, (int)I, (int)D, (int)accumulate);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_swiglu_clamp(const float* gu, int64_t ld, float* out, int64_t ldo, int64_t n, int64_t I, float lim,
+                              cudaStream_t st) {
+    FB_LAUNCH((swiglu_clamp_kernel), (n * I + 255) / 256, 256, 0, st, gu, (int)ld, out, (int)ldo, (int)n, (int)I, lim);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_engram_hash(const int* ids, const uint8_t* dead, const void* meta, const int* token_map, int* hist,
+                             int64_t hist_cap, const long long* mult, const long long* primes, const long long* offs,
+                             int64_t pad_id, int64_t n, int64_t L, int64_t G, int64_t heads, long long* out, cudaStream_t st) {
+    FB_LAUNCH((engram_hash_kernel), 1, 256, 0, st, ids, dead, (const RowMeta*)meta, token_map, hist, (int)hist_cap, mult, primes,
+              offs, (int)pad_id, (int)n, (int)L, (int)G, (int)heads, out);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_engram_gather(const long long* hash, int64_t L, int64_t l, int64_t cols, const void* table,
+                               const void* scale, int64_t row_lo, int64_t row_hi, int64_t hd, float* out, int64_t n,
+                               cudaStream_t st) {
+    FB_LAUNCH((engram_gather_kernel), dim3((unsigned)cols, (unsigned)n), 256, 0, st, hash, (int)L, (int)l, (int)cols,
+              (const uint8_t*)table, (const uint8_t*)scale, (long long)row_lo, (long long)row_hi, (int)hd, out);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_engram_apply(float* R, const float* kv, const float* qk, const uint8_t* dead, int64_t n, int64_t hc,
+                              int64_t D, float eps, cudaStream_t st) {
+    FB_LAUNCH((engram_apply_kernel), dim3((unsigned)hc, (unsigned)n), 256, 0, st, R, kv, qk, dead, (int)hc, (int)D, eps);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_copy_mean(const float* R, float* out, int64_t ldo, int64_t col0, int64_t n, int64_t hc, int64_t D,
+                           cudaStream_t st) {
+    FB_LAUNCH((copy_mean_kernel), dim3((unsigned)((D + 255) / 256), (unsigned)n), 256, 0, st, R, out, (int)ldo, (int)col0,
+              (int)hc, (int)D);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_gather_row(const void* table, const int* id, int64_t D, int64_t vocab, float* out, void* s_base,
+                            int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    FB_LAUNCH((gather_row_kernel), (D + 255) / 256, 256, 0, st, (const __nv_bfloat16*)table, id, (int)D, (int)vocab, out,
+              mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_gemv_f32w(const float* W, const float* x, int64_t ldx, float* out, int64_t ldo, int64_t m, int64_t N,
+                           int64_t K, cudaStream_t st) {
+    if (m > 8 || (K % 4) || (ldx % 4)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((gemv_f32w_kernel), (N + 7) / 8, 256, 0, st, W, x, (int)ldx, out, (int)ldo, (int)m, (int)N, (int)K);
+    return FB_LAUNCH_CHECK();
+}

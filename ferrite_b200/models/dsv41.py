@@ -1,0 +1,455 @@
+"""DSV41 on the device: weight packing, per-slot caches and the row-batched forward pass.
+
+One process per GPU.  ``forward(rows, ids)`` runs ``n <= max_rows`` rows (decode, multi-row
+verify or a prefill chunk) through the 40 layers with the kernels of ``csrc/kernels/dsv41.cu``
+plus the shared GEMV / tcgen05 GEMM, hyper-connection, argmax and all-reduce kernels.  Every
+position-dependent quantity is read from device-resident row metadata, so a decode step is
+replayable as one CUDA graph.
+
+Tensor parallelism follows the reference's mapping (``crates/ferrite-models/src/dsv41/
+weights.rs:27-330``): query heads / sinks / indexer heads by rank, ``wo_a`` by groups, ``wo_b``
+by input columns (all-reduce #1), every routed expert on every rank with its intermediate dim
+split (all-reduce #2), engram table by rows (all-reduce), indexer scores all-reduced; the
+shared expert is split like the routed ones (the reference's ``DSV41_SHARED_TP`` mode) when
+its slice stays a multiple of the quantisation block.
+
+Dense e4m3 weights are expanded to bf16 at load time (exact: 4 significant bits times a power
+of two) and stream through the bf16 tensor-core GEMV/GEMM; expert weights stay packed e2m1
+with ue8m0 scales.  Replaces ``crates/ferrite-models/src/dsv41/chain_dev.rs`` (``DevChain``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import _lib
+from ..ops import quant as Q
+from .dsv41_config import Dsv41Config
+from .dsv41_engram import EngramLayout, hash_multipliers
+from .dsv41_ref import rope_freqs
+from .dsv41_weights import padded_inter, shard_tensor
+from .glm import ROWMETA_BYTES, Act, GlmDeviceModel, RowSet, View
+
+KMAXMIX = 24
+
+
+class DictWeights:
+    """Full f32 tensors by checkpoint name."""
+
+    def __init__(self, weights: Dict[str, torch.Tensor]):
+        self.w = weights
+
+    def get(self, name: str) -> torch.Tensor:
+        return self.w[name]
+
+    def has(self, name: str) -> bool:
+        return name in self.w
+
+
+class Dsv41DeviceModel:
+    def __init__(self, cfg: Dsv41Config, src, rank: int = 0, world: int = 1, device="cuda", allreduce=None,
+                 max_rows: int = 8, max_ctx: int = 1024, n_slots: int = 1, token_map=None):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.dev = torch.device(device)
+        self.K = _lib.lib()
+        self.allreduce = allreduce
+        assert world == 1 or allreduce is not None
+        self.max_rows, self.max_ctx, self.n_slots = max_rows, max_ctx, n_slots
+        assert cfg.hc_mult == 4 and cfg.n_heads % world == 0 and cfg.o_groups % world == 0
+        assert cfg.index_n_heads % world == 0
+        self.Hl = cfg.n_heads // world
+        self.Gl = cfg.o_groups // world
+        self.IHl = cfg.index_n_heads // world
+        self.Il = padded_inter(cfg, world) if world > 1 else cfg.moe_inter_dim
+        per = (cfg.moe_inter_dim + world - 1) // world
+        self.shared_tp = world > 1 and per % 32 == 0 and per * world == cfg.moe_inter_dim
+        self.Is = per if self.shared_tp else cfg.moe_inter_dim
+        self.tc_min_rows = 16
+        self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.win_cap = cfg.window_size + max_rows
+        self.depth = 16
+        self.token_map = token_map
+        self.layout = EngramLayout.from_config(cfg)
+        self._pack(src)
+        self._alloc()
+
+    gemv = GlmDeviceModel.gemv
+
+    # ---- packing -------------------------------------------------------------------------------
+    def _bf(self, t):
+        return t.to(self.dev, torch.bfloat16).contiguous()
+
+    def _f(self, t):
+        return t.to(self.dev, torch.float32).contiguous()
+
+    def _sh(self, src, name):
+        return shard_tensor(self.cfg, name, src.get(name), self.rank, self.world)
+
+    def _pack_block(self, src, p: str, layer: int) -> dict:
+        cfg = self.cfg
+        a, f = p + "attn.", p + "ffn."
+        L: dict = {"layer": layer, "ratio": cfg.ratio(layer)}
+        L["w_qkv_a"] = self._bf(torch.cat([src.get(a + "wq_a.weight"), src.get(a + "wkv.weight")], 0))
+        L["q_norm"] = self._f(src.get(a + "q_norm.weight"))
+        L["kv_norm"] = self._f(src.get(a + "kv_norm.weight"))
+        L["wq_b"] = self._bf(self._sh(src, a + "wq_b.weight"))
+        L["sink"] = self._f(self._sh(src, a + "attn_sink"))
+        L["wo_a"] = self._bf(self._sh(src, a + "wo_a.weight"))
+        L["wo_b"] = self._bf(self._sh(src, a + "wo_b.weight"))
+        if layer < cfg.n_layers and cfg.is_kv_source(layer):
+            c = a + "compressor."
+            ws = [src.get(c + "wkv.weight")]
+            if cfg.ratio(layer) > 1:
+                ws.append(src.get(c + "wgate.weight"))
+            L["c_w"] = self._f(torch.cat(ws, 0))
+            L["c_norm"] = self._f(src.get(c + "norm.weight"))
+            L["i_wk"] = self._bf(src.get(a + "indexer.wk.weight"))
+            L["i_knorm"] = self._f(src.get(a + "indexer.k_norm.weight"))
+        if layer < cfg.n_layers and cfg.is_index_source(layer):
+            L["i_wq_b"] = self._bf(self._sh(src, a + "indexer.wq_b.weight"))
+            L["i_wproj"] = self._bf(self._sh(src, a + "indexer.weights_proj.weight"))
+        L["attn_norm"] = self._f(src.get(p + "attn_norm.weight"))
+        L["ffn_norm"] = self._f(src.get(p + "ffn_norm.weight"))
+        for w in ("attn", "ffn"):
+            L[f"hc_{w}_fn"] = self._f(src.get(p + f"hc_{w}_fn"))
+            L[f"hc_{w}_base"] = self._f(src.get(p + f"hc_{w}_base"))
+            L[f"hc_{w}_scale"] = self._f(src.get(p + f"hc_{w}_scale"))
+        E, topk = cfg.moe_shape(layer)
+        L["E"], L["topk"] = E, topk
+        L["gate_w"] = self._bf(src.get(f + "gate.weight"))
+        L["gate_b"] = self._f(src.get(f + "gate.bias"))
+        L["gate_bvl"] = self._f(src.get(f + "gate.bias_vl")) if src.has(f + "gate.bias_vl") else None
+        d, Il = cfg.dim, self.Il
+        if hasattr(src, "expert_pack"):
+            L["w13"], L["s13"], L["w2"], L["s2"] = src.expert_pack(f, E, Il, self.rank, self.world, self.dev)
+        else:
+            w13 = torch.empty(E, 2, Il, d // 2, dtype=torch.uint8, device=self.dev)
+            s13 = torch.empty(E, 2, Il, d // 32, dtype=torch.uint8, device=self.dev)
+            w2 = torch.empty(E, d, Il // 2, dtype=torch.uint8, device=self.dev)
+            s2 = torch.empty(E, d, Il // 32, dtype=torch.uint8, device=self.dev)
+            for e in range(E):
+                for k, nm in enumerate(("w1", "w3")):
+                    pk, sc = Q.quant_fp4_weight(self._sh(src, f + f"experts.{e}.{nm}.weight").float(), cfg.fp4_block)
+                    w13[e, k].copy_(pk)
+                    s13[e, k].copy_(sc)
+                pk, sc = Q.quant_fp4_weight(self._sh(src, f + f"experts.{e}.w2.weight").float(), cfg.fp4_block)
+                w2[e].copy_(pk)
+                s2[e].copy_(sc)
+            L["w13"], L["s13"], L["w2"], L["s2"] = w13, s13, w2, s2
+        sw1, sw3, sw2 = (src.get(f + f"shared_experts.{n}.weight") for n in ("w1", "w3", "w2"))
+        if self.shared_tp:
+            lo = self.rank * self.Is
+            sw1, sw3, sw2 = sw1[lo:lo + self.Is], sw3[lo:lo + self.Is], sw2[:, lo:lo + self.Is]
+        L["sh_w13"] = self._bf(torch.cat([sw1, sw3], 0))
+        L["sh_w2"] = self._bf(sw2)
+        return L
+
+    def _pack(self, src):
+        cfg = self.cfg
+        self.embed = self._bf(src.get("embed.weight"))
+        self.norm_w = self._f(src.get("norm.weight"))
+        self.head = self._bf(src.get("head.weight"))
+        self.layers: List[dict] = []
+        for l in range(cfg.n_layers):
+            p = f"layers.{l}."
+            L = self._pack_block(src, p, l)
+            ei = cfg.engram_index(l)
+            if ei >= 0:
+                tab = self._sh(src, p + "engram.embed.weight").float()
+                rows = cfg.engram_num_embeddings[ei]
+                per = (rows + self.world - 1) // self.world
+                q, sc = Q.fp8_act_quant(tab, cfg.fp8_block)
+                L["e_idx"] = ei
+                L["e_lo"], L["e_hi"] = self.rank * per, min(rows, (self.rank + 1) * per)
+                L["e_table"] = q.to(torch.float8_e4m3fn).view(torch.uint8).to(self.dev).contiguous()
+                L["e_scale"] = sc.to(self.dev).contiguous()
+                L["e_wkv"] = self._bf(src.get(p + "engram.wkv.weight"))
+                L["e_qk"] = self._f(src.get(p + "engram.q_weight").float() * src.get(p + "engram.k_weight").float())
+            self.layers.append(L)
+        self.freq_win = self._f(rope_freqs(cfg.rope_head_dim, cfg.rope_theta, 0, 1.0, cfg.beta_fast, cfg.beta_slow))
+        self.freq_cmp = self._f(rope_freqs(cfg.rope_head_dim, cfg.compress_rope_theta, cfg.original_seq_len,
+                                           cfg.rope_factor, cfg.beta_fast, cfg.beta_slow))
+        if self.layout is not None:
+            cv = cfg.engram_compressed_vocab_size
+            tm = self.token_map if self.token_map is not None else [t % cv for t in range(cfg.vocab_size)]
+            self.e_map = torch.tensor(list(tm), dtype=torch.int32, device=self.dev)
+            self.e_pad = int(tm[cfg.engram_pad_id])
+            self.e_mult = hash_multipliers(self.layout.layer_ids, self.layout.max_ngram, cv).to(self.dev).contiguous()
+            self.e_primes = self.layout.flat_primes().to(self.dev).contiguous()
+            self.e_offs = self.layout.offsets().to(self.dev).contiguous()
+
+    # ---- buffers -------------------------------------------------------------------------------
+    def _z(self, *shape, dtype=torch.float32):
+        return torch.zeros(*shape, dtype=dtype, device=self.dev)
+
+    def _alloc(self):
+        cfg, M, S = self.cfg, self.max_rows, self.n_slots
+        d, hd, ql = cfg.dim, cfg.head_dim, cfg.q_lora_rank
+        ws: dict = {}
+        ws["R0"], ws["R1"] = self._z(M, 4, d), self._z(M, 4, d)
+        ws["R"] = ws["R0"]
+        ws["hc_acc"] = self._z(M, KMAXMIX + 1)
+        ws["pre0"], ws["pre1"] = self._z(M, 4), self._z(M, 4)
+        ws["post"], ws["comb"] = self._z(M, 4), self._z(M, 16)
+        ws["x"] = Act(self.dev, M, d)
+        ws["xq"] = Act(self.dev, M, d)
+        ws["qa"] = self._z(M, ql + hd)
+        ws["qr"] = Act(self.dev, M, ql)
+        ws["q"] = self._z(M, self.Hl * hd)
+        ws["o"] = Act(self.dev, M, self.Hl * hd)
+        ws["low"] = Act(self.dev, M, self.Gl * cfg.o_lora_rank)
+        ws["y"] = self._z(M, d)
+        ws["ckv"] = self._z(M, 2 * hd)
+        ws["lat"] = self._z(M, hd)
+        ws["flag"] = self._z(M, dtype=torch.int32)
+        ws["kraw"] = self._z(M, cfg.index_head_dim)
+        ws["iq"] = self._z(M, self.IHl * cfg.index_head_dim)
+        ws["iw"] = self._z(M, max(self.IHl, 8))
+        self.ccap = {r: self.max_ctx // r for r in set(cfg.compress_ratios) if r > 0}
+        cmax = max(self.ccap.values()) if self.ccap else 32
+        ws["score"] = self._z(M, cmax)
+        nbmax = (cmax + cfg.candidate_block_size - 1) // cfg.candidate_block_size
+        ws["bscore"] = self._z(M, nbmax)
+        ws["bidx"] = self._z(M, max(1, min(cfg.candidate_topk_blocks, nbmax)), dtype=torch.int32)
+        ws["cand"] = self._z(M, cmax, dtype=torch.uint8)
+        ws["topk"] = torch.full((M, cfg.index_topk), -1, dtype=torch.int32, device=self.dev)
+        Emax = max(cfg.n_routed_experts, cfg.dspark_n_routed_experts)
+        kmax = max(cfg.n_activated_experts, cfg.dspark_n_activated_experts)
+        ws["rlogit"] = self._z(M, Emax)
+        ws["ridx"] = self._z(M, kmax, dtype=torch.int32)
+        ws["rw"] = self._z(M, kmax)
+        ws["h"] = self._z(M * kmax, self.Il)
+        ws["gu"] = self._z(M, 2 * self.Is)
+        ws["hs"] = Act(self.dev, M, self.Is)
+        ws["logits"] = self._z(M, cfg.vocab_size)
+        ws["amax_part"] = self._z(M * 64, dtype=torch.int64)
+        ws["out_ids"] = self._z(M, dtype=torch.int32)
+        ws["mh"] = self._z(M, d * max(1, len(cfg.dspark_target_layer_ids)))
+        ws["is_image"] = self._z(M, dtype=torch.uint8)
+        if self.layout is not None:
+            cols = self.layout.hash_cols
+            ws["ehash"] = self._z(M, len(self.layout.layer_ids), cols, dtype=torch.int64)
+            ws["egat"] = Act(self.dev, M, cols * cfg.engram_head_dim)
+            ws["ekv"] = self._z(M, (cfg.hc_mult + 1) * d)
+            self.e_hist = torch.full((S, self.max_ctx), -1, dtype=torch.int32, device=self.dev)
+        self.ws = ws
+        # per-slot caches
+        nl = cfg.n_total_layers
+        self.ring = torch.zeros(nl, S, self.win_cap, hd, dtype=torch.bfloat16, device=self.dev)
+        self.comp: Dict[int, torch.Tensor] = {}
+        self.kidx: Dict[int, torch.Tensor] = {}
+        self.cring: Dict[int, tuple] = {}
+        for l in cfg.kv_source_layers:
+            cap = self.ccap[cfg.ratio(l)]
+            self.comp[l] = torch.zeros(S, cap, hd, dtype=torch.bfloat16, device=self.dev)
+            self.kidx[l] = torch.zeros(S, cap, cfg.index_head_dim, dtype=torch.bfloat16, device=self.dev)
+            if cfg.ratio(l) > 1:
+                self.cring[l] = (self._z(S, self.depth, hd), self._z(S, self.depth, hd))
+        self.seq_len = self._z(S, dtype=torch.int32)
+
+    def reset_slot(self, slot: int):
+        self.seq_len[slot] = 0
+
+    def make_rows(self, slots: List[int], gsizes: List[int]) -> RowSet:
+        return GlmDeviceModel.make_rows(self, slots, gsizes)
+
+    # ---- forward ---------------------------------------------------------------------------------
+    def _reduce(self, t, n):
+        if self.world > 1:
+            self.allreduce(t[:n])
+
+    def _quant(self, src_f, dst: Act, n, K, ld=None):
+        """dst.f / dst planes = e4m3-per-32 round trip of src (may alias dst.f)."""
+        ld = ld if ld is not None else dst.ld
+        self.K.call("fb_d4_quant_rows", src_f, ld, dst.f, dst.ld, n, K, *dst.sp(1))
+
+    def _hc_post_mix(self, fn_next, n, first=False):
+        cfg, ws = self.cfg, self.ws
+        rin = ws["R"]
+        mix = (2 + cfg.hc_mult) * cfg.hc_mult
+        if first:
+            self.K.call("fb_hc_post_mix", rin, rin, None, None, None, fn_next, ws["hc_acc"], n, cfg.dim, mix)
+            return
+        rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
+        self.K.call("fb_hc_post_mix", rin, rout, ws["y"], ws["post"], ws["comb"], fn_next, ws["hc_acc"], n, cfg.dim, mix)
+        ws["R"] = rout
+
+    def _hc_pre(self, L, site, ln, n, coeffs=True):
+        """Coefficients of this site (stored for the next one) and the contraction with the previous
+        site's `pre`; leaves the normed input in ws['x'] (f32 + bf16 planes)."""
+        cfg, ws = self.cfg, self.ws
+        x = ws["x"]
+        pin, pout = ws["pre_cur"], ws["pre_nxt"]
+        self.K.call("fb_d4_hc_pre", ws["R"], ws["hc_acc"] if coeffs else None,
+                    L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
+                    ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
+                    cfg.hc_sinkhorn_iters, *x.sp(1))
+        if coeffs:
+            ws["pre_cur"], ws["pre_nxt"] = pout, pin
+
+    def _attention(self, L, rs: RowSet, shared: dict, ring, extra=None, n_extra=0, win_mode=0):
+        cfg, ws, n = self.cfg, self.ws, rs.n
+        d, hd, ql, rd = cfg.dim, cfg.head_dim, cfg.q_lora_rank, cfg.rope_head_dim
+        layer, r = L["layer"], L["ratio"]
+        x, xq, qr = ws["x"], ws["xq"], ws["qr"]
+        freqs = self.freq_cmp if r > 0 else self.freq_win
+        self._quant(x.f, xq, n, d)
+        self.gemv(L["w_qkv_a"], xq, ws["qa"], n, ql + hd, d)
+        self.K.call("fb_rmsnorm", ws["qa"], None, None, L["q_norm"], qr.f, n, ql, ql + hd, ql, float(cfg.norm_eps),
+                    None, 0, 0, 0)
+        self._quant(qr.f, qr, n, ql)
+        self.gemv(L["wq_b"], qr, ws["q"], n, self.Hl * hd, ql)
+        kv_raw = View(ws["qa"], ql)
+        if extra is None:
+            self.K.call("fb_d4_kv_append", kv_raw, ql + hd, L["kv_norm"], freqs, rs.meta, ring, self.win_cap, None, n, hd,
+                        rd, float(cfg.norm_eps), 0)
+        else:   # a draft block: its own KV rows stay out of the ring
+            self.K.call("fb_d4_kv_append", kv_raw, ql + hd, L["kv_norm"], freqs, rs.meta, None, self.win_cap, extra, n, hd,
+                        rd, float(cfg.norm_eps), 0)
+        comp, idx, ktop, ccap = None, None, 0, 0
+        if r > 0:
+            src = cfg.kv_source_of(layer)
+            ccap = self.ccap[r]
+            if "c_w" in L:
+                nc = L["c_w"].shape[0]
+                self.K.call("fb_d4_gemv_f32w", L["c_w"], x.f, d, ws["ckv"], 2 * hd, n, nc, d)
+                rk, rsc = self.cring.get(layer, (None, None))
+                self.K.call("fb_d4_compress", ws["ckv"], View(ws["ckv"], hd), 2 * hd, rs.meta, rk, rsc, self.depth,
+                            L["c_norm"], ws["lat"], ws["flag"], n, hd, r, float(cfg.norm_eps))
+                self.gemv(L["i_wk"], ws["lat"], ws["kraw"], n, cfg.index_head_dim, hd)
+                self.K.call("fb_d4_index_k_store", ws["kraw"], cfg.index_head_dim, ws["flag"], rs.meta, L["i_knorm"], freqs,
+                            self.kidx[layer], ccap, n, cfg.index_head_dim, rd, r, float(cfg.norm_eps))
+                self.K.call("fb_d4_latent_store", ws["lat"], ws["flag"], rs.meta, freqs, self.comp[layer], ccap, n, hd, rd, r)
+            if "i_wq_b" in L:
+                ID = cfg.index_head_dim
+                self.gemv(L["i_wq_b"], qr, ws["iq"], n, self.IHl * ID, ql)
+                self.K.call("fb_d4_rope_heads", ws["iq"], self.IHl * ID, n, self.IHl, ID, rd, freqs, rs.meta, 0, 0, 1,
+                            None, 0, 0, 0)
+                self.gemv(L["i_wproj"], x, ws["iw"], n, self.IHl, d, ldo=ws["iw"].shape[1])
+                lds = ws["score"].shape[1]
+                self.K.call("fb_d4_index_score", ws["iq"], self.IHl * ID, ws["iw"], ws["iw"].shape[1], self.kidx[src], ccap,
+                            rs.meta, ws["score"], lds, n, self.IHl, ID, r, float(ID ** -0.5 * cfg.index_n_heads ** -0.5))
+                self._reduce(ws["score"], n)
+                mask, ldm = None, 0
+                if layer == cfg.candidate_source_layer:
+                    bs = cfg.candidate_block_size
+                    ldb = ws["bscore"].shape[1]
+                    kb = ws["bidx"].shape[1]
+                    self.K.call("fb_d4_block_max", ws["score"], lds, rs.meta, r, bs, ws["bscore"], ldb, n)
+                    self.K.call("fb_d4_topk_sorted", ws["bscore"], ldb, None, 0, rs.meta, r, bs, kb, ws["bidx"], kb, n)
+                    self.K.call("fb_d4_cand_mask", ws["bidx"], kb, kb, bs, ws["cand"], ws["cand"].shape[1], n)
+                elif cfg.uses_candidates(layer):
+                    mask, ldm = ws["cand"], ws["cand"].shape[1]
+                self.K.call("fb_d4_topk_sorted", ws["score"], lds, mask, ldm, rs.meta, r, 1, cfg.index_topk, ws["topk"],
+                            cfg.index_topk, n)
+            comp, idx, ktop = self.comp[src], ws["topk"], cfg.index_topk
+        o = ws["o"]
+        self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
+                    cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
+                    self.Hl, hd, o.f, self.Hl * hd, n, *o.sp(1))
+        low = ws["low"]
+        R_ = cfg.o_lora_rank
+        self.gemv(L["wo_a"], o, low, n, self.Gl * R_, cfg.heads_per_group * hd, ldx=self.Hl * hd, group_rows=R_)
+        self._quant(low.f, low, n, self.Gl * R_)
+        self.gemv(L["wo_b"], low, ws["y"], n, d, self.Gl * R_)
+        self._reduce(ws["y"], n)
+
+    def _moe(self, L, n):
+        cfg, ws = self.cfg, self.ws
+        d, x, xq = cfg.dim, ws["x"], ws["xq"]
+        E, topk = L["E"], L["topk"]
+        ldl = ws["rlogit"].shape[1]
+        self.gemv(L["gate_w"], x, ws["rlogit"], n, E, d, ldo=ldl)
+        self.K.call("fb_d4_route", ws["rlogit"], ldl, L["gate_b"], L["gate_bvl"], ws["is_image"] if L["gate_bvl"] is not None else None,
+                    n, E, topk, float(cfg.route_scale), ws["ridx"], ws["rw"])
+        self._quant(x.f, xq, n, d)
+        self.K.call("fb_d4_expert_gate_up", xq.f, d, ws["ridx"], ws["rw"], L["w13"], L["s13"], ws["h"], n, topk, self.Il, d,
+                    float(cfg.swiglu_limit))
+        self.K.call("fb_d4_quant_rows", ws["h"], self.Il, ws["h"], self.Il, n * topk, self.Il, None, 0, 0, 0)
+        self.K.call("fb_d4_expert_down", ws["h"], ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
+        if not self.shared_tp:
+            self._reduce(ws["y"], n)
+        hs = ws["hs"]
+        self.gemv(L["sh_w13"], xq, ws["gu"], n, 2 * self.Is, d)
+        self.K.call("fb_d4_swiglu_clamp", ws["gu"], 2 * self.Is, hs.f, self.Is, n, self.Is, float(cfg.swiglu_limit))
+        self._quant(hs.f, hs, n, self.Is)
+        self.gemv(L["sh_w2"], hs, ws["y"], n, d, self.Is, accumulate=True)
+        if self.shared_tp:
+            self._reduce(ws["y"], n)
+
+    def _engram(self, L, rs, n):
+        cfg, ws = self.cfg, self.ws
+        lay = self.layout
+        g = ws["egat"]
+        cols, ehd = lay.hash_cols, cfg.engram_head_dim
+        self.K.call("fb_d4_engram_gather", ws["ehash"], len(lay.layer_ids), L["e_idx"], cols, L["e_table"], L["e_scale"],
+                    L["e_lo"], L["e_hi"], ehd, g.f, n)
+        self._reduce(g.f, n)
+        self._quant(g.f, g, n, cols * ehd)
+        self.gemv(L["e_wkv"], g, ws["ekv"], n, (cfg.hc_mult + 1) * cfg.dim, cols * ehd)
+        self.K.call("fb_d4_engram_apply", ws["R"], ws["ekv"], L["e_qk"], ws["is_image"] if self.has_images else None, n,
+                    cfg.hc_mult, cfg.dim, float(cfg.norm_eps))
+
+    has_images = False
+    debug = None   # callable(name, tensor) for op-by-op comparison against the golden model's trace
+
+    def _dbg(self, name, t):
+        if self.debug is not None:
+            self.debug(name, t)
+
+    def forward(self, rs: RowSet, ids: torch.Tensor, advance: bool = True, want_logits: bool = True):
+        """Run rs.n rows; ids [n] int32 on the device.  Leaves logits in ws['logits'], greedy ids in
+        ws['out_ids'] and the DSpark target hiddens in ws['mh']."""
+        cfg, ws, n = self.cfg, self.ws, rs.n
+        d = cfg.dim
+        self.K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.seq_len, rs.meta, n)
+        ws["R"] = ws["R0"]
+        self.K.call("fb_embed_expand", ids, self.embed, ws["R"], n, d, cfg.hc_mult, cfg.vocab_size)
+        ws["pre0"].zero_()
+        ws["pre0"][:, 0] = 1.0
+        ws["pre_cur"], ws["pre_nxt"] = ws["pre0"], ws["pre1"]
+        if self.layout is not None:
+            lay = self.layout
+            self.K.call("fb_d4_engram_hash", ids, ws["is_image"] if self.has_images else None, rs.meta, self.e_map,
+                        self.e_hist, self.max_ctx, self.e_mult, self.e_primes, self.e_offs, self.e_pad, n,
+                        len(lay.layer_ids), lay.max_ngram, lay.n_heads, ws["ehash"])
+        shared: dict = {}
+        tgt = list(cfg.dspark_target_layer_ids)
+        pending_mix = True   # the mix dots of the first site are not computed yet
+        for l, L in enumerate(self.layers):
+            if "e_idx" in L:
+                self._engram(L, rs, n)
+                pending_mix = True
+            if l in tgt:
+                self.K.call("fb_d4_copy_mean", ws["R"], ws["mh"], ws["mh"].shape[1], tgt.index(l) * d, n, cfg.hc_mult, d)
+            if pending_mix:
+                ws["hc_acc"].zero_()
+                self._hc_post_mix(L["hc_attn_fn"], n, first=True)
+                pending_mix = False
+            self._hc_pre(L, "attn", L["attn_norm"], n)
+            self._dbg(f"layers.{l}.attn_in", ws["x"].f[:n])
+            self._attention(L, rs, shared, self.ring[l])
+            self._dbg(f"layers.{l}.attn_o", ws["o"].f[:n])
+            if L["ratio"] > 0:
+                self._dbg(f"layers.{l}.topk", ws["topk"][:n])
+            self._dbg(f"layers.{l}.attn_out", ws["y"][:n])
+            self._hc_post_mix(L["hc_ffn_fn"], n)
+            self._hc_pre(L, "ffn", L["ffn_norm"], n)
+            self._moe(L, n)
+            self._dbg(f"layers.{l}.route_idx", ws["ridx"][:n, :L["topk"]])
+            self._dbg(f"layers.{l}.ffn_out", ws["y"][:n])
+            nxt = self.layers[l + 1] if l + 1 < len(self.layers) else None
+            if nxt is not None and "e_idx" not in nxt:
+                self._hc_post_mix(nxt["hc_attn_fn"], n)
+            else:
+                self._hc_post_mix(None, n)
+                pending_mix = True
+            self._dbg(f"layers.{l}.h", ws["R"][:n])
+        self._hc_pre({}, "", self.norm_w, n, coeffs=False)
+        if want_logits:
+            self.gemv(self.head, ws["x"], ws["logits"], n, cfg.vocab_size, d)
+            self.K.call("fb_argmax", ws["logits"], cfg.vocab_size, ws["amax_part"], ws["out_ids"], None, n, cfg.vocab_size, 1, 0)
+        if advance:
+            self.K.call("fb_advance_rows", rs.meta, None, self.seq_len, n)

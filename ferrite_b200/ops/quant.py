@@ -18,6 +18,9 @@ import torch
 E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 FP8_MAX = 448.0
 FP4_MAX = 6.0
+# the scale of a block is computed as amax * (1/max) in f32, like the reference kernels do
+_INV448 = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(448.0, dtype=torch.float32))
+_INV6 = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(6.0, dtype=torch.float32))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -87,7 +90,7 @@ def fp8_act_roundtrip(x: torch.Tensor, block: int = 32) -> torch.Tensor:
     sh = x.shape
     v = x.float().reshape(-1, sh[-1] // block, block)
     amax = v.abs().amax(-1, keepdim=True).clamp_min(1e-4)
-    s = pow2_ceil(amax / FP8_MAX)
+    s = pow2_ceil(amax * _INV448)
     return (e4m3_round(v / s) * s).reshape(sh)
 
 
@@ -96,7 +99,7 @@ def fp8_act_quant(x: torch.Tensor, block: int = 32):
     sh = x.shape
     v = x.float().reshape(-1, sh[-1] // block, block)
     amax = v.abs().amax(-1, keepdim=True).clamp_min(1e-4)
-    s = pow2_ceil(amax / FP8_MAX)
+    s = pow2_ceil(amax * _INV448)
     return e4m3_round(v / s).reshape(sh), ue8m0_encode(s.squeeze(-1)).reshape(*sh[:-1], sh[-1] // block)
 
 
@@ -108,7 +111,7 @@ def fp4_act_roundtrip(x: torch.Tensor, block: int = 32, scale: str = "ue8m0") ->
     if scale == "e4m3":
         s = e4m3_round(amax.clamp_min(6 * 2.0 ** -9) / FP4_MAX)
     else:
-        s = pow2_ceil(amax.clamp_min(6 * 2.0 ** -126) / FP4_MAX)
+        s = pow2_ceil(amax.clamp_min(6 * 2.0 ** -126) * _INV6)
     return (e2m1_decode(e2m1_encode(v / s)) * s).reshape(sh)
 
 
@@ -120,7 +123,7 @@ def quant_fp4_weight(w: torch.Tensor, block: int = 32):
     N, K = w.shape
     v = w.float().reshape(N, K // block, block)
     amax = v.abs().amax(-1, keepdim=True).clamp_min(6 * 2.0 ** -126)
-    s = pow2_ceil(amax / FP4_MAX)
+    s = pow2_ceil(amax * _INV6)
     code = e2m1_encode(v / s).reshape(N, K)
     return e2m1_pack(code), ue8m0_encode(s.squeeze(-1))
 
@@ -139,7 +142,7 @@ def quant_fp8_weight(w: torch.Tensor, block: int = 32):
     pad[:N, :K] = w.float()
     v = pad.reshape(nb, block, kb, block)
     amax = v.abs().amax(dim=(1, 3), keepdim=True).clamp_min(1e-4)
-    s = pow2_ceil(amax / FP8_MAX)
+    s = pow2_ceil(amax * _INV448)
     q = (v / s).clamp(-FP8_MAX, FP8_MAX).reshape(nb * block, kb * block)[:N, :K].to(torch.float8_e4m3fn)
     return q, ue8m0_encode(s.reshape(nb, kb))
 
