@@ -168,6 +168,17 @@ class Dsv41DeviceModel:
                 L["e_wkv"] = self._bf(src.get(p + "engram.wkv.weight"))
                 L["e_qk"] = self._f(src.get(p + "engram.q_weight").float() * src.get(p + "engram.k_weight").float())
             self.layers.append(L)
+        self.mtp: List[dict] = []
+        if cfg.dspark_block_size and cfg.n_mtp_layers and src.has("mtp.0.main_proj.weight"):
+            for j in range(cfg.n_mtp_layers):
+                self.mtp.append(self._pack_block(src, f"mtp.{j}.", cfg.n_layers + j))
+            last = f"mtp.{cfg.n_mtp_layers - 1}."
+            self.d_main_proj = self._bf(src.get("mtp.0.main_proj.weight"))
+            self.d_main_norm = self._f(src.get("mtp.0.main_norm.weight"))
+            self.d_norm = self._f(src.get(last + "norm.weight"))
+            self.d_membed = self._bf(src.get(last + "markov_head.embed.weight"))
+            self.d_mhead = self._bf(src.get(last + "markov_head.head.weight"))
+            self.d_conf = self._f(src.get(last + "confidence_head.proj.weight"))
         self.freq_win = self._f(rope_freqs(cfg.rope_head_dim, cfg.rope_theta, 0, 1.0, cfg.beta_fast, cfg.beta_slow))
         self.freq_cmp = self._f(rope_freqs(cfg.rope_head_dim, cfg.compress_rope_theta, cfg.original_seq_len,
                                            cfg.rope_factor, cfg.beta_fast, cfg.beta_slow))
@@ -234,6 +245,17 @@ class Dsv41DeviceModel:
             ws["egat"] = Act(self.dev, M, cols * cfg.engram_head_dim)
             ws["ekv"] = self._z(M, (cfg.hc_mult + 1) * d)
             self.e_hist = torch.full((S, self.max_ctx), -1, dtype=torch.int32, device=self.dev)
+        if self.mtp:
+            B, rk = cfg.dspark_block_size, cfg.dspark_markov_rank
+            ws["mhq"] = Act(self.dev, M, ws["mh"].shape[1])
+            ws["mx"] = Act(self.dev, M, d)
+            ws["mkv"] = self._z(M, hd)
+            ws["d_extra"] = self._z(M, hd)
+            ws["d_ids"] = self._z(B, dtype=torch.int32)
+            ws["d_out"] = self._z(B + 1, dtype=torch.int32)
+            ws["d_me"] = Act(self.dev, 1, rk)
+            ws["d_me_all"] = self._z(B, rk)
+            ws["d_xc"] = self._z(M, d)
         self.ws = ws
         # per-slot caches
         nl = cfg.n_total_layers
@@ -453,3 +475,74 @@ class Dsv41DeviceModel:
             self.K.call("fb_argmax", ws["logits"], cfg.vocab_size, ws["amax_part"], ws["out_ids"], None, n, cfg.vocab_size, 1, 0)
         if advance:
             self.K.call("fb_advance_rows", rs.meta, None, self.seq_len, n)
+
+    # ---- DSpark (block draft over the main model's KV) ---------------------------------------------
+    def dspark_seed(self, rs: RowSet, row0: int = 0, n: Optional[int] = None):
+        """Write the main-model KV of rows row0..row0+n-1 of the last forward (their target-layer
+        hiddens are in ws['mh']) into every DSpark layer's ring at those rows' positions.  `rs`
+        must be the row set of that forward, with its metadata still valid."""
+        cfg, ws = self.cfg, self.ws
+        n = rs.n if n is None else n
+        d, hd = cfg.dim, cfg.head_dim
+        km = ws["mh"].shape[1]
+        mh = ws["mh"][row0:]
+        mhq, mx = ws["mhq"], ws["mx"]
+        meta = View(rs.meta, row0 * ROWMETA_BYTES)
+        self.K.call("fb_d4_quant_rows", mh, km, mhq.f, km, n, km, *mhq.sp(1))
+        self.gemv(self.d_main_proj, mhq, mx, n, d, km)
+        self.K.call("fb_rmsnorm", mx.f, None, None, self.d_main_norm, mx.f, n, d, d, d, float(cfg.norm_eps), None, 0, 0, 0)
+        self._quant(mx.f, mx, n, d)
+        for j, L in enumerate(self.mtp):
+            # only the wkv rows of the fused [wq_a ; wkv] matrix
+            wkv = View(L["w_qkv_a"], cfg.q_lora_rank * d)
+            self.gemv(wkv, mx, ws["mkv"], n, hd, d)
+            self.K.call("fb_d4_kv_append", ws["mkv"], hd, L["kv_norm"], self.freq_win, meta, self.ring[cfg.n_layers + j],
+                        self.win_cap, None, n, hd, cfg.rope_head_dim, float(cfg.norm_eps), 0)
+
+    def dspark_draft(self, rs_block: RowSet, t0: torch.Tensor):
+        """Draft block after the committed sequence (seq_len rows, main KV seeded).  `t0` is a device
+        int32 tensor [1] holding the last emitted token.  Leaves [t0, d1..dB] in ws['d_out'] and the
+        block logits in ws['logits'][:B]."""
+        cfg, ws = self.cfg, self.ws
+        B, d = cfg.dspark_block_size, cfg.dim
+        assert rs_block.n == B
+        ids = ws["d_ids"]
+        ids.fill_(cfg.dspark_noise_token_id)
+        ids[0:1].copy_(t0)
+        self.K.call("fb_prep_rows", rs_block.row_slot, rs_block.row_off, rs_block.row_gsize, self.seq_len, rs_block.meta, B)
+        ws["R"] = ws["R0"]
+        self.K.call("fb_embed_expand", ids, self.embed, ws["R"], B, d, cfg.hc_mult, cfg.vocab_size)
+        ws["pre0"].zero_()
+        ws["pre0"][:, 0] = 1.0
+        ws["pre_cur"], ws["pre_nxt"] = ws["pre0"], ws["pre1"]
+        ws["hc_acc"].zero_()
+        for j, L in enumerate(self.mtp):
+            if j == 0:
+                self._hc_post_mix(L["hc_attn_fn"], B, first=True)
+            self._hc_pre(L, "attn", L["attn_norm"], B)
+            self._attention(L, rs_block, {}, self.ring[cfg.n_layers + j], extra=ws["d_extra"], n_extra=B, win_mode=1)
+            self._hc_post_mix(L["hc_ffn_fn"], B)
+            self._hc_pre(L, "ffn", L["ffn_norm"], B)
+            self._moe(L, B)
+            nxt = self.mtp[j + 1] if j + 1 < len(self.mtp) else None
+            self._hc_post_mix(nxt["hc_attn_fn"] if nxt else None, B)
+        x = ws["x"]
+        self.K.call("fb_d4_hc_pre", ws["R"], None, None, None, self.d_norm, ws["pre_cur"], ws["pre_nxt"], ws["post"],
+                    ws["comb"], x.f, ws["d_xc"], B, d, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
+                    cfg.hc_sinkhorn_iters, *x.sp(1))
+        V, rk = cfg.vocab_size, cfg.dspark_markov_rank
+        self.gemv(self.head, x, ws["logits"], B, V, d)
+        out, me = ws["d_out"], ws["d_me"]
+        out[0:1].copy_(t0)
+        for i in range(B):
+            self.K.call("fb_d4_gather_row", self.d_membed, View(out, i), rk, V, me.f, *me.sp(1))
+            ws["d_me_all"][i].copy_(me.f[0])
+            self.gemv(self.d_mhead, me, View(ws["logits"], i * V), 1, V, rk, accumulate=True)
+            self.K.call("fb_argmax", View(ws["logits"], i * V), V, ws["amax_part"], View(out, i + 1), None, 1, V, 1, 0)
+        return out
+
+    def dspark_confidence(self) -> torch.Tensor:
+        """Confidence scores of the last draft block, [B] (proj over [collapsed hidden | markov embed])."""
+        B, d = self.cfg.dspark_block_size, self.cfg.dim
+        w = self.d_conf[0]
+        return self.ws["d_xc"][:B] @ w[:d] + self.ws["d_me_all"] @ w[d:]

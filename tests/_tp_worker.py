@@ -74,6 +74,30 @@ def main():
             same = sum(a == b for a, b in zip(single, outs[1]))
             assert same >= 10, (name, single, outs[1])
             print(f"{name}: tp{world} tokens {outs[1]} (tp1 agreement {same}/14)")
+    # 3. DSV41: tensor-parallel engine (heads / groups / expert-inter / engram rows split) == single rank
+    from ferrite_b200.engine.dsv41_engine import Dsv41Engine
+    from ferrite_b200.models.dsv41 import DictWeights
+    from ferrite_b200.models.dsv41_config import Dsv41Config
+    from ferrite_b200.models.dsv41_weights import random_weights as d4_weights
+    if world == 2:
+        cfg = Dsv41Config.tiny()
+        w = d4_weights(cfg, 2)
+        prompt = [3, 17, 99, 250, 4, 8, 15, 16, 23, 42, 77]
+        outs = {}
+        for spec in (False, True):
+            eng = Dsv41Engine(cfg, DictWeights(w), rank=rank, world=world, device=dev, allreduce=ar, max_ctx=128)
+            outs[spec] = eng.generate(prompt, 12, spec=spec)
+            ar.check()
+        assert outs[False] == outs[True], outs
+        t = torch.tensor(outs[False], device=dev)
+        t0 = t.clone()
+        dist.broadcast(t0, 0)
+        assert torch.equal(t, t0), "DSV41 ranks emitted different tokens"
+        if rank == 0:
+            single = Dsv41Engine(cfg, DictWeights(w), device=dev, max_ctx=128).generate(prompt, 12)
+            same = sum(a == b for a, b in zip(single, outs[False]))
+            assert same >= 9, (single, outs)
+            print(f"dsv41 tiny: tp{world} tokens {outs[False]} (tp1 agreement {same}/12)")
     dist.barrier()
     ar.close()
     dist.destroy_process_group()

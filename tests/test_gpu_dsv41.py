@@ -98,3 +98,48 @@ def test_device_forward_matches_golden():
     err = (got - want).abs().max().item()
     assert not report and err < 5e-2 * max(1.0, want.abs().max().item()), (report[:12], err)
     assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.9
+
+
+def test_engine_plain_and_spec_generation():
+    from ferrite_b200.engine.dsv41_engine import Dsv41Engine
+    from ferrite_b200.models.dsv41 import DictWeights
+    cfg, w, ref = _pair(seed=2)
+    prompt = [3, 17, 99, 250, 4, 8, 15, 16, 23, 42, 77]
+    n_new = 14
+    want = ref.generate(prompt, n_new)
+    outs = {}
+    for graphs in (False, True):
+        eng = Dsv41Engine(cfg, DictWeights(w), max_ctx=128, use_graphs=graphs)
+        outs[("plain", graphs)] = eng.generate(prompt, n_new)
+        eng2 = Dsv41Engine(cfg, DictWeights(w), max_ctx=128, use_graphs=graphs)
+        outs[("spec", graphs)] = eng2.generate(prompt, n_new, spec=True)
+        assert all(1 <= k <= cfg.dspark_block_size + 1 for k in eng2.accept_hist)
+    torch.cuda.synchronize()
+    same = sum(a == b for a, b in zip(want, outs[("plain", False)]))
+    assert same >= n_new - 3, (want, outs)          # a flipped e4m3 rounding may move a late argmax
+    assert outs[("plain", True)] == outs[("plain", False)], outs
+    assert outs[("spec", False)] == outs[("plain", False)], outs
+    assert outs[("spec", True)] == outs[("plain", False)], outs
+
+
+def test_draft_block_matches_golden():
+    from ferrite_b200.models.dsv41 import DictWeights, Dsv41DeviceModel
+    cfg, w, ref = _pair(seed=4)
+    prompt = [5, 9, 200, 7, 7, 3, 88, 140, 31]
+    st = ref.new_seq()
+    logits, mh = ref.forward(st, prompt)
+    ref.dspark_seed(st, mh, 0)
+    t0 = int(logits[-1].argmax())
+    drafts, dl, conf = ref.dspark_draft(st, t0, len(prompt) - 1)
+    dev = Dsv41DeviceModel(cfg, DictWeights(w), max_rows=8, max_ctx=128)
+    for i in range(0, len(prompt), 8):
+        c = prompt[i:i + 8]
+        rs = dev.make_rows([0], [len(c)])
+        dev.forward(rs, torch.tensor(c, dtype=torch.int32, device="cuda"))
+        dev.dspark_seed(rs)
+    B = cfg.dspark_block_size
+    out = dev.dspark_draft(dev.make_rows([0], [B]), torch.tensor([t0], dtype=torch.int32, device="cuda"))
+    got = dev.ws["logits"][:B].cpu()
+    assert (got - dl).abs().max().item() < 5e-2 * max(1.0, dl.abs().max().item())
+    assert out.tolist()[0] == t0 and sum(a == b for a, b in zip(out.tolist()[1:], drafts)) >= B - 1
+    assert (dev.dspark_confidence().cpu() - conf).abs().max().item() < 5e-2 * max(1.0, conf.abs().max().item())
