@@ -86,6 +86,40 @@ def make_cases(K, only):
                     K.call("fb_gemv_bf16", w, x, Kd, out, N, m, N, Kd, 0, 0)
         cases.append(Case(name, N * Kd * esz, fn, f"N={N} K={Kd} m={m}"))
 
+    def fused_case(name, N, Kd, m, fold, fp8=False):
+        """GEMV + (world 1: no collective) + hyper-connection fold in one launch."""
+        if not want(name):
+            return
+        from ferrite_b200.parallel.symm import FusedGemvAllReduce
+        esz = 1 if fp8 else 2
+        reps = max(2, int(300e6 // (N * Kd * esz)) + 1)
+        x = torch.randn(m, Kd, device=dev)
+        xs = split_buf(x)
+        out = torch.zeros(m, N, device=dev)
+        if fp8:
+            ws = [fp8_rand(N, Kd) for _ in range(reps)]
+            sc = torch.rand((N + 127) // 128, (Kd + 127) // 128, device=dev) * 1e-3
+        else:
+            ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) for _ in range(reps)]
+            sc = None
+        R0, R1 = torch.randn(8, 4, N, device=dev), torch.zeros(8, 4, N, device=dev)
+        fns = [torch.randn(24, 4 * N, device=dev) * 0.02 for _ in range(40)]
+        acc = torch.zeros(8, 25, device=dev)
+        post, comb = torch.rand(8, 4, device=dev), torch.rand(8, 16, device=dev)
+        f = FusedGemvAllReduce(torch.device(dev), 0, 1)
+        state = {"i": 0}
+
+        def fn():
+            i = state["i"]
+            state["i"] += 1
+            fd = (R0, R1, post, comb, fns[i % 40], acc, 24) if fold else None
+            f(ws[i % reps], sc, xs, Kd, m * Kd, out, N, m, N, Kd, False, True, fd)
+        cases.append(Case(name, N * Kd * esz + (24 * 4 * N * 4 if fold else 0), fn, f"N={N} K={Kd} m={m} fold={fold}"))
+
+    fused_case("gemv_ar.gdn_o_proj.m3.nofold", 4096, 8192, 3, False)
+    fused_case("gemv_ar.gdn_o_proj.m3.fold", 4096, 8192, 3, True)
+    fused_case("gemv_ar.shared_down.m3.fold", 4096, 2048, 3, True)
+    fused_case("gemv_ar.dense_down.m3.fold", 4096, 12288, 3, True, fp8=True)
     gemv_case("gemv_mma_bf16.lm_head.m1", 154880, 4096, 1)
     gemv_case("gemv_mma_bf16.lm_head.m3", 154880, 4096, 3)
     gemv_case("gemv_simt_bf16.lm_head.m3", 154880, 4096, 3, mma=False)
@@ -174,7 +208,7 @@ def make_cases(K, only):
             K.call("fb_hc_post_mix", R0, R1, y, post, comb, f, acc, n, H, mix)
 
         def pa():
-            K.call("fb_hc_pre_apply", R1, acc, scale, base, ln, None, xn, post, comb, n, H, 4, 1e-5, 1e-6, 20, sp, H, n * H, 3)
+            K.call("fb_hc_pre_apply", R1, acc, scale, base, ln, None, xn, post, comb, n, H, 4, 1e-5, 1e-6, 20, sp, H, n * H, 3, None, None, 0)
         cases.append(Case("hc_post_mix.m3", mix * 4 * H * 4 + 2 * n * 4 * H * 4, pm, "fn 1.5 MB f32"))
         cases.append(Case("hc_pre_apply.m3", n * 4 * H * 4, pa, "latency-bound"))
     return cases

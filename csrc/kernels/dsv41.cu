@@ -77,7 +77,7 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
                      const float* __restrict__ base, const float* __restrict__ ln_w, const float* __restrict__ pre_in,
                      float* __restrict__ pre_out, float* __restrict__ post_out, float* __restrict__ comb_out,
                      float* __restrict__ xn_out, float* __restrict__ xc_out, int H, float rms_eps, float hc_eps, int iters,
-                     SplitBuf osp) {
+                     SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld) {
     PDL_PROLOGUE();
     extern __shared__ float sh[];
     float* red = sh;       // 32
@@ -85,6 +85,22 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
     const int n = 4;
     const int r = blockIdx.x;
     const float* row = R + (size_t)r * n * H;
+    if (acc && part_n) {
+        // per-tile partial mix dots left by a fused GEMV epilogue: one warp per dot sums the tiles
+        const int nt = part_n[r];
+        if (nt > 0) {
+            const int lane = threadIdx.x & 31;
+            for (int o = threadIdx.x >> 5; o <= kMaxMixD4; o += blockDim.x >> 5) {
+                const float* pp = part + ((size_t)r * (kMaxMixD4 + 1) + o) * part_ld;
+                float sum = 0.f;
+                for (int i = lane; i < nt; i += 32) sum += pp[i];
+                sum = warp_sum(sum);
+                if (lane == 0) acc[(size_t)r * (kMaxMixD4 + 1) + o] += sum;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) part_n[r] = 0;
+        }
+    }
     if (acc && threadIdx.x < 32) {
         float* a = acc + (size_t)r * (kMaxMixD4 + 1);
         const int lane = threadIdx.x;
@@ -988,12 +1004,14 @@ FB_API int fb_d4_quant_rows(const float* x, int64_t ldx, float* xq, int64_t ldq,
 FB_API int fb_d4_hc_pre(const float* R, float* acc, const float* scale, const float* base, const float* ln_w,
                         const float* pre_in, float* pre_out, float* post_out, float* comb_out, float* xn_out,
                         float* xc_out, int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
-                        void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
-    if (mult != 4) return (int)cudaErrorInvalidValue;
+                        void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, const float* part, int* part_n,
+                        int64_t part_ld, cudaStream_t st) {
+    if (mult != 4 || (part_n && n > 8)) return (int)cudaErrorInvalidValue;
     const size_t sm = (32 + H) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(hc_pre_offset_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     FB_LAUNCH((hc_pre_offset_kernel), n, 512, sm, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,
-              xn_out, xc_out, (int)H, rms_eps, hc_eps, (int)iters, mk_split(s_base, s_ld, s_plane, s_mask));
+              xn_out, xc_out, (int)H, rms_eps, hc_eps, (int)iters, mk_split(s_base, s_ld, s_plane, s_mask), part, part_n,
+              (int)part_ld);
     return FB_LAUNCH_CHECK();
 }
 

@@ -205,11 +205,27 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
                     const float* __restrict__ base, const float* __restrict__ ln_w,
                     float* __restrict__ x_out, float* __restrict__ xn_out, float* __restrict__ post_out,
                     float* __restrict__ comb_out, int H, int n, float rms_eps, float hc_eps, int iters,
-                    SplitBuf osp) {
+                    SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld) {
     PDL_PROLOGUE();
     __shared__ float red[32];
     __shared__ float pre[8];
     const int r = blockIdx.x;
+    if (part_n) {
+        // per-tile partial mix dots left by a fused GEMV epilogue: one warp per dot sums the tiles
+        const int nt = part_n[r];
+        if (nt > 0) {
+            const int lane = threadIdx.x & 31;
+            for (int o = threadIdx.x >> 5; o <= kMaxMix; o += blockDim.x >> 5) {
+                const float* pp = part + ((size_t)r * (kMaxMix + 1) + o) * part_ld;
+                float sum = 0.f;
+                for (int i = lane; i < nt; i += 32) sum += pp[i];
+                sum = warp_sum(sum);
+                if (lane == 0) acc[(size_t)r * (kMaxMix + 1) + o] += sum;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) part_n[r] = 0;
+        }
+    }
     const float* row = R + (size_t)r * n * H;
     const int j = threadIdx.x * 4;
     const bool act = j < H;
@@ -361,12 +377,12 @@ FB_API int fb_hc_mix(const float* R, const float* fn, float* acc, int64_t n, int
 FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const float* base,
                            const float* ln_w, float* x_out, float* xn_out, float* post_out, float* comb_out,
                            int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
-                           cudaStream_t st) {
+                           const float* part, int* part_n, int64_t part_ld, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    if (mult != 4 || (H % 4) || H / 4 > 1024) return (int)cudaErrorInvalidValue;
+    if (mult != 4 || (H % 4) || H / 4 > 1024 || (part_n && n > 8)) return (int)cudaErrorInvalidValue;
     const int threads = (int)(((H / 4) + 31) / 32 * 32);
     FB_LAUNCH((hc_pre_apply_kernel), n, threads, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
-                                               (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp);
+                                               (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp, part, part_n, (int)part_ld);
     return FB_LAUNCH_CHECK();
 }
 

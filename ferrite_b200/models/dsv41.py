@@ -307,7 +307,7 @@ class Dsv41DeviceModel:
         self.K.call("fb_d4_hc_pre", ws["R"], ws["hc_acc"] if coeffs else None,
                     L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
                     ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
-                    cfg.hc_sinkhorn_iters, *x.sp(1))
+                    cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0)
         if coeffs:
             ws["pre_cur"], ws["pre_nxt"] = pout, pin
 
@@ -529,7 +529,7 @@ class Dsv41DeviceModel:
         x = ws["x"]
         self.K.call("fb_d4_hc_pre", ws["R"], None, None, None, self.d_norm, ws["pre_cur"], ws["pre_nxt"], ws["post"],
                     ws["comb"], x.f, ws["d_xc"], B, d, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
-                    cfg.hc_sinkhorn_iters, *x.sp(1))
+                    cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0)
         V, rk = cfg.vocab_size, cfg.dspark_markov_rank
         self.gemv(self.head, x, ws["logits"], B, V, d)
         out, me = ws["d_out"], ws["d_me"]

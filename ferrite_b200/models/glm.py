@@ -90,6 +90,16 @@ class GlmDeviceModel:
         self.dev = torch.device(device)
         self.K = _lib.lib()
         self.allreduce = allreduce  # callable(tensor_view[n,H]) summing across ranks, in place
+        # GEMV + all-reduce + hyper-connection fold as one launch (None: separate kernels)
+        self.fused = None
+        if getattr(ecfg, "fuse_epilogue", True):
+            if world > 1:
+                self.fused = getattr(allreduce, "fused", None)
+            else:
+                from ..parallel.symm import FusedGemvAllReduce
+                self.fused = FusedGemvAllReduce(self.dev, 0, 1)
+        self._fold_next = None   # (fn_next,) while a hyper-connection site's sublayer runs
+        self._folded = False
         self.max_rows = max_rows
         self.n_slots = n_slots
         self.num_pages_arg = num_pages
@@ -393,6 +403,34 @@ class GlmDeviceModel:
         if self.world > 1:
             self.allreduce(y[:n])
 
+    def _out_gemv(self, w, x, n, N, K, ldx=None, scales=None, accumulate=False):
+        """The GEMV that ends a sublayer: ws['y'] = x . w^T (+ ws['y']) summed over the ranks.  When
+        the fused kernel applies, the all-reduce and (inside a hyper-connection site) hc_post plus
+        the next site's mix dots ride in the same launch; otherwise GEMV and all-reduce run
+        separately and the caller's _hc_post_mix does the fold."""
+        ws = self.ws
+        fold, self._fold_next = self._fold_next, None
+        xa = x if isinstance(x, Act) else None
+        ldx = ldx if ldx is not None else (xa.ld if xa else K)
+        kb = 128 if scales is not None else 64
+        ok = (self.fused is not None and xa is not None and xa.s is not None and n <= 8 and K % kb == 0
+              and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or n * N <= self.fused.max_elems)
+              and (self.world > 1 or fold is not None))
+        if not ok:
+            self.gemv(w, x, ws["y"], n, N, K, ldx=ldx, scales=scales, accumulate=accumulate)
+            self._reduce(ws["y"], n)
+            return
+        f = None
+        if fold is not None:
+            cfg = self.cfg
+            rin = ws["R"]
+            rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
+            f = (rin, rout, ws["post"], ws["comb"], fold[0], ws["hc_acc"], cfg.hc_mix)
+            ws["R"] = rout
+            self._folded = True
+        self.fused(w, scales, xa.s, ldx, xa.plane, ws["y"], N, n, N, K, accumulate,
+                   fold is None or self.debug_hook is not None, f)
+
     # ------------------------------------------------------------------ sublayers
     def _attn_linear(self, L, rs: RowSet, snapshots: bool):
         cfg, la, ws, n = self.cfg, self.cfg.linear_attn, self.ws, rs.n
@@ -406,8 +444,7 @@ class GlmDeviceModel:
                     L["a_log"], L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
                     rs.group_first, rs.n_groups, core.f, P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
                     self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps), *core.sp(1))
-        self.gemv(L["o_proj"], core, ws["y"], n, H, P)
-        self._reduce(ws["y"], n)
+        self._out_gemv(L["o_proj"], core, n, H, P)
 
     def _attn_dsa(self, L, rs: RowSet):
         cfg, ds, ws, n = self.cfg, self.cfg.dsa, self.ws, rs.n
@@ -437,8 +474,7 @@ class GlmDeviceModel:
         self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, self.nsplit, 1,
                     *ctx.sp(1))
         self.gemv(L["wv_abs"], ctx, ov, n, hl * dv, DL, group_rows=dv, omask=1)
-        self.gemv(L["o_proj"], ov, ws["y"], n, H, hl * dv)
-        self._reduce(ws["y"], n)
+        self._out_gemv(L["o_proj"], ov, n, H, hl * dv)
 
     def _ffn_dense(self, L, n):
         cfg, ws = self.cfg, self.ws
@@ -448,8 +484,7 @@ class GlmDeviceModel:
         self.gemv(L["d13"], ws["x"], ws["gu"], n, 2 * I, H, ldo=ldg, scales=L.get("d13s"))
         self.K.call("fb_swiglu_split", ws["gu"], ldg, act.f, *act.sp(3, ld=I), n, I, float(cfg.swiglu_limit))
         # fb_swiglu packs rows with stride I in both the f32 and the split form
-        self.gemv(L["d2"], act, ws["y"], n, H, I, ldx=I, scales=L.get("d2s"))
-        self._reduce(ws["y"], n)
+        self._out_gemv(L["d2"], act, n, H, I, ldx=I, scales=L.get("d2s"))
 
     def _ffn_moe(self, L, n):
         cfg, ws = self.cfg, self.ws
@@ -462,20 +497,21 @@ class GlmDeviceModel:
                     float(cfg.routed_scaling_factor))
         self.K.call("fb_swiglu_split", View(ws["moe_lg"], E), ldl, act.f, *act.sp(1, ld=Is), n, Is,
                     float(cfg.swiglu_limit))
-        self.gemv(L["s2"], act, ws["y"], n, H, Is, ldx=Is)
+        # routed experts write y, the shared expert's down projection adds to it and carries the
+        # all-reduce (and the hyper-connection fold) in its epilogue
         if H % 128 == 0 and Il % 128 == 0:
             mas = ws["moe_act_s"]
             ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
             self.K.call("fb_moe_gate_up_mma", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_ids"], ws["moe_wts"],
                         mas, ld_as, plane_as, n, topk, Il, H, 0, self.E_res, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_mma", L["w2"], L["s2s"], mas, ld_as, plane_as, ws["moe_ids"], ws["y"], H, n,
-                        topk, Il, H, 0, self.E_res, 1, None, 0, 0, 0)
+                        topk, Il, H, 0, self.E_res, 0, None, 0, 0, 0)
         else:
             self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], x.f, H, ws["moe_ids"], ws["moe_act"], n, topk,
                         Il, H, 0, self.E_res, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"],
-                        H, n, topk, Il, H, 0, self.E_res, 1)
-        self._reduce(ws["y"], n)
+                        H, n, topk, Il, H, 0, self.E_res, 0)
+        self._out_gemv(L["s2"], act, n, H, Is, ldx=Is, accumulate=True)
 
     def _attn(self, L, rs, snapshots):
         if L["dsa"]:
@@ -495,12 +531,16 @@ class GlmDeviceModel:
         x = ws["x"]
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
                     x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
-                    float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3))
+                    float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3),
+                    *(self.fused.partials() if self.fused is not None and n <= 8 else (None, None, 0)))
 
     def _hc_post_mix(self, fn_next, n, first=False):
         """hc_post of the finished site fused with the mix dots of the next one; the residual
         stream ping-pongs between two buffers because the mix blocks re-read the old one."""
         cfg, ws = self.cfg, self.ws
+        if self._folded:   # the sublayer's last GEMV already did hc_post and the mix dots
+            self._folded = False
+            return
         rin = ws["R"]
         rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
         if first:
@@ -526,13 +566,16 @@ class GlmDeviceModel:
         self._hc_post_mix(main[0]["hc_attn_fn"], n, first=True)
         for li, L in enumerate(main):
             self._hc_pre(L, "attn", L["ln1"], n)
+            self._fold_next = (L["hc_ffn_fn"],)
             self._attn(L, rs, snapshots)
             self._hc_post_mix(L["hc_ffn_fn"], n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "attn", ws, n)
             self._hc_pre(L, "ffn", L["ln2"], n)
+            fn_next = main[li + 1]["hc_attn_fn"] if li + 1 < len(main) else None
+            self._fold_next = (fn_next,)
             self._ffn(L, n)
-            self._hc_post_mix(main[li + 1]["hc_attn_fn"] if li + 1 < len(main) else None, n)
+            self._hc_post_mix(fn_next, n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "ffn", ws, n)
         xh = ws["xh"]

@@ -84,6 +84,7 @@ class P2PAllReduce:
         self._sp = arr(*self.staging.ptrs)
         self._fp = arr(*self.flags.ptrs)
         self.calls = 0
+        self.fused: Optional["FusedGemvAllReduce"] = None   # attached by make_allreduce
 
     def __call__(self, view: torch.Tensor):
         n = view.numel()
@@ -98,7 +99,68 @@ class P2PAllReduce:
         if s[0] == FB_TIMEOUT:
             self.status.zero_()
             raise CollectiveTimeout(s[1], s[2], s[3])
+        if self.fused is not None:
+            self.fused.check()
 
     def close(self):
+        if self.fused is not None:
+            self.fused.close()
         self.staging.close()
         self.flags.close()
+
+
+class FusedGemvAllReduce:
+    """Row-parallel GEMV + all-reduce (+ hyper-connection fold) as one kernel launch
+    (``csrc/kernels/gemv_ar.cu``).  With ``world == 1`` it needs no peer memory and only fuses
+    the fold epilogue into the GEMV.  ``check()`` reads the status word on the host."""
+
+    def __init__(self, device, rank: int, world: int, max_rows: int = 8, n_max: int = 8192,
+                 max_spins: int = 2_000_000, group=None):
+        self.K = _lib.lib()
+        self.rank, self.world, self.max_spins = rank, world, max_spins
+        mt, mw = ctypes.c_int(), ctypes.c_int()
+        self.K.lib.fb_gemv_ar_limits(ctypes.byref(mt), ctypes.byref(mw))
+        assert world <= mw.value
+        self.max_tiles = mt.value
+        self.max_elems = max_rows * n_max
+        self.epoch = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.part = torch.zeros(8 * 25 * self.max_tiles, dtype=torch.float32, device=device)
+        self.part_n = torch.zeros(8, dtype=torch.int32, device=device)
+        self.staging = self.flags = None
+        self._sp = self._fp = None
+        if world > 1:
+            self.staging = SymmetricRegion(2 * world * self.max_elems * 4, rank, world, group)
+            self.flags = SymmetricRegion(2 * world * self.max_tiles * 4, rank, world, group)
+            arr = ctypes.c_void_p * world
+            self._sp = arr(*self.staging.ptrs)
+            self._fp = arr(*self.flags.ptrs)
+        self.calls = 0
+
+    def __call__(self, W, scales, xs_ptr, xs_ld: int, xs_plane: int, y, ldo: int, m: int, N: int, K: int,
+                 accumulate: bool, store_y: bool, fold=None):
+        """fold = (Rin, Rout, post, comb, fn_or_None, acc, mix) or None."""
+        rin = rout = post = comb = fn = acc = None
+        mix = 0
+        if fold is not None:
+            rin, rout, post, comb, fn, acc, mix = fold
+        self.K.call("fb_gemv_ar", W, scales, xs_ptr, xs_ld, xs_plane, y, ldo, m, N, K, int(accumulate), int(store_y),
+                    self._sp, self._fp, self.epoch, self.status, self.rank, self.world, self.max_elems, self.max_spins,
+                    rin, rout, post, comb, fn, acc, mix, self.part, self.part_n)
+        self.calls += 1
+
+    def partials(self):
+        """(part, part_n, part_ld) arguments for the hc_pre kernel that consumes the mix-dot partials."""
+        return (self.part, self.part_n, self.max_tiles)
+
+    def check(self):
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3])
+
+    def close(self):
+        if self.staging is not None:
+            self.staging.close()
+            self.flags.close()
+            self.staging = self.flags = None

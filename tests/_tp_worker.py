@@ -11,7 +11,7 @@ from ferrite_b200.config import EngineConfig, GlmConfig  # noqa: E402
 from ferrite_b200.engine.glm_engine import GlmEngine  # noqa: E402
 from ferrite_b200.models.glm import DictSource  # noqa: E402
 from ferrite_b200.models.glm_weights import random_weights  # noqa: E402
-from ferrite_b200.parallel.symm import P2PAllReduce  # noqa: E402
+from ferrite_b200.parallel.symm import FusedGemvAllReduce, P2PAllReduce  # noqa: E402
 
 
 def main():
@@ -21,6 +21,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     ar = P2PAllReduce(dev, rank, world, max_elems=64 * 4096)
+    ar.fused = FusedGemvAllReduce(dev, rank, world)
     # 1. one-shot all-reduce == NCCL all-reduce, bit-identical across ranks, eager and in a graph
     for n in (4096, 3 * 4096, 16 * 4096 + 8, 64 * 4096):
         g = torch.Generator(device=dev).manual_seed(100 + rank)
@@ -49,6 +50,37 @@ def main():
         torch.cuda.synchronize()
         assert torch.all(buf == total), (it, buf[:4])
     ar.check()
+    # 1b. fused GEMV + all-reduce == GEMV then NCCL all-reduce (eager and replayed in a graph)
+    from ferrite_b200 import _lib
+    from ferrite_b200.models.glm import Act
+    K = _lib.lib()
+    for (N, Kd, m) in ((4096, 4096, 3), (4096, 1024, 8), (5120, 512, 1)):
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        W = (torch.randn(N, Kd, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        x = Act(dev, 8, Kd)
+        x.f.copy_(torch.randn(8, Kd, device=dev, generator=g))
+        K.call("fb_split_rows", x.f, Kd, *x.sp(3), 8, Kd)
+        want = (x.f[:m].double() @ W.double().t()).float()
+        dist.all_reduce(want)
+        y = torch.zeros(8, N, device=dev)
+        ar.fused(W, None, x.s, Kd, x.plane, y, N, m, N, Kd, False, True, None)
+        torch.cuda.synchronize()
+        ar.check()
+        err = (y[:m] - want).abs().max().item()
+        assert err < 2e-2 * max(1.0, want.abs().max().item()), (N, Kd, m, err)
+        ref = y.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(ref, y), "fused all-reduce: ranks disagree bitwise"
+        graph = torch.cuda.CUDAGraph()
+        y2 = torch.zeros(8, N, device=dev)
+        with torch.cuda.graph(graph):
+            ar.fused(W, None, x.s, Kd, x.plane, y2, N, m, N, Kd, False, True, None)
+        for it in range(3):
+            y2.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y2, y), (N, Kd, m, it)
+        ar.check()
     # 2. tensor-parallel engine == single-rank engine, token for token (greedy and MTP)
     for name in ("tiny", "golden4"):
         cfg = getattr(GlmConfig, name)()

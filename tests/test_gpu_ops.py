@@ -130,7 +130,7 @@ def test_hc_chain(K, H):
     sp = torch.zeros(4, n, H, dtype=torch.int16, device="cuda")
     post, comb = torch.zeros(n, 4, device="cuda"), torch.zeros(n, 16, device="cuda")
     K.call("fb_hc_mix", Rd, dev(fn), acc, n, mult * H, mix)
-    K.call("fb_hc_pre_apply", Rd, acc, dev(scale), dev(base), dev(ln), x, xn, post, comb, n, H, mult, 1e-5, 1e-6, 20, sp, H, n * H, 3)
+    K.call("fb_hc_pre_apply", Rd, acc, dev(scale), dev(base), dev(ln), x, xn, post, comb, n, H, mult, 1e-5, 1e-6, 20, sp, H, n * H, 3, None, None, 0)
     check_split("hc xn split", sp, xn, n, H)
     xr, pr, cr = R.hc_pre(Rr, fn, scale, base, 1e-5, 1e-6, 20)
     check("hc x", x, xr, 1e-4)
@@ -526,3 +526,51 @@ def test_gemm_tcgen05_bf16(K, M, N, K_):
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
     check("gemm tc acc", out, 2 * want, 4e-3 * max(1.0, want.abs().max().item()))
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_gemv_ar_fold_single_rank(K, fp8):
+    """Fused GEMV + hyper-connection fold (world = 1: no collective) against the separate ops."""
+    from ferrite_b200.models.glm import Act
+    from ferrite_b200.parallel.symm import FusedGemvAllReduce
+    m, N, Kd, mix = 5, 4096, 1024, 24
+    W = rnd(N, Kd, seed=1, scale=0.05)
+    x = Act(torch.device("cuda"), 8, Kd)
+    x.f.copy_(dev(rnd(8, Kd, seed=2)))
+    K.call("fb_split_rows", x.f, Kd, *x.sp(3), 8, Kd)
+    Rin, y0 = dev(rnd(8, 4, N, seed=3)), dev(rnd(8, N, seed=4))
+    post, comb = dev(rnd(8, 4, seed=5).abs()), dev(rnd(8, 4, 4, seed=6).abs())
+    fn = dev(rnd(mix, 4 * N, seed=7, scale=0.02))
+    if fp8:
+        wq, ws_ = R.quant_fp8_block(W)
+        wdev, sdev, wref = wq.cuda(), ws_.cuda(), R.dequant_fp8_block(wq, ws_)
+    else:
+        wdev, sdev, wref = W.to(torch.bfloat16).cuda(), None, W.to(torch.bfloat16).float()
+    y = y0.clone()
+    Rout = torch.zeros_like(Rin)
+    acc = torch.zeros(8, 25, device="cuda")
+    f = FusedGemvAllReduce(torch.device("cuda"), 0, 1)
+    f(wdev, sdev, x.s, Kd, x.plane, y, N, m, N, Kd, True, True, (Rin, Rout, post, comb, fn, acc, mix))
+    want_y = x.f[:m].cpu() @ wref.t() + y0[:m].cpu()
+    tol = 3e-2 if fp8 else 2e-3
+    check("gemv_ar y", y[:m], want_y, tol * want_y.abs().max().item())
+    want_R = R.hc_post(want_y, Rin[:m].cpu(), post[:m].cpu(), comb[:m].cpu())
+    check("gemv_ar R'", Rout[:m], want_R, tol * want_R.abs().max().item())
+    flat = want_R.reshape(m, -1)
+    part, part_n, ld = f.partials()
+    nt = part_n[:m].cpu().tolist()
+    assert len(set(nt)) == 1 and nt[0] in (N // 16, N // 32) and not part_n[m:].any()
+    sums = part.view(8, 25, ld)[:m, :, :nt[0]].sum(-1)
+    check("gemv_ar mix", sums[:, :mix], flat @ fn.cpu().t(), tol * (flat @ fn.cpu().t()).abs().max().item())
+    check("gemv_ar sumsq", sums[:, 24], flat.pow(2).sum(-1), tol * flat.pow(2).sum(-1).max().item())
+    assert not Rout[m:].any() and not acc.any()
+    # the consumer adds the partials to its accumulator and clears the tile count
+    Rd = Rout[:m].contiguous()
+    xn = torch.zeros(m, N, device="cuda")
+    po, co = torch.zeros(m, 4, device="cuda"), torch.zeros(m, 16, device="cuda")
+    scale, base, ln = torch.ones(3, device="cuda"), torch.zeros(mix, device="cuda"), torch.ones(N, device="cuda")
+    K.call("fb_hc_pre_apply", Rd, acc, scale, base, ln, None, xn, po, co, m, N, 4, 1e-5, 1e-6, 20, None, 0, 0, 0, part, part_n, ld)
+    xr, pr, cr = R.hc_pre(want_R, fn.cpu(), scale.cpu(), base.cpu(), 1e-5, 1e-6, 20)
+    check("gemv_ar -> hc_pre post", po, pr, 5 * tol)
+    check("gemv_ar -> hc_pre comb", co, cr.reshape(m, 16), 5 * tol)
+    assert not part_n.any() and not acc.any()
