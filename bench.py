@@ -92,6 +92,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--fuse", default="full", choices=["full", "ar", "off"],
+                    help="GEMV epilogue fusion: all-reduce + hyper-connection fold, all-reduce only, or separate kernels")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                     help="all-reduce used by the tensor-parallel chain: peer-memory one-shot kernel or NCCL")
     ap.add_argument("--profile", action="store_true",
@@ -125,7 +127,8 @@ def main():
     resident = args.experts_resident or (128 if world == 1 else cfg.n_routed_experts)
     ecfg = EngineConfig(tp=world, max_ctx=args.prompt_len + 3 * (args.steps * 2 + args.warmup * 2 + 16) + 64,
                         mtp_n=1 if args.no_mtp else 3,
-                        experts_resident=None if resident >= cfg.n_routed_experts else resident)
+                        experts_resident=None if resident >= cfg.n_routed_experts else resident,
+                        fuse_epilogue=args.fuse)
     t0 = time.time()
     eng = GlmEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank=rank, world=world, device=dev,
                     allreduce=allreduce, prefill_rows=64)
@@ -200,7 +203,7 @@ def main():
             "impl": "ours",
             "config": {"model": "GLM-5.3-Flash (45 layers: 34 GatedDeltaNet + 11 DSA, 3 dense + 42 MoE, 1 MTP layer)"
                                 if args.layers == 0 else f"DEBUG {args.layers}-layer slice (invalid as a result)",
-                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none",
+                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none", "gemv_epilogue_fusion": args.fuse,
                        "weights": "random-init; bf16, routed experts + dense FFN fp8 e4m3 128x128 block-scaled (W8A16)",
                        "mtp": "draft 2 / verify 3" if mtp else "off",
                        "accept_tokens_per_step": round(tokens / args.steps, 3),

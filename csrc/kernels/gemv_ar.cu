@@ -7,7 +7,8 @@
 // tensor-core GEMV core (mma.sync m16n8k16, software-pipelined weight loads), reduce their
 // partial tiles through shared memory, and then run the collective on that 8-row tile alone:
 //   push    16-byte peer stores of the tile into slot `rank` of every peer's staging buffer,
-//   publish one release store per peer of the tile's epoch stamp,
+//   publish tiles go out in groups (by default one group = the grid): the CTA that completes a group
+//           fences at system scope once and stamps the group's epoch on every peer,
 //   wait    bounded poll of the local flag words of all ranks (peers write them into local
 //           memory, so a poll never crosses NVLink); on expiry the kernel records
 //           {TIMEOUT, peer, epoch, tile}, skips the reduction and still returns,
@@ -28,10 +29,11 @@ namespace {
 constexpr int kMaxWorld = 8;
 constexpr int kMaxTiles = 512;
 constexpr int kMaxMix = 24;
+constexpr int kFlagPad = 32;   // words per flag: pollers of different tiles never share a cache line
 
 struct ArPtrs {
     float* staging[kMaxWorld];   // [2][world][max_elems]
-    uint32_t* flags[kMaxWorld];  // [2][world][kMaxTiles]
+    uint32_t* flags[kMaxWorld];  // [2][world][kMaxTiles][kFlagPad]: one 128-byte line per flag
 };
 
 struct HcFold {
@@ -54,6 +56,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -72,8 +79,8 @@ template <int RT, int NW, bool FP8>
 __global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
 gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, const uint16_t* __restrict__ xhi,
                const uint16_t* __restrict__ xlo, int ldx, float* __restrict__ y, int ldo, int mrows, int N, int K,
-               int accumulate, int store_y, ArPtrs t, uint32_t* __restrict__ epoch, int* __restrict__ status, int rank,
-               int world, int max_elems, int max_spins, HcFold hc) {
+               int accumulate, int store_y, ArPtrs t, uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status,
+               int rank, int world, int max_elems, int max_spins, int group, HcFold hc) {
     pdl_launch();
     constexpr int kTileN = 16 * RT;
     constexpr int KB = FP8 ? 128 : 64;
@@ -169,10 +176,16 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
     const bool live = owner && m < mrows && n0 + nl < N;
     float v = owner ? tile[m][nl] : 0.f;
     if (world > 1) {
+        // Tiles are published in groups of `group`: a CTA pushes its tile, fences at GPU scope and takes
+        // a ticket; the CTA that takes the group's last ticket fences at system scope and stamps the
+        // group's flag on every peer (one system fence per group instead of one per CTA: the GPU-scope
+        // release/acquire chain through the ticket makes the other CTAs' peer stores part of what the
+        // publishing thread's fence orders).  Every CTA of the group then waits for the group stamps.
         const int tl = blockIdx.x;
-        const uint32_t e = epoch[tl] + 1u;
+        const int grp = tl / group;
+        const int gsize = min(group, (int)gridDim.x - grp * group);
+        const uint32_t e = epoch[grp] + 1u;
         const int par = e & 1u;
-        // push: 8 rows x (kTileN / 4) float4 per peer
         constexpr int Q4 = kTileN / 4;
         for (int i = threadIdx.x; i < world * 8 * Q4; i += blockDim.x) {
             const int p = i / (8 * Q4), j = i % (8 * Q4), mm = j / Q4, c4 = j % Q4;
@@ -183,21 +196,29 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         }
         __syncthreads();
         if (threadIdx.x == 0) {
-            __threadfence_system();
-            for (int p = 0; p < world; ++p) st_release_sys(t.flags[p] + ((size_t)par * world + rank) * kMaxTiles + tl, e);
+            __threadfence();
+            if (atomicAdd(ticket + grp, 1u) == (unsigned)gsize - 1u) {
+                __threadfence_system();
+                for (int p = 0; p < world; ++p)
+                    st_release_sys(t.flags[p] + (((size_t)par * world + rank) * kMaxTiles + grp) * kFlagPad, e);
+                ticket[grp] = 0u;
+                epoch[grp] = e;   // every CTA of the group read the old value before it took its ticket
+            }
         }
         if (threadIdx.x < world) {
-            const uint32_t* f = t.flags[rank] + ((size_t)par * world + threadIdx.x) * kMaxTiles + tl;
+            const uint32_t* f = t.flags[rank] + (((size_t)par * world + threadIdx.x) * kMaxTiles + grp) * kFlagPad;
             int spins = 0;
-            while (ld_acquire_sys(f) < e) {
+            // relaxed polls (cheap, no cache maintenance), one acquire load once the stamp is there
+            while (ld_relaxed_sys(f) < e) {
                 if (++spins > max_spins) {
                     if (atomicCAS(&s_fail, 0, 1) == 0) {
-                        status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = tl;
+                        status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = grp;
                     }
                     break;
                 }
-                __nanosleep(32);
+                __nanosleep(64);
             }
+            (void)ld_acquire_sys(f);
         }
         __syncthreads();
         if (s_fail == 0 && live) {
@@ -205,8 +226,6 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
             for (int src = 0; src < world; ++src)
                 v += ld_cg_f32(t.staging[rank] + ((size_t)par * world + src) * max_elems + (size_t)m * N + n0 + nl);
         }
-        __syncthreads();
-        if (threadIdx.x == 0) epoch[tl] = e;  // stay in step with the peers even after a timeout
     }
     if (store_y && live) y[(size_t)m * ldo + n0 + nl] = v;
     if (!fold) return;
@@ -252,8 +271,8 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
 
 }  // namespace
 
-FB_API int fb_gemv_ar_limits(int* max_tiles, int* max_world) {
-    *max_tiles = kMaxTiles; *max_world = kMaxWorld;
+FB_API int fb_gemv_ar_limits(int* max_tiles, int* max_world, int* flag_words) {
+    *max_tiles = kMaxTiles; *max_world = kMaxWorld; *flag_words = kFlagPad;
     return 0;
 }
 
@@ -269,8 +288,8 @@ static void launch_ar(int N, cudaStream_t st, A... a) {
 // consumed and cleared by fb_hc_pre_apply / fb_d4_hc_pre; `acc` is not written by this kernel.
 FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_t xs_ld, int64_t xs_plane, float* y,
                       int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t accumulate, int64_t store_y,
-                      const void* const* staging_ptrs, const void* const* flag_ptrs, void* epoch, int* status,
-                      int64_t rank, int64_t world, int64_t max_elems, int64_t max_spins, const float* Rin, float* Rout,
+                      const void* const* staging_ptrs, const void* const* flag_ptrs, void* epoch, void* ticket,
+                      int* status, int64_t rank, int64_t world, int64_t max_elems, int64_t max_spins, int64_t group, const float* Rin, float* Rout,
                       const float* post, const float* comb, const float* fn, float* acc, int64_t mix, float* part,
                       int* part_n, cudaStream_t st) {
     const bool fp8 = scales != nullptr;
@@ -298,7 +317,7 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     else if ((N + 31) / 32 <= 256) shape = 2;
     else return (int)cudaErrorInvalidValue;
 #define AR_ARGS (const uint8_t*)W, scales, hi, lo, (int)xs_ld, y, (int)ldo, (int)m, (int)N, (int)K, (int)accumulate, \
-                (int)store_y, t, (uint32_t*)epoch, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, hc
+                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)(group > 0 ? group : 32), hc
     if (fp8) {
         if (shape == 0) launch_ar<1, 16, true>((int)N, st, AR_ARGS);
         else if (shape == 1) launch_ar<1, 8, true>((int)N, st, AR_ARGS);

@@ -241,7 +241,9 @@ class EngineConfig:
     fp8_experts: bool = True
     experts_resident: Optional[int] = None  # None = all routed experts of the shard
     kv_dtype: str = "bf16"  # latent cache dtype: "bf16" or "fp8"
-    fuse_epilogue: bool = True  # GEMV + all-reduce + hyper-connection fold in one kernel where it applies
+    # epilogue of a sublayer's last GEMV: "full" = all-reduce + hyper-connection fold in the same kernel,
+    # "ar" = all-reduce only, "off" = separate kernels (True / False are accepted for full / off)
+    fuse_epilogue: object = "full"
     collective: str = "p2p"  # "p2p" (fused peer-memory kernels) or "nccl"
     ar_max_spins: int = 20_000_000
     seed: int = 0

@@ -92,7 +92,10 @@ class GlmDeviceModel:
         self.allreduce = allreduce  # callable(tensor_view[n,H]) summing across ranks, in place
         # GEMV + all-reduce + hyper-connection fold as one launch (None: separate kernels)
         self.fused = None
-        if getattr(ecfg, "fuse_epilogue", True):
+        mode = getattr(ecfg, "fuse_epilogue", "full")
+        mode = {True: "full", False: "off"}.get(mode, mode)
+        self.fuse_fold = mode == "full"
+        if mode != "off" and (world > 1 or self.fuse_fold):
             if world > 1:
                 self.fused = getattr(allreduce, "fused", None)
             else:
@@ -410,6 +413,8 @@ class GlmDeviceModel:
         separately and the caller's _hc_post_mix does the fold."""
         ws = self.ws
         fold, self._fold_next = self._fold_next, None
+        if not self.fuse_fold:
+            fold = None
         xa = x if isinstance(x, Act) else None
         ldx = ldx if ldx is not None else (xa.ld if xa else K)
         kb = 128 if scales is not None else 64
