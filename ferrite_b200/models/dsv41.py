@@ -68,6 +68,16 @@ class Dsv41DeviceModel:
         self.Is = per if self.shared_tp else cfg.moe_inter_dim
         self.tc_min_rows = 16
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
+        self.fused = None
+        if world > 1:
+            self.fused = getattr(allreduce, "fused", None)
+        else:
+            from ..parallel.symm import FusedGemvAllReduce
+            self.fused = FusedGemvAllReduce(self.dev, 0, 1)
+        self._fold_next = None
+        self._folded = False
+        self.debug_hook = None
         self.win_cap = cfg.window_size + max_rows
         self.depth = 16
         self.token_map = token_map
@@ -289,6 +299,9 @@ class Dsv41DeviceModel:
 
     def _hc_post_mix(self, fn_next, n, first=False):
         cfg, ws = self.cfg, self.ws
+        if self._folded:   # the sublayer's last GEMV already did hc_post and the mix dots
+            self._folded = False
+            return
         rin = ws["R"]
         mix = (2 + cfg.hc_mult) * cfg.hc_mult
         if first:
@@ -297,6 +310,26 @@ class Dsv41DeviceModel:
         rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
         self.K.call("fb_hc_post_mix", rin, rout, ws["y"], ws["post"], ws["comb"], fn_next, ws["hc_acc"], n, cfg.dim, mix)
         ws["R"] = rout
+
+    def _out_gemv(self, w, x: Act, n, N, K, accumulate=False):
+        """Last GEMV of a sublayer into ws['y'], summed over ranks; inside a hyper-connection site
+        the fused kernel also applies hc_post and leaves the next site's mix-dot partials."""
+        ws = self.ws
+        fold, self._fold_next = self._fold_next, None
+        ok = (self.fused is not None and x.s is not None and n <= 8 and K % 64 == 0 and x.ld % 8 == 0 and N % 32 == 0
+              and (self.world == 1 or n * N <= self.fused.max_elems) and (self.world > 1 or fold is not None))
+        if not ok:
+            self.gemv(w, x, ws["y"], n, N, K, accumulate=accumulate)
+            self._reduce(ws["y"], n)
+            return
+        f = None
+        if fold is not None:
+            rin = ws["R"]
+            rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
+            f = (rin, rout, ws["post"], ws["comb"], fold[0], ws["hc_acc"], (2 + self.cfg.hc_mult) * self.cfg.hc_mult)
+            ws["R"] = rout
+            self._folded = True
+        self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f)
 
     def _hc_pre(self, L, site, ln, n, coeffs=True):
         """Coefficients of this site (stored for the next one) and the contraction with the previous
@@ -307,7 +340,8 @@ class Dsv41DeviceModel:
         self.K.call("fb_d4_hc_pre", ws["R"], ws["hc_acc"] if coeffs else None,
                     L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
                     ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
-                    cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0)
+                    cfg.hc_sinkhorn_iters, *x.sp(1),
+                    *(self.fused.partials() if self.fused is not None and coeffs and n <= 8 else (None, None, 0)))
         if coeffs:
             ws["pre_cur"], ws["pre_nxt"] = pout, pin
 
@@ -375,8 +409,7 @@ class Dsv41DeviceModel:
         R_ = cfg.o_lora_rank
         self.gemv(L["wo_a"], o, low, n, self.Gl * R_, cfg.heads_per_group * hd, ldx=self.Hl * hd, group_rows=R_)
         self._quant(low.f, low, n, self.Gl * R_)
-        self.gemv(L["wo_b"], low, ws["y"], n, d, self.Gl * R_)
-        self._reduce(ws["y"], n)
+        self._out_gemv(L["wo_b"], low, n, d, self.Gl * R_)
 
     def _moe(self, L, n):
         cfg, ws = self.cfg, self.ws
@@ -397,9 +430,11 @@ class Dsv41DeviceModel:
         self.gemv(L["sh_w13"], xq, ws["gu"], n, 2 * self.Is, d)
         self.K.call("fb_d4_swiglu_clamp", ws["gu"], 2 * self.Is, hs.f, self.Is, n, self.Is, float(cfg.swiglu_limit))
         self._quant(hs.f, hs, n, self.Is)
-        self.gemv(L["sh_w2"], hs, ws["y"], n, d, self.Is, accumulate=True)
-        if self.shared_tp:
-            self._reduce(ws["y"], n)
+        if self.shared_tp or self.world == 1:
+            self._out_gemv(L["sh_w2"], hs, n, d, self.Is, accumulate=True)
+        else:
+            self._fold_next = None
+            self.gemv(L["sh_w2"], hs, ws["y"], n, d, self.Is, accumulate=True)
 
     def _engram(self, L, rs, n):
         cfg, ws = self.cfg, self.ws
@@ -452,6 +487,7 @@ class Dsv41DeviceModel:
                 pending_mix = False
             self._hc_pre(L, "attn", L["attn_norm"], n)
             self._dbg(f"layers.{l}.attn_in", ws["x"].f[:n])
+            self._fold_next = (L["hc_ffn_fn"],)
             self._attention(L, rs, shared, self.ring[l])
             self._dbg(f"layers.{l}.attn_o", ws["o"].f[:n])
             if L["ratio"] > 0:
@@ -459,14 +495,14 @@ class Dsv41DeviceModel:
             self._dbg(f"layers.{l}.attn_out", ws["y"][:n])
             self._hc_post_mix(L["hc_ffn_fn"], n)
             self._hc_pre(L, "ffn", L["ffn_norm"], n)
+            nxt = self.layers[l + 1] if l + 1 < len(self.layers) else None
+            fn_next = nxt["hc_attn_fn"] if nxt is not None and "e_idx" not in nxt else None
+            self._fold_next = (fn_next,)
             self._moe(L, n)
             self._dbg(f"layers.{l}.route_idx", ws["ridx"][:n, :L["topk"]])
             self._dbg(f"layers.{l}.ffn_out", ws["y"][:n])
-            nxt = self.layers[l + 1] if l + 1 < len(self.layers) else None
-            if nxt is not None and "e_idx" not in nxt:
-                self._hc_post_mix(nxt["hc_attn_fn"], n)
-            else:
-                self._hc_post_mix(None, n)
+            self._hc_post_mix(fn_next, n)
+            if fn_next is None:
                 pending_mix = True
             self._dbg(f"layers.{l}.h", ws["R"][:n])
         self._hc_pre({}, "", self.norm_w, n, coeffs=False)
@@ -520,12 +556,15 @@ class Dsv41DeviceModel:
             if j == 0:
                 self._hc_post_mix(L["hc_attn_fn"], B, first=True)
             self._hc_pre(L, "attn", L["attn_norm"], B)
+            self._fold_next = (L["hc_ffn_fn"],)
             self._attention(L, rs_block, {}, self.ring[cfg.n_layers + j], extra=ws["d_extra"], n_extra=B, win_mode=1)
             self._hc_post_mix(L["hc_ffn_fn"], B)
             self._hc_pre(L, "ffn", L["ffn_norm"], B)
-            self._moe(L, B)
             nxt = self.mtp[j + 1] if j + 1 < len(self.mtp) else None
-            self._hc_post_mix(nxt["hc_attn_fn"] if nxt else None, B)
+            fn_next = nxt["hc_attn_fn"] if nxt else None
+            self._fold_next = (fn_next,)
+            self._moe(L, B)
+            self._hc_post_mix(fn_next, B)
         x = ws["x"]
         self.K.call("fb_d4_hc_pre", ws["R"], None, None, None, self.d_norm, ws["pre_cur"], ws["pre_nxt"], ws["post"],
                     ws["comb"], x.f, ws["d_xc"], B, d, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
