@@ -111,6 +111,73 @@ ar_oneshot_kernel(ArTables t, uint32_t* epoch, int* status, float* y, int n_elem
     if (ok && valid) *reinterpret_cast<float4*>(y + i) = r;
 }
 
+// Cross-rank argmax for a vocab-sliced head.  Each rank has the 64 per-slice partial keys of its
+// vocab slice for n rows (fb_argmax's first pass; a key orders by value, then by LOWER global index).
+// One CTA: thread r reduces row r's partials, stores the key into slot `rank` of every peer's
+// staging, the CTA publishes one epoch stamp per peer, waits (bounded) for all ranks' stamps and
+// takes the maximum key over the ranks - every rank ends with the same token id.  Replaces the
+// reference's argmax_xchg_v5 (kernels/cuda/dsv41_kernels.cu:11329,11393).
+struct XchgTables {
+    unsigned long long* staging[kMaxWorld];  // [2][world][kXchgRows]
+    uint32_t* flags[kMaxWorld];              // [2][world]
+};
+constexpr int kXchgRows = 64;
+
+__global__ void __launch_bounds__(64)
+argmax_xchg_kernel(const unsigned long long* __restrict__ part, XchgTables t, uint32_t* epoch, int* status,
+                   int* __restrict__ ids, float* __restrict__ vals, int id_stride, int n, int rank, int world,
+                   int max_spins) {
+    PDL_PROLOGUE();
+    __shared__ int s_fail;
+    const int r = threadIdx.x;
+    const uint32_t e = epoch[0] + 1u;
+    const int par = e & 1u;
+    if (r == 0) s_fail = 0;
+    unsigned long long best = 0ull;
+    if (r < n) {
+        for (int i = 0; i < 64; ++i) {
+            const unsigned long long k = part[(size_t)r * 64 + i];
+            best = k > best ? k : best;
+        }
+        for (int p = 0; p < world; ++p) t.staging[p][((size_t)par * world + rank) * kXchgRows + r] = best;
+    }
+    __syncthreads();
+    if (r == 0) {
+        __threadfence_system();
+        for (int p = 0; p < world; ++p) st_release_sys(t.flags[p] + par * world + rank, e);
+    }
+    if (r < world) {
+        const uint32_t* f = t.flags[rank] + par * world + r;
+        int spins = 0;
+        while (ld_acquire_sys(f) < e) {
+            if (++spins > max_spins) {
+                if (atomicCAS(&s_fail, 0, 1) == 0) { status[0] = FB_TIMEOUT; status[1] = r; status[2] = (int)e; status[3] = -2; }
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    if (r < n && s_fail == 0) {
+        for (int src = 0; src < world; ++src) {
+            unsigned long long k;
+            const unsigned long long* p = t.staging[rank] + ((size_t)par * world + src) * kXchgRows + r;
+            asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(k) : "l"(p));
+            best = k > best ? k : best;
+        }
+    }
+    if (r < n) {
+        ids[(size_t)r * id_stride] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+        if (vals) {
+            uint32_t u = (uint32_t)(best >> 32);
+            u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+            vals[r] = __uint_as_float(u);
+        }
+    }
+    __syncthreads();
+    if (r == 0) epoch[0] = e;
+}
+
 // A wait that nothing satisfies: used by the failure-detection test to check that a bounded
 // wait gives up with a status word and leaves the context usable.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, int max_spins, int* status) {
@@ -173,5 +240,23 @@ FB_API int fb_ar_oneshot(const void* const* staging_ptrs, const void* const* fla
 
 FB_API int fb_wait_flag(const void* flag, int64_t want, int64_t max_spins, int* status, cudaStream_t st) {
     FB_LAUNCH((wait_flag_kernel), 1, 1, 0, st, (const uint32_t*)flag, (uint32_t)want, (int)max_spins, status);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_argmax_xchg_limits(int* max_rows) { *max_rows = kXchgRows; return 0; }
+
+// part: this rank's first-pass argmax keys [n][64] (global indices: run fb_argmax_partial with the
+// slice's vocab offset).  staging_ptrs / flag_ptrs: `world` device pointers each.
+FB_API int fb_argmax_xchg(const void* part, const void* const* staging_ptrs, const void* const* flag_ptrs, void* epoch,
+                          int* status, int* ids, float* vals, int64_t id_stride, int64_t n, int64_t rank, int64_t world,
+                          int64_t max_spins, cudaStream_t st) {
+    if (n < 1 || n > kXchgRows || world > kMaxWorld) return (int)cudaErrorInvalidValue;
+    XchgTables t;
+    for (int i = 0; i < world; ++i) {
+        t.staging[i] = (unsigned long long*)staging_ptrs[i];
+        t.flags[i] = (uint32_t*)flag_ptrs[i];
+    }
+    FB_LAUNCH((argmax_xchg_kernel), 1, 64, 0, st, (const unsigned long long*)part, t, (uint32_t*)epoch, status, ids, vals,
+              (int)id_stride, (int)n, (int)rank, (int)world, (int)max_spins);
     return FB_LAUNCH_CHECK();
 }

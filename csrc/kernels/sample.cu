@@ -20,7 +20,8 @@ __device__ __forceinline__ unsigned long long amax_key(float v, int idx) {
 constexpr int kSlices = 64;
 
 __global__ void __launch_bounds__(256)
-argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long long* __restrict__ part, int V) {
+argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long long* __restrict__ part, int V,
+                      int key_offset) {
     PDL_PROLOGUE();
     __shared__ unsigned long long wb[8];
     const int r = blockIdx.y;
@@ -30,7 +31,7 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long lo
     for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         const float v = logits[(size_t)r * ld + i];
         if (v == v) {  // NaN never wins
-            const unsigned long long k = amax_key(v, i);
+            const unsigned long long k = amax_key(v, i + key_offset);
             best = k > best ? k : best;
         }
     }
@@ -134,8 +135,17 @@ __global__ void copy_i32_kernel(const int* __restrict__ src, int* __restrict__ d
 // part: scratch of n*64 u64.  ids[r*id_stride] = argmax (+ vocab_offset); vals (optional) = max.
 FB_API int fb_argmax(const float* logits, int64_t ld, void* part, int* ids, float* vals, int64_t n, int64_t V,
                      int64_t id_stride, int64_t vocab_offset, cudaStream_t st) {
-    FB_LAUNCH((argmax_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V);
+    FB_LAUNCH((argmax_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V, 0);
     FB_LAUNCH((argmax_final_kernel), n, 32, 0, st, (const unsigned long long*)part, ids, vals, (int)id_stride, (int)vocab_offset);
+    return FB_LAUNCH_CHECK();
+}
+
+// First pass only: part[r][64] keys over this rank's vocab slice with GLOBAL indices (i + vocab_offset),
+// to be merged across ranks by fb_argmax_xchg.
+FB_API int fb_argmax_partial(const float* logits, int64_t ld, void* part, int64_t n, int64_t V, int64_t vocab_offset,
+                             cudaStream_t st) {
+    FB_LAUNCH((argmax_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V,
+              (int)vocab_offset);
     return FB_LAUNCH_CHECK();
 }
 

@@ -223,7 +223,18 @@ class GlmDeviceModel:
     def _pack(self, src):
         cfg = self.cfg
         self.embed = self._bf(src.get("model.embed_tokens.weight"))
-        self.lm_head = self._bf(src.get("lm_head.weight"))
+        # the head is sliced by vocab rows when the ranks can merge their argmax (cross-rank exchange);
+        # every rank then streams 1/world of the largest matrix of the model
+        head = src.get("lm_head.weight")
+        self.xargmax = getattr(self.allreduce, "argmax", None) if self.world > 1 else None
+        self.vocab_off = 0
+        if self.xargmax is not None and head.shape[0] % (self.world * 16) == 0:
+            vl = head.shape[0] // self.world
+            self.vocab_off = self.rank * vl
+            head = head[self.vocab_off:self.vocab_off + vl]
+        else:
+            self.xargmax = None
+        self.lm_head = self._bf(head)
         self.final_norm = self._f(src.get("model.norm.weight"))
         n_total = cfg.num_layers + cfg.num_nextn_predict_layers
         for i in range(n_total):
@@ -401,6 +412,14 @@ class GlmDeviceModel:
                 self.K.call("fb_gemv_bf16", w, xp, ldx, op, ldo, mm, N, K, group_rows, accumulate)
             if osb[0] is not None:
                 self.K.call("fb_split_rows", op, ldo, *osb, mm, N)
+
+    def _argmax(self, out_ids, n, V):
+        """Greedy ids of ws['logits'][:n] (this rank's vocab slice when the head is sliced)."""
+        ws = self.ws
+        if self.xargmax is None:
+            self.K.call("fb_argmax", ws["logits"], V, ws["amax_part"], out_ids, None, n, V, 1, 0)
+        else:
+            self.xargmax(ws["logits"], V, ws["amax_part"], n, V, self.vocab_off, out_ids)
 
     def _reduce(self, y, n):
         if self.world > 1:
@@ -591,7 +610,7 @@ class GlmDeviceModel:
         if nh > 0:
             self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
             if judges is not None:
-                K.call("fb_argmax", ws["logits"], V, ws["amax_part"], View(judges, head_from), None, nh, V, 1, 0)
+                self._argmax(View(judges, head_from), nh, V)
         if advance:
             K.call("fb_advance_rows", rs.meta, None, self.main_len, n)
 
@@ -616,7 +635,7 @@ class GlmDeviceModel:
         if out_ids is not None and nh > 0:
             V = self.lm_head.shape[0]
             self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
-            K.call("fb_argmax", ws["logits"], V, ws["amax_part"], out_ids, None, nh, V, 1, 0)
+            self._argmax(out_ids, nh, V)
         if advance:
             K.call("fb_advance_rows", rs.meta, None, self.mtp_len, n)
 

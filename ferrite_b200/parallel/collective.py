@@ -14,10 +14,11 @@ import torch.distributed as dist
 def make_allreduce(device, rank: int, world: int, max_elems: int, kind: str = "nccl", fused: bool = True):
     """kind "p2p" also carries ``.fused``, the GEMV + all-reduce (+ fold) kernel, unless fused=False."""
     if kind == "p2p":
-        from .symm import FusedGemvAllReduce, P2PAllReduce
+        from .symm import CrossRankArgmax, FusedGemvAllReduce, P2PAllReduce
         ar = P2PAllReduce(device, rank, world, max_elems)
         if fused:
             ar.fused = FusedGemvAllReduce(device, rank, world)
+        ar.argmax = CrossRankArgmax(device, rank, world)   # enables the vocab-sliced head
         return ar
 
     def nccl_allreduce(view: torch.Tensor):

@@ -86,6 +86,7 @@ class P2PAllReduce:
         self._fp = arr(*self.flags.ptrs)
         self.calls = 0
         self.fused: Optional["FusedGemvAllReduce"] = None   # attached by make_allreduce
+        self.argmax: Optional["CrossRankArgmax"] = None      # attached by make_allreduce
 
     def __call__(self, view: torch.Tensor):
         n = view.numel()
@@ -102,10 +103,14 @@ class P2PAllReduce:
             raise CollectiveTimeout(s[1], s[2], s[3])
         if self.fused is not None:
             self.fused.check()
+        if self.argmax is not None:
+            self.argmax.check()
 
     def close(self):
         if self.fused is not None:
             self.fused.close()
+        if self.argmax is not None:
+            self.argmax.close()
         self.staging.close()
         self.flags.close()
 
@@ -169,3 +174,43 @@ class FusedGemvAllReduce:
             self.staging.close()
             self.flags.close()
             self.staging = self.flags = None
+
+
+class CrossRankArgmax:
+    """Greedy token of a vocab-sliced head: per-rank argmax partials merged over the ranks in one
+    small kernel (``fb_argmax_xchg``); every rank gets the same global token id."""
+
+    def __init__(self, device, rank: int, world: int, max_spins: int = 2_000_000, group=None):
+        self.K = _lib.lib()
+        self.rank, self.world, self.max_spins = rank, world, max_spins
+        mr = ctypes.c_int()
+        self.K.lib.fb_argmax_xchg_limits(ctypes.byref(mr))
+        self.max_rows = mr.value
+        self.staging = SymmetricRegion(2 * world * self.max_rows * 8, rank, world, group)
+        self.flags = SymmetricRegion(max(256, 2 * world * 4), rank, world, group)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        arr = ctypes.c_void_p * world
+        self._sp = arr(*self.staging.ptrs)
+        self._fp = arr(*self.flags.ptrs)
+
+    def __call__(self, logits, ld: int, part, n: int, v_local: int, vocab_offset: int, out_ids, id_stride: int = 1,
+                 vals=None):
+        self.K.call("fb_argmax_partial", logits, ld, part, n, v_local, vocab_offset)
+        for r0 in range(0, n, self.max_rows):   # the exchange kernel takes up to max_rows rows per launch
+            m = min(self.max_rows, n - r0)
+            pp = ctypes.c_void_p(part.data_ptr() + r0 * 64 * 8)
+            op = ctypes.c_void_p(out_ids.data_ptr() + r0 * id_stride * 4)
+            vp = ctypes.c_void_p(vals.data_ptr() + r0 * 4) if vals is not None else None
+            self.K.call("fb_argmax_xchg", pp, self._sp, self._fp, self.epoch, self.status, op, vp, id_stride, m,
+                        self.rank, self.world, self.max_spins)
+
+    def check(self):
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3])
+
+    def close(self):
+        self.staging.close()
+        self.flags.close()

@@ -11,7 +11,7 @@ from ferrite_b200.config import EngineConfig, GlmConfig  # noqa: E402
 from ferrite_b200.engine.glm_engine import GlmEngine  # noqa: E402
 from ferrite_b200.models.glm import DictSource  # noqa: E402
 from ferrite_b200.models.glm_weights import random_weights  # noqa: E402
-from ferrite_b200.parallel.symm import FusedGemvAllReduce, P2PAllReduce  # noqa: E402
+from ferrite_b200.parallel.symm import CrossRankArgmax, FusedGemvAllReduce, P2PAllReduce  # noqa: E402
 
 
 def main():
@@ -22,6 +22,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     ar = P2PAllReduce(dev, rank, world, max_elems=64 * 4096)
     ar.fused = FusedGemvAllReduce(dev, rank, world)
+    ar.argmax = CrossRankArgmax(dev, rank, world)
     # 1. one-shot all-reduce == NCCL all-reduce, bit-identical across ranks, eager and in a graph
     for n in (4096, 3 * 4096, 16 * 4096 + 8, 64 * 4096):
         g = torch.Generator(device=dev).manual_seed(100 + rank)
@@ -81,6 +82,23 @@ def main():
             torch.cuda.synchronize()
             assert torch.equal(y2, y), (N, Kd, m, it)
         ar.check()
+    # 1c. vocab-sliced argmax merged across ranks == argmax of the full row (first maximum wins)
+    V, n = 4096 * world, 5
+    full = torch.randn(n, V, device=dev, generator=torch.Generator(device=dev).manual_seed(11))
+    full[1, 17] = full[1, V - 3] = 60.0      # a tie across slices: the lower index wins
+    full[2, V - 1] = 70.0
+    vl = V // world
+    mine = full[:, rank * vl:(rank + 1) * vl].contiguous()
+    part = torch.zeros(n * 64, dtype=torch.int64, device=dev)
+    ids = torch.zeros(n, dtype=torch.int32, device=dev)
+    vals = torch.zeros(n, device=dev)
+    for it in range(3):
+        ar.argmax(mine, vl, part, n, vl, rank * vl, ids, 1, vals)
+        torch.cuda.synchronize()
+        ar.check()
+        from ferrite_b200.ops.reference import argmax_first
+        assert ids.tolist() == argmax_first(full.cpu()).tolist(), (it, ids.tolist())
+        assert torch.equal(vals.cpu(), full.max(-1).values.cpu())
     # 2. tensor-parallel engine == single-rank engine, token for token (greedy and MTP)
     for name in ("tiny", "golden4"):
         cfg = getattr(GlmConfig, name)()
