@@ -214,3 +214,36 @@ class CrossRankArgmax:
     def close(self):
         self.staging.close()
         self.flags.close()
+
+
+class DcpAttentionMerge:
+    """Cross-rank LSE merge of sparse-attention partials for a decode-context-parallel group
+    (``csrc/kernels/dsa_dcp.cu``): one launch per attention layer."""
+
+    def __init__(self, device, rank: int, world: int, max_rows: int, heads: int, latent_dim: int,
+                 max_spins: int = 2_000_000, group=None):
+        self.K = _lib.lib()
+        self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.slot_elems = max_rows * heads * (latent_dim + 4)
+        self.staging = SymmetricRegion(2 * world * self.slot_elems * 4, rank, world, group)
+        self.flags = SymmetricRegion(2 * world * 32 * 4, rank, world, group)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        arr = ctypes.c_void_p * world
+        self._sp = arr(*self.staging.ptrs)
+        self._fp = arr(*self.flags.ptrs)
+
+    def __call__(self, o_part, ml_part, ctx, n: int, heads: int, latent_dim: int, nsplit: int, split=(None, 0, 0, 0)):
+        self.K.call("fb_dsa_attn_merge_dcp", o_part, ml_part, ctx, n, heads, latent_dim, nsplit, self._sp, self._fp,
+                    self.epoch, self.ticket, self.status, self.rank, self.world, self.slot_elems, self.max_spins, *split)
+
+    def check(self):
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3])
+
+    def close(self):
+        self.staging.close()
+        self.flags.close()

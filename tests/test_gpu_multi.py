@@ -19,3 +19,12 @@ def test_p2p_allreduce_and_tp_engine():
            "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.join(HERE, "_tp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pdaf_handoff_prefill_rank_to_decode_rank():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29543", os.path.join(HERE, "_pdaf_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "PDAF_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

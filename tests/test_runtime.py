@@ -222,3 +222,15 @@ def test_tick_planner_page_pressure_evicts_cache_then_queues():
     assert plan.admitted == [b] and s.stats().queued == 1
     _drain(s)
     assert s.get(c).finish_reason == "length"
+
+
+def test_pdaf_transfer_plan_page_mask():
+    from ferrite_b200.parallel.pdaf import TransferPlan
+    plan = TransferPlan(n_tokens=70, page_size=16, n_dcp=4, d=1)
+    assert plan.n_pages == 5 and plan.src_pages == [1] and plan.dst_slots == [0]
+    got = sorted(p for d in range(4) for p in TransferPlan(70, 16, 4, d).src_pages)
+    assert got == [0, 1, 2, 3, 4]                       # every page goes to exactly one decode rank
+    p0 = TransferPlan(70, 16, 4, 0)
+    assert p0.src_pages == [0, 4] and p0.dst_slots == [0, 1]   # page p lands at slot p // n_dcp
+    assert TransferPlan(70, 16).src_pages == [0, 1, 2, 3, 4]
+    assert p0.bytes_moved(100, 7) == 207
