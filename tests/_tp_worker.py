@@ -99,6 +99,45 @@ def main():
         from ferrite_b200.ops.reference import argmax_first
         assert ids.tolist() == argmax_first(full.cpu()).tolist(), (it, ids.tolist())
         assert torch.equal(vals.cpu(), full.max(-1).values.cpu())
+    # 1d. expert-parallel MoE (all-to-all dispatch / combine) == all experts applied to this rank's own rows
+    from ferrite_b200.ops import reference as R
+    from ferrite_b200.parallel.ep import EpMoE
+    H_, I_, E_, topk_, n_max_ = 256, 128, 4 * world, 2, 4
+    gw = torch.Generator().manual_seed(21)
+    w13f = torch.randn(E_, 2 * I_, H_, generator=gw) * 0.05
+    w2f = torch.randn(E_, H_, I_, generator=gw) * 0.05
+    q13 = [R.quant_fp8_block(w13f[e]) for e in range(E_)]
+    q2 = [R.quant_fp8_block(w2f[e]) for e in range(E_)]
+    el = E_ // world
+    mine = range(rank * el, (rank + 1) * el)
+    w13 = torch.stack([q13[e][0] for e in mine]).to(dev)
+    s13 = torch.stack([q13[e][1] for e in mine]).to(dev)
+    w2 = torch.stack([q2[e][0] for e in mine]).to(dev)
+    s2 = torch.stack([q2[e][1] for e in mine]).to(dev)
+    ep = EpMoE(dev, rank, world, n_max_, H_, topk_, I_)
+    for it, n_loc in enumerate((3, 4, 1)):
+        gx = torch.Generator().manual_seed(100 * it + rank)
+        xa = Act(dev, n_max_, H_)
+        xa.f[:n_loc].copy_(torch.randn(n_loc, H_, generator=gx))
+        K.call("fb_split_rows", xa.f, H_, *xa.sp(3), n_max_, H_)
+        ids = torch.stack([torch.randperm(E_, generator=gx)[:topk_] for _ in range(n_loc)]).to(torch.int32).to(dev)
+        wts = torch.rand(n_loc, topk_, generator=gx).to(dev)
+        add = torch.randn(n_max_, H_, generator=gx).to(dev)
+        y = torch.zeros(n_max_, H_, device=dev)
+        ep.forward(xa.s, xa.plane, ids, wts, n_loc, w13, s13, w2, s2, el, 7.0, y, add)
+        torch.cuda.synchronize()
+        ep.check()
+        want = add[:n_loc].cpu().clone()
+        xc = xa.f[:n_loc].cpu()
+        for r in range(n_loc):
+            for s_ in range(topk_):
+                e = int(ids[r, s_])
+                gu = xc[r] @ R.dequant_fp8_block(*q13[e]).t()
+                h = R.swiglu_limited(gu[:I_], gu[I_:], 7.0) * float(wts[r, s_])
+                want[r] += h @ R.dequant_fp8_block(*q2[e]).t()
+        err = (y[:n_loc].cpu() - want).abs().max().item()
+        assert err < 3e-2 * max(1.0, want.abs().max().item()), (it, n_loc, err)
+    ep.close()
     # 2. tensor-parallel engine == single-rank engine, token for token (greedy and MTP)
     for name in ("tiny", "golden4"):
         cfg = getattr(GlmConfig, name)()
