@@ -1,0 +1,1 @@
+"""Host-side utilities: debug switches, tracing and timing, op traces, dumps, parity checks."""

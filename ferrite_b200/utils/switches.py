@@ -1,0 +1,62 @@
+"""One registry of debug switches, parsed once.
+
+The reference reads ~450 environment variables at their use sites, some by presence and some by
+value, with defaults that differ per translation unit (``AGENTS.md:49-95``;
+``scripts/dsv41_recovery_verify.sh:21-24``).  Here every switch is declared once with a type and a
+default, ``FERRITE_<NAME>`` overrides it, and code asks ``switches().name``.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, fields
+from typing import Optional
+
+
+def _parse_bool(v: str) -> bool:
+    return v.strip().lower() not in ("", "0", "false", "no", "off")
+
+
+@dataclass
+class Switches:
+    timing: bool = False            # per-phase CUDA-event timers in the engines
+    layer_sums: bool = False        # per-layer checksums of the residual stream
+    trace_tokens: bool = False      # print every emitted token id
+    trace_nan: bool = False         # check sublayer outputs for non-finite values (eager runs)
+    debug_sync: bool = False        # synchronise after every kernel call
+    nvtx: bool = False              # NVTX ranges around engine phases
+    pdl: bool = False               # programmatic dependent launch
+    ar_group: int = 0               # tiles per published group of the fused GEMV all-reduce (0 = whole grid)
+    dump_dir: str = ""              # directory for unit dumps ("" = off)
+    allow_stale_kernels: bool = False
+
+    @staticmethod
+    def from_env(env=None) -> "Switches":
+        env = os.environ if env is None else env
+        s = Switches()
+        for f in fields(s):
+            raw = env.get("FERRITE_" + f.name.upper())
+            if raw is None:
+                continue
+            if f.type in ("bool", bool):
+                setattr(s, f.name, _parse_bool(raw))
+            elif f.type in ("int", int):
+                setattr(s, f.name, int(raw))
+            else:
+                setattr(s, f.name, raw)
+        return s
+
+
+_CURRENT: Optional[Switches] = None
+
+
+def switches() -> Switches:
+    global _CURRENT
+    if _CURRENT is None:
+        _CURRENT = Switches.from_env()
+    return _CURRENT
+
+
+def set_switches(s: Optional[Switches]) -> None:
+    """Install (or with None: re-read from the environment on next use)."""
+    global _CURRENT
+    _CURRENT = s
