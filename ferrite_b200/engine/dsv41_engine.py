@@ -49,13 +49,15 @@ class Dsv41Engine(SpecStep):
         self.accept_hist: List[int] = []
 
     # ---- prefill -----------------------------------------------------------------------------------
-    def prefill(self, prompt: Sequence[int]) -> int:
+    def prefill(self, prompt: Sequence[int], start: int = 0) -> int:
+        """Prefill prompt[start:] on top of `start` positions that are already in the caches."""
         m = self.model
-        m.reset_slot(0)
-        self.pos = 0
+        if start == 0:
+            m.reset_slot(0)
+        self.pos = start
         ids = torch.tensor(list(prompt), dtype=torch.int32, device=self.dev)
         step = m.max_rows
-        for i in range(0, len(prompt), step):
+        for i in range(start, len(prompt), step):
             c = ids[i:i + step]
             rs = m.make_rows([0], [c.numel()])
             last = i + step >= len(prompt)
@@ -143,3 +145,42 @@ class Dsv41Engine(SpecStep):
             else:
                 out.append(self.step_plain())
         return out[:n_new]
+
+
+class Dsv41StepEngine:
+    """``StepEngine`` over :class:`Dsv41Engine` with a host-snapshot prefix cache (LRU): a prompt whose
+    beginning equals a cached prompt resumes from that snapshot and prefills only the rest
+    (reference ``crates/ferrite-dsv41/src/serve.rs:934-1039``, ``prefill_or_resume``)."""
+
+    def __init__(self, engine: Dsv41Engine, spec: bool = True, cache_entries: int = 4):
+        self.eng = engine
+        self.spec = spec and engine.has_spec
+        self.cache_entries = cache_entries
+        self.cache: List[tuple] = []     # (prompt tuple, snapshot), most recent last
+        self.hits = self.misses = 0
+
+    def _lookup(self, prompt: Sequence[int]):
+        best = None
+        for key, snap in self.cache:
+            if len(key) < len(prompt) and tuple(prompt[:len(key)]) == key and (best is None or len(key) > len(best[0])):
+                best = (key, snap)
+        return best
+
+    def start(self, prompt: List[int]):
+        hit = self._lookup(prompt)
+        cached = 0
+        if hit is not None:
+            self.eng.model.restore_slot(hit[1])
+            cached = len(hit[0])
+            self.hits += 1
+        else:
+            self.misses += 1
+        first = self.eng.prefill(prompt, start=cached)
+        if self.cache_entries:
+            self.cache = [(k, s) for k, s in self.cache if k != tuple(prompt)]
+            self.cache.append((tuple(prompt), self.eng.model.snapshot_slot()))
+            del self.cache[:-self.cache_entries]
+        return first, cached
+
+    def step(self) -> List[int]:
+        return self.eng.spec_step() if self.spec else [self.eng.step_plain()]

@@ -287,6 +287,36 @@ class Dsv41DeviceModel:
     def make_rows(self, slots: List[int], gsizes: List[int]) -> RowSet:
         return GlmDeviceModel.make_rows(self, slots, gsizes)
 
+    # ---- sequence snapshots (host-side prefix cache, speculative experiments) ------------------
+    def snapshot_slot(self, slot: int = 0) -> dict:
+        """Everything a sequence owns, copied to host memory (reference: the host-snapshot KV prefix
+        cache of ``crates/ferrite-dsv41/src/serve.rs:79-101,934-1020``)."""
+        n = int(self.seq_len[slot])
+        snap = {"len": n, "ring": self.ring[:, slot].cpu()}
+        for l, t in self.comp.items():
+            used = (n // self.cfg.ratio(l)) + 1
+            snap[f"comp{l}"] = t[slot, :used].cpu()
+            snap[f"kidx{l}"] = self.kidx[l][slot, :used].cpu()
+        for l, (a, b) in self.cring.items():
+            snap[f"cring{l}"] = (a[slot].cpu(), b[slot].cpu())
+        if self.layout is not None:
+            snap["e_hist"] = self.e_hist[slot, :n].cpu()
+        return snap
+
+    def restore_slot(self, snap: dict, slot: int = 0) -> None:
+        n = snap["len"]
+        self.ring[:, slot].copy_(snap["ring"])
+        for l, t in self.comp.items():
+            used = snap[f"comp{l}"].shape[0]
+            t[slot, :used].copy_(snap[f"comp{l}"])
+            self.kidx[l][slot, :used].copy_(snap[f"kidx{l}"])
+        for l, (a, b) in self.cring.items():
+            a[slot].copy_(snap[f"cring{l}"][0])
+            b[slot].copy_(snap[f"cring{l}"][1])
+        if self.layout is not None:
+            self.e_hist[slot, :n].copy_(snap["e_hist"])
+        self.seq_len[slot] = n
+
     # ---- forward ---------------------------------------------------------------------------------
     def _reduce(self, t, n):
         if self.world > 1:

@@ -26,6 +26,8 @@ def build_engine(args):
     if args.model == "mock":
         return HostEngine(vocab=tok.vocab_size, max_rows=args.max_seqs), tok, 0, 1
     import torch
+    if args.model.startswith("dsv41"):
+        return _build_dsv41(args, tok)
     from ..config import EngineConfig, GlmConfig
     cfgs = {"glm53": GlmConfig.production, "glm-tiny": GlmConfig.tiny, "glm-golden4": GlmConfig.golden4}
     if args.model not in cfgs:
@@ -73,6 +75,44 @@ def build_engine(args):
         from .tp_pool import ReplicatedEngine, make_control_group
         eng = ReplicatedEngine(eng, rank, world, make_control_group())
     return eng, tok, rank, world
+
+
+def _build_dsv41(args, tok):
+    """DSV41: ``--model dsv41-tiny`` (random weights) or ``--model dsv41 --model-dir DIR`` (checkpoint)."""
+    import torch
+    from ..engine.dsv41_engine import Dsv41Engine, Dsv41StepEngine
+    from ..models.dsv41 import DictWeights
+    from ..models.dsv41_config import Dsv41Config
+    from .engine import SingleFlight
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.tp, f"--tp {args.tp} needs {args.tp} processes (torch.distributed.run), got {world}"
+    cfg_path = os.path.join(args.model_dir, "config.json") if args.model_dir else None
+    if cfg_path and os.path.exists(cfg_path):
+        cfg = Dsv41Config.from_hf(cfg_path)
+    else:
+        cfg = Dsv41Config.tiny() if args.model == "dsv41-tiny" else Dsv41Config.flash()
+    if args.model_dir and not args.synthetic:
+        from ..models.dsv41_checkpoint import Dsv41CheckpointSource
+        src = Dsv41CheckpointSource(args.model_dir, cfg)
+    else:
+        from ..models.dsv41_weights import random_weights
+        src = DictWeights(random_weights(cfg, 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    allreduce = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from ..parallel.collective import make_allreduce
+        allreduce = make_allreduce(dev, rank, world, max_elems=64 * max(cfg.dim, 4096), kind="p2p")
+    eng = Dsv41Engine(cfg, src, rank, world, dev, allreduce, max_ctx=args.max_ctx)
+    serve_eng = SingleFlight(Dsv41StepEngine(eng, spec=args.mtp > 1))
+    if world > 1:
+        from .tp_pool import ReplicatedEngine, make_control_group
+        serve_eng = ReplicatedEngine(serve_eng, rank, world, make_control_group())
+    return serve_eng, tok, rank, world
 
 
 class _GlmStep:

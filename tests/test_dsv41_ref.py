@@ -148,3 +148,15 @@ def test_spec_generate_matches_greedy():
     spec, ks = m.spec_generate(prompt, 10)
     assert spec == plain
     assert all(1 <= k <= cfg.dspark_block_size + 1 for k in ks)
+
+
+def test_checkpoint_roundtrip_is_exact(tmp_path):
+    from ferrite_b200.models.dsv41_checkpoint import Dsv41CheckpointSource, save_checkpoint
+    cfg = Dsv41Config.tiny()
+    w = random_weights(cfg, 3)
+    save_checkpoint(str(tmp_path), cfg, w, shards=3)
+    src = Dsv41CheckpointSource(str(tmp_path), cfg)
+    for name in ("layers.1.attn.wq_b.weight", "layers.0.ffn.experts.3.w2.weight", "layers.1.engram.embed.weight",
+                 "layers.3.attn.compressor.wkv.weight", "layers.2.hc_attn_fn", "embed.weight", "mtp.1.markov_head.head.weight"):
+        assert src.has(name) and torch.equal(src.get(name), w[name]), name
+    assert not src.has("layers.0.attn.compressor.wkv.weight")

@@ -147,3 +147,28 @@ def test_draft_block_matches_golden():
     assert (got - dl).abs().max().item() < 5e-2 * max(1.0, dl.abs().max().item())
     assert out.tolist()[0] == t0 and sum(a == b for a, b in zip(out.tolist()[1:], drafts)) >= B - 1
     assert (dev.dspark_confidence().cpu() - conf).abs().max().item() < 5e-2 * max(1.0, conf.abs().max().item())
+
+
+def test_step_engine_prefix_cache_resumes_exactly():
+    from ferrite_b200.engine.dsv41_engine import Dsv41Engine, Dsv41StepEngine
+    from ferrite_b200.models.dsv41 import DictWeights
+    cfg, w, ref = _pair(seed=6)
+    a = [3, 17, 99, 250, 4, 8, 15, 16, 23, 42, 77, 5, 6]
+    b = a + [100, 101, 102, 7]
+    for spec in (False, True):
+        cold = Dsv41StepEngine(Dsv41Engine(cfg, DictWeights(w), max_ctx=128), spec=spec, cache_entries=0)
+        first, cached = cold.start(b)
+        want = [first]
+        while len(want) < 10:
+            want += cold.step()
+        warm = Dsv41StepEngine(Dsv41Engine(cfg, DictWeights(w), max_ctx=128), spec=spec)
+        f0, c0 = warm.start(a)
+        assert c0 == 0
+        for _ in range(3):
+            warm.step()                      # decode past the prompt: the snapshot must not include this
+        f1, c1 = warm.start(b)
+        assert c1 == len(a) and warm.hits == 1
+        got = [f1]
+        while len(got) < 10:
+            got += warm.step()
+        assert got[:10] == want[:10], (spec, got, want)

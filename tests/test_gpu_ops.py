@@ -574,3 +574,20 @@ def test_gemv_ar_fold_single_rank(K, fp8):
     check("gemv_ar -> hc_pre post", po, pr, 5 * tol)
     check("gemv_ar -> hc_pre comb", co, cr.reshape(m, 16), 5 * tol)
     assert not part_n.any() and not acc.any()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(K):
+    """Failure detection without a fault: a wait on a flag that nothing sets runs out of polls,
+    writes {TIMEOUT, -1, wanted, polls} to the status word and returns; the context stays usable."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.full((4,), -7, dtype=torch.int32, device="cuda")
+    K.call("fb_wait_flag", flag, 5, 2000, status)      # wants stamp 5, flag stays 0: gives up after 2000 polls
+    torch.cuda.synchronize()
+    s = status.tolist()
+    assert s[0] == 1 and s[1] == -1 and s[2] == 5 and s[3] > 2000
+    flag.fill_(5)
+    K.call("fb_wait_flag", flag, 5, 2000, status)      # satisfied at once
+    torch.cuda.synchronize()
+    assert status[0].item() == 0
+    x = torch.arange(8, device="cuda").sum().item()    # the context still runs kernels
+    assert x == 28
