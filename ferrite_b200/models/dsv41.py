@@ -486,14 +486,24 @@ class Dsv41DeviceModel:
         if self.debug is not None:
             self.debug(name, t)
 
-    def forward(self, rs: RowSet, ids: torch.Tensor, advance: bool = True, want_logits: bool = True):
+    def forward(self, rs: RowSet, ids: torch.Tensor, advance: bool = True, want_logits: bool = True,
+                image_embeds: Optional[torch.Tensor] = None, is_image: Optional[torch.Tensor] = None):
         """Run rs.n rows; ids [n] int32 on the device.  Leaves logits in ws['logits'], greedy ids in
-        ws['out_ids'] and the DSpark target hiddens in ws['mh']."""
+        ws['out_ids'] and the DSpark target hiddens in ws['mh'].  Rows flagged in `is_image` [n] take
+        their embedding from `image_embeds` [n, dim] (vision tower output), get no engram
+        contribution and route with the image bias."""
         cfg, ws, n = self.cfg, self.ws, rs.n
         d = cfg.dim
         self.K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.seq_len, rs.meta, n)
         ws["R"] = ws["R0"]
         self.K.call("fb_embed_expand", ids, self.embed, ws["R"], n, d, cfg.hc_mult, cfg.vocab_size)
+        self.has_images = image_embeds is not None
+        if self.has_images:
+            mask = is_image.to(self.dev).bool()
+            ws["is_image"][:n].copy_(mask)
+            ws["R"][:n] = torch.where(mask[:, None, None], image_embeds.to(self.dev).float()[:, None, :], ws["R"][:n])
+        else:
+            ws["is_image"].zero_()
         ws["pre0"].zero_()
         ws["pre0"][:, 0] = 1.0
         ws["pre_cur"], ws["pre_nxt"] = ws["pre0"], ws["pre1"]

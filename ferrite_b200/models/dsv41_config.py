@@ -29,7 +29,7 @@ class VisionConfig:
 
     @staticmethod
     def tiny() -> "VisionConfig":
-        return VisionConfig(n_layers=2, dim=64, n_heads=4, inter_dim=96, patch_size=4, downsample_ratio=2,
+        return VisionConfig(n_layers=2, dim=128, n_heads=4, inter_dim=192, patch_size=4, downsample_ratio=2,
                             max_image_tokens=16)
 
 

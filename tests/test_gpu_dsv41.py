@@ -172,3 +172,47 @@ def test_step_engine_prefix_cache_resumes_exactly():
         while len(got) < 10:
             got += warm.step()
         assert got[:10] == want[:10], (spec, got, want)
+
+
+def test_vision_tower_and_image_rows():
+    from ferrite_b200.models.dsv41 import DictWeights, Dsv41DeviceModel
+    from ferrite_b200.models.dsv41_vision import (IMAGE, VisionDevice, VisionReference, expand_image_tokens)
+    cfg = Dsv41Config.tiny(vision=True)
+    w = random_weights(cfg, 9)
+    n_h, n_w = 5, 6
+    patches = torch.randn(n_h * n_w, 3 * cfg.vision.patch_size ** 2, generator=torch.Generator().manual_seed(1))
+    patches = patches.to(torch.bfloat16).float()
+    vref = VisionReference(cfg, w)
+    vdev = VisionDevice(cfg, DictWeights(w))
+    want_vit = vref.vit(patches, n_h, n_w)
+    got_vit = vdev.vit(patches, n_h, n_w).cpu()
+    assert (got_vit - want_vit).abs().max().item() < 3e-2 * max(1.0, want_vit.abs().max().item())
+    want = vref.encode_image(patches, n_h, n_w)
+    got = vdev.encode_image(patches, n_h, n_w).cpu()
+    torch.cuda.synchronize()
+    assert int(vdev.status[0]) == 0 and got.shape == (9, cfg.dim)
+    assert (got - want).abs().max().item() < 3e-2 * max(1.0, want.abs().max().item())
+    # a prompt with one image: span rows take the tower's embeddings, no engram, image routing bias
+    toks, types, spans = expand_image_tokens([5, 9, cfg.image_token_id, 7, 3], cfg.image_token_id, [(n_h, n_w)],
+                                              cfg.vision.downsample_ratio)
+    span = spans[0]
+    assert len(toks) == 4 + len(span.types) and types.count(IMAGE) == 9 and span.start == 2
+    emb_span = vref.span_embeddings(span, patches)
+    mask = torch.tensor([t >= 0 for t in types])
+    embeds = torch.zeros(len(toks), cfg.dim)
+    embeds[mask] = emb_span
+    ref = Dsv41Reference(cfg, w)
+    st = ref.new_seq()
+    want_logits, _ = ref.forward(st, toks, image_mask=mask, embeds=embeds)
+    dev = Dsv41DeviceModel(cfg, DictWeights(w), max_rows=8, max_ctx=128)
+    outs = []
+    for i in range(0, len(toks), 8):
+        c = toks[i:i + 8]
+        rs = dev.make_rows([0], [len(c)])
+        dev.forward(rs, torch.tensor(c, dtype=torch.int32, device="cuda"), image_embeds=embeds[i:i + 8],
+                    is_image=mask[i:i + 8])
+        outs.append(dev.ws["logits"][:len(c)].cpu().clone())
+    got_logits = torch.cat(outs)
+    diff = (got_logits - want_logits).abs()
+    ref_max = max(1.0, want_logits.abs().max().item())
+    assert (diff > 3e-2 * ref_max).float().mean().item() < 0.01 and diff.max().item() < 0.25 * ref_max
