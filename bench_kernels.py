@@ -190,6 +190,59 @@ def make_cases(K, only):
             K.call("fb_gemm_tc_bf16", w, x, Kd, out, N, M, N, Kd, 0, status)
         cases.append(Case(name, N * Kd * 2, tcfn, f"M={M} N={N} K={Kd} FLOP={2 * M * N * Kd}"))
 
+    # ---- DSV41: fp4 experts (TP8 slice), sparse attention with sink, indexer scoring -----------------
+    if want("d4_expert"):
+        E, n, topk, I, D = 384, 1, 6, 320, 5120
+        w13 = torch.randint(0, 256, (E, 2, I, D // 2), dtype=torch.uint8, device=dev)
+        s13 = torch.full((E, 2, I, D // 32), 120, dtype=torch.uint8, device=dev)
+        w2 = torch.randint(0, 256, (E, D, I // 2), dtype=torch.uint8, device=dev)
+        s2 = torch.full((E, D, I // 32), 120, dtype=torch.uint8, device=dev)
+        x = torch.randn(n, D, device=dev)
+        hbuf = torch.zeros(n * topk, I, device=dev)
+        y = torch.zeros(n, D, device=dev)
+        wts = torch.rand(n, topk, device=dev)
+        idsets = [torch.randperm(E, device=dev)[:n * topk].to(torch.int32).view(n, topk).contiguous() for _ in range(64)]
+        st4 = {"i": 0}
+
+        def d4gu():
+            ids = idsets[st4["i"] % 64]; st4["i"] += 1
+            K.call("fb_d4_expert_gate_up", x, D, ids, wts, w13, s13, hbuf, n, topk, I, D, 10.0)
+
+        def d4dn():
+            ids = idsets[st4["i"] % 64]; st4["i"] += 1
+            K.call("fb_d4_expert_down", hbuf, ids, w2, s2, y, D, n, topk, I, D, 0)
+        cases.append(Case("d4_expert_gate_up.tp8.m1", topk * 2 * I * (D // 2 + D // 32), d4gu, f"6 experts x 2 x {I} x {D} e2m1"))
+        cases.append(Case("d4_expert_down.tp8.m1", topk * D * (I // 2 + I // 32), d4dn, f"6 experts x {D} x {I} e2m1"))
+    if want("d4_sparse_attn"):
+        n, Hl, hd, W, cap, ktop, ccap = 1, 8, 512, 128, 136, 512, 8192
+        ring = torch.randn(1, cap, hd, device=dev).to(torch.bfloat16)
+        comp = torch.randn(1, ccap, hd, device=dev).to(torch.bfloat16)
+        q = torch.randn(n, Hl * hd, device=dev)
+        idx = torch.randperm(ccap, device=dev)[:ktop].sort().values.to(torch.int32).view(n, ktop).contiguous()
+        sink = torch.zeros(Hl, device=dev)
+        freqs = torch.rand(32, device=dev)
+        meta = torch.zeros(n, 8, dtype=torch.int32, device=dev)
+        meta[:, 1] = 5000
+        out = torch.zeros(n, Hl * hd, device=dev)
+        at_o, at_ml = torch.zeros(n * Hl * 16 * hd, device=dev), torch.zeros(n * Hl * 16 * 2, device=dev)
+
+        def d4at():
+            K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta, 0, 0,
+                   float(hd ** -0.5), Hl, hd, out, Hl * hd, n, 16, at_o, at_ml, None, 0, 0, 0)
+        cases.append(Case("d4_sparse_attn.tp8.m1", (W + ktop) * hd * 2, d4at, f"{Hl} heads, {W}+{ktop} keys x {hd} bf16 (L2-resident)"))
+    if want("d4_index_score"):
+        n, IHl, ID, ccap = 1, 4, 128, 65536
+        kc = torch.randn(1, ccap, ID, device=dev).to(torch.bfloat16)
+        q = torch.randn(n, IHl * ID, device=dev)
+        wv = torch.rand(n, 8, device=dev)
+        meta = torch.zeros(n, 8, dtype=torch.int32, device=dev)
+        meta[:, 1] = ccap - 1
+        score = torch.zeros(n, ccap, device=dev)
+
+        def d4is():
+            K.call("fb_d4_index_score", q, IHl * ID, wv, 8, kc, ccap, meta, score, ccap, n, IHl, ID, 1, 0.01)
+        cases.append(Case("d4_index_score.tp8.m1.ctx64k", ccap * ID * 2, d4is, f"{IHl} heads x {ID}, {ccap} keys bf16"))
+
     # ---- MHC site -----------------------------------------------------------------------
     if want("hc_"):
         n, H, mix = 3, 4096, 24

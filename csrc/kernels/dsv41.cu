@@ -564,14 +564,14 @@ cand_mask_kernel(const int* __restrict__ blk, int ldb, int kb, int bs, uint8_t* 
 // conflict-free 4-byte reads of a staged bf16 key.  q is rotated on load, the output gets the
 // inverse rotation; softmax runs online with max over the real keys only, the sink logit
 // joins the denominator at the end, a row without keys yields zeros.
-constexpr int kAttnTile = 16;
+constexpr int kAttnTile = 8;
 template <int NJ>  // head_dim / 64
 __global__ void __launch_bounds__(256)
 sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ ring, int cap, int window,
                    const __nv_bfloat16* __restrict__ comp, int ccap, const int* __restrict__ idx, int ldi, int ktop,
                    const float* __restrict__ extra, int n_extra, const float* __restrict__ sink,
                    const float* __restrict__ freqs, int rd, const RowMeta* __restrict__ meta, int pos_off, int win_mode,
-                   float scale, int heads, float* __restrict__ out, int ldo, SplitBuf osp) {
+                   float scale, int heads, int nsplit, float* __restrict__ o_part, float* __restrict__ ml_part) {
     PDL_PROLOGUE();
     constexpr int HD = NJ * 64;
     __shared__ __align__(16) uint32_t ktile[kAttnTile][HD / 2];
@@ -603,20 +603,26 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
     float ov[NJ][2];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) ov[j][0] = ov[j][1] = 0.f;
-    for (int t0 = 0; t0 < L; t0 += kAttnTile) {
+    // this CTA's share of the key list (split-K over blockIdx.z; partials are merged by the second kernel)
+    const int sp = blockIdx.z;
+    const int per = ((L + nsplit - 1) / nsplit + kAttnTile - 1) / kAttnTile * kAttnTile;
+    const int k_lo = sp * per, k_hi = min(L, k_lo + per);
+    for (int t0 = k_lo; t0 < k_hi; t0 += kAttnTile) {
         __syncthreads();
         // stage up to kAttnTile keys
         for (int t = warp; t < kAttnTile; t += 8) {
             const int i = t0 + t;
             const __nv_bfloat16* src = nullptr;
             const float* srcf = nullptr;
-            if (i < nw) {
+            if (i >= k_hi) {
+                // past this CTA's share
+            } else if (i < nw) {
                 const int p = wpos - nw + 1 + i;
                 src = ring + ((size_t)m.slot * cap + (p % cap)) * HD;
             } else if (i < nw + ktop) {
                 const int c = idx[(size_t)r * ldi + (i - nw)];
                 if (c >= 0 && c < ccap) src = comp + ((size_t)m.slot * ccap + c) * HD;
-            } else if (i < L) {
+            } else if (i < k_hi) {
                 srcf = extra + (size_t)(i - nw - ktop) * HD;
             }
             if (lane == 0) kvalid[t] = (src || srcf) ? 1 : 0;
@@ -649,7 +655,7 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
 #pragma unroll
         for (int t = 0; t < kAttnTile; ++t) {
             sc[t] = warp_sum(sc[t]);
-            if (!kvalid[t] || t0 + t >= L) sc[t] = -INFINITY;
+            if (!kvalid[t] || t0 + t >= k_hi) sc[t] = -INFINITY;
             tmax = fmaxf(tmax, sc[t]);
         }
         const float mnew = fmaxf(mx, tmax);
@@ -671,19 +677,52 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
         mx = mnew;
     }
     if (!hv) return;
-    den += __expf(sink[h] - mx);
-    const float inv = 1.f / den;
+    // un-normalised partial of this split: o (already rotated keys), running max and denominator
+    const size_t pi = (((size_t)r * heads + h) * nsplit + sp);
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = 2 * lane + 64 * j;
-        const float a = ov[j][0] * inv, b = ov[j][1] * inv;
-        const float x0 = a * cs[j] + b * sn[j];   // inverse rotation
-        const float x1 = -a * sn[j] + b * cs[j];
-        float* o = out + (size_t)r * ldo + (size_t)h * HD + e;
+        o_part[pi * HD + e] = ov[j][0];
+        o_part[pi * HD + e + 1] = ov[j][1];
+    }
+    if (lane == 0) { ml_part[pi * 2] = mx; ml_part[pi * 2 + 1] = den; }
+}
+
+// Merge of the split-K partials: max-shifted sum, the sink logit joins the denominator, the output gets
+// the inverse rotation.  grid (heads, rows), 128 threads, one adjacent pair per thread step.
+__global__ void __launch_bounds__(128)
+sparse_attn_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, const float* __restrict__ sink,
+                         const float* __restrict__ freqs, int rd, const RowMeta* __restrict__ meta, int pos_off, int heads,
+                         int hd, int nsplit, float* __restrict__ out, int ldo, SplitBuf osp) {
+    PDL_PROLOGUE();
+    const int h = blockIdx.x, r = blockIdx.y;
+    const size_t p0 = ((size_t)r * heads + h) * nsplit;
+    float M = -1e30f;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(p0 + s) * 2]);
+    float den = __expf(sink[h] - M);
+    for (int s = 0; s < nsplit; ++s) den += ml_part[(p0 + s) * 2 + 1] * __expf(ml_part[(p0 + s) * 2] - M);
+    const float inv = 1.f / den;
+    const float pos = (float)(meta[r].pos + pos_off);
+    for (int e = 2 * threadIdx.x; e < hd; e += 2 * blockDim.x) {
+        float a = 0.f, b = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float w = __expf(ml_part[(p0 + s) * 2] - M);
+            a = fmaf(o_part[(p0 + s) * hd + e], w, a);
+            b = fmaf(o_part[(p0 + s) * hd + e + 1], w, b);
+        }
+        a *= inv; b *= inv;
+        float x0 = a, x1 = b;
+        if (e >= hd - rd) {
+            float sn, cs;
+            sincosf(pos * freqs[(e - (hd - rd)) >> 1], &sn, &cs);
+            x0 = a * cs + b * sn;    // inverse rotation
+            x1 = -a * sn + b * cs;
+        }
+        float* o = out + (size_t)r * ldo + (size_t)h * hd + e;
         o[0] = x0;
         o[1] = x1;
-        split_store(osp, r, h * HD + e, x0);
-        split_store(osp, r, h * HD + e + 1, x1);
+        split_store(osp, r, h * hd + e, x0);
+        split_store(osp, r, h * hd + e + 1, x1);
     }
 }
 
@@ -1097,33 +1136,41 @@ template <int NJ>
 static int launch_attn(const float* q, int ldq, const void* ring, int cap, int window, const void* comp, int ccap,
                        const int* idx, int ldi, int ktop, const float* extra, int n_extra, const float* sink,
                        const float* freqs, int rd, const void* meta, int pos_off, int win_mode, float scale, int heads,
-                       float* out, int ldo, SplitBuf osp, int n, cudaStream_t st) {
-    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n), 256, 0, st, q, ldq,
+                       int nsplit, float* o_part, float* ml_part, int n, cudaStream_t st) {
+    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n, (unsigned)nsplit), 256, 0, st, q, ldq,
               (const __nv_bfloat16*)ring, cap, window, (const __nv_bfloat16*)comp, ccap, idx, ldi, ktop, extra, n_extra, sink,
-              freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, out, ldo, osp);
+              freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, nsplit, o_part, ml_part);
     return FB_LAUNCH_CHECK();
 }
 
 // q [n][heads*hd] un-rotated; out gets the inverse rotation.  idx may be null (ktop = 0), extra may be null.
+// o_part: scratch of n * heads * nsplit * hd floats, ml_part: n * heads * nsplit * 2 floats.
 FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int64_t cap, int64_t window, const void* comp,
                              int64_t ccap, const int* idx, int64_t ldi, int64_t ktop, const float* extra, int64_t n_extra,
                              const float* sink, const float* freqs, int64_t rd, const void* meta, int64_t pos_off,
                              int64_t win_mode, float scale, int64_t heads, int64_t hd, float* out, int64_t ldo, int64_t n,
-                             void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+                             int64_t nsplit, float* o_part, float* ml_part, void* s_base, int64_t s_ld, int64_t s_plane,
+                             int64_t s_mask, cudaStream_t st) {
     const SplitBuf osp = mk_split(s_base, s_ld, s_plane, s_mask);
     if (!idx) ktop = 0;
     if (!extra) n_extra = 0;
+    if (nsplit < 1 || !o_part || !ml_part) return (int)cudaErrorInvalidValue;
+    int rc;
 #define D4_ATTN(NJ) launch_attn<NJ>(q, (int)ldq, ring, (int)cap, (int)window, comp, (int)ccap, idx, (int)ldi, (int)ktop, extra, \
-                                    (int)n_extra, sink, freqs, (int)rd, meta, (int)pos_off, (int)win_mode, scale, (int)heads, out, \
-                                    (int)ldo, osp, (int)n, st)
+                                    (int)n_extra, sink, freqs, (int)rd, meta, (int)pos_off, (int)win_mode, scale, (int)heads, \
+                                    (int)nsplit, o_part, ml_part, (int)n, st)
     switch (hd) {
-        case 64: return D4_ATTN(1);
-        case 128: return D4_ATTN(2);
-        case 256: return D4_ATTN(4);
-        case 512: return D4_ATTN(8);
+        case 64: rc = D4_ATTN(1); break;
+        case 128: rc = D4_ATTN(2); break;
+        case 256: rc = D4_ATTN(4); break;
+        case 512: rc = D4_ATTN(8); break;
         default: return (int)cudaErrorInvalidValue;
     }
 #undef D4_ATTN
+    if (rc) return rc;
+    FB_LAUNCH((sparse_attn_merge_kernel), dim3((unsigned)heads, (unsigned)n), 128, 0, st, o_part, ml_part, sink, freqs, (int)rd,
+              (const RowMeta*)meta, (int)pos_off, (int)heads, (int)hd, (int)nsplit, out, (int)ldo, osp);
+    return FB_LAUNCH_CHECK();
 }
 
 FB_API int fb_d4_route(const float* logits, int64_t ld, const float* bias, const float* bias_vl, const uint8_t* is_image,

@@ -221,6 +221,11 @@ class Dsv41DeviceModel:
         ws["q"] = self._z(M, self.Hl * hd)
         ws["o"] = Act(self.dev, M, self.Hl * hd)
         ws["low"] = Act(self.dev, M, self.Gl * cfg.o_lora_rank)
+        # split-K attention: keys of a row are spread over up to 16 CTAs per head tile
+        lmax = cfg.window_size + cfg.index_topk + max(cfg.dspark_block_size, 1)
+        self.at_split = max(1, min(16, (lmax + 31) // 32))
+        ws["at_o"] = self._z(M * self.Hl * self.at_split * hd)
+        ws["at_ml"] = self._z(M * self.Hl * self.at_split * 2)
         ws["y"] = self._z(M, d)
         ws["ckv"] = self._z(M, 2 * hd)
         ws["lat"] = self._z(M, hd)
@@ -434,7 +439,7 @@ class Dsv41DeviceModel:
         o = ws["o"]
         self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
                     cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
-                    self.Hl, hd, o.f, self.Hl * hd, n, *o.sp(1))
+                    self.Hl, hd, o.f, self.Hl * hd, n, self.at_split, ws["at_o"], ws["at_ml"], *o.sp(1))
         low = ws["low"]
         R_ = cfg.o_lora_rank
         self.gemv(L["wo_a"], o, low, n, self.Gl * R_, cfg.heads_per_group * hd, ldx=self.Hl * hd, group_rows=R_)
