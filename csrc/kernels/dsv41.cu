@@ -799,19 +799,44 @@ __device__ __forceinline__ void fp4x8_to_f32(uint32_t p, float* o) {
 }
 __device__ __forceinline__ float ue8m0_f32(uint8_t b) { return __uint_as_float((uint32_t)b << 23); }
 
-// dot of one packed fp4 row (K values, scales per 32) with x (shared memory, f32); whole warp.
+// Activations sit in shared memory "chunk-transposed": value k of a row of K is at
+// xs[(k % 16) * (K / 16 + 1) + k / 16], so the 32 lanes of a warp, which work on 32 different 16-value
+// chunks, read 32 consecutive words (no bank conflicts; a lane-major layout would be 16-way conflicted).
+__device__ __forceinline__ float fp4x16_dot(uint2 p, const float* __restrict__ xs, int c, int stride) {
+    float v[16];
+    fp4x8_to_f32(p.x, v);
+    fp4x8_to_f32(p.y, v + 8);
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) d = fmaf(v[i], xs[i * stride + c], d);
+    return d;
+}
+__device__ __forceinline__ void stage_transposed(float* __restrict__ xs, const float* __restrict__ x, int K) {
+    const int stride = K / 16 + 1;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[(k & 15) * stride + (k >> 4)] = x[k];
+}
+
+// dot of one packed fp4 row (K values, scales per 32) with x (shared memory, chunk-transposed); whole
+// warp.  Four 8-byte loads are in flight per lane before the first is consumed.
 __device__ __forceinline__ float fp4_row_dot(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ srow,
                                              const float* __restrict__ xs, int K, int lane) {
     float acc = 0.f;
-    for (int c = lane; c < K / 16; c += 32) {  // 16 values = 8 bytes per lane step
-        const uint2 p = *reinterpret_cast<const uint2*>(wrow + (size_t)c * 8);
-        float v[16];
-        fp4x8_to_f32(p.x, v);
-        fp4x8_to_f32(p.y, v + 8);
-        float d = 0.f;
+    const int nc = K / 16, stride = nc + 1;
+    int c = lane;
+    for (; c + 96 < nc; c += 128) {
+        uint2 p[4];
+        uint8_t sc[4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) d = fmaf(v[i], xs[c * 16 + i], d);
-        acc = fmaf(d, ue8m0_f32(srow[c >> 1]), acc);
+        for (int u = 0; u < 4; ++u) {
+            p[u] = *reinterpret_cast<const uint2*>(wrow + (size_t)(c + 32 * u) * 8);
+            sc[u] = srow[(c + 32 * u) >> 1];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc = fmaf(fp4x16_dot(p[u], xs, c + 32 * u, stride), ue8m0_f32(sc[u]), acc);
+    }
+    for (; c < nc; c += 32) {
+        const uint2 p = *reinterpret_cast<const uint2*>(wrow + (size_t)c * 8);
+        acc = fmaf(fp4x16_dot(p, xs, c, stride), ue8m0_f32(srow[c >> 1]), acc);
     }
     return warp_sum(acc);
 }
@@ -826,7 +851,7 @@ expert_gate_up_kernel(const float* __restrict__ x, int ldx, const int* __restric
     extern __shared__ float xs[];
     const int r = blockIdx.z, s = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = x[(size_t)r * ldx + k];
+    stage_transposed(xs, x + (size_t)r * ldx, K);
     __syncthreads();
     const int i = blockIdx.x * 8 + warp;
     if (i >= I) return;
@@ -850,20 +875,42 @@ __global__ void __launch_bounds__(256)
 expert_down_kernel(const float* __restrict__ hq, const int* __restrict__ idx, const uint8_t* __restrict__ w2,
                    const uint8_t* __restrict__ s2, float* __restrict__ y, int ldy, int topk, int I, int D, int accumulate) {
     PDL_PROLOGUE();
-    extern __shared__ float hs[];  // [topk][I]
+    extern __shared__ float hs[];  // [topk] chunk-transposed rows of I values
     const int r = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int k = threadIdx.x; k < topk * I; k += blockDim.x) hs[k] = hq[(size_t)r * topk * I + k];
+    const int hstride = 16 * (I / 16 + 1);
+    for (int s = 0; s < topk; ++s) stage_transposed(hs + (size_t)s * hstride, hq + ((size_t)r * topk + s) * I, I);
     __syncthreads();
     const int c = blockIdx.x * 8 + warp;
     if (c >= D) return;
+    // lanes walk the flattened (slot, 16-value chunk) list so that short rows still fill the warp
+    const int nc = I / 16, items = topk * nc;
     float acc = 0.f;
-    for (int s = 0; s < topk; ++s) {
-        const int e = idx[(size_t)r * topk + s];
-        const uint8_t* wr = w2 + ((size_t)e * D + c) * (I / 2);
-        const uint8_t* sr = s2 + ((size_t)e * D + c) * (I / 32);
-        acc += fp4_row_dot(wr, sr, hs + (size_t)s * I, I, lane);
+    for (int it = lane; it < items; it += 128) {
+        uint2 p[4];
+        float sc[4];
+        const float* xp[4];
+        int xc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = it + 32 * u;
+            p[u] = make_uint2(0u, 0u);
+            sc[u] = 0.f;
+            xp[u] = hs;
+            xc[u] = 0;
+            if (j < items) {
+                const int s = j / nc, ch = j % nc;
+                const int e = idx[(size_t)r * topk + s];
+                p[u] = *reinterpret_cast<const uint2*>(w2 + ((size_t)e * D + c) * (I / 2) + (size_t)ch * 8);
+                sc[u] = ue8m0_f32(s2[((size_t)e * D + c) * (I / 32) + (ch >> 1)]);
+                xp[u] = hs + (size_t)s * hstride;
+                xc[u] = ch;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc = fmaf(fp4x16_dot(p[u], xp[u], xc[u], nc + 1), sc[u], acc);
     }
+    acc = warp_sum(acc);
     if (lane == 0) {
         float* o = y + (size_t)r * ldy + c;
         *o = accumulate ? *o + acc : acc;
@@ -1185,7 +1232,7 @@ FB_API int fb_d4_expert_gate_up(const float* x, int64_t ldx, const int* idx, con
                                 const void* s13, float* h, int64_t n, int64_t topk, int64_t I, int64_t K, float lim,
                                 cudaStream_t st) {
     if (K % 32) return (int)cudaErrorInvalidValue;
-    const size_t sm = K * sizeof(float);
+    const size_t sm = 16 * (K / 16 + 1) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(expert_gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     FB_LAUNCH((expert_gate_up_kernel), dim3((unsigned)((I + 7) / 8), (unsigned)topk, (unsigned)n), 256, sm, st, x, (int)ldx, idx,
               wts, (const uint8_t*)w13, (const uint8_t*)s13, h, (int)topk, (int)I, (int)K, lim);
@@ -1195,7 +1242,7 @@ FB_API int fb_d4_expert_gate_up(const float* x, int64_t ldx, const int* idx, con
 FB_API int fb_d4_expert_down(const float* hq, const int* idx, const void* w2, const void* s2, float* y, int64_t ldy,
                              int64_t n, int64_t topk, int64_t I, int64_t D, int64_t accumulate, cudaStream_t st) {
     if (I % 32) return (int)cudaErrorInvalidValue;
-    const size_t sm = (size_t)topk * I * sizeof(float);
+    const size_t sm = (size_t)topk * 16 * (I / 16 + 1) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(expert_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     FB_LAUNCH((expert_down_kernel), dim3((unsigned)((D + 7) / 8), (unsigned)n), 256, sm, st, hq, idx, (const uint8_t*)w2,
               (const uint8_t*)s2, y, (int)ldy, (int)topk, (int)I, (int)D, (int)accumulate);
