@@ -493,19 +493,22 @@ class GlmDeviceModel:
         self.K.call("fb_dsa_select", ws["dsa_scores"], self.max_pools, ws["dsa_idx"], ldi, ws["dsa_cnt"], rs.meta,
                     n, ds.index_kpool, ds.select_pools)
         self.gemv(L["wk_abs"], qq, ws["dsa_qabs"], n, hl * DL, dk, group_rows=DL)
-        if self.dcp is None:
+        d_, n_ = (self.dcp[0], self.dcp[1]) if self.dcp is not None else (0, 1)
+        if DL == 512 and not self.kv_f32:   # tensor-core form (bf16 latents)
+            self.K.call("fb_dsa_attn_partial_tc", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
+                        float(dk ** -0.5))
+        else:
             self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, 0, 1,
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
                         float(dk ** -0.5), int(self.kv_f32))
+        if self.dcp is None:
             self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, self.nsplit, 1,
                         *ctx.sp(1))
         else:
             # decode context parallel: this rank attends over its own pages (page % n_dcp == d) of the
             # global top-k list; the merge kernel exchanges the partials with the peers and finishes
-            d_, n_, merge = self.dcp
-            self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
-                        float(dk ** -0.5), int(self.kv_f32))
+            merge = self.dcp[2]
             merge(ws["dsa_opart"], ws["dsa_ml"], ctx.f, n, hl, DL, self.nsplit, ctx.sp(1))
         self.gemv(L["wv_abs"], ctx, ov, n, hl * dv, DL, group_rows=dv, omask=1)
         self._out_gemv(L["o_proj"], ov, n, H, hl * dv)

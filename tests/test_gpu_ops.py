@@ -428,6 +428,51 @@ def test_dsa_attention(K, hl, DL, kv_f32, ntok, nshard):
     check("dsa attn", ctx, want, 2e-4)
 
 
+@pytest.mark.parametrize("hl,ntok,nsplit,nshard", [(64, 300, 4, 1), (64, 1024, 32, 1), (16, 130, 4, 4), (8, 70, 2, 1),
+                                                    (32, 2048, 32, 2)])
+def test_dsa_attention_tensor_core(K, hl, ntok, nsplit, nshard):
+    """mma.sync form of the sparse MLA attention (bf16 latents, DL = 512) against the fp32 statement."""
+    page, n, DL = 16, 3, 512
+    T = 2304
+    max_pages = T // page
+    g = torch.Generator().manual_seed(hl + ntok)
+    lat = torch.randn(T, DL, generator=g).bfloat16().float()
+    pt = torch.randperm(max_pages, generator=g).int().view(1, max_pages)
+    cache = torch.zeros(max_pages, page, DL)
+    cache[pt[0].long().repeat_interleave(page), torch.arange(T) % page] = lat
+    cache_d = dev(cache.bfloat16())
+    qabs = torch.randn(n, hl, DL, generator=g) * 0.3
+    W = ntok + 8
+    idx = torch.full((n, W), -1, dtype=torch.int32)
+    cnt = torch.tensor([ntok, max(1, ntok // 2), 1], dtype=torch.int32)
+    for i in range(n):
+        idx[i, :int(cnt[i])] = torch.randperm(T, generator=g)[:int(cnt[i])].int()
+    meta, _, _, _ = make_meta(K, [0], [n], [T - n])
+    scale = 0.11
+    parts_o, parts_ml = [], []
+    for sh in range(nshard):
+        o_part = torch.full((n, nsplit, hl, DL), float("nan"), device="cuda")
+        ml = torch.full((n, nsplit, hl, 2), float("nan"), device="cuda")
+        K.call("fb_dsa_attn_partial_tc", dev(qabs.reshape(n, -1)), cache_d, dev(idx), W, dev(cnt), o_part, ml, meta,
+               dev(pt), max_pages, page, n, hl, DL, nsplit, sh, nshard, scale)
+        ctx = torch.zeros(n, hl, DL, device="cuda")
+        lse = torch.zeros(n, hl, 2, device="cuda")
+        K.call("fb_dsa_attn_merge", o_part, ml, ctx, lse, n, hl, DL, nsplit, 1 if nshard == 1 else 0, None, 0, 0, 0)
+        parts_o.append(ctx)
+        parts_ml.append(lse)
+    if nshard > 1:
+        o_all = torch.stack(parts_o, 1).contiguous()
+        ml_all = torch.stack(parts_ml, 1).contiguous()
+        ctx = torch.zeros(n, hl, DL, device="cuda")
+        K.call("fb_dsa_attn_merge", o_all, ml_all, ctx, None, n, hl, DL, nshard, 1, None, 0, 0, 0)
+    want = torch.zeros(n, hl, DL)
+    for i in range(n):
+        ids = idx[i, :int(cnt[i])].long()
+        s = torch.einsum("hd,td->ht", qabs[i], lat[ids]) * scale
+        want[i] = torch.softmax(s, -1) @ lat[ids]
+    check("dsa attn tc", ctx, want, 6e-3, rtol=1e-2)   # probabilities are rounded to bf16 for the P.L product
+
+
 @pytest.mark.parametrize("m,N,K_,group", [(1, 48, 64, 0), (3, 4100, 512, 0), (8, 9600, 128, 0), (2, 16 * 64, 64, 64),
                                           (5, 777, 4096, 0), (3, 24896, 4096, 0)])
 def test_gemv_mma_bf16(K, m, N, K_, group):
