@@ -441,27 +441,40 @@ __global__ void dsa_attn_merge_kernel(const float* __restrict__ o_part, const fl
                                       float* __restrict__ ctx, float* __restrict__ lse_out, int hl, int DL,
                                       int nsplit, int normalise, SplitBuf osp) {
     PDL_PROLOGUE();
+    __shared__ float w_s[64];     // per-split weight e^{m_s - M} (0 for an empty split); nsplit <= 64
+    __shared__ float s_inv;
     const int r = blockIdx.y, h = blockIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(((size_t)r * nsplit + s) * hl + h) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float* ml = ml_part + (((size_t)r * nsplit + s) * hl + h) * 2;
-        if (ml[0] != -INFINITY) L += ml[1] * __expf(ml[0] - M);
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int s = threadIdx.x; s < nsplit; s += 32) M = fmaxf(M, ml_part[(((size_t)r * nsplit + s) * hl + h) * 2]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int s = threadIdx.x; s < nsplit; s += 32) {
+            const float* ml = ml_part + (((size_t)r * nsplit + s) * hl + h) * 2;
+            const float w = (ml[0] != -INFINITY) ? __expf(ml[0] - M) : 0.f;
+            w_s[s] = w;
+            L += ml[1] * w;
+        }
+        L = warp_sum(L);
+        if (threadIdx.x == 0) {
+            s_inv = normalise ? 1.f / (L + 1.1920929e-07f) : 1.f;
+            if (lse_out) {
+                lse_out[((size_t)r * hl + h) * 2] = M;
+                lse_out[((size_t)r * hl + h) * 2 + 1] = L;
+            }
+        }
     }
-    const float inv = normalise ? 1.f / (L + 1.1920929e-07f) : 1.f;
+    __syncthreads();
+    const float inv = s_inv;
     for (int d = threadIdx.x; d < DL; d += blockDim.x) {
         float o = 0.f;
+#pragma unroll 4
         for (int s = 0; s < nsplit; ++s) {
-            const float ms = ml_part[(((size_t)r * nsplit + s) * hl + h) * 2];
-            if (ms != -INFINITY) o += o_part[(((size_t)r * nsplit + s) * hl + h) * DL + d] * __expf(ms - M);
+            const float w = w_s[s];
+            if (w != 0.f) o = fmaf(o_part[(((size_t)r * nsplit + s) * hl + h) * DL + d], w, o);
         }
         ctx[((size_t)r * hl + h) * DL + d] = o * inv;
         split_store(osp, r, h * DL + d, o * inv);
-    }
-    if (lse_out && threadIdx.x == 0) {
-        lse_out[((size_t)r * hl + h) * 2] = M;
-        lse_out[((size_t)r * hl + h) * 2 + 1] = L;
     }
 }
 
@@ -564,6 +577,7 @@ FB_API int fb_dsa_attn_merge(const float* o_part, const float* ml_part, float* c
                              int64_t hl, int64_t DL, int64_t nsplit, int64_t normalise, void* s_base, int64_t s_ld,
                              int64_t s_plane, int64_t s_mask, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    if (nsplit > 64) return (int)cudaErrorInvalidValue;
     FB_LAUNCH((dsa_attn_merge_kernel), dim3((unsigned)hl, (unsigned)n), 128, 0, st, o_part, ml_part, ctx, lse_out, (int)hl,
                                                                            (int)DL, (int)nsplit, (int)normalise, osp);
     return FB_LAUNCH_CHECK();
