@@ -314,6 +314,13 @@ class GlmDeviceModel:
         Il += (-Il) % 8
         ws["moe_act"] = self._z(M, cfg.num_experts_per_tok, Il)
         ws["moe_act_s"] = torch.zeros(4, M * cfg.num_experts_per_tok, Il, dtype=torch.int16, device=self.dev)
+        self.moe_group_rows = 8      # more rows than this: group (row, slot) pairs by expert
+        if M > self.moe_group_rows:
+            npair = M * cfg.num_experts_per_tok
+            ws["moe_gpairs"] = torch.zeros(npair * 8, dtype=torch.int32, device=self.dev)
+            ws["moe_gexp"] = torch.zeros(npair, dtype=torch.int32, device=self.dev)
+            ws["moe_ngrp"] = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            ws["moe_ypair"] = torch.zeros(npair, cfg.hidden_size, device=self.dev)
         ws["h_final"] = self._z(M, H)
         ws["xh"] = self._act(H)
         ws["logits"] = self._z(M, self.lm_head.shape[0])
@@ -536,7 +543,19 @@ class GlmDeviceModel:
                     float(cfg.swiglu_limit))
         # routed experts write y, the shared expert's down projection adds to it and carries the
         # all-reduce (and the hyper-connection fold) in its epilogue
-        if H % 128 == 0 and Il % 128 == 0:
+        if H % 128 == 0 and Il % 128 == 0 and n > self.moe_group_rows:
+            # prefill-sized row counts: pairs grouped by expert, each expert's weights stream once per group
+            mas = ws["moe_act_s"]
+            ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
+            mg = n * topk
+            self.K.call("fb_moe_group", ws["moe_ids"], n * topk, 0, self.E_res, ws["moe_gpairs"], ws["moe_gexp"],
+                        ws["moe_ngrp"], mg)
+            self.K.call("fb_moe_gate_up_grp", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_wts"], ws["moe_gpairs"],
+                        ws["moe_gexp"], ws["moe_ngrp"], mas, ld_as, plane_as, mg, topk, Il, H, float(cfg.swiglu_limit))
+            self.K.call("fb_moe_down_grp", L["w2"], L["s2s"], mas, ld_as, plane_as, ws["moe_gpairs"], ws["moe_gexp"],
+                        ws["moe_ngrp"], ws["moe_ypair"], mg, Il, H)
+            self.K.call("fb_moe_sum_pairs", ws["moe_ypair"], ws["moe_ids"], ws["y"], H, n, topk, H, 0, self.E_res, 0)
+        elif H % 128 == 0 and Il % 128 == 0:
             mas = ws["moe_act_s"]
             ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
             self.K.call("fb_moe_gate_up_mma", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_ids"], ws["moe_wts"],

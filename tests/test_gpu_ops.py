@@ -554,6 +554,43 @@ def test_moe_experts_mma(K, n, E, topk, I, H):
     check("moe mma ep", out2, want2, 3e-3 * want2.abs().max().item())
 
 
+@pytest.mark.parametrize("n,E,topk,I,H,lo", [(20, 16, 4, 128, 256, 0), (64, 12, 8, 256, 512, 0), (33, 16, 4, 128, 256, 8)])
+def test_moe_experts_grouped_equals_per_pair(K, n, E, topk, I, H, lo):
+    """Expert-grouped kernels (prefill) give the same rows as the per-pair kernels (decode)."""
+    g = torch.Generator().manual_seed(17)
+    cnt = E - lo
+    q13, s13 = zip(*[R.quant_fp8_block(torch.randn(2 * I, H, generator=g) * 0.05) for _ in range(cnt)])
+    q2, s2 = zip(*[R.quant_fp8_block(torch.randn(H, I, generator=g) * 0.05) for _ in range(cnt)])
+    q13, s13, q2, s2 = dev(torch.stack(q13)), dev(torch.stack(s13)), dev(torch.stack(q2)), dev(torch.stack(s2))
+    x = torch.randn(n, H, generator=g)
+    ids = dev(torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(n)]).int())
+    wts = dev(torch.rand(n, topk, generator=g))
+    xs = dev(to_split(x))
+    npair = n * topk
+    asp = torch.zeros(4, npair, I, dtype=torch.int16, device="cuda")
+    want = torch.full((n, H), 0.5, device="cuda")
+    K.call("fb_moe_gate_up_mma", q13, s13, xs, H, n * H, ids, wts, asp, I, npair * I, n, topk, I, H, lo, cnt, 10.0)
+    K.call("fb_moe_down_mma", q2, s2, asp, I, npair * I, ids, want, H, n, topk, I, H, lo, cnt, 1, None, 0, 0, 0)
+    asp2 = torch.zeros_like(asp)
+    gp = torch.zeros(npair * 8, dtype=torch.int32, device="cuda")
+    ge = torch.zeros(npair, dtype=torch.int32, device="cuda")
+    ng = torch.zeros(1, dtype=torch.int32, device="cuda")
+    yp = torch.full((npair, H), float("nan"), device="cuda")
+    got = torch.full((n, H), 0.5, device="cuda")
+    K.call("fb_moe_group", ids, npair, lo, cnt, gp, ge, ng, npair)
+    K.call("fb_moe_gate_up_grp", q13, s13, xs, H, n * H, wts, gp, ge, ng, asp2, I, npair * I, npair, topk, I, H, 10.0)
+    K.call("fb_moe_down_grp", q2, s2, asp2, I, npair * I, gp, ge, ng, yp, npair, I, H)
+    K.call("fb_moe_sum_pairs", yp, ids, got, H, n, topk, H, lo, cnt, 1)
+    torch.cuda.synchronize()
+    local = ((ids >= lo) & (ids < lo + cnt)).flatten()
+    groups = gp.view(-1, 8)[:int(ng)]
+    members = groups[groups >= 0]
+    assert sorted(members.tolist()) == local.nonzero().flatten().tolist()      # every local pair in exactly one group
+    assert all(len(set(ids.flatten()[gr[gr >= 0]].tolist())) == 1 for gr in groups)   # one expert per group
+    check("grouped act", unsplit(asp2.cpu(), 1)[local.cpu()], unsplit(asp.cpu(), 1)[local.cpu()], 1e-6)
+    check("grouped out", got, want, 1e-4 * want.abs().max().item())
+
+
 @pytest.mark.parametrize("M,N,K_", [(5, 300, 256), (16, 128, 64), (64, 4096, 4096), (300, 1000, 512), (1, 129, 1536),
                                     (130, 256, 8192)])
 def test_gemm_tcgen05_bf16(K, M, N, K_):
