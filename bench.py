@@ -92,6 +92,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--prefill-rows", type=int, default=256, help="rows per prefill chunk")
     ap.add_argument("--fuse", default="full", choices=["full", "ar", "off"],
                     help="GEMV epilogue fusion: all-reduce + hyper-connection fold, all-reduce only, or separate kernels")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
@@ -131,7 +132,7 @@ def main():
                         fuse_epilogue=args.fuse)
     t0 = time.time()
     eng = GlmEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank=rank, world=world, device=dev,
-                    allreduce=allreduce, prefill_rows=64)
+                    allreduce=allreduce, prefill_rows=args.prefill_rows)
     torch.cuda.synchronize()
     t_load = time.time() - t0
     g = torch.Generator().manual_seed(0)

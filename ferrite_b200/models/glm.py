@@ -431,7 +431,9 @@ class GlmDeviceModel:
 
     def _reduce(self, y, n):
         if self.world > 1:
-            self.allreduce(y[:n])
+            step = max(1, getattr(self.allreduce, "max_elems", y[:n].numel()) // y.shape[1])
+            for r0 in range(0, n, step):   # the one-shot all-reduce takes a bounded payload per launch
+                self.allreduce(y[r0:min(n, r0 + step)])
 
     def _out_gemv(self, w, x, n, N, K, ldx=None, scales=None, accumulate=False):
         """The GEMV that ends a sublayer: ws['y'] = x . w^T (+ ws['y']) summed over the ranks.  When
