@@ -48,6 +48,50 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, unsigned long lo
     }
 }
 
+// Counter-based noise: one 32-bit hash per (seed, row key, global vocab index), the same on every
+// rank of a vocab-sliced head and on every replay of a captured step (the row key is the position).
+__device__ __forceinline__ uint32_t mix32(uint32_t h) {
+    h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+    return h;
+}
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t key, uint32_t idx) {
+    const uint32_t h = mix32(mix32(seed ^ (key * 0x9e3779b1u)) ^ (idx * 0x85ebca77u));
+    const float u = ((float)(h >> 8) + 0.5f) * (1.f / 16777216.f);   // (0, 1)
+    return -logf(-logf(u));
+}
+
+// First pass of temperature sampling by the Gumbel-max trick: argmax_i (logit_i / T + G_i) is a draw
+// from softmax(logits / T) (reference sampler: softmax(l / T) / Exp(1), ref_inference/model.py:1285-1292).
+__global__ void __launch_bounds__(256)
+gumbel_partial_kernel(const float* __restrict__ logits, int ld, unsigned long long* __restrict__ part, int V,
+                      int key_offset, float inv_t, uint32_t seed, const RowMeta* __restrict__ meta) {
+    PDL_PROLOGUE();
+    __shared__ unsigned long long wb[8];
+    const int r = blockIdx.y;
+    const uint32_t key = meta ? (uint32_t)meta[r].pos : (uint32_t)r;
+    const int per = (V + kSlices - 1) / kSlices;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
+    unsigned long long best = 0ull;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = logits[(size_t)r * ld + i] * inv_t + gumbel_noise(seed, key, (uint32_t)(i + key_offset));
+        if (v == v) {
+            const unsigned long long k = amax_key(v, i + key_offset);
+            best = k > best ? k : best;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
+        best = t > best ? t : best;
+    }
+    if ((threadIdx.x & 31) == 0) wb[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = wb[w] > best ? wb[w] : best;
+        part[(size_t)r * kSlices + blockIdx.x] = best;
+    }
+}
+
 __global__ void argmax_final_kernel(const unsigned long long* __restrict__ part, int* __restrict__ ids,
                                     float* __restrict__ vals, int id_stride, int vocab_offset) {
     PDL_PROLOGUE();
@@ -146,6 +190,20 @@ FB_API int fb_argmax_partial(const float* logits, int64_t ld, void* part, int64_
                              cudaStream_t st) {
     FB_LAUNCH((argmax_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V,
               (int)vocab_offset);
+    return FB_LAUNCH_CHECK();
+}
+
+// Temperature sampling (Gumbel-max).  With `final` != 0 the ids are written here; with 0 only the
+// partial keys are produced (global indices), to be merged across ranks by fb_argmax_xchg.
+// meta (optional): row metadata, the row's position keys the noise; otherwise the row index does.
+FB_API int fb_sample_gumbel(const float* logits, int64_t ld, void* part, int* ids, int64_t n, int64_t V,
+                            int64_t id_stride, int64_t vocab_offset, float temperature, int64_t seed, const void* meta,
+                            int64_t final, cudaStream_t st) {
+    if (!(temperature > 0.f)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((gumbel_partial_kernel), dim3(kSlices, (unsigned)n), 256, 0, st, logits, (int)ld, (unsigned long long*)part, (int)V,
+              (int)vocab_offset, 1.f / fmaxf(temperature, 1e-5f), (uint32_t)seed, (const RowMeta*)meta);
+    if (final)
+        FB_LAUNCH((argmax_final_kernel), n, 32, 0, st, (const unsigned long long*)part, ids, (float*)nullptr, (int)id_stride, 0);
     return FB_LAUNCH_CHECK();
 }
 

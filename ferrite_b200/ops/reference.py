@@ -320,3 +320,31 @@ def sparse_attn_partial(q, k, v, idx, owned: torch.Tensor):
     empty = (idx2 >= 0).sum(1) == 0
     lse = torch.where(empty.unsqueeze(1), torch.full_like(lse, float("-inf")), lse)
     return o, lse
+
+
+# ---- temperature sampling (Gumbel-max with a counter-based hash) ----------------------------
+def _mix32(h: torch.Tensor) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    h = h ^ (h >> 16)
+    h = (h * 0x85EBCA6B) & m
+    h = h ^ (h >> 13)
+    h = (h * 0xC2B2AE35) & m
+    return h ^ (h >> 16)
+
+
+def gumbel_noise(seed: int, keys: torch.Tensor, V: int, offset: int = 0) -> torch.Tensor:
+    """[len(keys), V] noise G = -log(-log u), u from a 32-bit hash of (seed, row key, global index)."""
+    m = 0xFFFFFFFF
+    idx = (torch.arange(V, dtype=torch.int64) + offset).unsqueeze(0)
+    k = (keys.to(torch.int64).unsqueeze(1) * 0x9E3779B1) & m
+    h = _mix32(_mix32((seed & m) ^ k) ^ ((idx * 0x85EBCA77) & m))
+    u = ((h >> 8).float() + 0.5) * (1.0 / 16777216.0)
+    return -torch.log(-torch.log(u))
+
+
+def sample_gumbel(logits, temperature: float, seed: int, keys: torch.Tensor):
+    """argmax(logits / T + G): one draw per row from softmax(logits / T); T = 0 is plain argmax."""
+    if temperature == 0:
+        return argmax_first(logits)
+    z = logits.float() * (1.0 / max(temperature, 1e-5)) + gumbel_noise(seed, keys, logits.shape[-1])
+    return argmax_first(z)

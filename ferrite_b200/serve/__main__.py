@@ -99,6 +99,11 @@ def _build_dsv41(args, tok):
     else:
         from ..models.dsv41_weights import random_weights
         src = DictWeights(random_weights(cfg, 0))
+    if args.backend == "cpu":
+        from ..models.dsv41_ref import Dsv41Reference
+        from ..models.dsv41_weights import tensor_specs
+        w = {k: src.get(k) for k in tensor_specs(cfg)}
+        return SingleFlight(_Dsv41RefStep(Dsv41Reference(cfg, w), spec=args.mtp > 1)), tok, 0, 1
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     allreduce = None
@@ -113,6 +118,43 @@ def _build_dsv41(args, tok):
         from .tp_pool import ReplicatedEngine, make_control_group
         serve_eng = ReplicatedEngine(serve_eng, rank, world, make_control_group())
     return serve_eng, tok, rank, world
+
+
+class _Dsv41RefStep:
+    """StepEngine over the fp32 DSV41 golden model (CPU): plain greedy steps or DSpark speculation."""
+
+    def __init__(self, ref, spec: bool):
+        self.ref, self.spec = ref, spec and ref.cfg.dspark_block_size > 0
+
+    def start(self, prompt):
+        from ..ops.reference import argmax_first
+        self.st = self.ref.new_seq()
+        logits, mh = self.ref.forward(self.st, prompt)
+        if self.spec:
+            self.ref.dspark_seed(self.st, mh, 0)
+        self.last = int(argmax_first(logits[-1:])[0])
+        return self.last, 0
+
+    def step(self):
+        from ..ops.reference import argmax_first
+        from ..spec import spec_accept
+        ref, st = self.ref, self.st
+        if not self.spec:
+            logits, _ = ref.forward(st, [self.last])
+            self.last = int(argmax_first(logits[-1:])[0])
+            return [self.last]
+        last_pos = st.pos - 1
+        drafts, _, _ = ref.dspark_draft(st, self.last, last_pos)
+        snap = st.clone()
+        block = [self.last] + drafts
+        logits, _ = ref.forward(st, block)
+        judges = argmax_first(logits).tolist()
+        m = spec_accept(drafts, judges, anchor_is_in_block=False)
+        self.st = st = snap
+        _, mh = ref.forward(st, block[:m + 1])
+        ref.dspark_seed(st, mh, last_pos + 1)
+        self.last = judges[m]
+        return judges[:m + 1]
 
 
 class _GlmStep:

@@ -673,3 +673,36 @@ def test_bounded_wait_reports_timeout_and_context_survives(K):
     assert status[0].item() == 0
     x = torch.arange(8, device="cuda").sum().item()    # the context still runs kernels
     assert x == 28
+
+
+def test_gumbel_sampling_matches_reference_and_distribution(K):
+    n, V = 4, 5000
+    logits = rnd(n, V, seed=3) * 2.0
+    keys = torch.tensor([17, 18, 900, 5])
+    meta = torch.zeros(n, 8, dtype=torch.int32)
+    meta[:, 1] = keys
+    part = torch.zeros(n * 64, dtype=torch.int64, device="cuda")
+    ids = torch.zeros(n, dtype=torch.int32, device="cuda")
+    K.call("fb_sample_gumbel", dev(logits), V, part, ids, n, V, 1, 0, 0.7, 1234, dev(meta), 1)
+    want = R.sample_gumbel(logits, 0.7, 1234, keys)
+    assert ids.cpu().tolist() == want.tolist()
+    # vocab-sliced: partial keys of two halves merge to the same draw
+    half = V // 2
+    p0 = torch.zeros(n * 64, dtype=torch.int64, device="cuda")
+    p1 = torch.zeros(n * 64, dtype=torch.int64, device="cuda")
+    K.call("fb_sample_gumbel", dev(logits[:, :half].contiguous()), half, p0, None, n, half, 1, 0, 0.7, 1234, dev(meta), 0)
+    K.call("fb_sample_gumbel", dev(logits[:, half:].contiguous()), half, p1, None, n, half, 1, half, 0.7, 1234, dev(meta), 0)
+    m64 = (1 << 64) - 1
+    for r in range(n):
+        keys_r = [int(k) & m64 for k in p0.view(n, 64)[r].tolist() + p1.view(n, 64)[r].tolist()]
+        assert 0xFFFFFFFF - (max(keys_r) & 0xFFFFFFFF) == int(want[r])
+    # draws over many positions follow softmax(logits / T)
+    V2, draws = 6, 4000
+    lg = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, 1.5]]).repeat(draws, 1)
+    meta2 = torch.zeros(draws, 8, dtype=torch.int32)
+    meta2[:, 1] = torch.arange(draws)
+    part2 = torch.zeros(draws * 64, dtype=torch.int64, device="cuda")
+    ids2 = torch.zeros(draws, dtype=torch.int32, device="cuda")
+    K.call("fb_sample_gumbel", dev(lg), V2, part2, ids2, draws, V2, 1, 0, 1.0, 7, dev(meta2), 1)
+    freq = torch.bincount(ids2.cpu().long(), minlength=V2).float() / draws
+    assert (freq - torch.softmax(lg[0], -1)).abs().max().item() < 0.03

@@ -108,3 +108,13 @@ def test_http_routes_and_streaming():
         assert set(st) == {"engine", "radix", "hicache"} and st["engine"]["tokens_committed"] >= 18
         assert c.post("/shutdown").json() == {"status": "shutting_down"}
     driver.shutdown()
+
+
+def test_cli_dsv41_cpu_backend_generates(capsys):
+    """One-shot generation through the CLI with the DSV41 golden model on CPU (plain and DSpark)."""
+    from ferrite_b200.serve.__main__ import main
+    outs = []
+    for mtp in ("1", "3"):
+        assert main(["--model", "dsv41-tiny", "--backend", "cpu", "--prompt", "hi", "--max-tokens", "6", "--mtp", mtp]) == 0
+        outs.append(capsys.readouterr().out)
+    assert outs[0] == outs[1] and len(outs[0]) > 0       # speculation does not change the text
