@@ -706,3 +706,42 @@ def test_gumbel_sampling_matches_reference_and_distribution(K):
     K.call("fb_sample_gumbel", dev(lg), V2, part2, ids2, draws, V2, 1, 0, 1.0, 7, dev(meta2), 1)
     freq = torch.bincount(ids2.cpu().long(), minlength=V2).float() / draws
     assert (freq - torch.softmax(lg[0], -1)).abs().max().item() < 0.03
+
+
+def test_device_runtime_fork_join_capture_replay(K):
+    """Side-stream fork/join inside a captured step, replayed as a graph, with pinned staging."""
+    import ctypes
+    from ferrite_b200.utils.devrt import DeviceRuntime
+    rt = DeviceRuntime(0, n_side=2)
+    a, b = torch.full((4096,), 1.0, device="cuda"), torch.full((4096,), 2.0, device="cuda")
+    c, d = torch.zeros(4096, device="cuda"), torch.zeros(4096, device="cuda")
+    torch.cuda.synchronize()
+    main, side = rt.stream(-1), rt.stream(0)
+    assert main and side and main != side
+
+    def step():
+        K.call("fb_add", a, b, c, 4096, stream=main)          # c = a + b          (main)
+        rt.fork(0)
+        K.call("fb_add", c, c, d, 4096, stream=side)          # d = 2c             (side, after c)
+        K.call("fb_add", a, a, a, 4096, stream=main)          # a = 2a             (main, concurrent)
+        rt.join(0)
+        K.call("fb_add", d, a, c, 4096, stream=main)          # c = d + a          (main, after both)
+
+    rt.capture_begin()
+    step()
+    g = rt.capture_end()
+    want_a, want_c = 1.0, 0.0
+    for _ in range(3):
+        rt.graph_launch(g)
+        want_c = 2 * (want_a + 2.0) + 2 * want_a
+        want_a *= 2
+    rt.sync()
+    assert a[0].item() == want_a and c[7].item() == want_c
+    host = rt.pinned_alloc(4096 * 4)
+    rt.copy(host, c.data_ptr(), 4096 * 4)
+    rt.sync()
+    got = (ctypes.c_float * 4096).from_address(host)
+    assert got[0] == want_c and got[4095] == want_c
+    rt.pinned_free(host)
+    rt.graph_free(g)
+    rt.close()
