@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "golden.h"
+#include "golden_dsv41.h"
 
 namespace py = pybind11;
 using farr = py::array_t<float, py::array::c_style | py::array::forcecast>;
@@ -97,5 +98,47 @@ void bind_golden(py::module_& m) {
     m.def("argmax_first", [](farr x) { return golden::argmax_first(x.data(), (int)x.size()); });
     m.def("spec_accept", [](std::vector<int64_t> drafts, std::vector<int64_t> judges, bool anchor_in_block) {
         return golden::spec_accept(drafts.data(), (int)drafts.size(), judges.data(), (int)judges.size(), anchor_in_block);
+    });
+    // ---- DSV41 family ----------------------------------------------------------------------------
+    m.def("d4_e4m3_round", [](farr x) {
+        farr out(std::vector<py::ssize_t>(x.shape(), x.shape() + x.ndim()));
+        for (py::ssize_t i = 0; i < x.size(); ++i) out.mutable_data()[i] = golden_d4::e4m3_round(x.data()[i]);
+        return out;
+    });
+    m.def("d4_e2m1_round", [](farr x) {
+        farr out(std::vector<py::ssize_t>(x.shape(), x.shape() + x.ndim()));
+        for (py::ssize_t i = 0; i < x.size(); ++i) out.mutable_data()[i] = golden_d4::e2m1_round(x.data()[i]);
+        return out;
+    });
+    m.def("d4_fp8_act_roundtrip", [](farr x, int block) {
+        farr out(std::vector<py::ssize_t>(x.shape(), x.shape() + x.ndim()));
+        std::copy(x.data(), x.data() + x.size(), out.mutable_data());
+        golden_d4::fp8_act_roundtrip(out.mutable_data(), (size_t)x.size(), block);
+        return out;
+    });
+    m.def("d4_fp4_act_roundtrip", [](farr x, int block, bool e4m3_scale) {
+        farr out(std::vector<py::ssize_t>(x.shape(), x.shape() + x.ndim()));
+        std::copy(x.data(), x.data() + x.size(), out.mutable_data());
+        golden_d4::fp4_act_roundtrip(out.mutable_data(), (size_t)x.size(), block, e4m3_scale);
+        return out;
+    });
+    m.def("d4_sparse_attn_sink", [](farr q, farr kv, farr sink, float scale) {
+        const int H = (int)q.shape(0), d = (int)q.shape(1), n = (int)kv.shape(0);
+        farr out = make({H, d});
+        golden_d4::sparse_attn_sink(q.data(), kv.data(), sink.data(), out.mutable_data(), H, d, n, scale);
+        return out;
+    });
+    m.def("d4_route", [](farr logits, farr bias, int topk, float route_scale) {
+        const int n = (int)logits.shape(0), E = (int)logits.shape(1);
+        iarr idx({(py::ssize_t)n, (py::ssize_t)topk});
+        farr wts = make({n, topk});
+        golden_d4::route_sqrtsoftplus(logits.data(), bias.data(), n, E, topk, route_scale, idx.mutable_data(), wts.mutable_data());
+        return py::make_tuple(wts, idx);
+    });
+    m.def("d4_candidate_blocks", [](farr score, int clen, int topk_blocks, int bs) {
+        const int n = (int)score.shape(0);
+        py::array_t<uint8_t> keep({(py::ssize_t)n});
+        golden_d4::candidate_blocks(score.data(), n, clen, topk_blocks, bs, keep.mutable_data());
+        return keep;
     });
 }

@@ -160,3 +160,33 @@ def test_checkpoint_roundtrip_is_exact(tmp_path):
                  "layers.3.attn.compressor.wkv.weight", "layers.2.hc_attn_fn", "embed.weight", "mtp.1.markov_head.head.weight"):
         assert src.has(name) and torch.equal(src.get(name), w[name]), name
     assert not src.has("layers.0.attn.compressor.wkv.weight")
+
+
+def test_cpp_golden_matches_python_statement():
+    """The C++ golden ops of the DSV41 family against the PyTorch statements."""
+    from ferrite_b200 import build
+    build.build_runtime()
+    from ferrite_b200 import _runtime as rt
+    from ferrite_b200.models.dsv41_ref import sparse_attn_rows
+    G = rt.golden if hasattr(rt, "golden") else rt
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(6, 128, generator=g) * torch.logspace(-4, 2, 6).unsqueeze(1)
+    assert torch.equal(torch.from_numpy(G.d4_e4m3_round(x.numpy())), Q.e4m3_round(x))
+    assert torch.equal(torch.from_numpy(G.d4_e2m1_round(x.numpy())), Q.e2m1_decode(Q.e2m1_encode(x)))
+    assert torch.equal(torch.from_numpy(G.d4_fp8_act_roundtrip(x.numpy(), 32)), Q.fp8_act_roundtrip(x, 32))
+    assert torch.equal(torch.from_numpy(G.d4_fp4_act_roundtrip(x.numpy(), 32, False)), Q.fp4_act_roundtrip(x, 32))
+    assert torch.equal(torch.from_numpy(G.d4_fp4_act_roundtrip(x.numpy(), 16, True)), Q.fp4_act_roundtrip(x, 16, "e4m3"))
+    q, kv, sink = torch.randn(4, 64, generator=g), torch.randn(9, 64, generator=g), torch.randn(4, generator=g)
+    got = torch.from_numpy(G.d4_sparse_attn_sink(q.numpy(), kv.numpy(), sink.numpy(), 0.125))
+    assert torch.allclose(got, sparse_attn_rows(q, kv, sink, 0.125), atol=1e-5)
+    assert not torch.from_numpy(G.d4_sparse_attn_sink(q.numpy(), kv[:0].numpy(), sink.numpy(), 0.125)).any()
+    cfg, m = _model()
+    xin = torch.randn(5, cfg.dim, generator=g)
+    wts, idx = m.route(xin, "layers.0.ffn.", 2, None)
+    logits = xin @ m.w["layers.0.ffn.gate.weight"].t()
+    w2, i2 = G.d4_route(logits.numpy(), m.w["layers.0.ffn.gate.bias"].numpy(), 2, cfg.route_scale)
+    assert torch.equal(torch.from_numpy(i2), idx) and torch.allclose(torch.from_numpy(w2), wts, atol=1e-5)
+    score = torch.tensor([0.1, 0.2, 5.0, 4.0, 0.0, 0.3, -1e30, -1e30])
+    keep = torch.from_numpy(G.d4_candidate_blocks(score.numpy(), 6, 2, 2)).bool()
+    assert keep.tolist() == select_candidate_blocks(score.masked_fill(torch.arange(8) >= 6, float("-inf")).unsqueeze(0),
+                                                    torch.tensor([6]), 2, 2)[0].tolist()
