@@ -1092,7 +1092,7 @@ FB_API int fb_d4_hc_pre(const float* R, float* acc, const float* scale, const fl
                         float* xc_out, int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
                         void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, const float* part, int* part_n,
                         int64_t part_ld, cudaStream_t st) {
-    if (mult != 4 || (part_n && n > 8)) return (int)cudaErrorInvalidValue;
+    if (mult != 4 || (part_n && n > 64)) return (int)cudaErrorInvalidValue;
     const size_t sm = (32 + H) * sizeof(float);
     if (sm > 48 * 1024) cudaFuncSetAttribute(hc_pre_offset_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     FB_LAUNCH((hc_pre_offset_kernel), n, 512, sm, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,

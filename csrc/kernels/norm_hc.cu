@@ -379,7 +379,7 @@ FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const
                            int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
                            const float* part, int* part_n, int64_t part_ld, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    if (mult != 4 || (H % 4) || H / 4 > 1024 || (part_n && n > 8)) return (int)cudaErrorInvalidValue;
+    if (mult != 4 || (H % 4) || H / 4 > 1024 || (part_n && n > 64)) return (int)cudaErrorInvalidValue;
     const int threads = (int)(((H / 4) + 31) / 32 * 32);
     FB_LAUNCH((hc_pre_apply_kernel), n, threads, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
                                                (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp, part, part_n, (int)part_ld);

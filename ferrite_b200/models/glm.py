@@ -102,6 +102,8 @@ class GlmDeviceModel:
                 from ..parallel.symm import FusedGemvAllReduce
                 self.fused = FusedGemvAllReduce(self.dev, 0, 1)
         self.dcp = None          # (d, n_dcp, DcpAttentionMerge): decode-context-parallel attention
+        self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
+                                 # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
         self._fold_next = None   # (fn_next,) while a hyper-connection site's sublayer runs
         self._folded = False
         self.max_rows = max_rows
@@ -447,8 +449,8 @@ class GlmDeviceModel:
         xa = x if isinstance(x, Act) else None
         ldx = ldx if ldx is not None else (xa.ld if xa else K)
         kb = 128 if scales is not None else 64
-        ok = (self.fused is not None and xa is not None and xa.s is not None and n <= 8 and K % kb == 0
-              and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or n * N <= self.fused.max_elems)
+        ok = (self.fused is not None and xa is not None and xa.s is not None and n <= self.fused_rows and K % kb == 0
+              and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or 8 * N <= self.fused.max_elems)
               and (self.world > 1 or fold is not None))
         if not ok:
             self.gemv(w, x, ws["y"], n, N, K, ldx=ldx, scales=scales, accumulate=accumulate)
@@ -590,7 +592,7 @@ class GlmDeviceModel:
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
                     x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
                     float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3),
-                    *(self.fused.partials() if self.fused is not None and n <= 8 else (None, None, 0)))
+                    *(self.fused.partials() if self.fused is not None and n <= self.fused_rows else (None, None, 0)))
 
     def _hc_post_mix(self, fn_next, n, first=False):
         """hc_post of the finished site fused with the mix dots of the next one; the residual

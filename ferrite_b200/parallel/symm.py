@@ -131,8 +131,11 @@ class FusedGemvAllReduce:
         self.max_elems = max_rows * n_max
         self.epoch = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
-        self.part = torch.zeros(8 * 25 * self.max_tiles, dtype=torch.float32, device=device)
-        self.part_n = torch.zeros(8, dtype=torch.int32, device=device)
+        # mix-dot partials and tile counts for up to `part_rows` rows: a forward of more than 8 rows calls the
+        # kernel once per 8-row window, each window with its own slice
+        self.part_rows = 64
+        self.part = torch.zeros(self.part_rows * 25 * self.max_tiles, dtype=torch.float32, device=device)
+        self.part_n = torch.zeros(self.part_rows, dtype=torch.int32, device=device)
         self.ticket = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
         # tiles per published group; the whole grid by default: system-scope fences are the expensive part
         # (measured on 2 GPUs, GLM decode step: 16 -> 11.99 ms, 64 -> 11.31, 128 -> 11.02, whole grid -> 10.88)
@@ -149,15 +152,25 @@ class FusedGemvAllReduce:
 
     def __call__(self, W, scales, xs_ptr, xs_ld: int, xs_plane: int, y, ldo: int, m: int, N: int, K: int,
                  accumulate: bool, store_y: bool, fold=None):
-        """fold = (Rin, Rout, post, comb, fn_or_None, acc, mix) or None."""
+        """fold = (Rin, Rout, post, comb, fn_or_None, acc, mix) or None.  m may exceed 8 (up to part_rows):
+        the kernel then runs once per 8-row window on row-offset pointers."""
         rin = rout = post = comb = fn = acc = None
         mix = 0
         if fold is not None:
             rin, rout, post, comb, fn, acc, mix = fold
-        self.K.call("fb_gemv_ar", W, scales, xs_ptr, xs_ld, xs_plane, y, ldo, m, N, K, int(accumulate), int(store_y),
-                    self._sp, self._fp, self.epoch, self.ticket, self.status, self.rank, self.world, self.max_elems,
-                    self.max_spins, self.group, rin, rout, post, comb, fn, acc, mix, self.part, self.part_n)
-        self.calls += 1
+        assert m <= self.part_rows
+
+        def off(t, elems, size=4):
+            return None if t is None else ctypes.c_void_p(t.data_ptr() + elems * size)
+
+        for r0 in range(0, m, 8):
+            mm = min(8, m - r0)
+            self.K.call("fb_gemv_ar", W, scales, off(xs_ptr, r0 * xs_ld, 2), xs_ld, xs_plane, off(y, r0 * ldo), ldo, mm, N, K,
+                        int(accumulate), int(store_y), self._sp, self._fp, self.epoch, self.ticket, self.status,
+                        self.rank, self.world, self.max_elems, self.max_spins, self.group,
+                        off(rin, r0 * 4 * N), off(rout, r0 * 4 * N), off(post, r0 * 4), off(comb, r0 * 16), fn,
+                        off(acc, r0 * 25), mix, off(self.part, r0 * 25 * self.max_tiles), off(self.part_n, r0))
+            self.calls += 1
 
     def partials(self):
         """(part, part_n, part_ld) arguments for the hc_pre kernel that consumes the mix-dot partials."""
