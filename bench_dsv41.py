@@ -1,0 +1,95 @@
+"""DSV41 decode step time at production dimensions on a LAYER-REDUCED model (the full 40-layer model is
+475 GiB and needs TP >= 4):
+
+    python bench_dsv41.py --layers 4 --steps 50
+
+Builds `--layers` backbone layers with the production widths (dim 5120, 64 heads x 512, 384 fp4 experts,
+window 128, compressed KV + indexer; one layer of every attention flavour), random weights generated on
+the device, prefills a short prompt and times graph-replayed decode steps with CUDA events.  The JSON
+line gives ms per step, ms per layer and the 40-layer extrapolation, which is an ESTIMATE (labelled as
+such), not a measurement of the full model.  Reference number for orientation: 6.15 ms/step at TP=8
+on B300 (docs/agent/unified-engine-battle-plan.md:4).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from dataclasses import replace
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--prompt-len", type=int, default=300)
+    ap.add_argument("--experts", type=int, default=384)
+    ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
+    args = ap.parse_args()
+    from ferrite_b200.engine.dsv41_engine import Dsv41Engine
+    from ferrite_b200.models.dsv41_config import Dsv41Config
+    from ferrite_b200.models.dsv41_synth import SyntheticDsv41Source
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    allreduce = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from ferrite_b200.parallel.collective import make_allreduce
+        allreduce = make_allreduce(dev, rank, world, max_elems=64 * 8192, kind="p2p")
+    L = args.layers
+    assert L >= 4
+    # one window-only layer, a ratio-2 source, a ratio-1 source (candidate source), an inheriting ratio-1 layer
+    ratios = [0, 2, 1] + [1] * (L - 3)
+    n_mtp = 3 if args.spec else 0
+    cfg = replace(Dsv41Config(), n_layers=L, n_mtp_layers=n_mtp, compress_ratios=tuple(ratios + [0] * n_mtp),
+                  kv_source_layers=(1, 2), index_source_layers=(1, 2) + ((L - 1,) if L > 4 else ()),
+                  candidate_source_layer=2, engram_layer_ids=(), engram_num_embeddings=(),
+                  dspark_target_layer_ids=tuple(range(max(0, L - 3), L)) if args.spec else (),
+                  dspark_block_size=5 if args.spec else 0, n_routed_experts=args.experts).validate()
+    eng = Dsv41Engine(cfg, SyntheticDsv41Source(cfg, dev), rank, world, dev, allreduce, max_ctx=args.prompt_len + 1024)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+    eng.prefill(prompt)
+    step = (lambda: eng.spec_step()) if args.spec else (lambda: eng.step_plain())
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    toks = 0
+    e0.record()
+    for _ in range(args.steps):
+        r = step()
+        toks += len(r) if isinstance(r, list) else 1
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "dsv41_decode_ms_per_step_layer_reduced", "value": round(ms, 4), "unit": "ms",
+                          "higher_is_better": False, "n_gpus": world, "steps": args.steps, "layers": L,
+                          "ms_per_layer": round(ms / L, 4),
+                          "estimate_40_layers_ms": round(ms / L * 40, 3), "estimate_note": "extrapolated, not measured",
+                          "tokens_per_step": round(toks / args.steps, 3), "dtype": "bf16 dense / e2m1 experts",
+                          "data": "synthetic", "config": {"dim": cfg.dim, "heads": cfg.n_heads, "experts": cfg.n_routed_experts,
+                                                          "topk": cfg.n_activated_experts, "context": args.prompt_len,
+                                                          "parallelism": f"tp{world}", "spec": bool(args.spec)}}))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
