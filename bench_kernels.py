@@ -116,6 +116,33 @@ def make_cases(K, only):
             f(ws[i % reps], sc, xs, Kd, m * Kd, out, N, m, N, Kd, False, True, fd)
         cases.append(Case(name, N * Kd * esz + (24 * 4 * N * 4 if fold else 0), fn, f"N={N} K={Kd} m={m} fold={fold}"))
 
+    def tc_gemv_case(name, N, Kd, m, nsplit):
+        """TMA + tcgen05 split-K GEMV (decode rows), hi + lo activation planes."""
+        if not want(name):
+            return
+        reps = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        x = torch.randn(16, Kd, device=dev)
+        xs = split_buf(x)
+        out = torch.zeros(m, N, device=dev)
+        ws = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) for _ in range(reps)]
+        tiles = (N + 127) // 128
+        part = torch.zeros(tiles * nsplit * 16 * 128, device=dev)
+        ticket = torch.zeros(tiles, dtype=torch.int32, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        state = {"i": 0}
+
+        def fn():
+            w = ws[state["i"] % reps]
+            state["i"] += 1
+            K.call("fb_gemv_tc_bf16", w, xs, Kd, 16 * Kd, out, N, m, N, Kd, 0, nsplit, part, ticket, status)
+        cases.append(Case(name, N * Kd * 2, fn, f"N={N} K={Kd} m={m} splits={nsplit} CTAs={tiles * nsplit}"))
+
+    for ns in (4, 8, 16):
+        tc_gemv_case(f"gemv_tc.gdn_o_proj.m3.s{ns}", 4096, 8192, 3, ns)
+    for ns in (1, 2, 3):
+        tc_gemv_case(f"gemv_tc.gdn_in.m3.s{ns}", 24896, 4096, 3, ns)
+    tc_gemv_case("gemv_tc.lm_head.m3.s1", 154880, 4096, 3, 1)
+    tc_gemv_case("gemv_tc.router_shared.m3.s8", 4384, 4096, 3, 8)
     fused_case("gemv_ar.gdn_o_proj.m3.nofold", 4096, 8192, 3, False)
     fused_case("gemv_ar.gdn_o_proj.m3.fold", 4096, 8192, 3, True)
     fused_case("gemv_ar.shared_down.m3.fold", 4096, 2048, 3, True)

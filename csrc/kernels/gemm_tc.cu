@@ -184,3 +184,171 @@ FB_API int fb_gemm_tc_bf16(const void* W, const void* x, int64_t ldx, float* out
         default: return launch_tc<256>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
     }
 }
+
+// ---- decode-sized row counts: split-K tcgen05 GEMV ----------------------------------------------
+// out[m, n] (+)= sum_k (x_hi + x_lo)[m, k] * W[n, k] for m <= 16 rows.  Same pipeline as the GEMM above
+// (TMA -> shared-memory ring -> tcgen05.mma -> TMEM), with three changes that make it a weight-streaming
+// kernel: (1) the reduction dim is split over blockIdx.z so that N / 128 x splits CTAs keep every SM
+// loading; (2) the activations come as a bf16 hi plane and a bf16 lo plane (x = hi + lo to ~16 bits):
+// both are multiplied into the same TMEM accumulator, so the result matches the split-activation
+// mma.sync GEMV; (3) split partials go to a scratch buffer and the LAST CTA of a weight tile (ticket)
+// sums them in split order - deterministic, no atomics on the output.
+namespace {
+
+constexpr int kGvBN = 16;
+constexpr int kGvStages = 5;     // 5 x 20 KB: two CTAs per SM
+constexpr int kGvStageBytes = kTileW * kBK * 2 + 2 * kGvBN * kBK * 2;   // weights + hi + lo
+constexpr size_t kGvSmem = (size_t)kGvStages * kGvStageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_hi,
+                      const __grid_constant__ CUtensorMap tmap_lo, float* __restrict__ out, int ldo, int M, int N, int K,
+                      int accumulate, float* __restrict__ part, unsigned* __restrict__ ticket, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = base + kGvStages * kGvStageBytes;
+    auto full = [&](int s) { return bars + 8u * s; };
+    auto empty = [&](int s) { return bars + 8u * (kGvStages + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * kGvStages);
+    const uint32_t tmem_slot = accum_bar + 8u;
+    __shared__ int s_fail, s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kTileW;
+    const int nsplit = gridDim.z, sp = blockIdx.z;
+    const int nkb_all = (K + kBK - 1) / kBK;
+    const int per = (nkb_all + nsplit - 1) / nsplit;
+    const int kb0 = sp * per, kb1 = min(nkb_all, kb0 + per);
+    const int nkb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        s_fail = 0;
+        for (int s = 0; s < kGvStages; ++s) { tc::mbar_init(full(s), 1); tc::mbar_init(empty(s), 1); }
+        tc::mbar_init(accum_bar, 1);
+        tc::mbar_fence_init();
+        tc::prefetch_tmap(&tmap_w);
+        tc::prefetch_tmap(&tmap_hi);
+        tc::prefetch_tmap(&tmap_lo);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, 32);
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+    pdl_launch();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % kGvStages;
+            if (i >= kGvStages && !tc::mbar_wait(empty(s), ((i / kGvStages) - 1) & 1)) { atomicExch(&s_fail, 1); break; }
+            const uint32_t a = base + s * kGvStageBytes, bh = a + kTileW * kBK * 2, bl = bh + kGvBN * kBK * 2;
+            tc::mbar_expect_tx(full(s), kGvStageBytes);
+            tc::tma_load_2d(a, &tmap_w, (kb0 + i) * kBK, n0, full(s));
+            tc::tma_load_2d(bh, &tmap_hi, (kb0 + i) * kBK, 0, full(s));
+            tc::tma_load_2d(bl, &tmap_lo, (kb0 + i) * kBK, 0, full(s));
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = tc::umma_idesc_bf16(kTileW, kGvBN);
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % kGvStages;
+            if (!tc::mbar_wait(full(s), (i / kGvStages) & 1)) { atomicExch(&s_fail, 1); break; }
+            tc::tc_fence_after();
+            const uint32_t a = base + s * kGvStageBytes, bh = a + kTileW * kBK * 2, bl = bh + kGvBN * kBK * 2;
+            const uint64_t ad = tc::umma_desc_sw128(a), hd = tc::umma_desc_sw128(bh), ld = tc::umma_desc_sw128(bl);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+                tc::umma_bf16(tmem_base, ad + 2u * k, hd + 2u * k, idesc, (i | k) ? 1u : 0u);
+                tc::umma_bf16(tmem_base, ad + 2u * k, ld + 2u * k, idesc, 1u);
+            }
+            tc::umma_commit(empty(s));
+        }
+        tc::umma_commit(accum_bar);
+    } else if (warp >= 2) {
+        const int q = warp & 3;
+        bool ok = true;
+        if (nkb > 0) ok = tc::mbar_wait(accum_bar, 0, 4000000000ll);
+        tc::tc_fence_after();
+        if (!ok) atomicExch(&s_fail, 1);
+        const bool go = __shfl_sync(0xffffffffu, (ok && s_fail == 0) ? 1 : 0, 0) != 0;
+        const int n = n0 + q * 32 + lane;
+        // partial tile of this split: part[tile][split][m][128]
+        float* pp = part + (((size_t)blockIdx.x * nsplit + sp) * kGvBN) * kTileW + q * 32 + lane;
+#pragma unroll
+        for (int c = 0; c < kGvBN; c += 8) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (go && nkb > 0) tc::tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pp[(size_t)(c + i) * kTileW] = v[i];
+        }
+        (void)n;
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_fail) { status[0] = FB_TIMEOUT; status[1] = blockIdx.x; status[2] = blockIdx.z; status[3] = nkb; }
+        __threadfence();
+        s_last = (atomicAdd(ticket + blockIdx.x, 1u) == (unsigned)nsplit - 1u) ? 1 : 0;
+    }
+    if (warp == 1) {
+        tc::tc_fence_after();
+        tc::tmem_dealloc(tmem_base, 32);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // the last CTA of this weight tile sums the splits in order and writes the rows
+    for (int i = threadIdx.x; i < M * kTileW; i += blockDim.x) {
+        const int m = i / kTileW, j = i % kTileW;
+        if (n0 + j >= N) continue;
+        float v = 0.f;
+        for (int s = 0; s < nsplit; ++s) v += __ldcg(part + (((size_t)blockIdx.x * nsplit + s) * kGvBN + m) * kTileW + j);
+        float* o = out + (size_t)m * ldo + n0 + j;
+        *o = accumulate ? *o + v : v;
+    }
+    if (threadIdx.x == 0) ticket[blockIdx.x] = 0u;
+}
+
+}  // namespace
+
+// W [N, K] bf16; xs: split activation planes (plane 0 = bf16 hi, plane 1 = bf16 lo), rows of xs_ld elements,
+// planes xs_plane elements apart; m <= 16.  part: scratch of ceil(N/128) * nsplit * 16 * 128 floats,
+// ticket: ceil(N/128) zero-initialised words (left at zero).  status: int[4].
+FB_API int fb_gemv_tc_bf16(const void* W, const void* xs, int64_t xs_ld, int64_t xs_plane, float* out, int64_t ldo, int64_t m,
+                           int64_t N, int64_t K, int64_t accumulate, int64_t nsplit, float* part, void* ticket, int* status,
+                           cudaStream_t st) {
+    if ((K % 8) || (xs_ld % 8) || m < 1 || m > kGvBN || nsplit < 1) return (int)cudaErrorInvalidValue;
+    CUtensorMap tw, th, tl;
+    int rc = fb_make_tmap_2d(&tw, W, (uint64_t)N, (uint64_t)K, kTileW, kBK, 2);
+    if (rc) return rc;
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p)
+        return (int)cudaErrorNotSupported;
+    const uint16_t* hi = (const uint16_t*)xs;
+    const uint16_t* lo = hi + xs_plane;
+    if (((uintptr_t)hi & 15) || ((uintptr_t)lo & 15)) return (int)cudaErrorInvalidValue;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)m};
+    cuuint64_t strides[1] = {(cuuint64_t)xs_ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kGvBN};
+    cuuint32_t estr[2] = {1, 1};
+    for (int which = 0; which < 2; ++which) {
+        CUresult r = ((EncodeFn)p)(which ? &tl : &th, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(which ? lo : hi),
+                                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_tc_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGvSmem);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    dim3 grid((unsigned)((N + kTileW - 1) / kTileW), 1, (unsigned)nsplit);
+    FB_LAUNCH((gemv_tc_splitk_kernel), grid, kThreads, kGvSmem, st, tw, th, tl, out, (int)ldo, (int)m, (int)N, (int)K,
+              (int)accumulate, part, (unsigned*)ticket, status);
+    return FB_LAUNCH_CHECK();
+}

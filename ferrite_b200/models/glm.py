@@ -9,6 +9,8 @@ lengths, snapshot cursor, token ids) live in device memory and are advanced by g
 """
 from __future__ import annotations
 
+import os
+
 import math
 import zlib
 from dataclasses import dataclass
@@ -102,6 +104,9 @@ class GlmDeviceModel:
                 from ..parallel.symm import FusedGemvAllReduce
                 self.fused = FusedGemvAllReduce(self.dev, 0, 1)
         self.dcp = None          # (d, n_dcp, DcpAttentionMerge): decode-context-parallel attention
+        # decode GEMVs with at least this many output rows go to the tcgen05 split-K kernel (0 = never)
+        self.tc_gemv_min_n = int(os.environ.get("FERRITE_TC_GEMV_MIN_N", "0"))
+        self._tc_part = self._tc_ticket = None
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
         self._fold_next = None   # (fn_next,) while a hyper-connection site's sublayer runs
@@ -397,6 +402,23 @@ class GlmDeviceModel:
             xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
             op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
             self.K.call("fb_gemm_tc_bf16", w, xp, ldx, op, ldo, m, N, K, int(accumulate), self.tc_status)
+            if oa is not None and omask:
+                self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
+                            omask, m, N)
+            return
+        if (use_mma and not fp8 and group_rows == 0 and m <= 16 and self.tc_gemv_min_n and N >= self.tc_gemv_min_n
+                and K % 64 == 0):
+            # decode-sized rows of a large matrix: TMA + tcgen05 split-K GEMV (bf16 hi + lo activation planes)
+            tiles = (N + 127) // 128
+            nsplit = max(1, min(K // 256, -(-296 // tiles)))
+            need = tiles * nsplit * 16 * 128
+            if self._tc_part is None or self._tc_part.numel() < need or self._tc_ticket.numel() < tiles:
+                self._tc_part = torch.zeros(max(need, 4 << 20), device=self.dev)
+                self._tc_ticket = torch.zeros(max(tiles, 2048), dtype=torch.int32, device=self.dev)
+            xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
+            op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
+            self.K.call("fb_gemv_tc_bf16", w, xp, ldx, xa.plane, op, ldo, m, N, K, int(accumulate), nsplit, self._tc_part,
+                        self._tc_ticket, self.tc_status)
             if oa is not None and omask:
                 self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
                             omask, m, N)

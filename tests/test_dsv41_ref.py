@@ -190,3 +190,16 @@ def test_cpp_golden_matches_python_statement():
     keep = torch.from_numpy(G.d4_candidate_blocks(score.numpy(), 6, 2, 2)).bool()
     assert keep.tolist() == select_candidate_blocks(score.masked_fill(torch.arange(8) >= 6, float("-inf")).unsqueeze(0),
                                                     torch.tensor([6]), 2, 2)[0].tolist()
+
+
+def test_synthetic_source_shapes_and_determinism():
+    from ferrite_b200.models.dsv41_synth import SyntheticDsv41Source
+    cfg = Dsv41Config.tiny()
+    a, b = SyntheticDsv41Source(cfg, "cpu", seed=1), SyntheticDsv41Source(cfg, "cpu", seed=1)
+    specs = tensor_specs(cfg)
+    for name in ("embed.weight", "layers.1.attn.wq_b.weight", "layers.3.attn.compressor.norm.weight", "mtp.0.main_proj.weight"):
+        assert a.has(name) and tuple(a.get(name).shape) == specs[name].shape and torch.equal(a.get(name), b.get(name))
+    assert not a.has("layers.0.ffn.experts.0.w1.weight")
+    w13, s13, w2, s2 = a.expert_pack("layers.0.ffn.", 8, 64, 0, 1, "cpu")
+    assert w13.shape == (8, 2, 64, cfg.dim // 2) and s13.shape == (8, 2, 64, cfg.dim // 32)
+    assert w2.shape == (8, cfg.dim, 32) and s2.shape == (8, cfg.dim, 2) and w13.dtype == torch.uint8

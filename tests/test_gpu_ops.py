@@ -745,3 +745,27 @@ def test_device_runtime_fork_join_capture_replay(K):
     rt.pinned_free(host)
     rt.graph_free(g)
     rt.close()
+
+
+@pytest.mark.parametrize("m,N,K_,nsplit", [(3, 4096, 8192, 8), (1, 24896, 4096, 2), (16, 300, 256, 3), (5, 129, 1536, 24),
+                                           (8, 4384, 4096, 6)])
+def test_gemv_tcgen05_splitk(K, m, N, K_, nsplit):
+    """Split-K tcgen05 GEMV with hi + lo activation planes against fp32 matmul."""
+    from ferrite_b200.models.glm import Act
+    W = rnd(N, K_, seed=1, scale=0.05).to(torch.bfloat16)
+    x = Act(torch.device("cuda"), 16, K_)
+    x.f[:m].copy_(dev(rnd(m, K_, seed=2)))
+    K.call("fb_split_rows", x.f, K_, *x.sp(1), 16, K_)
+    tiles = (N + 127) // 128
+    part = torch.zeros(tiles * nsplit * 16 * 128, device="cuda")
+    ticket = torch.zeros(tiles, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.full((m, N), 0.25, device="cuda")
+    want = x.f[:m].cpu() @ W.float().t()
+    for it, acc in enumerate((0, 1, 0)):
+        K.call("fb_gemv_tc_bf16", dev(W), x.s, K_, x.plane, out, N, m, N, K_, acc, nsplit, part, ticket, status)
+        torch.cuda.synchronize()
+        assert status.tolist()[0] == 0, status.tolist()
+        exp = want * (2 if acc else 1)
+        check(f"gemv tc splitk {it}", out, exp, 2e-3 * max(1.0, exp.abs().max().item()))
+        assert not ticket.any()
