@@ -68,6 +68,9 @@ class Dsv41DeviceModel:
         self.Is = per if self.shared_tp else cfg.moe_inter_dim
         self.tc_min_rows = 16
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.tc_gemv_min_n = 0
+        self._tc_part = None
+        self._tc_ticket = None
         # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
         self.fused = None
         if world > 1:

@@ -406,8 +406,8 @@ class GlmDeviceModel:
                 self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
                             omask, m, N)
             return
-        if (use_mma and not fp8 and group_rows == 0 and m <= 16 and self.tc_gemv_min_n and N >= self.tc_gemv_min_n
-                and K % 64 == 0):
+        tc_min_n = getattr(self, "tc_gemv_min_n", 0)
+        if use_mma and not fp8 and group_rows == 0 and m <= 16 and tc_min_n and N >= tc_min_n and K % 64 == 0:
             # decode-sized rows of a large matrix: TMA + tcgen05 split-K GEMV (bf16 hi + lo activation planes)
             tiles = (N + 127) // 128
             nsplit = max(1, min(K // 256, -(-296 // tiles)))
