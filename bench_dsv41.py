@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=300)
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
     from ferrite_b200.engine.dsv41_engine import Dsv41Engine
     from ferrite_b200.models.dsv41_config import Dsv41Config
@@ -64,12 +66,16 @@ def main():
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     toks = 0
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     e0.record()
     for _ in range(args.steps):
         r = step()
         toks += len(r) if isinstance(r, list) else 1
     e1.record()
     torch.cuda.synchronize()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     if world > 1:
         import torch.distributed as dist

@@ -157,25 +157,8 @@ FB_API int fb_gemm_tc_bf16(const void* W, const void* x, int64_t ldx, float* out
     CUtensorMap tw, tx;
     int rc = fb_make_tmap_2d(&tw, W, (uint64_t)N, (uint64_t)K, kTileW, kBK, 2);
     if (rc) return rc;
-    // the activation tensor is described with its row stride as the inner extent
-    {
-        typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p)
-            return (int)cudaErrorNotSupported;
-        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-        cuuint64_t strides[1] = {(cuuint64_t)ldx * 2};
-        cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)bn};
-        cuuint32_t estr[2] = {1, 1};
-        if (((uintptr_t)x & 15)) return (int)cudaErrorInvalidValue;
-        CUresult r = ((EncodeFn)p)(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
-                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
-    }
+    rc = fb_make_tmap_2d_strided(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, kBK, 2);
+    if (rc) return rc;
     switch (bn) {
         case 16: return launch_tc<16>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
         case 32: return launch_tc<32>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
@@ -321,26 +304,12 @@ FB_API int fb_gemv_tc_bf16(const void* W, const void* xs, int64_t xs_ld, int64_t
     CUtensorMap tw, th, tl;
     int rc = fb_make_tmap_2d(&tw, W, (uint64_t)N, (uint64_t)K, kTileW, kBK, 2);
     if (rc) return rc;
-    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p)
-        return (int)cudaErrorNotSupported;
     const uint16_t* hi = (const uint16_t*)xs;
     const uint16_t* lo = hi + xs_plane;
-    if (((uintptr_t)hi & 15) || ((uintptr_t)lo & 15)) return (int)cudaErrorInvalidValue;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)m};
-    cuuint64_t strides[1] = {(cuuint64_t)xs_ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kGvBN};
-    cuuint32_t estr[2] = {1, 1};
-    for (int which = 0; which < 2; ++which) {
-        CUresult r = ((EncodeFn)p)(which ? &tl : &th, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(which ? lo : hi),
-                                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
-    }
+    rc = fb_make_tmap_2d_strided(&th, hi, (uint64_t)m, (uint64_t)K, (uint64_t)xs_ld, kGvBN, kBK, 2);
+    if (rc) return rc;
+    rc = fb_make_tmap_2d_strided(&tl, lo, (uint64_t)m, (uint64_t)K, (uint64_t)xs_ld, kGvBN, kBK, 2);
+    if (rc) return rc;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(gemv_tc_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGvSmem);

@@ -98,8 +98,9 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 // ---- host: tensor maps ---------------------------------------------------------------------------
 // 2-D row-major [rows, cols] tensor of `esz`-byte elements, box = [box_rows, box_cols] with the
 // 128-byte swizzle (box_cols * esz must be 128).  Out-of-range rows/columns read as zero.
-inline int fb_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-                           uint32_t box_cols, int esz) {
+// `ld` is the row stride in elements (>= cols).
+inline int fb_make_tmap_2d_strided(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                   uint32_t box_rows, uint32_t box_cols, int esz) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -111,13 +112,17 @@ inline int fb_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, ui
             return (int)cudaErrorNotSupported;
         fn = (EncodeFn)p;
     }
-    if (((uintptr_t)base & 15) || ((cols * esz) & 15) || box_cols * esz != 128) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)base & 15) || ((ld * esz) & 15) || ld < cols || box_cols * esz != 128) return (int)cudaErrorInvalidValue;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * (uint64_t)esz};
+    cuuint64_t strides[1] = {ld * (uint64_t)esz};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+inline int fb_make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                           uint32_t box_cols, int esz) {
+    return fb_make_tmap_2d_strided(map, base, rows, cols, cols, box_rows, box_cols, esz);
 }

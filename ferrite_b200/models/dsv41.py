@@ -357,6 +357,12 @@ class Dsv41DeviceModel:
         ok = (self.fused is not None and x.s is not None and n <= 8 and K % 64 == 0 and x.ld % 8 == 0 and N % 32 == 0
               and (self.world == 1 or n * N <= self.fused.max_elems) and (self.world > 1 or fold is not None))
         if not ok:
+            gar = getattr(self.allreduce, "gemm_fused", None) if self.world > 1 else None
+            if (gar is not None and x.s is not None and n >= self.tc_min_rows and K % 8 == 0 and x.ld % 8 == 0
+                    and ws["y"].shape[1] % 4 == 0 and gar.fits(n, N)):
+                # prefill rows: TMA + tcgen05 GEMM with the two-shot all-reduce in its epilogue (one launch)
+                gar(w, x.s, x.ld, ws["y"], ws["y"].shape[1], n, N, K, accumulate)
+                return
             self.gemv(w, x, ws["y"], n, N, K, accumulate=accumulate)
             self._reduce(ws["y"], n)
             return

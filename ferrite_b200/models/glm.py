@@ -475,6 +475,12 @@ class GlmDeviceModel:
               and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or 8 * N <= self.fused.max_elems)
               and (self.world > 1 or fold is not None))
         if not ok:
+            gar = getattr(self.allreduce, "gemm_fused", None) if self.world > 1 else None
+            if (gar is not None and scales is None and xa is not None and xa.s is not None and n >= self.tc_min_rows
+                    and K % 8 == 0 and ldx % 8 == 0 and ws["y"].shape[1] % 4 == 0 and gar.fits(n, N)):
+                # prefill rows: TMA + tcgen05 GEMM with the two-shot all-reduce in its epilogue (one launch)
+                gar(w, xa.s, ldx, ws["y"], ws["y"].shape[1], n, N, K, accumulate)
+                return
             self.gemv(w, x, ws["y"], n, N, K, ldx=ldx, scales=scales, accumulate=accumulate)
             self._reduce(ws["y"], n)
             return

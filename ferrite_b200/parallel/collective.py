@@ -12,12 +12,14 @@ import torch.distributed as dist
 
 
 def make_allreduce(device, rank: int, world: int, max_elems: int, kind: str = "nccl", fused: bool = True):
-    """kind "p2p" also carries ``.fused``, the GEMV + all-reduce (+ fold) kernel, unless fused=False."""
+    """kind "p2p" also carries ``.fused``, the GEMV + all-reduce (+ fold) kernel for decode rows, and
+    ``.gemm_fused``, the tcgen05 GEMM + two-shot all-reduce kernel for prefill rows, unless fused=False."""
     if kind == "p2p":
-        from .symm import CrossRankArgmax, FusedGemvAllReduce, P2PAllReduce
+        from .symm import CrossRankArgmax, FusedGemmAllReduce, FusedGemvAllReduce, P2PAllReduce
         ar = P2PAllReduce(device, rank, world, max_elems)
         if fused:
             ar.fused = FusedGemvAllReduce(device, rank, world)
+            ar.gemm_fused = FusedGemmAllReduce(device, rank, world, max_rows=256, n_max=8192)
         ar.argmax = CrossRankArgmax(device, rank, world)   # enables the vocab-sliced head
         return ar
 

@@ -86,6 +86,7 @@ class P2PAllReduce:
         self._fp = arr(*self.flags.ptrs)
         self.calls = 0
         self.fused: Optional["FusedGemvAllReduce"] = None   # attached by make_allreduce
+        self.gemm_fused: Optional["FusedGemmAllReduce"] = None   # attached by make_allreduce
         self.argmax: Optional["CrossRankArgmax"] = None      # attached by make_allreduce
 
     def __call__(self, view: torch.Tensor):
@@ -103,12 +104,16 @@ class P2PAllReduce:
             raise CollectiveTimeout(s[1], s[2], s[3])
         if self.fused is not None:
             self.fused.check()
+        if self.gemm_fused is not None:
+            self.gemm_fused.check()
         if self.argmax is not None:
             self.argmax.check()
 
     def close(self):
         if self.fused is not None:
             self.fused.close()
+        if self.gemm_fused is not None:
+            self.gemm_fused.close()
         if self.argmax is not None:
             self.argmax.close()
         self.staging.close()
@@ -187,6 +192,66 @@ class FusedGemvAllReduce:
             self.staging.close()
             self.flags.close()
             self.staging = self.flags = None
+
+
+class FusedGemmAllReduce:
+    """Row-parallel prefill GEMM (TMA + tcgen05) + two-shot all-reduce over peer memory as one kernel
+    launch (``csrc/kernels/gemm_tc_ar.cu``): out[m, n] = sum over ranks of x_rank . W_rank^T.  Buffers
+    are sized for ``max_rows`` x ``n_max`` outputs; ``fits(m, N)`` says whether a shape can go through
+    the fused kernel (co-resident grid, at least one tile per rank)."""
+
+    def __init__(self, device, rank: int, world: int, max_rows: int = 256, n_max: int = 8192,
+                 max_spins: int = 2_000_000, group=None):
+        self.K = _lib.lib()
+        self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.max_rows, self.n_max = max_rows, n_max
+        pad_elems = (max_rows + 256) * (n_max + 128)          # whole tiles of any tile height
+        self.gather_cap = 2 * pad_elems
+        self.scatter_cap = 2 * pad_elems + 2 * world * 256 * 128   # + one rounding tile per source slot
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ticket = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.scatter = self.gather = self.flags = None
+        self._sp = self._gp = self._fp = None
+        if world > 1:
+            self.scatter = SymmetricRegion(self.scatter_cap * 4, rank, world, group)
+            self.gather = SymmetricRegion(self.gather_cap * 4, rank, world, group)
+            self.flags = SymmetricRegion(4 * world * 32 * 4, rank, world, group)
+            arr = ctypes.c_void_p * world
+            self._sp = arr(*self.scatter.ptrs)
+            self._gp = arr(*self.gather.ptrs)
+            self._fp = arr(*self.flags.ptrs)
+        self.calls = 0
+
+    def plan(self, m: int, N: int):
+        bn, nt = ctypes.c_int(), ctypes.c_int()
+        self.K.lib.fb_gemm_tc_ar_plan(ctypes.c_int64(m), ctypes.c_int64(N), ctypes.byref(bn), ctypes.byref(nt))
+        return bn.value, nt.value
+
+    def fits(self, m: int, N: int) -> bool:
+        bn, nt = self.plan(m, N)
+        return 1 <= m <= self.max_rows and N <= self.n_max and N % 4 == 0 and self.world <= nt <= 148
+
+    def __call__(self, W, x_bf16, ldx: int, out, ldo: int, m: int, N: int, K: int, accumulate: bool = False):
+        """W [N, K] bf16 (this rank's K slice), x_bf16: pointer/tensor of [m, K] bf16 rows (stride ldx),
+        out [m, N] f32 (stride ldo); all ranks must call with the same shape."""
+        self.K.call("fb_gemm_tc_ar", W, x_bf16, ldx, out, ldo, m, N, K, int(accumulate), self._sp, self._gp, self._fp,
+                    self.scatter_cap, self.gather_cap, self.epoch, self.ticket, self.status, self.rank, self.world,
+                    self.max_spins)
+        self.calls += 1
+
+    def check(self):
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3])
+
+    def close(self):
+        if self.scatter is not None:
+            self.scatter.close()
+            self.gather.close()
+            self.flags.close()
+            self.scatter = self.gather = self.flags = None
 
 
 class CrossRankArgmax:

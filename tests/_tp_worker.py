@@ -11,7 +11,7 @@ from ferrite_b200.config import EngineConfig, GlmConfig  # noqa: E402
 from ferrite_b200.engine.glm_engine import GlmEngine  # noqa: E402
 from ferrite_b200.models.glm import DictSource  # noqa: E402
 from ferrite_b200.models.glm_weights import random_weights  # noqa: E402
-from ferrite_b200.parallel.symm import CrossRankArgmax, FusedGemvAllReduce, P2PAllReduce  # noqa: E402
+from ferrite_b200.parallel.symm import CrossRankArgmax, FusedGemmAllReduce, FusedGemvAllReduce, P2PAllReduce  # noqa: E402
 
 
 def main():
@@ -82,6 +82,38 @@ def main():
             torch.cuda.synchronize()
             assert torch.equal(y2, y), (N, Kd, m, it)
         ar.check()
+    # 1b'. fused prefill GEMM (tcgen05) + two-shot all-reduce == GEMM then NCCL all-reduce, bitwise equal on all
+    # ranks, eager and replayed in a graph, with and without a local addend
+    gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096)
+    for (N, Kd, m, acc) in ((4096, 1024, 256, False), (4096, 512, 100, True), (1024, 256, 37, False), (512, 128, 16, False)):
+        assert gar.fits(m, N), (m, N, gar.plan(m, N))
+        g = torch.Generator(device=dev).manual_seed(31 + rank)
+        W = (torch.randn(N, Kd, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        xb = torch.randn(m, Kd, device=dev, generator=g).to(torch.bfloat16)
+        add = torch.randn(m, N, device=dev, generator=g) if acc else torch.zeros(m, N, device=dev)
+        want = (xb.double() @ W.double().t()).float() + add
+        dist.all_reduce(want)
+        y = add.clone()
+        gar(W, xb, Kd, y, N, m, N, Kd, acc)
+        torch.cuda.synchronize()
+        gar.check()
+        err = (y - want).abs().max().item()
+        assert err < 2e-3 * max(1.0, want.abs().max().item()), ("gemm_ar", N, Kd, m, err)
+        ref = y.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(ref, y), "fused GEMM all-reduce: ranks disagree bitwise"
+        graph = torch.cuda.CUDAGraph()
+        y2 = add.clone()
+        gar(W, xb, Kd, y2, N, m, N, Kd, acc)      # warm-up outside capture (keeps the epochs of all ranks aligned)
+        with torch.cuda.graph(graph):
+            gar(W, xb, Kd, y2, N, m, N, Kd, acc)
+        for it in range(3):
+            y2.copy_(add)
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y2, y), ("gemm_ar graph", N, Kd, m, it)
+        gar.check()
+    gar.close()
     # 1c. vocab-sliced argmax merged across ranks == argmax of the full row (first maximum wins)
     V, n = 4096 * world, 5
     full = torch.randn(n, V, device=dev, generator=torch.Generator(device=dev).manual_seed(11))

@@ -769,3 +769,25 @@ def test_gemv_tcgen05_splitk(K, m, N, K_, nsplit):
         exp = want * (2 if acc else 1)
         check(f"gemv tc splitk {it}", out, exp, 2e-3 * max(1.0, exp.abs().max().item()))
         assert not ticket.any()
+
+
+@pytest.mark.parametrize("M,N,K_", [(256, 4096, 1024), (100, 1000, 512), (16, 512, 128), (300, 4096, 256), (5, 300, 256)])
+def test_gemm_tc_ar_single_rank(K, M, N, K_):
+    """The fused GEMM + all-reduce kernel with one rank (no collective): a plain tcgen05 GEMM with an
+    optional local addend, against fp32 matmul of the same bf16 inputs."""
+    from ferrite_b200.parallel.symm import FusedGemmAllReduce
+    gar = FusedGemmAllReduce(torch.device("cuda"), 0, 1, max_rows=512, n_max=4096)
+    w = dev(rnd(N, K_, seed=1, scale=0.1).bfloat16())
+    x = dev(rnd(M, K_, seed=2).bfloat16())
+    add = dev(rnd(M, N, seed=3))
+    want = x.float() @ w.float().t()
+    out = torch.full((M, N), 3.0, device="cuda")
+    gar(w, x, K_, out, N, M, N, K_, False)
+    torch.cuda.synchronize()
+    gar.check()
+    check("gemm tc ar", out, want, 2e-3 * max(1.0, want.abs().max().item()))
+    out.copy_(add)
+    gar(w, x, K_, out, N, M, N, K_, True)
+    torch.cuda.synchronize()
+    gar.check()
+    check("gemm tc ar acc", out, want + add, 2e-3 * max(1.0, want.abs().max().item()))
