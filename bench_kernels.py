@@ -240,6 +240,39 @@ def make_cases(K, only):
             K.call("fb_d4_expert_down", hbuf, ids, w2, s2, y, D, n, topk, I, D, 0)
         cases.append(Case("d4_expert_gate_up.tp8.m1", topk * 2 * I * (D // 2 + D // 32), d4gu, f"6 experts x 2 x {I} x {D} e2m1"))
         cases.append(Case("d4_expert_down.tp8.m1", topk * D * (I // 2 + I // 32), d4dn, f"6 experts x {D} x {I} e2m1"))
+        # tensor-core variants (quad-interleaved bytes; random bytes need no repack), TP8 slice and the whole expert
+        from ferrite_b200.models.glm import Act
+        for tag, Im, Em in (("tp8", 320, 384), ("tp1", 2304, 48)):
+            w13m = torch.randint(0, 256, (Em, 2, Im, D // 2), dtype=torch.uint8, device=dev)
+            s13m = torch.full((Em, 2, Im, D // 32), 120, dtype=torch.uint8, device=dev)
+            w2m = torch.randint(0, 256, (Em, D, Im // 2), dtype=torch.uint8, device=dev)
+            s2m = torch.full((Em, D, Im // 32), 120, dtype=torch.uint8, device=dev)
+            xa, ha = Act(dev, 8, D), Act(dev, 8 * topk, Im)
+            xa.f.normal_()
+            K.call("fb_d4_quant_rows", xa.f, D, xa.f, D, 8, D, *xa.sp(2))
+            ha.f.normal_()
+            K.call("fb_d4_quant_rows", ha.f, Im, ha.f, Im, 8 * topk, Im, *ha.sp(2))
+            hout = torch.zeros(8 * topk, Im, device=dev)
+            ym = torch.zeros(8, D, device=dev)
+            for m in (1, 6):
+                sets = [torch.stack([torch.randperm(Em, device=dev)[:topk] for _ in range(m)]).to(torch.int32).contiguous()
+                        for _ in range(8)]
+                wm = torch.rand(m, topk, device=dev)
+                stm = {"i": 0}
+
+                def gu(m=m, sets=sets, wm=wm, stm=stm, w13m=w13m, s13m=s13m, xa=xa, hout=hout, Im=Im):
+                    ids = sets[stm["i"] % 8]; stm["i"] += 1
+                    K.call("fb_d4_expert_gate_up_mma", _lib.ctypes.c_void_p(xa.s.data_ptr() + 4 * xa.plane), D, ids, wm, w13m, s13m,
+                           hout, m, topk, Im, D, 10.0)
+
+                def dn(m=m, sets=sets, stm=stm, w2m=w2m, s2m=s2m, ha=ha, ym=ym, Im=Im):
+                    ids = sets[stm["i"] % 8]; stm["i"] += 1
+                    K.call("fb_d4_expert_down_mma", _lib.ctypes.c_void_p(ha.s.data_ptr() + 4 * ha.plane), ids, w2m, s2m, ym, D, m, topk,
+                           Im, D, 0)
+                cases.append(Case(f"d4_expert_gate_up_mma.{tag}.m{m}", m * topk * 2 * Im * (D // 2 + D // 32), gu,
+                                  f"{m * topk} pairs x 2 x {Im} x {D} e2m1 (bytes if all pairs differ)"))
+                cases.append(Case(f"d4_expert_down_mma.{tag}.m{m}", m * topk * D * (Im // 2 + Im // 32), dn,
+                                  f"{m * topk} pairs x {D} x {Im} e2m1"))
     if want("d4_sparse_attn"):
         n, Hl, hd, W, cap, ktop, ccap = 1, 8, 512, 128, 136, 512, 8192
         ring = torch.randn(1, cap, hd, device=dev).to(torch.bfloat16)

@@ -1,0 +1,243 @@
+// DSV41 routed experts on the tensor cores for decode-sized row counts: e2m1 weights with one ue8m0
+// scale per 32 values of K, activations e4m3-per-32 round-tripped (so their f16 copy is exact).
+//
+// out[16 weight rows x 8] tiles with mma.sync.m16n8k16 (f16 inputs, f32 accumulation): the WEIGHTS are
+// the A operand, the activation row is column 0 of the B operand.  e2m1 converts exactly to f16 (one
+// cvt per two values); the power-of-two block scale cannot be folded into an f16 operand without range
+// limits, so each 32-value block is multiplied into a fresh accumulator (two MMAs) that is then scaled
+// per weight row and added to the running sum.  All four lanes of a quad must therefore work on the
+// SAME scale block in one MMA, while a lane wants one 16-byte load per row and 128-value k-block.  Both
+// hold with a load-time repack of the weight bytes ("quad-interleaved", fb_d4_fp4_repack): inside every
+// 64-byte group of a row (128 values = 4 scale blocks x 4 words), word (block b, position q) moves to
+// (position q, block b).  Lane q of a quad then reads 16 bytes = its 8 values of each of the 4 blocks.
+//
+// gate/up:  grid (I / 16, topk, rows): 16 intermediate channels of one (row, slot) pair; the warps split K,
+//           partial tiles meet in shared memory, the epilogue applies the clamped SwiGLU and the routing
+//           weight.
+// down:     grid (D / 16, rows): 16 output channels; the warps split the (slot, k-block) list.
+// Replaces the reference's `expert_gemv_fp4_*` decode kernels (kernels/cuda/dsv41_kernels.cu).
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
+
+#include "mma_gemv.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+    const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)(byte & 0xffu), __NV_E2M1);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float ue8m0_of(uint32_t word, int b) { return __uint_as_float(((word >> (8 * b)) & 0xffu) << 23); }
+
+// One k-block (128 values) of one 16-row weight tile against the activation fragment: acc[0..1] belong to
+// weight row g, acc[2..3] to row g + 8 (columns 2q, 2q + 1 of the activation operand).
+//   wa / wb : the lane's 16 repacked bytes of rows g / g + 8;  sa / sb : the 4 scale bytes of the k-block
+//   x       : the lane's activation fragment, x[b] = 8 f16 values of scale block b
+__device__ __forceinline__ void mma_block_fp4(float (&acc)[4], const uint4& wa, const uint4& wb, uint32_t sa, uint32_t sb,
+                                              const uint4 (&x)[4], int nb = 4) {
+    const uint32_t A[4] = {wa.x, wa.y, wa.z, wa.w};
+    const uint32_t B[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        if (b >= nb) break;   // warp-uniform: a 64-value tail has two blocks
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_f16_16816(d, e2m1x2_to_f16x2(A[b]), e2m1x2_to_f16x2(B[b]), e2m1x2_to_f16x2(A[b] >> 8), e2m1x2_to_f16x2(B[b] >> 8),
+                      x[b].x, x[b].y);
+        mma_f16_16816(d, e2m1x2_to_f16x2(A[b] >> 16), e2m1x2_to_f16x2(B[b] >> 16), e2m1x2_to_f16x2(A[b] >> 24),
+                      e2m1x2_to_f16x2(B[b] >> 24), x[b].z, x[b].w);
+        const float fa = ue8m0_of(sa, b), fb = ue8m0_of(sb, b);
+        acc[0] = fmaf(d[0], fa, acc[0]);
+        acc[1] = fmaf(d[1], fa, acc[1]);
+        acc[2] = fmaf(d[2], fb, acc[2]);
+        acc[3] = fmaf(d[3], fb, acc[3]);
+    }
+}
+
+// The lane's activation fragment of a k-block: row pointer `xr` (f16), only column-0 lanes (g == 0) load.
+__device__ __forceinline__ void load_x_fp4(uint4 (&x)[4], const uint16_t* __restrict__ xr, int k0, int g, int tq, int nb = 4) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        x[b] = make_uint4(0u, 0u, 0u, 0u);
+        if (g == 0 && b < nb) x[b] = __ldg(reinterpret_cast<const uint4*>(xr + k0 + b * 32 + tq * 8));
+    }
+}
+
+struct Fp4Frag { uint4 wa, wb; uint32_t sa, sb; };
+__device__ __forceinline__ Fp4Frag load_fp4(const uint8_t* __restrict__ wa, const uint8_t* __restrict__ wb,
+                                            const uint8_t* __restrict__ sa, const uint8_t* __restrict__ sb, int kb, int tq) {
+    Fp4Frag f;
+    f.wa = ldg_nc_v4(wa + (size_t)kb * 64 + tq * 16);
+    f.wb = ldg_nc_v4(wb + (size_t)kb * 64 + tq * 16);
+    // scale rows are only 2-byte aligned when K / 32 is not a multiple of 4
+    const uint16_t* pa = reinterpret_cast<const uint16_t*>(sa + (size_t)kb * 4);
+    const uint16_t* pb = reinterpret_cast<const uint16_t*>(sb + (size_t)kb * 4);
+    f.sa = (uint32_t)__ldg(pa) | ((uint32_t)__ldg(pa + 1) << 16);
+    f.sb = (uint32_t)__ldg(pb) | ((uint32_t)__ldg(pb + 1) << 16);
+    return f;
+}
+// The 64-value tail of a row whose length is an odd multiple of 64: 8 bytes per lane, two scale bytes.
+__device__ __forceinline__ Fp4Frag load_fp4_tail(const uint8_t* __restrict__ wa, const uint8_t* __restrict__ wb,
+                                                 const uint8_t* __restrict__ sa, const uint8_t* __restrict__ sb, int kb, int tq) {
+    Fp4Frag f;
+    const uint2 a = __ldg(reinterpret_cast<const uint2*>(wa + (size_t)kb * 64 + tq * 8));
+    const uint2 b = __ldg(reinterpret_cast<const uint2*>(wb + (size_t)kb * 64 + tq * 8));
+    f.wa = make_uint4(a.x, a.y, 0u, 0u);
+    f.wb = make_uint4(b.x, b.y, 0u, 0u);
+    f.sa = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sa + (size_t)kb * 4));
+    f.sb = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(sb + (size_t)kb * 4));
+    return f;
+}
+
+constexpr int kNW = 8;
+
+__global__ void __launch_bounds__(kNW * 32)
+expert_gate_up_mma_kernel(const uint16_t* __restrict__ xh, int ldx, const int* __restrict__ idx, const float* __restrict__ wts,
+                          const uint8_t* __restrict__ w13, const uint8_t* __restrict__ s13, float* __restrict__ h, int topk,
+                          int I, int K, float lim) {
+    pdl_launch();
+    __shared__ float red[kNW][2][16];
+    const int r = blockIdx.z, s = blockIdx.y, i0 = blockIdx.x * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int nkb = K >> 7;
+    const size_t wrow = (size_t)K / 2, srow = (size_t)K / 32;
+    pdl_wait();
+    const int e = idx[(size_t)r * topk + s];
+    const int ra = min(i0 + g, I - 1), rb = min(i0 + g + 8, I - 1);
+    const uint8_t* wg = w13 + (size_t)e * 2 * I * wrow;
+    const uint8_t* sg = s13 + (size_t)e * 2 * I * srow;
+    const uint8_t *ga = wg + ra * wrow, *gb = wg + rb * wrow, *ua = wg + (I + ra) * wrow, *ub = wg + (I + rb) * wrow;
+    const uint8_t *gsa = sg + ra * srow, *gsb = sg + rb * srow, *usa = sg + (I + ra) * srow, *usb = sg + (I + rb) * srow;
+    const uint16_t* xr = xh + (size_t)r * ldx;
+    float accg[4] = {0.f, 0.f, 0.f, 0.f}, accu[4] = {0.f, 0.f, 0.f, 0.f};
+    Fp4Frag cg, cu, ng, nu;
+    if (warp < nkb) { cg = load_fp4(ga, gb, gsa, gsb, warp, tq); cu = load_fp4(ua, ub, usa, usb, warp, tq); }
+    for (int kb = warp; kb < nkb; kb += kNW) {
+        const int kn = kb + kNW;
+        if (kn < nkb) { ng = load_fp4(ga, gb, gsa, gsb, kn, tq); nu = load_fp4(ua, ub, usa, usb, kn, tq); }
+        uint4 x[4];
+        load_x_fp4(x, xr, kb * 128, g, tq);
+        mma_block_fp4(accg, cg.wa, cg.wb, cg.sa, cg.sb, x);
+        mma_block_fp4(accu, cu.wa, cu.wb, cu.sa, cu.sb, x);
+        if (kn < nkb) { cg = ng; cu = nu; }
+    }
+    if (tq == 0) {   // column 0 of the tile: rows g and g + 8
+        red[warp][0][g] = accg[0]; red[warp][0][g + 8] = accg[2];
+        red[warp][1][g] = accu[0]; red[warp][1][g + 8] = accu[2];
+    }
+    __syncthreads();
+    if (threadIdx.x < 16 && i0 + threadIdx.x < I) {
+        float gv = 0.f, uv = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) { gv += red[w][0][threadIdx.x]; uv += red[w][1][threadIdx.x]; }
+        if (lim > 0.f) { uv = fminf(fmaxf(uv, -lim), lim); gv = fminf(gv, lim); }
+        h[((size_t)r * topk + s) * I + i0 + threadIdx.x] = gv / (1.f + __expf(-gv)) * uv * wts[(size_t)r * topk + s];
+    }
+}
+
+__global__ void __launch_bounds__(kNW * 32)
+expert_down_mma_kernel(const uint16_t* __restrict__ hh, const int* __restrict__ idx, const uint8_t* __restrict__ w2,
+                       const uint8_t* __restrict__ s2, float* __restrict__ y, int ldy, int topk, int I, int D, int accumulate) {
+    pdl_launch();
+    __shared__ float red[kNW][16];
+    const int r = blockIdx.y, c0 = blockIdx.x * 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+    const int nfull = I >> 7, nkb = (I + 127) >> 7, items = topk * nkb;   // a slot's last k-block may hold 64 values
+    const size_t wrow = (size_t)I / 2, srow = (size_t)I / 32;
+    const int ra = min(c0 + g, D - 1), rb = min(c0 + g + 8, D - 1);
+    pdl_wait();
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    auto load_item = [&](int it) {
+        const int s = it / nkb, kb = it - s * nkb;
+        const int e = idx[(size_t)r * topk + s];
+        const uint8_t* wb = w2 + (size_t)e * D * wrow;
+        const uint8_t* sb = s2 + (size_t)e * D * srow;
+        if (kb < nfull) return load_fp4(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
+        return load_fp4_tail(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
+    };
+    Fp4Frag cur, nxt;
+    if (warp < items) cur = load_item(warp);
+    for (int it = warp; it < items; it += kNW) {
+        const int in = it + kNW;
+        if (in < items) nxt = load_item(in);
+        const int s = it / nkb, kb = it - s * nkb;
+        const int nb = kb < nfull ? 4 : 2;
+        uint4 x[4];
+        load_x_fp4(x, hh + ((size_t)r * topk + s) * I, kb * 128, g, tq, nb);
+        mma_block_fp4(acc, cur.wa, cur.wb, cur.sa, cur.sb, x, nb);
+        if (in < items) cur = nxt;
+    }
+    if (tq == 0) { red[warp][g] = acc[0]; red[warp][g + 8] = acc[2]; }
+    __syncthreads();
+    if (threadIdx.x < 16 && c0 + threadIdx.x < D) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kNW; ++w) v += red[w][threadIdx.x];
+        float* o = y + (size_t)r * ldy + c0 + threadIdx.x;
+        *o = accumulate ? *o + v : v;
+    }
+}
+
+// In place, per row: inside every 64-byte group the 4 x 4 matrix of 32-bit words is transposed; a
+// 32-byte tail (rows that are an odd multiple of 64 values) is a 2 x 4 matrix: word (block b, position
+// q) moves to q * 2 + b.  One thread per group.
+__global__ void __launch_bounds__(256)
+fp4_repack_kernel(uint8_t* __restrict__ w, size_t rows, int row_bytes, int inverse) {
+    const int gpr = (row_bytes + 63) / 64;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * gpr) return;
+    const size_t row = i / gpr;
+    const int grp = (int)(i % gpr);
+    uint8_t* base = w + row * row_bytes + (size_t)grp * 64;
+    if (grp * 64 + 64 <= row_bytes) {
+        uint4* p = reinterpret_cast<uint4*>(base);
+        const uint4 a = p[0], b = p[1], c = p[2], d = p[3];
+        p[0] = make_uint4(a.x, b.x, c.x, d.x);
+        p[1] = make_uint4(a.y, b.y, c.y, d.y);
+        p[2] = make_uint4(a.z, b.z, c.z, d.z);
+        p[3] = make_uint4(a.w, b.w, c.w, d.w);
+    } else {
+        uint4* p = reinterpret_cast<uint4*>(base);
+        const uint4 a = p[0], b = p[1];
+        if (!inverse) {
+            p[0] = make_uint4(a.x, b.x, a.y, b.y);
+            p[1] = make_uint4(a.z, b.z, a.w, b.w);
+        } else {
+            p[0] = make_uint4(a.x, a.z, b.x, b.z);
+            p[1] = make_uint4(a.y, a.w, b.y, b.w);
+        }
+    }
+}
+
+}  // namespace
+
+// Quad-interleave packed e2m1 rows in place; inverse != 0 restores the original bytes.
+// row_bytes (= K / 2) must be a multiple of 32; 16-byte aligned base.
+FB_API int fb_d4_fp4_repack(void* w, int64_t rows, int64_t row_bytes, int64_t inverse, cudaStream_t st) {
+    if ((row_bytes % 32) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+    const size_t groups = (size_t)rows * ((row_bytes + 63) / 64);
+    if (!groups) return 0;
+    FB_LAUNCH((fp4_repack_kernel), (unsigned)((groups + 255) / 256), 256, 0, st, (uint8_t*)w, (size_t)rows, (int)row_bytes,
+              (int)inverse);
+    return FB_LAUNCH_CHECK();
+}
+
+// xh: f16 plane of the e4m3-round-tripped input rows (row stride ldx elements); w13 [E][2][I][K/2]
+// quad-interleaved, s13 [E][2][I][K/32]; h [rows][topk][I] f32.  K % 128 == 0.
+FB_API int fb_d4_expert_gate_up_mma(const void* xh, int64_t ldx, const int* idx, const float* wts, const void* w13,
+                                    const void* s13, float* h, int64_t n, int64_t topk, int64_t I, int64_t K, float lim,
+                                    cudaStream_t st) {
+    if ((K % 128) || (ldx % 8) || ((uintptr_t)xh & 15)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((expert_gate_up_mma_kernel), dim3((unsigned)((I + 15) / 16), (unsigned)topk, (unsigned)n), kNW * 32, 0, st,
+              (const uint16_t*)xh, (int)ldx, idx, wts, (const uint8_t*)w13, (const uint8_t*)s13, h, (int)topk, (int)I, (int)K, lim);
+    return FB_LAUNCH_CHECK();
+}
+
+// hh: f16 plane of the e4m3-round-tripped h [rows][topk][I]; w2 [E][D][I/2] quad-interleaved, s2 [E][D][I/32].
+// I % 64 == 0.
+FB_API int fb_d4_expert_down_mma(const void* hh, const int* idx, const void* w2, const void* s2, float* y, int64_t ldy,
+                                 int64_t n, int64_t topk, int64_t I, int64_t D, int64_t accumulate, cudaStream_t st) {
+    if ((I % 64) || ((uintptr_t)hh & 15)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((expert_down_mma_kernel), dim3((unsigned)((D + 15) / 16), (unsigned)n), kNW * 32, 0, st, (const uint16_t*)hh, idx,
+              (const uint8_t*)w2, (const uint8_t*)s2, y, (int)ldy, (int)topk, (int)I, (int)D, (int)accumulate);
+    return FB_LAUNCH_CHECK();
+}

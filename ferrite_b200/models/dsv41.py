@@ -20,6 +20,7 @@ with ue8m0 scales.  Replaces ``crates/ferrite-models/src/dsv41/chain_dev.rs`` (`
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -69,6 +70,8 @@ class Dsv41DeviceModel:
         self.tc_min_rows = 16
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
         self.tc_gemv_min_n = 0
+        self.fp4_mma = os.environ.get("FERRITE_D4_FP4_MMA", "1") != "0"   # tensor-core routed experts (decode rows)
+        self.fp4_mma_rows = 1 << 30
         self._tc_part = None
         self._tc_ticket = None
         # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
@@ -151,6 +154,11 @@ class Dsv41DeviceModel:
                 w2[e].copy_(pk)
                 s2[e].copy_(sc)
             L["w13"], L["s13"], L["w2"], L["s2"] = w13, s13, w2, s2
+        # tensor-core expert kernels want 128-value k-blocks and quad-interleaved weight bytes (repacked in place)
+        L["fp4_mma"] = self.fp4_mma and d % 128 == 0 and Il % 64 == 0
+        if L["fp4_mma"]:
+            for t in (L["w13"], L["w2"]):
+                self.K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 0)
         sw1, sw3, sw2 = (src.get(f + f"shared_experts.{n}.weight") for n in ("w1", "w3", "w2"))
         if self.shared_tp:
             lo = self.rank * self.Is
@@ -249,7 +257,7 @@ class Dsv41DeviceModel:
         ws["rlogit"] = self._z(M, Emax)
         ws["ridx"] = self._z(M, kmax, dtype=torch.int32)
         ws["rw"] = self._z(M, kmax)
-        ws["h"] = self._z(M * kmax, self.Il)
+        ws["h"] = Act(self.dev, M * kmax, self.Il)
         ws["gu"] = self._z(M, 2 * self.Is)
         ws["hs"] = Act(self.dev, M, self.Is)
         ws["logits"] = self._z(M, cfg.vocab_size)
@@ -330,10 +338,11 @@ class Dsv41DeviceModel:
         if self.world > 1:
             self.allreduce(t[:n])
 
-    def _quant(self, src_f, dst: Act, n, K, ld=None):
-        """dst.f / dst planes = e4m3-per-32 round trip of src (may alias dst.f)."""
+    def _quant(self, src_f, dst: Act, n, K, ld=None, mask=1):
+        """dst.f / dst planes = e4m3-per-32 round trip of src (may alias dst.f); mask 1: bf16 planes,
+        2: f16 planes, 3: both."""
         ld = ld if ld is not None else dst.ld
-        self.K.call("fb_d4_quant_rows", src_f, ld, dst.f, dst.ld, n, K, *dst.sp(1))
+        self.K.call("fb_d4_quant_rows", src_f, ld, dst.f, dst.ld, n, K, *dst.sp(mask))
 
     def _hc_post_mix(self, fn_next, n, first=False):
         cfg, ws = self.cfg, self.ws
@@ -463,11 +472,23 @@ class Dsv41DeviceModel:
         self.gemv(L["gate_w"], x, ws["rlogit"], n, E, d, ldo=ldl)
         self.K.call("fb_d4_route", ws["rlogit"], ldl, L["gate_b"], L["gate_bvl"], ws["is_image"] if L["gate_bvl"] is not None else None,
                     n, E, topk, float(cfg.route_scale), ws["ridx"], ws["rw"])
-        self._quant(x.f, xq, n, d)
-        self.K.call("fb_d4_expert_gate_up", xq.f, d, ws["ridx"], ws["rw"], L["w13"], L["s13"], ws["h"], n, topk, self.Il, d,
-                    float(cfg.swiglu_limit))
-        self.K.call("fb_d4_quant_rows", ws["h"], self.Il, ws["h"], self.Il, n * topk, self.Il, None, 0, 0, 0)
-        self.K.call("fb_d4_expert_down", ws["h"], ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
+        h = ws["h"]
+        if L["fp4_mma"] and n <= self.fp4_mma_rows:
+            # decode rows: e2m1 weights x f16 activations on the tensor cores (activations are e4m3 round trips,
+            # exact in f16), one (row, slot) pair per CTA column
+            self._quant(x.f, xq, n, d, mask=3)
+            f16 = lambda a: _lib.ctypes.c_void_p(a.s.data_ptr() + 4 * a.plane)   # plane 2 of the int16 planes
+            self.K.call("fb_d4_expert_gate_up_mma", f16(xq), xq.ld, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk,
+                        self.Il, d, float(cfg.swiglu_limit))
+            self.K.call("fb_d4_quant_rows", h.f, self.Il, h.f, self.Il, n * topk, self.Il, *h.sp(2))
+            self.K.call("fb_d4_expert_down_mma", f16(h), ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
+        else:
+            assert not L["fp4_mma"], "quad-interleaved expert weights need the tensor-core kernels"
+            self._quant(x.f, xq, n, d)
+            self.K.call("fb_d4_expert_gate_up", xq.f, d, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk, self.Il, d,
+                        float(cfg.swiglu_limit))
+            self.K.call("fb_d4_quant_rows", h.f, self.Il, h.f, self.Il, n * topk, self.Il, None, 0, 0, 0)
+            self.K.call("fb_d4_expert_down", h.f, ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
         if not self.shared_tp:
             self._reduce(ws["y"], n)
         hs = ws["hs"]

@@ -216,3 +216,48 @@ def test_vision_tower_and_image_rows():
     diff = (got_logits - want_logits).abs()
     ref_max = max(1.0, want_logits.abs().max().item())
     assert (diff > 3e-2 * ref_max).float().mean().item() < 0.01 and diff.max().item() < 0.25 * ref_max
+
+
+@pytest.mark.parametrize("n,topk,E,I,D", [(3, 2, 8, 192, 256), (1, 6, 16, 128, 512), (5, 3, 8, 320, 384)])
+def test_fp4_expert_mma_kernels_match_simt(K, n, topk, E, I, D):
+    """Tensor-core routed-expert kernels (quad-interleaved weights, f16 activations) against the SIMT kernels
+    on the original byte layout; the repack is an involution up to its inverse flag."""
+    from ferrite_b200.models.glm import Act
+    import ctypes
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(5)
+    w13 = torch.randint(0, 256, (E, 2, I, D // 2), dtype=torch.uint8, device=dev, generator=g)
+    s13 = torch.randint(118, 124, (E, 2, I, D // 32), dtype=torch.uint8, device=dev, generator=g)
+    w2 = torch.randint(0, 256, (E, D, I // 2), dtype=torch.uint8, device=dev, generator=g)
+    s2 = torch.randint(118, 124, (E, D, I // 32), dtype=torch.uint8, device=dev, generator=g)
+    idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:topk] for _ in range(n)]).to(torch.int32).contiguous()
+    wts = torch.rand(n, topk, device=dev, generator=g)
+    x = Act(dev, n, D)
+    x.f.copy_(torch.randn(n, D, device=dev, generator=g))
+    K.call("fb_d4_quant_rows", x.f, D, x.f, D, n, D, *x.sp(2))
+    h_ref, h = torch.zeros(n * topk, I, device=dev), Act(dev, n * topk, I)
+    y_ref, y = torch.zeros(n, D, device=dev), torch.full((n, D), 0.5, device=dev)
+    K.call("fb_d4_expert_gate_up", x.f, D, idx, wts, w13, s13, h_ref, n, topk, I, D, 10.0)
+    K.call("fb_d4_quant_rows", h_ref, I, h_ref, I, n * topk, I, None, 0, 0, 0)
+    K.call("fb_d4_expert_down", h_ref, idx, w2, s2, y_ref, D, n, topk, I, D, 0)
+    w13p, w2p = w13.clone(), w2.clone()
+    for t in (w13p, w2p):
+        K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 0)
+    f16 = lambda a: ctypes.c_void_p(a.s.data_ptr() + 4 * a.plane)
+    K.call("fb_d4_expert_gate_up_mma", f16(x), D, idx, wts, w13p, s13, h.f, n, topk, I, D, 10.0)
+    torch.cuda.synchronize()
+    # compare before the re-quantisation (which can flip a rounding on a last-bit difference)
+    h_raw = torch.zeros(n * topk, I, device=dev)
+    K.call("fb_d4_expert_gate_up", x.f, D, idx, wts, w13, s13, h_raw, n, topk, I, D, 10.0)
+    assert torch.allclose(h.f, h_raw, atol=1e-5 * max(1.0, h_raw.abs().max().item()), rtol=1e-4), (h.f - h_raw).abs().max().item()
+    h.f.copy_(h_ref)   # identical quantised input for the down comparison
+    K.call("fb_d4_quant_rows", h.f, I, h.f, I, n * topk, I, *h.sp(2))
+    K.call("fb_d4_expert_down_mma", f16(h), idx, w2p, s2, y, D, n, topk, I, D, 0)
+    torch.cuda.synchronize()
+    assert torch.allclose(y, y_ref, atol=1e-5 * max(1.0, y_ref.abs().max().item()), rtol=1e-4), (y - y_ref).abs().max().item()
+    K.call("fb_d4_expert_down_mma", f16(h), idx, w2p, s2, y, D, n, topk, I, D, 1)
+    torch.cuda.synchronize()
+    assert torch.allclose(y, 2 * y_ref, atol=2e-5 * max(1.0, y_ref.abs().max().item()), rtol=1e-4)
+    for t, orig in ((w13p, w13), (w2p, w2)):
+        K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 1)
+        assert torch.equal(t, orig)
