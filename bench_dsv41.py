@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=300)
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
+    ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -46,6 +47,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         from ferrite_b200.parallel.collective import make_allreduce
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * 8192, kind="p2p")
+    if args.pdl:
+        from ferrite_b200 import _lib
+        _lib.lib().lib.fb_set_pdl(1)
     L = args.layers
     assert L >= 4
     # one window-only layer, a ratio-2 source, a ratio-1 source (candidate source), an inheriting ratio-1 layer
@@ -90,7 +94,7 @@ def main():
                           "tokens_per_step": round(toks / args.steps, 3), "dtype": "bf16 dense / e2m1 experts",
                           "data": "synthetic", "config": {"dim": cfg.dim, "heads": cfg.n_heads, "experts": cfg.n_routed_experts,
                                                           "topk": cfg.n_activated_experts, "context": args.prompt_len,
-                                                          "parallelism": f"tp{world}", "spec": bool(args.spec)}}))
+                                                          "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl)}}))
     if world > 1:
         import torch.distributed as dist
         dist.barrier()

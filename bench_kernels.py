@@ -338,7 +338,9 @@ def main():
     K = _lib.lib()
     peak, tag = hbm_peak_gbs()
     rows = []
-    for c in make_cases(K, args.only):
+    cases = make_cases(K, args.only)
+    exact = [c for c in cases if c.name == args.only]   # a full case name runs that case alone
+    for c in exact or cases:
         for _ in range(args.warmup):
             c.fn()
         torch.cuda.synchronize()

@@ -72,19 +72,35 @@ quant_rows_kernel(const float* __restrict__ x, int ldx, float* __restrict__ xq, 
 // Computes this site's (pre, post, comb); `pre` is only stored (the NEXT site contracts with
 // it), the contraction uses pre_in, the coefficients of the previous site.
 //   xn = rmsnorm(sum_i pre_in[i] R_i) * ln_w
-__global__ void __launch_bounds__(512)
+// Block = C contraction warps + one coefficient warp.  All warps first sum the per-tile partial dots; then
+// the contraction warps (which only need the PREVIOUS site's `pre`) and the coefficient warp (sigmoids +
+// Sinkhorn, a serial chain of ~40 divisions) run side by side; the contraction warps meet on a named
+// barrier of their own.  A thread owns up to two float4 columns, loaded before the first barrier.
+__global__ void __launch_bounds__(1024)
 hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
                      const float* __restrict__ base, const float* __restrict__ ln_w, const float* __restrict__ pre_in,
                      float* __restrict__ pre_out, float* __restrict__ post_out, float* __restrict__ comb_out,
                      float* __restrict__ xn_out, float* __restrict__ xc_out, int H, float rms_eps, float hc_eps, int iters,
                      SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld) {
     PDL_PROLOGUE();
-    extern __shared__ float sh[];
-    float* red = sh;       // 32
-    float* xs = sh + 32;   // H
+    __shared__ float red[32];
     const int n = 4;
     const int r = blockIdx.x;
     const float* row = R + (size_t)r * n * H;
+    const int nct = blockDim.x - 32;              // contraction threads
+    const bool coef_warp = (int)threadIdx.x >= nct;
+    // residual loads first: they are in flight while the partial dots are summed
+    float4 v[2][4], lw[2];
+    bool act[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int j = (threadIdx.x + c * nct) * 4;
+        act[c] = !coef_warp && j < H;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            v[c][k] = act[c] ? *reinterpret_cast<const float4*>(row + (size_t)k * H + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        lw[c] = act[c] ? *reinterpret_cast<const float4*>(ln_w + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (acc && part_n) {
         // per-tile partial mix dots left by a fused GEMV epilogue: one warp per dot sums the tiles
         const int nt = part_n[r];
@@ -101,9 +117,10 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
             if (threadIdx.x == 0) part_n[r] = 0;
         }
     }
-    if (acc && threadIdx.x < 32) {
+    if (coef_warp) {
+        if (!acc) return;
         float* a = acc + (size_t)r * (kMaxMixD4 + 1);
-        const int lane = threadIdx.x;
+        const int lane = threadIdx.x & 31;
         const float rr = rsqrtf(a[kMaxMixD4] / (float)(n * H) + rms_eps);
         if (lane < n) {
             pre_out[(size_t)r * n + lane] = sigmoidf_(a[lane] * rr * scale[0] + base[lane]) + hc_eps;
@@ -121,34 +138,48 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
         c = on ? e / den + hc_eps : 0.f;
         float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
         cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-        c = c / (cs + hc_eps);
+        c = __fdividef(c, cs + hc_eps);
         for (int it = 1; it < iters; ++it) {
             float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
             rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-            c = c / (rs + hc_eps);
+            c = __fdividef(c, rs + hc_eps);
             cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
             cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-            c = c / (cs + hc_eps);
+            c = __fdividef(c, cs + hc_eps);
         }
         if (on) comb_out[(size_t)r * n * n + lane] = c;
         __syncwarp();
         if (lane <= kMaxMixD4) a[lane] = 0.f;
+        return;
     }
     const float p0 = pre_in[r * n + 0], p1 = pre_in[r * n + 1], p2 = pre_in[r * n + 2], p3 = pre_in[r * n + 3];
+    float4 x[2];
     float ss = 0.f;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        const float v = p0 * row[j] + p1 * row[H + j] + p2 * row[2 * H + j] + p3 * row[3 * H + j];
-        xs[j] = v;
-        ss += v * v;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        x[c].x = p0 * v[c][0].x + p1 * v[c][1].x + p2 * v[c][2].x + p3 * v[c][3].x;
+        x[c].y = p0 * v[c][0].y + p1 * v[c][1].y + p2 * v[c][2].y + p3 * v[c][3].y;
+        x[c].z = p0 * v[c][0].z + p1 * v[c][1].z + p2 * v[c][2].z + p3 * v[c][3].z;
+        x[c].w = p0 * v[c][0].w + p1 * v[c][1].w + p2 * v[c][2].w + p3 * v[c][3].w;
+        if (act[c]) ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
     }
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / H + rms_eps);
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        const float v = xs[j];
-        if (xc_out) xc_out[(size_t)r * H + j] = v;
-        const float o = v * inv * ln_w[j];
-        xn_out[(size_t)r * H + j] = o;
-        split_store(osp, r, j, o);
+    // sum over the contraction warps only (named barrier 1; the coefficient warp never joins it)
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
+    float tot = 0.f;
+    for (int w = 0; w < (nct >> 5); ++w) tot += red[w];
+    const float inv = rsqrtf(tot / H + rms_eps);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        if (!act[c]) continue;
+        const int j = (threadIdx.x + c * nct) * 4;
+        if (xc_out) *reinterpret_cast<float4*>(xc_out + (size_t)r * H + j) = x[c];
+        float4 o;
+        o.x = x[c].x * inv * lw[c].x; o.y = x[c].y * inv * lw[c].y; o.z = x[c].z * inv * lw[c].z; o.w = x[c].w * inv * lw[c].w;
+        *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
+        split_store(osp, r, j, o.x); split_store(osp, r, j + 1, o.y);
+        split_store(osp, r, j + 2, o.z); split_store(osp, r, j + 3, o.w);
     }
 }
 
@@ -1092,10 +1123,10 @@ FB_API int fb_d4_hc_pre(const float* R, float* acc, const float* scale, const fl
                         float* xc_out, int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
                         void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, const float* part, int* part_n,
                         int64_t part_ld, cudaStream_t st) {
-    if (mult != 4 || (part_n && n > 64)) return (int)cudaErrorInvalidValue;
-    const size_t sm = (32 + H) * sizeof(float);
-    if (sm > 48 * 1024) cudaFuncSetAttribute(hc_pre_offset_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
-    FB_LAUNCH((hc_pre_offset_kernel), n, 512, sm, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,
+    if (mult != 4 || (part_n && n > 64) || (H % 4)) return (int)cudaErrorInvalidValue;
+    const int nct = (int)(((H / 4 + 1) / 2 + 31) / 32 * 32);   // two float4 columns per contraction thread
+    if (nct + 32 > 1024) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((hc_pre_offset_kernel), n, nct + 32, 0, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,
               xn_out, xc_out, (int)H, rms_eps, hc_eps, (int)iters, mk_split(s_base, s_ld, s_plane, s_mask), part, part_n,
               (int)part_ld);
     return FB_LAUNCH_CHECK();

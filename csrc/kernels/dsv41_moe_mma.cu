@@ -11,9 +11,9 @@
 // 64-byte group of a row (128 values = 4 scale blocks x 4 words), word (block b, position q) moves to
 // (position q, block b).  Lane q of a quad then reads 16 bytes = its 8 values of each of the 4 blocks.
 //
-// gate/up:  grid (I / 16, topk, rows): 16 intermediate channels of one (row, slot) pair; the warps split K,
-//           partial tiles meet in shared memory, the epilogue applies the clamped SwiGLU and the routing
-//           weight.
+// gate/up:  grid (I / 8, topk, rows): 8 intermediate channels of one (row, slot) pair (gate rows in the upper
+//           half of the MMA tile, up rows in the lower half); the warps split K, partial tiles meet in shared
+//           memory, the epilogue applies the clamped SwiGLU and the routing weight.
 // down:     grid (D / 16, rows): 16 output channels; the warps split the (slot, k-block) list.
 // Replaces the reference's `expert_gemv_fp4_*` decode kernels (kernels/cuda/dsv41_kernels.cu).
 #include <cuda_fp8.h>
@@ -90,42 +90,44 @@ __device__ __forceinline__ Fp4Frag load_fp4_tail(const uint8_t* __restrict__ wa,
 
 constexpr int kNW = 8;
 
+// One 16-row MMA tile holds 8 intermediate channels: rows 0..7 are their GATE rows, rows 8..15 their UP rows,
+// so a thread's accumulators d[0] / d[2] are the gate and up value of the same channel and the SwiGLU needs
+// no exchange.  Small tiles keep the grid large at tensor-parallel slice sizes (I = 320: 240 CTAs) and the
+// register count low enough for a two-deep prefetch of the weight fragments.
 __global__ void __launch_bounds__(kNW * 32)
 expert_gate_up_mma_kernel(const uint16_t* __restrict__ xh, int ldx, const int* __restrict__ idx, const float* __restrict__ wts,
                           const uint8_t* __restrict__ w13, const uint8_t* __restrict__ s13, float* __restrict__ h, int topk,
                           int I, int K, float lim) {
     pdl_launch();
-    __shared__ float red[kNW][2][16];
-    const int r = blockIdx.z, s = blockIdx.y, i0 = blockIdx.x * 16;
+    __shared__ float red[kNW][2][8];
+    const int r = blockIdx.z, s = blockIdx.y, i0 = blockIdx.x * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     const int nkb = K >> 7;
     const size_t wrow = (size_t)K / 2, srow = (size_t)K / 32;
     pdl_wait();
     const int e = idx[(size_t)r * topk + s];
-    const int ra = min(i0 + g, I - 1), rb = min(i0 + g + 8, I - 1);
-    const uint8_t* wg = w13 + (size_t)e * 2 * I * wrow;
-    const uint8_t* sg = s13 + (size_t)e * 2 * I * srow;
-    const uint8_t *ga = wg + ra * wrow, *gb = wg + rb * wrow, *ua = wg + (I + ra) * wrow, *ub = wg + (I + rb) * wrow;
-    const uint8_t *gsa = sg + ra * srow, *gsb = sg + rb * srow, *usa = sg + (I + ra) * srow, *usb = sg + (I + rb) * srow;
+    const int ri = min(i0 + g, I - 1);
+    const uint8_t* wg = w13 + ((size_t)e * 2 * I + ri) * wrow;       // gate row
+    const uint8_t* wu = wg + (size_t)I * wrow;                       // up row
+    const uint8_t* sg = s13 + ((size_t)e * 2 * I + ri) * srow;
+    const uint8_t* su = sg + (size_t)I * srow;
     const uint16_t* xr = xh + (size_t)r * ldx;
-    float accg[4] = {0.f, 0.f, 0.f, 0.f}, accu[4] = {0.f, 0.f, 0.f, 0.f};
-    Fp4Frag cg, cu, ng, nu;
-    if (warp < nkb) { cg = load_fp4(ga, gb, gsa, gsb, warp, tq); cu = load_fp4(ua, ub, usa, usb, warp, tq); }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    Fp4Frag f0, f1, f2;
+    if (warp < nkb) f0 = load_fp4(wg, wu, sg, su, warp, tq);
+    if (warp + kNW < nkb) f1 = load_fp4(wg, wu, sg, su, warp + kNW, tq);
     for (int kb = warp; kb < nkb; kb += kNW) {
-        const int kn = kb + kNW;
-        if (kn < nkb) { ng = load_fp4(ga, gb, gsa, gsb, kn, tq); nu = load_fp4(ua, ub, usa, usb, kn, tq); }
+        const int k2 = kb + 2 * kNW;
+        if (k2 < nkb) f2 = load_fp4(wg, wu, sg, su, k2, tq);
         uint4 x[4];
         load_x_fp4(x, xr, kb * 128, g, tq);
-        mma_block_fp4(accg, cg.wa, cg.wb, cg.sa, cg.sb, x);
-        mma_block_fp4(accu, cu.wa, cu.wb, cu.sa, cu.sb, x);
-        if (kn < nkb) { cg = ng; cu = nu; }
+        mma_block_fp4(acc, f0.wa, f0.wb, f0.sa, f0.sb, x);
+        f0 = f1;
+        f1 = f2;
     }
-    if (tq == 0) {   // column 0 of the tile: rows g and g + 8
-        red[warp][0][g] = accg[0]; red[warp][0][g + 8] = accg[2];
-        red[warp][1][g] = accu[0]; red[warp][1][g + 8] = accu[2];
-    }
+    if (tq == 0) { red[warp][0][g] = acc[0]; red[warp][1][g] = acc[2]; }   // column 0: gate (row g), up (row g + 8)
     __syncthreads();
-    if (threadIdx.x < 16 && i0 + threadIdx.x < I) {
+    if (threadIdx.x < 8 && i0 + threadIdx.x < I) {
         float gv = 0.f, uv = 0.f;
 #pragma unroll
         for (int w = 0; w < kNW; ++w) { gv += red[w][0][threadIdx.x]; uv += red[w][1][threadIdx.x]; }
@@ -154,17 +156,19 @@ expert_down_mma_kernel(const uint16_t* __restrict__ hh, const int* __restrict__ 
         if (kb < nfull) return load_fp4(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
         return load_fp4_tail(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
     };
-    Fp4Frag cur, nxt;
-    if (warp < items) cur = load_item(warp);
+    Fp4Frag f0, f1, f2;
+    if (warp < items) f0 = load_item(warp);
+    if (warp + kNW < items) f1 = load_item(warp + kNW);
     for (int it = warp; it < items; it += kNW) {
-        const int in = it + kNW;
-        if (in < items) nxt = load_item(in);
+        const int i2 = it + 2 * kNW;
+        if (i2 < items) f2 = load_item(i2);
         const int s = it / nkb, kb = it - s * nkb;
         const int nb = kb < nfull ? 4 : 2;
         uint4 x[4];
         load_x_fp4(x, hh + ((size_t)r * topk + s) * I, kb * 128, g, tq, nb);
-        mma_block_fp4(acc, cur.wa, cur.wb, cur.sa, cur.sb, x, nb);
-        if (in < items) cur = nxt;
+        mma_block_fp4(acc, f0.wa, f0.wb, f0.sa, f0.sb, x, nb);
+        f0 = f1;
+        f1 = f2;
     }
     if (tq == 0) { red[warp][g] = acc[0]; red[warp][g + 8] = acc[2]; }
     __syncthreads();
@@ -227,7 +231,7 @@ FB_API int fb_d4_expert_gate_up_mma(const void* xh, int64_t ldx, const int* idx,
                                     const void* s13, float* h, int64_t n, int64_t topk, int64_t I, int64_t K, float lim,
                                     cudaStream_t st) {
     if ((K % 128) || (ldx % 8) || ((uintptr_t)xh & 15)) return (int)cudaErrorInvalidValue;
-    FB_LAUNCH((expert_gate_up_mma_kernel), dim3((unsigned)((I + 15) / 16), (unsigned)topk, (unsigned)n), kNW * 32, 0, st,
+    FB_LAUNCH((expert_gate_up_mma_kernel), dim3((unsigned)((I + 7) / 8), (unsigned)topk, (unsigned)n), kNW * 32, 0, st,
               (const uint16_t*)xh, (int)ldx, idx, wts, (const uint8_t*)w13, (const uint8_t*)s13, h, (int)topk, (int)I, (int)K, lim);
     return FB_LAUNCH_CHECK();
 }
