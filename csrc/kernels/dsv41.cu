@@ -138,14 +138,14 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
         c = on ? e / den + hc_eps : 0.f;
         float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
         cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-        c = __fdividef(c, cs + hc_eps);
+        c = c / (cs + hc_eps);
         for (int it = 1; it < iters; ++it) {
             float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
             rs += __shfl_xor_sync(0xffffffffu, rs, 2);
-            c = __fdividef(c, rs + hc_eps);
+            c = c / (rs + hc_eps);
             cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
             cs += __shfl_xor_sync(0xffffffffu, cs, 8);
-            c = __fdividef(c, cs + hc_eps);
+            c = c / (cs + hc_eps);
         }
         if (on) comb_out[(size_t)r * n * n + lane] = c;
         __syncwarp();
