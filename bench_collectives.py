@@ -10,6 +10,7 @@ the measured peer-copy bandwidth of this pool); `frac` = roofline / achieved.
 Cases
   ar_oneshot.<rows>x4096      one-shot all-reduce (baseline for the fused kernels) vs NCCL all-reduce
   gemv_ar.<site>              GEMV + all-reduce (+ fold) in one kernel vs GEMV, all-reduce, hc_post_mix separately
+  gemm_ar.<site>.m<rows>      prefill rows: tcgen05 GEMM + two-shot all-reduce in one kernel vs GEMM, then all-reduce
   argmax_xchg                 vocab-sliced argmax merge
   dcp_merge                   cross-rank LSE merge of attention partials
   ep_moe                      dispatch -> grouped experts -> combine
@@ -69,7 +70,8 @@ def main():
     from ferrite_b200 import _lib
     from ferrite_b200.models.glm import Act
     from ferrite_b200.parallel.ep import EpMoE
-    from ferrite_b200.parallel.symm import CrossRankArgmax, DcpAttentionMerge, FusedGemvAllReduce, P2PAllReduce
+    from ferrite_b200.parallel.symm import (CrossRankArgmax, DcpAttentionMerge, FusedGemmAllReduce, FusedGemvAllReduce,
+                                            P2PAllReduce)
     K = _lib.lib()
     hbm = hbm_gbs()
     rows = []
@@ -140,6 +142,39 @@ def main():
         add(f"separate.{site}", timed(separate, args.iters), wbytes + 24 * 4 * H * 4, link, "gemv + all-reduce + hc_post_mix")
     fused.check()
 
+    # ---- prefill GEMM + two-shot all-reduce -----------------------------------------------------------
+    gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096)
+    tc_status = torch.zeros(4, dtype=torch.int32, device=dev)
+    for site, Kfull, M in (("gdn_o_proj", 8192, 256), ("dsa_o_proj", 16384, 256), ("gdn_o_proj", 8192, 64)):
+        Kl = Kfull // world
+        reps = max(2, int(300e6 // (H * Kl * 2)) + 1)
+        ws = [torch.randn(H, Kl, device=dev, dtype=torch.bfloat16) for _ in range(reps)]
+        xb = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
+        yg = torch.zeros(M, H, device=dev)
+        st = {"i": 0}
+
+        def fused_gemm():
+            w = ws[st["i"] % reps]; st["i"] += 1
+            gar(w, xb, Kl, yg, H, M, H, Kl, False)
+
+        def separate_gemm():
+            w = ws[st["i"] % reps]; st["i"] += 1
+            K.call("fb_gemm_tc_bf16", w, xb, Kl, yg, H, M, H, Kl, 0, tc_status)
+            step = ar.max_elems // H
+            for r0 in range(0, M, step):
+                ar(yg[r0:min(M, r0 + step)])
+
+        flops_us = 2.0 * M * H * Kl / 1611e12 * 1e6
+        link = 2 * (world - 1) * M * H * 4 // world       # reduce-scatter + all-gather volume per GPU
+        us_f = timed(fused_gemm, args.iters)
+        us_s = timed(separate_gemm, args.iters)
+        roof = max(H * Kl * 2 / hbm / 1e3, link / NVLINK_GBS / 1e3, flops_us)
+        rows.append({"case": f"gemm_ar.{site}.m{M}", "us": round(us_f, 2), "roofline_us": round(roof, 2),
+                     "frac": round(roof / us_f, 3), "note": f"K/rank={Kl}; tcgen05 GEMM + two-shot all-reduce, one launch"})
+        rows.append({"case": f"separate_gemm.{site}.m{M}", "us": round(us_s, 2), "roofline_us": round(roof, 2),
+                     "frac": round(roof / us_s, 3), "note": "tcgen05 GEMM, then one-shot all-reduce in 64-row chunks"})
+    gar.check()
+
     # ---- cross-rank argmax --------------------------------------------------------------------------
     xa = CrossRankArgmax(dev, rank, world)
     V = 154880 // world
@@ -188,7 +223,7 @@ def main():
             with open(args.json, "w") as f:
                 json.dump({"world": world, "rows": rows}, f, indent=1)
     dist.barrier()
-    for o in (ar, fused, xa, dm, ep):
+    for o in (ar, fused, gar, xa, dm, ep):
         o.close()
     dist.destroy_process_group()
 
