@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--layers", type=int, default=0, help="0 = the full 45-layer model")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed ticks with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
 
     from ferrite_b200.config import EngineConfig, GlmConfig
@@ -73,6 +75,8 @@ def main():
         assert ticks < 10000 and not eng.idle(), "the sequences finished before the timed window began"
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     e0.record()
     for _ in range(args.window):
         for _, ev in eng.tick():
@@ -80,6 +84,8 @@ def main():
                 produced += len(ev.ids)
     e1.record()
     torch.cuda.synchronize()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1)
     if world > 1:
         import torch.distributed as dist

@@ -143,7 +143,8 @@ def main():
     fused.check()
 
     # ---- prefill GEMM + two-shot all-reduce -----------------------------------------------------------
-    gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096)
+    gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096, mode=2)    # two-shot
+    gar1 = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096, mode=1)   # one-shot (needs world x the staging)
     tc_status = torch.zeros(4, dtype=torch.int32, device=dev)
     for site, Kfull, M in (("gdn_o_proj", 8192, 256), ("dsa_o_proj", 16384, 256), ("gdn_o_proj", 8192, 64)):
         Kl = Kfull // world
@@ -157,6 +158,10 @@ def main():
             w = ws[st["i"] % reps]; st["i"] += 1
             gar(w, xb, Kl, yg, H, M, H, Kl, False)
 
+        def fused_gemm1():
+            w = ws[st["i"] % reps]; st["i"] += 1
+            gar1(w, xb, Kl, yg, H, M, H, Kl, False)
+
         def separate_gemm():
             w = ws[st["i"] % reps]; st["i"] += 1
             K.call("fb_gemm_tc_bf16", w, xb, Kl, yg, H, M, H, Kl, 0, tc_status)
@@ -169,11 +174,17 @@ def main():
         us_f = timed(fused_gemm, args.iters)
         us_s = timed(separate_gemm, args.iters)
         roof = max(H * Kl * 2 / hbm / 1e3, link / NVLINK_GBS / 1e3, flops_us)
-        rows.append({"case": f"gemm_ar.{site}.m{M}", "us": round(us_f, 2), "roofline_us": round(roof, 2),
+        rows.append({"case": f"gemm_ar.{site}.m{M}.twoshot", "us": round(us_f, 2), "roofline_us": round(roof, 2),
                      "frac": round(roof / us_f, 3), "note": f"K/rank={Kl}; tcgen05 GEMM + two-shot all-reduce, one launch"})
+        if world == 2 or (world - 1) * M * H * 4 <= (8 << 20):
+            us_1 = timed(fused_gemm1, args.iters)
+            roof1 = max(H * Kl * 2 / hbm / 1e3, (world - 1) * M * H * 4 / NVLINK_GBS / 1e3, flops_us)
+            rows.append({"case": f"gemm_ar.{site}.m{M}.oneshot", "us": round(us_1, 2), "roofline_us": round(roof1, 2),
+                         "frac": round(roof1 / us_1, 3), "note": "every tile pushed to every rank, one publish / wait round"})
         rows.append({"case": f"separate_gemm.{site}.m{M}", "us": round(us_s, 2), "roofline_us": round(roof, 2),
                      "frac": round(roof / us_s, 3), "note": "tcgen05 GEMM, then one-shot all-reduce in 64-row chunks"})
     gar.check()
+    gar1.check()
 
     # ---- cross-rank argmax --------------------------------------------------------------------------
     xa = CrossRankArgmax(dev, rank, world)
@@ -223,7 +234,7 @@ def main():
             with open(args.json, "w") as f:
                 json.dump({"world": world, "rows": rows}, f, indent=1)
     dist.barrier()
-    for o in (ar, fused, gar, xa, dm, ep):
+    for o in (ar, fused, gar, gar1, xa, dm, ep):
         o.close()
     dist.destroy_process_group()
 

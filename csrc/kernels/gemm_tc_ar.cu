@@ -17,7 +17,9 @@
 //   gather   second ticket + stamp among the tiles this rank owns; every CTA then waits
 //            (bounded) for the stamp of its tile's owner and copies the tile to `out`.
 // Per rank (world - 1) / world of the output crosses NVLink twice: the reduce-scatter +
-// all-gather volume, against (world - 1) x for a one-shot push of whole tiles.
+// all-gather volume, against (world - 1) x for a one-shot push of whole tiles.  With two ranks, or
+// when the whole one-shot volume is under 1 MiB, the kernel runs ONE-SHOT instead: every tile goes to
+// every rank, one publish / wait round, and each CTA reduces its tile straight into `out`.
 // The grid must be co-resident (checked on the host with the occupancy API): a CTA only
 // waits for CTAs of OTHER ranks that are running or done, never for an unscheduled one.
 // Every wait is bounded; on expiry the kernel records {TIMEOUT, phase * 16 + peer, epoch,
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                   float* __restrict__ out, int ldo, int M, int N, int K, int accumulate, GarPtrs t,
                   uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status, int rank, int world,
-                  int tiles_per_rank, int max_spins) {
+                  int tiles_per_rank, int max_spins, int oneshot) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -162,9 +164,9 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         if (go) {
             const int nl = q * 32 + lane;
             const int n = n0 + nl;
-            float* dst = world > 1
-                ? t.scatter[owner] + (((size_t)par * world + rank) * tiles_per_rank + tile / world) * C::kTileElems + nl
-                : nullptr;
+            // two-shot: the tile goes to its owner only; one-shot: to every rank (slot index = tile)
+            const size_t slot_off = (((size_t)par * world + rank) * tiles_per_rank + (oneshot ? tile : tile / world)) * C::kTileElems + nl;
+            float* dst = world > 1 && !oneshot ? t.scatter[owner] + slot_off : nullptr;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 8) {
                 float v[8];
@@ -178,7 +180,10 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
                             if (accumulate) a += *o;
                             if (world == 1) *o = a;
                         }
-                        if (world > 1) dst[(size_t)(c + i) * kTileW] = a;   // 128 bytes per warp and row
+                        if (dst) dst[(size_t)(c + i) * kTileW] = a;   // 128 bytes per warp and row
+                        else if (world > 1) {
+                            for (int p = 0; p < world; ++p) t.scatter[p][slot_off + (size_t)(c + i) * kTileW] = a;
+                        }
                     }
                 }
             }
@@ -206,7 +211,7 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
             epoch[0] = e;   // every CTA read the old value before it took its ticket
         }
     }
-    const bool mine = owner == rank;
+    const bool mine = oneshot || owner == rank;
     if (mine && threadIdx.x < world) {
         const uint32_t* f = t.flags[rank] + (((size_t)par * 2 + 0) * world + threadIdx.x) * kFlagPad;
         if (!wait_flag(f, e, max_spins) && atomicCAS(&s_fail, 0, 1) == 0) {
@@ -214,6 +219,25 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
         }
     }
     __syncthreads();
+    if (oneshot) {
+        // ---- one-shot: every rank holds all partials of every tile; reduce in rank order straight into `out` ----
+        if (s_fail == 0) {
+            const float* src0 = t.scatter[rank] + ((size_t)par * world * tiles_per_rank + tile) * C::kTileElems;
+            const size_t slot = (size_t)tiles_per_rank * C::kTileElems;
+            for (int i = threadIdx.x; i < rows * (kTileW / 4); i += kThreads) {
+                const int rr = i / (kTileW / 4), c4 = i % (kTileW / 4);
+                const int n = n0 + c4 * 4;
+                if (n >= N) continue;
+                float4 a = ld_cg_f4(src0 + (size_t)i * 4);
+                for (int s = 1; s < world; ++s) {
+                    const float4 b = ld_cg_f4(src0 + s * slot + (size_t)i * 4);
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
+                *reinterpret_cast<float4*>(out + (size_t)(m0 + rr) * ldo + n) = a;
+            }
+        }
+        return;
+    }
     if (mine && s_fail == 0) {
         // ---- reduce this tile in rank order and hand it to every rank ----
         const float* src0 = t.scatter[rank] + ((size_t)par * world * tiles_per_rank + tile / world) * C::kTileElems;
@@ -260,7 +284,7 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
 template <int BN>
 int launch_gar(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo, int M, int N, int K, int accumulate,
                const GarPtrs& t, uint32_t* epoch, unsigned* ticket, int* status, int rank, int world, int64_t scatter_cap,
-               int64_t gather_cap, int max_spins, cudaStream_t st) {
+               int64_t gather_cap, int max_spins, int mode, cudaStream_t st) {
     auto k = gemm_tc_ar_kernel<BN>;
     static int resident = -1;
     if (resident < 0) {
@@ -275,14 +299,18 @@ int launch_gar(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo
     }
     dim3 grid((N + kTileW - 1) / kTileW, (M + BN - 1) / BN);
     const int ntiles = (int)(grid.x * grid.y);
-    const int tpr = (ntiles + world - 1) / world;
+    // one round trip instead of two when the one-shot volume is the same (two ranks) or small, and it fits
+    const int64_t tile_elems = Cfg<BN>::kTileElems;
+    const bool want_one = mode == 1 || (mode == 0 && (world == 2 || (int64_t)(world - 1) * ntiles * tile_elems * 4 <= (1 << 20)));
+    const bool oneshot = world > 1 && want_one && (int64_t)2 * world * ntiles * tile_elems <= scatter_cap;
+    const int tpr = oneshot ? ntiles : (ntiles + world - 1) / world;
     if (world > 1) {
         if (ntiles > resident || ntiles < world) return (int)cudaErrorInvalidValue;   // co-residency; every rank owns a tile
-        if ((int64_t)2 * world * tpr * Cfg<BN>::kTileElems > scatter_cap) return (int)cudaErrorInvalidValue;
-        if ((int64_t)2 * ntiles * Cfg<BN>::kTileElems > gather_cap) return (int)cudaErrorInvalidValue;
+        if ((int64_t)2 * world * tpr * tile_elems > scatter_cap) return (int)cudaErrorInvalidValue;
+        if (!oneshot && (int64_t)2 * ntiles * tile_elems > gather_cap) return (int)cudaErrorInvalidValue;
     }
     FB_LAUNCH((k), grid, kThreads, Cfg<BN>::kSmem, st, tw, tx, out, ldo, M, N, K, accumulate, t, epoch, ticket, status, rank,
-              world, tpr, max_spins);
+              world, tpr, max_spins, (int)oneshot);
     return FB_LAUNCH_CHECK();
 }
 
@@ -302,11 +330,11 @@ FB_API int fb_gemm_tc_ar_plan(int64_t M, int64_t N, int* bn_out, int* ntiles_out
 // ldo, ldo % 4 == 0, 16-byte aligned).  scatter_ptrs / gather_ptrs / flag_ptrs: host arrays of `world` device
 // pointers into peer-mapped buffers of scatter_cap / gather_cap floats and 4 * world * 32 words; epoch: one
 // word, ticket: two words (all zero-initialised, private to this collective).  With accumulate != 0 the local
-// `out` is added to this rank's partial before the reduction.
+// `out` is added to this rank's partial before the reduction.  mode: 0 = choose, 1 = one-shot, 2 = two-shot.
 FB_API int fb_gemm_tc_ar(const void* W, const void* x, int64_t ldx, float* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          int64_t accumulate, const void* const* scatter_ptrs, const void* const* gather_ptrs,
                          const void* const* flag_ptrs, int64_t scatter_cap, int64_t gather_cap, void* epoch, void* ticket,
-                         int* status, int64_t rank, int64_t world, int64_t max_spins, cudaStream_t st) {
+                         int* status, int64_t rank, int64_t world, int64_t max_spins, int64_t mode, cudaStream_t st) {
     if ((K % 8) || (ldx % 8) || (ldo % 4) || (N % 4) || M < 1 || world < 1 || world > kMaxWorld || ((uintptr_t)x & 15) ||
         ((uintptr_t)out & 15))
         return (int)cudaErrorInvalidValue;
@@ -325,7 +353,7 @@ FB_API int fb_gemm_tc_ar(const void* W, const void* x, int64_t ldx, float* out, 
     rc = fb_make_tmap_2d_strided(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)(bn < 16 ? 16 : bn), kBK, 2);
     if (rc) return rc;
 #define GAR_ARGS tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, t, (uint32_t*)epoch, (unsigned*)ticket, status, \
-                 (int)rank, (int)world, scatter_cap, gather_cap, (int)max_spins, st
+                 (int)rank, (int)world, scatter_cap, gather_cap, (int)max_spins, (int)mode, st
     switch (bn) {
         case 16: return launch_gar<16>(GAR_ARGS);
         case 32: return launch_gar<32>(GAR_ARGS);

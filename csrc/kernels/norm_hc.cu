@@ -197,9 +197,12 @@ hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, c
     }
 }
 
-// One block per row, one float4 column per thread (H/4 <= 1024 threads).  The residual
-// loads are issued before the barrier so they overlap warp 0's coefficient math; the
-// accumulator is cleared for reuse.
+// One block per row: C contraction warps (a thread owns up to two float4 columns, loaded before the first
+// barrier) plus one coefficient warp.  After the per-tile partial dots are summed, every contraction thread
+// derives the four `pre` weights itself (four sigmoids of the accumulated dots) and contracts right away,
+// while the coefficient warp runs the serial part - `post`, the row softmax and the Sinkhorn iterations of
+// `comb` - side by side.  The contraction warps meet on a named barrier of their own; a second named
+// barrier lets the coefficient warp clear the accumulator only after everyone has read it.
 __global__ void __launch_bounds__(1024)
 hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const float* __restrict__ scale,
                     const float* __restrict__ base, const float* __restrict__ ln_w,
@@ -208,8 +211,21 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
                     SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld) {
     PDL_PROLOGUE();
     __shared__ float red[32];
-    __shared__ float pre[8];
     const int r = blockIdx.x;
+    const int nct = blockDim.x - 32;
+    const bool coef_warp = (int)threadIdx.x >= nct;
+    const float* row = R + (size_t)r * n * H;
+    float4 v[2][4], lw[2];
+    bool act[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const int j = (threadIdx.x + c * nct) * 4;
+        act[c] = !coef_warp && j < H;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            v[c][k] = act[c] ? *reinterpret_cast<const float4*>(row + (size_t)k * H + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        lw[c] = act[c] ? *reinterpret_cast<const float4*>(ln_w + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (part_n) {
         // per-tile partial mix dots left by a fused GEMV epilogue: one warp per dot sums the tiles
         const int nt = part_n[r];
@@ -226,21 +242,11 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
             if (threadIdx.x == 0) part_n[r] = 0;
         }
     }
-    const float* row = R + (size_t)r * n * H;
-    const int j = threadIdx.x * 4;
-    const bool act = j < H;
-    float4 v[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = act ? *reinterpret_cast<const float4*>(row + (size_t)k * H + j) : make_float4(0, 0, 0, 0);
-    const float4 lw = act ? *reinterpret_cast<const float4*>(ln_w + j) : make_float4(0, 0, 0, 0);
     float* a = acc + (size_t)r * (kMaxMix + 1);
-    if (threadIdx.x < 32) {
-        const int lane = threadIdx.x;
-        const float rr = rsqrtf(a[kMaxMix] / (float)(n * H) + rms_eps);
-        if (lane < n) {
-            pre[lane] = sigmoidf_(a[lane] * rr * scale[0] + base[lane]) + hc_eps;
-            post_out[(size_t)r * n + lane] = 2.f * sigmoidf_(a[n + lane] * rr * scale[1] + base[n + lane]);
-        }
+    const float rr = rsqrtf(a[kMaxMix] / (float)(n * H) + rms_eps);
+    if (coef_warp) {
+        const int lane = threadIdx.x & 31;
+        if (lane < n) post_out[(size_t)r * n + lane] = 2.f * sigmoidf_(a[n + lane] * rr * scale[1] + base[n + lane]);
         // comb element (i = lane / n, k = lane % n); n == 4 so rows are 4-lane groups
         float c = 0.f;
         const bool on = lane < n * n;
@@ -264,22 +270,37 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
             c = __fdividef(c, cs + hc_eps);
         }
         if (on) comb_out[(size_t)r * n * n + lane] = c;
-        __syncwarp();
+        asm volatile("bar.sync 2, %0;" ::"r"((int)blockDim.x) : "memory");   // everyone has read the accumulator
         if (lane <= kMaxMix) a[lane] = 0.f;
+        return;
     }
-    __syncthreads();
-    float4 x;
-    x.x = pre[0] * v[0].x + pre[1] * v[1].x + pre[2] * v[2].x + pre[3] * v[3].x;
-    x.y = pre[0] * v[0].y + pre[1] * v[1].y + pre[2] * v[2].y + pre[3] * v[3].y;
-    x.z = pre[0] * v[0].z + pre[1] * v[1].z + pre[2] * v[2].z + pre[3] * v[3].z;
-    x.w = pre[0] * v[0].w + pre[1] * v[1].w + pre[2] * v[2].w + pre[3] * v[3].w;
-    float ss = act ? x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w : 0.f;
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / H + rms_eps);
-    if (act) {
-        if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)r * H + j) = x;
+    const float s0 = scale[0];
+    const float p0 = sigmoidf_(a[0] * rr * s0 + base[0]) + hc_eps, p1 = sigmoidf_(a[1] * rr * s0 + base[1]) + hc_eps;
+    const float p2 = sigmoidf_(a[2] * rr * s0 + base[2]) + hc_eps, p3 = sigmoidf_(a[3] * rr * s0 + base[3]) + hc_eps;
+    asm volatile("bar.arrive 2, %0;" ::"r"((int)blockDim.x) : "memory");
+    float4 x[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        x[c].x = p0 * v[c][0].x + p1 * v[c][1].x + p2 * v[c][2].x + p3 * v[c][3].x;
+        x[c].y = p0 * v[c][0].y + p1 * v[c][1].y + p2 * v[c][2].y + p3 * v[c][3].y;
+        x[c].z = p0 * v[c][0].z + p1 * v[c][1].z + p2 * v[c][2].z + p3 * v[c][3].z;
+        x[c].w = p0 * v[c][0].w + p1 * v[c][1].w + p2 * v[c][2].w + p3 * v[c][3].w;
+        if (act[c]) ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    asm volatile("bar.sync 1, %0;" ::"r"(nct) : "memory");
+    float tot = 0.f;
+    for (int w = 0; w < (nct >> 5); ++w) tot += red[w];
+    const float inv = rsqrtf(tot / H + rms_eps);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        if (!act[c]) continue;
+        const int j = (threadIdx.x + c * nct) * 4;
+        if (x_out) *reinterpret_cast<float4*>(x_out + (size_t)r * H + j) = x[c];
         float4 o;
-        o.x = x.x * inv * lw.x; o.y = x.y * inv * lw.y; o.z = x.z * inv * lw.z; o.w = x.w * inv * lw.w;
+        o.x = x[c].x * inv * lw[c].x; o.y = x[c].y * inv * lw[c].y; o.z = x[c].z * inv * lw[c].z; o.w = x[c].w * inv * lw[c].w;
         *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
         split_store(osp, r, j, o.x); split_store(osp, r, j + 1, o.y);
         split_store(osp, r, j + 2, o.z); split_store(osp, r, j + 3, o.w);
@@ -379,9 +400,10 @@ FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const
                            int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
                            const float* part, int* part_n, int64_t part_ld, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
-    if (mult != 4 || (H % 4) || H / 4 > 1024 || (part_n && n > 64)) return (int)cudaErrorInvalidValue;
-    const int threads = (int)(((H / 4) + 31) / 32 * 32);
-    FB_LAUNCH((hc_pre_apply_kernel), n, threads, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
+    if (mult != 4 || (H % 4) || (part_n && n > 64)) return (int)cudaErrorInvalidValue;
+    const int nct = (int)(((H / 4 + 1) / 2 + 31) / 32 * 32);   // two float4 columns per contraction thread
+    if (nct + 32 > 1024) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((hc_pre_apply_kernel), n, nct + 32, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
                                                (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp, part, part_n, (int)part_ld);
     return FB_LAUNCH_CHECK();
 }

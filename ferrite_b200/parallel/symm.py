@@ -201,13 +201,16 @@ class FusedGemmAllReduce:
     the fused kernel (co-resident grid, at least one tile per rank)."""
 
     def __init__(self, device, rank: int, world: int, max_rows: int = 256, n_max: int = 8192,
-                 max_spins: int = 2_000_000, group=None):
+                 max_spins: int = 2_000_000, group=None, mode: int = 0):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         self.max_rows, self.n_max = max_rows, n_max
+        self.mode = mode   # 0: the kernel chooses, 1: one-shot, 2: two-shot (all ranks must agree)
         pad_elems = (max_rows + 256) * (n_max + 128)          # whole tiles of any tile height
         self.gather_cap = 2 * pad_elems
-        self.scatter_cap = 2 * pad_elems + 2 * world * 256 * 128   # + one rounding tile per source slot
+        # two-shot: one rounding tile per source slot; two ranks run one-shot and hold both ranks' partials of all tiles
+        self.scatter_cap = (2 * world * pad_elems if world == 2 or mode == 1
+                            else 2 * pad_elems + 2 * world * 256 * 128)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.ticket = torch.zeros(2, dtype=torch.int32, device=device)
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
@@ -237,7 +240,7 @@ class FusedGemmAllReduce:
         out [m, N] f32 (stride ldo); all ranks must call with the same shape."""
         self.K.call("fb_gemm_tc_ar", W, x_bf16, ldx, out, ldo, m, N, K, int(accumulate), self._sp, self._gp, self._fp,
                     self.scatter_cap, self.gather_cap, self.epoch, self.ticket, self.status, self.rank, self.world,
-                    self.max_spins)
+                    self.max_spins, self.mode)
         self.calls += 1
 
     def check(self):

@@ -84,8 +84,9 @@ def main():
         ar.check()
     # 1b'. fused prefill GEMM (tcgen05) + two-shot all-reduce == GEMM then NCCL all-reduce, bitwise equal on all
     # ranks, eager and replayed in a graph, with and without a local addend
-    gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096)
-    for (N, Kd, m, acc) in ((4096, 1024, 256, False), (4096, 512, 100, True), (1024, 256, 37, False), (512, 128, 16, False)):
+    for mode, (N, Kd, m, acc) in [(md, c) for md in (1, 2) for c in ((4096, 1024, 256, False), (4096, 512, 100, True),
+                                                                    (1024, 256, 37, False), (512, 128, 16, False))]:
+        gar = FusedGemmAllReduce(dev, rank, world, max_rows=256, n_max=4096, mode=mode)   # one-shot, then two-shot
         assert gar.fits(m, N), (m, N, gar.plan(m, N))
         g = torch.Generator(device=dev).manual_seed(31 + rank)
         W = (torch.randn(N, Kd, device=dev, generator=g) * 0.05).to(torch.bfloat16)
@@ -111,9 +112,9 @@ def main():
             y2.copy_(add)
             graph.replay()
             torch.cuda.synchronize()
-            assert torch.equal(y2, y), ("gemm_ar graph", N, Kd, m, it)
+            assert torch.equal(y2, y), ("gemm_ar graph", mode, N, Kd, m, it)
         gar.check()
-    gar.close()
+        gar.close()
     # 1c. vocab-sliced argmax merged across ranks == argmax of the full row (first maximum wins)
     V, n = 4096 * world, 5
     full = torch.randn(n, V, device=dev, generator=torch.Generator(device=dev).manual_seed(11))
