@@ -71,9 +71,10 @@ __device__ __forceinline__ float4 ar_chunk(const ArTables& t, uint32_t* epoch, i
     if (threadIdx.x < world) {
         const uint32_t* f = t.flags[rank] + ((size_t)par * world + threadIdx.x) * kMaxChunks + chunk;
         int spins = 0;
+        const int budget = fb_spin_budget(status, max_spins);
         // stamps only grow; a stamp ahead of e cannot occur (see the parity argument above)
         while (ld_acquire_sys(f) < e) {
-            if (++spins > max_spins) {
+            if (++spins > budget) {
                 if (atomicCAS(&s_fail, 0, 1) == 0) {
                     status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = chunk;
                 }
@@ -149,8 +150,9 @@ argmax_xchg_kernel(const unsigned long long* __restrict__ part, XchgTables t, ui
     if (r < world) {
         const uint32_t* f = t.flags[rank] + par * world + r;
         int spins = 0;
+        const int budget = fb_spin_budget(status, max_spins);
         while (ld_acquire_sys(f) < e) {
-            if (++spins > max_spins) {
+            if (++spins > budget) {
                 if (atomicCAS(&s_fail, 0, 1) == 0) { status[0] = FB_TIMEOUT; status[1] = r; status[2] = (int)e; status[3] = -2; }
                 break;
             }
@@ -183,8 +185,9 @@ argmax_xchg_kernel(const unsigned long long* __restrict__ part, XchgTables t, ui
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, int max_spins, int* status) {
     PDL_PROLOGUE();
     int spins = 0;
+    const int budget = fb_spin_budget(status, max_spins);
     while (ld_acquire_sys(flag) < want) {
-        if (++spins > max_spins) {
+        if (++spins > budget) {
             status[0] = FB_TIMEOUT; status[1] = -1; status[2] = (int)want; status[3] = spins;
             return;
         }

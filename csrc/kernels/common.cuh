@@ -56,6 +56,13 @@ inline cudaError_t fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 #define FB_LAUNCH(kernel, grid, block, smem, st, ...) \
     (void)fb_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), st, __VA_ARGS__)
 
+// Wait budget of a collective kernel: once a wait of this collective has run out (status word = FB_TIMEOUT),
+// later launches do not wait again, so one missing peer costs one budget and not one per queued launch.
+// The host clears the status word when it reads the failure.
+__device__ __forceinline__ int fb_spin_budget(const int* status, int max_spins) {
+    return (*reinterpret_cast<const volatile int*>(status) == FB_TIMEOUT) ? 0 : max_spins;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

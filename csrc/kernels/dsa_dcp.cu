@@ -102,8 +102,9 @@ dsa_merge_dcp_kernel(const float* __restrict__ o_part, const float* __restrict__
     if (threadIdx.x < world) {
         const uint32_t* f = t.flags[rank] + (par * world + threadIdx.x) * 32;
         int spins = 0;
+        const int budget = fb_spin_budget(status, max_spins);
         while (ld_relaxed_sys(f) < e) {
-            if (++spins > max_spins) {
+            if (++spins > budget) {
                 if (atomicCAS(&s_fail, 0, 1) == 0) {
                     status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = -3;
                 }

@@ -75,10 +75,11 @@ __device__ __forceinline__ float4 ld_cg_f4(const float* p) {
 }
 
 // Bounded poll of a flag word that a peer writes into LOCAL memory; false on expiry.
-__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t e, int max_spins) {
+__device__ __forceinline__ bool wait_flag(const uint32_t* f, uint32_t e, int max_spins, const int* status) {
     int spins = 0;
+    const int budget = fb_spin_budget(status, max_spins);
     while (ld_relaxed_sys(f) < e) {
-        if (++spins > max_spins) return false;
+        if (++spins > budget) return false;
         __nanosleep(64);
     }
     (void)ld_acquire_sys(f);
@@ -214,7 +215,7 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     const bool mine = oneshot || owner == rank;
     if (mine && threadIdx.x < world) {
         const uint32_t* f = t.flags[rank] + (((size_t)par * 2 + 0) * world + threadIdx.x) * kFlagPad;
-        if (!wait_flag(f, e, max_spins) && atomicCAS(&s_fail, 0, 1) == 0) {
+        if (!wait_flag(f, e, max_spins, status) && atomicCAS(&s_fail, 0, 1) == 0) {
             status[0] = FB_TIMEOUT; status[1] = 16 + threadIdx.x; status[2] = (int)e; status[3] = tile;
         }
     }
@@ -266,7 +267,7 @@ gemm_tc_ar_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     // ---- gather: wait for the owner's stamp, copy the reduced tile out ----
     if (threadIdx.x == 0) {
         const uint32_t* f = t.flags[rank] + (((size_t)par * 2 + 1) * world + owner) * kFlagPad;
-        if (!wait_flag(f, e, max_spins) && atomicCAS(&s_fail, 0, 1) == 0) {
+        if (!wait_flag(f, e, max_spins, status) && atomicCAS(&s_fail, 0, 1) == 0) {
             status[0] = FB_TIMEOUT; status[1] = 32 + owner; status[2] = (int)e; status[3] = tile;
         }
     }

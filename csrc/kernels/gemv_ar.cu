@@ -208,9 +208,10 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         if (threadIdx.x < world) {
             const uint32_t* f = t.flags[rank] + (((size_t)par * world + threadIdx.x) * kMaxTiles + grp) * kFlagPad;
             int spins = 0;
+        const int budget = fb_spin_budget(status, max_spins);
             // relaxed polls (cheap, no cache maintenance), one acquire load once the stamp is there
             while (ld_relaxed_sys(f) < e) {
-                if (++spins > max_spins) {
+                if (++spins > budget) {
                     if (atomicCAS(&s_fail, 0, 1) == 0) {
                         status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = grp;
                     }

@@ -307,20 +307,23 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const int items = topk * kb_n;
     const size_t ra = (size_t)min(c0 + g, H - 1) * I + t * 32, rb = (size_t)min(c0 + g + 8, H - 1) * I + t * 32;
-    auto item_frag = [&](int it, WFrag& f) -> int {  // loads the item's weights; returns its local expert or -1
+    // loads the item's weights and block scale (both one item ahead of their use); returns its local expert or -1
+    auto item_frag = [&](int it, WFrag& f, float& sc) -> int {
         const int s = it / kb_n, kb = it % kb_n;
         const int le = ids[r * topk + s] - e_lo;
         if (le < 0 || le >= e_cnt) return -1;
         const uint8_t* W = W2 + (size_t)le * H * I + (size_t)kb * 128;
         f = load_wfrag(W + ra, W + rb);
+        sc = __ldg(S2 + (size_t)le * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
         return le;
     };
     WFrag cur, nxt;
+    float sc_cur = 0.f, sc_nxt = 0.f;
     int le_cur = -1, le_nxt = -1;
-    if (warp < items) le_cur = item_frag(warp, cur);
+    if (warp < items) le_cur = item_frag(warp, cur, sc_cur);
     for (int it = warp; it < items; it += 8) {
         const int in = it + 8;
-        if (in < items) le_nxt = item_frag(in, nxt);
+        if (in < items) le_nxt = item_frag(in, nxt, sc_nxt);
         if (le_cur >= 0) {  // warp-uniform
             const int s = it / kb_n, kb = it % kb_n;
             const int pair = r * topk + s;
@@ -328,11 +331,11 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
             load_xfrag<16, false>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, kb * 128 + t * 32, xh, xl);
             float d[4] = {0.f, 0.f, 0.f, 0.f};
             mma_wfrag_fp8<false>(d, cur, xh, xl);
-            const float sc = __ldg(S2 + (size_t)le_cur * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc, acc[c]);
+            for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc_cur, acc[c]);
         }
         cur = nxt;
+        sc_cur = sc_nxt;
         le_cur = le_nxt;
     }
 #pragma unroll
