@@ -9,6 +9,16 @@ the device, prefills a short prompt and times graph-replayed decode steps with C
 line gives ms per step, ms per layer and the 40-layer extrapolation, which is an ESTIMATE (labelled as
 such), not a measurement of the full model.  Reference number for orientation: 6.15 ms/step at TP=8
 on B300 (docs/agent/unified-engine-battle-plan.md:4).
+
+    python bench_dsv41.py --layers 0 --emulate-tp 8 --steps 50
+
+`--emulate-tp R` builds RANK 0's shard of an R-way tensor-parallel model on ONE GPU (its 1/R of the heads,
+output groups, expert intermediate columns and vocabulary): at R = 8 the full-depth 40-layer shard is
+~45 GB and fits, so `--layers 0` times the whole production model's per-rank kernel chain.  The collectives
+run as one-rank instances of the same kernels (pushes and flags go to this GPU, nothing crosses NVLink), so
+the number is the per-rank COMPUTE time of a TP=R step; the cross-GPU wait of the ~80 fused collectives
+(7-8 us each on two GPUs) comes on top.  The engram tables (197 G parameters) are left out: the synthetic
+source cannot build them.  The metric name says `emulated`.
 """
 from __future__ import annotations
 
@@ -29,6 +39,8 @@ def main():
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
     ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="build rank 0's shard of a TP=R model on one GPU with one-rank collectives (--layers 0: all 40 layers)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -50,17 +62,35 @@ def main():
     if args.pdl:
         from ferrite_b200 import _lib
         _lib.lib().lib.fb_set_pdl(1)
+    model_rank, model_world = rank, world
+    if args.emulate_tp > 1:
+        assert world == 1, "--emulate-tp runs as one process"
+        import torch.distributed as dist
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29571", rank=0, world_size=1, device_id=dev)
+        from ferrite_b200.parallel.collective import make_allreduce
+        allreduce = make_allreduce(dev, 0, 1, max_elems=64 * 8192, kind="p2p")   # one-rank instances of the collectives
+        model_rank, model_world = 0, args.emulate_tp
     L = args.layers
-    assert L >= 4
-    # one window-only layer, a ratio-2 source, a ratio-1 source (candidate source), an inheriting ratio-1 layer
-    ratios = [0, 2, 1] + [1] * (L - 3)
     n_mtp = 3 if args.spec else 0
-    cfg = replace(Dsv41Config(), n_layers=L, n_mtp_layers=n_mtp, compress_ratios=tuple(ratios + [0] * n_mtp),
-                  kv_source_layers=(1, 2), index_source_layers=(1, 2) + ((L - 1,) if L > 4 else ()),
-                  candidate_source_layer=2, engram_layer_ids=(), engram_num_embeddings=(),
-                  dspark_target_layer_ids=tuple(range(max(0, L - 3), L)) if args.spec else (),
-                  dspark_block_size=5 if args.spec else 0, n_routed_experts=args.experts).validate()
-    eng = Dsv41Engine(cfg, SyntheticDsv41Source(cfg, dev), rank, world, dev, allreduce, max_ctx=args.prompt_len + 1024)
+    if L == 0:
+        base = Dsv41Config()
+        L = base.n_layers
+        cfg = replace(base, n_mtp_layers=n_mtp, compress_ratios=tuple(base.compress_ratios[:L]) + (0,) * n_mtp,
+                      engram_layer_ids=(), engram_num_embeddings=(),
+                      dspark_target_layer_ids=base.dspark_target_layer_ids if args.spec else (),
+                      dspark_block_size=base.dspark_block_size if args.spec else 0,
+                      n_routed_experts=args.experts).validate()
+    else:
+        assert L >= 4
+        # one window-only layer, a ratio-2 source, a ratio-1 source (candidate source), an inheriting ratio-1 layer
+        ratios = [0, 2, 1] + [1] * (L - 3)
+        cfg = replace(Dsv41Config(), n_layers=L, n_mtp_layers=n_mtp, compress_ratios=tuple(ratios + [0] * n_mtp),
+                      kv_source_layers=(1, 2), index_source_layers=(1, 2) + ((L - 1,) if L > 4 else ()),
+                      candidate_source_layer=2, engram_layer_ids=(), engram_num_embeddings=(),
+                      dspark_target_layer_ids=tuple(range(max(0, L - 3), L)) if args.spec else (),
+                      dspark_block_size=5 if args.spec else 0, n_routed_experts=args.experts).validate()
+    eng = Dsv41Engine(cfg, SyntheticDsv41Source(cfg, dev), model_rank, model_world, dev, allreduce,
+                      max_ctx=args.prompt_len + 1024)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
     eng.prefill(prompt)
@@ -87,15 +117,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     if rank == 0:
-        print(json.dumps({"metric": "dsv41_decode_ms_per_step_layer_reduced", "value": round(ms, 4), "unit": "ms",
+        full = L == Dsv41Config().n_layers
+        name = "dsv41_decode_ms_per_step" + ("" if full else "_layer_reduced") + \
+               (f"_rank0_of_tp{args.emulate_tp}_emulated" if args.emulate_tp > 1 else "")
+        print(json.dumps({"metric": name, "value": round(ms, 4), "unit": "ms",
                           "higher_is_better": False, "n_gpus": world, "steps": args.steps, "layers": L,
                           "ms_per_layer": round(ms / L, 4),
                           "estimate_40_layers_ms": round(ms / L * 40, 3), "estimate_note": "extrapolated, not measured",
                           "tokens_per_step": round(toks / args.steps, 3), "dtype": "bf16 dense / e2m1 experts",
                           "data": "synthetic", "config": {"dim": cfg.dim, "heads": cfg.n_heads, "experts": cfg.n_routed_experts,
                                                           "topk": cfg.n_activated_experts, "context": args.prompt_len,
-                                                          "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl)}}))
-    if world > 1:
+                                                          "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl),
+                                                          "emulated_tp": args.emulate_tp, "engram": "left out",
+                                                          }}))
+    if world > 1 or args.emulate_tp > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()

@@ -171,7 +171,14 @@ class Dsv41DeviceModel:
         cfg = self.cfg
         self.embed = self._bf(src.get("embed.weight"))
         self.norm_w = self._f(src.get("norm.weight"))
-        self.head = self._bf(src.get("head.weight"))
+        # vocab-sliced head when the collective carries a cross-rank argmax: each rank streams 1/world of the rows
+        V = cfg.vocab_size
+        self.xargmax = getattr(self.allreduce, "argmax", None) if self.world > 1 else None
+        if self.xargmax is not None and V % self.world:
+            self.xargmax = None
+        self.Vl = V // self.world if self.xargmax is not None else V
+        self.v_lo = self.rank * self.Vl if self.xargmax is not None else 0
+        self.head = self._bf(src.get("head.weight")[self.v_lo:self.v_lo + self.Vl])
         self.layers: List[dict] = []
         for l in range(cfg.n_layers):
             p = f"layers.{l}."
@@ -198,7 +205,7 @@ class Dsv41DeviceModel:
             self.d_main_norm = self._f(src.get("mtp.0.main_norm.weight"))
             self.d_norm = self._f(src.get(last + "norm.weight"))
             self.d_membed = self._bf(src.get(last + "markov_head.embed.weight"))
-            self.d_mhead = self._bf(src.get(last + "markov_head.head.weight"))
+            self.d_mhead = self._bf(src.get(last + "markov_head.head.weight")[self.v_lo:self.v_lo + self.Vl])
             self.d_conf = self._f(src.get(last + "confidence_head.proj.weight"))
         self.freq_win = self._f(rope_freqs(cfg.rope_head_dim, cfg.rope_theta, 0, 1.0, cfg.beta_fast, cfg.beta_slow))
         self.freq_cmp = self._f(rope_freqs(cfg.rope_head_dim, cfg.compress_rope_theta, cfg.original_seq_len,
@@ -337,6 +344,15 @@ class Dsv41DeviceModel:
     def _reduce(self, t, n):
         if self.world > 1:
             self.allreduce(t[:n])
+
+    def _argmax(self, logits, out_ids, n):
+        """Greedy ids of `n` rows of logits [n, Vl] (this rank's vocab slice when the head is sliced: the
+        partial keys are merged across the ranks and every rank gets the global id)."""
+        ws = self.ws
+        if self.xargmax is None:
+            self.K.call("fb_argmax", logits, self.Vl, ws["amax_part"], out_ids, None, n, self.Vl, 1, 0)
+        else:
+            self.xargmax(logits, self.Vl, ws["amax_part"], n, self.Vl, self.v_lo, out_ids)
 
     def _quant(self, src_f, dst: Act, n, K, ld=None, mask=1):
         """dst.f / dst planes = e4m3-per-32 round trip of src (may alias dst.f); mask 1: bf16 planes,
@@ -582,8 +598,8 @@ class Dsv41DeviceModel:
             self._dbg(f"layers.{l}.h", ws["R"][:n])
         self._hc_pre({}, "", self.norm_w, n, coeffs=False)
         if want_logits:
-            self.gemv(self.head, ws["x"], ws["logits"], n, cfg.vocab_size, d)
-            self.K.call("fb_argmax", ws["logits"], cfg.vocab_size, ws["amax_part"], ws["out_ids"], None, n, cfg.vocab_size, 1, 0)
+            self.gemv(self.head, ws["x"], ws["logits"], n, self.Vl, d)
+            self._argmax(ws["logits"], ws["out_ids"], n)
         if advance:
             self.K.call("fb_advance_rows", rs.meta, None, self.seq_len, n)
 
@@ -644,15 +660,15 @@ class Dsv41DeviceModel:
         self.K.call("fb_d4_hc_pre", ws["R"], None, None, None, self.d_norm, ws["pre_cur"], ws["pre_nxt"], ws["post"],
                     ws["comb"], x.f, ws["d_xc"], B, d, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
                     cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0)
-        V, rk = cfg.vocab_size, cfg.dspark_markov_rank
-        self.gemv(self.head, x, ws["logits"], B, V, d)
+        V, Vl, rk = cfg.vocab_size, self.Vl, cfg.dspark_markov_rank
+        self.gemv(self.head, x, ws["logits"], B, Vl, d)
         out, me = ws["d_out"], ws["d_me"]
         out[0:1].copy_(t0)
         for i in range(B):
             self.K.call("fb_d4_gather_row", self.d_membed, View(out, i), rk, V, me.f, *me.sp(1))
             ws["d_me_all"][i].copy_(me.f[0])
-            self.gemv(self.d_mhead, me, View(ws["logits"], i * V), 1, V, rk, accumulate=True)
-            self.K.call("fb_argmax", View(ws["logits"], i * V), V, ws["amax_part"], View(out, i + 1), None, 1, V, 1, 0)
+            self.gemv(self.d_mhead, me, View(ws["logits"], i * Vl), 1, Vl, rk, accumulate=True)
+            self._argmax(View(ws["logits"], i * Vl), View(out, i + 1), 1)
         return out
 
     def dspark_confidence(self) -> torch.Tensor:
