@@ -71,7 +71,7 @@ quant_rows_kernel(const float* __restrict__ x, int ldx, float* __restrict__ xq, 
 // acc [n][25]: the 24 mix dots of the CURRENT stream R plus its sum of squares (cleared here).
 // Computes this site's (pre, post, comb); `pre` is only stored (the NEXT site contracts with
 // it), the contraction uses pre_in, the coefficients of the previous site.
-//   xn = rmsnorm(sum_i pre_in[i] R_i) * ln_w
+//   xn = rmsnorm(sum_i pre_in[i] R_i) * ln_w ; optionally also xq = the e4m3-per-32 round trip of xn
 // Block = C contraction warps + one coefficient warp.  All warps first sum the per-tile partial dots; then
 // the contraction warps (which only need the PREVIOUS site's `pre`) and the coefficient warp (sigmoids +
 // Sinkhorn, a serial chain of ~40 divisions) run side by side; the contraction warps meet on a named
@@ -81,7 +81,8 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
                      const float* __restrict__ base, const float* __restrict__ ln_w, const float* __restrict__ pre_in,
                      float* __restrict__ pre_out, float* __restrict__ post_out, float* __restrict__ comb_out,
                      float* __restrict__ xn_out, float* __restrict__ xc_out, int H, float rms_eps, float hc_eps, int iters,
-                     SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld) {
+                     SplitBuf osp, const float* __restrict__ part, int* __restrict__ part_n, int part_ld,
+                     float* __restrict__ xq_out, SplitBuf qsp) {
     PDL_PROLOGUE();
     __shared__ float red[32];
     const int n = 4;
@@ -172,14 +173,31 @@ hc_pre_offset_kernel(const float* __restrict__ R, float* __restrict__ acc, const
     const float inv = rsqrtf(tot / H + rms_eps);
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-        if (!act[c]) continue;
         const int j = (threadIdx.x + c * nct) * 4;
-        if (xc_out) *reinterpret_cast<float4*>(xc_out + (size_t)r * H + j) = x[c];
-        float4 o;
+        float4 o;   // zeros in inactive threads (their x and ln_w are zero)
         o.x = x[c].x * inv * lw[c].x; o.y = x[c].y * inv * lw[c].y; o.z = x[c].z * inv * lw[c].z; o.w = x[c].w * inv * lw[c].w;
-        *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
-        split_store(osp, r, j, o.x); split_store(osp, r, j + 1, o.y);
-        split_store(osp, r, j + 2, o.z); split_store(osp, r, j + 3, o.w);
+        if (act[c]) {
+            if (xc_out) *reinterpret_cast<float4*>(xc_out + (size_t)r * H + j) = x[c];
+            *reinterpret_cast<float4*>(xn_out + (size_t)r * H + j) = o;
+            split_store(osp, r, j, o.x); split_store(osp, r, j + 1, o.y);
+            split_store(osp, r, j + 2, o.z); split_store(osp, r, j + 3, o.w);
+        }
+        if (xq_out || qsp.base) {
+            // e4m3-per-32 round trip of the normed row (what the next projections consume): a 32-value block is the
+            // four values of eight consecutive threads; whole warps run the shuffles, only live threads store
+            float am = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 4));
+            const float sc = fp8_block_scale(am);
+            float4 q;
+            q.x = e4m3_rt(o.x / sc) * sc; q.y = e4m3_rt(o.y / sc) * sc; q.z = e4m3_rt(o.z / sc) * sc; q.w = e4m3_rt(o.w / sc) * sc;
+            if (act[c]) {
+                if (xq_out) *reinterpret_cast<float4*>(xq_out + (size_t)r * H + j) = q;
+                split_store(qsp, r, j, q.x); split_store(qsp, r, j + 1, q.y);
+                split_store(qsp, r, j + 2, q.z); split_store(qsp, r, j + 3, q.w);
+            }
+        }
     }
 }
 
@@ -1122,13 +1140,15 @@ FB_API int fb_d4_hc_pre(const float* R, float* acc, const float* scale, const fl
                         const float* pre_in, float* pre_out, float* post_out, float* comb_out, float* xn_out,
                         float* xc_out, int64_t n, int64_t H, int64_t mult, float rms_eps, float hc_eps, int64_t iters,
                         void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, const float* part, int* part_n,
-                        int64_t part_ld, cudaStream_t st) {
+                        int64_t part_ld, float* xq_out, void* q_base, int64_t q_ld, int64_t q_plane, int64_t q_mask,
+                        cudaStream_t st) {
     if (mult != 4 || (part_n && n > 64) || (H % 4)) return (int)cudaErrorInvalidValue;
+    if ((xq_out || q_base) && (H % 32)) return (int)cudaErrorInvalidValue;   // whole quantisation blocks
     const int nct = (int)(((H / 4 + 1) / 2 + 31) / 32 * 32);   // two float4 columns per contraction thread
     if (nct + 32 > 1024) return (int)cudaErrorInvalidValue;
     FB_LAUNCH((hc_pre_offset_kernel), n, nct + 32, 0, st, R, acc, scale, base, ln_w, pre_in, pre_out, post_out, comb_out,
               xn_out, xc_out, (int)H, rms_eps, hc_eps, (int)iters, mk_split(s_base, s_ld, s_plane, s_mask), part, part_n,
-              (int)part_ld);
+              (int)part_ld, xq_out, mk_split(q_base, q_ld, q_plane, q_mask));
     return FB_LAUNCH_CHECK();
 }
 

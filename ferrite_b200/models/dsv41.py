@@ -72,6 +72,7 @@ class Dsv41DeviceModel:
         self.tc_gemv_min_n = 0
         self.fp4_mma = os.environ.get("FERRITE_D4_FP4_MMA", "1") != "0"   # tensor-core routed experts (decode rows)
         self.fp4_mma_rows = 1 << 30
+        self._xq_ready = False
         self._tc_part = None
         self._tc_ticket = None
         # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
@@ -400,7 +401,7 @@ class Dsv41DeviceModel:
             self._folded = True
         self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f)
 
-    def _hc_pre(self, L, site, ln, n, coeffs=True):
+    def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
         """Coefficients of this site (stored for the next one) and the contraction with the previous
         site's `pre`; leaves the normed input in ws['x'] (f32 + bf16 planes)."""
         cfg, ws = self.cfg, self.ws
@@ -410,7 +411,9 @@ class Dsv41DeviceModel:
                     L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
                     ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
                     cfg.hc_sinkhorn_iters, *x.sp(1),
-                    *(self.fused.partials() if self.fused is not None and coeffs and n <= 8 else (None, None, 0)))
+                    *(self.fused.partials() if self.fused is not None and coeffs and n <= 8 else (None, None, 0)),
+                    *((ws["xq"].f, *ws["xq"].sp(3)) if quant else (None, None, 0, 0, 0)))
+        self._xq_ready = quant   # the sublayer's first quantisation of x is already done
         if coeffs:
             ws["pre_cur"], ws["pre_nxt"] = pout, pin
 
@@ -420,7 +423,9 @@ class Dsv41DeviceModel:
         layer, r = L["layer"], L["ratio"]
         x, xq, qr = ws["x"], ws["xq"], ws["qr"]
         freqs = self.freq_cmp if r > 0 else self.freq_win
-        self._quant(x.f, xq, n, d)
+        if not self._xq_ready:
+            self._quant(x.f, xq, n, d)
+        self._xq_ready = False
         self.gemv(L["w_qkv_a"], xq, ws["qa"], n, ql + hd, d)
         self.K.call("fb_rmsnorm", ws["qa"], None, None, L["q_norm"], qr.f, n, ql, ql + hd, ql, float(cfg.norm_eps),
                     None, 0, 0, 0)
@@ -492,7 +497,9 @@ class Dsv41DeviceModel:
         if L["fp4_mma"] and n <= self.fp4_mma_rows:
             # decode rows: e2m1 weights x f16 activations on the tensor cores (activations are e4m3 round trips,
             # exact in f16), one (row, slot) pair per CTA column
-            self._quant(x.f, xq, n, d, mask=3)
+            if not self._xq_ready:
+                self._quant(x.f, xq, n, d, mask=3)
+            self._xq_ready = False
             f16 = lambda a: _lib.ctypes.c_void_p(a.s.data_ptr() + 4 * a.plane)   # plane 2 of the int16 planes
             self.K.call("fb_d4_expert_gate_up_mma", f16(xq), xq.ld, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk,
                         self.Il, d, float(cfg.swiglu_limit))
@@ -500,7 +507,9 @@ class Dsv41DeviceModel:
             self.K.call("fb_d4_expert_down_mma", f16(h), ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
         else:
             assert not L["fp4_mma"], "quad-interleaved expert weights need the tensor-core kernels"
-            self._quant(x.f, xq, n, d)
+            if not self._xq_ready:
+                self._quant(x.f, xq, n, d)
+            self._xq_ready = False
             self.K.call("fb_d4_expert_gate_up", xq.f, d, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk, self.Il, d,
                         float(cfg.swiglu_limit))
             self.K.call("fb_d4_quant_rows", h.f, self.Il, h.f, self.Il, n * topk, self.Il, None, 0, 0, 0)
@@ -596,7 +605,7 @@ class Dsv41DeviceModel:
             if fn_next is None:
                 pending_mix = True
             self._dbg(f"layers.{l}.h", ws["R"][:n])
-        self._hc_pre({}, "", self.norm_w, n, coeffs=False)
+        self._hc_pre({}, "", self.norm_w, n, coeffs=False, quant=False)
         if want_logits:
             self.gemv(self.head, ws["x"], ws["logits"], n, self.Vl, d)
             self._argmax(ws["logits"], ws["out_ids"], n)
@@ -659,7 +668,7 @@ class Dsv41DeviceModel:
         x = ws["x"]
         self.K.call("fb_d4_hc_pre", ws["R"], None, None, None, self.d_norm, ws["pre_cur"], ws["pre_nxt"], ws["post"],
                     ws["comb"], x.f, ws["d_xc"], B, d, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
-                    cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0)
+                    cfg.hc_sinkhorn_iters, *x.sp(1), None, None, 0, None, None, 0, 0, 0)
         V, Vl, rk = cfg.vocab_size, self.Vl, cfg.dspark_markov_rank
         self.gemv(self.head, x, ws["logits"], B, Vl, d)
         out, me = ws["d_out"], ws["d_me"]
