@@ -93,6 +93,8 @@ def main():
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
     ap.add_argument("--prefill-rows", type=int, default=256, help="rows per prefill chunk")
+    ap.add_argument("--moe-shard", default="inter", choices=["inter", "expert"],
+                    help="routed experts split by intermediate columns (default) or by expert over the ranks")
     ap.add_argument("--fuse", default="full", choices=["full", "ar", "off"],
                     help="GEMV epilogue fusion: all-reduce + hyper-connection fold, all-reduce only, or separate kernels")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
@@ -129,7 +131,7 @@ def main():
     ecfg = EngineConfig(tp=world, max_ctx=args.prompt_len + 3 * (args.steps * 2 + args.warmup * 2 + 16) + 64,
                         mtp_n=1 if args.no_mtp else 3,
                         experts_resident=None if resident >= cfg.n_routed_experts else resident,
-                        fuse_epilogue=args.fuse)
+                        fuse_epilogue=args.fuse, moe_shard=args.moe_shard if world > 1 else "inter")
     t0 = time.time()
     eng = GlmEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank=rank, world=world, device=dev,
                     allreduce=allreduce, prefill_rows=args.prefill_rows)
@@ -204,7 +206,7 @@ def main():
             "impl": "ours",
             "config": {"model": "GLM-5.3-Flash (45 layers: 34 GatedDeltaNet + 11 DSA, 3 dense + 42 MoE, 1 MTP layer)"
                                 if args.layers == 0 else f"DEBUG {args.layers}-layer slice (invalid as a result)",
-                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none", "gemv_epilogue_fusion": args.fuse,
+                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none", "gemv_epilogue_fusion": args.fuse, "moe_shard": args.moe_shard if world > 1 else "n/a",
                        "weights": "random-init; bf16, routed experts + dense FFN fp8 e4m3 128x128 block-scaled (W8A16)",
                        "mtp": "draft 2 / verify 3" if mtp else "off",
                        "accept_tokens_per_step": round(tokens / args.steps, 3),

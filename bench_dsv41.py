@@ -93,7 +93,13 @@ def main():
                       max_ctx=args.prompt_len + 1024)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+    torch.cuda.synchronize()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
     eng.prefill(prompt)
+    p1.record()
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)   # chunked prefill of the prompt (eager launches, 8 rows per chunk)
     step = (lambda: eng.spec_step()) if args.spec else (lambda: eng.step_plain())
     for _ in range(max(args.warmup, 3)):
         step()
@@ -129,6 +135,8 @@ def main():
                                                           "topk": cfg.n_activated_experts, "context": args.prompt_len,
                                                           "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl),
                                                           "emulated_tp": args.emulate_tp, "engram": "left out",
+                                                          "prefill_ms": round(prefill_ms, 2),
+                                                          "prefill_ms_per_token": round(prefill_ms / args.prompt_len, 4),
                                                           }}))
     if world > 1 or args.emulate_tp > 1:
         import torch.distributed as dist

@@ -1103,13 +1103,28 @@ gemv_f32w_kernel(const float* __restrict__ W, const float* __restrict__ x, int l
     float acc[8];
 #pragma unroll
     for (int r = 0; r < 8; ++r) acc[r] = 0.f;
-    for (int k = lane * 4; k < K; k += 128) {
-        const float4 w = *reinterpret_cast<const float4*>(W + (size_t)n * K + k);
+    const float* wrow = W + (size_t)n * K;
+    for (int k0 = lane * 4; k0 < K; k0 += 512) {   // four independent 16-byte weight loads in flight per lane
+        float4 w[4];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r < m) {
-                const float4 v = *reinterpret_cast<const float4*>(x + (size_t)r * ldx + k);
-                acc[r] += w.x * v.x + w.y * v.y + w.z * v.z + w.w * v.w;
+        for (int u = 0; u < 4; ++u) {
+            const int k = k0 + 128 * u;
+            w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < K) {
+                const uint4 t = ldg_nc_v4(wrow + k);
+                w[u] = make_float4(__uint_as_float(t.x), __uint_as_float(t.y), __uint_as_float(t.z), __uint_as_float(t.w));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = k0 + 128 * u;
+            if (k >= K) break;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < m) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + (size_t)r * ldx + k);
+                    acc[r] += w[u].x * v.x + w[u].y * v.y + w[u].z * v.z + w[u].w * v.w;
+                }
             }
         }
     }

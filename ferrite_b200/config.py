@@ -240,6 +240,11 @@ class EngineConfig:
     use_graphs: bool = True
     fp8_experts: bool = True
     experts_resident: Optional[int] = None  # None = all routed experts of the shard
+    # how the routed experts are split over the tensor-parallel ranks: "inter" = every rank holds a 1/tp slice of
+    # every expert's intermediate dim; "expert" = every rank holds E/tp whole experts (activations stay replicated,
+    # a rank computes the pairs routed to its experts, the sublayer's all-reduce sums the ranks: expert parallelism
+    # without an all-to-all; longer weight rows per expert, load follows the routing)
+    moe_shard: str = "inter"
     kv_dtype: str = "bf16"  # latent cache dtype: "bf16" or "fp8"
     # epilogue of a sublayer's last GEMV: "full" = all-reduce + hyper-connection fold in the same kernel,
     # "ar" = all-reduce only, "off" = separate kernels (True / False are accepted for full / off)

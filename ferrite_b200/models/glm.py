@@ -122,6 +122,13 @@ class GlmDeviceModel:
         self.kv_f32 = ecfg.kv_dtype == "f32"
         self.nbuf = (ecfg.mtp_n + 1) if ecfg.mtp_n > 1 else 1
         self.E_res = ecfg.experts_resident or cfg.n_routed_experts
+        self.moe_by_expert = getattr(ecfg, "moe_shard", "inter") == "expert" and world > 1
+        if self.moe_by_expert:
+            assert cfg.n_routed_experts % world == 0 and not ecfg.experts_resident
+            self.e_cnt = cfg.n_routed_experts // world
+            self.e_lo = rank * self.e_cnt
+        else:
+            self.e_lo, self.e_cnt = 0, self.E_res
         self.tc_min_rows = 16  # row count from which dense bf16 projections use the tcgen05 GEMM
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
         self.layers: List[dict] = []
@@ -202,7 +209,10 @@ class GlmDeviceModel:
         L["gate_s13"] = self._bf(torch.cat([src.get(f"{pfx}.mlp.gate.weight").float(), sg, su], 0))
         L["s2"] = self._bf(self._sh(src, f"{pfx}.mlp.shared_expert.down_proj.weight"))
         L["I_shared"] = sg.shape[0]
-        Il = cfg.moe_intermediate_size // self.world
+        by_e = self.moe_by_expert
+        Il = cfg.moe_intermediate_size if by_e else cfg.moe_intermediate_size // self.world
+        e_lo, Er = (self.e_lo, self.e_cnt) if by_e else (0, Er)   # the experts this rank stores (local index = id - e_lo)
+        get = (lambda name: src.get(name)) if by_e else (lambda name: self._sh(src, name))
         H = cfg.hidden_size
         w13 = torch.empty(Er, 2 * Il, H, dtype=torch.float8_e4m3fn, device=self.dev)
         s13 = torch.empty(Er, (2 * Il + 127) // 128, (H + 127) // 128, device=self.dev)
@@ -213,16 +223,16 @@ class GlmDeviceModel:
             step = 16
             for e0 in range(0, Er, step):
                 e1 = min(Er, e0 + step)
-                a13, a2 = chunk(pfx, e0, e1, Il, H)
+                a13, a2 = chunk(pfx, e_lo + e0, e_lo + e1, Il, H)
                 q, s = quant_fp8_block(a13.view(-1, H))
                 w13[e0:e1], s13[e0:e1] = q.view(e1 - e0, 2 * Il, H), s.view(e1 - e0, -1, s.shape[1])
                 q, s = quant_fp8_block(a2.view(-1, Il))
                 w2[e0:e1], s2[e0:e1] = q.view(e1 - e0, H, Il), s.view(e1 - e0, -1, s.shape[1])
         else:
             for e in range(Er):
-                g = self._sh(src, f"{pfx}.mlp.experts.{e}.gate_proj.weight").float()
-                u = self._sh(src, f"{pfx}.mlp.experts.{e}.up_proj.weight").float()
-                d = self._sh(src, f"{pfx}.mlp.experts.{e}.down_proj.weight").float()
+                g = get(f"{pfx}.mlp.experts.{e_lo + e}.gate_proj.weight").float()
+                u = get(f"{pfx}.mlp.experts.{e_lo + e}.up_proj.weight").float()
+                d = get(f"{pfx}.mlp.experts.{e_lo + e}.down_proj.weight").float()
                 w13[e], s13[e] = quant_fp8_block(torch.cat([g, u], 0))
                 w2[e], s2[e] = quant_fp8_block(d)
         L["w13"], L["s13s"], L["w2"], L["s2s"] = w13, s13, w2, s2
@@ -580,25 +590,25 @@ class GlmDeviceModel:
             mas = ws["moe_act_s"]
             ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
             mg = n * topk
-            self.K.call("fb_moe_group", ws["moe_ids"], n * topk, 0, self.E_res, ws["moe_gpairs"], ws["moe_gexp"],
+            self.K.call("fb_moe_group", ws["moe_ids"], n * topk, self.e_lo, self.e_cnt, ws["moe_gpairs"], ws["moe_gexp"],
                         ws["moe_ngrp"], mg)
             self.K.call("fb_moe_gate_up_grp", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_wts"], ws["moe_gpairs"],
                         ws["moe_gexp"], ws["moe_ngrp"], mas, ld_as, plane_as, mg, topk, Il, H, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_grp", L["w2"], L["s2s"], mas, ld_as, plane_as, ws["moe_gpairs"], ws["moe_gexp"],
                         ws["moe_ngrp"], ws["moe_ypair"], mg, Il, H)
-            self.K.call("fb_moe_sum_pairs", ws["moe_ypair"], ws["moe_ids"], ws["y"], H, n, topk, H, 0, self.E_res, 0)
+            self.K.call("fb_moe_sum_pairs", ws["moe_ypair"], ws["moe_ids"], ws["y"], H, n, topk, H, self.e_lo, self.e_cnt, 0)
         elif H % 128 == 0 and Il % 128 == 0:
             mas = ws["moe_act_s"]
             ld_as, plane_as = mas.shape[2], mas.shape[1] * mas.shape[2]
             self.K.call("fb_moe_gate_up_mma", L["w13"], L["s13s"], x.s, x.ld, x.plane, ws["moe_ids"], ws["moe_wts"],
-                        mas, ld_as, plane_as, n, topk, Il, H, 0, self.E_res, float(cfg.swiglu_limit))
+                        mas, ld_as, plane_as, n, topk, Il, H, self.e_lo, self.e_cnt, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_mma", L["w2"], L["s2s"], mas, ld_as, plane_as, ws["moe_ids"], ws["y"], H, n,
-                        topk, Il, H, 0, self.E_res, 0, None, 0, 0, 0)
+                        topk, Il, H, self.e_lo, self.e_cnt, 0, None, 0, 0, 0)
         else:
             self.K.call("fb_moe_gate_up_fp8", L["w13"], L["s13s"], x.f, H, ws["moe_ids"], ws["moe_act"], n, topk,
-                        Il, H, 0, self.E_res, float(cfg.swiglu_limit))
+                        Il, H, self.e_lo, self.e_cnt, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"],
-                        H, n, topk, Il, H, 0, self.E_res, 0)
+                        H, n, topk, Il, H, self.e_lo, self.e_cnt, 0)
         self._out_gemv(L["s2"], act, n, H, Is, ldx=Is, accumulate=True)
 
     def _attn(self, L, rs, snapshots):

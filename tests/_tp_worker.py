@@ -184,6 +184,16 @@ def main():
             outs[mtp_n], _ = eng.generate(prompt, 14)
             ar.check()
         assert outs[1] == outs[3], (name, outs)
+        # routed experts split by expert instead of by intermediate columns: whole experts per rank are quantised
+        # exactly like the single-rank engine's, so the tokens agree with the column-split run up to fp8 block effects
+        if cfg.n_routed_experts % world == 0:
+            ecfg = EngineConfig(max_ctx=256, mtp_n=3, kv_dtype="f32", tp=world, moe_shard="expert")
+            eng = GlmEngine(cfg, ecfg, DictSource(w, dev), rank=rank, world=world, device=dev, allreduce=ar,
+                            prefill_rows=16)
+            by_expert, _ = eng.generate(prompt, 14)
+            ar.check()
+            same = sum(a == b for a, b in zip(by_expert, outs[1]))
+            assert same >= 10, (name, "expert-sharded", by_expert, outs[1])
         t = torch.tensor(outs[1], device=dev)
         t0 = t.clone()
         dist.broadcast(t0, 0)
