@@ -978,6 +978,49 @@ swiglu_clamp_kernel(const float* __restrict__ gu, int ld, float* __restrict__ ou
     out[(size_t)r * ldo + i] = siluf_(g) * u;
 }
 
+// RMSNorm of a row slice followed by the e4m3-per-32 round trip (the q-lora vector on its way to wq_b):
+// out = rt(x * rsqrt(mean x^2 + eps) * w).  One CTA per row, a warp per 32-value block.
+__global__ void __launch_bounds__(256)
+rmsnorm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ out, int ldo,
+                     int K, float eps, SplitBuf osp) {
+    PDL_PROLOGUE();
+    __shared__ float red[32];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = x + (size_t)r * ldx;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) { const float v = row[k]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / K + eps);
+    for (int b = warp; b < K / 32; b += blockDim.x >> 5) {
+        const int k = b * 32 + lane;
+        const float v = row[k] * inv * w[k];
+        const float s = fp8_block_scale(warp_max(fabsf(v)));
+        const float q = e4m3_rt(v / s) * s;
+        out[(size_t)r * ldo + k] = q;
+        split_store(osp, r, k, q);
+    }
+}
+
+// Shared expert: SwiGLU with clamps, then the e4m3-per-32 round trip of the result (f32 + split planes).
+// One warp per 32-value block.
+__global__ void __launch_bounds__(256)
+swiglu_clamp_quant_kernel(const float* __restrict__ gu, int ld, float* __restrict__ out, int ldo, int n, int I, float lim,
+                          SplitBuf osp) {
+    PDL_PROLOGUE();
+    const int lane = threadIdx.x & 31;
+    const int nb = I / 32;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= n * nb) return;
+    const int r = w / nb, i = (w % nb) * 32 + lane;
+    float g = gu[(size_t)r * ld + i], u = gu[(size_t)r * ld + I + i];
+    if (lim > 0.f) { u = fminf(fmaxf(u, -lim), lim); g = fminf(g, lim); }
+    const float v = siluf_(g) * u;
+    const float s = fp8_block_scale(warp_max(fabsf(v)));
+    const float q = e4m3_rt(v / s) * s;
+    out[(size_t)r * ldo + i] = q;
+    split_store(osp, r, i, q);
+}
+
 // ---- engram --------------------------------------------------------------------------------------
 // Phase 1 stores each row's compressed token id (DEAD = -1 for masked rows) at its position of
 // the slot's history; phase 2 hashes the 2..G-grams ending at each row.
@@ -1318,6 +1361,23 @@ FB_API int fb_d4_expert_down(const float* hq, const int* idx, const void* w2, co
 FB_API int fb_d4_swiglu_clamp(const float* gu, int64_t ld, float* out, int64_t ldo, int64_t n, int64_t I, float lim,
                               cudaStream_t st) {
     FB_LAUNCH((swiglu_clamp_kernel), (n * I + 255) / 256, 256, 0, st, gu, (int)ld, out, (int)ldo, (int)n, (int)I, lim);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_rmsnorm_quant(const float* x, int64_t ldx, const float* w, float* out, int64_t ldo, int64_t n, int64_t K,
+                               float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (K % 32) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((rmsnorm_quant_kernel), n, 256, 0, st, x, (int)ldx, w, out, (int)ldo, (int)K, eps,
+              mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_d4_swiglu_clamp_quant(const float* gu, int64_t ld, float* out, int64_t ldo, int64_t n, int64_t I, float lim,
+                                    void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (I % 32) return (int)cudaErrorInvalidValue;
+    const int64_t warps = n * (I / 32);
+    FB_LAUNCH((swiglu_clamp_quant_kernel), (warps + 7) / 8, 256, 0, st, gu, (int)ld, out, (int)ldo, (int)n, (int)I, lim,
+              mk_split(s_base, s_ld, s_plane, s_mask));
     return FB_LAUNCH_CHECK();
 }
 

@@ -65,8 +65,9 @@ class Dsv41DeviceModel:
         self.IHl = cfg.index_n_heads // world
         self.Il = padded_inter(cfg, world) if world > 1 else cfg.moe_inter_dim
         per = (cfg.moe_inter_dim + world - 1) // world
-        self.shared_tp = world > 1 and per % 32 == 0 and per * world == cfg.moe_inter_dim
-        self.Is = per if self.shared_tp else cfg.moe_inter_dim
+        self.shared_tp = world > 1 and per * world == cfg.moe_inter_dim
+        self.Is_real = per if self.shared_tp else cfg.moe_inter_dim      # columns of the shared expert this rank owns
+        self.Is = (self.Is_real + 63) // 64 * 64                        # zero-padded to the tensor-core GEMV's k-block
         self.tc_min_rows = 16
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
         self.tc_gemv_min_n = 0
@@ -162,8 +163,13 @@ class Dsv41DeviceModel:
                 self.K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 0)
         sw1, sw3, sw2 = (src.get(f + f"shared_experts.{n}.weight") for n in ("w1", "w3", "w2"))
         if self.shared_tp:
-            lo = self.rank * self.Is
-            sw1, sw3, sw2 = sw1[lo:lo + self.Is], sw3[lo:lo + self.Is], sw2[:, lo:lo + self.Is]
+            lo = self.rank * self.Is_real
+            sw1, sw3, sw2 = sw1[lo:lo + self.Is_real], sw3[lo:lo + self.Is_real], sw2[:, lo:lo + self.Is_real]
+        pad = self.Is - sw1.shape[0]
+        if pad:   # padded channels compute silu(0) * 0 = 0 and meet zero columns of w2
+            z = torch.zeros(pad, sw1.shape[1], dtype=sw1.dtype, device=sw1.device)
+            sw1, sw3 = torch.cat([sw1, z], 0), torch.cat([sw3, z], 0)
+            sw2 = torch.cat([sw2, torch.zeros(sw2.shape[0], pad, dtype=sw2.dtype, device=sw2.device)], 1)
         L["sh_w13"] = self._bf(torch.cat([sw1, sw3], 0))
         L["sh_w2"] = self._bf(sw2)
         return L
@@ -401,7 +407,10 @@ class Dsv41DeviceModel:
             self._folded = True
         self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f)
 
+    fuse_quant = os.environ.get("FERRITE_D4_FUSE_QUANT", "1") != "0"   # hc_pre also emits the e4m3 round trip of its output
+
     def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
+        quant = quant and self.fuse_quant
         """Coefficients of this site (stored for the next one) and the contraction with the previous
         site's `pre`; leaves the normed input in ws['x'] (f32 + bf16 planes)."""
         cfg, ws = self.cfg, self.ws
@@ -427,9 +436,7 @@ class Dsv41DeviceModel:
             self._quant(x.f, xq, n, d)
         self._xq_ready = False
         self.gemv(L["w_qkv_a"], xq, ws["qa"], n, ql + hd, d)
-        self.K.call("fb_rmsnorm", ws["qa"], None, None, L["q_norm"], qr.f, n, ql, ql + hd, ql, float(cfg.norm_eps),
-                    None, 0, 0, 0)
-        self._quant(qr.f, qr, n, ql)
+        self.K.call("fb_d4_rmsnorm_quant", ws["qa"], ql + hd, L["q_norm"], qr.f, ql, n, ql, float(cfg.norm_eps), *qr.sp(1))
         self.gemv(L["wq_b"], qr, ws["q"], n, self.Hl * hd, ql)
         kv_raw = View(ws["qa"], ql)
         if extra is None:
@@ -518,8 +525,9 @@ class Dsv41DeviceModel:
             self._reduce(ws["y"], n)
         hs = ws["hs"]
         self.gemv(L["sh_w13"], xq, ws["gu"], n, 2 * self.Is, d)
-        self.K.call("fb_d4_swiglu_clamp", ws["gu"], 2 * self.Is, hs.f, self.Is, n, self.Is, float(cfg.swiglu_limit))
-        self._quant(hs.f, hs, n, self.Is)
+        # clamped SwiGLU and its e4m3-per-32 round trip in one launch
+        self.K.call("fb_d4_swiglu_clamp_quant", ws["gu"], 2 * self.Is, hs.f, self.Is, n, self.Is, float(cfg.swiglu_limit),
+                    *hs.sp(1))
         if self.shared_tp or self.world == 1:
             self._out_gemv(L["sh_w2"], hs, n, d, self.Is, accumulate=True)
         else:
