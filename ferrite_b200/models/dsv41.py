@@ -407,7 +407,10 @@ class Dsv41DeviceModel:
             self._folded = True
         self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f)
 
-    fuse_quant = os.environ.get("FERRITE_D4_FUSE_QUANT", "1") != "0"   # hc_pre also emits the e4m3 round trip of its output
+    # hc_pre can also emit the e4m3 round trip of its output (two launches fewer per layer).  Off by default: measured
+    # 1 % SLOWER at TP1 and on the TP8 shard (2.175 vs 2.161 ms, 5.94 vs 5.88 ms): hc_pre is a one-CTA latency chain
+    # on the critical path, the separate quantiser spreads over many CTAs
+    fuse_quant = os.environ.get("FERRITE_D4_FUSE_QUANT", "0") != "0"
 
     def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
         quant = quant and self.fuse_quant
