@@ -288,8 +288,21 @@ def make_cases(K, only):
 
         def d4at():
             K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta, 0, 0,
-                   float(hd ** -0.5), Hl, hd, out, Hl * hd, n, 16, at_o, at_ml, None, 0, 0, 0)
-        cases.append(Case("d4_sparse_attn.tp8.m1", (W + ktop) * hd * 2, d4at, f"{Hl} heads, {W}+{ktop} keys x {hd} bf16 (L2-resident)"))
+                   float(hd ** -0.5), Hl, hd, out, Hl * hd, n, 16, at_o, at_ml, None, 0, 0, 0, None)
+        at_tk = torch.zeros(n * ((Hl + 7) // 8), dtype=torch.int32, device=dev)
+
+        def d4at1():
+            K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta, 0, 0,
+                   float(hd ** -0.5), Hl, hd, out, Hl * hd, n, 16, at_o, at_ml, None, 0, 0, 0, at_tk)
+        cases.append(Case("d4_sparse_attn.tp8.m1", (W + ktop) * hd * 2, d4at, f"{Hl} heads, {W}+{ktop} keys x {hd} bf16 (L2-resident), two kernels"))
+        cases.append(Case("d4_sparse_attn_1k.tp8.m1", (W + ktop) * hd * 2, d4at1, "same, the last CTA of a head tile merges the splits"))
+        for ns in (32, 40, 80):
+            bo, bm = torch.zeros(n * Hl * ns * hd, device=dev), torch.zeros(n * Hl * ns * 2, device=dev)
+            for tk, tag in ((None, "2k"), (at_tk, "1k")):
+                def f(ns=ns, bo=bo, bm=bm, tk=tk):
+                    K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta,
+                           0, 0, float(hd ** -0.5), Hl, hd, out, Hl * hd, n, ns, bo, bm, None, 0, 0, 0, tk)
+                cases.append(Case(f"d4_sparse_attn_{tag}.split{ns}.tp8.m1", (W + ktop) * hd * 2, f, f"{ns} splits"))
     if want("d4_index_score"):
         n, IHl, ID, ccap = 1, 4, 128, 65536
         kc = torch.randn(1, ccap, ID, device=dev).to(torch.bfloat16)

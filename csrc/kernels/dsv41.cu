@@ -614,17 +614,20 @@ cand_mask_kernel(const int* __restrict__ blk, int ldb, int kb, int bs, uint8_t* 
 // inverse rotation; softmax runs online with max over the real keys only, the sink logit
 // joins the denominator at the end, a row without keys yields zeros.
 constexpr int kAttnTile = 8;
+constexpr int kAttnStage = 48;   // keys staged per pass (48 KB of shared memory at head_dim 512)
 template <int NJ>  // head_dim / 64
 __global__ void __launch_bounds__(256)
 sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ ring, int cap, int window,
                    const __nv_bfloat16* __restrict__ comp, int ccap, const int* __restrict__ idx, int ldi, int ktop,
                    const float* __restrict__ extra, int n_extra, const float* __restrict__ sink,
                    const float* __restrict__ freqs, int rd, const RowMeta* __restrict__ meta, int pos_off, int win_mode,
-                   float scale, int heads, int nsplit, float* __restrict__ o_part, float* __restrict__ ml_part) {
+                   float scale, int heads, int nsplit, float* __restrict__ o_part, float* __restrict__ ml_part,
+                   unsigned* __restrict__ ticket, float* __restrict__ out, int ldo, SplitBuf osp) {
     PDL_PROLOGUE();
     constexpr int HD = NJ * 64;
-    __shared__ __align__(16) uint32_t ktile[kAttnTile][HD / 2];
-    __shared__ int kvalid[kAttnTile];
+    extern __shared__ __align__(16) uint32_t ktile[];   // [kAttnStage][HD / 2] staged bf16 keys
+    __shared__ int kvalid[kAttnStage];
+    __shared__ int s_last;
     const int r = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x * 8 + warp;
@@ -652,89 +655,139 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
     float ov[NJ][2];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) ov[j][0] = ov[j][1] = 0.f;
-    // this CTA's share of the key list (split-K over blockIdx.z; partials are merged by the second kernel)
+    // this CTA's share of the key list (split-K over blockIdx.z).  The share is staged in passes of up to kAttnStage
+    // keys: every warp issues the 16-byte loads of its keys back to back, so a pass costs one memory latency, and
+    // the 8-key tiles of the pass are then consumed from shared memory.
     const int sp = blockIdx.z;
     const int per = ((L + nsplit - 1) / nsplit + kAttnTile - 1) / kAttnTile * kAttnTile;
     const int k_lo = sp * per, k_hi = min(L, k_lo + per);
-    for (int t0 = k_lo; t0 < k_hi; t0 += kAttnTile) {
+    for (int base = k_lo; base < k_hi; base += kAttnStage) {
+        const int cnt = min(kAttnStage, k_hi - base);
+        const int cnt8 = (cnt + kAttnTile - 1) / kAttnTile * kAttnTile;
         __syncthreads();
-        // stage up to kAttnTile keys
-        for (int t = warp; t < kAttnTile; t += 8) {
-            const int i = t0 + t;
+        for (int t = warp; t < cnt8; t += 8) {
+            const int i = base + t;
             const __nv_bfloat16* src = nullptr;
             const float* srcf = nullptr;
-            if (i >= k_hi) {
-                // past this CTA's share
+            if (t >= cnt) {
+                // padding of the last tile
             } else if (i < nw) {
                 const int p = wpos - nw + 1 + i;
                 src = ring + ((size_t)m.slot * cap + (p % cap)) * HD;
             } else if (i < nw + ktop) {
                 const int c = idx[(size_t)r * ldi + (i - nw)];
                 if (c >= 0 && c < ccap) src = comp + ((size_t)m.slot * ccap + c) * HD;
-            } else if (i < k_hi) {
+            } else {
                 srcf = extra + (size_t)(i - nw - ktop) * HD;
             }
+            uint32_t* dst = ktile + (size_t)t * (HD / 2);
             if (lane == 0) kvalid[t] = (src || srcf) ? 1 : 0;
-            if (!src && !srcf) {
-                for (int e = lane; e < HD / 2; e += 32) ktile[t][e] = 0u;  // a masked key must not feed NaN into 0 * k
-            } else if (src) {
-                const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
-                for (int e = lane; e < HD / 2; e += 32) ktile[t][e] = s32[e];
+            if (src) {
+                const uint4* s16 = reinterpret_cast<const uint4*>(src);
+                for (int v = lane; v < HD / 8; v += 32) reinterpret_cast<uint4*>(dst)[v] = __ldg(s16 + v);
             } else if (srcf) {
                 for (int e = lane; e < HD / 2; e += 32) {
                     const __nv_bfloat162 v = __floats2bfloat162_rn(srcf[2 * e], srcf[2 * e + 1]);
-                    ktile[t][e] = *reinterpret_cast<const uint32_t*>(&v);
+                    dst[e] = *reinterpret_cast<const uint32_t*>(&v);
                 }
+            } else {
+                for (int e = lane; e < HD / 2; e += 32) dst[e] = 0u;  // a masked key must not feed NaN into 0 * k
             }
         }
         __syncthreads();
-        float sc[kAttnTile];
-        float tmax = -INFINITY;
+        for (int t0 = 0; t0 < cnt; t0 += kAttnTile) {
+            const uint32_t* kt = ktile + (size_t)t0 * (HD / 2);
+            float sc[kAttnTile];
+            float tmax = -INFINITY;
 #pragma unroll
-        for (int t = 0; t < kAttnTile; ++t) {
-            float d = 0.f;
+            for (int t = 0; t < kAttnTile; ++t) {
+                float d = 0.f;
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const uint32_t kw = ktile[t][lane + 32 * j];
-                d = fmaf(qv[j][0], bf16lo(kw), d);
-                d = fmaf(qv[j][1], bf16hi(kw), d);
+                for (int j = 0; j < NJ; ++j) {
+                    const uint32_t kw = kt[t * (HD / 2) + lane + 32 * j];
+                    d = fmaf(qv[j][0], bf16lo(kw), d);
+                    d = fmaf(qv[j][1], bf16hi(kw), d);
+                }
+                sc[t] = d;
             }
-            sc[t] = d;
-        }
 #pragma unroll
-        for (int t = 0; t < kAttnTile; ++t) {
-            sc[t] = warp_sum(sc[t]);
-            if (!kvalid[t] || t0 + t >= k_hi) sc[t] = -INFINITY;
-            tmax = fmaxf(tmax, sc[t]);
-        }
-        const float mnew = fmaxf(mx, tmax);
-        const float resc = __expf(mx - mnew);
-        den *= resc;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) { ov[j][0] *= resc; ov[j][1] *= resc; }
-#pragma unroll
-        for (int t = 0; t < kAttnTile; ++t) {
-            const float p = __expf(sc[t] - mnew);  // exp(-inf) = 0 for masked keys
-            den += p;
-#pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                const uint32_t kw = ktile[t][lane + 32 * j];
-                ov[j][0] = fmaf(p, bf16lo(kw), ov[j][0]);
-                ov[j][1] = fmaf(p, bf16hi(kw), ov[j][1]);
+            for (int t = 0; t < kAttnTile; ++t) {
+                sc[t] = warp_sum(sc[t]);
+                if (!kvalid[t0 + t] || t0 + t >= cnt) sc[t] = -INFINITY;
+                tmax = fmaxf(tmax, sc[t]);
             }
+            const float mnew = fmaxf(mx, tmax);
+            const float resc = __expf(mx - mnew);
+            den *= resc;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) { ov[j][0] *= resc; ov[j][1] *= resc; }
+#pragma unroll
+            for (int t = 0; t < kAttnTile; ++t) {
+                const float p = __expf(sc[t] - mnew);  // exp(-inf) = 0 for masked keys
+                den += p;
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    const uint32_t kw = kt[t * (HD / 2) + lane + 32 * j];
+                    ov[j][0] = fmaf(p, bf16lo(kw), ov[j][0]);
+                    ov[j][1] = fmaf(p, bf16hi(kw), ov[j][1]);
+                }
+            }
+            mx = mnew;
         }
-        mx = mnew;
     }
-    if (!hv) return;
     // un-normalised partial of this split: o (already rotated keys), running max and denominator
-    const size_t pi = (((size_t)r * heads + h) * nsplit + sp);
+    const size_t p0 = ((size_t)r * heads + h) * nsplit;
+    if (hv) {
+        const size_t pi = p0 + sp;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const int e = 2 * lane + 64 * j;
+            *reinterpret_cast<float2*>(o_part + pi * HD + e) = make_float2(ov[j][0], ov[j][1]);
+        }
+        if (lane == 0) { ml_part[pi * 2] = mx; ml_part[pi * 2 + 1] = den; }
+    }
+    if (!ticket) return;   // the partials are merged by a second kernel
+    // The CTA that finishes a (row, head tile) last merges its splits: max-shifted sum, the sink logit joins the
+    // denominator, the output gets the inverse rotation (this lane's factors are the ones computed above).
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* tk = ticket + (size_t)r * gridDim.x + blockIdx.x;
+        const unsigned t = atomicAdd(tk, 1u);
+        s_last = (t == (unsigned)nsplit - 1u) ? 1 : 0;
+        if (s_last) *tk = 0u;   // every CTA of the group has taken its ticket
+    }
+    __syncthreads();
+    if (!s_last || !hv) return;
+    __threadfence();
+    float M = -1e30f;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(ml_part + (p0 + s) * 2));
+    float dsum = __expf(sink[h] - M);
+    float a[NJ], b[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) a[j] = b[j] = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float w = __expf(__ldcg(ml_part + (p0 + s) * 2) - M);
+        dsum = fmaf(__ldcg(ml_part + (p0 + s) * 2 + 1), w, dsum);
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const float2 o = __ldcg(reinterpret_cast<const float2*>(o_part + (p0 + s) * HD + 2 * lane + 64 * j));
+            a[j] = fmaf(o.x, w, a[j]);
+            b[j] = fmaf(o.y, w, b[j]);
+        }
+    }
+    const float inv = 1.f / dsum;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int e = 2 * lane + 64 * j;
-        o_part[pi * HD + e] = ov[j][0];
-        o_part[pi * HD + e + 1] = ov[j][1];
+        const float x = a[j] * inv, y = b[j] * inv;
+        const float x0 = x * cs[j] + y * sn[j], x1 = -x * sn[j] + y * cs[j];   // inverse rotation (identity where cs = 1, sn = 0)
+        float* o = out + (size_t)r * ldo + (size_t)h * HD + e;
+        o[0] = x0;
+        o[1] = x1;
+        split_store(osp, r, h * HD + e, x0);
+        split_store(osp, r, h * HD + e + 1, x1);
     }
-    if (lane == 0) { ml_part[pi * 2] = mx; ml_part[pi * 2 + 1] = den; }
 }
 
 // Merge of the split-K partials: max-shifted sum, the sink logit joins the denominator, the output gets
@@ -1292,21 +1345,30 @@ template <int NJ>
 static int launch_attn(const float* q, int ldq, const void* ring, int cap, int window, const void* comp, int ccap,
                        const int* idx, int ldi, int ktop, const float* extra, int n_extra, const float* sink,
                        const float* freqs, int rd, const void* meta, int pos_off, int win_mode, float scale, int heads,
-                       int nsplit, float* o_part, float* ml_part, int n, cudaStream_t st) {
-    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n, (unsigned)nsplit), 256, 0, st, q, ldq,
+                       int nsplit, float* o_part, float* ml_part, int n, unsigned* ticket, float* out, int ldo, SplitBuf osp,
+                       cudaStream_t st) {
+    constexpr int kSm = kAttnStage * NJ * 64 * 2;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(sparse_attn_kernel<NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSm);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n, (unsigned)nsplit), 256, kSm, st, q, ldq,
               (const __nv_bfloat16*)ring, cap, window, (const __nv_bfloat16*)comp, ccap, idx, ldi, ktop, extra, n_extra, sink,
-              freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, nsplit, o_part, ml_part);
+              freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, nsplit, o_part, ml_part, ticket, out, ldo, osp);
     return FB_LAUNCH_CHECK();
 }
 
 // q [n][heads*hd] un-rotated; out gets the inverse rotation.  idx may be null (ktop = 0), extra may be null.
-// o_part: scratch of n * heads * nsplit * hd floats, ml_part: n * heads * nsplit * 2 floats.
+// o_part: scratch of n * heads * nsplit * hd floats, ml_part: n * heads * nsplit * 2 floats.  ticket: null (a second
+// kernel merges the splits) or n * ceil(heads / 8) zero-initialised words, left at zero (the last CTA of a group merges).
 FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int64_t cap, int64_t window, const void* comp,
                              int64_t ccap, const int* idx, int64_t ldi, int64_t ktop, const float* extra, int64_t n_extra,
                              const float* sink, const float* freqs, int64_t rd, const void* meta, int64_t pos_off,
                              int64_t win_mode, float scale, int64_t heads, int64_t hd, float* out, int64_t ldo, int64_t n,
                              int64_t nsplit, float* o_part, float* ml_part, void* s_base, int64_t s_ld, int64_t s_plane,
-                             int64_t s_mask, cudaStream_t st) {
+                             int64_t s_mask, void* ticket, cudaStream_t st) {
     const SplitBuf osp = mk_split(s_base, s_ld, s_plane, s_mask);
     if (!idx) ktop = 0;
     if (!extra) n_extra = 0;
@@ -1314,7 +1376,7 @@ FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int6
     int rc;
 #define D4_ATTN(NJ) launch_attn<NJ>(q, (int)ldq, ring, (int)cap, (int)window, comp, (int)ccap, idx, (int)ldi, (int)ktop, extra, \
                                     (int)n_extra, sink, freqs, (int)rd, meta, (int)pos_off, (int)win_mode, scale, (int)heads, \
-                                    (int)nsplit, o_part, ml_part, (int)n, st)
+                                    (int)nsplit, o_part, ml_part, (int)n, (unsigned*)ticket, out, (int)ldo, osp, st)
     switch (hd) {
         case 64: rc = D4_ATTN(1); break;
         case 128: rc = D4_ATTN(2); break;
@@ -1323,7 +1385,7 @@ FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int6
         default: return (int)cudaErrorInvalidValue;
     }
 #undef D4_ATTN
-    if (rc) return rc;
+    if (rc || ticket) return rc;   // with a ticket buffer the last CTA of every (row, head tile) has merged the splits
     FB_LAUNCH((sparse_attn_merge_kernel), dim3((unsigned)heads, (unsigned)n), 128, 0, st, o_part, ml_part, sink, freqs, (int)rd,
               (const RowMeta*)meta, (int)pos_off, (int)heads, (int)hd, (int)nsplit, out, (int)ldo, osp);
     return FB_LAUNCH_CHECK();
