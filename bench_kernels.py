@@ -296,6 +296,10 @@ def make_cases(K, only):
                    float(hd ** -0.5), Hl, hd, out, Hl * hd, n, 16, at_o, at_ml, None, 0, 0, 0, at_tk)
         cases.append(Case("d4_sparse_attn.tp8.m1", (W + ktop) * hd * 2, d4at, f"{Hl} heads, {W}+{ktop} keys x {hd} bf16 (L2-resident), two kernels"))
         cases.append(Case("d4_sparse_attn_1k.tp8.m1", (W + ktop) * hd * 2, d4at1, "same, the last CTA of a head tile merges the splits"))
+        def d4attc():
+            K.call("fb_d4_sparse_attn_tc", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, sink, freqs, 64, meta, 0, 0,
+                   float(hd ** -0.5), Hl, out, Hl * hd, n, 10, at_o, at_ml, None, 0, 0, 0)
+        cases.append(Case("d4_sparse_attn_tc.tp8.m1", (W + ktop) * hd * 2, d4attc, "tensor-core form, 10 splits of 64 keys + merge kernel"))
         for ns in (32, 40, 80):
             bo, bm = torch.zeros(n * Hl * ns * hd, device=dev), torch.zeros(n * Hl * ns * 2, device=dev)
             for tk, tag in ((None, "2k"), (at_tk, "1k")):

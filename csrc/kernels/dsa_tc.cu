@@ -40,11 +40,53 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+// Where a row's keys and its query come from.  A source gives the number of keys of row r, the address of key i
+// (null = masked) and one adjacent pair of the pre-scaled query.
+struct GlmSrc {   // selected tokens of the paged latent cache (GLM DSA)
+    const float* qabs; const __nv_bfloat16* lat_cache; const int* idx; int ld_idx; const int* cnt;
+    PageViewT pv; int hl, shard, nshard; float scale;
+    __device__ int n_keys(int r, const RowMeta&) const { return cnt[r]; }
+    __device__ const __nv_bfloat16* key(int r, const RowMeta& m, int i) const {
+        const int t = idx[(size_t)r * ld_idx + i];
+        if (t < 0) return nullptr;
+        if (nshard > 1 && ((t / pv.page_size) % nshard) != shard) return nullptr;   // DCP ownership
+        const int pg = pv.table[(size_t)m.slot * pv.max_pages + t / pv.page_size];
+        return lat_cache + ((long long)pg * pv.page_size + (t % pv.page_size)) * DL;
+    }
+    __device__ float2 q_pair(int r, const RowMeta&, int h, int d) const {
+        const float2 v = *reinterpret_cast<const float2*>(qabs + ((size_t)r * hl + h) * DL + d);
+        return make_float2(v.x * scale, v.y * scale);
+    }
+};
+struct D4Src {    // DSV41: the row's window positions of the KV ring, then the selected compressed rows; q is rotated here
+    const float* q; int ldq; const __nv_bfloat16* ring; int cap, window; const __nv_bfloat16* comp; int ccap;
+    const int* idx; int ldi, ktop; const float* freqs; int rd, pos_off, win_mode; float scale;
+    __device__ int wpos(const RowMeta& m) const { return win_mode ? m.ctx0 - 1 : m.pos; }
+    __device__ int n_win(const RowMeta& m) const { return max(min(wpos(m) + 1, window), 0); }
+    __device__ int n_keys(int, const RowMeta& m) const { return n_win(m) + ktop; }
+    __device__ const __nv_bfloat16* key(int r, const RowMeta& m, int i) const {
+        const int nw = n_win(m);
+        if (i < nw) return ring + ((size_t)m.slot * cap + ((wpos(m) - nw + 1 + i) % cap)) * DL;
+        const int c = idx[(size_t)r * ldi + (i - nw)];
+        return (c >= 0 && c < ccap) ? comp + ((size_t)m.slot * ccap + c) * DL : nullptr;
+    }
+    __device__ float2 q_pair(int r, const RowMeta& m, int h, int d) const {
+        const float2 v = *reinterpret_cast<const float2*>(q + (size_t)r * ldq + (size_t)h * DL + d);
+        float a = v.x, b = v.y;
+        if (d >= DL - rd) {
+            float sn, cs;
+            sincosf((float)(m.pos + pos_off) * freqs[(d - (DL - rd)) >> 1], &sn, &cs);
+            a = v.x * cs - v.y * sn;
+            b = v.x * sn + v.y * cs;
+        }
+        return make_float2(a * scale, b * scale);
+    }
+};
+
+template <class Src>
 __global__ void __launch_bounds__(256, 1)
-dsa_attn_partial_tc_kernel(const float* __restrict__ qabs, const __nv_bfloat16* __restrict__ lat_cache,
-                           const int* __restrict__ idx, int ld_idx, const int* __restrict__ cnt,
-                           float* __restrict__ o_part, float* __restrict__ ml_part, const RowMeta* __restrict__ meta,
-                           PageViewT pv, int hl, int nsplit, int shard, int nshard, float scale) {
+attn_partial_tc_kernel(Src src, float* __restrict__ o_part, float* __restrict__ ml_part, const RowMeta* __restrict__ meta,
+                       int hl, int nsplit) {
     PDL_PROLOGUE();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smem_raw);         // [64][QS]
@@ -53,14 +95,14 @@ dsa_attn_partial_tc_kernel(const float* __restrict__ qabs, const __nv_bfloat16* 
     __nv_bfloat16* Ps = Lt + TT * QS;                                         // [64][PS]
     float* rmax = reinterpret_cast<float*>(Ps + 64 * PS);                    // [2][64]
     float* lsum = rmax + 128;                                                 // [2][64]
-    long long* toff = reinterpret_cast<long long*>(lsum + 128);              // [TT] element offsets, -1 = masked
+    const __nv_bfloat16** tptr = reinterpret_cast<const __nv_bfloat16**>(lsum + 128);   // [TT] key rows, null = masked
 
     const int r = blockIdx.y, sp = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int mt = warp & 3, half = warp >> 2;
     const RowMeta m = meta[r];
-    const int n_tok = cnt[r];
+    const int n_tok = src.n_keys(r, m);
     const int per = ((n_tok + nsplit - 1) / nsplit + TT - 1) / TT * TT;
     const int lo = sp * per, hi = min(n_tok, lo + per);
 
@@ -69,9 +111,9 @@ dsa_attn_partial_tc_kernel(const float* __restrict__ qabs, const __nv_bfloat16* 
         const int h = i / (DL / 2), d = (i % (DL / 2)) * 2;
         float a = 0.f, b = 0.f;
         if (h < hl) {
-            const float2 v = *reinterpret_cast<const float2*>(qabs + ((size_t)r * hl + h) * DL + d);
-            a = v.x * scale;
-            b = v.y * scale;
+            const float2 v = src.q_pair(r, m, h, d);
+            a = v.x;
+            b = v.y;
         }
         const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
         *reinterpret_cast<__nv_bfloat162*>(Qh + h * QS + d) = __nv_bfloat162(ah, bh);
@@ -86,21 +128,12 @@ dsa_attn_partial_tc_kernel(const float* __restrict__ qabs, const __nv_bfloat16* 
 
     for (int t0 = lo; t0 < hi; t0 += TT) {
         __syncthreads();   // previous tile fully consumed (and Q staged, first time)
-        if (tid < TT) {
-            int t = (t0 + tid < hi) ? idx[(size_t)r * ld_idx + t0 + tid] : -1;
-            if (t >= 0 && nshard > 1 && ((t / pv.page_size) % nshard) != shard) t = -1;   // DCP ownership
-            long long off = -1;
-            if (t >= 0) {
-                const int pg = pv.table[(size_t)m.slot * pv.max_pages + t / pv.page_size];
-                off = ((long long)pg * pv.page_size + (t % pv.page_size)) * DL;
-            }
-            toff[tid] = off;
-        }
+        if (tid < TT) tptr[tid] = (t0 + tid < hi) ? src.key(r, m, t0 + tid) : nullptr;
         __syncthreads();
         for (int i = tid; i < TT * (DL / 8); i += 256) {   // 16-byte pieces
             const int t = i / (DL / 8), d = (i % (DL / 8)) * 8;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (toff[t] >= 0) v = *reinterpret_cast<const uint4*>(lat_cache + toff[t] + d);
+            if (tptr[t]) v = *reinterpret_cast<const uint4*>(tptr[t] + d);
             *reinterpret_cast<uint4*>(Lt + t * QS + d) = v;
         }
         __syncthreads();
@@ -134,7 +167,7 @@ dsa_attn_partial_tc_kernel(const float* __restrict__ qabs, const __nv_bfloat16* 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int tk = half * 32 + j * 8 + 2 * t4 + (c & 1);
-                if (toff[tk] < 0) S[j][c] = -INFINITY;
+                if (!tptr[tk]) S[j][c] = -INFINITY;
                 pm[c >> 1] = fmaxf(pm[c >> 1], S[j][c]);
             }
         }
@@ -240,14 +273,88 @@ FB_API int fb_dsa_attn_partial_tc(const float* qabs, const void* lat_cache, cons
     if (latent_dim != DL || hl < 1 || hl > 64) return (int)cudaErrorInvalidValue;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(dsa_attn_partial_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_tc_kernel<GlmSrc>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
     PageViewT pv{page_table, (int)max_pages, (int)page_size};
-    FB_LAUNCH((dsa_attn_partial_tc_kernel), dim3((unsigned)nsplit, (unsigned)n), 256, kSmemBytes, st, qabs,
-              (const __nv_bfloat16*)lat_cache, idx, (int)ld_idx, cnt, o_part, ml_part, (const RowMeta*)meta, pv, (int)hl,
-              (int)nsplit, (int)shard, (int)nshard, scale);
+    GlmSrc src{qabs, (const __nv_bfloat16*)lat_cache, idx, (int)ld_idx, cnt, pv, (int)hl, (int)shard, (int)nshard, scale};
+    FB_LAUNCH((attn_partial_tc_kernel<GlmSrc>), dim3((unsigned)nsplit, (unsigned)n), 256, kSmemBytes, st, src, o_part, ml_part,
+              (const RowMeta*)meta, (int)hl, (int)nsplit);
+    return FB_LAUNCH_CHECK();
+}
+
+namespace {
+
+// DSV41 merge of the tensor-core partials (o [n][nsplit][hl][DL], ml [n][nsplit][hl][2]): max-shifted sum, the sink
+// logit joins the denominator, the output gets the inverse rotation.  grid (heads, rows), 128 threads.
+__global__ void __launch_bounds__(128)
+d4_attn_merge_tc_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, const float* __restrict__ sink,
+                        const float* __restrict__ freqs, int rd, const RowMeta* __restrict__ meta, int pos_off, int hl,
+                        int nsplit, float* __restrict__ out, int ldo, SplitBuf osp) {
+    PDL_PROLOGUE();
+    const int h = blockIdx.x, r = blockIdx.y;
+    auto ml = [&](int s) { return ml_part + (((size_t)r * nsplit + s) * hl + h) * 2; };
+    float M = -1e30f;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml(s)[0]);
+    float den = __expf(sink[h] - M);
+    for (int s = 0; s < nsplit; ++s) den += ml(s)[1] * __expf(ml(s)[0] - M);
+    const float inv = 1.f / den;
+    const float pos = (float)(meta[r].pos + pos_off);
+    for (int e = 2 * threadIdx.x; e < DL; e += 2 * blockDim.x) {
+        float a = 0.f, b = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float w = __expf(ml(s)[0] - M);
+            if (w != 0.f) {   // an empty split holds no data
+                const float2 o = *reinterpret_cast<const float2*>(o_part + (((size_t)r * nsplit + s) * hl + h) * DL + e);
+                a = fmaf(o.x, w, a);
+                b = fmaf(o.y, w, b);
+            }
+        }
+        a *= inv; b *= inv;
+        float x0 = a, x1 = b;
+        if (e >= DL - rd) {
+            float sn, cs;
+            sincosf(pos * freqs[(e - (DL - rd)) >> 1], &sn, &cs);
+            x0 = a * cs + b * sn;    // inverse rotation
+            x1 = -a * sn + b * cs;
+        }
+        float* o = out + (size_t)r * ldo + (size_t)h * DL + e;
+        o[0] = x0;
+        o[1] = x1;
+        split_store(osp, r, h * DL + e, x0);
+        split_store(osp, r, h * DL + e + 1, x1);
+    }
+}
+
+}  // namespace
+
+// DSV41 sparse attention with a sink on the tensor cores: head_dim 512, up to 64 heads, keys = the row's window
+// positions of the ring + the selected compressed rows (no extra rows).  o_part: n * nsplit * heads * 512 floats,
+// ml_part: n * nsplit * heads * 2 floats; q is un-rotated, out gets the inverse rotation.
+FB_API int fb_d4_sparse_attn_tc(const float* q, int64_t ldq, const void* ring, int64_t cap, int64_t window, const void* comp,
+                                int64_t ccap, const int* idx, int64_t ldi, int64_t ktop, const float* sink, const float* freqs,
+                                int64_t rd, const void* meta, int64_t pos_off, int64_t win_mode, float scale, int64_t heads,
+                                float* out, int64_t ldo, int64_t n, int64_t nsplit, float* o_part, float* ml_part,
+                                void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (heads < 1 || heads > 64 || nsplit < 1 || (rd % 2) || rd > DL || (ldq % 2)) return (int)cudaErrorInvalidValue;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_partial_tc_kernel<D4Src>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    if (!idx) ktop = 0;
+    D4Src src{q, (int)ldq, (const __nv_bfloat16*)ring, (int)cap, (int)window, (const __nv_bfloat16*)comp, (int)ccap, idx,
+              (int)ldi, (int)ktop, freqs, (int)rd, (int)pos_off, (int)win_mode, scale};
+    FB_LAUNCH((attn_partial_tc_kernel<D4Src>), dim3((unsigned)nsplit, (unsigned)n), 256, kSmemBytes, st, src, o_part, ml_part,
+              (const RowMeta*)meta, (int)heads, (int)nsplit);
+    int rc = FB_LAUNCH_CHECK();
+    if (rc) return rc;
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    FB_LAUNCH((d4_attn_merge_tc_kernel), dim3((unsigned)heads, (unsigned)n), 128, 0, st, o_part, ml_part, sink, freqs, (int)rd,
+              (const RowMeta*)meta, (int)pos_off, (int)heads, (int)nsplit, out, (int)ldo, osp);
     return FB_LAUNCH_CHECK();
 }

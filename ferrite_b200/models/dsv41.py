@@ -74,6 +74,9 @@ class Dsv41DeviceModel:
         self.fp4_mma = os.environ.get("FERRITE_D4_FP4_MMA", "1") != "0"   # tensor-core routed experts (decode rows)
         self.fp4_mma_rows = 1 << 30
         self._xq_ready = False
+        # tensor-core sparse attention (head_dim 512), opt-in: at decode sizes (640 keys) it measured 21.6 us against
+        # 16.3 us for the SIMT kernel with the in-kernel split merge (8 heads), and 2.37 vs 2.15 ms on the 8-layer bench
+        self.attn_tc = os.environ.get("FERRITE_D4_ATTN_TC", "0") != "0"
         self._tc_part = None
         self._tc_ticket = None
         # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
@@ -487,9 +490,16 @@ class Dsv41DeviceModel:
                             cfg.index_topk, n)
             comp, idx, ktop = self.comp[src], ws["topk"], cfg.index_topk
         o = ws["o"]
-        self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
-                    cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
-                    self.Hl, hd, o.f, self.Hl * hd, n, self.at_split, ws["at_o"], ws["at_ml"], *o.sp(1), ws["at_ticket"])
+        if self.attn_tc and hd == 512 and extra is None and self.Hl <= 64:
+            # tensor cores: all heads of a row share one key sequence, so QK^T and PV are two small GEMMs per 64-key tile
+            nsp = min(self.at_split, (cfg.window_size + (ktop if idx is not None else 0) + 63) // 64)
+            self.K.call("fb_d4_sparse_attn_tc", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
+                        cfg.index_topk, ktop, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5), self.Hl,
+                        o.f, self.Hl * hd, n, max(1, nsp), ws["at_o"], ws["at_ml"], *o.sp(1))
+        else:
+            self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
+                        cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
+                        self.Hl, hd, o.f, self.Hl * hd, n, self.at_split, ws["at_o"], ws["at_ml"], *o.sp(1), ws["at_ticket"])
         low = ws["low"]
         R_ = cfg.o_lora_rank
         self.gemv(L["wo_a"], o, low, n, self.Gl * R_, cfg.heads_per_group * hd, ldx=self.Hl * hd, group_rows=R_)

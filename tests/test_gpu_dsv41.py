@@ -261,3 +261,36 @@ def test_fp4_expert_mma_kernels_match_simt(K, n, topk, E, I, D):
     for t, orig in ((w13p, w13), (w2p, w2)):
         K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 1)
         assert torch.equal(t, orig)
+
+
+@pytest.mark.parametrize("n,heads,pos,ktop", [(1, 8, 5000, 512), (3, 64, 70, 40), (2, 16, 300, 0)])
+def test_sparse_attn_tensor_core_matches_simt(K, n, heads, pos, ktop):
+    """Tensor-core sparse attention with sink (head_dim 512) against the SIMT kernel on the same ring / compressed rows."""
+    dev = torch.device("cuda")
+    hd, W, cap, ccap, rd = 512, 128, 136, 2048, 64
+    g = torch.Generator(device=dev).manual_seed(9)
+    ring = torch.randn(2, cap, hd, device=dev, generator=g).to(torch.bfloat16)
+    comp = torch.randn(2, ccap, hd, device=dev, generator=g).to(torch.bfloat16)
+    q = torch.randn(n, heads * hd, device=dev, generator=g)
+    sink = torch.randn(heads, device=dev, generator=g)
+    freqs = torch.rand(rd // 2, device=dev, generator=g)
+    meta = torch.zeros(n, 8, dtype=torch.int32, device=dev)
+    meta[:, 0] = 1                                     # slot
+    meta[:, 1] = torch.arange(n, device=dev) + pos     # pos
+    meta[:, 2] = pos                                   # ctx0
+    idx = None
+    if ktop:
+        idx = torch.stack([torch.randperm(ccap, device=dev, generator=g)[:ktop].sort().values for _ in range(n)]).to(torch.int32)
+        idx[:, -3:] = -1                                # unreachable entries are masked
+        idx = idx.contiguous()
+    ns = 16
+    o_part, ml = torch.zeros(n * heads * ns * hd, device=dev), torch.zeros(n * heads * ns * 2, device=dev)
+    want, got = torch.zeros(n, heads * hd, device=dev), torch.zeros(n, heads * hd, device=dev)
+    K.call("fb_d4_sparse_attn", q, heads * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, rd, meta, 0, 0,
+           float(hd ** -0.5), heads, hd, want, heads * hd, n, ns, o_part, ml, None, 0, 0, 0, None)
+    nsp = max(1, min(ns, (W + ktop + 63) // 64))
+    K.call("fb_d4_sparse_attn_tc", q, heads * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, sink, freqs, rd, meta, 0, 0,
+           float(hd ** -0.5), heads, got, heads * hd, n, nsp, o_part, ml, None, 0, 0, 0)
+    torch.cuda.synchronize()
+    err = (got - want).abs().max().item()
+    assert err < 2e-2 * max(1.0, want.abs().max().item()), (err, want.abs().max().item())
