@@ -99,11 +99,15 @@ def main():
                     help="GEMV epilogue fusion: all-reduce + hyper-connection fold, all-reduce only, or separate kernels")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                     help="all-reduce used by the tensor-parallel chain: peer-memory one-shot kernel or NCCL")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="diagnostic: run RANK 0's shard of a TP=R model on one GPU with one-rank collectives (per-rank "
+                         "compute time and shape coverage of a TP=R step; prints a differently named metric)")
     ap.add_argument("--profile", action="store_true",
                     help="open the CUDA profiler window around the timed device loop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    emu = args.emulate_tp if args.emulate_tp > 1 else 0
 
     import torch
     import torch.distributed as dist
@@ -122,18 +126,25 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         from ferrite_b200.parallel.collective import make_allreduce
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * 4096, kind=args.collective)
+    model_world = world
+    if emu:
+        assert world == 1, "--emulate-tp runs as one process"
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29573", rank=0, world_size=1, device_id=dev)
+        from ferrite_b200.parallel.collective import make_allreduce
+        allreduce = make_allreduce(dev, 0, 1, max_elems=64 * 4096, kind="p2p")
+        model_world = emu
 
     cfg = GlmConfig.production() if args.layers == 0 else GlmConfig.scaled(args.layers)
     # 288 experts x 43 MoE layers are 312 GB in fp8: one 180 GB GPU cannot hold them, so at
     # N=1 only the first `resident` experts of every layer are kept and routing is restricted
     # to them.  Per-step work (8 routed experts per token, same matrices) is unchanged.
-    resident = args.experts_resident or (128 if world == 1 else cfg.n_routed_experts)
-    ecfg = EngineConfig(tp=world, max_ctx=args.prompt_len + 3 * (args.steps * 2 + args.warmup * 2 + 16) + 64,
+    resident = args.experts_resident or (128 if model_world == 1 else cfg.n_routed_experts)
+    ecfg = EngineConfig(tp=model_world, max_ctx=args.prompt_len + 3 * (args.steps * 2 + args.warmup * 2 + 16) + 64,
                         mtp_n=1 if args.no_mtp else 3,
                         experts_resident=None if resident >= cfg.n_routed_experts else resident,
-                        fuse_epilogue=args.fuse, moe_shard=args.moe_shard if world > 1 else "inter")
+                        fuse_epilogue=args.fuse, moe_shard=args.moe_shard if model_world > 1 else "inter")
     t0 = time.time()
-    eng = GlmEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank=rank, world=world, device=dev,
+    eng = GlmEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank=rank, world=model_world, device=dev,
                     allreduce=allreduce, prefill_rows=args.prefill_rows)
     torch.cuda.synchronize()
     t_load = time.time() - t0
@@ -199,7 +210,8 @@ def main():
         value = tokens / (ms * 1e-3)
         launches = (eng.launches_mtp if mtp else eng.launches_plain) * args.steps
         out = {
-            "metric": "decode_tok_s_bs1_mtp" if mtp else "decode_tok_s_bs1", "value": round(value, 2),
+            "metric": ("decode_tok_s_bs1_mtp" if mtp else "decode_tok_s_bs1") + (f"_rank0_of_tp{emu}_emulated" if emu else ""),
+            "value": round(value, 2),
             "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": "bf16", "data": "synthetic",
@@ -220,7 +232,7 @@ def main():
             "gpu_launches": launches,
         }
         print(json.dumps(out))
-    if world > 1:
+    if world > 1 or emu:
         dist.destroy_process_group()
     return 0
 
