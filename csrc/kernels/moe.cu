@@ -305,38 +305,41 @@ moe_down_mma_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
     const int kb_n = I >> 7;
     const int nb = (H + 127) >> 7;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const int items = topk * kb_n;
     const size_t ra = (size_t)min(c0 + g, H - 1) * I + t * 32, rb = (size_t)min(c0 + g + 8, H - 1) * I + t * 32;
-    // loads the item's weights and block scale (both one item ahead of their use); returns its local expert or -1
-    auto item_frag = [&](int it, WFrag& f, float& sc) -> int {
-        const int s = it / kb_n, kb = it % kb_n;
-        const int le = ids[r * topk + s] - e_lo;
-        if (le < 0 || le >= e_cnt) return -1;
-        const uint8_t* W = W2 + (size_t)le * H * I + (size_t)kb * 128;
+    // Items are (slot, k-block) pairs; warp w takes items w, w + 8, ...  The coordinates advance incrementally (no
+    // division per item) and the two fragment buffers alternate roles (no register copies): the kernel issues about
+    // as many instructions per weight byte as the memory system can hide, so the bookkeeping is kept minimal.
+    struct Item { int s, kb, le; float sc; };
+    auto advance = [&](Item& q) { q.kb += 8; while (q.kb >= kb_n) { q.kb -= kb_n; ++q.s; } };
+    auto fetch = [&](Item& q, WFrag& f) {   // loads the item's weights and block scale; le = -1: not a local expert
+        q.le = -1;
+        if (q.s >= topk) return;
+        const int le = ids[r * topk + q.s] - e_lo;
+        if (le < 0 || le >= e_cnt) return;
+        const uint8_t* W = W2 + (size_t)le * H * I + (size_t)q.kb * 128;
         f = load_wfrag(W + ra, W + rb);
-        sc = __ldg(S2 + (size_t)le * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
-        return le;
+        q.sc = __ldg(S2 + (size_t)le * nb * kb_n + (size_t)(c0 >> 7) * kb_n + q.kb);
+        q.le = le;
     };
-    WFrag cur, nxt;
-    float sc_cur = 0.f, sc_nxt = 0.f;
-    int le_cur = -1, le_nxt = -1;
-    if (warp < items) le_cur = item_frag(warp, cur, sc_cur);
-    for (int it = warp; it < items; it += 8) {
-        const int in = it + 8;
-        if (in < items) le_nxt = item_frag(in, nxt, sc_nxt);
-        if (le_cur >= 0) {  // warp-uniform
-            const int s = it / kb_n, kb = it % kb_n;
-            const int pair = r * topk + s;
-            uint32_t xh[16], xl[16];
-            load_xfrag<16, false>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, kb * 128 + t * 32, xh, xl);
-            float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_wfrag_fp8<false>(d, cur, xh, xl);
+    auto compute = [&](const Item& q, const WFrag& f) {
+        if (q.le < 0) return;  // warp-uniform
+        const int pair = r * topk + q.s;
+        uint32_t xh[16], xl[16];
+        load_xfrag<16, false>(ahi + (size_t)pair * lda, alo + (size_t)pair * lda, 0, g, 1, q.kb * 128 + t * 32, xh, xl);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_wfrag_fp8<false>(d, f, xh, xl);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc_cur, acc[c]);
-        }
-        cur = nxt;
-        sc_cur = sc_nxt;
-        le_cur = le_nxt;
+        for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], q.sc, acc[c]);
+    };
+    WFrag fa, fb;
+    Item qa{warp / kb_n, warp % kb_n, -1, 0.f}, qb;
+    fetch(qa, fa);
+    while (qa.s < topk) {
+        qb = qa; advance(qb); fetch(qb, fb);
+        compute(qa, fa);
+        if (qb.s >= topk) break;
+        qa = qb; advance(qa); fetch(qa, fa);
+        compute(qb, fb);
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) red[warp][lane][c] = acc[c];
