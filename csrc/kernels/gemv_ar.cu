@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
 gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, const uint16_t* __restrict__ xhi,
                const uint16_t* __restrict__ xlo, int ldx, float* __restrict__ y, int ldo, int mrows, int N, int K,
                int accumulate, int store_y, ArPtrs t, uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status,
-               int rank, int world, int max_elems, int max_spins, int group, HcFold hc) {
+               int rank, int world, int max_elems, int max_spins, int group, HcFold hc, int l2_ahead) {
     pdl_launch();
     constexpr int kTileN = 16 * RT;
     constexpr int KB = FP8 ? 128 : 64;
@@ -132,6 +132,11 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         if (kn < nkb) {
 #pragma unroll
             for (int r = 0; r < RT; ++r) nxt[r] = load_wfrag(wa[r] + (size_t)kn * 128, wb[r] + (size_t)kn * 128);
+        }
+        const int kp = kb + l2_ahead * NW;
+        if (l2_ahead > 0 && kp < nkb && tq == 0) {   // one lane per 128-byte line
+#pragma unroll
+            for (int r = 0; r < RT; ++r) { prefetch_l2(wa[r] + (size_t)kp * 128); prefetch_l2(wb[r] + (size_t)kp * 128); }
         }
         uint32_t xh[XW], xl[XW];
         load_xfrag<XW, !FP8>(xhi, xlo, ldx, g, mrows, kb * KB + tq * (KB / 4), xh, xl);
@@ -318,7 +323,7 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     else if ((N + 31) / 32 <= 256) shape = 2;
     else return (int)cudaErrorInvalidValue;
 #define AR_ARGS (const uint8_t*)W, scales, hi, lo, (int)xs_ld, y, (int)ldo, (int)m, (int)N, (int)K, (int)accumulate, \
-                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)(group > 0 ? group : 32), hc
+                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)(group > 0 ? group : 32), hc, g_fb_l2_ahead
     if (fp8) {
         if (shape == 0) launch_ar<1, 16, true>((int)N, st, AR_ARGS);
         else if (shape == 1) launch_ar<1, 8, true>((int)N, st, AR_ARGS);

@@ -87,6 +87,12 @@ __device__ __forceinline__ void load_xfrag(const uint16_t* __restrict__ hi, cons
 // issued before the current block's math (software pipelining).
 struct WFrag { uint4 a0, a1, b0, b1; };
 
+// Register-free read-ahead: asks L2 for a 128-byte line that a later k-block will load.  The weight-streaming
+// kernels keep one k-block per warp in flight in registers; lines requested two or three k-blocks ahead are in L2
+// by the time they are loaded, which shortens the latency each warp has to cover.
+extern int g_fb_l2_ahead;   // host: read-ahead distance in units of the warp's k-block stride; 0 disables (fb_set_l2_ahead)
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ WFrag load_wfrag(const uint8_t* wa, const uint8_t* wb) {
     WFrag f;
     f.a0 = ldg_nc_v4(wa); f.a1 = ldg_nc_v4(wa + 16);
