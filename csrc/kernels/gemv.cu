@@ -247,41 +247,44 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
         wa[r] = W + (size_t)min(n0 + r * 16 + g, N - 1) * K * esz + (size_t)t * 32;
         wb[r] = W + (size_t)min(n0 + r * 16 + g + 8, N - 1) * K * esz + (size_t)t * 32;
     }
-    WFrag cur[RT], nxt[RT];
-    if (warp < nkb) {
+    // two fragment sets alternate roles (one is loaded while the other is multiplied): no register copies per k-block
+    WFrag fa[RT], fb[RT];
+    auto fetch = [&](WFrag (&f)[RT], int kb) {
 #pragma unroll
-        for (int r = 0; r < RT; ++r) cur[r] = load_wfrag(wa[r] + (size_t)warp * 128, wb[r] + (size_t)warp * 128);
-    }
-    pdl_wait();
-    for (int kb = warp; kb < nkb; kb += NW) {
-        const int kn = kb + NW;
-        if (kn < nkb) {
-#pragma unroll
-            for (int r = 0; r < RT; ++r) nxt[r] = load_wfrag(wa[r] + (size_t)kn * 128, wb[r] + (size_t)kn * 128);
-        }
-        const int kp = kb + l2_ahead * NW;
-        if (l2_ahead > 0 && kp < nkb && t == 0) {   // one lane per 128-byte line
+        for (int r = 0; r < RT; ++r) f[r] = load_wfrag(wa[r] + (size_t)kb * 128, wb[r] + (size_t)kb * 128);
+        const int kp = kb + (l2_ahead - 1) * NW;   // read-ahead into L2, one lane per 128-byte line
+        if (l2_ahead > 1 && kp < nkb && t == 0) {
 #pragma unroll
             for (int r = 0; r < RT; ++r) { prefetch_l2(wa[r] + (size_t)kp * 128); prefetch_l2(wb[r] + (size_t)kp * 128); }
         }
+    };
+    auto compute = [&](const WFrag (&f)[RT], int kb) {
         uint32_t xh[XW], xl[XW];
         load_xfrag<XW, !FP8>(xhi, xlo, ldx, g, mrows, kb * KB + t * (KB / 4), xh, xl);
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
             if (FP8) {
                 float d[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_wfrag_fp8<false>(d, cur[r], reinterpret_cast<const uint32_t(&)[16]>(xh), reinterpret_cast<const uint32_t(&)[16]>(xl));
+                mma_wfrag_fp8<false>(d, f[r], reinterpret_cast<const uint32_t(&)[16]>(xh), reinterpret_cast<const uint32_t(&)[16]>(xl));
                 const float sc = __ldg(scales + (size_t)((n0 + r * 16) >> 7) * kblocks + kb);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(d[c], sc, acc[r][c]);
             } else {
-                mma_wfrag_bf16(acc[r], cur[r], reinterpret_cast<const uint32_t(&)[8]>(xh), reinterpret_cast<const uint32_t(&)[8]>(xl));
+                mma_wfrag_bf16(acc[r], f[r], reinterpret_cast<const uint32_t(&)[8]>(xh), reinterpret_cast<const uint32_t(&)[8]>(xl));
             }
         }
-        if (kn < nkb) {
-#pragma unroll
-            for (int r = 0; r < RT; ++r) cur[r] = nxt[r];
-        }
+    };
+    if (warp < nkb) fetch(fa, warp);
+    pdl_wait();
+    for (int kb = warp; kb < nkb;) {
+        const int k1 = kb + NW;
+        if (k1 < nkb) fetch(fb, k1);
+        compute(fa, kb);
+        if (k1 >= nkb) break;
+        const int k2 = k1 + NW;
+        if (k2 < nkb) fetch(fa, k2);
+        compute(fb, k1);
+        kb = k2;
     }
 #pragma unroll
     for (int r = 0; r < RT; ++r)

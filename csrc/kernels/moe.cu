@@ -249,28 +249,35 @@ moe_gate_up_mma_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const uint16_t* xh_row = xhi + (size_t)r * ldx;
     const uint16_t* xl_row = xlo + (size_t)r * ldx;
-    WFrag cur[2], nxt[2];
-    if (warp < kb_n) {
+    // two fragment sets alternate roles (load one while the other is multiplied): no register copies per k-block
+    WFrag fa[2], fb[2];
+    auto fetch = [&](WFrag (&f)[2], int kb) {
 #pragma unroll
-        for (int q = 0; q < 2; ++q) cur[q] = load_wfrag(wa[q] + (size_t)warp * 128, wb[q] + (size_t)warp * 128);
-    }
-    for (int kb = warp; kb < kb_n; kb += kGuWarps) {
-        const int kn = kb + kGuWarps;
-        if (kn < kb_n) {
-#pragma unroll
-            for (int q = 0; q < 2; ++q) nxt[q] = load_wfrag(wa[q] + (size_t)kn * 128, wb[q] + (size_t)kn * 128);
-        }
+        for (int q = 0; q < 2; ++q) f[q] = load_wfrag(wa[q] + (size_t)kb * 128, wb[q] + (size_t)kb * 128);
+    };
+    auto compute = [&](const WFrag (&f)[2], int kb) {
         uint32_t xh[16], xl[16];
         load_xfrag<16, false>(xh_row, xl_row, 0, g, 1, kb * 128 + t * 32, xh, xl);  // column 0 only
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_wfrag_fp8<false>(d, cur[q], xh, xl);
+            mma_wfrag_fp8<false>(d, f[q], xh, xl);
             const float sc = __ldg(S + (size_t)rowblk[q] * kb_n + kb);
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[q][c] = fmaf(d[c], sc, acc[q][c]);
         }
-        if (kn < kb_n) { cur[0] = nxt[0]; cur[1] = nxt[1]; }
+    };
+    int kb = warp;
+    if (kb < kb_n) fetch(fa, kb);
+    while (kb < kb_n) {
+        const int k1 = kb + kGuWarps;
+        if (k1 < kb_n) fetch(fb, k1);
+        compute(fa, kb);
+        if (k1 >= kb_n) break;
+        const int k2 = k1 + kGuWarps;
+        if (k2 < kb_n) fetch(fa, k2);
+        compute(fb, k1);
+        kb = k2;
     }
 #pragma unroll
     for (int q = 0; q < 2; ++q)
