@@ -102,28 +102,34 @@ moe_gate_up_grp_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
         rowblk[q] = (base + i0) >> 7;
     }
     float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    WFrag cur[2], nxt[2];
-    if (warp < kb_n) {
+    WFrag fa[2], fb[2];   // alternate roles: no register copies per k-block
+    auto fetch = [&](WFrag (&f)[2], int kb) {
 #pragma unroll
-        for (int q = 0; q < 2; ++q) cur[q] = load_wfrag(wa[q] + (size_t)warp * 128, wb[q] + (size_t)warp * 128);
-    }
-    for (int kb = warp; kb < kb_n; kb += kGuWarps) {
-        const int kn = kb + kGuWarps;
-        if (kn < kb_n) {
-#pragma unroll
-            for (int q = 0; q < 2; ++q) nxt[q] = load_wfrag(wa[q] + (size_t)kn * 128, wb[q] + (size_t)kn * 128);
-        }
+        for (int q = 0; q < 2; ++q) f[q] = load_wfrag(wa[q] + (size_t)kb * 128, wb[q] + (size_t)kb * 128);
+    };
+    auto compute = [&](const WFrag (&f)[2], int kb) {
         uint32_t xh[16];
         load_xfrag_gather(xhi, ldx, my_row, kb * 128 + t * 32, xh);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             float d[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_wfrag_fp8<false>(d, cur[q], xh, xh);
+            mma_wfrag_fp8<false>(d, f[q], xh, xh);
             const float sc = __ldg(S + (size_t)rowblk[q] * kb_n + kb);
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[q][c] = fmaf(d[c], sc, acc[q][c]);
         }
-        if (kn < kb_n) { cur[0] = nxt[0]; cur[1] = nxt[1]; }
+    };
+    int kb = warp;
+    if (kb < kb_n) fetch(fa, kb);
+    while (kb < kb_n) {
+        const int k1 = kb + kGuWarps;
+        if (k1 < kb_n) fetch(fb, k1);
+        compute(fa, kb);
+        if (k1 >= kb_n) break;
+        const int k2 = k1 + kGuWarps;
+        if (k2 < kb_n) fetch(fa, k2);
+        compute(fb, k1);
+        kb = k2;
     }
 #pragma unroll
     for (int q = 0; q < 2; ++q)
@@ -145,8 +151,9 @@ moe_gate_up_grp_kernel(const uint8_t* __restrict__ W13, const float* __restrict_
     }
 }
 
-// grid (H / 16, max_groups), 256 threads.  W2 [e_cnt][H][I], S2 [e_cnt][H/128][I/128];
-// act: f16 hi plane [pairs][lda]; ypair [pairs][H].
+// grid (H / 32, max_groups), 256 threads = two groups of four warps; a group owns 16 output rows and its warps
+// split K (512 contiguous bytes of a weight row per step of the group).  W2 [e_cnt][H][I], S2 [e_cnt][H/128][I/128];
+// act: f16 hi plane [pairs][lda]; ypair [pairs][H].  Two fragment buffers alternate (no register copies).
 __global__ void __launch_bounds__(256, 3)
 moe_down_grp_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2, const uint16_t* __restrict__ ahi, int lda,
                     const int* __restrict__ g_pairs, const int* __restrict__ g_expert, const int* __restrict__ n_groups,
@@ -158,39 +165,50 @@ moe_down_grp_kernel(const uint8_t* __restrict__ W2, const float* __restrict__ S2
     const int le = g_expert[grp];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int c0 = blockIdx.x * 16;
+    const int half = warp >> 2, wk = warp & 3;
+    const int c0 = (blockIdx.x * 2 + half) * 16;
     const int kb_n = I >> 7;
     const int nb = (H + 127) >> 7;
     const int my_pair = g_pairs[(size_t)grp * 8 + g];
     const uint8_t* W = W2 + (size_t)le * H * I;
     const size_t ra = (size_t)min(c0 + g, H - 1) * I + t * 32, rb = (size_t)min(c0 + g + 8, H - 1) * I + t * 32;
+    const float* S = S2 + (size_t)le * nb * kb_n + (size_t)(min(c0, H - 1) >> 7) * kb_n;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    WFrag cur, nxt;
-    if (warp < kb_n) cur = load_wfrag(W + ra + (size_t)warp * 128, W + rb + (size_t)warp * 128);
-    for (int kb = warp; kb < kb_n; kb += 8) {
-        const int kn = kb + 8;
-        if (kn < kb_n) nxt = load_wfrag(W + ra + (size_t)kn * 128, W + rb + (size_t)kn * 128);
+    WFrag fa, fb;
+    auto compute = [&](const WFrag& f, int kb) {
         uint32_t xh[16];
         load_xfrag_gather(ahi, lda, my_pair, kb * 128 + t * 32, xh);
         float d[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_wfrag_fp8<false>(d, cur, xh, xh);
-        const float sc = __ldg(S2 + (size_t)le * nb * kb_n + (size_t)(c0 >> 7) * kb_n + kb);
+        mma_wfrag_fp8<false>(d, f, xh, xh);
+        const float sc = __ldg(S + kb);
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[c] = fmaf(d[c], sc, acc[c]);
-        if (kn < kb_n) cur = nxt;
+    };
+    int kb = wk;
+    if (kb < kb_n) fa = load_wfrag(W + ra + (size_t)kb * 128, W + rb + (size_t)kb * 128);
+    while (kb < kb_n) {
+        const int k1 = kb + 4;
+        if (k1 < kb_n) fb = load_wfrag(W + ra + (size_t)k1 * 128, W + rb + (size_t)k1 * 128);
+        compute(fa, kb);
+        if (k1 >= kb_n) break;
+        const int k2 = k1 + 4;
+        if (k2 < kb_n) fa = load_wfrag(W + ra + (size_t)k2 * 128, W + rb + (size_t)k2 * 128);
+        compute(fb, k1);
+        kb = k2;
     }
 #pragma unroll
     for (int c = 0; c < 4; ++c) red[warp][lane][c] = acc[c];
     __syncthreads();
-    if (threadIdx.x < 128) {
-        const int j = threadIdx.x & 15, col = threadIdx.x >> 4;
+    {   // thread -> (tile of the CTA, tile row j, column): sums the four warps of its tile
+        const int th = threadIdx.x >> 7, j = threadIdx.x & 15, col = (threadIdx.x >> 4) & 7;
+        const int row = (blockIdx.x * 2 + th) * 16 + j;
         const int pair = g_pairs[(size_t)grp * 8 + col];
-        if (pair >= 0 && c0 + j < H) {
+        if (pair >= 0 && row < H) {
             const int l = (j & 7) * 4 + (col >> 1), c = (j >> 3) * 2 + (col & 1);
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) v += red[w][l][c];
-            ypair[(size_t)pair * H + c0 + j] = v;
+            for (int w = 0; w < 4; ++w) v += red[th * 4 + w][l][c];
+            ypair[(size_t)pair * H + row] = v;
         }
     }
 }
@@ -242,7 +260,7 @@ FB_API int fb_moe_down_grp(const void* W2, const float* S2, const void* as_base,
                            int64_t max_groups, int64_t I, int64_t H, cudaStream_t st) {
     if ((I % 128) || (as_ld % 8)) return (int)cudaErrorInvalidValue;
     const uint16_t* hi = (const uint16_t*)as_base + 2 * as_plane;
-    dim3 grid((unsigned)((H + 15) / 16), (unsigned)max_groups);
+    dim3 grid((unsigned)((H + 31) / 32), (unsigned)max_groups);
     FB_LAUNCH((moe_down_grp_kernel), grid, 256, 0, st, (const uint8_t*)W2, S2, hi, (int)as_ld, g_pairs, g_expert, n_groups, ypair,
               (int)I, (int)H);
     return FB_LAUNCH_CHECK();
