@@ -407,7 +407,9 @@ class GlmDeviceModel:
         fp8 = scales is not None
         kb = 128 if fp8 else 64
         use_mma = xa is not None and xa.s is not None and K % kb == 0 and group_rows % 16 == 0 and ldx % 8 == 0
-        if use_mma and not fp8 and group_rows == 0 and m >= self.tc_min_rows:
+        tc_min_n = getattr(self, "tc_gemv_min_n", 0)
+        tc_gemv = use_mma and not fp8 and group_rows == 0 and 8 < m <= 16 and tc_min_n and N >= tc_min_n and K % 64 == 0
+        if use_mma and not fp8 and group_rows == 0 and m >= self.tc_min_rows and not tc_gemv:
             # prefill-sized row counts: TMA + tcgen05 GEMM over the bf16 high plane of the activations
             xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
             op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
@@ -416,8 +418,7 @@ class GlmDeviceModel:
                 self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
                             omask, m, N)
             return
-        tc_min_n = getattr(self, "tc_gemv_min_n", 0)
-        if use_mma and not fp8 and group_rows == 0 and m <= 16 and tc_min_n and N >= tc_min_n and K % 64 == 0:
+        if tc_gemv or (use_mma and not fp8 and group_rows == 0 and m <= 16 and tc_min_n and N >= tc_min_n and K % 64 == 0):
             # decode-sized rows of a large matrix: TMA + tcgen05 split-K GEMV (bf16 hi + lo activation planes)
             tiles = (N + 127) // 128
             nsplit = max(1, min(K // 256, -(-296 // tiles)))
