@@ -113,17 +113,24 @@ expert_gate_up_mma_kernel(const uint16_t* __restrict__ xh, int ldx, const int* _
     const uint8_t* su = sg + (size_t)I * srow;
     const uint16_t* xr = xh + (size_t)r * ldx;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    Fp4Frag f0, f1, f2;
-    if (warp < nkb) f0 = load_fp4(wg, wu, sg, su, warp, tq);
-    if (warp + kNW < nkb) f1 = load_fp4(wg, wu, sg, su, warp + kNW, tq);
-    for (int kb = warp; kb < nkb; kb += kNW) {
-        const int k2 = kb + 2 * kNW;
-        if (k2 < nkb) f2 = load_fp4(wg, wu, sg, su, k2, tq);
+    // two fragment buffers alternate roles (one loads while the other is multiplied): no register copies
+    Fp4Frag fa, fb;
+    auto compute = [&](const Fp4Frag& f, int kb) {
         uint4 x[4];
         load_x_fp4(x, xr, kb * 128, g, tq);
-        mma_block_fp4(acc, f0.wa, f0.wb, f0.sa, f0.sb, x);
-        f0 = f1;
-        f1 = f2;
+        mma_block_fp4(acc, f.wa, f.wb, f.sa, f.sb, x);
+    };
+    int kb = warp;
+    if (kb < nkb) fa = load_fp4(wg, wu, sg, su, kb, tq);
+    while (kb < nkb) {
+        const int k1 = kb + kNW;
+        if (k1 < nkb) fb = load_fp4(wg, wu, sg, su, k1, tq);
+        compute(fa, kb);
+        if (k1 >= nkb) break;
+        const int k2 = k1 + kNW;
+        if (k2 < nkb) fa = load_fp4(wg, wu, sg, su, k2, tq);
+        compute(fb, k1);
+        kb = k2;
     }
     if (tq == 0) { red[warp][0][g] = acc[0]; red[warp][1][g] = acc[2]; }   // column 0: gate (row g), up (row g + 8)
     __syncthreads();
@@ -143,32 +150,38 @@ expert_down_mma_kernel(const uint16_t* __restrict__ hh, const int* __restrict__ 
     __shared__ float red[kNW][16];
     const int r = blockIdx.y, c0 = blockIdx.x * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-    const int nfull = I >> 7, nkb = (I + 127) >> 7, items = topk * nkb;   // a slot's last k-block may hold 64 values
+    const int nfull = I >> 7, nkb = (I + 127) >> 7;   // a slot's last k-block may hold 64 values
     const size_t wrow = (size_t)I / 2, srow = (size_t)I / 32;
     const int ra = min(c0 + g, D - 1), rb = min(c0 + g + 8, D - 1);
     pdl_wait();
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    auto load_item = [&](int it) {
-        const int s = it / nkb, kb = it - s * nkb;
-        const int e = idx[(size_t)r * topk + s];
+    // items are (slot, k-block) pairs; coordinates advance incrementally (no division per item), two fragment
+    // buffers alternate roles
+    struct Item { int s, kb; };
+    auto advance = [&](Item& q) { q.kb += kNW; while (q.kb >= nkb) { q.kb -= nkb; ++q.s; } };
+    auto fetch = [&](const Item& q, Fp4Frag& f) {
+        if (q.s >= topk) return;
+        const int e = idx[(size_t)r * topk + q.s];
         const uint8_t* wb = w2 + (size_t)e * D * wrow;
         const uint8_t* sb = s2 + (size_t)e * D * srow;
-        if (kb < nfull) return load_fp4(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
-        return load_fp4_tail(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, kb, tq);
+        f = q.kb < nfull ? load_fp4(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, q.kb, tq)
+                         : load_fp4_tail(wb + ra * wrow, wb + rb * wrow, sb + ra * srow, sb + rb * srow, q.kb, tq);
     };
-    Fp4Frag f0, f1, f2;
-    if (warp < items) f0 = load_item(warp);
-    if (warp + kNW < items) f1 = load_item(warp + kNW);
-    for (int it = warp; it < items; it += kNW) {
-        const int i2 = it + 2 * kNW;
-        if (i2 < items) f2 = load_item(i2);
-        const int s = it / nkb, kb = it - s * nkb;
-        const int nb = kb < nfull ? 4 : 2;
+    auto compute = [&](const Item& q, const Fp4Frag& f) {
+        const int nb = q.kb < nfull ? 4 : 2;
         uint4 x[4];
-        load_x_fp4(x, hh + ((size_t)r * topk + s) * I, kb * 128, g, tq, nb);
-        mma_block_fp4(acc, f0.wa, f0.wb, f0.sa, f0.sb, x, nb);
-        f0 = f1;
-        f1 = f2;
+        load_x_fp4(x, hh + ((size_t)r * topk + q.s) * I, q.kb * 128, g, tq, nb);
+        mma_block_fp4(acc, f.wa, f.wb, f.sa, f.sb, x, nb);
+    };
+    Fp4Frag fa, fb;
+    Item qa{warp / nkb, warp % nkb}, qb;
+    fetch(qa, fa);
+    while (qa.s < topk) {
+        qb = qa; advance(qb); fetch(qb, fb);
+        compute(qa, fa);
+        if (qb.s >= topk) break;
+        qa = qb; advance(qa); fetch(qa, fa);
+        compute(qb, fb);
     }
     if (tq == 0) { red[warp][g] = acc[0]; red[warp][g + 8] = acc[2]; }
     __syncthreads();
