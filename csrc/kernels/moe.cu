@@ -21,15 +21,12 @@ __device__ __forceinline__ uint32_t okey(float f) {
 }
 
 // One block (256 threads) per row; E <= 1024.
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int* __restrict__ ids,
-                 float* __restrict__ wts, int E, int topk, float scaling) {
-    PDL_PROLOGUE();
+__device__ __forceinline__ void moe_route_row(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                              int* __restrict__ ids, float* __restrict__ wts, int E, int topk, float scaling, int r) {
     __shared__ unsigned long long wbest[8];
     __shared__ unsigned long long s_pick;
     __shared__ float s_sig[1024];
     __shared__ float s_sel[32];
-    const int r = blockIdx.x;
     unsigned long long key[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -74,6 +71,14 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restri
         for (int k = 0; k < topk; ++k) wts[(size_t)r * topk + k] = s_sel[k] * inv;
     }
 }
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int* __restrict__ ids,
+                 float* __restrict__ wts, int E, int topk, float scaling) {
+    PDL_PROLOGUE();
+    moe_route_row(logits, ld, bias, ids, wts, E, topk, scaling, blockIdx.x);
+}
+
 
 // act[r][s][i] = swiglu(gate_i . x_r, up_i . x_r) for expert ids[r][s]; one warp owns IPW pairs.
 template <int IPW>
@@ -377,7 +382,40 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, float* __res
     split_store(asplit, r, i, v);
 }
 
+// Route and the shared expert's SwiGLU in one launch: both read the row of [router logits | shared gate | shared up]
+// that one GEMV produced.  grid (1 + ceil(I / 256), rows): block x == 0 routes, the others apply the SwiGLU.
+__global__ void __launch_bounds__(256)
+moe_route_swiglu_kernel(const float* __restrict__ lg, int ld, const float* __restrict__ bias, int* __restrict__ ids,
+                        float* __restrict__ wts, int E, int topk, float scaling, float* __restrict__ act, int I, float limit,
+                        SplitBuf asplit) {
+    PDL_PROLOGUE();
+    if (blockIdx.x == 0) {
+        moe_route_row(lg, ld, bias, ids, wts, E, topk, scaling, blockIdx.y);
+        return;
+    }
+    const int r = blockIdx.y;
+    const int i = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float* gu = lg + E;
+    const float g = fminf(gu[(size_t)r * ld + i], limit);
+    const float u = fminf(fmaxf(gu[(size_t)r * ld + I + i], -limit), limit);
+    const float v = siluf_(g) * u;
+    if (act) act[(size_t)r * I + i] = v;
+    split_store(asplit, r, i, v);
+}
+
 }  // namespace
+
+// lg [n, ld] = [E router logits | I shared gate | I shared up] per row; act / split planes get the shared SwiGLU.
+FB_API int fb_moe_route_swiglu(const float* lg, int64_t ld, const float* bias, int* ids, float* wts, int64_t n, int64_t E,
+                               int64_t topk, float scaling, float* act, void* s_base, int64_t s_ld, int64_t s_plane,
+                               int64_t s_mask, int64_t I, float limit, cudaStream_t st) {
+    if (E > 1024 || topk > 32) return (int)cudaErrorInvalidValue;
+    SplitBuf sp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    FB_LAUNCH((moe_route_swiglu_kernel), dim3((unsigned)(1 + (I + 255) / 256), (unsigned)n), 256, 0, st, lg, (int)ld, bias, ids,
+              wts, (int)E, (int)topk, scaling, act, (int)I, limit, sp);
+    return FB_LAUNCH_CHECK();
+}
 
 FB_API int fb_moe_route(const float* logits, int64_t ld, const float* bias, int* ids, float* wts, int64_t n,
                         int64_t E, int64_t topk, float scaling, cudaStream_t st) {

@@ -580,10 +580,9 @@ class GlmDeviceModel:
         ldl = ws["moe_lg"].shape[1]
         act, x = ws["act"], ws["x"]
         self.gemv(L["gate_s13"], x, ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
-        self.K.call("fb_moe_route", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
-                    float(cfg.routed_scaling_factor))
-        self.K.call("fb_swiglu_split", View(ws["moe_lg"], E), ldl, act.f, *act.sp(1, ld=Is), n, Is,
-                    float(cfg.swiglu_limit))
+        # routing and the shared expert's SwiGLU read the same GEMV output row: one launch
+        self.K.call("fb_moe_route_swiglu", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
+                    float(cfg.routed_scaling_factor), act.f, *act.sp(1, ld=Is), Is, float(cfg.swiglu_limit))
         # routed experts write y, the shared expert's down projection adds to it and carries the
         # all-reduce (and the hyper-connection fold) in its epilogue
         if H % 128 == 0 and Il % 128 == 0 and n > self.moe_group_rows:
