@@ -122,10 +122,15 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     allreduce = None
+    collective_check = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from ferrite_b200.parallel.collective import make_allreduce
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * 4096, kind=args.collective)
+        if args.collective == "p2p":
+            # start-up check of the peer-memory kernels against NCCL; a fused kernel that fails is detached
+            from ferrite_b200.parallel.collective import self_test
+            collective_check = self_test(allreduce, dev, rank, world)
     model_world = world
     if emu:
         assert world == 1, "--emulate-tp runs as one process"
@@ -221,7 +226,7 @@ def main():
             "impl": "ours",
             "config": {"model": "GLM-5.3-Flash (45 layers: 34 GatedDeltaNet + 11 DSA, 3 dense + 42 MoE, 1 MTP layer)"
                                 if args.layers == 0 else f"DEBUG {args.layers}-layer slice (invalid as a result)",
-                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none", "gemv_epilogue_fusion": args.fuse, "moe_shard": args.moe_shard if world > 1 else "n/a",
+                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}", "collective": args.collective if world > 1 else "none", "gemv_epilogue_fusion": args.fuse, "moe_shard": args.moe_shard if world > 1 else "n/a", "collective_self_test": collective_check,
                        "weights": "random-init; bf16, routed experts + dense FFN fp8 e4m3 128x128 block-scaled (W8A16)",
                        "mtp": "draft 2 / verify 3" if mtp else "off",
                        "accept_tokens_per_step": round(tokens / args.steps, 3),
