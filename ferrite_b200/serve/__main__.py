@@ -55,8 +55,11 @@ def build_engine(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-        from ..parallel.collective import make_allreduce
+        from ..parallel.collective import make_allreduce, self_test
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * cfg.hidden_size, kind="p2p")
+        verdict = self_test(allreduce, dev, rank, world)   # a fused kernel that fails its check is detached
+        if rank == 0:
+            print(f"collective self-test: {verdict}", flush=True)
     from ..models.glm import SyntheticSource
     if args.model_dir and not args.synthetic:
         from ..models.checkpoint import CheckpointSource
@@ -110,8 +113,11 @@ def _build_dsv41(args, tok):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-        from ..parallel.collective import make_allreduce
+        from ..parallel.collective import make_allreduce, self_test
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * max(cfg.dim, 4096), kind="p2p")
+        verdict = self_test(allreduce, dev, rank, world)   # a fused kernel that fails its check is detached
+        if rank == 0:
+            print(f"collective self-test: {verdict}", flush=True)
     eng = Dsv41Engine(cfg, src, rank, world, dev, allreduce, max_ctx=args.max_ctx)
     serve_eng = SingleFlight(Dsv41StepEngine(eng, spec=args.mtp > 1))
     if world > 1:
