@@ -217,6 +217,21 @@ def make_cases(K, only):
             K.call("fb_gemm_tc_bf16", w, x, Kd, out, N, M, N, Kd, 0, status)
         cases.append(Case(name, N * Kd * 2, tcfn, f"M={M} N={N} K={Kd} FLOP={2 * M * N * Kd}"))
 
+    # ---- the fused GEMM + all-reduce kernel with one rank: its tcgen05 / TMA pipeline without the collective --------
+    if want("gemm_tc_ar"):
+        from ferrite_b200.parallel.symm import FusedGemmAllReduce
+        gar = FusedGemmAllReduce(torch.device("cuda"), 0, 1, max_rows=256, n_max=4096)
+        for tag, M, N, Kd in (("o_proj.m256", 256, 4096, 8192), ("o_proj.m64", 64, 4096, 8192)):
+            ws_ = [torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) for _ in range(4)]   # 4 x 67 MB > L2
+            x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+            out = torch.zeros(M, N, device=dev)
+            stg = {"i": 0}
+
+            def garfn(ws_=ws_, x=x, out=out, stg=stg, M=M, N=N, Kd=Kd):
+                w = ws_[stg["i"] % 4]; stg["i"] += 1
+                gar(w, x, Kd, out, N, M, N, Kd, False)
+            cases.append(Case(f"gemm_tc_ar.world1.{tag}", N * Kd * 2, garfn, f"M={M} N={N} K={Kd} FLOP={2 * M * N * Kd}"))
+
     # ---- DSV41: fp4 experts (TP8 slice), sparse attention with sink, indexer scoring -----------------
     if want("d4_expert"):
         E, n, topk, I, D = 384, 1, 6, 320, 5120
