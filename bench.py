@@ -102,6 +102,8 @@ def main():
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="diagnostic: run RANK 0's shard of a TP=R model on one GPU with one-rank collectives (per-rank "
                          "compute time and shape coverage of a TP=R step; prints a differently named metric)")
+    ap.add_argument("--profile-prefill", action="store_true",
+                    help="open the CUDA profiler window around the prefill instead (for ncu --profile-from-start off)")
     ap.add_argument("--profile", action="store_true",
                     help="open the CUDA profiler window around the timed device loop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -158,10 +160,14 @@ def main():
     t_load = time.time() - t0
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
+    if args.profile_prefill:
+        torch.cuda.profiler.start()
     t0 = time.time()
     eng.prefill(prompt)
     torch.cuda.synchronize()
     t_prefill = time.time() - t0
+    if args.profile_prefill:
+        torch.cuda.profiler.stop()
     mtp = not args.no_mtp
     eng.build_graphs(mtp)
     m = eng.model

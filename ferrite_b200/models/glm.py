@@ -106,6 +106,7 @@ class GlmDeviceModel:
         self.dcp = None          # (d, n_dcp, DcpAttentionMerge): decode-context-parallel attention
         # decode GEMVs with at least this many output rows go to the tcgen05 split-K kernel (0 = never)
         self.tc_gemv_min_n = int(os.environ.get("FERRITE_TC_GEMV_MIN_N", "0"))
+        self.tc_gemv_max_n = int(os.environ.get("FERRITE_TC_GEMV_MAX_N", "0"))
         self._tc_part = self._tc_ticket = None
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
@@ -408,7 +409,9 @@ class GlmDeviceModel:
         kb = 128 if fp8 else 64
         use_mma = xa is not None and xa.s is not None and K % kb == 0 and group_rows % 16 == 0 and ldx % 8 == 0
         tc_min_n = getattr(self, "tc_gemv_min_n", 0)
-        tc_gemv = use_mma and not fp8 and group_rows == 0 and 8 < m <= 16 and tc_min_n and N >= tc_min_n and K % 64 == 0
+        tc_max_n = getattr(self, "tc_gemv_max_n", 0)   # 9-16 rows: matrices with few row tiles leave the plain GEMM with few CTAs
+        tc_gemv = (use_mma and not fp8 and group_rows == 0 and 8 < m <= 16 and K % 64 == 0
+                   and ((tc_min_n and N >= tc_min_n) or (tc_max_n and N <= tc_max_n)))
         if use_mma and not fp8 and group_rows == 0 and m >= self.tc_min_rows and not tc_gemv:
             # prefill-sized row counts: TMA + tcgen05 GEMM over the bf16 high plane of the activations
             xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
