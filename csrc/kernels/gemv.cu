@@ -235,6 +235,12 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
     const int n0 = blockIdx.x * 16 * RT;
     const int nkb = K / KB;
     const int kblocks = (K + 127) >> 7;
+    // blockIdx.y walks 8-row windows of the activations: prefill-sized row counts take one launch, every
+    // window streams the weights again (from L2 after the first)
+    const int r0 = blockIdx.y * 8;
+    xhi += (size_t)r0 * ldx;
+    xlo += (size_t)r0 * ldx;
+    mrows = min(8, mrows - r0);
     if (group_rows > 0) { const size_t go = (size_t)(n0 / group_rows) * K; xhi += go; xlo += go; }
     float acc[RT][4];
 #pragma unroll
@@ -299,10 +305,10 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; ++w) v += red[w][r][l][c];
-            float* o = out + (size_t)col * ldo + row;
+            float* o = out + (size_t)(r0 + col) * ldo + row;
             if (accumulate) v += *o;
             *o = v;
-            split_store(osplit, col, row, v);
+            split_store(osplit, r0 + col, row, v);
         }
     }
 }
@@ -316,13 +322,13 @@ int launch_mma(const void* W, const float* scales, const uint16_t* xs, int ldx, 
     constexpr int KB = FP8 ? 128 : 64;
     const int nkb = K / KB;
     if (N >= 9472 && (group_rows == 0 || group_rows % 32 == 0)) {
-        FB_LAUNCH((gemv_mma_kernel<2, 8, FP8>), (N + 31) / 32, 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<2, 8, FP8>), dim3((unsigned)((N + 31) / 32), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
     } else if (nkb >= 64 && N <= 8192) {  // few row tiles, long rows: split K over 16 warps
-        FB_LAUNCH((gemv_mma_kernel<1, 16, FP8>), (N + 15) / 16, 512, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 16, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 512, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
     } else if (nkb >= 8) {
-        FB_LAUNCH((gemv_mma_kernel<1, 8, FP8>), (N + 15) / 16, 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 8, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
     } else {
-        FB_LAUNCH((gemv_mma_kernel<1, 2, FP8>), (N + 15) / 16, 64, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 2, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 64, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
     }
     return FB_LAUNCH_CHECK();
 }
@@ -387,7 +393,7 @@ FB_API int fb_gemv_fp8(const void* W, const float* scales, const float* x, int64
 FB_API int fb_gemv_mma_bf16(const void* W, const void* xs, int64_t xs_ld, int64_t xs_plane, float* out,
                             int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t group_rows, int64_t accumulate,
                             void* os_base, int64_t os_ld, int64_t os_plane, int64_t os_mask, cudaStream_t st) {
-    if (m < 1 || m > 8 || (K % 64) || (xs_ld % 8) || (group_rows % 16)) return (int)cudaErrorInvalidValue;
+    if (m < 1 || m > 8 * 65535 || (K % 64) || (xs_ld % 8) || (group_rows % 16)) return (int)cudaErrorInvalidValue;
     SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
     return launch_mma<false>(W, nullptr, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
                              (int)K, (int)group_rows, (int)accumulate, os, st);
@@ -396,7 +402,7 @@ FB_API int fb_gemv_mma_bf16(const void* W, const void* xs, int64_t xs_ld, int64_
 FB_API int fb_gemv_mma_fp8(const void* W, const float* scales, const void* xs, int64_t xs_ld, int64_t xs_plane,
                            float* out, int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t accumulate,
                            void* os_base, int64_t os_ld, int64_t os_plane, int64_t os_mask, cudaStream_t st) {
-    if (m < 1 || m > 8 || (K % 128) || (xs_ld % 8)) return (int)cudaErrorInvalidValue;
+    if (m < 1 || m > 8 * 65535 || (K % 128) || (xs_ld % 8)) return (int)cudaErrorInvalidValue;
     SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
     return launch_mma<true>(W, scales, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
                             (int)K, 0, (int)accumulate, os, st);

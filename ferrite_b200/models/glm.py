@@ -437,6 +437,17 @@ class GlmDeviceModel:
                 self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
                             omask, m, N)
             return
+        if use_mma:
+            # one launch: the kernel's second grid dimension walks the 8-row windows
+            op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
+            osb = ((_lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane, omask) if oa is not None and omask
+                   else (None, 0, 0, 0))
+            xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
+            if fp8:
+                self.K.call("fb_gemv_mma_fp8", w, scales, xp, ldx, xa.plane, op, ldo, m, N, K, accumulate, *osb)
+            else:
+                self.K.call("fb_gemv_mma_bf16", w, xp, ldx, xa.plane, op, ldo, m, N, K, group_rows, accumulate, *osb)
+            return
         for r0 in range(0, m, 8):
             mm = min(8, m - r0)
             op = _lib.ctypes.c_void_p(of.data_ptr() + (r0 * ldo + ocol) * 4)
