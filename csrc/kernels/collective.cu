@@ -202,6 +202,7 @@ __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, int max_sp
 FB_API int fb_symm_alloc(int64_t bytes, void** out) {
     cudaError_t e = cudaMalloc(out, (size_t)bytes);
     if (e == cudaSuccess) e = cudaMemset(*out, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();   // zeroed before any peer can learn the address
     return (int)e;
 }
 FB_API int fb_symm_free(void* p) { return (int)cudaFree(p); }

@@ -31,7 +31,7 @@ class _Ptr:
 
 class EpMoE:
     def __init__(self, device, rank: int, world: int, n_max: int, hidden: int, topk: int, inter: int,
-                 max_spins: int = 2_000_000, group=None):
+                 max_spins: int = 20_000_000, group=None):
         self.K = _lib.lib()
         self.dev, self.rank, self.world = torch.device(device), rank, world
         self.n_max, self.H, self.topk, self.I, self.max_spins = n_max, hidden, topk, inter, max_spins

@@ -70,7 +70,7 @@ class P2PAllReduce:
     """Callable ``f(view)``: in-place sum of a contiguous f32 view across the ranks, one
     kernel launch on the current stream.  ``check()`` reads the status word on the host."""
 
-    def __init__(self, device, rank: int, world: int, max_elems: int, max_spins: int = 2_000_000, group=None):
+    def __init__(self, device, rank: int, world: int, max_elems: int, max_spins: int = 20_000_000, group=None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         mc, ce = ctypes.c_int(), ctypes.c_int()
@@ -126,7 +126,7 @@ class FusedGemvAllReduce:
     the fold epilogue into the GEMV.  ``check()`` reads the status word on the host."""
 
     def __init__(self, device, rank: int, world: int, max_rows: int = 8, n_max: int = 8192,
-                 max_spins: int = 2_000_000, group=None):
+                 max_spins: int = 20_000_000, group=None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         mt, mw, fw = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
@@ -201,7 +201,7 @@ class FusedGemmAllReduce:
     the fused kernel (co-resident grid, at least one tile per rank)."""
 
     def __init__(self, device, rank: int, world: int, max_rows: int = 256, n_max: int = 8192,
-                 max_spins: int = 2_000_000, group=None, mode: int = 0):
+                 max_spins: int = 20_000_000, group=None, mode: int = 0):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         self.max_rows, self.n_max = max_rows, n_max
@@ -261,7 +261,7 @@ class CrossRankArgmax:
     """Greedy token of a vocab-sliced head: per-rank argmax partials merged over the ranks in one
     small kernel (``fb_argmax_xchg``); every rank gets the same global token id."""
 
-    def __init__(self, device, rank: int, world: int, max_spins: int = 2_000_000, group=None):
+    def __init__(self, device, rank: int, world: int, max_spins: int = 20_000_000, group=None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         mr = ctypes.c_int()
@@ -302,7 +302,7 @@ class DcpAttentionMerge:
     (``csrc/kernels/dsa_dcp.cu``): one launch per attention layer."""
 
     def __init__(self, device, rank: int, world: int, max_rows: int, heads: int, latent_dim: int,
-                 max_spins: int = 2_000_000, group=None):
+                 max_spins: int = 20_000_000, group=None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
         self.slot_elems = max_rows * heads * (latent_dim + 4)
