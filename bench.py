@@ -141,9 +141,6 @@ def main():
         allreduce = make_allreduce(dev, 0, 1, max_elems=64 * 4096, kind="p2p")
         model_world = emu
 
-    if os.environ.get("FERRITE_L2_AHEAD") is not None:
-        from ferrite_b200 import _lib
-        _lib.lib().lib.fb_set_l2_ahead(int(os.environ["FERRITE_L2_AHEAD"]))
     cfg = GlmConfig.production() if args.layers == 0 else GlmConfig.scaled(args.layers)
     # 288 experts x 43 MoE layers are 312 GB in fp8: one 180 GB GPU cannot hold them, so at
     # N=1 only the first `resident` experts of every layer are kept and routing is restricted

@@ -311,6 +311,10 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
         t.staging[i] = (float*)staging_ptrs[i];
         t.flags[i] = (uint32_t*)flag_ptrs[i];
     }
+    // One published group per launch (`group` is kept in the ABI and ignored): with several groups each group has
+    // its own epoch, launches of different widths advance them unevenly, and two launches could then meet on the
+    // same staging parity while a peer still reduces the earlier one.  One group = one epoch per launch.
+    (void)group;
     HcFold hc{Rin, Rout, post, comb, fn, acc, (int)mix, part, part_n};
     if (Rin && fn && (!part || !part_n)) return (int)cudaErrorInvalidValue;
     if (Rin && (N % 32)) return (int)cudaErrorInvalidValue;  // the fold works on whole column tiles
@@ -326,7 +330,7 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     else if ((N + 31) / 32 <= 256) shape = 2;
     else return (int)cudaErrorInvalidValue;
 #define AR_ARGS (const uint8_t*)W, scales, hi, lo, (int)xs_ld, y, (int)ldo, (int)m, (int)N, (int)K, (int)accumulate, \
-                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)(group > 0 ? group : 32), hc, g_fb_l2_ahead
+                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)kMaxTiles, hc, g_fb_l2_ahead
     if (fp8) {
         if (shape == 0) launch_ar<1, 16, true>((int)N, st, AR_ARGS);
         else if (shape == 1) launch_ar<1, 8, true>((int)N, st, AR_ARGS);

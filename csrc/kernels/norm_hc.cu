@@ -14,9 +14,14 @@
 
 namespace {
 
+// Every position a forward pass touches derives from the RowMeta written here, so this is the one place
+// that enforces the context limit on the device: a group that would run past `max_pos` is moved back so
+// that its last row sits on position max_pos - 1 (it overwrites the tail of its OWN sequence, never a
+// page-table entry or cache row of another one) and the status word reports FB_BAD_ARG with the slot and
+// the offending length.  The host stops a sequence before this point; the clamp is the backstop.
 __global__ void prep_rows_kernel(const int* __restrict__ row_slot, const int* __restrict__ row_off,
                                  const int* __restrict__ row_gsize, const int* __restrict__ seq_len,
-                                 RowMeta* __restrict__ meta, int n) {
+                                 RowMeta* __restrict__ meta, int n, int max_pos, int* __restrict__ status) {
     PDL_PROLOGUE();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
@@ -25,6 +30,10 @@ __global__ void prep_rows_kernel(const int* __restrict__ row_slot, const int* __
     m.off = row_off[r];
     m.gsize = row_gsize[r];
     m.ctx0 = seq_len[m.slot];
+    if (m.ctx0 < 0 || m.ctx0 + m.gsize > max_pos) {
+        if (status && m.off == 0) { status[0] = FB_BAD_ARG; status[1] = m.slot; status[2] = m.ctx0; status[3] = m.gsize; }
+        m.ctx0 = max(0, min(m.ctx0, max_pos - m.gsize));
+    }
     m.pos = m.ctx0 + m.off;
     m.total = m.ctx0 + m.gsize;
     m.first = (m.off == 0);
@@ -344,9 +353,12 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
 
 }  // namespace
 
+// max_pos: positions are kept below it (<= 0: no limit); status: 4 ints or null (see the kernel).
 FB_API int fb_prep_rows(const int* row_slot, const int* row_off, const int* row_gsize, const int* seq_len,
-                        void* meta, int64_t n, cudaStream_t st) {
-    FB_LAUNCH((prep_rows_kernel), (n + 127) / 128, 128, 0, st, row_slot, row_off, row_gsize, seq_len, (RowMeta*)meta, (int)n);
+                        void* meta, int64_t n, int64_t max_pos, int* status, cudaStream_t st) {
+    const int lim = max_pos > 0 && max_pos < 0x7fffffff ? (int)max_pos : 0x7fffffff;
+    FB_LAUNCH((prep_rows_kernel), (n + 127) / 128, 128, 0, st, row_slot, row_off, row_gsize, seq_len, (RowMeta*)meta, (int)n,
+              lim, status);
     return FB_LAUNCH_CHECK();
 }
 

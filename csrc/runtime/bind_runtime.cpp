@@ -118,7 +118,9 @@ PYBIND11_MODULE(_runtime, m) {
         .def_readwrite("page_size", &SchedConfig::page_size).def_readwrite("num_pages", &SchedConfig::num_pages)
         .def_readwrite("device_slots", &SchedConfig::device_slots).def_readwrite("host_slots", &SchedConfig::host_slots)
         .def_readwrite("disk_slots", &SchedConfig::disk_slots).def_readwrite("buckets", &SchedConfig::buckets)
-        .def_readwrite("max_ctx", &SchedConfig::max_ctx);
+        .def_readwrite("max_ctx", &SchedConfig::max_ctx)
+        .def_readwrite("spec_rows", &SchedConfig::spec_rows)
+        .def("ctx_headroom", &SchedConfig::ctx_headroom);
     py::class_<PrefillChunk>(m, "PrefillChunk")
         .def_readonly("req", &PrefillChunk::req).def_readonly("row", &PrefillChunk::row)
         .def_readonly("start", &PrefillChunk::start).def_readonly("len", &PrefillChunk::len)
@@ -154,6 +156,7 @@ PYBIND11_MODULE(_runtime, m) {
         .def_readonly("max_new", &Request::max_new);
     py::class_<BatchScheduler>(m, "BatchScheduler")
         .def(py::init<const SchedConfig&>())
+        .def("max_prompt", &BatchScheduler::max_prompt)
         .def("submit", &BatchScheduler::submit, py::arg("prompt"), py::arg("max_new"), py::arg("stop_ids") = std::vector<int32_t>())
         .def("cancel", &BatchScheduler::cancel)
         .def("plan", &BatchScheduler::plan)

@@ -12,6 +12,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -66,12 +67,20 @@ public:
     // `scale_begin` -> f32 rows [r0, r1) into dst.
     void dequant_e4m3_block(size_t begin, size_t scale_begin, size_t rows, size_t cols, size_t blk, size_t r0,
                             size_t r1, float* dst) const {
-        const size_t kb = (cols + blk - 1) / blk;
-        if (begin + rows * cols > data_size() || r1 > rows) throw std::out_of_range("dequant range");
-        const float* sc = (const float*)(data() + scale_begin);
+        if (blk == 0) throw std::out_of_range("dequant block size");
+        const size_t kb = (cols + blk - 1) / blk, rb = (rows + blk - 1) / blk;
+        if (begin + rows * cols > data_size() || r1 > rows || r0 > r1) throw std::out_of_range("dequant range");
+        if (scale_begin + rb * kb * sizeof(float) > data_size()) throw std::out_of_range("dequant scale range");
+        // tensor data in a safetensors file is only byte-aligned: read the scales through memcpy
+        const uint8_t* sc = data() + scale_begin;
         for (size_t r = r0; r < r1; ++r) {
             const uint8_t* src = data() + begin + r * cols;
-            for (size_t c = 0; c < cols; ++c) dst[(r - r0) * cols + c] = e4m3_to_f32(src[c]) * sc[(r / blk) * kb + c / blk];
+            for (size_t cb = 0; cb < kb; ++cb) {
+                float scale;
+                std::memcpy(&scale, sc + ((r / blk) * kb + cb) * sizeof(float), sizeof(float));
+                const size_t c1 = std::min(cols, (cb + 1) * blk);
+                for (size_t c = cb * blk; c < c1; ++c) dst[(r - r0) * cols + c] = e4m3_to_f32(src[c]) * scale;
+            }
         }
     }
 

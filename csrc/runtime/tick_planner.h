@@ -32,6 +32,10 @@ struct SchedConfig {
     int device_slots = 512, host_slots = 4096, disk_slots = 65536;
     std::vector<int> buckets = {1, 2, 4, 8, 16, 32};
     int max_ctx = 1 << 20;
+    int spec_rows = 1;   // rows one decode step may append to a sequence (speculative verify width)
+    // A sequence must stop while a whole step (spec_rows rows, plus the two positions the MTP cache runs
+    // ahead) still fits below max_ctx: page tables and caches are sized for max_ctx positions.
+    int ctx_headroom() const { return spec_rows + 2; }
 };
 
 inline int bucket_for(const std::vector<int>& ladder, int n) {

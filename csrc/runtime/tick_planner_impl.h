@@ -9,7 +9,13 @@ public:
         : cfg_(c), pages_(c.num_pages), radix_(c.page_size), store_(c.device_slots, c.host_slots, c.disk_slots),
           rows_(c.max_rows, -1) {}
 
+    // Longest prompt that can still produce a token.
+    int max_prompt() const { return cfg_.max_ctx - cfg_.ctx_headroom() - 1; }
+
+    // Returns the request id, or -1 when the prompt is empty or leaves no room below the context limit
+    // (the caller answers 400; nothing is queued).
     int64_t submit(const std::vector<int32_t>& prompt, int max_new, const std::vector<int32_t>& stop_ids) {
+        if (prompt.empty() || (int)prompt.size() > max_prompt()) return -1;
         Request r;
         r.id = next_id_++;
         r.prompt = prompt;
@@ -195,6 +201,8 @@ private:
             t.tokens.push_back(tok);
             ++committed_;
             if ((int)r.generated.size() >= r.max_new) { reason = "length"; break; }
+            // context limit: the next step would write positions >= max_ctx
+            if ((int)(r.prompt.size() + r.generated.size()) + cfg_.ctx_headroom() >= cfg_.max_ctx) { reason = "length"; break; }
         }
         if (!t.tokens.empty()) ev->push_back(t);
         if (!reason.empty()) finish(r, reason, ev);

@@ -250,7 +250,7 @@ class EngineConfig:
     # "ar" = all-reduce only, "off" = separate kernels (True / False are accepted for full / off)
     fuse_epilogue: object = "full"
     collective: str = "p2p"  # "p2p" (fused peer-memory kernels) or "nccl"
-    ar_max_spins: int = 20_000_000
+    ar_max_spins: int = 2_000_000   # polls of a bounded device wait (about two seconds)
     seed: int = 0
     sched: SchedConfig = field(default_factory=SchedConfig)
     debug_sync: bool = False

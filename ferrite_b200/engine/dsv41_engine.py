@@ -22,6 +22,7 @@ import torch
 from ..config import EngineConfig
 from ..models.dsv41 import Dsv41DeviceModel
 from ..models.dsv41_config import Dsv41Config
+from ..serve.engine import ContextOverflow
 from ..spec import SpecStep, spec_accept
 
 
@@ -47,10 +48,29 @@ class Dsv41Engine(SpecStep):
         self.graph_verify: Optional[torch.cuda.CUDAGraph] = None
         self.pos = 0
         self.accept_hist: List[int] = []
+        from ..parallel.collective import startup_barrier
+        startup_barrier(world)
+
+    # ---- context limit -----------------------------------------------------------------------------
+    def _step_rows(self) -> int:
+        return (self.cfg.dspark_block_size + 1) if self.has_spec else 1
+
+    def max_prompt(self) -> int:
+        return self.model.max_ctx - self._step_rows() - 3
+
+    def room(self) -> int:
+        """Positions left before the next (speculative) step would write past max_ctx."""
+        return self.model.max_ctx - self.pos - self._step_rows() - 2
+
+    def _require_room(self):
+        if self.room() <= 0:
+            raise ContextOverflow(f"sequence of {self.pos} tokens is at the context limit ({self.model.max_ctx})")
 
     # ---- prefill -----------------------------------------------------------------------------------
     def prefill(self, prompt: Sequence[int], start: int = 0) -> int:
         """Prefill prompt[start:] on top of `start` positions that are already in the caches."""
+        if not 1 <= len(prompt) <= self.max_prompt():
+            raise ContextOverflow(f"prompt of {len(prompt)} tokens does not fit (1..{self.max_prompt()})")
         m = self.model
         if start == 0:
             m.reset_slot(0)
@@ -67,7 +87,9 @@ class Dsv41Engine(SpecStep):
             if last:
                 self.tok.copy_(m.ws["out_ids"][c.numel() - 1:c.numel()])
         self.pos = len(prompt)
-        return int(self.tok.item())
+        first = int(self.tok.item())
+        m.arena.verify(snapshot=False)
+        return first
 
     # ---- plain decode ------------------------------------------------------------------------------
     def _plain_body(self):
@@ -78,6 +100,7 @@ class Dsv41Engine(SpecStep):
         self.tok.copy_(m.ws["out_ids"][0:1])
 
     def step_plain(self) -> int:
+        self._require_room()
         if not self.use_graphs:
             self._plain_body()
         elif self.graph_plain is None:
@@ -93,7 +116,10 @@ class Dsv41Engine(SpecStep):
         else:
             self.graph_plain.replay()
         self.pos += 1
-        return int(self.tok.item())
+        self.model.arena.snapshot_async()
+        tok = int(self.tok.item())
+        self.model.arena.verify()
+        return tok
 
     def launch_plain_async(self) -> None:
         """Replay the decode graph without reading the token back (for timing loops)."""
@@ -121,10 +147,13 @@ class Dsv41Engine(SpecStep):
 
     def spec_step(self) -> List[int]:
         assert self.has_spec
+        self._require_room()
         m, B = self.model, self.cfg.dspark_block_size
         self._run("graph_draft", lambda: m.dspark_draft(self.rs_draft, self.tok))
         self._run("graph_verify", lambda: m.forward(self.rs_verify, m.ws["d_out"], advance=False))
+        m.arena.snapshot_async()
         block = m.ws["d_out"].tolist()                   # [t0, d1..dB]   (one sync per step)
+        m.arena.verify()
         judges = m.ws["out_ids"][:B + 1].tolist()
         n_acc = spec_accept(block[1:], judges, anchor_is_in_block=False)
         k = n_acc + 1                                    # verify rows that stay: t0 + accepted drafts
@@ -139,7 +168,7 @@ class Dsv41Engine(SpecStep):
     # ---- generation --------------------------------------------------------------------------------
     def generate(self, prompt: Sequence[int], n_new: int, spec: bool = False) -> List[int]:
         out = [self.prefill(prompt)]
-        while len(out) < n_new:
+        while len(out) < n_new and self.room() > 0:
             if spec:
                 out += self.spec_step()
             else:
@@ -184,3 +213,9 @@ class Dsv41StepEngine:
 
     def step(self) -> List[int]:
         return self.eng.spec_step() if self.spec else [self.eng.step_plain()]
+
+    def max_prompt(self) -> int:
+        return self.eng.max_prompt()
+
+    def room(self) -> int:
+        return self.eng.room()

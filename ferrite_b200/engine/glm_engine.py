@@ -15,6 +15,7 @@ import torch
 
 from ..config import EngineConfig, GlmConfig
 from ..models.glm import GlmDeviceModel, RowSet, View
+from ..serve.engine import ContextOverflow
 from ..spec import SpecStep
 
 
@@ -51,6 +52,25 @@ class GlmEngine(SpecStep):
         self.launches_plain = 0
         self.launches_mtp = 0
         self.n_ctx = 0
+        from ..parallel.collective import startup_barrier
+        startup_barrier(world)
+
+    # ------------------------------------------------------------------ context limit
+    def max_prompt(self) -> int:
+        """Longest prompt after which one decode step still fits below the context limit."""
+        return self.ecfg.max_ctx - self.nv - 3
+
+    def room(self) -> int:
+        """Positions left before the next step (nv rows, the MTP cache two ahead) would pass max_ctx."""
+        return self.ecfg.max_ctx - self.n_ctx - self.nv - 2
+
+    def _require_room(self):
+        if self.room() <= 0:
+            raise ContextOverflow(f"sequence of {self.n_ctx} tokens is at the context limit ({self.ecfg.max_ctx})")
+
+    def _check_status(self):
+        """Status words and guards read back with the step's tokens (see parallel/status.py)."""
+        self.model.arena.verify()
 
     # ------------------------------------------------------------------ prefill
     def _rows(self, g: int) -> RowSet:
@@ -62,7 +82,8 @@ class GlmEngine(SpecStep):
         """Chunked prefill of one prompt into slot 0; returns the first generated token."""
         m, cfg = self.model, self.cfg
         n = len(prompt)
-        assert 2 <= n < self.ecfg.max_ctx - 8
+        if not 2 <= n <= self.max_prompt():
+            raise ContextOverflow(f"prompt of {n} tokens does not fit (2..{self.max_prompt()})")
         m.reset_slot(0)
         use_mtp = self.nv > 1
         toks = torch.tensor(prompt, dtype=torch.int32)
@@ -89,6 +110,7 @@ class GlmEngine(SpecStep):
                     self.mtp_h[0].copy_(self.mtp_h[1])
                 self.mtp_h[1].copy_(hf[g - 1])
         first = int(self.judges[(n - 1) % C].item())
+        m.arena.verify(snapshot=False)
         self.block_ids[0] = first
         if use_mtp:
             self.mtp_ids.copy_(torch.tensor([prompt[-1], first], dtype=torch.int32))
@@ -158,6 +180,7 @@ class GlmEngine(SpecStep):
     # ------------------------------------------------------------------ stepping
     def step_plain(self, token: Optional[int] = None) -> int:
         """One greedy decode step.  ``token`` (host) overrides the device-resident anchor."""
+        self._require_room()
         if token is not None:
             self.pin_in[0] = token
             self.block_ids[:1].copy_(self.pin_in, non_blocking=True)
@@ -166,12 +189,15 @@ class GlmEngine(SpecStep):
         else:
             self._plain_body()
         self.pin_out[:2].copy_(self.out_tokens[:2], non_blocking=True)
+        self.model.arena.snapshot_async()
         torch.cuda.current_stream().synchronize()
+        self._check_status()
         self.n_ctx += 1
         return int(self.pin_out[1])
 
     def spec_step(self, token: Optional[int] = None) -> List[int]:
         """One speculative step (draft -> verify -> accept -> commit); returns 1..nv tokens."""
+        self._require_room()
         if token is not None:
             self.pin_in[0] = token
             self.block_ids[:1].copy_(self.pin_in, non_blocking=True)
@@ -180,7 +206,9 @@ class GlmEngine(SpecStep):
         else:
             self._mtp_body()
         self.pin_out.copy_(self.out_tokens, non_blocking=True)
+        self.model.arena.snapshot_async()
         torch.cuda.current_stream().synchronize()
+        self._check_status()
         k = int(self.pin_out[0])
         self.n_ctx += k
         return [int(t) for t in self.pin_out[1:1 + k]]
@@ -201,7 +229,7 @@ class GlmEngine(SpecStep):
         first = self.prefill(prompt)
         self.build_graphs(mtp)
         out, accepts = [first], []
-        while len(out) < max_new and out[-1] not in stop_ids and self.n_ctx + self.nv + 2 < self.ecfg.max_ctx:
+        while len(out) < max_new and out[-1] not in stop_ids and self.room() > 0:
             if mtp:
                 em = self.spec_step()
                 accepts.append(len(em))

@@ -19,7 +19,7 @@ import torch
 from .. import build
 from ..config import EngineConfig, GlmConfig
 from ..models.glm import GlmDeviceModel, RowSet
-from ..serve.engine import ReqEvent, RequestSpec, Usage
+from ..serve.engine import ContextOverflow, ReqEvent, RequestSpec, Usage
 
 
 class GpuEngine:
@@ -64,10 +64,17 @@ class GpuEngine:
         self.snap_dev = (torch.zeros(device_snapshots, *gs.shape, device=dev), torch.zeros(device_snapshots, *cs.shape, device=dev))
         self.snap_host = (torch.zeros(host_snapshots, *gs.shape).pin_memory(), torch.zeros(host_snapshots, *cs.shape).pin_memory())
         self.launches = 0
+        from ..parallel.collective import startup_barrier
+        startup_barrier(world)
 
     # ------------------------------------------------------------------ ServeEngine
+    def validate(self, spec: RequestSpec) -> None:
+        if not spec.prompt_ids or len(spec.prompt_ids) > self.sched.max_prompt():
+            raise ContextOverflow(f"prompt of {len(spec.prompt_ids)} tokens does not fit the context limit "
+                                  f"(at most {self.sched.max_prompt()})")
+
     def submit(self, spec: RequestSpec) -> int:
-        assert len(spec.prompt_ids) >= 1
+        self.validate(spec)
         rid = self.sched.submit(list(spec.prompt_ids), spec.max_new_tokens, list(spec.stop_ids))
         self.prompts[rid] = list(spec.prompt_ids)
         return rid
@@ -191,7 +198,9 @@ class GpuEngine:
             self._decode(bucket)
             self.tok_slot[idx] = self.out[:bucket]
             self.pin_out.copy_(self.out, non_blocking=True)
+            m.arena.snapshot_async()
             torch.cuda.current_stream().synchronize()
+            m.arena.verify()   # status words and guards of the tick: a timed-out wait or a clamped position raises here
             toks = [[] for _ in plan.decode.rows]
             for i, row in enumerate(live):
                 toks[row] = [int(self.pin_out[i])]
@@ -209,6 +218,7 @@ class GpuEngine:
                                judges=self.first_tok if last else None, head_from=n - 1 if last else n)
                 if last:
                     first = int(self.first_tok[n - 1].item())
+                    m.arena.verify(snapshot=False)
                     self.tok_slot[ch.row] = first
             evs, moves = self.sched.ingest_prefill(ch.req, ch.len, first, ch.snapshot_after)
             self._apply_state_moves(moves)

@@ -80,6 +80,11 @@ class CheckpointIndex:
                 b, e = meta["data_offsets"]
                 if meta["dtype"] not in _DT or e > f.data_size or b > e:
                     raise ValueError(f"bad entry {name} in {fn}")
+                want = _DT[meta["dtype"]][1]
+                for d in meta["shape"]:
+                    want *= int(d)
+                if e - b != want:   # a row copy would otherwise read the neighbouring tensor's bytes
+                    raise ValueError(f"bad entry {name} in {fn}: {e - b} bytes for shape {meta['shape']} {meta['dtype']}")
                 self.tensors[name] = TensorInfo(f, meta["dtype"], meta["shape"], b, e)
 
     def __contains__(self, name: str) -> bool:
@@ -109,10 +114,14 @@ class CheckpointIndex:
 
     def dequant_fp8(self, name: str, scale_name: str, r0: int = 0, r1: Optional[int] = None, block: int = 128) -> torch.Tensor:
         ti, si = self.tensors[name], self.tensors[scale_name]
-        assert ti.dtype == "F8_E4M3" and si.dtype == "F32" and ti.file is si.file or True
+        if ti.dtype != "F8_E4M3" or len(ti.shape) != 2:
+            raise ValueError(f"{name}: not a 2-D e4m3 tensor")
         rows, cols = ti.shape
+        want = [(rows + block - 1) // block, (cols + block - 1) // block]
+        if list(si.shape) != want:
+            raise ValueError(f"{scale_name}: scale shape {list(si.shape)} != {want} for a {rows}x{cols} weight")
         r1 = rows if r1 is None else r1
-        if ti.file is si.file:
+        if ti.file is si.file and si.dtype == "F32":   # the C++ path reads f32 scales; others go through torch
             return torch.from_numpy(ti.file.dequant_e4m3_block(ti.begin, si.begin, rows, cols, block, r0, r1))
         w = self.view(name)[r0:r1].float()
         s = self.view(scale_name).float().repeat_interleave(block, 0)[r0:r1].repeat_interleave(block, 1)[:, :cols]
@@ -153,7 +162,10 @@ class CheckpointSource:
         if leaf in ("f_b_proj.weight", "g_b_proj.weight"):
             f = f"{head}.self_attn.fused_fg_b_proj.weight"
             if f in self.idx:
-                return self._load_src(f)[0 if leaf.startswith("f_") else 1]
+                t = self._load_src(f)
+                if t.dim() == 2:     # flat [2 * proj, low_rank]: f rows first, then g (reference weights.rs:374-387)
+                    t = t.view(2, t.shape[0] // 2, t.shape[1])
+                return t[0 if leaf.startswith("f_") else 1]
         if leaf in ("q_a_proj.weight", "kv_a_proj_with_mqa.weight"):
             f = f"{head}.self_attn.fused_qkv_a_proj_with_mqa.weight"
             if f in self.idx:

@@ -20,13 +20,13 @@ with ue8m0 scales.  Replaces ``crates/ferrite-models/src/dsv41/chain_dev.rs`` (`
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Dict, List, Optional
 
 import torch
 
 from .. import _lib
 from ..ops import quant as Q
+from ..utils.switches import switches
 from .dsv41_config import Dsv41Config
 from .dsv41_engram import EngramLayout, hash_multipliers
 from .dsv41_ref import rope_freqs
@@ -69,14 +69,17 @@ class Dsv41DeviceModel:
         self.Is_real = per if self.shared_tp else cfg.moe_inter_dim      # columns of the shared expert this rank owns
         self.Is = (self.Is_real + 63) // 64 * 64                        # zero-padded to the tensor-core GEMV's k-block
         self.tc_min_rows = 16
-        self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        from ..parallel.status import StatusArena
+        self.arena = getattr(allreduce, "arena", None) or StatusArena(self.dev, 2048)
+        self.tc_status = self.arena.status("tcgen05")
+        self.row_status = self.arena.status("rows")
         self.tc_gemv_min_n = 0
-        self.fp4_mma = os.environ.get("FERRITE_D4_FP4_MMA", "1") != "0"   # tensor-core routed experts (decode rows)
+        self.fp4_mma = switches().d4_fp4_mma   # tensor-core routed experts (decode rows)
         self.fp4_mma_rows = 1 << 30
         self._xq_ready = False
         # tensor-core sparse attention (head_dim 512), opt-in: at decode sizes (640 keys) it measured 21.6 us against
         # 16.3 us for the SIMT kernel with the in-kernel split merge (8 heads), and 2.37 vs 2.15 ms on the 8-layer bench
-        self.attn_tc = os.environ.get("FERRITE_D4_ATTN_TC", "0") != "0"
+        self.attn_tc = switches().d4_attn_tc
         self._tc_part = None
         self._tc_ticket = None
         # GEMV + all-reduce + hyper-connection fold as one launch (csrc/kernels/gemv_ar.cu)
@@ -85,7 +88,7 @@ class Dsv41DeviceModel:
             self.fused = getattr(allreduce, "fused", None)
         else:
             from ..parallel.symm import FusedGemvAllReduce
-            self.fused = FusedGemvAllReduce(self.dev, 0, 1)
+            self.fused = FusedGemvAllReduce(self.dev, 0, 1, arena=self.arena)
         self._fold_next = None
         self._folded = False
         self.debug_hook = None
@@ -414,7 +417,7 @@ class Dsv41DeviceModel:
     # hc_pre can also emit the e4m3 round trip of its output (two launches fewer per layer).  Off by default: measured
     # 1 % SLOWER at TP1 and on the TP8 shard (2.175 vs 2.161 ms, 5.94 vs 5.88 ms): hc_pre is a one-CTA latency chain
     # on the critical path, the separate quantiser spreads over many CTAs
-    fuse_quant = os.environ.get("FERRITE_D4_FUSE_QUANT", "0") != "0"
+    fuse_quant = property(lambda self: switches().d4_fuse_quant)
 
     def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
         quant = quant and self.fuse_quant
@@ -576,7 +579,8 @@ class Dsv41DeviceModel:
         contribution and route with the image bias."""
         cfg, ws, n = self.cfg, self.ws, rs.n
         d = cfg.dim
-        self.K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.seq_len, rs.meta, n)
+        self.K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.seq_len, rs.meta, n, self.max_ctx,
+                    self.row_status)
         ws["R"] = ws["R0"]
         self.K.call("fb_embed_expand", ids, self.embed, ws["R"], n, d, cfg.hc_mult, cfg.vocab_size)
         self.has_images = image_embeds is not None
@@ -667,7 +671,8 @@ class Dsv41DeviceModel:
         ids = ws["d_ids"]
         ids.fill_(cfg.dspark_noise_token_id)
         ids[0:1].copy_(t0)
-        self.K.call("fb_prep_rows", rs_block.row_slot, rs_block.row_off, rs_block.row_gsize, self.seq_len, rs_block.meta, B)
+        self.K.call("fb_prep_rows", rs_block.row_slot, rs_block.row_off, rs_block.row_gsize, self.seq_len, rs_block.meta, B,
+                    self.max_ctx, self.row_status)
         ws["R"] = ws["R0"]
         self.K.call("fb_embed_expand", ids, self.embed, ws["R"], B, d, cfg.hc_mult, cfg.vocab_size)
         ws["pre0"].zero_()

@@ -9,8 +9,6 @@ lengths, snapshot cursor, token ids) live in device memory and are advanced by g
 """
 from __future__ import annotations
 
-import os
-
 import math
 import zlib
 from dataclasses import dataclass
@@ -21,6 +19,7 @@ import torch
 from .. import _lib
 from ..config import EngineConfig, GlmConfig
 from ..ops.reference import quant_fp8_block
+from ..utils.switches import switches
 from .glm_weights import init_kind, shard_weight, weight_layout
 
 ROWMETA_BYTES = 32
@@ -94,6 +93,8 @@ class GlmDeviceModel:
         self.allreduce = allreduce  # callable(tensor_view[n,H]) summing across ranks, in place
         # GEMV + all-reduce + hyper-connection fold as one launch (None: separate kernels)
         self.fused = None
+        from ..parallel.status import StatusArena
+        self.arena = getattr(allreduce, "arena", None) or StatusArena(self.dev, 2048)
         mode = getattr(ecfg, "fuse_epilogue", "full")
         mode = {True: "full", False: "off"}.get(mode, mode)
         self.fuse_fold = mode == "full"
@@ -102,11 +103,13 @@ class GlmDeviceModel:
                 self.fused = getattr(allreduce, "fused", None)
             else:
                 from ..parallel.symm import FusedGemvAllReduce
-                self.fused = FusedGemvAllReduce(self.dev, 0, 1)
+                self.fused = FusedGemvAllReduce(self.dev, 0, 1, arena=self.arena, ar_group=switches().ar_group)
         self.dcp = None          # (d, n_dcp, DcpAttentionMerge): decode-context-parallel attention
         # decode GEMVs with at least this many output rows go to the tcgen05 split-K kernel (0 = never)
-        self.tc_gemv_min_n = int(os.environ.get("FERRITE_TC_GEMV_MIN_N", "0"))
-        self.tc_gemv_max_n = int(os.environ.get("FERRITE_TC_GEMV_MAX_N", "0"))
+        sw = switches()
+        self.tc_gemv_min_n, self.tc_gemv_max_n = sw.tc_gemv_min_n, sw.tc_gemv_max_n
+        if sw.l2_ahead >= 0:
+            self.K.lib.fb_set_l2_ahead(sw.l2_ahead)
         self._tc_part = self._tc_ticket = None
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
@@ -131,7 +134,8 @@ class GlmDeviceModel:
         else:
             self.e_lo, self.e_cnt = 0, self.E_res
         self.tc_min_rows = 16  # row count from which dense bf16 projections use the tcgen05 GEMM
-        self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.tc_status = self.arena.status("tcgen05")       # bounded mbarrier waits of the tcgen05 kernels
+        self.row_status = self.arena.status("rows")         # a sequence that reached the context limit (positions clamped)
         self.layers: List[dict] = []
         self.debug_hook = None  # callable(layer_index, site, ws, n) after each sublayer (eager runs only)
         self._pack(src)
@@ -670,7 +674,8 @@ class GlmDeviceModel:
         ``judges`` is given, the greedy token of every row there."""
         cfg, ws, n, K = self.cfg, self.ws, rs.n, self.K
         H = cfg.hidden_size
-        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.main_len, rs.meta, n)
+        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.main_len, rs.meta, n, self.ecfg.max_ctx,
+               self.row_status)
         ws["R"] = ws["R0"]
         K.call("fb_embed_expand", ids, self.embed, ws["R"], n, H, cfg.hc_mult, cfg.vocab_size)
         ws["R"] = ws["R0"]
@@ -710,7 +715,8 @@ class GlmDeviceModel:
         H = cfg.hidden_size
         L = self.layers[cfg.num_layers]
         eps = float(cfg.rms_norm_eps)
-        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.mtp_len, rs.meta, n)
+        K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.mtp_len, rs.meta, n, self.ecfg.max_ctx,
+               self.row_status)
         mi, x, xh = ws["mtp_in"], ws["x"], ws["xh"]
         K.call("fb_mtp_prep", ids, self.embed, h_prev, L["enorm"], L["hnorm"], mi.f, n, H, cfg.vocab_size, eps, *mi.sp(1))
         self.gemv(L["eh_proj"], mi, ws["res"], n, H, 2 * H)

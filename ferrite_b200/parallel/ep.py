@@ -18,7 +18,8 @@ import ctypes
 import torch
 
 from .. import _lib
-from .symm import FB_TIMEOUT, CollectiveTimeout, SymmetricRegion
+from .status import StatusArena
+from .symm import DEFAULT_MAX_SPINS, SymmetricRegion, _Checked
 
 
 class _Ptr:
@@ -29,9 +30,11 @@ class _Ptr:
         return self.p
 
 
-class EpMoE:
+class EpMoE(_Checked):
+    name = "ep_moe"
+
     def __init__(self, device, rank: int, world: int, n_max: int, hidden: int, topk: int, inter: int,
-                 max_spins: int = 20_000_000, group=None):
+                 max_spins: int = DEFAULT_MAX_SPINS, group=None, arena=None):
         self.K = _lib.lib()
         self.dev, self.rank, self.world = torch.device(device), rank, world
         self.n_max, self.H, self.topk, self.I, self.max_spins = n_max, hidden, topk, inter, max_spins
@@ -47,9 +50,10 @@ class EpMoE:
         arr = ctypes.c_void_p * (5 * world)
         self._ptrs = arr(*[p for reg in self.regions for p in reg.ptrs])
         self.xs_all, self.ids_all, self.wts_all = (_Ptr(self.regions[i].local) for i in range(3))
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self.ticket = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.dev)
+        self.arena = arena if arena is not None else StatusArena(self.dev, 256)
+        self.epoch = self.arena.take(1, "ep_moe.epoch")
+        self.ticket = self.arena.take(1, "ep_moe.ticket")
+        self.status = self.arena.status("ep_moe")
         self.act_s = torch.zeros(4, self.n_all * topk, inter, dtype=torch.int16, device=self.dev)
         self.y_all = torch.zeros(self.n_all, hidden, device=self.dev)
 
@@ -74,12 +78,6 @@ class EpMoE:
         self.K.call("fb_moe_down_mma", w2, s2, self.act_s, ld_as, plane_as, self.ids_all, self.y_all, H, self.n_all,
                     topk, I, H, e_lo, e_per_rank, 0, None, 0, 0, 0)
         self.combine(y_out, n_loc, addend)
-
-    def check(self):
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
 
     def close(self):
         for r in self.regions:

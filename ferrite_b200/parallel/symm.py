@@ -10,7 +10,6 @@ The reference keeps its ranks as threads of one process and enables peer access 
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import List, Optional
 
 import torch
@@ -18,13 +17,25 @@ import torch.distributed as dist
 
 from .. import _lib
 
-FB_OK, FB_TIMEOUT, FB_BAD_CANARY, FB_BAD_ARG = 0, 1, 2, 3
+from .status import (FB_BAD_ARG, FB_BAD_CANARY, FB_OK, FB_TIMEOUT, CollectiveTimeout,  # noqa: F401
+                     StatusArena)
+
+# Polls of a bounded device wait before it gives up (about two seconds).  Ranks line up on a host barrier
+# after their engines are built, so a wait only has to cover the skew inside a step, and a peer that died
+# is reported within seconds.  A wait that ran out is sticky until the host clears the status word.
+DEFAULT_MAX_SPINS = 2_000_000
 
 
-class CollectiveTimeout(RuntimeError):
-    def __init__(self, peer: int, epoch: int, chunk: int):
-        super().__init__(f"all-reduce wait ran out: peer {peer}, epoch {epoch}, chunk {chunk}")
-        self.peer, self.epoch, self.chunk = peer, epoch, chunk
+class _Checked:
+    """Shared ``check()``: read this object's status word on the host (synchronises)."""
+    status: torch.Tensor
+    name = "collective"
+
+    def check(self):
+        s = self.status.tolist()
+        if s[0] == FB_TIMEOUT:
+            self.status.zero_()
+            raise CollectiveTimeout(s[1], s[2], s[3], self.name)
 
 
 class SymmetricRegion:
@@ -66,21 +77,25 @@ class SymmetricRegion:
             self.local = 0
 
 
-class P2PAllReduce:
+class P2PAllReduce(_Checked):
     """Callable ``f(view)``: in-place sum of a contiguous f32 view across the ranks, one
     kernel launch on the current stream.  ``check()`` reads the status word on the host."""
 
-    def __init__(self, device, rank: int, world: int, max_elems: int, max_spins: int = 20_000_000, group=None):
+    name = "allreduce"
+
+    def __init__(self, device, rank: int, world: int, max_elems: int, max_spins: int = DEFAULT_MAX_SPINS, group=None,
+                 arena: Optional[StatusArena] = None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.arena = arena if arena is not None else StatusArena(device)
         mc, ce = ctypes.c_int(), ctypes.c_int()
         self.K.lib.fb_ar_limits(ctypes.byref(mc), ctypes.byref(ce))
         self.max_chunks, self.chunk = mc.value, ce.value
         self.max_elems = min((max_elems + self.chunk - 1) // self.chunk, self.max_chunks) * self.chunk
         self.staging = SymmetricRegion(2 * world * self.max_elems * 4, rank, world, group)
         self.flags = SymmetricRegion(2 * world * self.max_chunks * 4, rank, world, group)
-        self.epoch = torch.zeros(self.max_chunks, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = self.arena.take(self.max_chunks, "allreduce.epoch")
+        self.status = self.arena.status("allreduce")
         arr = ctypes.c_void_p * world
         self._sp = arr(*self.staging.ptrs)
         self._fp = arr(*self.flags.ptrs)
@@ -97,11 +112,10 @@ class P2PAllReduce:
         self.calls += 1
 
     def check(self):
-        """Host-side read of the status word (synchronises the device)."""
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
+        """Host-side read of the guards and of every status word of this rank's collectives
+        (synchronises the device)."""
+        self.arena.verify(snapshot=False)
+        _Checked.check(self)
         if self.fused is not None:
             self.fused.check()
         if self.gemm_fused is not None:
@@ -120,31 +134,35 @@ class P2PAllReduce:
         self.flags.close()
 
 
-class FusedGemvAllReduce:
+class FusedGemvAllReduce(_Checked):
     """Row-parallel GEMV + all-reduce (+ hyper-connection fold) as one kernel launch
     (``csrc/kernels/gemv_ar.cu``).  With ``world == 1`` it needs no peer memory and only fuses
     the fold epilogue into the GEMV.  ``check()`` reads the status word on the host."""
 
+    name = "gemv_ar"
+
     def __init__(self, device, rank: int, world: int, max_rows: int = 8, n_max: int = 8192,
-                 max_spins: int = 20_000_000, group=None):
+                 max_spins: int = DEFAULT_MAX_SPINS, group=None, arena: Optional[StatusArena] = None, ar_group: int = 0):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.arena = arena if arena is not None else StatusArena(device)
         mt, mw, fw = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         self.K.lib.fb_gemv_ar_limits(ctypes.byref(mt), ctypes.byref(mw), ctypes.byref(fw))
         assert world <= mw.value
         self.max_tiles = mt.value
         self.max_elems = max_rows * n_max
-        self.epoch = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = self.arena.take(self.max_tiles, "gemv_ar.epoch")
+        self.status = self.arena.status("gemv_ar")
         # mix-dot partials and tile counts for up to `part_rows` rows: a forward of more than 8 rows calls the
         # kernel once per 8-row window, each window with its own slice
         self.part_rows = 64
         self.part = torch.zeros(self.part_rows * 25 * self.max_tiles, dtype=torch.float32, device=device)
         self.part_n = torch.zeros(self.part_rows, dtype=torch.int32, device=device)
-        self.ticket = torch.zeros(self.max_tiles, dtype=torch.int32, device=device)
-        # tiles per published group; the whole grid by default: system-scope fences are the expensive part
-        # (measured on 2 GPUs, GLM decode step: 16 -> 11.99 ms, 64 -> 11.31, 128 -> 11.02, whole grid -> 10.88)
-        self.group = int(os.environ.get("FERRITE_AR_GROUP", str(self.max_tiles)))
+        self.ticket = self.arena.take(self.max_tiles, "gemv_ar.ticket")
+        # one published group = the whole grid: system-scope fences are the expensive part (measured on 2 GPUs,
+        # GLM decode step: groups of 16 tiles 11.99 ms, 64 -> 11.31, 128 -> 11.02, whole grid -> 10.88), and one
+        # group means one epoch per launch, so staging parity cannot alias between launches of different widths
+        self.group = ar_group if ar_group > 0 else self.max_tiles
         self.staging = self.flags = None
         self._sp = self._fp = None
         if world > 1:
@@ -181,12 +199,6 @@ class FusedGemvAllReduce:
         """(part, part_n, part_ld) arguments for the hc_pre kernel that consumes the mix-dot partials."""
         return (self.part, self.part_n, self.max_tiles)
 
-    def check(self):
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
-
     def close(self):
         if self.staging is not None:
             self.staging.close()
@@ -194,16 +206,19 @@ class FusedGemvAllReduce:
             self.staging = self.flags = None
 
 
-class FusedGemmAllReduce:
+class FusedGemmAllReduce(_Checked):
     """Row-parallel prefill GEMM (TMA + tcgen05) + two-shot all-reduce over peer memory as one kernel
     launch (``csrc/kernels/gemm_tc_ar.cu``): out[m, n] = sum over ranks of x_rank . W_rank^T.  Buffers
     are sized for ``max_rows`` x ``n_max`` outputs; ``fits(m, N)`` says whether a shape can go through
     the fused kernel (co-resident grid, at least one tile per rank)."""
 
+    name = "gemm_ar"
+
     def __init__(self, device, rank: int, world: int, max_rows: int = 256, n_max: int = 8192,
-                 max_spins: int = 20_000_000, group=None, mode: int = 0):
+                 max_spins: int = DEFAULT_MAX_SPINS, group=None, mode: int = 0, arena: Optional[StatusArena] = None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.arena = arena if arena is not None else StatusArena(device)
         self.max_rows, self.n_max = max_rows, n_max
         self.mode = mode   # 0: the kernel chooses, 1: one-shot, 2: two-shot (all ranks must agree)
         pad_elems = (max_rows + 256) * (n_max + 128)          # whole tiles of any tile height
@@ -211,9 +226,9 @@ class FusedGemmAllReduce:
         # two-shot: one rounding tile per source slot; two ranks run one-shot and hold both ranks' partials of all tiles
         self.scatter_cap = (2 * world * pad_elems if world == 2 or mode == 1
                             else 2 * pad_elems + 2 * world * 256 * 128)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
-        self.ticket = torch.zeros(2, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = self.arena.take(1, "gemm_ar.epoch")
+        self.ticket = self.arena.take(2, "gemm_ar.ticket")
+        self.status = self.arena.status("gemm_ar")
         self.scatter = self.gather = self.flags = None
         self._sp = self._gp = self._fp = None
         if world > 1:
@@ -243,12 +258,6 @@ class FusedGemmAllReduce:
                     self.max_spins, self.mode)
         self.calls += 1
 
-    def check(self):
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
-
     def close(self):
         if self.scatter is not None:
             self.scatter.close()
@@ -257,20 +266,24 @@ class FusedGemmAllReduce:
             self.scatter = self.gather = self.flags = None
 
 
-class CrossRankArgmax:
+class CrossRankArgmax(_Checked):
     """Greedy token of a vocab-sliced head: per-rank argmax partials merged over the ranks in one
     small kernel (``fb_argmax_xchg``); every rank gets the same global token id."""
 
-    def __init__(self, device, rank: int, world: int, max_spins: int = 20_000_000, group=None):
+    name = "argmax_xchg"
+
+    def __init__(self, device, rank: int, world: int, max_spins: int = DEFAULT_MAX_SPINS, group=None,
+                 arena: Optional[StatusArena] = None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.arena = arena if arena is not None else StatusArena(device)
         mr = ctypes.c_int()
         self.K.lib.fb_argmax_xchg_limits(ctypes.byref(mr))
         self.max_rows = mr.value
         self.staging = SymmetricRegion(2 * world * self.max_rows * 8, rank, world, group)
         self.flags = SymmetricRegion(max(256, 2 * world * 4), rank, world, group)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = self.arena.take(1, "argmax_xchg.epoch")
+        self.status = self.arena.status("argmax_xchg")
         arr = ctypes.c_void_p * world
         self._sp = arr(*self.staging.ptrs)
         self._fp = arr(*self.flags.ptrs)
@@ -286,31 +299,28 @@ class CrossRankArgmax:
             self.K.call("fb_argmax_xchg", pp, self._sp, self._fp, self.epoch, self.status, op, vp, id_stride, m,
                         self.rank, self.world, self.max_spins)
 
-    def check(self):
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
-
     def close(self):
         self.staging.close()
         self.flags.close()
 
 
-class DcpAttentionMerge:
+class DcpAttentionMerge(_Checked):
     """Cross-rank LSE merge of sparse-attention partials for a decode-context-parallel group
     (``csrc/kernels/dsa_dcp.cu``): one launch per attention layer."""
 
+    name = "dcp_merge"
+
     def __init__(self, device, rank: int, world: int, max_rows: int, heads: int, latent_dim: int,
-                 max_spins: int = 20_000_000, group=None):
+                 max_spins: int = DEFAULT_MAX_SPINS, group=None, arena: Optional[StatusArena] = None):
         self.K = _lib.lib()
         self.rank, self.world, self.max_spins = rank, world, max_spins
+        self.arena = arena if arena is not None else StatusArena(device)
         self.slot_elems = max_rows * heads * (latent_dim + 4)
         self.staging = SymmetricRegion(2 * world * self.slot_elems * 4, rank, world, group)
         self.flags = SymmetricRegion(2 * world * 32 * 4, rank, world, group)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
-        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = self.arena.take(1, "dcp_merge.epoch")
+        self.ticket = self.arena.take(1, "dcp_merge.ticket")
+        self.status = self.arena.status("dcp_merge")
         arr = ctypes.c_void_p * world
         self._sp = arr(*self.staging.ptrs)
         self._fp = arr(*self.flags.ptrs)
@@ -318,12 +328,6 @@ class DcpAttentionMerge:
     def __call__(self, o_part, ml_part, ctx, n: int, heads: int, latent_dim: int, nsplit: int, split=(None, 0, 0, 0)):
         self.K.call("fb_dsa_attn_merge_dcp", o_part, ml_part, ctx, n, heads, latent_dim, nsplit, self._sp, self._fp,
                     self.epoch, self.ticket, self.status, self.rank, self.world, self.slot_elems, self.max_spins, *split)
-
-    def check(self):
-        s = self.status.tolist()
-        if s[0] == FB_TIMEOUT:
-            self.status.zero_()
-            raise CollectiveTimeout(s[1], s[2], s[3])
 
     def close(self):
         self.staging.close()

@@ -177,6 +177,12 @@ class _GlmStep:
     def step(self):
         return self.eng.spec_step() if self.mtp else [self.eng.step_plain()]
 
+    def max_prompt(self):
+        return self.eng.max_prompt()
+
+    def room(self):
+        return self.eng.room()
+
 
 class _RefStep:
     """StepEngine over the fp32 CPU reference engine."""

@@ -15,19 +15,36 @@ cancels the request.
 import asyncio
 import json
 import os
-import queue as _queue
 import threading
 import time
 import uuid
 from typing import List, Optional
 
-from .engine import EngineDriver, RequestSpec, Usage
+from .engine import ContextOverflow, EngineDriver, EngineFailed, RequestSpec, Usage
 from .tokenizer import ChatTokenizer, utf8_holdback
 
 
-def _err(msg: str, status: int = 400):
+def _err(msg: str, status: int = 400, kind: str = "invalid_request_error"):
     from fastapi.responses import JSONResponse
-    return JSONResponse({"error": {"message": msg, "type": "invalid_request_error"}}, status_code=status)
+    return JSONResponse({"error": {"message": msg, "type": kind}}, status_code=status)
+
+
+class _LoopSink:
+    """Event sink of one request: the driver thread calls ``put``, the event loop awaits ``get``.  Events
+    cross threads with ``call_soon_threadsafe``, so a waiting request costs nothing and wakes at once."""
+
+    def __init__(self, loop):
+        self.loop = loop
+        self.q: "asyncio.Queue" = asyncio.Queue()
+
+    def put(self, ev) -> None:
+        try:
+            self.loop.call_soon_threadsafe(self.q.put_nowait, ev)
+        except RuntimeError:      # the loop is closed (server shutting down)
+            pass
+
+    async def get(self):
+        return await self.q.get()
 
 
 def _usage(u: Optional[Usage]) -> dict:
@@ -48,12 +65,7 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
     app = FastAPI(title="ferrite_b200")
 
     async def _next_event(sink):
-        loop = asyncio.get_running_loop()
-        while True:
-            try:
-                return sink.get_nowait()
-            except _queue.Empty:
-                await asyncio.sleep(0.001)
+        return await sink.get()
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
@@ -75,7 +87,13 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
         include_usage = bool(body.get("include_usage", False)) or bool((body.get("stream_options") or {}).get("include_usage"))
         prompt = tokenizer.encode_chat(msgs)
         spec = RequestSpec(prompt, max_new, tuple(tokenizer.stop_ids()))
-        rid, sink = driver.submit(spec)
+        loop = asyncio.get_running_loop()
+        try:   # the driver admits between ticks: wait for it off the event loop
+            rid, sink = await loop.run_in_executor(None, driver.submit, spec, _LoopSink(loop))
+        except ContextOverflow as e:
+            return _err(str(e), 400)
+        except EngineFailed as e:
+            return _err(f"engine failed: {e}", 503, "server_error")
         cid = "chatcmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
 
@@ -137,6 +155,8 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
 
     @app.get("/health")
     async def health():
+        if driver.poisoned:
+            return _err(f"engine failed: {driver.poisoned}", 503, "server_error")
         e = driver.stats().get("engine", {})
         return {"status": "ok", "engine": {"ticks": e.get("ticks", 0), "tokens_committed": e.get("tokens_committed", 0)}}
 

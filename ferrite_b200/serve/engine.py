@@ -16,6 +16,14 @@ from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Protocol, Tuple
 
 
+class ContextOverflow(ValueError):
+    """The prompt leaves no room below the engine's context limit (the HTTP layer answers 400)."""
+
+
+class EngineFailed(RuntimeError):
+    """The engine raised outside a single request's step; the driver is poisoned (HTTP 503)."""
+
+
 @dataclass
 class RequestSpec:
     prompt_ids: List[int]
@@ -59,13 +67,18 @@ class StepEngine(Protocol):
 
     def start(self, prompt_ids: List[int]) -> Tuple[int, int]: ...  # (first token, cached prefix tokens)
     def step(self) -> List[int]: ...  # 1..n tokens (n > 1 with speculative decoding)
+    # optional: max_prompt() -> longest prompt that still fits; room() -> steps' worth of tokens left below the
+    # context limit (<= 0: the sequence must stop)
 
 
 class SingleFlight:
     """Adapts a :class:`StepEngine` to :class:`ServeEngine`: one request in flight, FIFO."""
 
-    def __init__(self, inner: StepEngine):
+    def __init__(self, inner: StepEngine, swallow_errors: bool = True):
         self.inner = inner
+        # False under a ReplicatedEngine: an exception must reach the all-rank acknowledgement so that every
+        # rank drops the request together; swallowing it on one rank would desynchronise the planners
+        self.swallow_errors = swallow_errors
         self.queue: List[Tuple[int, RequestSpec]] = []
         self.cur: Optional[Tuple[int, RequestSpec]] = None
         self.done = 0
@@ -74,7 +87,14 @@ class SingleFlight:
         self.tokens_committed = 0
         self.poisoned: Optional[str] = None
 
+    def validate(self, spec: RequestSpec) -> None:
+        mp = getattr(self.inner, "max_prompt", None)
+        if not spec.prompt_ids or (mp is not None and len(spec.prompt_ids) > mp()):
+            raise ContextOverflow(f"prompt of {len(spec.prompt_ids)} tokens does not fit the context limit"
+                                  + (f" (at most {mp()})" if mp is not None else ""))
+
     def submit(self, spec: RequestSpec) -> int:
+        self.validate(spec)
         rid = self.next_id
         self.next_id += 1
         self.queue.append((rid, spec))
@@ -99,6 +119,9 @@ class SingleFlight:
             if self.done >= spec.max_new_tokens:
                 reason = "length"
                 break
+        room = getattr(self.inner, "room", None)
+        if not reason and room is not None and room() <= 0:
+            reason = "length"   # the next step would run past the context limit
         if keep:
             self.tokens_committed += len(keep)
             out.append((rid, ReqEvent("tokens", ids=keep)))
@@ -125,6 +148,11 @@ class SingleFlight:
             rid, spec = self.cur
             self._emit(rid, spec, self.inner.step(), out)
         except Exception as e:  # a failed step poisons only the current request
+            if not self.swallow_errors:
+                self.abort_current("error:" + type(e).__name__, out)
+                self.poisoned = repr(e)
+                self.pending_events = out
+                raise
             if self.cur is not None:
                 rid, spec = self.cur
                 out.append((rid, ReqEvent("finished", reason="error:" + type(e).__name__,
@@ -132,6 +160,13 @@ class SingleFlight:
                 self.poisoned = repr(e)
                 self.cur = None
         return out
+
+    def abort_current(self, reason: str, out: list) -> None:
+        """Finish the request in flight with `reason` (used when a step failed on some rank)."""
+        if self.cur is not None:
+            rid, spec = self.cur
+            out.append((rid, ReqEvent("finished", reason=reason, usage=Usage(len(spec.prompt_ids), self.done, 0))))
+            self.cur = None
 
     def stats(self) -> dict:
         return {"engine": {"ticks": self.ticks, "tokens_committed": self.tokens_committed,
@@ -154,19 +189,27 @@ class HostEngine:
     prefill, the radix prefix cache and continuous batching without a model."""
 
     def __init__(self, vocab: int = 257, max_rows: int = 8, prefill_budget: int = 64, num_pages: int = 4096,
-                 page_size: int = 16, next_token: Optional[Callable[[List[int]], int]] = None):
+                 page_size: int = 16, next_token: Optional[Callable[[List[int]], int]] = None,
+                 max_ctx: int = 1 << 20):
         from .. import build
         build.build_runtime()
         from .. import _runtime as rt
         self.rt = rt
         cfg = rt.SchedConfig()
         cfg.max_rows, cfg.prefill_budget, cfg.num_pages, cfg.page_size = max_rows, prefill_budget, num_pages, page_size
+        cfg.max_ctx = max_ctx
         self.sched = rt.BatchScheduler(cfg)
         self.vocab = vocab
         self.next_token = next_token or (lambda toks: _mock_next(toks, vocab))
         self.ctx: Dict[int, List[int]] = {}
 
+    def validate(self, spec: RequestSpec) -> None:
+        if not spec.prompt_ids or len(spec.prompt_ids) > self.sched.max_prompt():
+            raise ContextOverflow(f"prompt of {len(spec.prompt_ids)} tokens does not fit the context limit "
+                                  f"(at most {self.sched.max_prompt()})")
+
     def submit(self, spec: RequestSpec) -> int:
+        self.validate(spec)
         rid = self.sched.submit(list(spec.prompt_ids), spec.max_new_tokens, list(spec.stop_ids))
         self.ctx[rid] = list(spec.prompt_ids)
         return rid
@@ -218,24 +261,44 @@ class HostEngine:
 
 class EngineDriver:
     """One thread owns the engine.  Callers talk to it through a command queue and receive a
-    request's events on their own queue; dropping a request cancels it."""
+    request's events on their own sink (anything with ``put``); dropping a request cancels it.
 
-    def __init__(self, engine: ServeEngine, idle_sleep: float = 0.002):
+    The thread never dies silently: a request the engine refuses is answered with the exception
+    (``submit`` re-raises it in the caller), and an error out of ``tick`` finishes every open request
+    with ``error:<type>``, answers every pending command, and poisons the driver: ``poisoned`` holds
+    the message, ``submit`` raises :class:`EngineFailed`, the HTTP layer answers 503.  With a replicated
+    (multi-process) engine an idle driver runs an empty heartbeat round every ``heartbeat_s`` seconds so
+    that the follower ranks, which block in the command broadcast, never run into the control group's
+    timeout while the server simply has nothing to do."""
+
+    def __init__(self, engine: ServeEngine, idle_sleep: float = 0.002, heartbeat_s: float = 5.0):
         self.engine = engine
         self.cmds: "queue.Queue" = queue.Queue()
-        self.sinks: Dict[int, "queue.Queue"] = {}
+        self.sinks: Dict[int, object] = {}
         self.idle_sleep = idle_sleep
+        self.heartbeat_s = heartbeat_s
+        self.poisoned: Optional[str] = None
         self._stop = threading.Event()
         self._stats_lock = threading.Lock()
         self._stats: dict = engine.stats()
         self.thread = threading.Thread(target=self._run, name="engine-driver", daemon=True)
         self.thread.start()
 
-    def submit(self, spec: RequestSpec) -> Tuple[int, "queue.Queue"]:
+    def submit(self, spec: RequestSpec, sink=None, timeout: float = 600.0) -> Tuple[int, object]:
+        """Blocks until the driver thread has admitted the request (at most one tick).  Raises what the
+        engine raised (:class:`ContextOverflow` for a prompt that does not fit) or :class:`EngineFailed`."""
+        if self.poisoned:
+            raise EngineFailed(self.poisoned)
         reply: "queue.Queue" = queue.Queue()
-        sink: "queue.Queue" = queue.Queue()
+        sink = sink if sink is not None else queue.Queue()
         self.cmds.put(("submit", spec, sink, reply))
-        return reply.get(), sink
+        try:
+            res = reply.get(timeout=timeout)
+        except queue.Empty:
+            raise EngineFailed("the engine driver did not answer") from None
+        if isinstance(res, BaseException):
+            raise res
+        return res, sink
 
     def cancel(self, req: int) -> None:
         self.cmds.put(("cancel", req, None, None))
@@ -248,24 +311,63 @@ class EngineDriver:
         self._stop.set()
         self.thread.join(timeout=5)
 
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                while True:
-                    kind, a, sink, reply = self.cmds.get_nowait()
-                    if kind == "submit":
+    def _fail(self, e: BaseException) -> None:
+        self.poisoned = f"{type(e).__name__}: {e}"
+        reason = "error:" + type(e).__name__
+        carried = getattr(self.engine, "take_pending_events", None)
+        if carried is not None:   # events produced before the failure (tokens of other requests)
+            for rid, ev in carried():
+                sink = self.sinks.get(rid)
+                if sink is not None:
+                    sink.put(ev)
+                    if ev.kind == "finished":
+                        self.sinks.pop(rid, None)
+        for rid, sink in list(self.sinks.items()):
+            sink.put(ReqEvent("finished", reason=reason, usage=Usage()))
+        self.sinks.clear()
+
+    def _drain_cmds(self) -> None:
+        try:
+            while True:
+                kind, a, sink, reply = self.cmds.get_nowait()
+                if kind == "submit":
+                    if self.poisoned:
+                        reply.put(EngineFailed(self.poisoned))
+                        continue
+                    try:
                         rid = self.engine.submit(a)
-                        self.sinks[rid] = sink
-                        reply.put(rid)
-                    elif kind == "cancel":
-                        self.engine.cancel(a)
-                        self.sinks.pop(a, None)
-            except queue.Empty:
-                pass
-            if self.engine.idle():
+                    except Exception as e:      # refused (too long, malformed): the caller gets the reason
+                        reply.put(e)
+                        continue
+                    self.sinks[rid] = sink
+                    reply.put(rid)
+                elif kind == "cancel" and not self.poisoned:
+                    self.engine.cancel(a)
+                    self.sinks.pop(a, None)
+        except queue.Empty:
+            pass
+
+    def _run(self):
+        last_beat = time.monotonic()
+        while not self._stop.is_set():
+            self._drain_cmds()
+            if self.poisoned:
                 time.sleep(self.idle_sleep)
                 continue
-            for rid, ev in self.engine.tick():
+            try:
+                if self.engine.idle():
+                    beat = getattr(self.engine, "heartbeat", None)
+                    if beat is not None and time.monotonic() - last_beat >= self.heartbeat_s:
+                        beat()
+                        last_beat = time.monotonic()
+                    time.sleep(self.idle_sleep)
+                    continue
+                events = self.engine.tick()
+                last_beat = time.monotonic()
+            except Exception as e:
+                self._fail(e)
+                continue
+            for rid, ev in events:
                 sink = self.sinks.get(rid)
                 if sink is not None:
                     sink.put(ev)

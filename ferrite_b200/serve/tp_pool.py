@@ -39,6 +39,9 @@ class ReplicatedEngine:
     # ---- rank 0 side (ServeEngine protocol) ---------------------------------------------
     def submit(self, spec: RequestSpec) -> int:
         assert self.rank == 0
+        validate = getattr(self.engine, "validate", None)
+        if validate is not None:
+            validate(spec)   # refuse on rank 0, before the command reaches the other ranks
         self.pending.append(("submit", (list(spec.prompt_ids), spec.max_new_tokens, tuple(spec.stop_ids))))
         # ids are assigned by the deterministic planner in submit order: predict it
         self.local_ids += 1
@@ -61,6 +64,19 @@ class ReplicatedEngine:
     def stop(self) -> None:
         if self.rank == 0:
             self._round([("stop", None)])
+
+    def heartbeat(self) -> None:
+        """An empty round: keeps the followers' blocking broadcast (and the control group's watchdog) alive
+        while rank 0 has nothing to do."""
+        if self.rank == 0 and self.world > 1:
+            self._round([("beat", None)])
+
+    def take_pending_events(self):
+        """Events the engine produced in the tick that failed (the driver still delivers them)."""
+        ev = getattr(self.engine, "pending_events", None) or []
+        if hasattr(self.engine, "pending_events"):
+            self.engine.pending_events = []
+        return ev
 
     # ---- follower side -------------------------------------------------------------------
     def follow(self) -> None:
@@ -97,6 +113,10 @@ class ReplicatedEngine:
         else:
             errs = [err]
         if any(errs):
+            # every rank saw the same list: all of them drop the request in flight together
+            abort = getattr(self.engine, "abort_current", None)
+            if abort is not None:
+                abort("error:RankFailure", [])
             self.poisoned = str(errs)
             raise RankFailure(errs)
         if stop:

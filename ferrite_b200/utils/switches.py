@@ -26,6 +26,12 @@ class Switches:
     nvtx: bool = False              # NVTX ranges around engine phases
     pdl: bool = False               # programmatic dependent launch
     ar_group: int = 0               # tiles per published group of the fused GEMV all-reduce (0 = whole grid)
+    tc_gemv_min_n: int = 0          # decode GEMVs with at least this many outputs use the tcgen05 split-K kernel (0 = never)
+    tc_gemv_max_n: int = 0          # ... and, for 9-16 rows, matrices with at most this many outputs (0 = never)
+    l2_ahead: int = -1              # read-ahead distance of the weight-streaming kernels (-1 = library default)
+    d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores
+    d4_attn_tc: bool = False        # DSV41 tensor-core sparse attention (slower than the SIMT kernel at decode sizes)
+    d4_fuse_quant: bool = False     # DSV41 activation quantiser fused into hc_pre (a one-CTA latency chain; slower)
     dump_dir: str = ""              # directory for unit dumps ("" = off)
     allow_stale_kernels: bool = False
 

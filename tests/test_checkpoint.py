@@ -81,3 +81,51 @@ def test_fused_aliases_and_fp8_experts_on_disk(tmp_path):
     q2, s2 = src.get_fp8(k)
     assert torch.equal(q2.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s2, s)
     assert src.get_fp8("model.layers.2.mlp.experts.2.down_proj.weight") is None
+
+
+def test_bad_scale_tensors_and_sizes_are_refused(tmp_path):
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(300, 260, generator=g)
+    q, s = quant_fp8_block(a)
+    d = tmp_path / "short"
+    d.mkdir()
+    write_safetensors(str(d / "m.safetensors"), {"a.weight": q, "a.weight_scale_inv": s[:2].contiguous()})
+    idx = CheckpointIndex(str(d))
+    with pytest.raises(ValueError, match="scale shape"):      # a truncated scale tensor never reaches the reader
+        idx.dequant_fp8("a.weight", "a.weight_scale_inv")
+    d = tmp_path / "bf16"
+    d.mkdir()
+    write_safetensors(str(d / "m.safetensors"), {"a.weight": q, "a.weight_scale_inv": s.bfloat16()})
+    idx = CheckpointIndex(str(d))
+    want = dequant_fp8_block(q, s.bfloat16().float())
+    assert torch.equal(idx.dequant_fp8("a.weight", "a.weight_scale_inv"), want)   # bf16 scales: torch path, not a reinterpret
+    # an entry whose byte range disagrees with shape x dtype is refused when the index is built
+    d = tmp_path / "size"
+    d.mkdir()
+    import json
+    hdr = json.dumps({"x": {"dtype": "F32", "shape": [4, 4], "data_offsets": [0, 32]}}).encode()
+    (d / "m.safetensors").write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 64)
+    with pytest.raises(ValueError, match="bytes for shape"):
+        CheckpointIndex(str(d))
+    # the C++ reader bounds-checks the scale range itself
+    from ferrite_b200 import _runtime as rt
+    d = tmp_path / "ok"
+    d.mkdir()
+    write_safetensors(str(d / "m.safetensors"), {"a.weight": q, "a.weight_scale_inv": s})
+    idx = CheckpointIndex(str(d))
+    ti, si = idx.tensors["a.weight"], idx.tensors["a.weight_scale_inv"]
+    with pytest.raises(Exception):
+        ti.file.dequant_e4m3_block(ti.begin, si.end - 8, 300, 260, 128, 0, 300)
+
+
+def test_flat_fused_fg_b_alias(tmp_path):
+    cfg = GlmConfig.tiny()
+    w = {k: (v.bfloat16().float() if v.dim() > 1 else v) for k, v in random_weights(cfg, 0, std=0.05).items()}
+    out = {("model.language_model." + k[len("model."):] if k.startswith("model.") else k): v for k, v in w.items()}
+    a = "model.language_model.layers.0.self_attn."
+    out[a + "fused_fg_b_proj.weight"] = torch.cat([out.pop(a + "f_b_proj.weight"), out.pop(a + "g_b_proj.weight")], 0)
+    write_safetensors(str(tmp_path / "model.safetensors"), out)
+    src = CheckpointSource(str(tmp_path), cfg)
+    for leaf in ("f_b_proj", "g_b_proj"):
+        k = f"model.layers.0.self_attn.{leaf}.weight"
+        assert torch.equal(src.get(k).float(), w[k]), k

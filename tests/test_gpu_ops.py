@@ -71,8 +71,24 @@ def make_meta(K, slots, gsizes, seq_len):
     n = len(rs)
     meta = torch.zeros(n * 32, dtype=torch.uint8, device="cuda")
     sl = t(seq_len)
-    K.call("fb_prep_rows", t(rs), t(ro), t(rg), sl, meta, n)
+    K.call("fb_prep_rows", t(rs), t(ro), t(rg), sl, meta, n, 0, None)
     return meta, t(gf), n, sl
+
+
+def test_prep_rows_clamps_at_the_context_limit(K):
+    """Row metadata is the single source of positions: a group that would pass the limit is moved back
+    below it and the status word names the slot.  Only metadata is computed here; no cache is touched."""
+    import struct
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    meta = torch.zeros(5 * 32, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    # slot 0: 3 rows from 10 (fine); slot 1: 2 rows from 63 with a limit of 64 (one too many)
+    K.call("fb_prep_rows", t([0, 0, 0, 1, 1]), t([0, 1, 2, 0, 1]), t([3, 3, 3, 2, 2]), t([10, 63]), meta, 5, 64, status)
+    torch.cuda.synchronize()
+    rows = [struct.unpack("8i", bytes(meta[i * 32:(i + 1) * 32].tolist())) for i in range(5)]
+    assert [r[1] for r in rows] == [10, 11, 12, 62, 63]            # positions
+    assert [r[3] for r in rows] == [13, 13, 13, 64, 64]            # totals stay <= limit
+    assert status.tolist() == [3, 1, 63, 2]                         # FB_BAD_ARG, slot, length, rows
 
 
 @pytest.mark.parametrize("m,N,K_,group", [(1, 300, 256, 0), (3, 4100, 512, 0), (8, 9600, 128, 0),
