@@ -7,6 +7,9 @@
 //   q *= dk^-0.5 -> beta = sigmoid(b) -> decay = exp(lb * sigmoid(exp(A_log)(fb + dt_bias)))
 //   S *= decay (rows); u = S^T k; S += beta k (v - u)^T; o = S^T q
 //   -> gated RMSNorm with sigmoid(gb) and o_norm.
+// For decode-sized groups (<= 8 rows) the kernel can also apply the second halves of the low-rank decay / gate
+// projections itself (fb = f_b . f_a_out, gb = g_b . g_a_out: 2 * dk rows of 128 weights per head), which removes
+// the GEMV launch that would otherwise sit between the input projection and this kernel.
 // State and conv tails live in `nbuf` rotating buffers per sequence slot: with snapshots on
 // (MTP verify) the state after row i goes to buffer (cur+1+i) % nbuf, so accepting k rows is
 // just cur += k (see fb_mtp_commit) -- no state copy, where the reference restores from
@@ -28,13 +31,17 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
                  float* __restrict__ conv_state, const int* __restrict__ cur,
                  const RowMeta* __restrict__ meta, const int* __restrict__ group_first,
                  float* __restrict__ out, int ld_out, int H, int b_off, int nbuf, int snapshots, float lb, float eps,
-                 SplitBuf osp) {
+                 SplitBuf osp, const __nv_bfloat16* __restrict__ fgw, int fa_off, int lr) {
     PDL_PROLOGUE();
     constexpr int RPT = DK / 4;  // state rows per thread
+    constexpr int kFgRows = 8;   // rows per group the in-kernel low-rank projection covers
+    constexpr int kLrMax = 128;
     __shared__ float qs[DK], ks[DK], vs[DK], dec[DK];
     __shared__ float part[4][DK];
     __shared__ float red[32];
     __shared__ float s_beta;
+    __shared__ float fg_s[kFgRows][2][DK];       // [row][f | g][channel]
+    __shared__ float fin_s[kFgRows][2 * kLrMax];  // f_a | g_a outputs of the group's rows
 
     const int h = blockIdx.x;
     const int row0 = group_first[blockIdx.y];
@@ -69,6 +76,43 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
     }
     const float a_exp = __expf(a_log[h]);
     const float qscale = rsqrtf((float)DK);
+    const bool own_fg = fgw != nullptr;   // host guarantees gsize <= kFgRows and lr <= kLrMax then
+    if (own_fg) {
+        for (int i = tid; i < gsize * 2 * lr; i += blockDim.x) {
+            const int rr = i / (2 * lr), k = i % (2 * lr);
+            fin_s[rr][k] = proj[(size_t)(row0 + rr) * ld_proj + fa_off + k];
+        }
+        __syncthreads();
+        // two adjacent lanes share an output channel, each takes half of the low-rank dimension
+        const int o = tid >> 1, half = tid & 1;          // o in [0, 2 DK): f channels then g channels
+        const int isg = o / DK, e = o % DK;
+        const int kh = lr / 2;
+        const __nv_bfloat16* wrow = fgw + ((size_t)isg * P + (size_t)h * DK + e) * lr + half * kh;
+        float acc[kFgRows];
+#pragma unroll
+        for (int rr = 0; rr < kFgRows; ++rr) acc[rr] = 0.f;
+        for (int k = 0; k < kh; k += 8) {
+            const uint4 w4 = ldg_nc_v4(wrow + k);
+            const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+            float wf[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { wf[2 * j] = bf16lo(ww[j]); wf[2 * j + 1] = bf16hi(ww[j]); }
+#pragma unroll
+            for (int rr = 0; rr < kFgRows; ++rr) {
+                if (rr < gsize) {
+                    const float* xin = &fin_s[rr][isg * lr + half * kh + k];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[rr] = fmaf(wf[j], xin[j], acc[rr]);
+                }
+            }
+        }
+#pragma unroll
+        for (int rr = 0; rr < kFgRows; ++rr) {
+            const float tot = acc[rr] + __shfl_xor_sync(0xffffffffu, acc[rr], 1);
+            if (half == 0 && rr < gsize) fg_s[rr][isg][e] = tot;
+        }
+        __syncthreads();
+    }
 
     for (int i = 0; i < gsize; ++i) {
         const int r = row0 + i;
@@ -81,7 +125,7 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
             val = siluf_(val);
         } else {
             const int e = tid - 3 * DK;
-            const float g = fb[(size_t)r * ld_fg + h * DK + e] + dt_bias[h * DK + e];
+            const float g = (own_fg ? fg_s[i][0][e] : fb[(size_t)r * ld_fg + h * DK + e]) + dt_bias[h * DK + e];
             dec[e] = __expf(lb * sigmoidf_(a_exp * g));
             if (e == 0) s_beta = sigmoidf_(prow[b_off + h]);
         }
@@ -136,7 +180,7 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
         const float tot = block_sum(o2, red);
         if (rg == 0) {
             const float inv = rsqrtf(tot / DK + eps);
-            const float gate = sigmoidf_(gb[(size_t)r * ld_fg + h * DK + c]);
+            const float gate = sigmoidf_(own_fg ? fg_s[i][1][c] : gb[(size_t)r * ld_fg + h * DK + c]);
             const float ov = o * inv * o_norm_w[c] * gate;
             out[(size_t)r * ld_out + h * DK + c] = ov;
             split_store(osp, r, h * DK + c, ov);
@@ -161,16 +205,22 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
 // decay and output-gate pre-activations (P each).  state [slots][nbuf][H][dk][dk],
 // conv_state [slots][nbuf][3P][3].  group_first[g] = first row of group g; rows of a group
 // are contiguous and ordered.  snapshots=1 requires gsize < nbuf.
+// fg_w (may be null): bf16 [2 * H * dk, lr] = f_b rows then g_b rows.  When given, fb / gb are not read: the kernel
+// applies f_b / g_b itself to the f_a | g_a outputs at columns [fa_off, fa_off + 2 lr) of proj; every group must
+// then have at most 8 rows (max_gsize) and lr <= 128, lr % 16 == 0.
 FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, const float* gb, int64_t ld_fg,
                         const float* conv_w, const float* a_log, const float* dt_bias,
                         const float* o_norm_w, float* state, float* conv_state, const int* cur,
                         const void* meta, const int* group_first, int64_t n_groups, float* out,
                         int64_t ld_out, int64_t H, int64_t dk, int64_t b_off, int64_t nbuf, int64_t snapshots, float lb,
-                        float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+                        float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
+                        const void* fg_w, int64_t fa_off, int64_t lr, int64_t max_gsize, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    if (fg_w && (max_gsize > 8 || lr > 128 || (lr % 16) || lr < 16)) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)H, (unsigned)n_groups);
 #define GDN_ARGS proj, (int)ld_proj, fb, gb, (int)ld_fg, conv_w, a_log, dt_bias, o_norm_w, state, conv_state, cur, \
-        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps, osp
+        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, (int)snapshots, lb, eps, osp, \
+        (const __nv_bfloat16*)fg_w, (int)fa_off, (int)lr
     if (dk == 128) FB_LAUNCH((gdn_fused_kernel<128>), grid, 512, 0, st, GDN_ARGS);
     else if (dk == 64) FB_LAUNCH((gdn_fused_kernel<64>), grid, 256, 0, st, GDN_ARGS);
     else if (dk == 32) FB_LAUNCH((gdn_fused_kernel<32>), grid, 128, 0, st, GDN_ARGS);

@@ -216,6 +216,74 @@ int launch_sk_rb(const void* W, const float* scales, const float* x, int ldx, fl
 }
 
 
+// ---- MoE routing as the tail of the router GEMV ---------------------------------------------
+// The router logits are the first E outputs of the [router | shared gate | shared up] GEMV.  The CTAs that own
+// those outputs take a ticket when their tile is stored; the last of them routes every row (one warp per row)
+// while the rest of the grid is still streaming the shared expert's rows, so routing costs no launch and no time.
+//   s = sigmoid(logit); top-k of (s + bias), ties to the lower index; w = s_sel / (sum s_sel + eps_f32) * scaling
+struct RouteTail {
+    const float* bias;   // [E]   (null: no routing)
+    int* ids;            // [m][topk]
+    float* wts;          // [m][topk]
+    unsigned* ticket;
+    int E, topk;
+    float scaling;
+};
+
+__device__ __forceinline__ uint32_t route_okey(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ld_cg(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+constexpr int kRouteKeys = 12;   // experts per lane: E <= 384
+
+__device__ __noinline__ void route_row_warp(const float* __restrict__ logits, const RouteTail& rt, int row, int lane) {
+    unsigned long long key[kRouteKeys];
+    float sig[kRouteKeys];
+#pragma unroll
+    for (int i = 0; i < kRouteKeys; ++i) {
+        const int e = lane + 32 * i;
+        key[i] = 0ull;
+        sig[i] = 0.f;
+        if (e < rt.E) {
+            const float sv = 1.f / (1.f + expf(-ld_cg(logits + e)));
+            sig[i] = sv;
+            key[i] = ((unsigned long long)route_okey(sv + rt.bias[e]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)e);
+        }
+    }
+    float my_s = 0.f;
+    int my_id = 0;
+    for (int k = 0; k < rt.topk; ++k) {
+        unsigned long long best = 0ull;
+#pragma unroll
+        for (int i = 0; i < kRouteKeys; ++i) best = key[i] > best ? key[i] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
+            best = t > best ? t : best;
+        }
+        const int e = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+        float cand = 0.f;
+#pragma unroll
+        for (int i = 0; i < kRouteKeys; ++i)
+            if (key[i] == best) { cand = sig[i]; key[i] = 0ull; }
+        const float sv = __shfl_sync(0xffffffffu, cand, e & 31);
+        if (lane == k) { my_s = sv; my_id = e; }
+    }
+    float sum = 0.f;
+    for (int k = 0; k < rt.topk; ++k) sum += __shfl_sync(0xffffffffu, my_s, k);
+    const float inv = rt.scaling / (sum + 1.1920929e-07f);
+    if (lane < rt.topk) {
+        rt.ids[(size_t)row * rt.topk + lane] = my_id;
+        rt.wts[(size_t)row * rt.topk + lane] = my_s * inv;
+    }
+}
+
 // ---- tensor-core form (see mma_gemv.cuh) ---------------------------------------------------
 // A CTA owns 16*RT weight rows; its NW warps take interleaved k-blocks (64 bf16 / 128 e4m3
 // elements) with the next block's weight loads in flight while the current block is
@@ -225,7 +293,7 @@ __global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
 gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
                 const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
                 float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,
-                SplitBuf osplit, int l2_ahead) {
+                SplitBuf osplit, int l2_ahead, RouteTail rt) {
     pdl_launch();  // weights are constant: the first k-block is fetched before pdl_wait()
     constexpr int KB = FP8 ? 128 : 64;
     constexpr int XW = FP8 ? 16 : 8;
@@ -311,24 +379,40 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
             split_store(osplit, r0 + col, row, v);
         }
     }
+    if (rt.bias != nullptr && n0 < rt.E && blockIdx.y == 0) {
+        __shared__ int s_route;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const unsigned owners = (unsigned)((rt.E + 16 * RT - 1) / (16 * RT));
+            s_route = atomicAdd(rt.ticket, 1u) == owners - 1u;
+            if (s_route) *rt.ticket = 0u;
+        }
+        __syncthreads();
+        if (s_route) {
+            __threadfence();
+            for (int row = warp; row < mrows; row += NW) route_row_warp(out + (size_t)row * ldo, rt, row, lane);
+        }
+    }
 }
 
 template <bool FP8>
 int launch_mma(const void* W, const float* scales, const uint16_t* xs, int ldx, int plane, float* out, int ldo,
-               int mrows, int N, int K, int group_rows, int accumulate, SplitBuf osplit, cudaStream_t st) {
+               int mrows, int N, int K, int group_rows, int accumulate, SplitBuf osplit, cudaStream_t st,
+               RouteTail rt = RouteTail{}) {
     const uint16_t* hi = xs + (FP8 ? 2 * (size_t)plane : 0);
     const uint16_t* lo = hi + plane;
     const uint8_t* w8 = static_cast<const uint8_t*>(W);
     constexpr int KB = FP8 ? 128 : 64;
     const int nkb = K / KB;
     if (N >= 9472 && (group_rows == 0 || group_rows % 32 == 0)) {
-        FB_LAUNCH((gemv_mma_kernel<2, 8, FP8>), dim3((unsigned)((N + 31) / 32), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<2, 8, FP8>), dim3((unsigned)((N + 31) / 32), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead, rt);
     } else if (nkb >= 64 && N <= 8192) {  // few row tiles, long rows: split K over 16 warps
-        FB_LAUNCH((gemv_mma_kernel<1, 16, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 512, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 16, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 512, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead, rt);
     } else if (nkb >= 8) {
-        FB_LAUNCH((gemv_mma_kernel<1, 8, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 8, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 256, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead, rt);
     } else {
-        FB_LAUNCH((gemv_mma_kernel<1, 2, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 64, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead);
+        FB_LAUNCH((gemv_mma_kernel<1, 2, FP8>), dim3((unsigned)((N + 15) / 16), (unsigned)((mrows + 7) / 8)), 64, 0, st, w8, scales, hi, lo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, g_fb_l2_ahead, rt);
     }
     return FB_LAUNCH_CHECK();
 }
@@ -397,6 +481,18 @@ FB_API int fb_gemv_mma_bf16(const void* W, const void* xs, int64_t xs_ld, int64_
     SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
     return launch_mma<false>(W, nullptr, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
                              (int)K, (int)group_rows, (int)accumulate, os, st);
+}
+
+// fb_gemv_mma_bf16 for the MoE router matrix [E router rows | shared gate | shared up]: the launch also routes the
+// rows (ids / wts [m][topk]) from its first E outputs; E <= 384, m <= 8; ticket: one zeroed counter.
+FB_API int fb_gemv_mma_bf16_route(const void* W, const void* xs, int64_t xs_ld, int64_t xs_plane, float* out,
+                                  int64_t ldo, int64_t m, int64_t N, int64_t K, const float* bias, int* ids, float* wts,
+                                  void* ticket, int64_t E, int64_t topk, float scaling, cudaStream_t st) {
+    if (m < 1 || m > 8 || (K % 64) || (xs_ld % 8) || E > 32 * kRouteKeys || E > N || topk > 32 || !bias || !ids || !wts || !ticket)
+        return (int)cudaErrorInvalidValue;
+    RouteTail rt{bias, ids, wts, (unsigned*)ticket, (int)E, (int)topk, scaling};
+    return launch_mma<false>(W, nullptr, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
+                             (int)K, 0, 0, SplitBuf{nullptr, 0, 0, 0}, st, rt);
 }
 
 FB_API int fb_gemv_mma_fp8(const void* W, const float* scales, const void* xs, int64_t xs_ld, int64_t xs_plane,

@@ -19,6 +19,18 @@
 // Epochs and parity double-buffering follow the stand-alone all-reduce (collective.cu).
 // With world == 1 the collective is skipped and the kernel is a GEMV with the fold epilogue.
 //
+// Two more stages can ride in the same launch, so that a sublayer boundary is ONE kernel:
+//   * activation source: instead of split planes the GEMV can read the f32 [gate | up] row a previous GEMV left
+//     and apply SwiGLU while it builds its B fragments (the shared expert's and the dense FFN's down projection);
+//   * hyper-connection front of the NEXT site: besides the mix dots every tile leaves the 10 Gram dots
+//     <R'_i, R'_j> of its columns.  CTAs meet on a grid barrier (the grid is co-resident by construction); the
+//     last CTA to arrive sums the tiles' partials in tile order, derives pre = sigmoid(mix * r * s0 + b) + eps
+//     and the RMS of x = sum_i pre_i R'_i from the Gram matrix (|x|^2 = sum_ij pre_i pre_j G_ij), publishes
+//     both, and goes on to post / comb (softmax + Sinkhorn), which only the next fold reads.  Every CTA then
+//     contracts and normalises its own columns of x and writes them in f32 and split form.  This replaces a
+//     one-CTA-per-row kernel (11 us, 90 launches per decode step) by about 3 us inside a kernel that is
+//     running anyway.
+//
 // Replaces the reference's store-carrying GEMV epilogues + `p2p_ar_pubred_v5(_hcpost)`
 // (kernels/cuda/ferrite_kernels.cu:8968-9524; crates/ferrite-exec/src/tp.rs:742-1059).
 #include "common.cuh"
@@ -48,6 +60,71 @@ struct HcFold {
     int* part_n;        // [8] number of valid tiles per row (the consumer clears it)
 };
 
+struct HcPre {
+    const float* scale;  // [3]   (null: no front)
+    const float* base;   // [mix]
+    const float* ln_w;   // [N]
+    float* post;         // [m][4]   next site's coefficients (may alias HcFold::post: written after the barrier)
+    float* comb;         // [m][16]
+    float* x;            // [m][N] normalised layer input
+    SplitBuf xs;         // ... and its split planes
+    float* gram;         // [8][10][kMaxTiles] per-tile Gram partials
+    float* coef;         // [8][8]: pre[4], rms factor of x
+    unsigned* bar;       // [2]: arrivals of this launch, generation
+    float rms_eps, hc_eps;
+    int iters;
+};
+
+struct XSrc {            // where the activations come from
+    const float* gu;     // null: split planes; else f32 rows [gate(I) | up(I)] with stride ld
+    int ld, up_off;
+    float limit;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// B fragment built from f32 [gate | up]: act = silu(min(g, L)) * clamp(u, -L, L), split into a 16-bit high and low
+// part (bf16 pair for bf16 weights, f16 high part only for e4m3 weights, as the plane-reading path does).
+template <int WORDS, bool FP8>
+__device__ __forceinline__ void swiglu_xfrag(const XSrc& xs, int g, int mrows, int k0, uint32_t (&xh)[WORDS], uint32_t (&xl)[WORDS]) {
+    if (g >= mrows) {
+#pragma unroll
+        for (int i = 0; i < WORDS; ++i) { xh[i] = 0u; xl[i] = 0u; }
+        return;
+    }
+    const float4* pg = reinterpret_cast<const float4*>(xs.gu + (size_t)g * xs.ld + k0);
+    const float4* pu = reinterpret_cast<const float4*>(xs.gu + (size_t)g * xs.ld + xs.up_off + k0);
+#pragma unroll
+    for (int i = 0; i < WORDS / 2; ++i) {
+        const float4 a = pg[i], b = pu[i];
+        const float ga[4] = {a.x, a.y, a.z, a.w}, ua[4] = {b.x, b.y, b.z, b.w};
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = siluf_(fminf(ga[j], xs.limit)) * fminf(fmaxf(ua[j], -xs.limit), xs.limit);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (FP8) {
+                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                xh[2 * i + j] = *reinterpret_cast<const uint32_t*>(&h);
+                xl[2 * i + j] = 0u;
+            } else {
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(v[2 * j]), h1 = __float2bfloat16_rn(v[2 * j + 1]);
+                const __nv_bfloat16 l0 = __float2bfloat16_rn(v[2 * j] - __bfloat162float(h0));
+                const __nv_bfloat16 l1 = __float2bfloat16_rn(v[2 * j + 1] - __bfloat162float(h1));
+                xh[2 * i + j] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+                xl[2 * i + j] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -75,12 +152,14 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
 }
 
-template <int RT, int NW, bool FP8>
+constexpr int kGram = 10;   // pairs (i <= j) of the four residual streams
+
+template <int RT, int NW, bool FP8, bool SWIGLU>
 __global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
 gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, const uint16_t* __restrict__ xhi,
                const uint16_t* __restrict__ xlo, int ldx, float* __restrict__ y, int ldo, int mrows, int N, int K,
                int accumulate, int store_y, ArPtrs t, uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status,
-               int rank, int world, int max_elems, int max_spins, int group, HcFold hc, int l2_ahead) {
+               int rank, int world, int max_elems, int max_spins, int group, HcFold hc, int l2_ahead, XSrc xsrc, HcPre pre) {
     pdl_launch();
     constexpr int kTileN = 16 * RT;
     constexpr int KB = FP8 ? 128 : 64;
@@ -119,7 +198,8 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
     };
     auto compute = [&](const WFrag (&f)[RT], int kb) {
         uint32_t xh[XW], xl[XW];
-        load_xfrag<XW, !FP8>(xhi, xlo, ldx, g, mrows, kb * KB + tq * (KB / 4), xh, xl);
+        if (SWIGLU) swiglu_xfrag<XW, FP8>(xsrc, g, mrows, kb * KB + tq * (KB / 4), xh, xl);
+        else load_xfrag<XW, !FP8>(xhi, xlo, ldx, g, mrows, kb * KB + tq * (KB / 4), xh, xl);
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
             if (FP8) {
@@ -143,6 +223,9 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         }
     }
     pdl_wait();
+    const bool front = fold && hc.fn && pre.scale != nullptr;
+    // generation of the grid barrier: read before this CTA arrives, so it is the value of this launch
+    const uint32_t gen0 = front ? ld_acquire_gpu(pre.bar + 1) : 0u;
     if (fold) {
         constexpr int Q4 = kTileN / 4;
         for (int i = threadIdx.x; i < mrows * 4 * Q4; i += blockDim.x) {
@@ -275,7 +358,145 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
             if (lane == 0) hc.part[((size_t)mm * (kMaxMix + 1) + (q < hc.mix ? q : kMaxMix)) * kMaxTiles + tl] = d;
         }
     }
-    if (blockIdx.x == 0 && threadIdx.x < mrows) hc.part_n[threadIdx.x] = gridDim.x;
+    if (!front) {
+        if (blockIdx.x == 0 && threadIdx.x < mrows) hc.part_n[threadIdx.x] = gridDim.x;
+        return;
+    }
+    // ---- hyper-connection front of the next site ------------------------------------------------------------
+    // Gram partials of this tile: pair p = (i, j), i <= j, one warp per (row, pair)
+    for (int w = warp; w < mrows * kGram; w += NW) {
+        const int mm = w / kGram, p = w % kGram;
+        int i = 0, rem = p;
+        while (rem >= 4 - i) { rem -= 4 - i; ++i; }
+        const int j = i + rem;
+        float d = 0.f;
+        for (int c = lane; c < kTileN; c += 32) d = fmaf(r_s[mm][i][c], r_s[mm][j][c], d);
+        d = warp_sum(d);
+        if (lane == 0) pre.gram[((size_t)mm * kGram + p) * kMaxTiles + tl] = d;
+    }
+    __shared__ int s_last;
+    __shared__ float s_sum[8][kMaxMix + 1 + kGram];
+    __shared__ float s_chunk[NW * 32];
+    __shared__ float s_coef[8][8];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(pre.bar, 1u) == gridDim.x - 1u;
+    }
+    __syncthreads();
+    const int nt = gridDim.x;
+    // sums tile partials of NQ quantities per row, in a fixed order: thread (pair, chunk) adds its tiles, then one
+    // thread per pair adds the chunks.  sel(q): index of the q-th quantity in [0, kMaxMix] (mix / sum of squares) or
+    // kMaxMix + 1 + p (Gram pair p).
+    auto reduce_parts = [&](int q0, int nq, auto sel) {
+        const int npairs = mrows * nq;
+        const int chunks = max(1, (int)blockDim.x / npairs);
+        for (int base = 0; base < npairs; base += blockDim.x / chunks) {
+            const int pr = base + threadIdx.x / chunks, ck = threadIdx.x % chunks;
+            float a = 0.f;
+            if (pr < npairs && (int)threadIdx.x < (int)(blockDim.x / chunks) * chunks) {
+                const int mm = pr / nq, qi = sel(q0 + pr % nq);
+                const float* src = qi <= kMaxMix ? hc.part + ((size_t)mm * (kMaxMix + 1) + qi) * kMaxTiles
+                                                 : pre.gram + ((size_t)mm * kGram + (qi - kMaxMix - 1)) * kMaxTiles;
+                const int per = (nt + chunks - 1) / chunks;
+                const int t0 = ck * per, t1 = min(nt, t0 + per);
+                for (int tt = t0; tt < t1; ++tt) a += ld_cg_f32(src + tt);
+            }
+            s_chunk[threadIdx.x] = a;
+            __syncthreads();
+            if (ck == 0 && pr < npairs && (int)threadIdx.x < (int)(blockDim.x / chunks) * chunks) {
+                float tot = 0.f;
+                for (int c = 0; c < chunks; ++c) tot += s_chunk[threadIdx.x + c];
+                s_sum[pr / nq][sel(q0 + pr % nq)] = tot;
+            }
+            __syncthreads();
+        }
+    };
+    if (s_last) {
+        __threadfence();
+        // phase 1: what x needs: mix dots 0..3, the sum of squares, the Gram matrix
+        reduce_parts(0, 5 + kGram, [&](int q) { return q < 4 ? q : (q == 4 ? kMaxMix : kMaxMix + 1 + (q - 5)); });
+        if (threadIdx.x < mrows) {
+            const int mm = threadIdx.x;
+            const float rr = rsqrtf(s_sum[mm][kMaxMix] / (float)(4 * N) + pre.rms_eps);
+            float pw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(s_sum[mm][i] * rr * pre.scale[0] + pre.base[i]) + pre.hc_eps;
+            float xss = 0.f;
+            int p = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = i; j < 4; ++j, ++p) xss += (i == j ? 1.f : 2.f) * pw[i] * pw[j] * s_sum[mm][kMaxMix + 1 + p];
+            const float inv = rsqrtf(fmaxf(xss, 0.f) / (float)N + pre.rms_eps);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { s_coef[mm][i] = pw[i]; pre.coef[mm * 8 + i] = pw[i]; }
+            s_coef[mm][4] = inv; pre.coef[mm * 8 + 4] = inv;
+            s_coef[mm][5] = rr;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            pre.bar[0] = 0u;
+            __threadfence();
+            st_release_gpu(pre.bar + 1, gen0 + 1u);   // everyone else may go on
+        }
+    } else {
+        if (threadIdx.x == 0) {
+            int spins = 0;
+            const int budget = fb_spin_budget(status, max_spins);
+            while (ld_acquire_gpu(pre.bar + 1) == gen0) {
+                if (++spins > budget) {
+                    status[0] = FB_TIMEOUT; status[1] = -1; status[2] = (int)gen0; status[3] = tl;
+                    s_fail = 1;
+                    break;
+                }
+                __nanosleep(32);
+            }
+        }
+        __syncthreads();
+        if (s_fail) return;
+        if (threadIdx.x < mrows * 8) s_coef[threadIdx.x >> 3][threadIdx.x & 7] = ld_cg_f32(pre.coef + threadIdx.x);
+        __syncthreads();
+    }
+    if (live) {
+        const float* cf = s_coef[m];
+        const float xv = cf[0] * r_s[m][0][nl] + cf[1] * r_s[m][1][nl] + cf[2] * r_s[m][2][nl] + cf[3] * r_s[m][3][nl];
+        const float o = xv * cf[4] * __ldg(pre.ln_w + n0 + nl);
+        pre.x[(size_t)m * N + n0 + nl] = o;
+        split_store(pre.xs, m, n0 + nl, o);
+    }
+    if (!s_last) return;
+    // phase 2 (off the critical path: only the next fold reads it): post and comb of the next site
+    reduce_parts(4, hc.mix - 4, [&](int q) { return q; });
+    if (warp < mrows) {
+        const int mm = warp;
+        const float rr = s_coef[mm][5];
+        const float* a = s_sum[mm];
+        if (lane < 4) pre.post[mm * 4 + lane] = 2.f * sigmoidf_(a[4 + lane] * rr * pre.scale[1] + pre.base[4 + lane]);
+        // comb element (i = lane / 4, k = lane % 4): row softmax + eps, column normalise, then Sinkhorn rounds
+        float c = 0.f;
+        const bool on = lane < 16;
+        if (on) c = a[8 + lane] * rr * pre.scale[2] + pre.base[8 + lane];
+        float mx = on ? c : -INFINITY;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float e = on ? __expf(c - mx) : 0.f;
+        float den = e + __shfl_xor_sync(0xffffffffu, e, 1);
+        den += __shfl_xor_sync(0xffffffffu, den, 2);
+        c = on ? e / den + pre.hc_eps : 0.f;
+        float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        c = __fdividef(c, cs + pre.hc_eps);
+        for (int it = 1; it < pre.iters; ++it) {
+            float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            c = __fdividef(c, rs + pre.hc_eps);
+            cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            c = __fdividef(c, cs + pre.hc_eps);
+        }
+        if (on) pre.comb[mm * 16 + lane] = c;
+    }
 }
 
 }  // namespace
@@ -285,27 +506,42 @@ FB_API int fb_gemv_ar_limits(int* max_tiles, int* max_world, int* flag_words) {
     return 0;
 }
 
-template <int RT, int NW, bool FP8, typename... A>
+template <int RT, int NW, bool FP8, bool SWIGLU, typename... A>
 static void launch_ar(int N, cudaStream_t st, A... a) {
-    FB_LAUNCH((gemv_ar_kernel<RT, NW, FP8>), (N + 16 * RT - 1) / (16 * RT), NW * 32, 0, st, a...);
+    FB_LAUNCH((gemv_ar_kernel<RT, NW, FP8, SWIGLU>), (N + 16 * RT - 1) / (16 * RT), NW * 32, 0, st, a...);
 }
+
+// Optional stages of fb_gemv_ar (all pointers null / zero: off).
+struct FbGemvArExt {
+    // activation source: f32 rows [gate | up] (stride gu_ld, up at column gu_up_off) instead of split planes
+    const float* gu; int64_t gu_ld, gu_up_off; float limit;
+    // hyper-connection front of the next site (needs the fold with fn): see HcPre
+    const float* pre_scale; const float* pre_base; const float* pre_ln_w;
+    float* pre_post; float* pre_comb; float* pre_x;
+    void* xs_base; int64_t xs_ld, xs_plane, xs_mask;
+    float* gram; float* coef; void* bar;
+    float rms_eps, hc_eps; int64_t iters;
+};
 
 // W [N, K] bf16 (scales == null) or e4m3 with 128x128 f32 block scales; xs: split activation planes
 // (see fb_gemv_mma_bf16).  staging_ptrs / flag_ptrs: host arrays of `world` device pointers, or null
 // when world == 1.  Rin == null disables the fold; fn == null keeps the fold but skips the mix dots.
 // part: 8 * 25 * max_tiles floats of per-tile mix-dot partials and part_n: 8 ints (tiles per row), both
 // consumed and cleared by fb_hc_pre_apply / fb_d4_hc_pre; `acc` is not written by this kernel.
+// ext (may be null): the SwiGLU activation source and the next site's hyper-connection front.
 FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_t xs_ld, int64_t xs_plane, float* y,
                       int64_t ldo, int64_t m, int64_t N, int64_t K, int64_t accumulate, int64_t store_y,
                       const void* const* staging_ptrs, const void* const* flag_ptrs, void* epoch, void* ticket,
                       int* status, int64_t rank, int64_t world, int64_t max_elems, int64_t max_spins, int64_t group, const float* Rin, float* Rout,
                       const float* post, const float* comb, const float* fn, float* acc, int64_t mix, float* part,
-                      int* part_n, cudaStream_t st) {
+                      int* part_n, const FbGemvArExt* ext, cudaStream_t st) {
     const bool fp8 = scales != nullptr;
     const int kb = fp8 ? 128 : 64;
-    if (m < 1 || m > 8 || (N % 4) || (K % kb) || (xs_ld % 8) || world > kMaxWorld || mix > kMaxMix ||
+    const bool swiglu = ext && ext->gu;
+    if (m < 1 || m > 8 || (N % 4) || (K % kb) || (!swiglu && (xs_ld % 8)) || world > kMaxWorld || mix > kMaxMix ||
         (world > 1 && m * N > max_elems) || (Rin && Rin == Rout))
         return (int)cudaErrorInvalidValue;
+    if (swiglu && ((ext->gu_ld % 4) || (ext->gu_up_off % 4) || ((uintptr_t)ext->gu % 16))) return (int)cudaErrorInvalidValue;
     ArPtrs t = {};
     for (int i = 0; i < world && world > 1; ++i) {
         t.staging[i] = (float*)staging_ptrs[i];
@@ -318,9 +554,20 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     HcFold hc{Rin, Rout, post, comb, fn, acc, (int)mix, part, part_n};
     if (Rin && fn && (!part || !part_n)) return (int)cudaErrorInvalidValue;
     if (Rin && (N % 32)) return (int)cudaErrorInvalidValue;  // the fold works on whole column tiles
+    XSrc xsrc{};
+    if (swiglu) xsrc = XSrc{ext->gu, (int)ext->gu_ld, (int)ext->gu_up_off, ext->limit};
+    HcPre pre{};
+    if (ext && ext->pre_scale) {
+        if (!Rin || !fn || mix < 8 || !ext->pre_base || !ext->pre_ln_w || !ext->pre_post || !ext->pre_comb || !ext->pre_x ||
+            !ext->gram || !ext->coef || !ext->bar)
+            return (int)cudaErrorInvalidValue;
+        pre = HcPre{ext->pre_scale, ext->pre_base, ext->pre_ln_w, ext->pre_post, ext->pre_comb, ext->pre_x,
+                    SplitBuf{(uint16_t*)ext->xs_base, (int)ext->xs_ld, (int)ext->xs_plane, (int)ext->xs_mask},
+                    ext->gram, ext->coef, (unsigned*)ext->bar, ext->rms_eps, ext->hc_eps, (int)ext->iters};
+    }
     const uint16_t* base = (const uint16_t*)xs;
-    const uint16_t* hi = base + (fp8 ? 2 * xs_plane : 0);
-    const uint16_t* lo = hi + xs_plane;
+    const uint16_t* hi = base ? base + (fp8 ? 2 * xs_plane : 0) : nullptr;
+    const uint16_t* lo = hi ? hi + xs_plane : nullptr;
     const int nkb = (int)(K / kb);
     const int t16 = (int)((N + 15) / 16);
     // tile shape: every CTA of the grid must be resident at once (148 SMs x CTAs per SM of the bounds)
@@ -330,16 +577,16 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     else if ((N + 31) / 32 <= 256) shape = 2;
     else return (int)cudaErrorInvalidValue;
 #define AR_ARGS (const uint8_t*)W, scales, hi, lo, (int)xs_ld, y, (int)ldo, (int)m, (int)N, (int)K, (int)accumulate, \
-                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)kMaxTiles, hc, g_fb_l2_ahead
-    if (fp8) {
-        if (shape == 0) launch_ar<1, 16, true>((int)N, st, AR_ARGS);
-        else if (shape == 1) launch_ar<1, 8, true>((int)N, st, AR_ARGS);
-        else launch_ar<2, 8, true>((int)N, st, AR_ARGS);
-    } else {
-        if (shape == 0) launch_ar<1, 16, false>((int)N, st, AR_ARGS);
-        else if (shape == 1) launch_ar<1, 8, false>((int)N, st, AR_ARGS);
-        else launch_ar<2, 8, false>((int)N, st, AR_ARGS);
-    }
+                (int)store_y, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank, (int)world, (int)max_elems, (int)max_spins, (int)kMaxTiles, hc, g_fb_l2_ahead, xsrc, pre
+#define AR_SHAPES(F8, SW)                                                       \
+    do {                                                                        \
+        if (shape == 0) launch_ar<1, 16, F8, SW>((int)N, st, AR_ARGS);          \
+        else if (shape == 1) launch_ar<1, 8, F8, SW>((int)N, st, AR_ARGS);      \
+        else launch_ar<2, 8, F8, SW>((int)N, st, AR_ARGS);                      \
+    } while (0)
+    if (fp8) { if (swiglu) AR_SHAPES(true, true); else AR_SHAPES(true, false); }
+    else { if (swiglu) AR_SHAPES(false, true); else AR_SHAPES(false, false); }
+#undef AR_SHAPES
 #undef AR_ARGS
     return FB_LAUNCH_CHECK();
 }

@@ -60,7 +60,7 @@ class KernelLib:
                 cargs.append(ctypes.c_int64(a))
             elif isinstance(a, float):
                 cargs.append(ctypes.c_float(a))
-            elif isinstance(a, (ctypes._SimpleCData, ctypes.Array)):
+            elif isinstance(a, (ctypes._SimpleCData, ctypes.Array, ctypes._Pointer)):
                 cargs.append(a)
             else:
                 raise TypeError(f"{name}: unsupported argument {type(a)}")

@@ -113,8 +113,16 @@ class GlmDeviceModel:
         self._tc_part = self._tc_ticket = None
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
-        self._fold_next = None   # (fn_next,) while a hyper-connection site's sublayer runs
+        self._fold_next = None   # (fn_next, front) while a hyper-connection site's sublayer runs; front = (scale,
+                                 # base, ln_w) of the NEXT site when its hc_pre can ride in the closing GEMV
         self._folded = False
+        self._pre_done = False   # the closing GEMV of the previous site already produced this site's x / post / comb
+        # sublayer-boundary fusion for decode rows (see csrc/kernels/gemv_ar.cu, gemv.cu, gdn.cu): next site's
+        # hyper-connection front, SwiGLU as the down projection's activation source, routing as the router GEMV's
+        # tail, the low-rank decay / gate projections inside the GatedDeltaNet kernel
+        self.fuse_front = self.fuse_fold and cfg.hc_mult == 4
+        self.fuse_small = mode != "off"
+        self.route_ticket = self.arena.take(1, "route.ticket")
         self.max_rows = max_rows
         self.n_slots = n_slots
         self.num_pages_arg = num_pages
@@ -488,12 +496,14 @@ class GlmDeviceModel:
             for r0 in range(0, n, step):   # the one-shot all-reduce takes a bounded payload per launch
                 self.allreduce(y[r0:min(n, r0 + step)])
 
-    def _out_gemv(self, w, x, n, N, K, ldx=None, scales=None, accumulate=False):
+    def _out_gemv(self, w, x, n, N, K, ldx=None, scales=None, accumulate=False, swiglu=None):
         """The GEMV that ends a sublayer: ws['y'] = x . w^T (+ ws['y']) summed over the ranks.  When
-        the fused kernel applies, the all-reduce and (inside a hyper-connection site) hc_post plus
-        the next site's mix dots ride in the same launch; otherwise GEMV and all-reduce run
-        separately and the caller's _hc_post_mix does the fold."""
-        ws = self.ws
+        the fused kernel applies, the all-reduce and (inside a hyper-connection site) hc_post, the
+        next site's mix dots and its whole hc_pre ride in the same launch; otherwise GEMV and
+        all-reduce run separately and the caller's _hc_post_mix / _hc_pre do the rest.
+        swiglu = (gu, ld, up_off): x = SwiGLU of the f32 [gate | up] rows `gu`; the fused kernel applies it
+        while it loads its activations, the fallback runs the SwiGLU kernel into `x` first."""
+        ws, cfg = self.ws, self.cfg
         fold, self._fold_next = self._fold_next, None
         if not self.fuse_fold:
             fold = None
@@ -502,7 +512,14 @@ class GlmDeviceModel:
         kb = 128 if scales is not None else 64
         ok = (self.fused is not None and xa is not None and xa.s is not None and n <= self.fused_rows and K % kb == 0
               and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or 8 * N <= self.fused.max_elems)
-              and (self.world > 1 or fold is not None))
+              and (self.world > 1 or fold is not None or (swiglu is not None and self.fuse_small)))
+        sw = None
+        if swiglu is not None:
+            gu, ldg, up_off = swiglu
+            if ok and self.fuse_small and ldg % 4 == 0 and up_off % 4 == 0 and gu.data_ptr() % 16 == 0:
+                sw = (gu, ldg, up_off, float(cfg.swiglu_limit))
+            else:
+                self.K.call("fb_swiglu_split", gu, ldg, xa.f, *xa.sp(3, ld=K), n, K, float(cfg.swiglu_limit))
         if not ok:
             gar = getattr(self.allreduce, "gemm_fused", None) if self.world > 1 else None
             if (gar is not None and scales is None and xa is not None and xa.s is not None and n >= self.tc_min_rows
@@ -513,30 +530,38 @@ class GlmDeviceModel:
             self.gemv(w, x, ws["y"], n, N, K, ldx=ldx, scales=scales, accumulate=accumulate)
             self._reduce(ws["y"], n)
             return
-        f = None
+        f = front = None
         if fold is not None:
-            cfg = self.cfg
             rin = ws["R"]
             rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
             f = (rin, rout, ws["post"], ws["comb"], fold[0], ws["hc_acc"], cfg.hc_mix)
             ws["R"] = rout
             self._folded = True
-        self.fused(w, scales, xa.s, ldx, xa.plane, ws["y"], N, n, N, K, accumulate,
-                   fold is None or self.debug_hook is not None, f)
+            nxt = fold[1] if len(fold) > 1 else None
+            if nxt is not None and fold[0] is not None and self.fuse_front and n <= 8 and N == cfg.hidden_size:
+                xo = ws["x"]
+                front = (nxt[0], nxt[1], nxt[2], ws["post"], ws["comb"], xo.f, xo.sp(3), float(cfg.rms_norm_eps),
+                         float(cfg.hc_eps), cfg.hc_sinkhorn_iters)
+                self._pre_done = True
+        self.fused(w, scales, None if sw is not None else xa.s, ldx, xa.plane, ws["y"], N, n, N, K, accumulate,
+                   fold is None or self.debug_hook is not None, f, swiglu=sw, front=front)
 
     # ------------------------------------------------------------------ sublayers
     def _attn_linear(self, L, rs: RowSet, snapshots: bool):
         cfg, la, ws, n = self.cfg, self.cfg.linear_attn, self.ws, rs.n
         H, P, r = cfg.hidden_size, self.P, la.low_rank
         proj = ws["gdn_proj"]
-        self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, omask=1)
-        self.gemv(L["fg_b"], proj, ws["gdn_fg"], n, 2 * P, r, group_rows=P, xcol=3 * P)
+        own_fg = self.fuse_small and rs.gsize_max <= 8 and r <= 128 and r % 16 == 0
+        self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, omask=0 if own_fg else 1)
+        if not own_fg:
+            self.gemv(L["fg_b"], proj, ws["gdn_fg"], n, 2 * P, r, group_rows=P, xcol=3 * P)
         gi = L["gdn_index"]
         core = ws["gdn_core"]
         self.K.call("fb_gdn_fused", proj.f, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"],
                     L["a_log"], L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
                     rs.group_first, rs.n_groups, core.f, P, self.h_gdn, la.head_dim, 3 * P + 2 * r,
-                    self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps), *core.sp(1))
+                    self.nbuf, int(snapshots), float(la.gate_lower_bound), float(cfg.rms_norm_eps), *core.sp(1),
+                    L["fg_b"] if own_fg else None, 3 * P, r, rs.gsize_max)
         self._out_gemv(L["o_proj"], core, n, H, P)
 
     def _attn_dsa(self, L, rs: RowSet):
@@ -587,9 +612,8 @@ class GlmDeviceModel:
         ldg = ws["gu"].shape[1]
         act = ws["act"]
         self.gemv(L["d13"], ws["x"], ws["gu"], n, 2 * I, H, ldo=ldg, scales=L.get("d13s"))
-        self.K.call("fb_swiglu_split", ws["gu"], ldg, act.f, *act.sp(3, ld=I), n, I, float(cfg.swiglu_limit))
-        # fb_swiglu packs rows with stride I in both the f32 and the split form
-        self._out_gemv(L["d2"], act, n, H, I, ldx=I, scales=L.get("d2s"))
+        # SwiGLU rides in the down projection's activation load (or runs as its own kernel, rows packed with stride I)
+        self._out_gemv(L["d2"], act, n, H, I, ldx=I, scales=L.get("d2s"), swiglu=(ws["gu"], ldg, I))
 
     def _ffn_moe(self, L, n):
         cfg, ws = self.cfg, self.ws
@@ -597,10 +621,19 @@ class GlmDeviceModel:
         Il, Is = L["I_moe"], L["I_shared"]
         ldl = ws["moe_lg"].shape[1]
         act, x = ws["act"], ws["x"]
-        self.gemv(L["gate_s13"], x, ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
-        # routing and the shared expert's SwiGLU read the same GEMV output row: one launch
-        self.K.call("fb_moe_route_swiglu", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
-                    float(cfg.routed_scaling_factor), act.f, *act.sp(1, ld=Is), Is, float(cfg.swiglu_limit))
+        tail = (self.fuse_small and n <= 8 and E <= 384 and H % 64 == 0 and x.ld % 8 == 0 and x.s is not None
+                and not self.tc_gemv_min_n)
+        if tail:
+            # router logits | shared gate | shared up in one GEMV whose last router CTA also routes the rows; the
+            # shared expert's SwiGLU is applied by its down projection (below)
+            self.K.call("fb_gemv_mma_bf16_route", L["gate_s13"], x.s, x.ld, x.plane, ws["moe_lg"], ldl, n, E + 2 * Is, H,
+                        L["gate_bias"], ws["moe_ids"], ws["moe_wts"], self.route_ticket, E, topk,
+                        float(cfg.routed_scaling_factor))
+        else:
+            self.gemv(L["gate_s13"], x, ws["moe_lg"], n, E + 2 * Is, H, ldo=ldl)  # router logits | shared gate|up
+            # routing and the shared expert's SwiGLU read the same GEMV output row: one launch
+            self.K.call("fb_moe_route_swiglu", ws["moe_lg"], ldl, L["gate_bias"], ws["moe_ids"], ws["moe_wts"], n, E, topk,
+                        float(cfg.routed_scaling_factor), act.f, *act.sp(1, ld=Is), Is, float(cfg.swiglu_limit))
         # routed experts write y, the shared expert's down projection adds to it and carries the
         # all-reduce (and the hyper-connection fold) in its epilogue
         if H % 128 == 0 and Il % 128 == 0 and n > self.moe_group_rows:
@@ -627,7 +660,8 @@ class GlmDeviceModel:
                         Il, H, self.e_lo, self.e_cnt, float(cfg.swiglu_limit))
             self.K.call("fb_moe_down_fp8", L["w2"], L["s2s"], ws["moe_act"], ws["moe_ids"], ws["moe_wts"], ws["y"],
                         H, n, topk, Il, H, self.e_lo, self.e_cnt, 0)
-        self._out_gemv(L["s2"], act, n, H, Is, ldx=Is, accumulate=True)
+        self._out_gemv(L["s2"], act, n, H, Is, ldx=Is, accumulate=True,
+                       swiglu=(View(ws["moe_lg"], E), ldl, Is) if tail else None)
 
     def _attn(self, L, rs, snapshots):
         if L["dsa"]:
@@ -644,6 +678,9 @@ class GlmDeviceModel:
     def _hc_pre(self, L, site, ln, n):
         """Coefficients + contraction + RMSNorm of one site; its mix dots are already in hc_acc."""
         cfg, ws = self.cfg, self.ws
+        if self._pre_done:   # the previous site's closing GEMV already left x, post and comb
+            self._pre_done = False
+            return
         x = ws["x"]
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
                     x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
@@ -683,14 +720,15 @@ class GlmDeviceModel:
         self._hc_post_mix(main[0]["hc_attn_fn"], n, first=True)
         for li, L in enumerate(main):
             self._hc_pre(L, "attn", L["ln1"], n)
-            self._fold_next = (L["hc_ffn_fn"],)
+            self._fold_next = (L["hc_ffn_fn"], (L["hc_ffn_scale"], L["hc_ffn_base"], L["ln2"]))
             self._attn(L, rs, snapshots)
             self._hc_post_mix(L["hc_ffn_fn"], n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "attn", ws, n)
             self._hc_pre(L, "ffn", L["ln2"], n)
-            fn_next = main[li + 1]["hc_attn_fn"] if li + 1 < len(main) else None
-            self._fold_next = (fn_next,)
+            nl = main[li + 1] if li + 1 < len(main) else None
+            fn_next = nl["hc_attn_fn"] if nl is not None else None
+            self._fold_next = (fn_next, (nl["hc_attn_scale"], nl["hc_attn_base"], nl["ln1"]) if nl is not None else None)
             self._ffn(L, n)
             self._hc_post_mix(fn_next, n)
             if self.debug_hook:

@@ -134,6 +134,21 @@ class P2PAllReduce(_Checked):
         self.flags.close()
 
 
+class _GemvArExt(ctypes.Structure):
+    """Optional stages of ``fb_gemv_ar`` (``FbGemvArExt`` in csrc/kernels/gemv_ar.cu)."""
+    _fields_ = [("gu", ctypes.c_void_p), ("gu_ld", ctypes.c_int64), ("gu_up_off", ctypes.c_int64), ("limit", ctypes.c_float),
+                ("pre_scale", ctypes.c_void_p), ("pre_base", ctypes.c_void_p), ("pre_ln_w", ctypes.c_void_p),
+                ("pre_post", ctypes.c_void_p), ("pre_comb", ctypes.c_void_p), ("pre_x", ctypes.c_void_p),
+                ("xs_base", ctypes.c_void_p), ("xs_ld", ctypes.c_int64), ("xs_plane", ctypes.c_int64),
+                ("xs_mask", ctypes.c_int64),
+                ("gram", ctypes.c_void_p), ("coef", ctypes.c_void_p), ("bar", ctypes.c_void_p),
+                ("rms_eps", ctypes.c_float), ("hc_eps", ctypes.c_float), ("iters", ctypes.c_int64)]
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
 class FusedGemvAllReduce(_Checked):
     """Row-parallel GEMV + all-reduce (+ hyper-connection fold) as one kernel launch
     (``csrc/kernels/gemv_ar.cu``).  With ``world == 1`` it needs no peer memory and only fuses
@@ -163,6 +178,10 @@ class FusedGemvAllReduce(_Checked):
         # GLM decode step: groups of 16 tiles 11.99 ms, 64 -> 11.31, 128 -> 11.02, whole grid -> 10.88), and one
         # group means one epoch per launch, so staging parity cannot alias between launches of different widths
         self.group = ar_group if ar_group > 0 else self.max_tiles
+        # hyper-connection front computed inside the launch: Gram partials, published coefficients, grid barrier
+        self.gram = torch.zeros(8 * 10 * self.max_tiles, dtype=torch.float32, device=device)
+        self.coef = torch.zeros(8 * 8, dtype=torch.float32, device=device)
+        self.bar = self.arena.take(2, "gemv_ar.front_barrier")
         self.staging = self.flags = None
         self._sp = self._fp = None
         if world > 1:
@@ -174,14 +193,32 @@ class FusedGemvAllReduce(_Checked):
         self.calls = 0
 
     def __call__(self, W, scales, xs_ptr, xs_ld: int, xs_plane: int, y, ldo: int, m: int, N: int, K: int,
-                 accumulate: bool, store_y: bool, fold=None):
+                 accumulate: bool, store_y: bool, fold=None, swiglu=None, front=None):
         """fold = (Rin, Rout, post, comb, fn_or_None, acc, mix) or None.  m may exceed 8 (up to part_rows):
-        the kernel then runs once per 8-row window on row-offset pointers."""
+        the kernel then runs once per 8-row window on row-offset pointers.
+        swiglu = (gu, ld, up_off, limit): read the activations as SwiGLU of f32 [gate | up] rows instead of split planes.
+        front = (scale, base, ln_w, post, comb, x_f32, (xs_base, xs_ld, xs_plane, xs_mask), rms_eps, hc_eps, iters):
+        compute the NEXT site's hyper-connection front in the same launch (needs the fold with fn; m <= 8)."""
         rin = rout = post = comb = fn = acc = None
         mix = 0
         if fold is not None:
             rin, rout, post, comb, fn, acc, mix = fold
         assert m <= self.part_rows
+        ext = None
+        if swiglu is not None or front is not None:
+            assert m <= 8
+            e = _GemvArExt()
+            if swiglu is not None:
+                gu, ld, up_off, limit = swiglu
+                e.gu, e.gu_ld, e.gu_up_off, e.limit = gu.data_ptr(), ld, up_off, limit
+            if front is not None:
+                scale, base, ln_w, fpost, fcomb, xf, xsp, rms_eps, hc_eps, iters = front
+                e.pre_scale, e.pre_base, e.pre_ln_w = scale.data_ptr(), base.data_ptr(), ln_w.data_ptr()
+                e.pre_post, e.pre_comb, e.pre_x = fpost.data_ptr(), fcomb.data_ptr(), xf.data_ptr()
+                e.xs_base, e.xs_ld, e.xs_plane, e.xs_mask = _p(xsp[0]), xsp[1], xsp[2], xsp[3]
+                e.gram, e.coef, e.bar = self.gram.data_ptr(), self.coef.data_ptr(), self.bar.data_ptr()
+                e.rms_eps, e.hc_eps, e.iters = rms_eps, hc_eps, iters
+            ext = ctypes.pointer(e)   # read by the launcher during the call only
 
         def off(t, elems, size=4):
             return None if t is None else ctypes.c_void_p(t.data_ptr() + elems * size)
@@ -192,7 +229,7 @@ class FusedGemvAllReduce(_Checked):
                         int(accumulate), int(store_y), self._sp, self._fp, self.epoch, self.ticket, self.status,
                         self.rank, self.world, self.max_elems, self.max_spins, self.group,
                         off(rin, r0 * 4 * N), off(rout, r0 * 4 * N), off(post, r0 * 4), off(comb, r0 * 16), fn,
-                        off(acc, r0 * 25), mix, off(self.part, r0 * 25 * self.max_tiles), off(self.part_n, r0))
+                        off(acc, r0 * 25), mix, off(self.part, r0 * 25 * self.max_tiles), off(self.part_n, r0), ext)
             self.calls += 1
 
     def partials(self):

@@ -207,7 +207,8 @@ def test_gdn_fused(K, dk, H, groups, nbuf, snap):
     sd, cd = dev(state.clone()), dev(conv_state.clone())
     out = torch.zeros(n, P, device="cuda")
     K.call("fb_gdn_fused", dev(proj), ld, dev(fb), dev(gb), P, dev(conv_w), dev(a_log), dev(dt_bias), dev(o_norm),
-           sd, cd, dev(cur), meta, gf, len(groups), out, P, H, dk, b_off, nbuf, snap, -5.0, 1e-5, None, 0, 0, 0)
+           sd, cd, dev(cur), meta, gf, len(groups), out, P, H, dk, b_off, nbuf, snap, -5.0, 1e-5, None, 0, 0, 0,
+           None, 0, 0, 0)
     r0 = 0
     for gi, g in enumerate(groups):
         c = int(cur[gi])
@@ -672,6 +673,109 @@ def test_gemv_ar_fold_single_rank(K, fp8):
     check("gemv_ar -> hc_pre post", po, pr, 5 * tol)
     check("gemv_ar -> hc_pre comb", co, cr.reshape(m, 16), 5 * tol)
     assert not part_n.any() and not acc.any()
+
+
+@pytest.mark.parametrize("fp8,N,Kd,m", [(False, 4096, 1024, 3), (True, 4096, 2048, 2), (False, 2048, 4096, 1)])
+def test_gemv_ar_swiglu_source_and_front(K, fp8, N, Kd, m):
+    """One launch: SwiGLU as the activation source + GEMV + hyper-connection fold + the NEXT site's hc_pre
+    (coefficients by the last CTA at a grid barrier, x from the Gram matrix), against the separate fp32 ops."""
+    from ferrite_b200.models.glm import Act
+    from ferrite_b200.parallel.symm import FusedGemvAllReduce
+    mix = 24
+    W = rnd(N, Kd, seed=1, scale=0.05)
+    gu = dev(rnd(8, 2 * Kd + 8, seed=2, scale=2.0))          # [gate | up] rows with a padded stride
+    act = R.swiglu_limited(gu[:m, :Kd].cpu(), gu[:m, Kd:2 * Kd].cpu(), 10.0)
+    Rin, y0 = dev(rnd(8, 4, N, seed=3)), dev(rnd(8, N, seed=4))
+    post, comb = dev(rnd(8, 4, seed=5).abs()), dev(rnd(8, 4, 4, seed=6).abs())
+    fn = dev(rnd(mix, 4 * N, seed=7, scale=0.02))
+    scale, base, ln = dev(rnd(3, seed=8).abs() + 0.5), dev(rnd(mix, seed=9, scale=0.3)), dev(rnd(N, seed=10).abs() + 0.5)
+    if fp8:
+        wq, ws_ = R.quant_fp8_block(W)
+        wdev, sdev, wref = wq.cuda(), ws_.cuda(), R.dequant_fp8_block(wq, ws_)
+    else:
+        wdev, sdev, wref = W.to(torch.bfloat16).cuda(), None, W.to(torch.bfloat16).float()
+    y = y0.clone()
+    Rout = torch.zeros_like(Rin)
+    acc = torch.zeros(8, 25, device="cuda")
+    xo = Act(torch.device("cuda"), 8, N)
+    npost, ncomb = torch.zeros(8, 4, device="cuda"), torch.zeros(8, 16, device="cuda")
+    f = FusedGemvAllReduce(torch.device("cuda"), 0, 1)
+    for rep in range(2):      # twice: the barrier's generation and arrival counters must re-arm
+        y.copy_(y0)
+        f(wdev, sdev, None, Kd, 0, y, N, m, N, Kd, True, True, (Rin, Rout, post, comb, fn, acc, mix),
+          swiglu=(gu, 2 * Kd + 8, Kd, 10.0),
+          front=(scale, base, ln, npost, ncomb, xo.f, xo.sp(3), 1e-5, 1e-6, 20))
+        torch.cuda.synchronize()
+        f.check()
+    want_y = act @ wref.t() + y0[:m].cpu()
+    tol = 3e-2 if fp8 else 2e-3
+    check("y", y[:m], want_y, tol * want_y.abs().max().item())
+    want_R = R.hc_post(want_y, Rin[:m].cpu(), post[:m].cpu(), comb[:m].cpu())
+    check("R'", Rout[:m], want_R, tol * want_R.abs().max().item())
+    # the front is checked against the fp32 statement applied to the DEVICE's R' (isolates it from the GEMV error)
+    xr, pr, cr = R.hc_pre(Rout[:m].cpu(), fn.cpu(), scale.cpu(), base.cpu(), 1e-5, 1e-6, 20)
+    xn = R.rmsnorm(xr, ln.cpu(), 1e-5)
+    check("front post", npost[:m], pr, 2e-4)
+    check("front comb", ncomb[:m], cr.reshape(m, 16), 2e-4)
+    check("front x", xo.f[:m], xn, 5e-4 * max(1.0, xn.abs().max().item()))
+    hi = xo.s[0, :m].view(torch.bfloat16).float() + xo.s[1, :m].view(torch.bfloat16).float()
+    check("front x split", hi, xn, 5e-4 * max(1.0, xn.abs().max().item()))
+    assert not xo.f[m:].any() and not npost[m:].any()
+
+
+def test_router_gemv_routes_in_its_tail(K):
+    """[router | shared gate | shared up] GEMV whose last router CTA also routes: ids / weights equal the
+    stand-alone route kernel run on the same logits."""
+    from ferrite_b200.models.glm import Act
+    n, E, Is, H, topk = 3, 288, 256, 1024, 8
+    W = (rnd(E + 2 * Is, H, seed=1, scale=0.05)).to(torch.bfloat16)
+    x = Act(torch.device("cuda"), 8, H)
+    x.f.copy_(dev(rnd(8, H, seed=2)))
+    K.call("fb_split_rows", x.f, H, *x.sp(3), 8, H)
+    bias = dev(rnd(E, seed=3, scale=0.1))
+    ldl = E + 2 * Is
+    lg = torch.zeros(8, ldl, device="cuda")
+    ids, wts = torch.zeros(8, topk, dtype=torch.int32, device="cuda"), torch.zeros(8, topk, device="cuda")
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for rep in range(2):
+        K.call("fb_gemv_mma_bf16_route", dev(W), x.s, H, x.plane, lg, ldl, n, ldl, H, bias, ids, wts, ticket, E, topk, 2.5)
+    torch.cuda.synchronize()
+    want = x.f[:n].cpu() @ W.float().t()
+    check("router gemv", lg[:n], want, 2e-3 * want.abs().max().item())
+    ids2, wts2 = torch.zeros_like(ids), torch.zeros_like(wts)
+    K.call("fb_moe_route", lg, ldl, bias, ids2, wts2, n, E, topk, 2.5)
+    assert torch.equal(ids[:n], ids2[:n]) and ticket.item() == 0
+    check("route w", wts[:n], wts2[:n].cpu(), 1e-6)
+    w_ref, i_ref = R.moe_route(lg[:n, :E].cpu(), bias.cpu(), topk, 2.5)
+    assert torch.equal(ids[:n].cpu().long(), i_ref)
+
+
+@pytest.mark.parametrize("dk,H,groups", [(128, 2, [3]), (64, 3, [1, 2])])
+def test_gdn_fused_applies_low_rank_projections(K, dk, H, groups):
+    """fb / gb computed inside the GatedDeltaNet kernel from f_a | g_a outputs == GEMV first, then the kernel."""
+    lr, P, n, S = 64, H * dk, sum(groups), len(groups)
+    ld = 3 * P + 2 * lr + H
+    ld += (-ld) % 4
+    b_off = 3 * P + 2 * lr
+    proj = rnd(n, ld, seed=1)
+    fgw = (rnd(2 * P, lr, seed=2, scale=0.2)).to(torch.bfloat16)
+    fa, ga = proj[:, 3 * P:3 * P + lr], proj[:, 3 * P + lr:3 * P + 2 * lr]
+    fb, gb = fa @ fgw[:P].float().t(), ga @ fgw[P:].float().t()
+    conv_w = rnd(3 * P, 4, seed=4, scale=0.5)
+    a_log, dt_bias, o_norm = rnd(H, seed=5, scale=0.3), rnd(P, seed=6, scale=0.3), rnd(dk, seed=7).abs() + 0.5
+    state, conv_state = rnd(S, 1, H, dk, dk, seed=8, scale=0.2), rnd(S, 1, 3 * P, 3, seed=9)
+    cur = torch.zeros(S, dtype=torch.int32)
+    meta, gf, _, _ = make_meta(K, list(range(S)), groups, [10] * S)
+    outs = []
+    for own in (False, True):
+        sd, cd = dev(state.clone()), dev(conv_state.clone())
+        out = torch.zeros(n, P, device="cuda")
+        K.call("fb_gdn_fused", dev(proj), ld, dev(fb), dev(gb), P, dev(conv_w), dev(a_log), dev(dt_bias), dev(o_norm),
+               sd, cd, dev(cur), meta, gf, S, out, P, H, dk, b_off, 1, 0, -5.0, 1e-5, None, 0, 0, 0,
+               dev(fgw) if own else None, 3 * P, lr, max(groups))
+        outs.append((out, sd))
+    check("gdn own-fg out", outs[1][0], outs[0][0].cpu(), 1e-4)
+    check("gdn own-fg state", outs[1][1], outs[0][1].cpu(), 1e-4)
 
 
 def test_bounded_wait_reports_timeout_and_context_survives(K):
