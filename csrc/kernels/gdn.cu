@@ -78,21 +78,30 @@ gdn_fused_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
     const float qscale = rsqrtf((float)DK);
     const bool own_fg = fgw != nullptr;   // host guarantees gsize <= kFgRows and lr <= kLrMax then
     if (own_fg) {
-        for (int i = tid; i < gsize * 2 * lr; i += blockDim.x) {
-            const int rr = i / (2 * lr), k = i % (2 * lr);
-            fin_s[rr][k] = proj[(size_t)(row0 + rr) * ld_proj + fa_off + k];
-        }
-        __syncthreads();
         // two adjacent lanes share an output channel, each takes half of the low-rank dimension
         const int o = tid >> 1, half = tid & 1;          // o in [0, 2 DK): f channels then g channels
         const int isg = o / DK, e = o % DK;
         const int kh = lr / 2;
         const __nv_bfloat16* wrow = fgw + ((size_t)isg * P + (size_t)h * DK + e) * lr + half * kh;
+        // this thread's weights (constant: may be read before the previous kernel's output) go in flight first,
+        // then the rows' f_a | g_a outputs are staged
+        constexpr int KV = kLrMax / 16;   // 16-byte weight loads per thread
+        uint4 wv[KV];
+#pragma unroll
+        for (int j = 0; j < KV; ++j) wv[j] = (8 * j < kh) ? ldg_nc_v4(wrow + 8 * j) : make_uint4(0u, 0u, 0u, 0u);
+        for (int i = tid; i < gsize * 2 * lr; i += blockDim.x) {
+            const int rr = i / (2 * lr), k = i % (2 * lr);
+            fin_s[rr][k] = proj[(size_t)(row0 + rr) * ld_proj + fa_off + k];
+        }
+        __syncthreads();
         float acc[kFgRows];
 #pragma unroll
         for (int rr = 0; rr < kFgRows; ++rr) acc[rr] = 0.f;
-        for (int k = 0; k < kh; k += 8) {
-            const uint4 w4 = ldg_nc_v4(wrow + k);
+#pragma unroll
+        for (int kj = 0; kj < KV; ++kj) {
+            const int k = 8 * kj;
+            if (k >= kh) break;
+            const uint4 w4 = wv[kj];
             const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
             float wf[8];
 #pragma unroll

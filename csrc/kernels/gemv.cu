@@ -234,26 +234,27 @@ __device__ __forceinline__ uint32_t route_okey(float f) {
     const uint32_t u = __float_as_uint(f);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-__device__ __forceinline__ float ld_cg(const float* p) {
-    float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
 
 constexpr int kRouteKeys = 12;   // experts per lane: E <= 384
 
 __device__ __noinline__ void route_row_warp(const float* __restrict__ logits, const RouteTail& rt, int row, int lane) {
     unsigned long long key[kRouteKeys];
-    float sig[kRouteKeys];
+    float sig[kRouteKeys], lg[kRouteKeys], bs[kRouteKeys];
+#pragma unroll
+    for (int i = 0; i < kRouteKeys; ++i) {   // every load in flight before the first use (L2 reads: other CTAs wrote them)
+        const int e = lane + 32 * i;
+        lg[i] = e < rt.E ? __ldcg(logits + e) : 0.f;
+        bs[i] = e < rt.E ? __ldg(rt.bias + e) : 0.f;
+    }
 #pragma unroll
     for (int i = 0; i < kRouteKeys; ++i) {
         const int e = lane + 32 * i;
         key[i] = 0ull;
         sig[i] = 0.f;
         if (e < rt.E) {
-            const float sv = 1.f / (1.f + expf(-ld_cg(logits + e)));
+            const float sv = 1.f / (1.f + expf(-lg[i]));
             sig[i] = sv;
-            key[i] = ((unsigned long long)route_okey(sv + rt.bias[e]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)e);
+            key[i] = ((unsigned long long)route_okey(sv + bs[i]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)e);
         }
     }
     float my_s = 0.f;

@@ -376,7 +376,6 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
     }
     __shared__ int s_last;
     __shared__ float s_sum[8][kMaxMix + 1 + kGram];
-    __shared__ float s_chunk[NW * 32];
     __shared__ float s_coef[8][8];
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -385,37 +384,42 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
     }
     __syncthreads();
     const int nt = gridDim.x;
-    // sums tile partials of NQ quantities per row, in a fixed order: thread (pair, chunk) adds its tiles, then one
-    // thread per pair adds the chunks.  sel(q): index of the q-th quantity in [0, kMaxMix] (mix / sum of squares) or
-    // kMaxMix + 1 + p (Gram pair p).
-    auto reduce_parts = [&](int q0, int nq, auto sel) {
-        const int npairs = mrows * nq;
-        const int chunks = max(1, (int)blockDim.x / npairs);
-        for (int base = 0; base < npairs; base += blockDim.x / chunks) {
-            const int pr = base + threadIdx.x / chunks, ck = threadIdx.x % chunks;
-            float a = 0.f;
-            if (pr < npairs && (int)threadIdx.x < (int)(blockDim.x / chunks) * chunks) {
-                const int mm = pr / nq, qi = sel(q0 + pr % nq);
-                const float* src = qi <= kMaxMix ? hc.part + ((size_t)mm * (kMaxMix + 1) + qi) * kMaxTiles
-                                                 : pre.gram + ((size_t)mm * kGram + (qi - kMaxMix - 1)) * kMaxTiles;
-                const int per = (nt + chunks - 1) / chunks;
-                const int t0 = ck * per, t1 = min(nt, t0 + per);
-                for (int tt = t0; tt < t1; ++tt) a += ld_cg_f32(src + tt);
+    // Sums the tiles' partials of nq quantities per row in a fixed order: one warp per (row, quantity), every lane
+    // loads its tiles (lane, lane + 32, ...) with all loads in flight before the first add, then a shuffle tree.
+    // Two pairs per warp iteration keep twice as many loads in flight.  sel(q): index of the q-th quantity in
+    // [0, kMaxMix] (mix dot / sum of squares) or kMaxMix + 1 + p (Gram pair p).
+    auto part_src = [&](int mm, int qi) -> const float* {
+        return qi <= kMaxMix ? hc.part + ((size_t)mm * (kMaxMix + 1) + qi) * kMaxTiles
+                             : pre.gram + ((size_t)mm * kGram + (qi - kMaxMix - 1)) * kMaxTiles;
+    };
+    auto reduce_parts = [&](int row0, int nrows, int q0, int nq, auto sel) {
+        const int npairs = nrows * nq;
+        constexpr int TPL = kMaxTiles / 32;   // tiles per lane
+        for (int pr = warp * 2; pr < npairs; pr += NW * 2) {
+            float v[2][TPL];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int p = min(pr + u, npairs - 1);
+                const float* src = part_src(row0 + p / nq, sel(q0 + p % nq));
+#pragma unroll
+                for (int j = 0; j < TPL; ++j) v[u][j] = (lane + 32 * j < nt) ? __ldcg(src + lane + 32 * j) : 0.f;
             }
-            s_chunk[threadIdx.x] = a;
-            __syncthreads();
-            if (ck == 0 && pr < npairs && (int)threadIdx.x < (int)(blockDim.x / chunks) * chunks) {
-                float tot = 0.f;
-                for (int c = 0; c < chunks; ++c) tot += s_chunk[threadIdx.x + c];
-                s_sum[pr / nq][sel(q0 + pr % nq)] = tot;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < TPL; ++j) a += v[u][j];
+                a = warp_sum(a);
+                const int p = pr + u;
+                if (lane == 0 && p < npairs) s_sum[row0 + p / nq][sel(q0 + p % nq)] = a;
             }
-            __syncthreads();
         }
+        __syncthreads();
     };
     if (s_last) {
         __threadfence();
         // phase 1: what x needs: mix dots 0..3, the sum of squares, the Gram matrix
-        reduce_parts(0, 5 + kGram, [&](int q) { return q < 4 ? q : (q == 4 ? kMaxMix : kMaxMix + 1 + (q - 5)); });
+        reduce_parts(0, mrows, 0, 5 + kGram, [&](int q) { return q < 4 ? q : (q == 4 ? kMaxMix : kMaxMix + 1 + (q - 5)); });
         if (threadIdx.x < mrows) {
             const int mm = threadIdx.x;
             const float rr = rsqrtf(s_sum[mm][kMaxMix] / (float)(4 * N) + pre.rms_eps);
@@ -432,7 +436,7 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
 #pragma unroll
             for (int i = 0; i < 4; ++i) { s_coef[mm][i] = pw[i]; pre.coef[mm * 8 + i] = pw[i]; }
             s_coef[mm][4] = inv; pre.coef[mm * 8 + 4] = inv;
-            s_coef[mm][5] = rr;
+            s_coef[mm][5] = rr; pre.coef[mm * 8 + 5] = rr;
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -465,11 +469,13 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         pre.x[(size_t)m * N + n0 + nl] = o;
         split_store(pre.xs, m, n0 + nl, o);
     }
-    if (!s_last) return;
-    // phase 2 (off the critical path: only the next fold reads it): post and comb of the next site
-    reduce_parts(4, hc.mix - 4, [&](int q) { return q; });
-    if (warp < mrows) {
-        const int mm = warp;
+    // phase 2 (only the next fold reads it): post and comb of the next site, row r by CTA r, side by side with the
+    // other CTAs' x tiles
+    if ((int)blockIdx.x >= mrows) return;
+    __syncthreads();
+    reduce_parts(blockIdx.x, 1, 4, hc.mix - 4, [&](int q) { return q; });
+    if (warp == 0) {
+        const int mm = blockIdx.x;
         const float rr = s_coef[mm][5];
         const float* a = s_sum[mm];
         if (lane < 4) pre.post[mm * 4 + lane] = 2.f * sigmoidf_(a[4 + lane] * rr * pre.scale[1] + pre.base[4 + lane]);
@@ -558,7 +564,7 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     if (swiglu) xsrc = XSrc{ext->gu, (int)ext->gu_ld, (int)ext->gu_up_off, ext->limit};
     HcPre pre{};
     if (ext && ext->pre_scale) {
-        if (!Rin || !fn || mix < 8 || !ext->pre_base || !ext->pre_ln_w || !ext->pre_post || !ext->pre_comb || !ext->pre_x ||
+        if (N < 512 /* one CTA per row finishes post / comb */ || !Rin || !fn || mix < 8 || !ext->pre_base || !ext->pre_ln_w || !ext->pre_post || !ext->pre_comb || !ext->pre_x ||
             !ext->gram || !ext->coef || !ext->bar)
             return (int)cudaErrorInvalidValue;
         pre = HcPre{ext->pre_scale, ext->pre_base, ext->pre_ln_w, ext->pre_post, ext->pre_comb, ext->pre_x,
