@@ -358,12 +358,11 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
             if (lane == 0) hc.part[((size_t)mm * (kMaxMix + 1) + (q < hc.mix ? q : kMaxMix)) * kMaxTiles + tl] = d;
         }
     }
-    if (!front) {
-        if (blockIdx.x == 0 && threadIdx.x < mrows) hc.part_n[threadIdx.x] = gridDim.x;
-        return;
-    }
+    if (!front && blockIdx.x == 0 && threadIdx.x < mrows) hc.part_n[threadIdx.x] = gridDim.x;
+    if (!pre.gram) return;
     // ---- hyper-connection front of the next site ------------------------------------------------------------
-    // Gram partials of this tile: pair p = (i, j), i <= j, one warp per (row, pair)
+    // Gram partials of this tile: pair p = (i, j), i <= j, one warp per (row, pair).  With them the consumer gets
+    // |x|^2 of x = sum_i pre_i R'_i as sum_ij pre_i pre_j G_ij, i.e. the RMSNorm of x needs no pass over x.
     for (int w = warp; w < mrows * kGram; w += NW) {
         const int mm = w / kGram, p = w % kGram;
         int i = 0, rem = p;
@@ -374,6 +373,7 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
         d = warp_sum(d);
         if (lane == 0) pre.gram[((size_t)mm * kGram + p) * kMaxTiles + tl] = d;
     }
+    if (!front) return;   // the column-parallel front kernel (fb_hc_pre_wide) consumes the partials
     __shared__ int s_last;
     __shared__ float s_sum[8][kMaxMix + 1 + kGram];
     __shared__ float s_coef[8][8];
@@ -563,6 +563,10 @@ FB_API int fb_gemv_ar(const void* W, const float* scales, const void* xs, int64_
     XSrc xsrc{};
     if (swiglu) xsrc = XSrc{ext->gu, (int)ext->gu_ld, (int)ext->gu_up_off, ext->limit};
     HcPre pre{};
+    if (ext && ext->gram && !ext->pre_scale) {   // Gram partials only
+        if (!Rin || !fn) return (int)cudaErrorInvalidValue;
+        pre.gram = ext->gram;
+    }
     if (ext && ext->pre_scale) {
         if (N < 512 /* one CTA per row finishes post / comb */ || !Rin || !fn || mix < 8 || !ext->pre_base || !ext->pre_ln_w || !ext->pre_post || !ext->pre_comb || !ext->pre_x ||
             !ext->gram || !ext->coef || !ext->bar)

@@ -316,6 +316,111 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
     }
 }
 
+// Column-parallel hyper-connection front for decode rows, fed by the per-tile partials the fused GEMV + fold kernel
+// leaves (24 mix dots, the sum of squares and the 10 Gram dots <R_i, R_j> per tile):
+//   CTA (c, r), c < nx : columns [512 c, 512 c + 512) of row r.  15 warps sum one quantity each over the tiles
+//                         (all loads in flight, fixed order), every thread derives pre_i = sigmoid(mix_i r s0 + b_i)
+//                         + eps and the RMS factor of x from the Gram matrix (|x|^2 = sum_ij pre_i pre_j G_ij), and
+//                         writes its column of x = rmsnorm(sum_i pre_i R_i) * w in f32 and split form;
+//   CTA (nx, r)         : post and comb of row r (softmax + Sinkhorn), which only the next fold reads, side by side
+//                         with the x CTAs.
+// No CTA waits for another one, and the serial part (Sinkhorn) is off the path to x.
+constexpr int kWideCols = 512;
+constexpr int kGramPairs = 10;
+
+__device__ __forceinline__ float tile_sum(const float* __restrict__ src, int nt, int lane) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = (lane + 32 * j < nt) ? __ldcg(src + lane + 32 * j) : 0.f;
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a += v[j];
+    return warp_sum(a);
+}
+
+__global__ void __launch_bounds__(kWideCols)
+hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, const float* __restrict__ gram,
+                   const int* __restrict__ part_n, int part_ld, const float* __restrict__ scale,
+                   const float* __restrict__ base, const float* __restrict__ ln_w, float* __restrict__ xn_out,
+                   float* __restrict__ post_out, float* __restrict__ comb_out, int H, int mix, float rms_eps,
+                   float hc_eps, int iters, SplitBuf osp) {
+    PDL_PROLOGUE();
+    __shared__ float s_sum[kMaxMix + 1 + kGramPairs];
+    const int r = blockIdx.y, nx = gridDim.x - 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nt = min(part_n[r], 512);
+    const float* prow = part + (size_t)r * (kMaxMix + 1) * part_ld;
+    const float* grow = gram + (size_t)r * kGramPairs * part_ld;
+    if ((int)blockIdx.x == nx) {
+        // ---- coefficient CTA: all 24 mix dots + the sum of squares, then post / comb ----
+        for (int q = warp; q <= mix; q += kWideCols / 32) {
+            const int qi = q < mix ? q : kMaxMix;
+            const float v = tile_sum(prow + (size_t)qi * part_ld, nt, lane);
+            if (lane == 0) s_sum[qi] = v;
+        }
+        __syncthreads();
+        if (warp != 0) return;
+        const float rr = rsqrtf(s_sum[kMaxMix] / (float)(4 * H) + rms_eps);
+        if (lane < 4) post_out[(size_t)r * 4 + lane] = 2.f * sigmoidf_(s_sum[4 + lane] * rr * scale[1] + base[4 + lane]);
+        float c = 0.f;
+        const bool on = lane < 16;
+        if (on) c = s_sum[8 + lane] * rr * scale[2] + base[8 + lane];
+        float mx = on ? c : -INFINITY;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float e = on ? __expf(c - mx) : 0.f;
+        float den = e + __shfl_xor_sync(0xffffffffu, e, 1);
+        den += __shfl_xor_sync(0xffffffffu, den, 2);
+        c = on ? e / den + hc_eps : 0.f;
+        float cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        c = __fdividef(c, cs + hc_eps);
+        for (int it = 1; it < iters; ++it) {
+            float rs = c + __shfl_xor_sync(0xffffffffu, c, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            c = __fdividef(c, rs + hc_eps);
+            cs = c + __shfl_xor_sync(0xffffffffu, c, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            c = __fdividef(c, cs + hc_eps);
+        }
+        if (on) comb_out[(size_t)r * 16 + lane] = c;
+        return;
+    }
+    // ---- x CTA ----
+    const int j = blockIdx.x * kWideCols + threadIdx.x;
+    const bool act = j < H;
+    float rv[4] = {0.f, 0.f, 0.f, 0.f};
+    float lw = 0.f;
+    if (act) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) rv[k] = R[((size_t)r * 4 + k) * H + j];
+        lw = __ldg(ln_w + j);
+    }
+    if (warp < 5 + kGramPairs) {   // mix dots 0..3, the sum of squares, the Gram pairs
+        const float* src = warp < 4 ? prow + (size_t)warp * part_ld
+                                    : (warp == 4 ? prow + (size_t)kMaxMix * part_ld : grow + (size_t)(warp - 5) * part_ld);
+        const float v = tile_sum(src, nt, lane);
+        if (lane == 0) s_sum[warp < 4 ? warp : (warp == 4 ? kMaxMix : kMaxMix + 1 + (warp - 5))] = v;
+    }
+    __syncthreads();
+    const float rr = rsqrtf(s_sum[kMaxMix] / (float)(4 * H) + rms_eps);
+    float pw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(s_sum[i] * rr * scale[0] + base[i]) + hc_eps;
+    float xss = 0.f;
+    int p = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = i; k < 4; ++k, ++p) xss += (i == k ? 1.f : 2.f) * pw[i] * pw[k] * s_sum[kMaxMix + 1 + p];
+    const float inv = rsqrtf(fmaxf(xss, 0.f) / (float)H + rms_eps);
+    if (act) {
+        const float o = (pw[0] * rv[0] + pw[1] * rv[1] + pw[2] * rv[2] + pw[3] * rv[3]) * inv * lw;
+        xn_out[(size_t)r * H + j] = o;
+        split_store(osp, r, j, o);
+    }
+}
+
 // h_final = mean_i R_i ; xn = rmsnorm(h_final) * w
 __global__ void hc_head_kernel(const float* __restrict__ R, const float* __restrict__ w,
                                float* __restrict__ h_final, float* __restrict__ xn, int H, int n, float eps,
@@ -417,6 +522,20 @@ FB_API int fb_hc_pre_apply(const float* R, float* acc, const float* scale, const
     if (nct + 32 > 1024) return (int)cudaErrorInvalidValue;
     FB_LAUNCH((hc_pre_apply_kernel), n, nct + 32, 0, st, R, acc, scale, base, ln_w, x_out, xn_out, post_out, comb_out,
                                                (int)H, (int)mult, rms_eps, hc_eps, (int)iters, osp, part, part_n, (int)part_ld);
+    return FB_LAUNCH_CHECK();
+}
+
+// Decode-row front from the partials of fb_gemv_ar (part: [n][25][part_ld], gram: [n][10][part_ld], part_n[r] tiles;
+// none of them is modified).  n <= 8 rows, mult == 4, at most 512 tiles.
+FB_API int fb_hc_pre_wide(const float* R, const float* part, const float* gram, const int* part_n, int64_t part_ld,
+                          const float* scale, const float* base, const float* ln_w, float* xn_out, float* post_out,
+                          float* comb_out, int64_t n, int64_t H, int64_t mix, float rms_eps, float hc_eps, int64_t iters,
+                          void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    if (n < 1 || n > 8 || mix > kMaxMix || mix < 24 || !part || !gram || !part_n) return (int)cudaErrorInvalidValue;
+    const unsigned nx = (unsigned)((H + kWideCols - 1) / kWideCols);
+    FB_LAUNCH((hc_pre_wide_kernel), dim3(nx + 1, (unsigned)n), kWideCols, 0, st, R, part, gram, part_n, (int)part_ld, scale,
+              base, ln_w, xn_out, post_out, comb_out, (int)H, (int)mix, rms_eps, hc_eps, (int)iters, osp);
     return FB_LAUNCH_CHECK();
 }
 

@@ -117,11 +117,16 @@ class GlmDeviceModel:
                                  # base, ln_w) of the NEXT site when its hc_pre can ride in the closing GEMV
         self._folded = False
         self._pre_done = False   # the closing GEMV of the previous site already produced this site's x / post / comb
+        self._wide_ready = False  # ... or left the partials (mix dots + Gram) for the column-parallel front kernel
         # sublayer-boundary fusion for decode rows (see csrc/kernels/gemv_ar.cu, gemv.cu, gdn.cu): next site's
         # hyper-connection front, SwiGLU as the down projection's activation source, routing as the router GEMV's
         # tail, the low-rank decay / gate projections inside the GatedDeltaNet kernel
-        self.fuse_front = self.fuse_fold and cfg.hc_mult == 4
-        self.fuse_small = mode != "off"
+        sw = switches()
+        self.fuse_front = self.fuse_fold and cfg.hc_mult == 4 and sw.fuse_front
+        self.fuse_route = mode != "off" and sw.fuse_route
+        self.fuse_swiglu = mode != "off" and sw.fuse_swiglu
+        self.gdn_own_fg = sw.gdn_own_fg
+        self.hc_pre_wide = self.fuse_fold and cfg.hc_mult == 4 and sw.hc_pre_wide and not self.fuse_front
         self.route_ticket = self.arena.take(1, "route.ticket")
         self.max_rows = max_rows
         self.n_slots = n_slots
@@ -512,11 +517,11 @@ class GlmDeviceModel:
         kb = 128 if scales is not None else 64
         ok = (self.fused is not None and xa is not None and xa.s is not None and n <= self.fused_rows and K % kb == 0
               and ldx % 8 == 0 and N % 4 == 0 and (self.world == 1 or 8 * N <= self.fused.max_elems)
-              and (self.world > 1 or fold is not None or (swiglu is not None and self.fuse_small)))
+              and (self.world > 1 or fold is not None or (swiglu is not None and self.fuse_swiglu)))
         sw = None
         if swiglu is not None:
             gu, ldg, up_off = swiglu
-            if ok and self.fuse_small and ldg % 4 == 0 and up_off % 4 == 0 and gu.data_ptr() % 16 == 0:
+            if ok and self.fuse_swiglu and ldg % 4 == 0 and up_off % 4 == 0 and gu.data_ptr() % 16 == 0:
                 sw = (gu, ldg, up_off, float(cfg.swiglu_limit))
             else:
                 self.K.call("fb_swiglu_split", gu, ldg, xa.f, *xa.sp(3, ld=K), n, K, float(cfg.swiglu_limit))
@@ -531,6 +536,7 @@ class GlmDeviceModel:
             self._reduce(ws["y"], n)
             return
         f = front = None
+        want_gram = False
         if fold is not None:
             rin = ws["R"]
             rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
@@ -543,15 +549,17 @@ class GlmDeviceModel:
                 front = (nxt[0], nxt[1], nxt[2], ws["post"], ws["comb"], xo.f, xo.sp(3), float(cfg.rms_norm_eps),
                          float(cfg.hc_eps), cfg.hc_sinkhorn_iters)
                 self._pre_done = True
+            elif fold[0] is not None and self.hc_pre_wide and n <= 8 and N == cfg.hidden_size and N // 16 <= 512:
+                self._wide_ready = want_gram = True
         self.fused(w, scales, None if sw is not None else xa.s, ldx, xa.plane, ws["y"], N, n, N, K, accumulate,
-                   fold is None or self.debug_hook is not None, f, swiglu=sw, front=front)
+                   fold is None or self.debug_hook is not None, f, swiglu=sw, front=front, gram=want_gram)
 
     # ------------------------------------------------------------------ sublayers
     def _attn_linear(self, L, rs: RowSet, snapshots: bool):
         cfg, la, ws, n = self.cfg, self.cfg.linear_attn, self.ws, rs.n
         H, P, r = cfg.hidden_size, self.P, la.low_rank
         proj = ws["gdn_proj"]
-        own_fg = self.fuse_small and rs.gsize_max <= 8 and r <= 128 and r % 16 == 0
+        own_fg = self.gdn_own_fg and rs.gsize_max <= 8 and r <= 128 and r % 16 == 0
         self.gemv(L["w_in"], ws["x"], proj, n, L["w_in"].shape[0], H, omask=0 if own_fg else 1)
         if not own_fg:
             self.gemv(L["fg_b"], proj, ws["gdn_fg"], n, 2 * P, r, group_rows=P, xcol=3 * P)
@@ -621,7 +629,7 @@ class GlmDeviceModel:
         Il, Is = L["I_moe"], L["I_shared"]
         ldl = ws["moe_lg"].shape[1]
         act, x = ws["act"], ws["x"]
-        tail = (self.fuse_small and n <= 8 and E <= 384 and H % 64 == 0 and x.ld % 8 == 0 and x.s is not None
+        tail = (self.fuse_route and n <= 8 and E <= 384 and H % 64 == 0 and x.ld % 8 == 0 and x.s is not None
                 and not self.tc_gemv_min_n)
         if tail:
             # router logits | shared gate | shared up in one GEMV whose last router CTA also routes the rows; the
@@ -675,17 +683,26 @@ class GlmDeviceModel:
         else:
             self._ffn_dense(L, n)
 
-    def _hc_pre(self, L, site, ln, n):
+    def _hc_pre(self, L, site, ln, n, first=False):
         """Coefficients + contraction + RMSNorm of one site; its mix dots are already in hc_acc."""
         cfg, ws = self.cfg, self.ws
         if self._pre_done:   # the previous site's closing GEMV already left x, post and comb
             self._pre_done = False
             return
         x = ws["x"]
+        if self._wide_ready:   # partials (mix dots, sum of squares, Gram) are waiting: column-parallel front
+            self._wide_ready = False
+            part, gram, part_n, ld = self.fused.wide_partials()
+            self.K.call("fb_hc_pre_wide", ws["R"], part, gram, part_n, ld, L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln,
+                        x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mix, float(cfg.rms_norm_eps),
+                        float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3))
+            return
+        # the first site of a forward has no producer: its mix dots are in hc_acc, never in the partial buffers
         self.K.call("fb_hc_pre_apply", ws["R"], ws["hc_acc"], L[f"hc_{site}_scale"], L[f"hc_{site}_base"], ln, None,
                     x.f, ws["post"], ws["comb"], n, cfg.hidden_size, cfg.hc_mult, float(cfg.rms_norm_eps),
                     float(cfg.hc_eps), cfg.hc_sinkhorn_iters, *x.sp(3),
-                    *(self.fused.partials() if self.fused is not None and n <= self.fused_rows else (None, None, 0)))
+                    *(self.fused.partials() if self.fused is not None and n <= self.fused_rows and not first
+                      else (None, None, 0)))
 
     def _hc_post_mix(self, fn_next, n, first=False):
         """hc_post of the finished site fused with the mix dots of the next one; the residual
@@ -719,7 +736,7 @@ class GlmDeviceModel:
         main = self.layers[:cfg.num_layers]
         self._hc_post_mix(main[0]["hc_attn_fn"], n, first=True)
         for li, L in enumerate(main):
-            self._hc_pre(L, "attn", L["ln1"], n)
+            self._hc_pre(L, "attn", L["ln1"], n, first=(li == 0))
             self._fold_next = (L["hc_ffn_fn"], (L["hc_ffn_scale"], L["hc_ffn_base"], L["ln2"]))
             self._attn(L, rs, snapshots)
             self._hc_post_mix(L["hc_ffn_fn"], n)

@@ -193,21 +193,24 @@ class FusedGemvAllReduce(_Checked):
         self.calls = 0
 
     def __call__(self, W, scales, xs_ptr, xs_ld: int, xs_plane: int, y, ldo: int, m: int, N: int, K: int,
-                 accumulate: bool, store_y: bool, fold=None, swiglu=None, front=None):
+                 accumulate: bool, store_y: bool, fold=None, swiglu=None, front=None, gram: bool = False):
         """fold = (Rin, Rout, post, comb, fn_or_None, acc, mix) or None.  m may exceed 8 (up to part_rows):
         the kernel then runs once per 8-row window on row-offset pointers.
         swiglu = (gu, ld, up_off, limit): read the activations as SwiGLU of f32 [gate | up] rows instead of split planes.
         front = (scale, base, ln_w, post, comb, x_f32, (xs_base, xs_ld, xs_plane, xs_mask), rms_eps, hc_eps, iters):
-        compute the NEXT site's hyper-connection front in the same launch (needs the fold with fn; m <= 8)."""
+        compute the NEXT site's hyper-connection front in the same launch (needs the fold with fn; m <= 8).
+        gram: also leave the per-tile Gram partials of R' (for fb_hc_pre_wide; needs the fold with fn; m <= 8)."""
         rin = rout = post = comb = fn = acc = None
         mix = 0
         if fold is not None:
             rin, rout, post, comb, fn, acc, mix = fold
         assert m <= self.part_rows
         ext = None
-        if swiglu is not None or front is not None:
+        if swiglu is not None or front is not None or gram:
             assert m <= 8
             e = _GemvArExt()
+            if gram:
+                e.gram = self.gram.data_ptr()
             if swiglu is not None:
                 gu, ld, up_off, limit = swiglu
                 e.gu, e.gu_ld, e.gu_up_off, e.limit = gu.data_ptr(), ld, up_off, limit
@@ -235,6 +238,10 @@ class FusedGemvAllReduce(_Checked):
     def partials(self):
         """(part, part_n, part_ld) arguments for the hc_pre kernel that consumes the mix-dot partials."""
         return (self.part, self.part_n, self.max_tiles)
+
+    def wide_partials(self):
+        """(part, gram, part_n, part_ld) arguments for fb_hc_pre_wide."""
+        return (self.part, self.gram, self.part_n, self.max_tiles)
 
     def close(self):
         if self.staging is not None:

@@ -28,6 +28,15 @@ class Switches:
     ar_group: int = 0               # tiles per published group of the fused GEMV all-reduce (0 = whole grid)
     tc_gemv_min_n: int = 0          # decode GEMVs with at least this many outputs use the tcgen05 split-K kernel (0 = never)
     tc_gemv_max_n: int = 0          # ... and, for 9-16 rows, matrices with at most this many outputs (0 = never)
+    # Sublayer-boundary fusions for decode rows, each measured on the GLM decode step (1 GPU / rank 0 of TP=8):
+    # fewer launches did not mean a shorter step where the fused stage became a serial tail of its kernel
+    fuse_front: bool = False        # next site's hyper-connection front at a grid barrier inside the closing GEMV
+                                    # (90 launches fewer, +0.28 / +0.27 ms: the barrier costs more than the launch)
+    fuse_route: bool = False        # routing as the tail of the router GEMV
+    fuse_swiglu: bool = False       # SwiGLU while the down projection loads its activations (with fuse_route:
+                                    # 88 launches fewer, +0.4 / +0.2 ms)
+    gdn_own_fg: bool = True         # low-rank decay / gate projections inside the GatedDeltaNet kernel
+    hc_pre_wide: bool = True        # hyper-connection front as a column-parallel kernel fed by Gram partials
     l2_ahead: int = -1              # read-ahead distance of the weight-streaming kernels (-1 = library default)
     d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores
     d4_attn_tc: bool = False        # DSV41 tensor-core sparse attention (slower than the SIMT kernel at decode sizes)

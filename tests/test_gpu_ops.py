@@ -723,6 +723,40 @@ def test_gemv_ar_swiglu_source_and_front(K, fp8, N, Kd, m):
     assert not xo.f[m:].any() and not npost[m:].any()
 
 
+@pytest.mark.parametrize("N,m", [(4096, 3), (2048, 1), (4096, 8)])
+def test_hc_pre_wide_from_gram_partials(K, N, m):
+    """Column-parallel hyper-connection front fed by the fused GEMV's partials (mix dots, sum of squares, Gram)
+    against the fp32 statement applied to the device's R'."""
+    from ferrite_b200.models.glm import Act
+    from ferrite_b200.parallel.symm import FusedGemvAllReduce
+    Kd, mix = 512, 24
+    W = rnd(N, Kd, seed=1, scale=0.05).to(torch.bfloat16)
+    x = Act(torch.device("cuda"), 8, Kd)
+    x.f.copy_(dev(rnd(8, Kd, seed=2)))
+    K.call("fb_split_rows", x.f, Kd, *x.sp(3), 8, Kd)
+    Rin = dev(rnd(8, 4, N, seed=3))
+    post, comb = dev(rnd(8, 4, seed=5).abs()), dev(rnd(8, 4, 4, seed=6).abs())
+    fn = dev(rnd(mix, 4 * N, seed=7, scale=0.02))
+    scale, base, ln = dev(rnd(3, seed=8).abs() + 0.5), dev(rnd(mix, seed=9, scale=0.3)), dev(rnd(N, seed=10).abs() + 0.5)
+    y, Rout, acc = torch.zeros(8, N, device="cuda"), torch.zeros_like(Rin), torch.zeros(8, 25, device="cuda")
+    xo = Act(torch.device("cuda"), 8, N)
+    npost, ncomb = torch.zeros(8, 4, device="cuda"), torch.zeros(8, 16, device="cuda")
+    f = FusedGemvAllReduce(torch.device("cuda"), 0, 1)
+    f(dev(W), None, x.s, Kd, x.plane, y, N, m, N, Kd, False, True, (Rin, Rout, post, comb, fn, acc, mix), gram=True)
+    part, gram, part_n, ld = f.wide_partials()
+    K.call("fb_hc_pre_wide", Rout, part, gram, part_n, ld, scale, base, ln, xo.f, npost, ncomb, m, N, mix, 1e-5, 1e-6, 20,
+           *xo.sp(3))
+    torch.cuda.synchronize()
+    xr, pr, cr = R.hc_pre(Rout[:m].cpu(), fn.cpu(), scale.cpu(), base.cpu(), 1e-5, 1e-6, 20)
+    xn = R.rmsnorm(xr, ln.cpu(), 1e-5)
+    check("wide post", npost[:m], pr, 2e-4)
+    check("wide comb", ncomb[:m], cr.reshape(m, 16), 2e-4)
+    check("wide x", xo.f[:m], xn, 5e-4 * max(1.0, xn.abs().max().item()))
+    hi = xo.s[0, :m].view(torch.bfloat16).float() + xo.s[1, :m].view(torch.bfloat16).float()
+    check("wide x split", hi, xn, 5e-4 * max(1.0, xn.abs().max().item()))
+    assert not xo.f[m:].any() and part_n[:m].tolist() == [N // 16] * m
+
+
 def test_router_gemv_routes_in_its_tail(K):
     """[router | shared gate | shared up] GEMV whose last router CTA also routes: ids / weights equal the
     stand-alone route kernel run on the same logits."""
