@@ -112,43 +112,57 @@ __global__ void dsa_pool_kernel(const float* __restrict__ kidx_cache, const floa
     }
 }
 
-// scores[r][p] = ID^-0.5 * sum_h wi[r][h] * relu(qi[r][h] . pool_key[p]); one thread per pool.
+// scores[r][p] = ID^-0.5 * sum_h wi[r][h] * relu(qi[r][h] . pool_key[p]).  A CTA of 128 threads owns kScPools pools;
+// thread (pool, head group) covers IH / kScGroups heads of one pool, the groups' partial sums meet in shared memory
+// (a decode step scores a few hundred pools: one thread per pool would leave a 4096-FMA chain on 2 % of the GPU).
+constexpr int kScPools = 16, kScGroups = 8;
 template <int ID>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kScPools * kScGroups)
 dsa_score_kernel(const float* __restrict__ qi, int ld_qi, const float* __restrict__ wi,
                  const float* __restrict__ pool_cache, float* __restrict__ scores, int ld_sc,
                  const RowMeta* __restrict__ meta, PageView pv, int IH, int kpool) {
     PDL_PROLOGUE();
     extern __shared__ float sq[];  // [IH][ID] then [IH]
     float* sw = sq + IH * ID;
+    __shared__ float part[kScGroups][kScPools];
     const int r = blockIdx.y;
     const RowMeta m = meta[r];
     const int npools = (m.total + kpool - 1) / kpool;
     const int nvis = min(npools, m.ctx0 / kpool + m.off + 1);
-    if ((int)(blockIdx.x * blockDim.x) >= nvis) return;
+    if ((int)(blockIdx.x * kScPools) >= nvis) return;
     for (int i = threadIdx.x; i < IH * ID; i += blockDim.x) sq[i] = qi[(size_t)r * ld_qi + i];
     for (int i = threadIdx.x; i < IH; i += blockDim.x) sw[i] = wi[(size_t)r * IH + i];
     __syncthreads();
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= nvis) return;
-    const int ppp = pv.page_size / kpool;
-    const int pg = pv.table[(size_t)m.slot * pv.max_pages + p / ppp];
-    const float4* src = reinterpret_cast<const float4*>(pool_cache + ((size_t)pg * ppp + (p % ppp)) * ID);
-    float4 pk[ID / 4];
-#pragma unroll
-    for (int i = 0; i < ID / 4; ++i) pk[i] = src[i];
+    const int pl = threadIdx.x % kScPools, hg = threadIdx.x / kScPools;
+    const int p = blockIdx.x * kScPools + pl;
     float s = 0.f;
-    for (int h = 0; h < IH; ++h) {
-        const float4* q4 = reinterpret_cast<const float4*>(sq + h * ID);
-        float d = 0.f;
+    if (p < nvis) {
+        const int ppp = pv.page_size / kpool;
+        const int pg = pv.table[(size_t)m.slot * pv.max_pages + p / ppp];
+        const float4* src = reinterpret_cast<const float4*>(pool_cache + ((size_t)pg * ppp + (p % ppp)) * ID);
+        float4 pk[ID / 4];
 #pragma unroll
-        for (int i = 0; i < ID / 4; ++i) {
-            const float4 q = q4[i];
-            d += q.x * pk[i].x + q.y * pk[i].y + q.z * pk[i].z + q.w * pk[i].w;
+        for (int i = 0; i < ID / 4; ++i) pk[i] = src[i];
+        const int hper = (IH + kScGroups - 1) / kScGroups;
+        for (int h = hg * hper; h < min(IH, (hg + 1) * hper); ++h) {
+            const float4* q4 = reinterpret_cast<const float4*>(sq + h * ID);
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < ID / 4; ++i) {
+                const float4 q = q4[i];
+                d += q.x * pk[i].x + q.y * pk[i].y + q.z * pk[i].z + q.w * pk[i].w;
+            }
+            s += sw[h] * fmaxf(d, 0.f);
         }
-        s += sw[h] * fmaxf(d, 0.f);
     }
-    scores[(size_t)r * ld_sc + p] = s * rsqrtf((float)ID);
+    part[hg][pl] = s;
+    __syncthreads();
+    if (hg == 0 && p < nvis) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < kScGroups; ++g) t += part[g][pl];   // fixed order: every rank gets the same bits
+        scores[(size_t)r * ld_sc + p] = t * rsqrtf((float)ID);
+    }
 }
 
 __device__ __forceinline__ uint32_t order_key(float f) {
@@ -468,10 +482,17 @@ __global__ void dsa_attn_merge_kernel(const float* __restrict__ o_part, const fl
     const float inv = s_inv;
     for (int d = threadIdx.x; d < DL; d += blockDim.x) {
         float o = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < nsplit; ++s) {
-            const float w = w_s[s];
-            if (w != 0.f) o = fmaf(o_part[(((size_t)r * nsplit + s) * hl + h) * DL + d], w, o);
+        // 16 splits at a time with every load in flight before the first add (an empty split's partial is never
+        // read: it may hold anything)
+        for (int s0 = 0; s0 < nsplit; s0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int sp = s0 + j;
+                v[j] = (sp < nsplit && w_s[sp] != 0.f) ? o_part[(((size_t)r * nsplit + sp) * hl + h) * DL + d] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o = fmaf(v[j], s0 + j < nsplit ? w_s[s0 + j] : 0.f, o);
         }
         ctx[((size_t)r * hl + h) * DL + d] = o * inv;
         split_store(osp, r, h * DL + d, o * inv);
@@ -517,7 +538,7 @@ FB_API int fb_dsa_scores(const float* qi, int64_t ld_qi, const float* wi, const 
                          int64_t max_pages, int64_t page_size, int64_t n, int64_t IH, int64_t ID,
                          int64_t kpool, int64_t max_pools, cudaStream_t st) {
     PageView pv = make_pv(page_table, max_pages, page_size);
-    dim3 grid((unsigned)((max_pools + 127) / 128), (unsigned)n);
+    dim3 grid((unsigned)((max_pools + kScPools - 1) / kScPools), (unsigned)n);
     size_t sm = (size_t)(IH * ID + IH) * sizeof(float);
 #define SC_ARGS qi, (int)ld_qi, wi, pool_cache, scores, (int)ld_sc, (const RowMeta*)meta, pv, (int)IH, (int)kpool
     if (ID == 128) FB_LAUNCH((dsa_score_kernel<128>), grid, 128, sm, st, SC_ARGS);

@@ -110,6 +110,7 @@ class GlmDeviceModel:
         self.tc_gemv_min_n, self.tc_gemv_max_n = sw.tc_gemv_min_n, sw.tc_gemv_max_n
         if sw.l2_ahead >= 0:
             self.K.lib.fb_set_l2_ahead(sw.l2_ahead)
+        self.K.lib.fb_set_pdl(1 if sw.pdl else 0)
         self._tc_part = self._tc_ticket = None
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once

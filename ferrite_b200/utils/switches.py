@@ -35,8 +35,10 @@ class Switches:
     fuse_route: bool = False        # routing as the tail of the router GEMV
     fuse_swiglu: bool = False       # SwiGLU while the down projection loads its activations (with fuse_route:
                                     # 88 launches fewer, +0.4 / +0.2 ms)
-    gdn_own_fg: bool = True         # low-rank decay / gate projections inside the GatedDeltaNet kernel
+    gdn_own_fg: bool = False        # low-rank decay / gate projections inside the GatedDeltaNet kernel (34 launches
+                                    # fewer, +0.04 / +0.12 ms: 8..64 CTAs do serially what a wide GEMV does in parallel)
     hc_pre_wide: bool = True        # hyper-connection front as a column-parallel kernel fed by Gram partials
+                                    # (-0.32 / -0.27 ms against the one-CTA-per-row kernel)
     l2_ahead: int = -1              # read-ahead distance of the weight-streaming kernels (-1 = library default)
     d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores
     d4_attn_tc: bool = False        # DSV41 tensor-core sparse attention (slower than the SIMT kernel at decode sizes)
