@@ -82,6 +82,32 @@ def reference_arm():
     return 0
 
 
+def tp_identity_check(rank, world, dev, allreduce, n_new=14):
+    """Token identity of the tensor-parallel engine against the single-rank engine on a 4-layer slice of the
+    production architecture (3 GatedDeltaNet + 1 DSA layer, dense and MoE FFNs, MTP; 32 routed experts): every
+    rank runs the TP=world engine through the real collectives, rank 0 then runs TP=1 on the same weights.
+    Returns "n/14" on rank 0 (None elsewhere).  Seconds of work, outside the timed region."""
+    import torch
+    from ferrite_b200.config import EngineConfig, GlmConfig
+    from ferrite_b200.engine.glm_engine import GlmEngine
+    from ferrite_b200.models.glm import SyntheticSource
+    cfg = GlmConfig.scaled(4, n_routed_experts=32)
+    prompt = torch.randint(0, cfg.vocab_size, (48,), generator=torch.Generator().manual_seed(3)).tolist()
+    eng = GlmEngine(cfg, EngineConfig(tp=world, max_ctx=256, mtp_n=3), SyntheticSource(cfg, dev, seed=1), rank=rank,
+                    world=world, device=dev, allreduce=allreduce, prefill_rows=64)
+    out_tp, _ = eng.generate(prompt, n_new)
+    del eng
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    eng1 = GlmEngine(cfg, EngineConfig(tp=1, max_ctx=256, mtp_n=3), SyntheticSource(cfg, dev, seed=1), rank=0, world=1,
+                     device=dev, allreduce=None, prefill_rows=64)
+    out_1, _ = eng1.generate(prompt, n_new)
+    del eng1
+    torch.cuda.empty_cache()
+    return f"{sum(int(a == b) for a, b in zip(out_tp, out_1))}/{n_new}"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -133,6 +159,10 @@ def main():
             # start-up check of the peer-memory kernels against NCCL; a fused kernel that fails is detached
             from ferrite_b200.parallel.collective import self_test
             collective_check = self_test(allreduce, dev, rank, world)
+    tokens_match_tp1 = None
+    if world > 1 and args.layers == 0:
+        tokens_match_tp1 = tp_identity_check(rank, world, dev, allreduce)
+        dist.barrier()
     model_world = world
     if emu:
         assert world == 1, "--emulate-tp runs as one process"
@@ -178,9 +208,20 @@ def main():
         for _ in range(k):
             eng.launch_step_async(mtp)
 
+    def device_status():
+        """Status words and guard words of every bounded wait (collectives, tcgen05 barriers, row limits)."""
+        try:
+            m.arena.verify(snapshot=False)
+            if allreduce is not None and hasattr(allreduce, "check"):
+                allreduce.check()
+            return "ok"
+        except Exception as e:
+            return f"{type(e).__name__}: {e}"
+
     # ---- device-timed loop: K back-to-back graph launches --------------------------------
     run_device_loop(args.warmup)
     barrier()
+    status = [device_status()]
     len0 = int(m.main_len[0].item())
     sampler = ClockSampler(local)
     if rank == 0:
@@ -199,6 +240,7 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1)
     tokens = int(m.main_len[0].item()) - len0
+    status.append(device_status())
     # ---- end-to-end loop through the public API ------------------------------------------
     last = int(eng.block_ids[0].item())
     for _ in range(args.warmup):
@@ -213,10 +255,14 @@ def main():
     barrier()
     ms_e2e = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop() if rank == 0 else {}
+    status.append(device_status())
+    bad = [s for s in status if s != "ok"]
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=dev)
+        t = torch.tensor([ms, ms_e2e, float(len(bad))], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+        if float(t[2]) > 0 and not bad:
+            bad = ["a bounded wait failed on another rank"]
     if rank == 0:
         value = tokens / (ms * 1e-3)
         launches = (eng.launches_mtp if mtp else eng.launches_plain) * args.steps
@@ -235,13 +281,17 @@ def main():
                        "accept_tokens_per_step": round(tokens / args.steps, 3),
                        "experts_resident_per_layer": resident, "n_routed_experts": cfg.n_routed_experts,
                        "l2": "inputs larger than L2: every step streams >10 GB of weights per GPU",
-                       "prefill_s": round(t_prefill, 3), "load_s": round(t_load, 1)},
+                       "prefill_s": round(t_prefill, 3), "load_s": round(t_load, 1),
+                       "tokens_match_tp1": tokens_match_tp1,
+                       "device_status": "ok" if not bad else bad[0]},
             "clocks": clocks,
             "e2e": {"value": round(tok_e2e / (ms_e2e * 1e-3), 2), "unit": "tok/s",
                     "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * (eng.nv + 1),
                     "ms_per_step": round(ms_e2e / args.steps, 4)},
             "gpu_launches": launches,
         }
+        if bad:   # a timed-out wait leaves vectors unreduced: the step was not the model's step
+            out["valid"] = False
         print(json.dumps(out))
     if world > 1 or emu:
         dist.destroy_process_group()
