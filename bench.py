@@ -83,29 +83,41 @@ def reference_arm():
 
 
 def tp_identity_check(rank, world, dev, allreduce, n_new=14):
-    """Token identity of the tensor-parallel engine against the single-rank engine on a 4-layer slice of the
-    production architecture (3 GatedDeltaNet + 1 DSA layer, dense and MoE FFNs, MTP; 32 routed experts): every
-    rank runs the TP=world engine through the real collectives, rank 0 then runs TP=1 on the same weights.
-    Returns "n/14" on rank 0 (None elsewhere).  Seconds of work, outside the timed region."""
+    """The tensor-parallel engine against the single-rank engine on a 4-layer slice of the production architecture
+    (3 GatedDeltaNet + 1 DSA layer, dense and MoE FFNs; 32 routed experts; production widths): every rank runs the
+    TP=world engine through the real collectives (48-token prefill, then greedy steps), rank 0 then runs TP=1 on
+    the same weights FED WITH THE SAME TOKENS, so one flipped argmax cannot cascade.  Returns on rank 0
+    {"tokens": "n/14" (steps whose greedy token agrees), "hidden_rel_err": worst relative error of the final
+    hidden state over the steps}; None elsewhere.  Seconds of work, outside the timed region."""
     import torch
     from ferrite_b200.config import EngineConfig, GlmConfig
     from ferrite_b200.engine.glm_engine import GlmEngine
     from ferrite_b200.models.glm import SyntheticSource
     cfg = GlmConfig.scaled(4, n_routed_experts=32)
     prompt = torch.randint(0, cfg.vocab_size, (48,), generator=torch.Generator().manual_seed(3)).tolist()
-    eng = GlmEngine(cfg, EngineConfig(tp=world, max_ctx=256, mtp_n=3), SyntheticSource(cfg, dev, seed=1), rank=rank,
+
+    def run(eng, feed):
+        toks, hid = [eng.prefill(prompt)], []
+        eng.build_graphs(False)
+        for i in range(n_new - 1):
+            toks.append(eng.step_plain(feed[i] if feed is not None else None))
+            hid.append(eng.model.ws["h_final"][0].clone())
+        return toks, hid
+
+    eng = GlmEngine(cfg, EngineConfig(tp=world, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1), rank=rank,
                     world=world, device=dev, allreduce=allreduce, prefill_rows=64)
-    out_tp, _ = eng.generate(prompt, n_new)
+    toks_tp, hid_tp = run(eng, None)
     del eng
     torch.cuda.empty_cache()
     if rank != 0:
         return None
-    eng1 = GlmEngine(cfg, EngineConfig(tp=1, max_ctx=256, mtp_n=3), SyntheticSource(cfg, dev, seed=1), rank=0, world=1,
+    eng1 = GlmEngine(cfg, EngineConfig(tp=1, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1), rank=0, world=1,
                      device=dev, allreduce=None, prefill_rows=64)
-    out_1, _ = eng1.generate(prompt, n_new)
+    toks_1, hid_1 = run(eng1, toks_tp)      # step i is fed the TP engine's token i
     del eng1
     torch.cuda.empty_cache()
-    return f"{sum(int(a == b) for a, b in zip(out_tp, out_1))}/{n_new}"
+    err = max(float((a - b).abs().max() / b.abs().max().clamp_min(1e-20)) for a, b in zip(hid_tp, hid_1))
+    return {"tokens": f"{sum(int(a == b) for a, b in zip(toks_tp, toks_1))}/{n_new}", "hidden_rel_err": round(err, 6)}
 
 
 def main():
