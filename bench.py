@@ -104,15 +104,15 @@ def tp_identity_check(rank, world, dev, allreduce, n_new=14):
             hid.append(eng.model.ws["h_final"][0].clone())
         return toks, hid
 
-    eng = GlmEngine(cfg, EngineConfig(tp=world, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1), rank=rank,
-                    world=world, device=dev, allreduce=allreduce, prefill_rows=64)
+    eng = GlmEngine(cfg, EngineConfig(tp=world, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1, exact_shards=True),
+                    rank=rank, world=world, device=dev, allreduce=allreduce, prefill_rows=64)
     toks_tp, hid_tp = run(eng, None)
     del eng
     torch.cuda.empty_cache()
     if rank != 0:
         return None
-    eng1 = GlmEngine(cfg, EngineConfig(tp=1, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1), rank=0, world=1,
-                     device=dev, allreduce=None, prefill_rows=64)
+    eng1 = GlmEngine(cfg, EngineConfig(tp=1, max_ctx=256, mtp_n=1), SyntheticSource(cfg, dev, seed=1, exact_shards=True),
+                     rank=0, world=1, device=dev, allreduce=None, prefill_rows=64)
     toks_1, hid_1 = run(eng1, toks_tp)      # step i is fed the TP engine's token i
     del eng1
     torch.cuda.empty_cache()

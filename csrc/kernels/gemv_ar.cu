@@ -337,7 +337,12 @@ gemv_ar_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales, 
             r_s[m][i][nl] = o;   // the inputs of this column are already in rk
         }
     }
-    if (!hc.fn) return;
+    if (!hc.fn) {
+        // a fold without a next site ends a forward: leave the tile counts at zero, so that the first front of the
+        // next forward (which has no producer) never sees partials of this one
+        if (blockIdx.x == 0 && threadIdx.x < mrows && hc.part_n) hc.part_n[threadIdx.x] = 0;
+        return;
+    }
     __syncthreads();
     // mix dots of R' with fn and |R'|^2 as per-tile partials; the consumer (hc_pre) sums the tiles.
     // One warp per mix row q (q == mix: the sum of squares); lanes cover the 4 x kTileN tile.

@@ -43,9 +43,13 @@ class SyntheticSource:
     """Random-init weights generated on the device, tensor by tensor (no host copy).
     Matrices N(0, std); norm weights / HC scales 1; biases, A_log, dt_bias, HC bases 0."""
 
-    def __init__(self, cfg: GlmConfig, device, seed: int = 0, std: float = 0.02):
+    def __init__(self, cfg: GlmConfig, device, seed: int = 0, std: float = 0.02, exact_shards: bool = False):
         self.layout = weight_layout(cfg)
         self.device, self.seed, self.std = device, seed, std
+        # False: a rank draws its slice of the routed experts directly at the shard's width (fast; the model of a
+        # TP=N run is then a different random model than that of a TP=1 run).  True: every rank draws the
+        # full-width experts and slices them, so TP=N and TP=1 hold the same weights (token-identity checks).
+        self.exact_shards = exact_shards
 
     def get(self, name: str) -> torch.Tensor:
         shape = self.layout[name]
@@ -58,12 +62,20 @@ class SyntheticSource:
         dt = torch.bfloat16 if len(shape) > 1 and shape[0] * shape[1] > (1 << 22) else torch.float32
         return torch.randn(shape, generator=g, device=self.device, dtype=dt) * self.std
 
-    def expert_chunk(self, pfx: str, e0: int, e1: int, Il: int, H: int):
-        """Routed experts e0..e1 of one layer, already at the shard's width: (gate|up
-        [n, 2*Il, H], down [n, H, Il]) in bf16."""
+    def expert_chunk(self, pfx: str, e0: int, e1: int, Il: int, H: int, rank: int = 0, world: int = 1):
+        """Routed experts e0..e1 of one layer at the shard's width: (gate|up [n, 2*Il, H], down [n, H, Il]) in
+        bf16; rank / world say which slice of the intermediate dim (only used with exact_shards)."""
         g = torch.Generator(device=self.device).manual_seed((self.seed << 32) ^ zlib.crc32(f"{pfx}.{e0}".encode()))
-        a13 = torch.randn(e1 - e0, 2 * Il, H, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
-        a2 = torch.randn(e1 - e0, H, Il, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+        n = e1 - e0
+        if self.exact_shards and world > 1:
+            I = Il * world
+            full13 = torch.randn(n, 2 * I, H, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+            full2 = torch.randn(n, H, I, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+            lo, hi = rank * Il, (rank + 1) * Il
+            a13 = torch.cat([full13[:, lo:hi], full13[:, I + lo:I + hi]], 1).contiguous()
+            return a13, full2[:, :, lo:hi].contiguous()
+        a13 = torch.randn(n, 2 * Il, H, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
+        a2 = torch.randn(n, H, Il, generator=g, device=self.device, dtype=torch.bfloat16) * self.std
         return a13, a2
 
 
@@ -242,7 +254,7 @@ class GlmDeviceModel:
             step = 16
             for e0 in range(0, Er, step):
                 e1 = min(Er, e0 + step)
-                a13, a2 = chunk(pfx, e_lo + e0, e_lo + e1, Il, H)
+                a13, a2 = chunk(pfx, e_lo + e0, e_lo + e1, Il, H, *((0, 1) if by_e else (self.rank, self.world)))
                 q, s = quant_fp8_block(a13.view(-1, H))
                 w13[e0:e1], s13[e0:e1] = q.view(e1 - e0, 2 * Il, H), s.view(e1 - e0, -1, s.shape[1])
                 q, s = quant_fp8_block(a2.view(-1, Il))
