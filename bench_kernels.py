@@ -288,6 +288,28 @@ def make_cases(K, only):
                                   f"{m * topk} pairs x 2 x {Im} x {D} e2m1 (bytes if all pairs differ)"))
                 cases.append(Case(f"d4_expert_down_mma.{tag}.m{m}", m * topk * D * (Im // 2 + Im // 32), dn,
                                   f"{m * topk} pairs x {D} x {Im} e2m1"))
+    # ---- DSV41: block-scaled tcgen05 grouped GEMM (e2m1 weights x e4m3 rows, ue8m0 scales), prefill / batched sizes ----
+    if want("mx_gemm"):
+        from ferrite_b200.ops import mx
+        D = 5120
+        for tag, Em, Nm, rows_per in (("gate_up.tp8.48e", 48, 2 * 384, 64), ("gate_up.tp1.16e", 16, 2 * 2304, 64),
+                                      ("gate_up.tp1.16e.r256", 16, 2 * 2304, 256)):
+            wp = torch.randint(0, 256, (Em, Nm, D // 2), dtype=torch.uint8, device=dev)
+            sfa = mx.pack_weight_scales(torch.full((Em, Nm, D // 32), 120, dtype=torch.uint8, device=dev))
+            Mr = Em * rows_per
+            x8 = (torch.randn(Mr, D, device=dev) * 2).to(torch.float8_e4m3fn)
+            xsf = torch.full((Mr, D // 32), 124, dtype=torch.uint8, device=dev)
+            bn = mx.pick_bn(rows_per)
+            tiles, n_tiles, _ = mx.make_tiles(torch.full((Em,), rows_per, dtype=torch.int32, device=dev), bn)
+            outm = torch.zeros(Mr, Nm, device=dev)
+            stat = torch.zeros(4, dtype=torch.int32, device=dev)
+
+            def mxfn(wp=wp, sfa=sfa, x8=x8, xsf=xsf, tiles=tiles, n_tiles=n_tiles, outm=outm, bn=bn, stat=stat):
+                mx.mx_gemm_grouped(wp, sfa, x8, xsf, tiles, n_tiles, outm, bn, stat)
+            wbytes = Em * Nm * (D // 2 + D // 32)
+            cases.append(Case(f"mx_gemm.{tag}", wbytes + Mr * D + Mr * Nm * 4, mxfn,
+                              f"{Em} experts x {Nm} x {D} e2m1, {rows_per} rows each (bn {bn}); FLOP={2 * Mr * Nm * D}; "
+                              f"weights {wbytes / 1e6:.0f} MB"))
     if want("d4_sparse_attn"):
         n, Hl, hd, W, cap, ktop, ccap = 1, 8, 512, 128, 136, 512, 8192
         ring = torch.randn(1, cap, hd, device=dev).to(torch.bfloat16)
