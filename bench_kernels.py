@@ -292,7 +292,7 @@ def make_cases(K, only):
     if want("mx_gemm"):
         from ferrite_b200.ops import mx
         D = 5120
-        for tag, Em, Nm, rows_per in (("gate_up.tp8.48e", 48, 2 * 384, 64), ("gate_up.tp1.16e", 16, 2 * 2304, 64),
+        for tag, Em, Nm, rows_per in (("gate_up.tp8.96e", 96, 2 * 384, 64), ("gate_up.tp1.16e", 16, 2 * 2304, 64),
                                       ("gate_up.tp1.16e.r256", 16, 2 * 2304, 256)):
             wp = torch.randint(0, 256, (Em, Nm, D // 2), dtype=torch.uint8, device=dev)
             sfa = mx.pack_weight_scales(torch.full((Em, Nm, D // 32), 120, dtype=torch.uint8, device=dev))
@@ -308,8 +308,8 @@ def make_cases(K, only):
                 mx.mx_gemm_grouped(wp, sfa, x8, xsf, tiles, n_tiles, outm, bn, stat)
             wbytes = Em * Nm * (D // 2 + D // 32)
             cases.append(Case(f"mx_gemm.{tag}", wbytes + Mr * D + Mr * Nm * 4, mxfn,
-                              f"{Em} experts x {Nm} x {D} e2m1, {rows_per} rows each (bn {bn}); FLOP={2 * Mr * Nm * D}; "
-                              f"weights {wbytes / 1e6:.0f} MB"))
+                              f"{Em} experts x {Nm} x {D} e2m1 ({wbytes / 1e6:.0f} MB), {rows_per} rows each (bn {bn}) "
+                              f"FLOP={2 * Mr * Nm * D}"))
     if want("d4_sparse_attn"):
         n, Hl, hd, W, cap, ktop, ccap = 1, 8, 512, 128, 136, 512, 8192
         ring = torch.randn(1, cap, hd, device=dev).to(torch.bfloat16)
