@@ -45,7 +45,7 @@ constexpr int kConvWarps = 8;
 
 template <int BN>
 struct MxCfg {
-    static constexpr int kStages = BN >= 256 ? 3 : 4;
+    static constexpr int kStages = BN == 128 ? 4 : 3;   // BN <= 64: two CTAs per SM (two sets of expander warps)
     static constexpr int kABytes = kTileW * kBK;          // expanded e4m3 weights
     static constexpr int kRawBytes = kTileW * kBK / 2;    // packed nibbles
     static constexpr int kBBytes = BN * kBK;
@@ -97,12 +97,12 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_
 // 1.5, 2, 3, 4, 6 are the e4m3 bytes 00 30 38 3C 40 44 48 4C; the sign bit moves from nibble bit 3 to byte bit 7.
 __device__ __forceinline__ uint32_t e2m1x4_to_e4m3x4(uint32_t h) {
     const uint32_t mag = __byte_perm(0x3C383000u, 0x4C484440u, h & 0x7777u);
-    const uint32_t s = h & 0x8888u;
-    return mag | ((s & 0x8u) << 4) | ((s & 0x80u) << 8) | ((s & 0x800u) << 12) | ((s & 0x8000u) << 16);
+    const uint32_t sgn = __byte_perm(0x00008000u, 0u, (h >> 3) & 0x1111u);   // byte j = 0x80 if nibble j is negative
+    return mag | sgn;
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kMxThreads, 1)
+__global__ void __launch_bounds__(kMxThreads, (BN <= 64 ? 2 : 1))
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const uint8_t* __restrict__ sfa_packed, const uint8_t* __restrict__ x_sf, int ld_xsf,
                const MxTile* __restrict__ tiles, const int* __restrict__ n_tiles, float* __restrict__ out, int ldo,
@@ -190,17 +190,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else {
         // ---- expanders (warps 2..9), then epilogue (warps 2..5) ----
         const int ct = threadIdx.x - 64;           // 0..255
-        const int row = ct >> 1, half = ct & 1;    // two threads per weight row, 32 packed bytes each
         bool ok = true;
+        const bool sf_row = ct < BN && ct < tl.nrows && tl.row0 + ct < m_total;
+        const uint8_t* sf_src = x_sf + (size_t)(tl.row0 + (sf_row ? ct : 0)) * ld_xsf;
         for (int kb = 0; kb < nkb && ok; ++kb) {
             const int s = kb % C::kStages;
+            // this k-block's activation scale bytes (global) go in flight before the wait: they do not depend on it
+            uint32_t sv = 0x7f7f7f7fu;
+            if (sf_row) sv = __ldg(reinterpret_cast<const uint32_t*>(sf_src + kb * 4));
             if (!tc::mbar_wait(raw_full(s), (kb / C::kStages) & 1)) { atomicExch(&s_fail, 1); ok = false; }
             if (ok) {
-                const uint4* src = reinterpret_cast<const uint4*>(base_g + raw_off(s) + row * (kBK / 2) + half * 32);
-                uint8_t* arow = base_g + a_off(s) + row * kBK;
+                // 512 units of 16 packed bytes per stage; consecutive threads take consecutive units (conflict-free
+                // loads), each unit becomes two 16-byte chunks of e4m3 at their swizzled place in the row
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {      // 16 packed bytes -> two 16-byte chunks of e4m3
-                    const uint4 p = src[u];
+                for (int u = 0; u < 2; ++u) {
+                    const int q = ct + 256 * u;
+                    const int row = q >> 2, c16 = q & 3;
+                    const uint4 p = *reinterpret_cast<const uint4*>(base_g + raw_off(s) + q * 16);
                     const uint32_t w[4] = {p.x, p.y, p.z, p.w};
                     uint32_t o[8];
 #pragma unroll
@@ -208,17 +214,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         o[2 * j] = e2m1x4_to_e4m3x4(w[j] & 0xffffu);
                         o[2 * j + 1] = e2m1x4_to_e4m3x4(w[j] >> 16);
                     }
-                    const int c0 = half * 4 + u * 2;   // 16-byte chunk index inside the 128-byte row
+                    uint8_t* arow = base_g + a_off(s) + row * kBK;
+                    const int c0 = c16 * 2;            // 16-byte chunk index inside the 128-byte row
                     *reinterpret_cast<uint4*>(arow + (((c0) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                     *reinterpret_cast<uint4*>(arow + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
                 }
                 // activation rows' scale bytes of this k-block -> tcgen05.cp layout (rows past the tile: scale 1)
-                if (ct < BN) {
-                    uint32_t sv = 0x7f7f7f7fu;
-                    if (ct < tl.nrows && tl.row0 + ct < m_total)
-                        sv = *reinterpret_cast<const uint32_t*>(x_sf + (size_t)(tl.row0 + ct) * ld_xsf + kb * 4);
+                if (ct < BN)
                     *reinterpret_cast<uint32_t*>(base_g + sfb_off(s) + (ct >> 7) * 512 + (ct & 31) * 16 + ((ct >> 5) & 3) * 4) = sv;
-                }
                 fence_proxy_async();
             }
             __syncwarp();
