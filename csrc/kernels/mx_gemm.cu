@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kMxThreads, (BN <= 64 ? 2 : 1))
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const uint8_t* __restrict__ sfa_packed, const uint8_t* __restrict__ x_sf, int ld_xsf,
                const MxTile* __restrict__ tiles, const int* __restrict__ n_tiles, float* __restrict__ out, int ldo,
-               int m_total, int N, int K, int* __restrict__ status) {
+               int m_total, int N, int K, int quad, int* __restrict__ status) {
     using C = MxCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -125,7 +125,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     pdl_wait();   // the tile list is written by the kernel before this one
     if ((int)blockIdx.y >= *n_tiles) return;   // uniform for the CTA; nothing allocated yet
     const MxTile tl = tiles[blockIdx.y];
-    const int nkb = K / kBK;
+    const int nkb = (K + kBK - 1) / kBK;   // a last k-block past K reads zeros (TMA fill) with scale bytes the caller padded
     // stage layout: [A expanded 16 KB][B BN*128][raw 8 KB][sfa 512][sfb 512 * atoms]
     auto a_off = [&](int s) { return (uint32_t)(s * C::kStageBytes); };
     auto b_off = [&](int s) { return a_off(s) + C::kABytes; };
@@ -215,9 +215,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         o[2 * j + 1] = e2m1x4_to_e4m3x4(w[j] >> 16);
                     }
                     uint8_t* arow = base_g + a_off(s) + row * kBK;
-                    const int c0 = c16 * 2;            // 16-byte chunk index inside the 128-byte row
-                    *reinterpret_cast<uint4*>(arow + (((c0) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(arow + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    if (!quad) {
+                        const int c0 = c16 * 2;        // 16-byte chunk index inside the 128-byte row
+                        *reinterpret_cast<uint4*>(arow + (((c0) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(arow + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else if (kb * kBK + kBK <= K) {
+                        // quad-interleaved weight bytes (the decode kernels' load-time repack): word j of unit c16 is
+                        // word c16 of the ORIGINAL unit j, i.e. the 8 values 32 j + 8 c16 .. + 8 of the k-block
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint2*>(arow + (((2 * j + (c16 >> 1)) ^ (row & 7)) << 4) + (c16 & 1) * 8) =
+                                make_uint2(o[2 * j], o[2 * j + 1]);
+                    } else {
+                        // 64-value tail of a quad-interleaved row: word (block b, position q) sits at q * 2 + b;
+                        // units 2 and 3 are past the row (zeros from the TMA fill) and expand to zeros in place
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int qq = 2 * c16 + (j >> 1), bb = j & 1;
+                            const int chunk = c16 < 2 ? 2 * bb + (qq >> 1) : 2 * c16 + (j >> 1);
+                            const int hf = c16 < 2 ? (qq & 1) : (j & 1);
+                            *reinterpret_cast<uint2*>(arow + ((chunk ^ (row & 7)) << 4) + hf * 8) = make_uint2(o[2 * j], o[2 * j + 1]);
+                        }
+                    }
                 }
                 // activation rows' scale bytes of this k-block -> tcgen05.cp layout (rows past the tile: scale 1)
                 if (ct < BN)
@@ -286,7 +305,7 @@ int make_tmap_u8_plain(CUtensorMap* map, const void* base, uint64_t rows, uint64
 template <int BN>
 int launch_mx(const CUtensorMap& tw, const CUtensorMap& tx, const uint8_t* sfa, const uint8_t* xsf, int ld_xsf,
               const MxTile* tiles, const int* n_tiles, int max_tiles, float* out, int ldo, int m_total, int N, int K,
-              int* status, cudaStream_t st) {
+              int quad, int* status, cudaStream_t st) {
     auto k = mx_gemm_kernel<BN>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -296,7 +315,7 @@ int launch_mx(const CUtensorMap& tw, const CUtensorMap& tx, const uint8_t* sfa, 
     }
     dim3 grid(N / kTileW, max_tiles);
     FB_LAUNCH((k), grid, kMxThreads, MxCfg<BN>::kSmem, st, tw, tx, sfa, xsf, ld_xsf, tiles, n_tiles, out, ldo, m_total, N, K,
-              status);
+              quad, status);
     return FB_LAUNCH_CHECK();
 }
 
@@ -320,22 +339,27 @@ __global__ void mx_tiles_kernel(const int* __restrict__ counts, int E, int bn, M
 
 }  // namespace
 
-// Wp        [E * N, K / 2] packed e2m1 (even k in the low nibble), N % 128 == 0, K % 128 == 0
-// sfa       [E][N / 128][K / 128][512] ue8m0 weight scales in the tcgen05.cp chunk layout (fb_mx_pack_sf)
-// X8        [m_total, K] e4m3 activation rows sorted by expert;  x_sf [m_total, ld_xsf] their ue8m0 scales per 32
+// Wp        [E * N, K / 2] packed e2m1 (even k in the low nibble), N % 128 == 0, K % 32 == 0; quad != 0: the bytes of
+//           every 64-byte group are quad-interleaved (fb_d4_fp4_repack), which needs K % 64 == 0
+// sfa       [E][N / 128][ceil(K / 128)][512] ue8m0 weight scales in the tcgen05.cp chunk layout
+// X8        [m_total, K] e4m3 activation rows sorted by expert;  x_sf [m_total, ld_xsf] their ue8m0 scales per 32,
+//           ld_xsf >= 4 * ceil(K / 128); scale bytes of blocks past K must be valid exponents (they meet zeros)
 // tiles     [max_tiles] of (expert, first row, rows, 0);  n_tiles: device int (CTAs past it exit)
 // out       [m_total, N] f32 (row stride ldo);  bn: activation rows per tile, one of 32 / 64 / 128 / 256
 FB_API int fb_mx_gemm_grouped(const void* Wp, const void* sfa, const void* X8, const void* x_sf, int64_t ld_xsf,
                               const void* tiles, const int* n_tiles, int64_t max_tiles, float* out, int64_t ldo,
-                              int64_t m_total, int64_t E, int64_t N, int64_t K, int64_t bn, int* status, cudaStream_t st) {
-    if ((N % kTileW) || (K % kBK) || m_total < 1 || max_tiles < 1 || (ld_xsf % 4) || ld_xsf * 32 < K) return (int)cudaErrorInvalidValue;
+                              int64_t m_total, int64_t E, int64_t N, int64_t K, int64_t bn, int64_t quad, int* status,
+                              cudaStream_t st) {
+    if ((N % kTileW) || (K % 32) || (quad && (K % 64)) || m_total < 1 || max_tiles < 1 || (ld_xsf % 4) ||
+        ld_xsf < 4 * ((K + kBK - 1) / kBK))
+        return (int)cudaErrorInvalidValue;
     CUtensorMap tw, tx;
     int rc = make_tmap_u8_plain(&tw, Wp, (uint64_t)(E * N), (uint64_t)(K / 2), kTileW, kBK / 2);
     if (rc) return rc;
     rc = fb_make_tmap_2d(&tx, X8, (uint64_t)m_total, (uint64_t)K, (uint32_t)bn, kBK, 1);
     if (rc) return rc;
 #define MX_ARGS tw, tx, (const uint8_t*)sfa, (const uint8_t*)x_sf, (int)ld_xsf, (const MxTile*)tiles, n_tiles, (int)max_tiles, \
-                out, (int)ldo, (int)m_total, (int)N, (int)K, status, st
+                out, (int)ldo, (int)m_total, (int)N, (int)K, (int)quad, status, st
     switch (bn) {
         case 32: return launch_mx<32>(MX_ARGS);
         case 64: return launch_mx<64>(MX_ARGS);

@@ -76,6 +76,10 @@ class Dsv41DeviceModel:
         self.tc_gemv_min_n = 0
         self.fp4_mma = switches().d4_fp4_mma   # tensor-core routed experts (decode rows)
         self.fp4_mma_rows = 1 << 30
+        # row count from which the routed experts run as block-scaled tcgen05 grouped GEMMs (csrc/kernels/mx_gemm.cu):
+        # below it the weight-streaming mma.sync kernels stream every (row, slot) pair's expert once per pair
+        self.mx_min_rows = switches().d4_mx_min_rows
+        self._mx_ws = None
         self._xq_ready = False
         # tensor-core sparse attention (head_dim 512), opt-in: at decode sizes (640 keys) it measured 21.6 us against
         # 16.3 us for the SIMT kernel with the in-kernel split merge (8 heads), and 2.37 vs 2.15 ms on the 8-layer bench
@@ -167,6 +171,14 @@ class Dsv41DeviceModel:
         if L["fp4_mma"]:
             for t in (L["w13"], L["w2"]):
                 self.K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 0)
+        # block-scaled tcgen05 path for prefill-sized row counts: weight scale bytes once more, in the layout tcgen05.cp
+        # reads (1/16 of the weight bytes); the packed weights are shared with the decode kernels (either byte order)
+        L["mx"] = (self.mx_min_rows > 0 and self.max_rows >= self.mx_min_rows and (2 * Il) % 128 == 0 and d % 128 == 0
+                   and Il % 32 == 0 and E <= 512 and (not L["fp4_mma"] or Il % 64 == 0))
+        if L["mx"]:
+            from ..ops import mx
+            L["sfa13"] = mx.pack_weight_scales(L["s13"].view(E, 2 * Il, d // 32))
+            L["sfa2"] = mx.pack_weight_scales(L["s2"])
         sw1, sw3, sw2 = (src.get(f + f"shared_experts.{n}.weight") for n in ("w1", "w3", "w2"))
         if self.shared_tp:
             lo = self.rank * self.Is_real
@@ -509,6 +521,40 @@ class Dsv41DeviceModel:
         self._quant(low.f, low, n, self.Gl * R_)
         self._out_gemv(L["wo_b"], low, n, d, self.Gl * R_)
 
+    def _moe_mx(self, L, n):
+        """Routed experts of `n` rows as two block-scaled tcgen05 grouped GEMMs: pairs sorted by expert, rows
+        quantised (e4m3 + ue8m0 per 32) straight into their sorted places, gate | up GEMM, weighted SwiGLU +
+        requantisation, down GEMM, slot-ordered combine into ws['y'].  Every expert's weights stream once per
+        call, however many rows it has."""
+        from ..ops import mx
+        cfg, ws, K = self.cfg, self.ws, self.K
+        d, Il, E, topk = cfg.dim, self.Il, L["E"], L["topk"]
+        npairs = n * topk
+        W = self._mx_ws
+        if W is None:
+            M, kmax = self.max_rows, ws["ridx"].shape[1]
+            P = M * kmax
+            i32 = lambda *s_: torch.zeros(*s_, dtype=torch.int32, device=self.dev)
+            u8 = lambda *s_: torch.zeros(*s_, dtype=torch.uint8, device=self.dev)
+            W = self._mx_ws = {
+                "pos": i32(P), "wts": self._z(P), "counts": i32(512), "offsets": i32(513),
+                "tiles": i32(512 + P // 32 + 1, 4), "n_tiles": i32(1),
+                "x8": u8(P, d), "xsf": u8(P, mx.sf_ld(d)), "h": self._z(P, 2 * Il), "a8": u8(P, Il),
+                "asf": u8(P, mx.sf_ld(Il)), "ypair": self._z(P, d)}
+        bn = mx.pick_bn(max(1.0, npairs / E))
+        K.call("fb_mx_sort", ws["ridx"], ws["rw"], npairs, 0, E, bn, W["pos"], W["wts"], W["counts"], W["offsets"], W["tiles"],
+               W["n_tiles"], W["tiles"].shape[0])
+        K.call("fb_mx_quant_scatter", ws["x"].f, ws["x"].ld, W["pos"], topk, n, d, W["x8"], W["xsf"], W["xsf"].shape[1])
+        quad = bool(L["fp4_mma"])
+        mx.mx_gemm_grouped(L["w13"].view(E, 2 * Il, d // 2), L["sfa13"], W["x8"][:npairs], W["xsf"], W["tiles"], W["n_tiles"],
+                           W["h"], bn, self.tc_status, quad=quad, m_total=npairs)
+        lim = float(cfg.swiglu_limit) if cfg.swiglu_limit > 0 else 3.0e38
+        K.call("fb_mx_swiglu_quant", W["h"], 2 * Il, W["wts"], View(W["offsets"], E), npairs, Il, lim, W["a8"], W["asf"],
+               W["asf"].shape[1])
+        mx.mx_gemm_grouped(L["w2"], L["sfa2"], W["a8"][:npairs], W["asf"], W["tiles"], W["n_tiles"], W["ypair"], bn,
+                           self.tc_status, quad=quad, m_total=npairs)
+        K.call("fb_mx_combine", W["ypair"], d, W["pos"], topk, ws["y"], ws["y"].shape[1], n, d, 0)
+
     def _moe(self, L, n):
         cfg, ws = self.cfg, self.ws
         d, x, xq = cfg.dim, ws["x"], ws["xq"]
@@ -518,7 +564,12 @@ class Dsv41DeviceModel:
         self.K.call("fb_d4_route", ws["rlogit"], ldl, L["gate_b"], L["gate_bvl"], ws["is_image"] if L["gate_bvl"] is not None else None,
                     n, E, topk, float(cfg.route_scale), ws["ridx"], ws["rw"])
         h = ws["h"]
-        if L["fp4_mma"] and n <= self.fp4_mma_rows:
+        if L.get("mx") and n >= self.mx_min_rows:
+            if not self._xq_ready:      # the shared expert below reads the quantised planes
+                self._quant(x.f, xq, n, d)
+            self._xq_ready = False
+            self._moe_mx(L, n)
+        elif L["fp4_mma"] and n <= self.fp4_mma_rows:
             # decode rows: e2m1 weights x f16 activations on the tensor cores (activations are e4m3 round trips,
             # exact in f16), one (row, slot) pair per CTA column
             if not self._xq_ready:

@@ -22,8 +22,11 @@ def pack_weight_scales(scales: torch.Tensor) -> torch.Tensor:
     128-value k-block) the 512-byte chunk tcgen05.cp reads, byte (i * 16 + g * 4 + s) for row 32 g + i and
     32-value sub-block s.  Done once at load time."""
     E, N, KS = scales.shape
-    assert N % TILE_W == 0 and KS % 4 == 0 and scales.dtype == torch.uint8
-    t = scales.view(E, N // TILE_W, 4, 32, KS // 4, 4)          # [E, tile, g, i, kb, s]
+    assert N % TILE_W == 0 and scales.dtype == torch.uint8
+    if KS % 4:   # a last k-block past K meets zero values: any valid exponent will do
+        scales = torch.nn.functional.pad(scales, (0, 4 - KS % 4), value=127)
+        KS = scales.shape[2]
+    t = scales.contiguous().view(E, N // TILE_W, 4, 32, KS // 4, 4)          # [E, tile, g, i, kb, s]
     return t.permute(0, 1, 4, 3, 2, 5).contiguous().view(E, N // TILE_W, KS // 4, 512)
 
 
@@ -48,12 +51,20 @@ def pick_bn(rows_per_expert: float) -> int:
     return 256
 
 
+def sf_ld(K: int) -> int:
+    """Row stride (bytes) of an activation scale buffer: whole 128-value k-blocks."""
+    return 4 * ((K + KB - 1) // KB)
+
+
 def mx_gemm_grouped(w_packed: torch.Tensor, sfa: torch.Tensor, x8: torch.Tensor, x_sf: torch.Tensor, tiles: torch.Tensor,
-                    n_tiles: torch.Tensor, out: torch.Tensor, bn: int, status: torch.Tensor) -> None:
-    """out[p, :] = W[e(p)] . x[p] for the rows of the tile list.  w_packed [E, N, K/2] uint8, sfa from
-    :func:`pack_weight_scales`, x8 [M, K] e4m3 rows sorted by expert, x_sf [M, K/32] uint8, out [M, N] f32."""
+                    n_tiles: torch.Tensor, out: torch.Tensor, bn: int, status: torch.Tensor, quad: bool = False,
+                    m_total: Optional[int] = None) -> None:
+    """out[p, :] = W[e(p)] . x[p] for the rows of the tile list.  w_packed [E, N, K/2] uint8 (quad: quad-interleaved
+    bytes), sfa from :func:`pack_weight_scales`, x8 [M, K] e4m3 rows sorted by expert, x_sf [M, >= sf_ld(K)] uint8
+    (bytes past K / 32 must be valid exponents), out [M, >= N] f32."""
     E, N, K2 = w_packed.shape
     M, K = x8.shape
-    assert K == 2 * K2 and x_sf.shape == (M, K // 32) and out.shape[0] == M and out.shape[1] >= N
+    M = M if m_total is None else m_total
+    assert K == 2 * K2 and x_sf.shape[0] >= M and x_sf.stride(0) >= sf_ld(K) and out.shape[0] >= M and out.shape[1] >= N
     _lib.lib().call("fb_mx_gemm_grouped", w_packed, sfa, x8, x_sf, x_sf.stride(0), tiles, n_tiles, tiles.shape[0], out,
-                    out.stride(0), M, E, N, K, bn, status)
+                    out.stride(0), M, E, N, K, bn, int(quad), status)
