@@ -473,7 +473,9 @@ class Dsv41DeviceModel:
             ccap = self.ccap[r]
             if "c_w" in L:
                 nc = L["c_w"].shape[0]
-                self.K.call("fb_d4_gemv_f32w", L["c_w"], x.f, d, ws["ckv"], 2 * hd, n, nc, d)
+                for r0 in range(0, n, 8):   # the f32-weight GEMV takes 8 rows per launch
+                    self.K.call("fb_d4_gemv_f32w", L["c_w"], View(x.f, r0 * x.f.shape[1]), d, View(ws["ckv"], r0 * 2 * hd),
+                                2 * hd, min(8, n - r0), nc, d)
                 rk, rsc = self.cring.get(layer, (None, None))
                 self.K.call("fb_d4_compress", ws["ckv"], View(ws["ckv"], hd), 2 * hd, rs.meta, rk, rsc, self.depth,
                             L["c_norm"], ws["lat"], ws["flag"], n, hd, r, float(cfg.norm_eps))
