@@ -97,7 +97,8 @@ class Dsv41DeviceModel:
         self._folded = False
         self.debug_hook = None
         self.win_cap = cfg.window_size + max_rows
-        self.depth = 16
+        # compressor ring: positions that one forward may look back over (ratio + rows of the forward)
+        self.depth = max(16, max_rows + max([r for r in cfg.compress_ratios] + [1]))
         self.token_map = token_map
         self.layout = EngramLayout.from_config(cfg)
         self._pack(src)
