@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--prompt-len", type=int, default=300)
     ap.add_argument("--experts", type=int, default=384)
+    ap.add_argument("--max-rows", type=int, default=64,
+                    help="rows per prefill chunk (>= 16: routed experts run as block-scaled tcgen05 grouped GEMMs)")
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
     ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     ap.add_argument("--emulate-tp", type=int, default=0,
@@ -90,7 +92,7 @@ def main():
                       dspark_target_layer_ids=tuple(range(max(0, L - 3), L)) if args.spec else (),
                       dspark_block_size=5 if args.spec else 0, n_routed_experts=args.experts).validate()
     eng = Dsv41Engine(cfg, SyntheticDsv41Source(cfg, dev), model_rank, model_world, dev, allreduce,
-                      max_ctx=args.prompt_len + 1024)
+                      max_ctx=args.prompt_len + 1024, max_rows=args.max_rows)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist()
     torch.cuda.synchronize()
@@ -99,7 +101,7 @@ def main():
     eng.prefill(prompt)
     p1.record()
     torch.cuda.synchronize()
-    prefill_ms = p0.elapsed_time(p1)   # chunked prefill of the prompt (eager launches, 8 rows per chunk)
+    prefill_ms = p0.elapsed_time(p1)   # chunked prefill of the prompt (eager launches, --max-rows rows per chunk)
     step = (lambda: eng.spec_step()) if args.spec else (lambda: eng.step_plain())
     for _ in range(max(args.warmup, 3)):
         step()
@@ -135,6 +137,7 @@ def main():
                                                           "topk": cfg.n_activated_experts, "context": args.prompt_len,
                                                           "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl),
                                                           "emulated_tp": args.emulate_tp, "engram": "left out",
+                                                          "prefill_rows_per_chunk": args.max_rows,
                                                           "prefill_ms": round(prefill_ms, 2),
                                                           "prefill_ms_per_token": round(prefill_ms / args.prompt_len, 4),
                                                           }}))

@@ -133,27 +133,32 @@ def test_sort_quant_swiglu_combine_glue():
 
 
 def test_dsv41_prefill_through_block_scaled_experts_matches_decode_kernels():
-    """The tiny DSV41 model prefilled in 16-row chunks (routed experts as block-scaled tcgen05 grouped GEMMs, quad-
-    interleaved weights, 64-value k tail) against 8-row chunks (weight-streaming decode kernels): same logits up to
-    summation order, same greedy tokens."""
+    """The tiny DSV41 model prefilled in 16-row chunks with the routed experts as block-scaled tcgen05 grouped GEMMs
+    (quad-interleaved weights, 64-value k tail) against the same chunks through the weight-streaming kernels: both
+    multiply the same e2m1 x e4m3 values, so the logits agree up to summation order."""
     from ferrite_b200.models.dsv41 import DictWeights, Dsv41DeviceModel
     from ferrite_b200.models.dsv41_config import Dsv41Config
     from ferrite_b200.models.dsv41_weights import random_weights
+    from ferrite_b200.utils.switches import Switches, set_switches
     cfg = Dsv41Config.tiny()
     w = random_weights(cfg, 4)
     ids = torch.randint(0, cfg.vocab_size - 20, (32,), generator=torch.Generator().manual_seed(3)).tolist()
     logits = {}
-    for rows in (8, 16):
-        dev = Dsv41DeviceModel(cfg, DictWeights(w), max_rows=rows, max_ctx=128)
-        assert any(L.get("mx") for L in dev.layers) == (rows == 16)
-        out = []
-        for i in range(0, len(ids), rows):
-            c = ids[i:i + rows]
-            dev.forward(dev.make_rows([0], [len(c)]), torch.tensor(c, dtype=torch.int32, device="cuda"))
-            out.append(dev.ws["logits"][:len(c)].cpu().clone())
-        torch.cuda.synchronize()
-        assert int(dev.tc_status[0]) == 0
-        logits[rows] = torch.cat(out)
-    a, b = logits[16], logits[8]
-    assert (a - b).abs().max().item() < 0.1 * b.abs().max().item(), (a - b).abs().max().item()
-    assert (a.argmax(-1) == b.argmax(-1)).float().mean() > 0.9
+    try:
+        for mx_rows in (0, 16):
+            set_switches(Switches(d4_mx_min_rows=mx_rows))
+            dev = Dsv41DeviceModel(cfg, DictWeights(w), max_rows=16, max_ctx=128)
+            assert any(L.get("mx") for L in dev.layers) == (mx_rows > 0)
+            out = []
+            for i in range(0, len(ids), 16):
+                c = ids[i:i + 16]
+                dev.forward(dev.make_rows([0], [len(c)]), torch.tensor(c, dtype=torch.int32, device="cuda"))
+                out.append(dev.ws["logits"][:len(c)].cpu().clone())
+            torch.cuda.synchronize()
+            assert int(dev.tc_status[0]) == 0
+            logits[mx_rows] = torch.cat(out)
+    finally:
+        set_switches(None)
+    a, b = logits[16], logits[0]
+    assert (a - b).abs().max().item() < 2e-3 * b.abs().max().item(), (a - b).abs().max().item()
+    assert torch.equal(a.argmax(-1), b.argmax(-1))
