@@ -237,3 +237,331 @@ FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, con
 #undef GDN_ARGS
     return FB_LAUNCH_CHECK();
 }
+
+// ---- WY-chunked scan for prefill-sized groups ------------------------------------------------------
+// The recurrence above costs a dozen block-wide barriers per token; over a prompt that serial chain is the whole
+// cost (2.4 us per token and layer).  Here a CTA (one head of one sequence, state [dk x dv] resident in shared
+// memory) advances C = 32 tokens at a time with matrix products (crates/ferrite-kernel/src/wyf.rs:38-147 is the
+// reference's statement of the same algebra for its older decay form):
+//   L[t]   = sum_{r <= t} g[r]                 per-channel log decay, cumulative inside the chunk (all <= 0)
+//   K+ = k * e^{L - Lref},  K- = k * e^{Lref - L},  Q+ = q * e^{L - Lref}      Lref = L[15]: every exponent stays
+//                                                                             inside +-80, no overflow for g >= -5
+//   S' = diag(e^{Lref}) S0
+//   B  = K+ S'            C = K+ K-^T (strictly lower)        M = Q+ K-^T (lower)
+//   W  = (I + diag(beta) C)^-1 diag(beta) (V - B)             inverse of a unit lower-triangular 32 x 32 matrix as
+//                                                             (I - A)(I + A^2)(I + A^4)(I + A^8)(I + A^16), A nilpotent
+//   O  = Q+ S' + M W      S_C = diag(e^{L[C-1] - Lref}) (S' + K-^T W)
+// All products are f32 FMAs on register tiles (2 x 4 or 8 x 4 outputs per thread, operands from shared memory): the
+// state is f32 and the oracle is the step recurrence, so no precision is given away to the tensor cores here.
+// About 4600 FMAs per thread and chunk against 32 x 12 barriers of the serial form.
+namespace {
+
+constexpr int kWyC = 32;      // tokens per chunk
+constexpr int kWyRef = 15;    // reference row of the decay exponents
+
+template <int DK>
+__global__ void __launch_bounds__(512, 1)
+gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __restrict__ fb, const float* __restrict__ gb,
+                 int ld_fg, const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                 const float* __restrict__ dt_bias, const float* __restrict__ o_norm_w, float* __restrict__ state,
+                 float* __restrict__ conv_state, const int* __restrict__ cur, const RowMeta* __restrict__ meta,
+                 const int* __restrict__ group_first, float* __restrict__ out, int ld_out, int H, int b_off, int nbuf,
+                 float lb, float eps, SplitBuf osp) {
+    PDL_PROLOGUE();
+    constexpr int C = kWyC;
+    constexpr int LDT = C + 1;                       // padded row of the small matrices
+    extern __shared__ __align__(16) float sm[];
+    float* S = sm;                                   // [DK][DK]   state, row = key channel, column = value channel
+    float* Qp = S + DK * DK;                         // [C][DK]
+    float* Kp = Qp + C * DK;                         // [C][DK]
+    float* Vb = Kp + C * DK;                         // [C][DK]    v, then beta (v - b)
+    float* Bm = Vb + C * DK;                         // [C][DK]    b, then w
+    float* Lb = Bm + C * DK;                         // [C][DK]    cumulative log decay
+    float* KmT = Lb + C * DK;                        // [DK][LDT]  K- transposed
+    float* Cm = KmT + DK * LDT;                      // [C][LDT]   A = beta C, then its powers
+    float* Mm = Cm + C * LDT;                        // [C][LDT]
+    float* Tm = Mm + C * LDT;                        // [C][LDT]   running product -> (I + A)^-1
+    float* Xm = Tm + C * LDT;                        // [C][LDT]   scratch
+    float* beta = Xm + C * LDT;                      // [C]
+    float* nq = beta + C;                            // [C]
+    float* nk = nq + C;                              // [C]
+    float* eref = nk + C;                            // [DK]
+    float* elast = eref + DK;                        // [DK]
+
+    const int h = blockIdx.x;
+    const int row0g = group_first[blockIdx.y];
+    const RowMeta m0 = meta[row0g];
+    const int slot = m0.slot, gsize = m0.gsize;
+    const int P = H * DK;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cbuf = (nbuf > 1) ? cur[slot] % nbuf : 0;
+    const size_t head_elems = (size_t)DK * DK;
+    float* st = state + ((size_t)slot * nbuf + cbuf) * H * head_elems + (size_t)h * head_elems;
+    const size_t cv_buf = (size_t)3 * P * 3;
+    float* cv = conv_state + ((size_t)slot * nbuf + cbuf) * cv_buf;
+
+    for (int i = tid; i < DK * DK; i += blockDim.x) S[i] = st[i];
+    const bool conv_owner = tid < 3 * DK;
+    const int ch = conv_owner ? (tid / DK) * P + h * DK + (tid % DK) : 0;
+    float hist[3] = {0.f, 0.f, 0.f}, cw[4] = {0.f, 0.f, 0.f, 0.f};
+    if (conv_owner) {
+        hist[0] = cv[(size_t)ch * 3]; hist[1] = cv[(size_t)ch * 3 + 1]; hist[2] = cv[(size_t)ch * 3 + 2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cw[i] = conv_w[(size_t)ch * 4 + i];
+    }
+    const float a_exp = __expf(a_log[h]);
+    const float qscale = rsqrtf((float)DK);
+    // register-tile mappings: (2 rows x 4 columns) of a [C x DK] product, (8 rows x 4 columns) of the state
+    constexpr int Q4 = DK / 4;                       // float4 columns per row
+    const bool rt_on = tid < (C / 2) * Q4;           // DK = 128: all 512 threads
+    const int rt_t = (tid / Q4) * 2, rt_c = (tid % Q4) * 4;
+    constexpr int SG = DK / 8;
+    const bool st_on = tid < SG * Q4;
+    const int st_i = (tid / Q4) * 8, st_c = (tid % Q4) * 4;
+
+    for (int c0 = 0; c0 < gsize; c0 += C) {
+        const int nc = min(C, gsize - c0);
+        const int row0 = row0g + c0;
+        // ---- A: conv + SiLU, decay prefix sums, beta ----
+        if (conv_owner) {
+            float* dstb = (tid / DK == 0) ? Qp : (tid / DK == 1 ? Kp : Vb);
+            const int e = tid % DK;
+            for (int t = 0; t < C; ++t) {
+                float val = 0.f;
+                if (t < nc) {
+                    const float xin = proj[(size_t)(row0 + t) * ld_proj + ch];
+                    val = cw[0] * hist[0] + cw[1] * hist[1] + cw[2] * hist[2] + cw[3] * xin;
+                    hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = xin;
+                    val = siluf_(val);
+                }
+                dstb[t * DK + e] = val;
+            }
+        } else if (tid < 4 * DK) {
+            const int e = tid - 3 * DK;
+            float L = 0.f;
+            const float db = dt_bias[h * DK + e];
+            for (int t = 0; t < C; ++t) {
+                if (t < nc) L += lb * sigmoidf_(a_exp * (fb[(size_t)(row0 + t) * ld_fg + h * DK + e] + db));
+                Lb[t * DK + e] = L;
+            }
+        }
+        if (tid < C) beta[tid] = tid < nc ? sigmoidf_(proj[(size_t)(row0 + tid) * ld_proj + b_off + h]) : 0.f;
+        __syncthreads();
+        // L2 norms of the q and k rows: warp per (row, q | k)
+        for (int w = warp; w < 2 * C; w += (int)(blockDim.x >> 5)) {
+            const float* src = (w < C ? Qp : Kp) + (w % C) * DK;
+            float ss = 0.f;
+            for (int e = lane; e < DK; e += 32) ss += src[e] * src[e];
+            ss = warp_sum(ss);
+            if (lane == 0) {
+                const float nrm = sqrtf(ss);
+                (w < C ? nq : nk)[w % C] = nrm > 0.f ? 1.f / nrm : 0.f;
+            }
+        }
+        if (tid < DK) {
+            const float lr = Lb[min(kWyRef, nc - 1) * DK + tid];
+            eref[tid] = expf(lr);
+            elast[tid] = expf(Lb[(nc - 1) * DK + tid] - lr);
+        }
+        __syncthreads();
+        for (int i = tid; i < C * DK; i += blockDim.x) {
+            const int t = i / DK, e = i % DK;
+            const float d = Lb[i] - Lb[min(kWyRef, nc - 1) * DK + e];
+            const float ep = expf(d), em = expf(-d);
+            const float kk = Kp[i] * nk[t];
+            Qp[i] = Qp[i] * nq[t] * qscale * ep;
+            Kp[i] = kk * ep;
+            KmT[e * LDT + t] = kk * em;
+        }
+        for (int i = tid; i < DK * DK; i += blockDim.x) S[i] *= eref[i / DK];
+        __syncthreads();
+        // ---- B: b = K+ S', o1 = Q+ S' (register tiles), C and M ----
+        float o1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (rt_on) {
+            float bt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+            for (int i = 0; i < DK; ++i) {
+                const float4 s4 = *reinterpret_cast<const float4*>(S + i * DK + rt_c);
+                const float k0 = Kp[rt_t * DK + i], k1 = Kp[(rt_t + 1) * DK + i];
+                const float q0 = Qp[rt_t * DK + i], q1 = Qp[(rt_t + 1) * DK + i];
+                bt[0][0] = fmaf(k0, s4.x, bt[0][0]); bt[0][1] = fmaf(k0, s4.y, bt[0][1]);
+                bt[0][2] = fmaf(k0, s4.z, bt[0][2]); bt[0][3] = fmaf(k0, s4.w, bt[0][3]);
+                bt[1][0] = fmaf(k1, s4.x, bt[1][0]); bt[1][1] = fmaf(k1, s4.y, bt[1][1]);
+                bt[1][2] = fmaf(k1, s4.z, bt[1][2]); bt[1][3] = fmaf(k1, s4.w, bt[1][3]);
+                o1[0][0] = fmaf(q0, s4.x, o1[0][0]); o1[0][1] = fmaf(q0, s4.y, o1[0][1]);
+                o1[0][2] = fmaf(q0, s4.z, o1[0][2]); o1[0][3] = fmaf(q0, s4.w, o1[0][3]);
+                o1[1][0] = fmaf(q1, s4.x, o1[1][0]); o1[1][1] = fmaf(q1, s4.y, o1[1][1]);
+                o1[1][2] = fmaf(q1, s4.z, o1[1][2]); o1[1][3] = fmaf(q1, s4.w, o1[1][3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                // Vb <- beta (v - b)
+                float4 v4 = *reinterpret_cast<float4*>(Vb + (rt_t + r) * DK + rt_c);
+                const float bb = beta[rt_t + r];
+                v4.x = bb * (v4.x - bt[r][0]); v4.y = bb * (v4.y - bt[r][1]);
+                v4.z = bb * (v4.z - bt[r][2]); v4.w = bb * (v4.w - bt[r][3]);
+                *reinterpret_cast<float4*>(Vb + (rt_t + r) * DK + rt_c) = v4;
+            }
+        }
+        // C[t][s] = K+_t . K-_s (s < t),  M[t][s] = Q+_t . K-_s (s <= t); A = beta C
+        for (int o = tid; o < C * C; o += blockDim.x) {
+            const int t = o / C, s2 = o % C;
+            float cc = 0.f, mm = 0.f;
+            if (s2 <= t) {
+#pragma unroll 4
+                for (int i = 0; i < DK; ++i) {
+                    const float km = KmT[i * LDT + s2];
+                    cc = fmaf(Kp[t * DK + i], km, cc);
+                    mm = fmaf(Qp[t * DK + i], km, mm);
+                }
+            }
+            const float a = (s2 < t) ? beta[t] * cc : 0.f;
+            Cm[t * LDT + s2] = a;
+            Mm[t * LDT + s2] = (s2 <= t) ? mm : 0.f;
+            Tm[t * LDT + s2] = (s2 == t ? 1.f : 0.f) - a;      // I - A
+        }
+        __syncthreads();
+        // ---- C: (I + A)^-1 = (I - A)(I + A^2)(I + A^4)(I + A^8)(I + A^16) ----
+        for (int pw = 0; pw < 4; ++pw) {
+            for (int o = tid; o < C * C; o += blockDim.x) {     // X = A A
+                const int t = o / C, s2 = o % C;
+                float a = 0.f;
+#pragma unroll 8
+                for (int j = 0; j < C; ++j) a = fmaf(Cm[t * LDT + j], Cm[j * LDT + s2], a);
+                Xm[t * LDT + s2] = a;
+            }
+            __syncthreads();
+            for (int o = tid; o < C * C; o += blockDim.x) Cm[(o / C) * LDT + o % C] = Xm[(o / C) * LDT + o % C];
+            __syncthreads();
+            for (int o = tid; o < C * C; o += blockDim.x) {     // X = T (I + A)
+                const int t = o / C, s2 = o % C;
+                float a = Tm[t * LDT + s2];
+#pragma unroll 8
+                for (int j = 0; j < C; ++j) a = fmaf(Tm[t * LDT + j], Cm[j * LDT + s2], a);
+                Xm[t * LDT + s2] = a;
+            }
+            __syncthreads();
+            for (int o = tid; o < C * C; o += blockDim.x) Tm[(o / C) * LDT + o % C] = Xm[(o / C) * LDT + o % C];
+            __syncthreads();
+        }
+        // ---- D: W = T U (U in Vb) -> Bm ----
+        if (rt_on) {
+            float wt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+            for (int s2 = 0; s2 < C; ++s2) {
+                const float4 u4 = *reinterpret_cast<const float4*>(Vb + s2 * DK + rt_c);
+                const float t0 = Tm[rt_t * LDT + s2], t1 = Tm[(rt_t + 1) * LDT + s2];
+                wt[0][0] = fmaf(t0, u4.x, wt[0][0]); wt[0][1] = fmaf(t0, u4.y, wt[0][1]);
+                wt[0][2] = fmaf(t0, u4.z, wt[0][2]); wt[0][3] = fmaf(t0, u4.w, wt[0][3]);
+                wt[1][0] = fmaf(t1, u4.x, wt[1][0]); wt[1][1] = fmaf(t1, u4.y, wt[1][1]);
+                wt[1][2] = fmaf(t1, u4.z, wt[1][2]); wt[1][3] = fmaf(t1, u4.w, wt[1][3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                *reinterpret_cast<float4*>(Bm + (rt_t + r) * DK + rt_c) = make_float4(wt[r][0], wt[r][1], wt[r][2], wt[r][3]);
+        }
+        __syncthreads();
+        // ---- E: O = o1 + M W, gated RMSNorm, store ----
+        if (rt_on) {
+#pragma unroll 4
+            for (int s2 = 0; s2 < C; ++s2) {
+                const float4 w4 = *reinterpret_cast<const float4*>(Bm + s2 * DK + rt_c);
+                const float m0 = Mm[rt_t * LDT + s2], m1 = Mm[(rt_t + 1) * LDT + s2];
+                o1[0][0] = fmaf(m0, w4.x, o1[0][0]); o1[0][1] = fmaf(m0, w4.y, o1[0][1]);
+                o1[0][2] = fmaf(m0, w4.z, o1[0][2]); o1[0][3] = fmaf(m0, w4.w, o1[0][3]);
+                o1[1][0] = fmaf(m1, w4.x, o1[1][0]); o1[1][1] = fmaf(m1, w4.y, o1[1][1]);
+                o1[1][2] = fmaf(m1, w4.z, o1[1][2]); o1[1][3] = fmaf(m1, w4.w, o1[1][3]);
+            }
+        }
+        // one row's DK columns are spread over Q4 consecutive threads (a whole warp for DK = 128)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float ss = rt_on ? o1[r][0] * o1[r][0] + o1[r][1] * o1[r][1] + o1[r][2] * o1[r][2] + o1[r][3] * o1[r][3] : 0.f;
+#pragma unroll
+            for (int off = Q4 / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            const int t = rt_t + r;
+            if (rt_on && t < nc) {
+                const float inv = rsqrtf(ss / DK + eps);
+                const int row = row0 + t;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int cidx = rt_c + j;
+                    const float gate = sigmoidf_(gb[(size_t)row * ld_fg + h * DK + cidx]);
+                    const float ov = o1[r][j] * inv * o_norm_w[cidx] * gate;
+                    out[(size_t)row * ld_out + h * DK + cidx] = ov;
+                    split_store(osp, row, h * DK + cidx, ov);
+                }
+            }
+        }
+        // ---- F: S = diag(elast) (S' + K-^T W) ----
+        if (st_on) {
+            float acc[8][4];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float4 s4 = *reinterpret_cast<const float4*>(S + (st_i + r) * DK + st_c);
+                acc[r][0] = s4.x; acc[r][1] = s4.y; acc[r][2] = s4.z; acc[r][3] = s4.w;
+            }
+#pragma unroll 2
+            for (int s2 = 0; s2 < C; ++s2) {
+                const float4 w4 = *reinterpret_cast<const float4*>(Bm + s2 * DK + st_c);
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float km = KmT[(st_i + r) * LDT + s2];
+                    acc[r][0] = fmaf(km, w4.x, acc[r][0]); acc[r][1] = fmaf(km, w4.y, acc[r][1]);
+                    acc[r][2] = fmaf(km, w4.z, acc[r][2]); acc[r][3] = fmaf(km, w4.w, acc[r][3]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float el = elast[st_i + r];
+                *reinterpret_cast<float4*>(S + (st_i + r) * DK + st_c) =
+                    make_float4(acc[r][0] * el, acc[r][1] * el, acc[r][2] * el, acc[r][3] * el);
+            }
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < DK * DK; i += blockDim.x) st[i] = S[i];
+    if (conv_owner) { cv[(size_t)ch * 3] = hist[0]; cv[(size_t)ch * 3 + 1] = hist[1]; cv[(size_t)ch * 3 + 2] = hist[2]; }
+}
+
+template <int DK>
+constexpr size_t wy_smem() {
+    return sizeof(float) * ((size_t)DK * DK + 5 * kWyC * DK + (size_t)DK * (kWyC + 1) + 4 * kWyC * (kWyC + 1) + 3 * kWyC + 2 * DK);
+}
+
+}  // namespace
+
+// Same contract as fb_gdn_fused without snapshots: rows of a group are contiguous and ordered, the group's state
+// and conv tail are read from and written to buffer cur % nbuf.  For prefill-sized groups (any size; 32 tokens per
+// chunk).  dk: 64 or 128.
+FB_API int fb_gdn_chunk(const float* proj, int64_t ld_proj, const float* fb, const float* gb, int64_t ld_fg,
+                        const float* conv_w, const float* a_log, const float* dt_bias, const float* o_norm_w, float* state,
+                        float* conv_state, const int* cur, const void* meta, const int* group_first, int64_t n_groups,
+                        float* out, int64_t ld_out, int64_t H, int64_t dk, int64_t b_off, int64_t nbuf, float lb, float eps,
+                        void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    dim3 grid((unsigned)H, (unsigned)n_groups);
+#define WY_ARGS proj, (int)ld_proj, fb, gb, (int)ld_fg, conv_w, a_log, dt_bias, o_norm_w, state, conv_state, cur, \
+        (const RowMeta*)meta, group_first, out, (int)ld_out, (int)H, (int)b_off, (int)nbuf, lb, eps, osp
+    if (dk == 128) {
+        static bool done = false;
+        if (!done) {
+            cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wy_smem<128>());
+            if (e != cudaSuccess) return (int)e;
+            done = true;
+        }
+        FB_LAUNCH((gdn_chunk_kernel<128>), grid, 512, wy_smem<128>(), st, WY_ARGS);
+    } else if (dk == 64) {
+        static bool done = false;
+        if (!done) {
+            cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wy_smem<64>());
+            if (e != cudaSuccess) return (int)e;
+            done = true;
+        }
+        FB_LAUNCH((gdn_chunk_kernel<64>), grid, 512, wy_smem<64>(), st, WY_ARGS);
+    } else {
+        return (int)cudaErrorInvalidValue;
+    }
+#undef WY_ARGS
+    return FB_LAUNCH_CHECK();
+}

@@ -362,6 +362,7 @@ class GlmDeviceModel:
         Il += (-Il) % 8
         ws["moe_act"] = self._z(M, cfg.num_experts_per_tok, Il)
         ws["moe_act_s"] = torch.zeros(4, M * cfg.num_experts_per_tok, Il, dtype=torch.int16, device=self.dev)
+        self.gdn_chunk_rows = switches().gdn_chunk_rows   # groups of at least this many rows take the WY-chunked scan
         self.moe_group_rows = 8      # more rows than this: group (row, slot) pairs by expert
         # from this row count the grouped experts run as tcgen05 GEMMs (fp8 weights widened to bf16 in shared memory,
         # csrc/kernels/fp8w_gemm.cu); below it the mma.sync grouped kernels (0 = never)
@@ -590,6 +591,14 @@ class GlmDeviceModel:
             self.gemv(L["fg_b"], proj, ws["gdn_fg"], n, 2 * P, r, group_rows=P, xcol=3 * P)
         gi = L["gdn_index"]
         core = ws["gdn_core"]
+        if not snapshots and rs.gsize_max >= self.gdn_chunk_rows > 0 and la.head_dim in (64, 128):
+            # prefill-sized groups: WY-chunked scan (32 tokens per step of matrix products instead of 32 serial steps)
+            self.K.call("fb_gdn_chunk", proj.f, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"],
+                        L["a_log"], L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
+                        rs.group_first, rs.n_groups, core.f, P, self.h_gdn, la.head_dim, 3 * P + 2 * r, self.nbuf,
+                        float(la.gate_lower_bound), float(cfg.rms_norm_eps), *core.sp(1))
+            self._out_gemv(L["o_proj"], core, n, H, P)
+            return
         self.K.call("fb_gdn_fused", proj.f, self.ld_gdn, ws["gdn_fg"], View(ws["gdn_fg"], P), 2 * P, L["conv_w"],
                     L["a_log"], L["dt_bias"], L["o_norm"], self.gdn_state[gi], self.conv_state[gi], self.cur, rs.meta,
                     rs.group_first, rs.n_groups, core.f, P, self.h_gdn, la.head_dim, 3 * P + 2 * r,

@@ -40,6 +40,7 @@ class Switches:
     hc_pre_wide: bool = True        # hyper-connection front as a column-parallel kernel fed by Gram partials
                                     # (-0.32 / -0.27 ms against the one-CTA-per-row kernel)
     l2_ahead: int = -1              # read-ahead distance of the weight-streaming kernels (-1 = library default)
+    gdn_chunk_rows: int = 16        # GatedDeltaNet: groups of at least this many rows use the WY-chunked scan (0 = never)
     moe_tc_rows: int = 64           # GLM routed experts: rows from which the tcgen05 grouped GEMM runs (0 = never)
     d4_mx_min_rows: int = 16        # DSV41 routed experts: rows from which the block-scaled tcgen05 grouped GEMM runs (0 = never)
     d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores

@@ -232,6 +232,42 @@ def test_gdn_fused(K, dk, H, groups, nbuf, snap):
         r0 += g
 
 
+@pytest.mark.parametrize("dk,H,groups", [(128, 2, [70]), (64, 3, [33, 5, 64]), (128, 1, [16, 1])])
+def test_gdn_chunk_wy_matches_recurrence(K, dk, H, groups):
+    """WY-chunked scan (32 tokens per step) against the fp32 step recurrence, with strong decays (gate floor -5)."""
+    r_lr, P, S, n = 16, H * dk, len(groups), sum(groups)
+    ld = 3 * P + 2 * r_lr + H
+    ld += (-ld) % 4
+    b_off = 3 * P + 2 * r_lr
+    proj = rnd(n, ld, seed=1)
+    fb, gb = rnd(n, P, seed=2, scale=3.0), rnd(n, P, seed=3)        # wide range of decays, down to e^-5 per token
+    conv_w = rnd(3 * P, 4, seed=4, scale=0.5)
+    a_log, dt_bias, o_norm = rnd(H, seed=5, scale=0.3), rnd(P, seed=6, scale=0.3), rnd(dk, seed=7).abs() + 0.5
+    state, conv_state = rnd(S, 1, H, dk, dk, seed=8, scale=0.2), rnd(S, 1, 3 * P, 3, seed=9)
+    cur = torch.zeros(S, dtype=torch.int32)
+    meta, gf, _, _ = make_meta(K, list(range(S)), groups, [10] * S)
+    sd, cd = dev(state.clone()), dev(conv_state.clone())
+    out = torch.zeros(n, P, device="cuda")
+    K.call("fb_gdn_chunk", dev(proj), ld, dev(fb), dev(gb), P, dev(conv_w), dev(a_log), dev(dt_bias), dev(o_norm),
+           sd, cd, dev(cur), meta, gf, S, out, P, H, dk, b_off, 1, -5.0, 1e-5, None, 0, 0, 0)
+    torch.cuda.synchronize()
+    r0 = 0
+    for gi, g in enumerate(groups):
+        rows = slice(r0, r0 + g)
+        co, tail = R.causal_conv1d(proj[rows, :3 * P], conv_w, conv_state[gi, 0])
+        co = torch.nn.functional.silu(co)
+        q, k, v = (co[:, i * P:(i + 1) * P].reshape(g, H, dk) for i in range(3))
+        q, k = R.l2norm_heads(q) * dk ** -0.5, R.l2norm_heads(k)
+        beta = torch.sigmoid(proj[rows, b_off:b_off + H])
+        gl = R.gdn_log_decay(fb[rows], dt_bias, a_log, -5.0, H)
+        core, s_new = R.gdn_recurrent(q, k, v, beta, gl, state[gi, 0])
+        want = R.gated_rmsnorm(core, gb[rows].view(g, H, dk), o_norm, 1e-5).reshape(g, P)
+        check(f"wy out g{gi}", out[rows], want, 5e-4)
+        check(f"wy state g{gi}", sd[gi, 0], s_new, 5e-4)
+        check(f"wy conv g{gi}", cd[gi, 0], tail, 1e-6)
+        r0 += g
+
+
 @pytest.mark.parametrize("E,topk", [(8, 2), (288, 8)])
 def test_moe_route(K, E, topk):
     n = 6
