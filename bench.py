@@ -130,7 +130,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the run invalid)")
     ap.add_argument("--no-mtp", action="store_true", help="plain greedy decode instead of MTP (side metric)")
     ap.add_argument("--experts-resident", type=int, default=0)
-    ap.add_argument("--prefill-rows", type=int, default=256, help="rows per prefill chunk")
+    ap.add_argument("--prefill-rows", type=int, default=1024, help="rows per prefill chunk")
     ap.add_argument("--moe-shard", default="inter", choices=["inter", "expert"],
                     help="routed experts split by intermediate columns (default) or by expert over the ranks")
     ap.add_argument("--fuse", default="full", choices=["full", "ar", "off"],
