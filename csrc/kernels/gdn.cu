@@ -323,25 +323,33 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
         const int nc = min(C, gsize - c0);
         const int row0 = row0g + c0;
         // ---- A: conv + SiLU, decay prefix sums, beta ----
+        // a thread's 32 global loads go in flight together (the serial part is arithmetic on registers)
         if (conv_owner) {
+            float xin[C];
+#pragma unroll
+            for (int t = 0; t < C; ++t) xin[t] = t < nc ? proj[(size_t)(row0 + t) * ld_proj + ch] : 0.f;
             float* dstb = (tid / DK == 0) ? Qp : (tid / DK == 1 ? Kp : Vb);
             const int e = tid % DK;
+#pragma unroll
             for (int t = 0; t < C; ++t) {
                 float val = 0.f;
                 if (t < nc) {
-                    const float xin = proj[(size_t)(row0 + t) * ld_proj + ch];
-                    val = cw[0] * hist[0] + cw[1] * hist[1] + cw[2] * hist[2] + cw[3] * xin;
-                    hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = xin;
+                    val = cw[0] * hist[0] + cw[1] * hist[1] + cw[2] * hist[2] + cw[3] * xin[t];
+                    hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = xin[t];
                     val = siluf_(val);
                 }
                 dstb[t * DK + e] = val;
             }
         } else if (tid < 4 * DK) {
             const int e = tid - 3 * DK;
+            float fv[C];
+#pragma unroll
+            for (int t = 0; t < C; ++t) fv[t] = t < nc ? fb[(size_t)(row0 + t) * ld_fg + h * DK + e] : 0.f;
             float L = 0.f;
             const float db = dt_bias[h * DK + e];
+#pragma unroll
             for (int t = 0; t < C; ++t) {
-                if (t < nc) L += lb * sigmoidf_(a_exp * (fb[(size_t)(row0 + t) * ld_fg + h * DK + e] + db));
+                if (t < nc) L += lb * sigmoidf_(a_exp * (fv[t] + db));
                 Lb[t * DK + e] = L;
             }
         }

@@ -37,7 +37,8 @@ struct Cfg {
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-               float* __restrict__ out, int ldo, int M, int N, int K, int accumulate, int* __restrict__ status) {
+               float* __restrict__ out, int ldo, int M, int N, int K, int accumulate, int group_rows,
+               int* __restrict__ status) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;  // SW128 tiles need 1024-byte alignment
@@ -52,6 +53,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const int n0 = blockIdx.x * kTileW;
     const int m0 = blockIdx.y * BN;
     const int nkb = (K + kBK - 1) / kBK;
+    const int xk0 = group_rows > 0 ? (n0 / group_rows) * K : 0;   // block-diagonal: group g reads x columns [g K, (g + 1) K)
 
     if (threadIdx.x == 0) {
         s_fail = 0;
@@ -78,7 +80,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             const uint32_t a = base + s * C::kStageBytes, b = a + C::kABytes;
             tc::mbar_expect_tx(full(s), C::kStageBytes);
             tc::tma_load_2d(a, &tmap_w, kb * kBK, n0, full(s));
-            tc::tma_load_2d(b, &tmap_x, kb * kBK, m0, full(s));
+            tc::tma_load_2d(b, &tmap_x, xk0 + kb * kBK, m0, full(s));
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
@@ -133,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
 template <int BN>
 int launch_tc(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo, int M, int N, int K, int accumulate,
-              int* status, cudaStream_t st) {
+              int group_rows, int* status, cudaStream_t st) {
     auto k = gemm_tc_kernel<BN>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -142,7 +144,7 @@ int launch_tc(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo,
         attr_done = true;
     }
     dim3 grid((N + kTileW - 1) / kTileW, (M + BN - 1) / BN);
-    FB_LAUNCH((k), grid, kThreads, Cfg<BN>::kSmem, st, tw, tx, out, ldo, M, N, K, accumulate, status);
+    FB_LAUNCH((k), grid, kThreads, Cfg<BN>::kSmem, st, tw, tx, out, ldo, M, N, K, accumulate, group_rows, status);
     return FB_LAUNCH_CHECK();
 }
 
@@ -150,22 +152,32 @@ int launch_tc(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo,
 
 // W [N, K] bf16 row-major, x [M, K] bf16 row-major (row stride ldx elements), out [M, N] f32.
 // K % 8 == 0, ldx % 8 == 0, 16-byte aligned bases.  status: int[4] device buffer.
-FB_API int fb_gemm_tc_bf16(const void* W, const void* x, int64_t ldx, float* out, int64_t ldo, int64_t M, int64_t N,
-                           int64_t K, int64_t accumulate, int* status, cudaStream_t st) {
+// group_rows > 0: block-diagonal form, rows [g group_rows, (g + 1) group_rows) of W contract with x columns
+// [g K, (g + 1) K); group_rows % 128 == 0, K % 64 == 0, N % group_rows == 0.
+FB_API int fb_gemm_tc_bf16_grouped(const void* W, const void* x, int64_t ldx, float* out, int64_t ldo, int64_t M, int64_t N,
+                                   int64_t K, int64_t group_rows, int64_t accumulate, int* status, cudaStream_t st) {
     if ((K % 8) || (ldx % 8) || M < 1) return (int)cudaErrorInvalidValue;
+    if (group_rows > 0 && ((group_rows % kTileW) || (K % kBK) || (N % group_rows))) return (int)cudaErrorInvalidValue;
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const uint64_t xcols = group_rows > 0 ? (uint64_t)(N / group_rows) * (uint64_t)K : (uint64_t)K;
     CUtensorMap tw, tx;
     int rc = fb_make_tmap_2d(&tw, W, (uint64_t)N, (uint64_t)K, kTileW, kBK, 2);
     if (rc) return rc;
-    rc = fb_make_tmap_2d_strided(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, kBK, 2);
+    rc = fb_make_tmap_2d_strided(&tx, x, (uint64_t)M, xcols, (uint64_t)ldx, (uint32_t)bn, kBK, 2);
     if (rc) return rc;
+    const int g = (int)group_rows;
     switch (bn) {
-        case 16: return launch_tc<16>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
-        case 32: return launch_tc<32>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
-        case 64: return launch_tc<64>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
-        case 128: return launch_tc<128>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
-        default: return launch_tc<256>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, status, st);
+        case 16: return launch_tc<16>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, g, status, st);
+        case 32: return launch_tc<32>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, g, status, st);
+        case 64: return launch_tc<64>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, g, status, st);
+        case 128: return launch_tc<128>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, g, status, st);
+        default: return launch_tc<256>(tw, tx, out, (int)ldo, (int)M, (int)N, (int)K, (int)accumulate, g, status, st);
     }
+}
+
+FB_API int fb_gemm_tc_bf16(const void* W, const void* x, int64_t ldx, float* out, int64_t ldo, int64_t M, int64_t N,
+                           int64_t K, int64_t accumulate, int* status, cudaStream_t st) {
+    return fb_gemm_tc_bf16_grouped(W, x, ldx, out, ldo, M, N, K, 0, accumulate, status, st);
 }
 
 // ---- decode-sized row counts: split-K tcgen05 GEMV ----------------------------------------------

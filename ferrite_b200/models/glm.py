@@ -455,6 +455,16 @@ class GlmDeviceModel:
         tc_max_n = getattr(self, "tc_gemv_max_n", 0)   # 9-16 rows: matrices with few row tiles leave the plain GEMM with few CTAs
         tc_gemv = (use_mma and not fp8 and group_rows == 0 and 8 < m <= 16 and K % 64 == 0
                    and ((tc_min_n and N >= tc_min_n) or (tc_max_n and N <= tc_max_n)))
+        if (use_mma and not fp8 and group_rows > 0 and group_rows % 128 == 0 and N % group_rows == 0
+                and m >= self.tc_min_rows):
+            # a block-diagonal projection at prefill row counts: the tcgen05 GEMM picks each tile's x columns by group
+            xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)
+            op = _lib.ctypes.c_void_p(of.data_ptr() + ocol * 4)
+            self.K.call("fb_gemm_tc_bf16_grouped", w, xp, ldx, op, ldo, m, N, K, group_rows, int(accumulate), self.tc_status)
+            if oa is not None and omask:
+                self.K.call("fb_split_rows", op, ldo, _lib.ctypes.c_void_p(oa.s.data_ptr() + ocol * 2), ldo, oa.plane,
+                            omask, m, N)
+            return
         if use_mma and not fp8 and group_rows == 0 and m >= self.tc_min_rows and not tc_gemv:
             # prefill-sized row counts: TMA + tcgen05 GEMM over the bf16 high plane of the activations
             xp = _lib.ctypes.c_void_p(xa.s.data_ptr() + xcol * 2)

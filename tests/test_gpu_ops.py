@@ -663,6 +663,20 @@ def test_gemm_tcgen05_bf16(K, M, N, K_):
     check("gemm tc acc", out, 2 * want, 4e-3 * max(1.0, want.abs().max().item()))
 
 
+@pytest.mark.parametrize("M,G,gr,K_", [(40, 2, 1024, 128), (300, 8, 512, 192), (17, 4, 256, 512)])
+def test_gemm_tcgen05_block_diagonal(K, M, G, gr, K_):
+    """Grouped form of the tcgen05 GEMM: rows of group g contract with x columns [g K, (g + 1) K)."""
+    w = rnd(G * gr, K_, seed=3, scale=0.1).bfloat16()
+    x = rnd(M, G * K_ + 64, seed=4).bfloat16()            # wider rows than the groups use
+    out = torch.zeros(M, G * gr, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    K.call("fb_gemm_tc_bf16_grouped", dev(w), dev(x), x.shape[1], out, G * gr, M, G * gr, K_, gr, 0, status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0, f"kernel reported {status.tolist()}"
+    want = torch.cat([x[:, g * K_:(g + 1) * K_].float() @ w[g * gr:(g + 1) * gr].float().t() for g in range(G)], dim=1)
+    check("gemm tc grouped", out, want, 2e-3 * max(1.0, want.abs().max().item()))
+
+
 @pytest.mark.parametrize("fp8", [False, True])
 def test_gemv_ar_fold_single_rank(K, fp8):
     """Fused GEMV + hyper-connection fold (world = 1: no collective) against the separate ops."""
