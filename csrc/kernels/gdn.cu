@@ -246,18 +246,25 @@ FB_API int fb_gdn_fused(const float* proj, int64_t ld_proj, const float* fb, con
 //   L[t]   = sum_{r <= t} g[r]                 per-channel log decay, cumulative inside the chunk (all <= 0)
 //   K+ = k * e^{L - Lref},  K- = k * e^{Lref - L},  Q+ = q * e^{L - Lref}      Lref = L[15]: every exponent stays
 //                                                                             inside +-80, no overflow for g >= -5
-//   S' = diag(e^{Lref}) S0
-//   B  = K+ S'            C = K+ K-^T (strictly lower)        M = Q+ K-^T (lower)
-//   W  = (I + diag(beta) C)^-1 diag(beta) (V - B)             inverse of a unit lower-triangular 32 x 32 matrix as
-//                                                             (I - A)(I + A^2)(I + A^4)(I + A^8)(I + A^16), A nilpotent
-//   O  = Q+ S' + M W      S_C = diag(e^{L[C-1] - Lref}) (S' + K-^T W)
-// All products are f32 FMAs on register tiles (2 x 4 or 8 x 4 outputs per thread, operands from shared memory): the
-// state is f32 and the oracle is the step recurrence, so no precision is given away to the tensor cores here.
-// About 4600 FMAs per thread and chunk against 32 x 12 barriers of the serial form.
+//   Kb = k * e^{L},  Qb = q * e^{L}            the decayed rows that meet the chunk's incoming state S0
+//   B  = Kb S0            C = K+ K-^T (strictly lower)        M = Q+ K-^T (lower)
+//   W  = (I + diag(beta) C)^-1 diag(beta) (V - B)             forward substitution down the 32 rows, one thread per
+//                                                             value channel with its column of W in registers
+//   O  = Qb S0 + M W      S_C = diag(e^{L[C-1]}) S0 + diag(e^{L[C-1] - Lref}) K-^T W
+// All products are f32 FMAs on register tiles: the state is f32 and the oracle is the step recurrence, so no
+// precision is given away to the tensor cores here.  Shared memory bandwidth, not the FMA pipe, bounds a naive
+// tiling (one LDS per two FMAs): the tiles below are 4 x 4 (B, O) and 8 x 4 (state) outputs per thread with the
+// broadcast operand read four reduction steps at a time (LDS.128), which leaves the FMAs as the longer side.
+// B / O run on half of the CTA while the other half builds C and M.
 namespace {
 
 constexpr int kWyC = 32;      // tokens per chunk
 constexpr int kWyRef = 15;    // reference row of the decay exponents
+
+__device__ __forceinline__ float dot4(const float4& a, const float4& b) {
+    return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+__device__ __forceinline__ float f4c(const float4& a, int i) { return i == 0 ? a.x : i == 1 ? a.y : i == 2 ? a.z : a.w; }
 
 template <int DK>
 __global__ void __launch_bounds__(512, 1)
@@ -269,24 +276,24 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
                  float lb, float eps, SplitBuf osp) {
     PDL_PROLOGUE();
     constexpr int C = kWyC;
-    constexpr int LDT = C + 1;                       // padded row of the small matrices
+    constexpr int LDK = DK + 4;                      // padded row of K-: float4 reads by 8 lanes hit 32 distinct banks
     extern __shared__ __align__(16) float sm[];
     float* S = sm;                                   // [DK][DK]   state, row = key channel, column = value channel
-    float* Qp = S + DK * DK;                         // [C][DK]
-    float* Kp = Qp + C * DK;                         // [C][DK]
-    float* Vb = Kp + C * DK;                         // [C][DK]    v, then beta (v - b)
-    float* Bm = Vb + C * DK;                         // [C][DK]    b, then w
-    float* Lb = Bm + C * DK;                         // [C][DK]    cumulative log decay
-    float* KmT = Lb + C * DK;                        // [DK][LDT]  K- transposed
-    float* Cm = KmT + DK * LDT;                      // [C][LDT]   A = beta C, then its powers
-    float* Mm = Cm + C * LDT;                        // [C][LDT]
-    float* Tm = Mm + C * LDT;                        // [C][LDT]   running product -> (I + A)^-1
-    float* Xm = Tm + C * LDT;                        // [C][LDT]   scratch
-    float* beta = Xm + C * LDT;                      // [C]
+    float* Qp = S + DK * DK;                         // [C][DK]    Q+
+    float* Kp = Qp + C * DK;                         // [C][DK]    K+
+    float* Qb = Kp + C * DK;                         // [C][DK]
+    float* Kb = Qb + C * DK;                         // [C][DK]
+    float* Vb = Kb + C * DK;                         // [C][DK]    v, then beta (v - b)
+    float* Bm = Vb + C * DK;                         // [C][DK]    cumulative log decay L, later W
+    float* Lb = Bm;
+    float* Km = Bm + C * DK;                         // [C][LDK]   K-
+    float* Cm = Km + C * LDK;                        // [C][C]     A = diag(beta) C
+    float* Mm = Cm + C * C;                          // [C][C]
+    float* beta = Mm + C * C;                        // [C]
     float* nq = beta + C;                            // [C]
     float* nk = nq + C;                              // [C]
-    float* eref = nk + C;                            // [DK]
-    float* elast = eref + DK;                        // [DK]
+    float* eref = nk + C;                            // [DK]  e^{Lref}
+    float* elast = eref + DK;                        // [DK]  e^{L[C-1] - Lref}
 
     const int h = blockIdx.x;
     const int row0g = group_first[blockIdx.y];
@@ -311,10 +318,11 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
     }
     const float a_exp = __expf(a_log[h]);
     const float qscale = rsqrtf((float)DK);
-    // register-tile mappings: (2 rows x 4 columns) of a [C x DK] product, (8 rows x 4 columns) of the state
+    // register-tile mappings: (4 rows x 4 columns) of a [C x DK] product, (8 rows x 4 columns) of the state
     constexpr int Q4 = DK / 4;                       // float4 columns per row
-    const bool rt_on = tid < (C / 2) * Q4;           // DK = 128: all 512 threads
-    const int rt_t = (tid / Q4) * 2, rt_c = (tid % Q4) * 4;
+    constexpr int NB = (C / 4) * Q4;                 // threads of the B / O tiles (DK = 128: 256)
+    const bool rt_on = tid < NB;
+    const int rt_t = (tid / Q4) * 4, rt_c = (tid % Q4) * 4;
     constexpr int SG = DK / 8;
     const bool st_on = tid < SG * Q4;
     const int st_i = (tid / Q4) * 8, st_c = (tid % Q4) * 4;
@@ -322,6 +330,7 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
     for (int c0 = 0; c0 < gsize; c0 += C) {
         const int nc = min(C, gsize - c0);
         const int row0 = row0g + c0;
+        const int tref = min(kWyRef, nc - 1);
         // ---- A: conv + SiLU, decay prefix sums, beta ----
         // a thread's 32 global loads go in flight together (the serial part is arithmetic on registers)
         if (conv_owner) {
@@ -367,42 +376,60 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
             }
         }
         if (tid < DK) {
-            const float lr = Lb[min(kWyRef, nc - 1) * DK + tid];
+            const float lr = Lb[tref * DK + tid];
             eref[tid] = expf(lr);
             elast[tid] = expf(Lb[(nc - 1) * DK + tid] - lr);
         }
         __syncthreads();
         for (int i = tid; i < C * DK; i += blockDim.x) {
             const int t = i / DK, e = i % DK;
-            const float d = Lb[i] - Lb[min(kWyRef, nc - 1) * DK + e];
+            const float d = Lb[i] - Lb[tref * DK + e];
             const float ep = expf(d), em = expf(-d);
+            const float ea = ep * eref[e];
             const float kk = Kp[i] * nk[t];
-            Qp[i] = Qp[i] * nq[t] * qscale * ep;
+            const float qq = Qp[i] * nq[t] * qscale;
+            Qp[i] = qq * ep;
             Kp[i] = kk * ep;
-            KmT[e * LDT + t] = kk * em;
+            Qb[i] = qq * ea;
+            Kb[i] = kk * ea;
+            Km[t * LDK + e] = kk * em;
         }
-        for (int i = tid; i < DK * DK; i += blockDim.x) S[i] *= eref[i / DK];
         __syncthreads();
-        // ---- B: b = K+ S', o1 = Q+ S' (register tiles), C and M ----
-        float o1[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // ---- B: b = Kb S0, o1 = Qb S0 on the first NB threads; C and M on the others ----
+        float o1[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o1[r][j] = 0.f;
         if (rt_on) {
-            float bt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
-            for (int i = 0; i < DK; ++i) {
-                const float4 s4 = *reinterpret_cast<const float4*>(S + i * DK + rt_c);
-                const float k0 = Kp[rt_t * DK + i], k1 = Kp[(rt_t + 1) * DK + i];
-                const float q0 = Qp[rt_t * DK + i], q1 = Qp[(rt_t + 1) * DK + i];
-                bt[0][0] = fmaf(k0, s4.x, bt[0][0]); bt[0][1] = fmaf(k0, s4.y, bt[0][1]);
-                bt[0][2] = fmaf(k0, s4.z, bt[0][2]); bt[0][3] = fmaf(k0, s4.w, bt[0][3]);
-                bt[1][0] = fmaf(k1, s4.x, bt[1][0]); bt[1][1] = fmaf(k1, s4.y, bt[1][1]);
-                bt[1][2] = fmaf(k1, s4.z, bt[1][2]); bt[1][3] = fmaf(k1, s4.w, bt[1][3]);
-                o1[0][0] = fmaf(q0, s4.x, o1[0][0]); o1[0][1] = fmaf(q0, s4.y, o1[0][1]);
-                o1[0][2] = fmaf(q0, s4.z, o1[0][2]); o1[0][3] = fmaf(q0, s4.w, o1[0][3]);
-                o1[1][0] = fmaf(q1, s4.x, o1[1][0]); o1[1][1] = fmaf(q1, s4.y, o1[1][1]);
-                o1[1][2] = fmaf(q1, s4.z, o1[1][2]); o1[1][3] = fmaf(q1, s4.w, o1[1][3]);
+            float bt[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bt[r][j] = 0.f;
+#pragma unroll 1
+            for (int i4 = 0; i4 < DK; i4 += 4) {
+                float4 kx[4], qx[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    kx[r] = *reinterpret_cast<const float4*>(Kb + (rt_t + r) * DK + i4);
+                    qx[r] = *reinterpret_cast<const float4*>(Qb + (rt_t + r) * DK + i4);
+                }
+#pragma unroll
+                for (int ii = 0; ii < 4; ++ii) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(S + (i4 + ii) * DK + rt_c);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float kv = f4c(kx[r], ii), qv = f4c(qx[r], ii);
+                        bt[r][0] = fmaf(kv, s4.x, bt[r][0]); bt[r][1] = fmaf(kv, s4.y, bt[r][1]);
+                        bt[r][2] = fmaf(kv, s4.z, bt[r][2]); bt[r][3] = fmaf(kv, s4.w, bt[r][3]);
+                        o1[r][0] = fmaf(qv, s4.x, o1[r][0]); o1[r][1] = fmaf(qv, s4.y, o1[r][1]);
+                        o1[r][2] = fmaf(qv, s4.z, o1[r][2]); o1[r][3] = fmaf(qv, s4.w, o1[r][3]);
+                    }
+                }
             }
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
+            for (int r = 0; r < 4; ++r) {
                 // Vb <- beta (v - b)
                 float4 v4 = *reinterpret_cast<float4*>(Vb + (rt_t + r) * DK + rt_c);
                 const float bb = beta[rt_t + r];
@@ -410,120 +437,122 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
                 v4.z = bb * (v4.z - bt[r][2]); v4.w = bb * (v4.w - bt[r][3]);
                 *reinterpret_cast<float4*>(Vb + (rt_t + r) * DK + rt_c) = v4;
             }
-        }
-        // C[t][s] = K+_t . K-_s (s < t),  M[t][s] = Q+_t . K-_s (s <= t); A = beta C
-        for (int o = tid; o < C * C; o += blockDim.x) {
-            const int t = o / C, s2 = o % C;
-            float cc = 0.f, mm = 0.f;
-            if (s2 <= t) {
-#pragma unroll 4
-                for (int i = 0; i < DK; ++i) {
-                    const float km = KmT[i * LDT + s2];
-                    cc = fmaf(Kp[t * DK + i], km, cc);
-                    mm = fmaf(Qp[t * DK + i], km, mm);
+        } else {
+            // C[t][s] = K+_t . K-_s (s < t),  M[t][s] = Q+_t . K-_s (s <= t); A = beta C.  A thread owns rows
+            // (ta, ta + 16) x columns (sb, sb + 16); the (ta, sb + 16) corner is above the diagonal.
+            for (int blk = tid - NB; blk < (C / 2) * (C / 2); blk += (int)blockDim.x - NB) {
+                const int ta = blk / (C / 2), sb = blk % (C / 2);
+                float cc0 = 0.f, cc1 = 0.f, cc2 = 0.f, mm0 = 0.f, mm1 = 0.f, mm2 = 0.f;
+#pragma unroll 2
+                for (int i4 = 0; i4 < DK; i4 += 4) {
+                    const float4 k0 = *reinterpret_cast<const float4*>(Kp + ta * DK + i4);
+                    const float4 k1 = *reinterpret_cast<const float4*>(Kp + (ta + C / 2) * DK + i4);
+                    const float4 q0 = *reinterpret_cast<const float4*>(Qp + ta * DK + i4);
+                    const float4 q1 = *reinterpret_cast<const float4*>(Qp + (ta + C / 2) * DK + i4);
+                    const float4 n0 = *reinterpret_cast<const float4*>(Km + sb * LDK + i4);
+                    const float4 n1 = *reinterpret_cast<const float4*>(Km + (sb + C / 2) * LDK + i4);
+                    cc0 += dot4(k0, n0); mm0 += dot4(q0, n0);
+                    cc1 += dot4(k1, n0); mm1 += dot4(q1, n0);
+                    cc2 += dot4(k1, n1); mm2 += dot4(q1, n1);
                 }
+                const int tb = ta + C / 2, sc = sb + C / 2;
+                Cm[ta * C + sb] = sb < ta ? beta[ta] * cc0 : 0.f;
+                Mm[ta * C + sb] = sb <= ta ? mm0 : 0.f;
+                Cm[ta * C + sc] = 0.f;
+                Mm[ta * C + sc] = 0.f;
+                Cm[tb * C + sb] = beta[tb] * cc1;
+                Mm[tb * C + sb] = mm1;
+                Cm[tb * C + sc] = sb < ta ? beta[tb] * cc2 : 0.f;
+                Mm[tb * C + sc] = sb <= ta ? mm2 : 0.f;
             }
-            const float a = (s2 < t) ? beta[t] * cc : 0.f;
-            Cm[t * LDT + s2] = a;
-            Mm[t * LDT + s2] = (s2 <= t) ? mm : 0.f;
-            Tm[t * LDT + s2] = (s2 == t ? 1.f : 0.f) - a;      // I - A
         }
         __syncthreads();
-        // ---- C: (I + A)^-1 = (I - A)(I + A^2)(I + A^4)(I + A^8)(I + A^16) ----
-        for (int pw = 0; pw < 4; ++pw) {
-            for (int o = tid; o < C * C; o += blockDim.x) {     // X = A A
-                const int t = o / C, s2 = o % C;
-                float a = 0.f;
-#pragma unroll 8
-                for (int j = 0; j < C; ++j) a = fmaf(Cm[t * LDT + j], Cm[j * LDT + s2], a);
-                Xm[t * LDT + s2] = a;
-            }
-            __syncthreads();
-            for (int o = tid; o < C * C; o += blockDim.x) Cm[(o / C) * LDT + o % C] = Xm[(o / C) * LDT + o % C];
-            __syncthreads();
-            for (int o = tid; o < C * C; o += blockDim.x) {     // X = T (I + A)
-                const int t = o / C, s2 = o % C;
-                float a = Tm[t * LDT + s2];
-#pragma unroll 8
-                for (int j = 0; j < C; ++j) a = fmaf(Tm[t * LDT + j], Cm[j * LDT + s2], a);
-                Xm[t * LDT + s2] = a;
-            }
-            __syncthreads();
-            for (int o = tid; o < C * C; o += blockDim.x) Tm[(o / C) * LDT + o % C] = Xm[(o / C) * LDT + o % C];
-            __syncthreads();
-        }
-        // ---- D: W = T U (U in Vb) -> Bm ----
-        if (rt_on) {
-            float wt[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll 4
-            for (int s2 = 0; s2 < C; ++s2) {
-                const float4 u4 = *reinterpret_cast<const float4*>(Vb + s2 * DK + rt_c);
-                const float t0 = Tm[rt_t * LDT + s2], t1 = Tm[(rt_t + 1) * LDT + s2];
-                wt[0][0] = fmaf(t0, u4.x, wt[0][0]); wt[0][1] = fmaf(t0, u4.y, wt[0][1]);
-                wt[0][2] = fmaf(t0, u4.z, wt[0][2]); wt[0][3] = fmaf(t0, u4.w, wt[0][3]);
-                wt[1][0] = fmaf(t1, u4.x, wt[1][0]); wt[1][1] = fmaf(t1, u4.y, wt[1][1]);
-                wt[1][2] = fmaf(t1, u4.z, wt[1][2]); wt[1][3] = fmaf(t1, u4.w, wt[1][3]);
-            }
+        // ---- C: (I + A) W = U by forward substitution; thread c keeps column c of W in registers ----
+        if (tid < DK) {
+            float w[C];
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
-                *reinterpret_cast<float4*>(Bm + (rt_t + r) * DK + rt_c) = make_float4(wt[r][0], wt[r][1], wt[r][2], wt[r][3]);
+            for (int t = 0; t < C; ++t) {
+                float a0 = Vb[t * DK + tid], a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int s4 = 0; s4 < t; s4 += 4) {
+                    const float4 a = *reinterpret_cast<const float4*>(Cm + t * C + s4);   // same address in every lane
+                    a0 = fmaf(-a.x, w[s4], a0);
+                    if (s4 + 1 < t) a1 = fmaf(-a.y, w[s4 + 1], a1);
+                    if (s4 + 2 < t) a2 = fmaf(-a.z, w[s4 + 2], a2);
+                    if (s4 + 3 < t) a3 = fmaf(-a.w, w[s4 + 3], a3);
+                }
+                w[t] = (a0 + a1) + (a2 + a3);
+                Bm[t * DK + tid] = w[t];
+            }
         }
         __syncthreads();
         // ---- E: O = o1 + M W, gated RMSNorm, store ----
         if (rt_on) {
-#pragma unroll 4
-            for (int s2 = 0; s2 < C; ++s2) {
-                const float4 w4 = *reinterpret_cast<const float4*>(Bm + s2 * DK + rt_c);
-                const float m0 = Mm[rt_t * LDT + s2], m1 = Mm[(rt_t + 1) * LDT + s2];
-                o1[0][0] = fmaf(m0, w4.x, o1[0][0]); o1[0][1] = fmaf(m0, w4.y, o1[0][1]);
-                o1[0][2] = fmaf(m0, w4.z, o1[0][2]); o1[0][3] = fmaf(m0, w4.w, o1[0][3]);
-                o1[1][0] = fmaf(m1, w4.x, o1[1][0]); o1[1][1] = fmaf(m1, w4.y, o1[1][1]);
-                o1[1][2] = fmaf(m1, w4.z, o1[1][2]); o1[1][3] = fmaf(m1, w4.w, o1[1][3]);
+#pragma unroll 1
+            for (int s4 = 0; s4 < C; s4 += 4) {
+                float4 mx[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) mx[r] = *reinterpret_cast<const float4*>(Mm + (rt_t + r) * C + s4);
+#pragma unroll
+                for (int ii = 0; ii < 4; ++ii) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(Bm + (s4 + ii) * DK + rt_c);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float mv = f4c(mx[r], ii);
+                        o1[r][0] = fmaf(mv, w4.x, o1[r][0]); o1[r][1] = fmaf(mv, w4.y, o1[r][1]);
+                        o1[r][2] = fmaf(mv, w4.z, o1[r][2]); o1[r][3] = fmaf(mv, w4.w, o1[r][3]);
+                    }
+                }
             }
-        }
-        // one row's DK columns are spread over Q4 consecutive threads (a whole warp for DK = 128)
+            // one row's DK columns are spread over Q4 consecutive threads (a whole warp for DK = 128)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float ss = rt_on ? o1[r][0] * o1[r][0] + o1[r][1] * o1[r][1] + o1[r][2] * o1[r][2] + o1[r][3] * o1[r][3] : 0.f;
+            for (int r = 0; r < 4; ++r) {
+                float ss = o1[r][0] * o1[r][0] + o1[r][1] * o1[r][1] + o1[r][2] * o1[r][2] + o1[r][3] * o1[r][3];
 #pragma unroll
-            for (int off = Q4 / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-            const int t = rt_t + r;
-            if (rt_on && t < nc) {
-                const float inv = rsqrtf(ss / DK + eps);
-                const int row = row0 + t;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int cidx = rt_c + j;
-                    const float gate = sigmoidf_(gb[(size_t)row * ld_fg + h * DK + cidx]);
-                    const float ov = o1[r][j] * inv * o_norm_w[cidx] * gate;
-                    out[(size_t)row * ld_out + h * DK + cidx] = ov;
-                    split_store(osp, row, h * DK + cidx, ov);
+                for (int off = Q4 / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                const int t = rt_t + r;
+                if (t < nc) {
+                    const float inv = rsqrtf(ss / DK + eps);
+                    const int row = row0 + t;
+                    const float4 g4 = *reinterpret_cast<const float4*>(gb + (size_t)row * ld_fg + h * DK + rt_c);
+                    const float4 n4 = *reinterpret_cast<const float4*>(o_norm_w + rt_c);
+                    float4 ov;
+                    ov.x = o1[r][0] * inv * n4.x * sigmoidf_(g4.x);
+                    ov.y = o1[r][1] * inv * n4.y * sigmoidf_(g4.y);
+                    ov.z = o1[r][2] * inv * n4.z * sigmoidf_(g4.z);
+                    ov.w = o1[r][3] * inv * n4.w * sigmoidf_(g4.w);
+                    *reinterpret_cast<float4*>(out + (size_t)row * ld_out + h * DK + rt_c) = ov;
+                    split_store(osp, row, h * DK + rt_c, ov.x);
+                    split_store(osp, row, h * DK + rt_c + 1, ov.y);
+                    split_store(osp, row, h * DK + rt_c + 2, ov.z);
+                    split_store(osp, row, h * DK + rt_c + 3, ov.w);
                 }
             }
         }
-        // ---- F: S = diag(elast) (S' + K-^T W) ----
+        // ---- F: S = diag(e^{L[C-1]}) S0 + diag(elast) K-^T W ----
         if (st_on) {
             float acc[8][4];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                const float4 s4 = *reinterpret_cast<const float4*>(S + (st_i + r) * DK + st_c);
-                acc[r][0] = s4.x; acc[r][1] = s4.y; acc[r][2] = s4.z; acc[r][3] = s4.w;
-            }
+            for (int r = 0; r < 8; ++r) { acc[r][0] = 0.f; acc[r][1] = 0.f; acc[r][2] = 0.f; acc[r][3] = 0.f; }
 #pragma unroll 2
             for (int s2 = 0; s2 < C; ++s2) {
                 const float4 w4 = *reinterpret_cast<const float4*>(Bm + s2 * DK + st_c);
+                const float4 ka = *reinterpret_cast<const float4*>(Km + s2 * LDK + st_i);
+                const float4 kb = *reinterpret_cast<const float4*>(Km + s2 * LDK + st_i + 4);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
-                    const float km = KmT[(st_i + r) * LDT + s2];
+                    const float km = r < 4 ? f4c(ka, r) : f4c(kb, r - 4);
                     acc[r][0] = fmaf(km, w4.x, acc[r][0]); acc[r][1] = fmaf(km, w4.y, acc[r][1]);
                     acc[r][2] = fmaf(km, w4.z, acc[r][2]); acc[r][3] = fmaf(km, w4.w, acc[r][3]);
                 }
             }
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-                const float el = elast[st_i + r];
-                *reinterpret_cast<float4*>(S + (st_i + r) * DK + st_c) =
-                    make_float4(acc[r][0] * el, acc[r][1] * el, acc[r][2] * el, acc[r][3] * el);
+                const float el = elast[st_i + r], et = el * eref[st_i + r];
+                float4 s4 = *reinterpret_cast<const float4*>(S + (st_i + r) * DK + st_c);
+                s4.x = fmaf(s4.x, et, acc[r][0] * el); s4.y = fmaf(s4.y, et, acc[r][1] * el);
+                s4.z = fmaf(s4.z, et, acc[r][2] * el); s4.w = fmaf(s4.w, et, acc[r][3] * el);
+                *reinterpret_cast<float4*>(S + (st_i + r) * DK + st_c) = s4;
             }
         }
         __syncthreads();
@@ -534,7 +563,7 @@ gdn_chunk_kernel(const float* __restrict__ proj, int ld_proj, const float* __res
 
 template <int DK>
 constexpr size_t wy_smem() {
-    return sizeof(float) * ((size_t)DK * DK + 5 * kWyC * DK + (size_t)DK * (kWyC + 1) + 4 * kWyC * (kWyC + 1) + 3 * kWyC + 2 * DK);
+    return sizeof(float) * ((size_t)DK * DK + 6 * kWyC * DK + (size_t)kWyC * (DK + 4) + 2 * kWyC * kWyC + 3 * kWyC + 2 * DK);
 }
 
 }  // namespace
