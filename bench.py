@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: GLM-5.3-Flash decode tok/s at batch 1 with MTP speculative decoding.
 
-Config (BASELINE.json, second config): the full 45-layer GLM-5.3-Flash architecture with
+Config (the reference's second published configuration): the full 45-layer GLM-5.3-Flash architecture with
 random-init weights (bf16, routed experts and dense FFNs fp8-e4m3 block-scaled), tensor
 parallel over N GPUs, one 1024-token uniform-random prompt, then K speculative decode
 steps (draft 2, verify 3) with one CUDA graph per step.

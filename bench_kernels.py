@@ -310,6 +310,30 @@ def make_cases(K, only):
             cases.append(Case(f"mx_gemm.{tag}", wbytes + Mr * D + Mr * Nm * 4, mxfn,
                               f"{Em} experts x {Nm} x {D} e2m1 ({wbytes / 1e6:.0f} MB), {rows_per} rows each (bn {bn}) "
                               f"FLOP={2 * Mr * Nm * D}"))
+    # ---- GLM: W8A16 grouped tcgen05 GEMM (e4m3 weights + 128x128 f32 scales, f16 rows), prefill sizes ----
+    if want("fp8w_gemm"):
+        for tag, Em, Nm, Km, rows_per in (("gate_up.128e.r64", 128, 4096, 4096, 64), ("down.128e.r64", 128, 4096, 2048, 64),
+                                          ("gate_up.36e.r228", 36, 4096, 4096, 228), ("gate_up.128e.r24", 128, 4096, 4096, 24),
+                                          ("gate_up.16e.r64", 16, 4096, 4096, 64)):
+            wq = torch.randint(0, 120, (Em * Nm, Km), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+            sc = torch.rand(Em, Nm // 128, Km // 128, device=dev) * 0.01
+            Mr = Em * rows_per
+            xh = torch.randn(Mr, Km, device=dev).half()
+            bn = 32 if rows_per <= 32 else 64 if rows_per <= 64 else 128
+            mt = Em * ((rows_per + bn - 1) // bn) + 8
+            tiles = torch.zeros(mt, 4, dtype=torch.int32, device=dev)
+            n_tiles = torch.zeros(1, dtype=torch.int32, device=dev)
+            offs = torch.zeros(Em + 1, dtype=torch.int32, device=dev)
+            K.call("fb_mx_tiles", torch.full((Em,), rows_per, dtype=torch.int32, device=dev), Em, bn, tiles, n_tiles, offs, mt)
+            outw = torch.zeros(Mr, Nm, device=dev)
+            stat = torch.zeros(4, dtype=torch.int32, device=dev)
+
+            def fwfn(wq=wq, sc=sc, xh=xh, tiles=tiles, n_tiles=n_tiles, mt=mt, outw=outw, Mr=Mr, Em=Em, Nm=Nm, Km=Km, bn=bn, stat=stat):
+                K.call("fb_fp8w_gemm_grouped", wq, sc, xh, tiles, n_tiles, mt, outw, Nm, Mr, Em, Nm, Km, bn, stat)
+            wbytes = Em * Nm * Km
+            cases.append(Case(f"fp8w_gemm.{tag}", wbytes + Mr * Km * 2 + Mr * Nm * 4, fwfn,
+                              f"{Em} experts x {Nm} x {Km} e4m3 ({wbytes / 1e6:.0f} MB), {rows_per} rows each (bn {bn}) "
+                              f"FLOP={2 * Mr * Nm * Km}"))
     if want("d4_sparse_attn"):
         n, Hl, hd, W, cap, ktop, ccap = 1, 8, 512, 128, 136, 512, 8192
         ring = torch.randn(1, cap, hd, device=dev).to(torch.bfloat16)

@@ -16,6 +16,11 @@
 //     calls on one stream or order them with events.
 //   * Every partial slot that the final pass reads is written by the first pass of the same
 //     call, so the array needs no clearing between calls and stale contents are harmless.
+//   * A NaN never wins a comparison.  A row that holds nothing but NaNs therefore has no
+//     winner: its id comes back as vocab_offset - 1 (one below the first valid id of the
+//     slice, i.e. -1 for vocab_offset = 0) and its value as a NaN.  A
+//     caller that samples from unchecked logits should treat an id below vocab_offset as
+//     "no token" rather than index with it.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -373,9 +373,9 @@ class GlmDeviceModel:
             ws["tc_pos"], ws["tc_wts"] = i32(npair), self._z(npair)
             ws["tc_counts"], ws["tc_offsets"] = i32(512), i32(513)
             ws["tc_tiles"], ws["tc_ntiles"] = i32(512 + npair // 32 + 1, 4), i32(1)
-            ws["tc_x"] = torch.zeros(npair, H, dtype=torch.bfloat16, device=self.dev)
+            ws["tc_x"] = torch.zeros(npair, H, dtype=torch.float16, device=self.dev)
             ws["tc_h"] = self._z(npair, 2 * Il)
-            ws["tc_act"] = torch.zeros(npair, Il, dtype=torch.bfloat16, device=self.dev)
+            ws["tc_act"] = torch.zeros(npair, Il, dtype=torch.float16, device=self.dev)
         if M > self.moe_group_rows:
             npair = M * cfg.num_experts_per_tok
             ws["moe_gpairs"] = torch.zeros(npair * 8, dtype=torch.int32, device=self.dev)
@@ -689,18 +689,18 @@ class GlmDeviceModel:
         # routed experts write y, the shared expert's down projection adds to it and carries the
         # all-reduce (and the hyper-connection fold) in its epilogue
         if H % 128 == 0 and Il % 128 == 0 and 0 < self.moe_tc_rows <= n and self.e_cnt <= 512:
-            # prefill-sized row counts on tcgen05: pairs sorted by expert, bf16 rows scattered to their sorted places,
+            # prefill-sized row counts on tcgen05: pairs sorted by expert, f16 rows scattered to their sorted places,
             # gate | up GEMM, weighted SwiGLU, down GEMM, slot-ordered combine; every expert's weights stream once
             K = self.K
             npairs = n * topk
-            bn = 32 if npairs <= 32 * self.e_cnt else 64 if npairs <= 64 * self.e_cnt else 128 if npairs <= 128 * self.e_cnt else 256
+            bn = 32 if npairs <= 32 * self.e_cnt else 64 if npairs <= 64 * self.e_cnt else 128
             mt = ws["tc_tiles"].shape[0]
             K.call("fb_mx_sort", ws["moe_ids"], ws["moe_wts"], npairs, self.e_lo, self.e_cnt, bn, ws["tc_pos"], ws["tc_wts"],
                    ws["tc_counts"], ws["tc_offsets"], ws["tc_tiles"], ws["tc_ntiles"], mt)
-            K.call("fb_scatter_rows_bf16", x.s, x.ld, ws["tc_pos"], topk, n, H, ws["tc_x"])
+            K.call("fb_scatter_rows_f16", x.f, x.ld, ws["tc_pos"], topk, n, H, ws["tc_x"])
             K.call("fb_fp8w_gemm_grouped", L["w13"], L["s13s"], ws["tc_x"], ws["tc_tiles"], ws["tc_ntiles"], mt, ws["tc_h"],
                    ws["tc_h"].shape[1], npairs, self.e_cnt, 2 * Il, H, bn, self.tc_status)
-            K.call("fb_swiglu_rows_bf16", ws["tc_h"], ws["tc_h"].shape[1], ws["tc_wts"], View(ws["tc_offsets"], self.e_cnt),
+            K.call("fb_swiglu_rows_f16", ws["tc_h"], ws["tc_h"].shape[1], ws["tc_wts"], View(ws["tc_offsets"], self.e_cnt),
                    npairs, Il, float(cfg.swiglu_limit), ws["tc_act"])
             K.call("fb_fp8w_gemm_grouped", L["w2"], L["s2s"], ws["tc_act"], ws["tc_tiles"], ws["tc_ntiles"], mt, ws["moe_ypair"],
                    H, npairs, self.e_cnt, H, Il, bn, self.tc_status)

@@ -271,9 +271,10 @@ class EngineDriver:
     that the follower ranks, which block in the command broadcast, never run into the control group's
     timeout while the server simply has nothing to do."""
 
-    def __init__(self, engine: ServeEngine, idle_sleep: float = 0.002, heartbeat_s: float = 5.0):
+    def __init__(self, engine: ServeEngine, idle_sleep: float = 0.05, heartbeat_s: float = 5.0):
         self.engine = engine
         self.cmds: "queue.Queue" = queue.Queue()
+        self._wake = threading.Event()   # set by submit / cancel: an idle driver wakes at once, not after a sleep
         self.sinks: Dict[int, object] = {}
         self.idle_sleep = idle_sleep
         self.heartbeat_s = heartbeat_s
@@ -292,6 +293,7 @@ class EngineDriver:
         reply: "queue.Queue" = queue.Queue()
         sink = sink if sink is not None else queue.Queue()
         self.cmds.put(("submit", spec, sink, reply))
+        self._wake.set()
         try:
             res = reply.get(timeout=timeout)
         except queue.Empty:
@@ -302,6 +304,7 @@ class EngineDriver:
 
     def cancel(self, req: int) -> None:
         self.cmds.put(("cancel", req, None, None))
+        self._wake.set()
 
     def stats(self) -> dict:
         with self._stats_lock:
@@ -309,6 +312,7 @@ class EngineDriver:
 
     def shutdown(self) -> None:
         self._stop.set()
+        self._wake.set()
         self.thread.join(timeout=5)
 
     def _fail(self, e: BaseException) -> None:
@@ -352,7 +356,8 @@ class EngineDriver:
         while not self._stop.is_set():
             self._drain_cmds()
             if self.poisoned:
-                time.sleep(self.idle_sleep)
+                self._wake.wait(self.idle_sleep)
+                self._wake.clear()
                 continue
             try:
                 if self.engine.idle():
@@ -360,7 +365,8 @@ class EngineDriver:
                     if beat is not None and time.monotonic() - last_beat >= self.heartbeat_s:
                         beat()
                         last_beat = time.monotonic()
-                    time.sleep(self.idle_sleep)
+                    self._wake.wait(self.idle_sleep)
+                    self._wake.clear()
                     continue
                 events = self.engine.tick()
                 last_beat = time.monotonic()

@@ -1,6 +1,6 @@
-"""GPU: the expert-grouped W8A16 tcgen05 GEMM (e4m3 weights with 128x128 f32 block scales widened to bf16 in shared
-memory, bf16 activation rows) against fp32 matmuls of the dequantised weights, and the GLM prefill path through it
-against the mma.sync grouped kernels."""
+"""GPU: the expert-grouped W8A16 tcgen05 GEMM (e4m3 weights widened to f16 in shared memory, f16 activation rows, the
+128x128 f32 block scales applied to each k-block's accumulator) against fp32 matmuls of the dequantised weights, and
+the GLM prefill path through it against the mma.sync grouped kernels."""
 import pytest
 import torch
 
@@ -11,7 +11,8 @@ from ferrite_b200.ops import reference as R  # noqa: E402
 
 
 @pytest.mark.parametrize("E,N,K,counts,bn", [(2, 128, 128, [20, 3], 32), (3, 256, 512, [64, 0, 70], 64),
-                                             (2, 384, 2048, [130, 40], 128), (1, 256, 4096, [300], 256)])
+                                             (2, 384, 2048, [130, 40], 128), (1, 256, 4096, [300], 128),
+                                             (40, 512, 1024, [7 * (i % 5) for i in range(40)], 32)])
 def test_fp8w_grouped_gemm(E, N, K, counts, bn):
     Kl = _lib.lib()
     g = torch.Generator().manual_seed(E + N)
@@ -20,9 +21,9 @@ def test_fp8w_grouped_gemm(E, N, K, counts, bn):
     wq = torch.stack([q for q, _ in qs]).cuda()
     sc = torch.stack([s for _, s in qs]).cuda()
     M = sum(counts)
-    x = torch.randn(M, K, generator=g).bfloat16()
+    x = torch.randn(M, K, generator=g).half()
     cnt = torch.tensor(counts, dtype=torch.int32, device="cuda")
-    tiles = torch.zeros(64, 4, dtype=torch.int32, device="cuda")
+    tiles = torch.zeros(64, 4, dtype=torch.int32, device="cuda")          # more tile slots than tiles: the grid is sized by it
     n_tiles = torch.zeros(1, dtype=torch.int32, device="cuda")
     offsets = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
     Kl.call("fb_mx_tiles", cnt, E, bn, tiles, n_tiles, offsets, 64)
@@ -37,7 +38,7 @@ def test_fp8w_grouped_gemm(E, N, K, counts, bn):
         want[r:r + c] = (x[r:r + c].double() @ R.dequant_fp8_block(*qs[e]).double().t()).float()
         r += c
     err = (out.cpu() - want).abs().max().item()
-    assert err < 6e-3 * max(1.0, want.abs().max().item()), (err, want.abs().max().item())   # weights rounded once to bf16
+    assert err < 1e-3 * max(1.0, want.abs().max().item()), (err, want.abs().max().item())   # exact operands, f32 accumulation
 
 
 def test_glm_prefill_through_tcgen05_experts_matches_grouped_kernels():
