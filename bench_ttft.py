@@ -33,12 +33,13 @@ def main(argv=None):
     ap.add_argument("--port", type=int, default=18431)
     ap.add_argument("--max-ctx", type=int, default=8192)
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--prefill-rows", type=int, default=1024)
     args = ap.parse_args(argv)
 
     from ferrite_b200.serve.__main__ import build_engine
     resident = args.experts_resident or (128 if args.tp == 1 else 0)
     eargs = argparse.Namespace(model="glm53", model_dir=None, backend="cuda", tp=args.tp, synthetic=True, max_seqs=1, mtp=3,
-                               max_ctx=args.max_ctx, experts_resident=resident)
+                               max_ctx=args.max_ctx, experts_resident=resident, prefill_rows=args.prefill_rows)
     eng, tok, rank, world = build_engine(eargs)
     if rank != 0:
         eng.follow()
@@ -100,7 +101,7 @@ def main(argv=None):
         "prefill_tok_s": round(ntok / (p50 * 1e-3), 1),
         "config": {"model": "GLM-5.3-Flash (45 layers, 1 MTP layer)", "parallelism": f"tp{world}",
                    "experts_resident_per_layer": resident or 288, "path": "HTTP /v1/chat/completions, SSE, byte tokenizer",
-                   "weights": "random-init", "batch": 1, "sampling": "greedy"}}))
+                   "weights": "random-init", "batch": 1, "sampling": "greedy", "prefill_rows": args.prefill_rows}}))
     return 0
 
 

@@ -70,7 +70,8 @@ def build_engine(args):
     ecfg = EngineConfig(tp=world, max_ctx=args.max_ctx, mtp_n=mtp, experts_resident=args.experts_resident or None)
     if args.max_seqs == 1:
         from ..engine.glm_engine import GlmEngine
-        eng = SingleFlight(_GlmStep(GlmEngine(cfg, ecfg, src, rank, world, dev, allreduce), mtp > 1))
+        eng = SingleFlight(_GlmStep(GlmEngine(cfg, ecfg, src, rank, world, dev, allreduce,
+                                              prefill_rows=getattr(args, "prefill_rows", 1024)), mtp > 1))
     else:
         from ..engine.gpu_engine import GpuEngine
         eng = GpuEngine(cfg, ecfg, src, rank, world, dev, allreduce, max_rows=args.max_seqs)
@@ -217,6 +218,9 @@ def main(argv=None):
     ap.add_argument("--mtp", type=int, default=3)
     ap.add_argument("--synthetic", action="store_true", help="random-init weights instead of a checkpoint")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--prefill-rows", type=int, default=1024,
+                    help="rows per prefill chunk of the single-sequence engine (the tensor-core expert GEMM and the "
+                         "chunked GatedDeltaNet scan take over from 64 rows)")
     args = ap.parse_args(argv)
     eng, tok, rank, world = build_engine(args)
     if rank != 0:
