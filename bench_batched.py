@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--layers", type=int, default=0, help="0 = the full 45-layer model")
     ap.add_argument("--experts-resident", type=int, default=0)
+    ap.add_argument("--mtp", type=int, default=1, help="verify width of the batched speculative step (1 = greedy decode)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed ticks with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -50,7 +51,7 @@ def main():
         allreduce = make_allreduce(dev, rank, world, max_elems=64 * 4096, kind="p2p")
     cfg = GlmConfig.production() if not args.layers else GlmConfig.scaled(args.layers)
     resident = args.experts_resident or (128 if world == 1 else cfg.n_routed_experts)
-    ecfg = EngineConfig(tp=world, max_ctx=args.prompt_len + args.new_tokens + 64, mtp_n=1,
+    ecfg = EngineConfig(tp=world, max_ctx=args.prompt_len + args.new_tokens + 64, mtp_n=args.mtp,
                         experts_resident=None if resident >= cfg.n_routed_experts else resident)
     t0 = time.time()
     eng = GpuEngine(cfg, ecfg, SyntheticSource(cfg, dev, seed=0), rank, world, dev, allreduce, max_rows=args.seqs,
@@ -98,7 +99,9 @@ def main():
             "ms_per_tick": round(ms / args.window, 4), "ticks": args.window, "tokens": produced, "impl": "ours",
             "dtype": "bf16", "data": "synthetic",
             "config": {"model": cfg.name, "sequences": args.seqs, "prompt_len": args.prompt_len,
-                       "parallelism": f"tp{world}", "experts_resident_per_layer": resident, "mtp": "off",
+                       "parallelism": f"tp{world}", "experts_resident_per_layer": resident,
+                       "mtp": "off" if args.mtp <= 1 else f"batched, draft {args.mtp - 1} / verify {args.mtp}",
+                       "accept_tokens_per_seq_step": round(produced / max(1, args.window * args.seqs), 3),
                        "kernel_launches_per_tick": eng.launches, "load_s": round(load_s, 1)},
             "vs_reference_published": round(produced / ms * 1e3 / 971.0, 3)}))
     if world > 1:

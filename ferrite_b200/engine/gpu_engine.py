@@ -4,11 +4,22 @@ A tick replays the planner's decisions: row compaction moves, prefix-cache resto
 snapshot moves, chunked-prefill passes and ONE decode graph for the padded bucket.  Decode
 rows are physical: row r = state slot r = graph row r, so batch membership changes only
 touch device tables (sequence lengths, page table, token ids, state rows) and never force a
-re-capture; there is one CUDA graph per bucket of the ladder.  Speculative decoding is a
-single-sequence feature (as in the reference, where MTP forces one sequence), so the
-batched engine decodes greedily.  Counterpart of ``GpuEngine::tick``
-(``crates/ferrite-serve/src/gpu_engine.rs:858-1117``) and ``decode_step_batched``
-(``crates/ferrite-exec/src/tp.rs:914-1288``).
+re-capture; there is one CUDA graph per bucket of the ladder.  Counterpart of
+``GpuEngine::tick`` (``crates/ferrite-serve/src/gpu_engine.rs:858-1117``) and
+``decode_step_batched`` (``crates/ferrite-exec/src/tp.rs:914-1288``).
+
+With ``EngineConfig.mtp_n = nv > 1`` the decode graph of a bucket is a batched speculative step
+(``mtp_step_batched``, ``crates/ferrite-exec/src/tp.rs:1327``; layout ``mtp_batch.rs:146-530``):
+every live sequence is one GROUP of the row-batched kernels.  Draft pass 0 runs two rows per
+sequence on the MTP layer (the pair to repair and the new anchor), passes 1..nv-2 one row each,
+the main model verifies nv rows per sequence with GatedDeltaNet state snapshots into the
+rotating buffers, and ONE accept kernel walks every sequence's accept chain on the device,
+advances its lengths and snapshot cursor (commit without copying state) and stages its next
+draft inputs.  Per-sequence draft inputs live per state slot between ticks and are gathered
+into / scattered from the bucket's rows around the graph.  After a prefix-cache restore the MTP
+layer's cache entry of the last shared position was written by the sequence that published the
+block (it pairs that position's hidden state with ITS next token); it is left as it is: drafts
+only propose, the main model's verify decides every emitted token.
 """
 from __future__ import annotations
 
@@ -20,6 +31,7 @@ from .. import build
 from ..config import EngineConfig, GlmConfig
 from ..models.glm import GlmDeviceModel, RowSet
 from ..serve.engine import ContextOverflow, ReqEvent, RequestSpec, Usage
+from . import mtp_batch as MB
 
 
 class GpuEngine:
@@ -29,18 +41,20 @@ class GpuEngine:
         build.build_runtime()
         from .. import _runtime as rt
         self.rt, self.cfg = rt, cfg
-        assert ecfg.mtp_n <= 1, "the batched engine decodes greedily (MTP is single-sequence)"
+        self.nv = nv = max(1, ecfg.mtp_n)
         ps = cfg.dsa.page_size
         max_pages_seq = (ecfg.max_ctx + ps - 1) // ps
         num_pages = num_pages or (max_rows * max_pages_seq + 1)
         self.model = GlmDeviceModel(cfg, ecfg, src, rank, world, device, allreduce,
-                                    max_rows=max(prefill_rows, max_rows), n_slots=max_rows + 1, num_pages=num_pages)
+                                    max_rows=max(prefill_rows, MB.verify_rows(max_rows, max(nv, 2))), n_slots=max_rows + 1,
+                                    num_pages=num_pages)
         m, dev = self.model, self.model.dev
         sc = rt.SchedConfig()
         sc.max_rows, sc.page_size, sc.num_pages = max_rows, ps, num_pages
         sc.prefill_budget = prefill_budget or ecfg.sched.prefill_budget
         sc.device_slots, sc.host_slots, sc.disk_slots = device_snapshots, host_snapshots, 0
         sc.max_ctx = ecfg.max_ctx
+        sc.spec_rows = nv
         sc.buckets = [b for b in ecfg.sched.buckets if b <= max_rows] or [max_rows]
         if sc.buckets[-1] < max_rows:
             sc.buckets = sc.buckets + [max_rows]
@@ -57,6 +71,18 @@ class GpuEngine:
         self.pin_out = torch.zeros(max_rows, dtype=torch.int32).pin_memory()
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.rowsets: Dict[int, RowSet] = {b: m.make_rows(list(range(b)), [1] * b) for b in self.buckets}
+        if nv > 1:
+            H, S = cfg.hidden_size, max_rows + 1
+            i32 = lambda *sh: torch.zeros(*sh, dtype=torch.int32, device=dev)
+            self.rs2 = {b: m.make_rows(list(range(b)), [2] * b) for b in self.buckets}
+            self.rsv = {b: m.make_rows(list(range(b)), [nv] * b) for b in self.buckets}
+            self.mtp_ids_slot, self.mtp_h_slot = i32(S, 2), torch.zeros(S, 2, H, device=dev)   # between ticks
+            self.block_ids, self.judges = i32(max_rows, nv), i32(max_rows, nv)
+            self.out_tokens = i32(max_rows, nv + 1)
+            self.mtp_ids, self.mtp_h = i32(max_rows, 2), torch.zeros(max_rows, 2, H, device=dev)
+            self.hchain, self.cur_ids, self.draft_ids = torch.zeros(max_rows, H, device=dev), i32(max_rows), i32(2 * max_rows)
+            self.mtp_pre_ids = i32(prefill_rows)
+            self.pin_spec = torch.zeros(max_rows, nv + 1, dtype=torch.int32).pin_memory()
         self.prompts: Dict[int, List[int]] = {}
         self.page_count: Dict[int, int] = {}
         # tiered recurrent-state snapshots: device tier on the GPU, host tier in pinned memory
@@ -75,8 +101,11 @@ class GpuEngine:
 
     def submit(self, spec: RequestSpec) -> int:
         self.validate(spec)
-        rid = self.sched.submit(list(spec.prompt_ids), spec.max_new_tokens, list(spec.stop_ids))
-        self.prompts[rid] = list(spec.prompt_ids)
+        prompt = list(spec.prompt_ids)
+        if self.nv > 1 and len(prompt) == 1:
+            prompt = prompt * 2          # the draft layer pairs every position with its successor: two tokens at least
+        rid = self.sched.submit(prompt, spec.max_new_tokens, list(spec.stop_ids))
+        self.prompts[rid] = prompt
         return rid
 
     def cancel(self, req: int) -> None:
@@ -123,6 +152,9 @@ class GpuEngine:
         m.conv_state[:, dst].copy_(m.conv_state[:, src])
         for t in (m.main_len, m.mtp_len, m.cur, self.tok_slot):
             t[dst] = t[src]
+        if self.nv > 1:
+            self.mtp_ids_slot[dst].copy_(self.mtp_ids_slot[src])
+            self.mtp_h_slot[dst].copy_(self.mtp_h_slot[src])
         m.page_table[dst].copy_(m.page_table[src])
         m.main_len[src] = 0
         m.page_table[src].zero_()
@@ -138,16 +170,39 @@ class GpuEngine:
 
     # ------------------------------------------------------------------ tick
     def _decode_body(self, bucket: int):
+        if self.nv > 1:
+            return self._spec_body(bucket)
         self.model.main_forward(self.rowsets[bucket], self.ids, snapshots=False, advance=True, judges=self.out)
+
+    def _spec_body(self, G: int):
+        """One speculative step of G sequences (groups): draft chain, verify, device accept / commit."""
+        m, nv, H = self.model, self.nv, self.cfg.hidden_size
+        blk = self.block_ids[:G]
+        # draft 0: rows (pair to repair, new anchor) of every sequence; the anchor rows' tokens are draft 1
+        m.mtp_forward(self.rs2[G], self.mtp_ids, self.mtp_h, self.draft_ids, head_from=0, advance=True)
+        blk[:, 1].copy_(self.draft_ids[:2 * G].view(G, 2)[:, 1])
+        hout = m.ws["mtp_hout"]
+        for d in range(1, nv - 1):
+            self.hchain[:G].copy_(hout[:2 * G].view(G, 2, H)[:, 1] if d == 1 else hout[:G])
+            self.cur_ids[:G].copy_(blk[:, d])
+            m.mtp_forward(self.rowsets[G], self.cur_ids, self.hchain, self.draft_ids, advance=True)
+            blk[:, d + 1].copy_(self.draft_ids[:G])
+        rsv = self.rsv[G]
+        m.main_forward(rsv, self.block_ids, snapshots=True, advance=False, judges=self.judges)
+        m.K.call("fb_mtp_accept", self.block_ids, self.judges, self.out_tokens, m.ws["h_final"], self.mtp_ids, self.mtp_h,
+                 rsv.group_slot, m.main_len, m.mtp_len, m.cur, G, nv, H, m.nbuf)
 
     def _decode(self, bucket: int):
         g = self.graphs.get(bucket)
         if g is None and self.model.ecfg.use_graphs:
             # first use: run once eagerly on a saved copy of the small state, then capture
             m = self.model
-            keep = [t.clone() for t in (m.main_len, m.gdn_state, m.conv_state)]
+            small = (m.main_len, m.mtp_len, m.cur, m.gdn_state, m.conv_state)
+            if self.nv > 1:
+                small = small + (self.block_ids, self.mtp_ids, self.mtp_h)
+            keep = [t.clone() for t in small]
             self._decode_body(bucket)
-            for dst, src in zip((m.main_len, m.gdn_state, m.conv_state), keep):
+            for dst, src in zip(small, keep):
                 dst.copy_(src)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -173,6 +228,7 @@ class GpuEngine:
             m.gdn_state[:, rs.row, 0].copy_(self.snap_dev[0][rs.device_slot])
             m.conv_state[:, rs.row, 0].copy_(self.snap_dev[1][rs.device_slot])
             m.main_len[rs.row] = req.cached_tokens
+            m.mtp_len[rs.row] = req.cached_tokens
             m.cur[rs.row] = 0
         for rid in plan.admitted:
             req = self.sched.get(rid)
@@ -180,7 +236,10 @@ class GpuEngine:
                 m.gdn_state[:, req.row].zero_()
                 m.conv_state[:, req.row].zero_()
                 m.main_len[req.row] = 0
+                m.mtp_len[req.row] = 0
                 m.cur[req.row] = 0
+            if self.nv > 1:
+                self.mtp_h_slot[req.row].zero_()
             self.page_count.pop(rid, None)
             self._bind_pages(req.row, rid)
         # decode first: rows of sequences that were already decoding before this tick
@@ -194,16 +253,37 @@ class GpuEngine:
             rs.group_slot.copy_(slot_t)
             m.main_len[self.dummy_slot] = 0
             idx = rs.row_slot.long()
-            self.ids[:bucket].copy_(self.tok_slot[idx])
-            self._decode(bucket)
-            self.tok_slot[idx] = self.out[:bucket]
-            self.pin_out.copy_(self.out, non_blocking=True)
+            toks = [[] for _ in plan.decode.rows]
+            if self.nv > 1:
+                for rsx, g in ((self.rs2[bucket], 2), (self.rsv[bucket], self.nv)):
+                    rsx.row_slot.copy_(slot_t.repeat_interleave(g))
+                    rsx.group_slot.copy_(slot_t)
+                m.mtp_len[self.dummy_slot] = 0
+                m.cur[self.dummy_slot] = 0
+                self.block_ids[:bucket, 0].copy_(self.tok_slot[idx])
+                self.mtp_ids[:bucket].copy_(self.mtp_ids_slot[idx])
+                self.mtp_h[:bucket].copy_(self.mtp_h_slot[idx])
+                self._decode(bucket)
+                self.tok_slot[idx] = self.block_ids[:bucket, 0]
+                self.mtp_ids_slot[idx] = self.mtp_ids[:bucket]
+                self.mtp_h_slot[idx] = self.mtp_h[:bucket]
+                self.pin_spec.copy_(self.out_tokens, non_blocking=True)
+            else:
+                self.ids[:bucket].copy_(self.tok_slot[idx])
+                self._decode(bucket)
+                self.tok_slot[idx] = self.out[:bucket]
+                self.pin_out.copy_(self.out, non_blocking=True)
             m.arena.snapshot_async()
             torch.cuda.current_stream().synchronize()
             m.arena.verify()   # status words and guards of the tick: a timed-out wait or a clamped position raises here
-            toks = [[] for _ in plan.decode.rows]
+            rmap = MB.SeqRowMap(len(live), bucket, self.nv)     # sequence i of the bucket owns verify rows rmap.rows_of(i)
             for i, row in enumerate(live):
-                toks[row] = [int(self.pin_out[i])]
+                if self.nv > 1:
+                    k = int(self.pin_spec[i, 0])
+                    assert 1 <= k <= rmap.width, (i, k)
+                    toks[row] = [int(t) for t in self.pin_spec[i, 1:1 + k]]
+                else:
+                    toks[row] = [int(self.pin_out[i])]
             self._convert(self.sched.ingest_decode(toks), out)
         # chunked prefill
         for ch in plan.prefill:
@@ -216,10 +296,25 @@ class GpuEngine:
                 rs = m.make_rows([ch.row], [n])
                 m.main_forward(rs, self.prefill_ids, snapshots=False, advance=True,
                                judges=self.first_tok if last else None, head_from=n - 1 if last else n)
+                if self.nv > 1:
+                    # the draft layer's cache: pairs (h_t, tok_{t+1}) for t < N - 2; the last two hidden rows of the
+                    # prompt stay with the slot as the first draft pass's inputs
+                    N, hf = len(prompt), m.ws["h_final"]
+                    t_hi = min(s0 + n, N - 2)
+                    if t_hi > s0:
+                        gm = t_hi - s0
+                        self.mtp_pre_ids[:gm].copy_(torch.tensor(prompt[s0 + 1:t_hi + 1], dtype=torch.int32))
+                        m.mtp_forward(m.make_rows([ch.row], [gm]), self.mtp_pre_ids, hf, None, advance=True)
+                    hs = self.mtp_h_slot[ch.row]
+                    hs[0].copy_(hf[n - 2] if n >= 2 else hs[1])
+                    hs[1].copy_(hf[n - 1])
                 if last:
                     first = int(self.first_tok[n - 1].item())
                     m.arena.verify(snapshot=False)
                     self.tok_slot[ch.row] = first
+                    if self.nv > 1:
+                        self.mtp_ids_slot[ch.row].copy_(torch.tensor([prompt[-1], first], dtype=torch.int32))
+                        m.mtp_len[ch.row] = len(prompt) - 2
             evs, moves = self.sched.ingest_prefill(ch.req, ch.len, first, ch.snapshot_after)
             self._apply_state_moves(moves)
             self._convert(evs, out)

@@ -8,7 +8,7 @@
 Flags follow the reference binary (``crates/ferrite-serve/src/main.rs:39-68``): ``--model``,
 ``--model-dir``, ``--backend cpu|cuda``, ``--tp``, ``--prompt``, ``--serve``, ``--port``,
 ``--max-seqs``, ``--model-name``, ``--max-tokens``; ``--mtp N`` selects the verify width of the
-single-sequence speculative engine (``--max-seqs 1``).
+speculative step (single-sequence engine with ``--max-seqs 1``, batched engine otherwise; 1 = greedy).
 """
 from __future__ import annotations
 
@@ -66,7 +66,7 @@ def build_engine(args):
         src = CheckpointSource(args.model_dir, cfg, dev)
     else:
         src = SyntheticSource(cfg, dev)
-    mtp = args.mtp if args.max_seqs == 1 else 1
+    mtp = args.mtp      # verify width: the single-sequence engine's step, or every sequence's group in the batched one
     ecfg = EngineConfig(tp=world, max_ctx=args.max_ctx, mtp_n=mtp, experts_resident=args.experts_resident or None)
     if args.max_seqs == 1:
         from ..engine.glm_engine import GlmEngine

@@ -91,6 +91,30 @@ def test_mtp_accepts_when_draft_is_right():
     assert acc and all(k == 3 for k in acc), acc
 
 
+def test_batched_engine_speculative_steps_match_greedy():
+    """Batched MTP: every live sequence is one group of the draft / verify / accept step; the tokens are the greedy
+    engine's whatever the drafts were, across bucket changes, chunked prefill and prefix-cache restores."""
+    from ferrite_b200.engine.gpu_engine import GpuEngine
+    from ferrite_b200.models.glm import DictSource
+    from ferrite_b200.serve.engine import RequestSpec
+    cfg = GlmConfig.tiny()
+    w = random_weights(cfg, 0, std=0.05)
+    prompts = [_prompt(cfg, n, seed=10 + n) for n in (37, 5, 64, 18, 50, 2)] + [[7]]
+    single = _engine(cfg, w, mtp_n=1)
+    want = [single.generate(p if len(p) > 1 else p * 2, 11, mtp=False)[0] for p in prompts]
+    ecfg = EngineConfig(max_ctx=512, mtp_n=3, kv_dtype="f32")
+    eng = GpuEngine(cfg, ecfg, DictSource(w, "cuda"), max_rows=4, prefill_rows=16, prefill_budget=48)
+    got = eng.run_all([RequestSpec(p, 11) for p in prompts])
+    for (rid, toks), w_ in zip(sorted(got.items()), want):
+        assert toks == w_, (rid, toks, w_)
+    ticks = eng.stats()["engine"]["ticks"]
+    again = eng.run_all([RequestSpec(prompts[2], 11), RequestSpec(prompts[0], 11)])
+    (r2, t2), (r0, t0) = sorted(again.items())
+    assert t2 == want[2] and t0 == want[0]
+    assert eng.usage[r2].cached_tokens == 48 and eng.usage[r0].cached_tokens == 32
+    assert ticks > 0 and eng.launches > 0
+
+
 def test_batched_engine_matches_single_sequence_engine():
     """Continuous batching with chunked prefill, bucket graphs and the radix prefix cache gives
     every request the tokens the single-sequence engine gives it."""
