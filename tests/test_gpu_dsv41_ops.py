@@ -1,0 +1,183 @@
+"""GPU: DSV41 kernels one at a time against plain fp32 statements of the same op (``ops/quant.py`` codecs,
+``models/dsv41_ref.py`` helpers, fp32 matmuls of dequantised weights)."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from ferrite_b200.models import dsv41_ref as G
+from ferrite_b200.ops import quant as Q
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ferrite_b200 import _lib
+    return _lib.lib()
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def meta_for(pos):
+    m = torch.zeros(len(pos), 8, dtype=torch.int32)
+    m[:, 1] = torch.tensor(pos, dtype=torch.int32)
+    return m.cuda()
+
+
+def close(name, got, want, tol):
+    err = (got.float().cpu() - want.float()).abs().max().item()
+    assert err <= tol, f"{name}: max abs err {err} > {tol}"
+
+
+@pytest.mark.parametrize("inverse,fp4_rt", [(0, 0), (1, 0), (0, 1)])
+def test_rope_heads(K, inverse, fp4_rt):
+    n, heads, hd, rd = 4, 3, 128, 64
+    x = torch.randn(n, heads * hd, generator=gen(1))
+    freqs = torch.rand(rd // 2, generator=gen(2)) * 0.1
+    pos = [0, 7, 1234, 99999]
+    xd = x.clone().cuda()
+    K.call("fb_d4_rope_heads", xd, heads * hd, n, heads, hd, rd, freqs.cuda(), meta_for(pos), 0, inverse, fp4_rt, None, 0, 0, 0)
+    want = G.apply_rope(x.view(n, heads, hd), torch.tensor(pos), freqs, inverse=bool(inverse))
+    if fp4_rt:
+        # the device computes sin / cos in f32 of an f32 angle, the statement too; a value within one ulp of an e2m1
+        # rounding boundary may still land on the other side, so the comparison is on the un-quantised rotation
+        got_rt = xd.cpu().view(n, heads, hd)
+        want_rt = Q.fp4_act_roundtrip(want, 32)
+        frac = ((got_rt - want_rt).abs() > 1e-6).float().mean().item()
+        assert frac < 0.01, frac
+    else:
+        close("rope", xd.view(n, heads, hd), want, 2e-3)     # angles up to 1e4 rad in f32
+
+
+def test_rmsnorm_quant(K):
+    n, Kd = 5, 1536
+    x = torch.randn(n, Kd, generator=gen(3)) * torch.logspace(-2, 1, n).unsqueeze(1)
+    w = 1 + 0.1 * torch.randn(Kd, generator=gen(4))
+    out = torch.zeros(n, Kd, device="cuda")
+    K.call("fb_d4_rmsnorm_quant", x.cuda(), Kd, w.cuda(), out, Kd, n, Kd, 1e-6, None, 0, 0, 0)
+    normed = G.rmsnorm(x, w, 1e-6)
+    want = Q.fp8_act_roundtrip(normed, 32)
+    # identical up to elements whose un-quantised value sits on an e4m3 rounding boundary (the two sides sum the
+    # squares in different orders): such an element moves by one e4m3 step = 1/8 of its magnitude at most
+    diff = (out.cpu() - want).abs()
+    assert (diff > 1e-6).float().mean().item() < 0.002
+    assert (diff <= 0.126 * normed.abs() + 1e-6).all()
+
+
+@pytest.mark.parametrize("lim", [0.0, 7.0])
+def test_swiglu_clamp_and_quant(K, lim):
+    n, I = 3, 384
+    gu = torch.randn(n, 2 * I, generator=gen(5)) * 6
+    g, u = gu[:, :I], gu[:, I:]
+    if lim > 0:
+        g, u = g.clamp(max=lim), u.clamp(-lim, lim)
+    want = F.silu(g) * u
+    out = torch.zeros(n, I, device="cuda")
+    K.call("fb_d4_swiglu_clamp", gu.cuda(), 2 * I, out, I, n, I, lim)
+    close("swiglu", out, want, 1e-5 * want.abs().max().item())
+    outq = torch.zeros(n, I, device="cuda")
+    K.call("fb_d4_swiglu_clamp_quant", gu.cuda(), 2 * I, outq, I, n, I, lim, None, 0, 0, 0)
+    wq = Q.fp8_act_roundtrip(want, 32)
+    diff = (outq.cpu() - wq).abs()
+    assert (diff > 1e-6).float().mean().item() < 0.005 and (diff <= 0.126 * want.abs() + 1e-6).all()
+
+
+@pytest.mark.parametrize("E,topk,image", [(64, 6, False), (256, 8, True), (16, 1, False)])
+def test_route_sqrt_softplus(K, E, topk, image):
+    n = 6
+    logits = torch.randn(n, E, generator=gen(6)) * 3
+    logits[0, 3] = logits[0, 9]                       # a tie: the lower index wins
+    bias = torch.randn(E, generator=gen(7)) * 0.1
+    bias_vl = torch.randn(E, generator=gen(8)) * 0.1
+    is_img = torch.tensor([0, 1, 0, 1, 1, 0], dtype=torch.uint8)
+    idx = torch.zeros(n, topk, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(n, topk, device="cuda")
+    K.call("fb_d4_route", logits.cuda(), E, bias.cuda(), bias_vl.cuda() if image else None, is_img.cuda() if image else None,
+           n, E, topk, 2.5, idx, wts)
+    scores = F.softplus(logits).sqrt()
+    b = bias.expand(n, E)
+    if image:
+        b = torch.where(is_img.bool().unsqueeze(-1), bias_vl.expand(n, E), b)
+    widx = G.topk_stable(scores + b, topk)
+    ww = scores.gather(1, widx)
+    if topk > 1:
+        ww = ww / (ww.sum(-1, keepdim=True) + 1e-20)
+    assert idx.cpu().tolist() == widx.tolist()
+    close("route weights", wts, ww * 2.5, 1e-5)
+
+
+def _fp4_experts(E, N, Kd, seed):
+    w = torch.randn(E, N, Kd, generator=gen(seed)) * 0.05
+    packed, scales, deq = [], [], []
+    for e in range(E):
+        p, s = Q.quant_fp4_weight(w[e], 32)
+        packed.append(p); scales.append(s); deq.append(Q.dequant_fp4_weight(p, s, 32))
+    return torch.stack(packed), torch.stack(scales), torch.stack(deq)
+
+
+@pytest.mark.parametrize("n,topk,E,I,D", [(2, 2, 4, 64, 128), (3, 4, 8, 192, 512)])
+def test_fp4_expert_gate_up_and_down(K, n, topk, E, I, D):
+    w13p, w13s, w13 = _fp4_experts(E, 2 * I, D, 9)          # [E][gate I | up I][D]
+    w2p, w2s, w2 = _fp4_experts(E, D, I, 10)
+    x = Q.fp8_act_roundtrip(torch.randn(n, D, generator=gen(11)), 32)
+    idx = torch.stack([torch.randperm(E, generator=gen(12 + r))[:topk] for r in range(n)]).to(torch.int32)
+    wts = torch.rand(n, topk, generator=gen(20)) + 0.1
+    lim = 7.0
+    h = torch.zeros(n, topk, I, device="cuda")
+    K.call("fb_d4_expert_gate_up", x.cuda(), D, idx.cuda(), wts.cuda(), w13p.cuda(), w13s.cuda(), h, n, topk, I, D, lim)
+    want_h = torch.zeros(n, topk, I)
+    for r in range(n):
+        for s in range(topk):
+            gu = w13[idx[r, s]] @ x[r]
+            g, u = gu[:I].clamp(max=lim), gu[I:].clamp(-lim, lim)
+            want_h[r, s] = F.silu(g) * u * wts[r, s]
+    close("expert gate/up", h, want_h, 2e-5 * max(1.0, want_h.abs().max().item()))
+    hq = Q.fp8_act_roundtrip(want_h, 32)
+    y = torch.full((n, D), 0.5, device="cuda")
+    K.call("fb_d4_expert_down", hq.cuda(), idx.cuda(), w2p.cuda(), w2s.cuda(), y, D, n, topk, I, D, 1)
+    want_y = torch.full((n, D), 0.5)
+    for r in range(n):
+        for s in range(topk):
+            want_y[r] += w2[idx[r, s]] @ hq[r, s]
+    close("expert down", y, want_y, 2e-5 * max(1.0, want_y.abs().max().item()))
+
+
+def test_gemv_f32_weights(K):
+    m, N, Kd = 5, 70, 1024
+    W = torch.randn(N, Kd, generator=gen(30))
+    x = torch.randn(m, Kd + 4, generator=gen(31))
+    out = torch.zeros(m, N, device="cuda")
+    K.call("fb_d4_gemv_f32w", W.cuda(), x.cuda(), Kd + 4, out, N, m, N, Kd)
+    close("gemv f32w", out, x[:, :Kd].double() @ W.double().t(), 1e-3)
+
+
+def test_sparse_attention_with_sink_matches_rows_statement(K):
+    """Window ring + compressed rows + sink against models/dsv41_ref.py::sparse_attn_rows on the gathered keys."""
+    n, Hl, hd, W, cap, ccap, ktop = 2, 4, 128, 16, 24, 64, 8
+    pos = [40, 9]                                       # row 1: fewer positions than the window holds
+    ring = (torch.randn(1, cap, hd, generator=gen(40)) * 0.5).to(torch.bfloat16)
+    comp = (torch.randn(1, ccap, hd, generator=gen(41)) * 0.5).to(torch.bfloat16)
+    q = torch.randn(n, Hl * hd, generator=gen(42))
+    idx = torch.stack([torch.randperm(ccap, generator=gen(43 + r))[:ktop].sort().values for r in range(n)]).to(torch.int32)
+    idx[1, 5:] = -1                                     # a short candidate list
+    sink = torch.randn(Hl, generator=gen(50))
+    freqs = torch.zeros(32)                             # no output rotation: rd = 64 dims with zero angles
+    meta = meta_for(pos)
+    out = torch.zeros(n, Hl * hd, device="cuda")
+    nsplit = 4
+    o_part = torch.zeros(n * Hl * nsplit * hd, device="cuda")
+    ml_part = torch.zeros(n * Hl * nsplit * 2, device="cuda")
+    scale = hd ** -0.5
+    K.call("fb_d4_sparse_attn", q.cuda(), Hl * hd, ring.cuda(), cap, W, comp.cuda(), ccap, idx.cuda(), ktop, ktop, None, 0,
+           sink.cuda(), freqs.cuda(), 64, meta, 0, 0, float(scale), Hl, hd, out, Hl * hd, n, nsplit, o_part, ml_part,
+           None, 0, 0, 0, None)
+    for r in range(n):
+        win = [p % cap for p in G.window_positions(pos[r], W)]
+        keys = [ring[0, p].float() for p in win] + [comp[0, int(j)].float() for j in idx[r] if j >= 0]
+        kv = torch.stack(keys)                                        # [keys, hd]
+        want = G.sparse_attn_rows(q[r].view(Hl, hd), kv, sink, scale)  # [Hl, hd]
+        close(f"sparse attention row {r}", out[r].view(Hl, hd), want, 3e-3)
