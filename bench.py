@@ -120,6 +120,37 @@ def tp_identity_check(rank, world, dev, allreduce, n_new=14):
     return {"tokens": f"{sum(int(a == b) for a, b in zip(toks_tp, toks_1))}/{n_new}", "hidden_rel_err": round(err, 6)}
 
 
+def kernel_times(eng, mtp, path, barrier, steps=5):
+    """Per-kernel device time of a decode step from the profiler's activity records (no replay, no serialisation:
+    usable on a real multi-rank step, unlike a kernel-replaying profiler).  Every rank runs the steps."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    if path is None:
+        for _ in range(steps):
+            eng.launch_step_async(mtp)
+        torch.cuda.synchronize()
+        barrier()
+        return
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            eng.launch_step_async(mtp)
+        torch.cuda.synchronize()
+    barrier()
+    rows = {}
+    for ev in prof.events():
+        if ev.device_type is not None and "cuda" in str(ev.device_type).lower() and ev.name:
+            r = rows.setdefault(ev.name, [0, 0.0])
+            r[0] += 1
+            r[1] += float(ev.time_range.elapsed_us())
+    tot = sum(v[1] for v in rows.values())
+    with open(path, "w") as f:
+        f.write(f"# per-kernel device time, {steps} decode steps, rank 0; total {tot / steps:.1f} us of kernel time per step\n")
+        f.write("# us_per_step  launches_per_step  avg_us  kernel\n")
+        for name, (n, us) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+            f.write(f"{us / steps:10.1f} {n / steps:8.1f} {us / max(n, 1):8.2f}  {name[:110]}\n")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +173,9 @@ def main():
                          "compute time and shape coverage of a TP=R step; prints a differently named metric)")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="open the CUDA profiler window around the prefill instead (for ncu --profile-from-start off)")
+    ap.add_argument("--kernel-times", default=None, metavar="FILE",
+                    help="after the timed regions, run 5 more steps under torch.profiler (CUPTI activity records, every "
+                         "rank steps, rank 0 records) and write per-kernel device times of one step to FILE")
     ap.add_argument("--profile", action="store_true",
                     help="open the CUDA profiler window around the timed device loop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -269,6 +303,8 @@ def main():
     clocks = sampler.stop() if rank == 0 else {}
     status.append(device_status())
     bad = [s for s in status if s != "ok"]
+    if args.kernel_times:
+        kernel_times(eng, mtp, args.kernel_times if rank == 0 else None, barrier)
     if world > 1:
         t = torch.tensor([ms, ms_e2e, float(len(bad))], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -36,14 +36,21 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
                 const float* __restrict__ kv_ln, const float* __restrict__ kn_w,
                 const float* __restrict__ kn_b, float* __restrict__ qa_out, float* __restrict__ wi_out,
                 KVT* __restrict__ lat_cache, float* __restrict__ kidx_cache, float* __restrict__ kgate_cache,
-                const RowMeta* __restrict__ meta, PageView pv, int QL, int DL, int ID, int IH, float eps,
-                SplitBuf osp) {
+                const RowMeta* __restrict__ meta, PageView pv, const int* __restrict__ lat_table, int QL, int DL, int ID,
+                int IH, float eps, SplitBuf osp) {
     PDL_PROLOGUE();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const RowMeta m = meta[r];
     const float* p = proj + (size_t)r * ld;
     const size_t ti = tok_index(pv, m.slot, m.pos);
+    // the latent cache may have a page table of its own (decode context parallel: a rank stores only the latent
+    // pages it owns, compactly; entries of the other ranks' pages are negative and the row's latent is not stored)
+    long long tl = (long long)ti;
+    if (lat_table) {
+        const int pg = lat_table[(size_t)m.slot * pv.max_pages + m.pos / pv.page_size];
+        tl = pg < 0 ? -1 : (long long)pg * pv.page_size + (m.pos % pv.page_size);
+    }
     // q_a RMSNorm
     float ss = 0.f;
     for (int j = threadIdx.x; j < QL; j += blockDim.x) ss += p[j] * p[j];
@@ -60,7 +67,8 @@ dsa_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict_
     for (int j = threadIdx.x; j < DL; j += blockDim.x) ss += pl[j] * pl[j];
     ss = block_sum(ss, red);
     inv = rsqrtf(ss / DL + eps);
-    for (int j = threadIdx.x; j < DL; j += blockDim.x) st_kv(lat_cache + ti * DL + j, pl[j] * inv * kv_ln[j]);
+    if (tl >= 0)
+        for (int j = threadIdx.x; j < DL; j += blockDim.x) st_kv(lat_cache + tl * DL + j, pl[j] * inv * kv_ln[j]);
     // indexer key LayerNorm (mean/var) -> cache; gate -> cache; head weights scaled
     const float* pk = pl + DL;
     float s1 = 0.f;
@@ -344,6 +352,7 @@ dsa_attn_partial_kernel(const float* __restrict__ qabs, const KVT* __restrict__ 
         if (tid < kTT) {
             int t = (t0 + tid < hi) ? idx[(size_t)r * ld_idx + t0 + tid] : -1;
             if (t >= 0 && nshard > 1 && ((t / pv.page_size) % nshard) != shard) t = -1;  // DCP ownership
+            if (t >= 0 && pv.table[(size_t)m.slot * pv.max_pages + t / pv.page_size] < 0) t = -1;   // page not held here
             tok_s[tid] = t;
             off_s[tid] = t >= 0 ? tok_index(pv, m.slot, t) * DL : 0;
         }
@@ -510,17 +519,17 @@ static PageView make_pv(const int* table, int64_t max_pages, int64_t page_size) 
 FB_API int fb_dsa_prep(const float* proj, int64_t ld, const float* qa_ln, const float* kv_ln,
                        const float* kn_w, const float* kn_b, float* qa_out, float* wi_out, void* lat_cache,
                        float* kidx_cache, float* kgate_cache, const void* meta, const int* page_table,
-                       int64_t max_pages, int64_t page_size, int64_t n, int64_t QL, int64_t DL, int64_t ID,
-                       int64_t IH, float eps, int64_t kv_f32, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask,
-                       cudaStream_t st) {
+                       const int* lat_table, int64_t max_pages, int64_t page_size, int64_t n, int64_t QL, int64_t DL,
+                       int64_t ID, int64_t IH, float eps, int64_t kv_f32, void* s_base, int64_t s_ld, int64_t s_plane,
+                       int64_t s_mask, cudaStream_t st) {
     SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
     PageView pv = make_pv(page_table, max_pages, page_size);
     if (kv_f32)
         FB_LAUNCH((dsa_prep_kernel<float>), n, 512, 0, st, proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
-            (float*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
+            (float*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, lat_table, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     else
         FB_LAUNCH((dsa_prep_kernel<__nv_bfloat16>), n, 512, 0, st, proj, (int)ld, qa_ln, kv_ln, kn_w, kn_b, qa_out, wi_out,
-            (__nv_bfloat16*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
+            (__nv_bfloat16*)lat_cache, kidx_cache, kgate_cache, (const RowMeta*)meta, pv, lat_table, (int)QL, (int)DL, (int)ID, (int)IH, eps, osp);
     return FB_LAUNCH_CHECK();
 }
 

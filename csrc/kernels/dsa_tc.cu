@@ -51,6 +51,7 @@ struct GlmSrc {   // selected tokens of the paged latent cache (GLM DSA)
         if (t < 0) return nullptr;
         if (nshard > 1 && ((t / pv.page_size) % nshard) != shard) return nullptr;   // DCP ownership
         const int pg = pv.table[(size_t)m.slot * pv.max_pages + t / pv.page_size];
+        if (pg < 0) return nullptr;                                                  // page not held on this rank
         return lat_cache + ((long long)pg * pv.page_size + (t % pv.page_size)) * DL;
     }
     __device__ float2 q_pair(int r, const RowMeta&, int h, int d) const {

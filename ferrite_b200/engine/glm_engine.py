@@ -23,12 +23,12 @@ class GlmEngine(SpecStep):
     ANCHOR_IS_IN_BLOCK = True
 
     def __init__(self, cfg: GlmConfig, ecfg: EngineConfig, src, rank: int = 0, world: int = 1,
-                 device="cuda", allreduce=None, prefill_rows: int = 64):
+                 device="cuda", allreduce=None, prefill_rows: int = 64, dcp_shard=None):
         self.cfg, self.ecfg = cfg, ecfg
         self.nv = ecfg.mtp_n if (ecfg.mtp_n > 1 and cfg.num_nextn_predict_layers > 0) else 1
         self.prefill_rows = max(prefill_rows, self.nv, 2)
         self.model = GlmDeviceModel(cfg, ecfg, src, rank, world, device, allreduce,
-                                    max_rows=self.prefill_rows, n_slots=1)
+                                    max_rows=self.prefill_rows, n_slots=1, dcp_shard=dcp_shard)
         m, dev = self.model, self.model.dev
         H = cfg.hidden_size
         self.slot = 0

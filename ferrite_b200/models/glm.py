@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 import zlib
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -97,8 +97,13 @@ class RowSet:
 class GlmDeviceModel:
     def __init__(self, cfg: GlmConfig, ecfg: EngineConfig, src, rank: int = 0, world: int = 1,
                  device="cuda", allreduce=None, max_rows: int = 8, n_slots: int = 1,
-                 num_pages: Optional[int] = None):
+                 num_pages: Optional[int] = None, layer_range: Optional[Tuple[int, int]] = None,
+                 dcp_shard: Optional[Tuple[int, int]] = None):
         self.cfg, self.ecfg = cfg, ecfg
+        # A pipeline stage of a layer-split (context-parallel) prefill group holds main layers [l0, l1) only
+        # (crates/ferrite-kv/src/shard.rs:60-66 cp_layer_range); the MTP layer lives with the last stage.
+        self.l0, self.l1 = layer_range if layer_range is not None else (0, cfg.num_layers)
+        assert 0 <= self.l0 < self.l1 <= cfg.num_layers
         self.rank, self.world = rank, world
         self.dev = torch.device(device)
         self.K = _lib.lib()
@@ -117,6 +122,10 @@ class GlmDeviceModel:
                 from ..parallel.symm import FusedGemvAllReduce
                 self.fused = FusedGemvAllReduce(self.dev, 0, 1, arena=self.arena, ar_group=switches().ar_group)
         self.dcp = None          # (d, n_dcp, DcpAttentionMerge): decode-context-parallel attention
+        # (d, n): this rank of a decode-context-parallel group of n stores ONLY the latent pages p with p % n == d,
+        # compactly (page p of a slot at latent page p // n): 1 / n of the latent cache per rank.  The indexer caches
+        # stay whole on every rank (the top-k is global).
+        self.dcp_shard = dcp_shard
         # decode GEMVs with at least this many output rows go to the tcgen05 split-K kernel (0 = never)
         sw = switches()
         self.tc_gemv_min_n, self.tc_gemv_max_n = sw.tc_gemv_min_n, sw.tc_gemv_max_n
@@ -288,6 +297,10 @@ class GlmDeviceModel:
         n_total = cfg.num_layers + cfg.num_nextn_predict_layers
         for i in range(n_total):
             pfx = f"model.layers.{i}"
+            owned = (self.l0 <= i < self.l1) if i < cfg.num_layers else self.l1 == cfg.num_layers
+            if not owned:
+                self.layers.append(None)      # another stage's layer: no weights here
+                continue
             L = {"idx": i, "dsa": cfg.is_dsa(i), "moe": cfg.is_moe(i), "mtp": i >= cfg.num_layers}
             L["ln1"] = self._f(src.get(f"{pfx}.input_layernorm.weight"))
             L["ln2"] = self._f(src.get(f"{pfx}.post_attention_layernorm.weight"))
@@ -350,15 +363,16 @@ class GlmDeviceModel:
         ws["dsa_ml"] = self._z(M, self.nsplit, self.h_dsa, 2)
         ws["dsa_ctx"] = self._act(self.h_dsa * ds.kv_lora_rank)
         ws["dsa_ov"] = self._act(self.h_dsa * ds.v_head_dim)
-        Imax = max([L.get("I_dense", 0) for L in self.layers] + [L.get("I_shared", 0) for L in self.layers] + [8])
+        owned = [L for L in self.layers if L is not None]
+        Imax = max([L.get("I_dense", 0) for L in owned] + [L.get("I_shared", 0) for L in owned] + [8])
         Imax += (-Imax) % 8
         ws["gu"] = self._z(M, 2 * Imax)
         ws["act"] = self._act(Imax)
-        Ismax = max([L.get("I_shared", 0) for L in self.layers] + [1])
+        Ismax = max([L.get("I_shared", 0) for L in owned] + [1])
         ws["moe_lg"] = self._z(M, cfg.n_routed_experts + 2 * Ismax)
         ws["moe_ids"] = self._z(M, cfg.num_experts_per_tok, dtype=torch.int32)
         ws["moe_wts"] = self._z(M, cfg.num_experts_per_tok)
-        Il = max([L.get("I_moe", 0) for L in self.layers] + [8])
+        Il = max([L.get("I_moe", 0) for L in owned] + [8])
         Il += (-Il) % 8
         ws["moe_act"] = self._z(M, cfg.num_experts_per_tok, Il)
         ws["moe_act_s"] = torch.zeros(4, M * cfg.num_experts_per_tok, Il, dtype=torch.int16, device=self.dev)
@@ -403,7 +417,18 @@ class GlmDeviceModel:
         self.num_pages = self.num_pages_arg or S * self.max_pages
         nf = cfg.n_dsa_families
         kvdt = torch.float32 if self.kv_f32 else torch.bfloat16
-        self.lat_cache = torch.zeros(nf, self.num_pages, ps, ds.kv_lora_rank, dtype=kvdt, device=self.dev)
+        self.lat_table = None
+        lat_pages = self.num_pages
+        if self.dcp_shard is not None:
+            d, nd = self.dcp_shard
+            assert not self.num_pages_arg, "compact DCP storage is built on static identity paging"
+            self.lat_pages_slot = (self.max_pages + nd - 1) // nd
+            lat_pages = S * self.lat_pages_slot
+            lp = torch.arange(self.max_pages)
+            row = torch.where(lp % nd == d, lp // nd, torch.full_like(lp, -1))
+            tab = torch.stack([torch.where(row >= 0, row + s_ * self.lat_pages_slot, row) for s_ in range(S)])
+            self.lat_table = tab.to(torch.int32).to(self.dev).contiguous()
+        self.lat_cache = torch.zeros(nf, lat_pages, ps, ds.kv_lora_rank, dtype=kvdt, device=self.dev)
         self.kidx_cache = self._z(nf, self.num_pages, ps, ds.index_head_dim)
         self.kgate_cache = self._z(nf, self.num_pages, ps, ds.index_head_dim)
         self.pool_cache = self._z(nf, self.num_pages, ps // ds.index_kpool, ds.index_head_dim)
@@ -627,8 +652,9 @@ class GlmDeviceModel:
         pt, mp, ps = self.page_table, self.max_pages, ds.page_size
         qa, qq, ctx, ov = ws["dsa_qa"], ws["dsa_qq"], ws["dsa_ctx"], ws["dsa_ov"]
         self.K.call("fb_dsa_prep", ws["dsa_proj"], ldp, L["qa_ln"], L["kv_ln"], L["kn_w"], L["kn_b"], qa.f,
-                    ws["dsa_wi"], self.lat_cache[f], self.kidx_cache[f], self.kgate_cache[f], rs.meta, pt, mp, ps,
-                    n, QL, DL, ID, IH, float(cfg.rms_norm_eps), int(self.kv_f32), *qa.sp(1))
+                    ws["dsa_wi"], self.lat_cache[f], self.kidx_cache[f], self.kgate_cache[f], rs.meta, pt, self.lat_table,
+                    mp, ps, n, QL, DL, ID, IH, float(cfg.rms_norm_eps), int(self.kv_f32), *qa.sp(1))
+        lt = self.lat_table if self.lat_table is not None else pt     # the latent cache's own page table
         self.K.call("fb_dsa_pool", self.kidx_cache[f], self.kgate_cache[f], L["ape"], self.pool_cache[f], rs.meta,
                     pt, mp, ps, n, ID, ds.index_kpool)
         self.gemv(L["w_q"], qa, qq, n, self.ld_qq, QL, omask=1)
@@ -641,11 +667,11 @@ class GlmDeviceModel:
         d_, n_ = (self.dcp[0], self.dcp[1]) if self.dcp is not None else (0, 1)
         if DL == 512 and not self.kv_f32:   # tensor-core form (bf16 latents)
             self.K.call("fb_dsa_attn_partial_tc", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
                         float(dk ** -0.5))
         else:
             self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, pt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
                         float(dk ** -0.5), int(self.kv_f32))
         if self.dcp is None:
             self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, self.nsplit, 1,
@@ -792,9 +818,10 @@ class GlmDeviceModel:
         K.call("fb_prep_rows", rs.row_slot, rs.row_off, rs.row_gsize, self.main_len, rs.meta, n, self.ecfg.max_ctx,
                self.row_status)
         ws["R"] = ws["R0"]
-        K.call("fb_embed_expand", ids, self.embed, ws["R"], n, H, cfg.hc_mult, cfg.vocab_size)
-        ws["R"] = ws["R0"]
-        main = self.layers[:cfg.num_layers]
+        if self.l0 == 0:
+            K.call("fb_embed_expand", ids, self.embed, ws["R"], n, H, cfg.hc_mult, cfg.vocab_size)
+        # a later pipeline stage finds the residual streams of its rows in ws["R0"][:n] (the previous stage's output)
+        main = self.layers[self.l0:self.l1]
         self._hc_post_mix(main[0]["hc_attn_fn"], n, first=True)
         for li, L in enumerate(main):
             self._hc_pre(L, "attn", L["ln1"], n, first=(li == 0))
@@ -811,15 +838,16 @@ class GlmDeviceModel:
             self._hc_post_mix(fn_next, n)
             if self.debug_hook:
                 self.debug_hook(L["idx"], "ffn", ws, n)
-        xh = ws["xh"]
-        K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], xh.f, n, H, cfg.hc_mult,
-               float(cfg.rms_norm_eps), *xh.sp(1))
-        V = self.lm_head.shape[0]
-        nh = n - head_from  # the head runs on rows [head_from, n); their logits land in rows [0, nh)
-        if nh > 0:
-            self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
-            if judges is not None:
-                self._argmax(View(judges, head_from), nh, V)
+        if self.l1 == cfg.num_layers:
+            xh = ws["xh"]
+            K.call("fb_hc_head", ws["R"], self.final_norm, ws["h_final"], xh.f, n, H, cfg.hc_mult,
+                   float(cfg.rms_norm_eps), *xh.sp(1))
+            V = self.lm_head.shape[0]
+            nh = n - head_from  # the head runs on rows [head_from, n); their logits land in rows [0, nh)
+            if nh > 0:
+                self.gemv(self.lm_head, xh, ws["logits"], nh, V, H, xcol=head_from * H)
+                if judges is not None:
+                    self._argmax(View(judges, head_from), nh, V)
         if advance:
             K.call("fb_advance_rows", rs.meta, None, self.main_len, n)
 

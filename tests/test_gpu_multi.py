@@ -28,3 +28,14 @@ def test_pdaf_handoff_prefill_rank_to_decode_rank():
            "--master-addr", "127.0.0.1", "--master-port", "29543", os.path.join(HERE, "_pdaf_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "PDAF_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_cp_prefill_group_hands_off_to_compact_dcp_group():
+    """Layer-split prefill over two stages, per-stage export to a DCP group of two with compact latent pages."""
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29545", os.path.join(HERE, "_cp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
