@@ -127,12 +127,14 @@ def kernel_times(eng, mtp, path, barrier, steps=5):
     from torch.profiler import ProfilerActivity, profile
     barrier()
     if path is None:
+        barrier()
         for _ in range(steps):
             eng.launch_step_async(mtp)
         torch.cuda.synchronize()
         barrier()
         return
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        barrier()     # the profiler's start-up is over: the peers' bounded waits must not pay for it
         for _ in range(steps):
             eng.launch_step_async(mtp)
         torch.cuda.synchronize()
