@@ -49,7 +49,7 @@ class Dsv41Engine(SpecStep):
         self.pos = 0
         self.accept_hist: List[int] = []
         from ..parallel.collective import startup_barrier
-        startup_barrier(world)
+        startup_barrier(world, getattr(allreduce, "group", None))
 
     # ---- context limit -----------------------------------------------------------------------------
     def _step_rows(self) -> int:

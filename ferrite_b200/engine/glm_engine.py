@@ -53,7 +53,7 @@ class GlmEngine(SpecStep):
         self.launches_mtp = 0
         self.n_ctx = 0
         from ..parallel.collective import startup_barrier
-        startup_barrier(world)
+        startup_barrier(world, getattr(allreduce, "group", None))
 
     # ------------------------------------------------------------------ context limit
     def max_prompt(self) -> int:

@@ -91,7 +91,7 @@ class GpuEngine:
         self.snap_host = (torch.zeros(host_snapshots, *gs.shape).pin_memory(), torch.zeros(host_snapshots, *cs.shape).pin_memory())
         self.launches = 0
         from ..parallel.collective import startup_barrier
-        startup_barrier(world)
+        startup_barrier(world, getattr(allreduce, "group", None))
 
     # ------------------------------------------------------------------ ServeEngine
     def validate(self, spec: RequestSpec) -> None:

@@ -12,28 +12,32 @@ import torch.distributed as dist
 
 
 def make_allreduce(device, rank: int, world: int, max_elems: int, kind: str = "nccl", fused: bool = True,
-                   max_spins: int = 0):
+                   max_spins: int = 0, group=None):
     """kind "p2p" also carries ``.fused``, the GEMV + all-reduce (+ fold) kernel for decode rows, and
-    ``.gemm_fused``, the tcgen05 GEMM + two-shot all-reduce kernel for prefill rows, unless fused=False."""
+    ``.gemm_fused``, the tcgen05 GEMM + two-shot all-reduce kernel for prefill rows, unless fused=False.
+    ``group``: the process group of the ``world`` ranks (``rank`` is the rank inside it); None = all ranks."""
     if kind == "p2p":
         from .status import StatusArena
         from .symm import DEFAULT_MAX_SPINS, CrossRankArgmax, FusedGemmAllReduce, FusedGemvAllReduce, P2PAllReduce
         spins = max_spins or DEFAULT_MAX_SPINS
         arena = StatusArena(device)   # one block of status / epoch / ticket words per rank, read back once per step
-        ar = P2PAllReduce(device, rank, world, max_elems, max_spins=spins, arena=arena)
+        ar = P2PAllReduce(device, rank, world, max_elems, max_spins=spins, arena=arena, group=group)
+        ar.group = group
         if fused:
-            ar.fused = FusedGemvAllReduce(device, rank, world, max_spins=spins, arena=arena)
-            ar.gemm_fused = FusedGemmAllReduce(device, rank, world, max_rows=256, n_max=8192, max_spins=spins, arena=arena)
-        ar.argmax = CrossRankArgmax(device, rank, world, max_spins=spins, arena=arena)   # enables the vocab-sliced head
+            ar.fused = FusedGemvAllReduce(device, rank, world, max_spins=spins, arena=arena, group=group)
+            ar.gemm_fused = FusedGemmAllReduce(device, rank, world, max_rows=256, n_max=8192, max_spins=spins, arena=arena,
+                                               group=group)
+        ar.argmax = CrossRankArgmax(device, rank, world, max_spins=spins, arena=arena, group=group)   # vocab-sliced head
         return ar
 
     def nccl_allreduce(view: torch.Tensor):
-        dist.all_reduce(view)
+        dist.all_reduce(view, group=group)
 
+    nccl_allreduce.group = group
     return nccl_allreduce
 
 
-def startup_barrier(world: int) -> None:
+def startup_barrier(world: int, group=None) -> None:
     """Line the ranks up after an engine is built and before its first peer-memory launch.  Weight loading
     and graph warm-up take seconds to minutes and differ between ranks; the device-side waits are sized for
     the skew inside a step (about two seconds), so the start-up skew is absorbed here, on the host, where a
@@ -41,7 +45,7 @@ def startup_barrier(world: int) -> None:
     if world > 1 and dist.is_available() and dist.is_initialized():
         if torch.cuda.is_available():
             torch.cuda.synchronize()
-        dist.barrier()
+        dist.barrier(group=group)
 
 
 def self_test(ar, device, rank: int, world: int) -> dict:

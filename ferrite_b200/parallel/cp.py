@@ -146,9 +146,11 @@ def _caches(model):
     return {"lat": model.lat_cache, "kidx": model.kidx_cache, "kgate": model.kgate_cache, "pool": model.pool_cache}
 
 
-def _parts(src_model, dst_model, plan: TransferPlan, fams, gidx, compact: bool, slot: int):
+def _parts(src_model, dst_model, plan: TransferPlan, fams, gidx, compact: bool, slot: int, tp=(0, 1)):
     """Matching (source view builder, destination writer) pairs of one stage -> decode-rank transfer, in a
-    fixed order.  Either model may be None (the side that is on another rank)."""
+    fixed order.  Either model may be None (the side that is on another rank).  ``tp = (r, n)``: the destination
+    is tensor-parallel rank r of n and takes its heads of the recurrent states (the caches are replicated)."""
+    td, tn = tp
     items = []
     dev = (src_model or dst_model).dev
     f_idx = torch.tensor(fams, dtype=torch.long, device=dev)
@@ -177,25 +179,41 @@ def _parts(src_model, dst_model, plan: TransferPlan, fams, gidx, compact: bool, 
         out.append((shape, dtype, read, write))
     for nm in ("gdn_state", "conv_state"):
         for gi in gidx:
-            ref = getattr(src_model or dst_model, nm)
-            shape = tuple(ref[gi, slot].shape)
+            if src_model is not None:
+                full = getattr(src_model, nm)[gi, slot]          # [nbuf, heads, dk, dv] or [nbuf, 3 P, taps]
+                per = full.shape[1] // tn if nm == "gdn_state" else full.shape[1] // (3 * tn)
+                shape = (full.shape[0], per if nm == "gdn_state" else 3 * per) + tuple(full.shape[2:])
+            else:
+                shape = tuple(getattr(dst_model, nm)[gi, slot].shape)
+            dtype = getattr(src_model or dst_model, nm).dtype
 
             def read(nm=nm, gi=gi):
-                return getattr(src_model, nm)[gi, slot].contiguous()
+                full = getattr(src_model, nm)[gi, slot]
+                if tn == 1:
+                    return full.contiguous()
+                if nm == "gdn_state":
+                    hl = full.shape[1] // tn
+                    return full[:, td * hl:(td + 1) * hl].contiguous()
+                pf = full.shape[1] // 3                          # q | k | v channel thirds, each split by heads
+                pl = pf // tn
+                return torch.cat([full[:, j * pf + td * pl:j * pf + (td + 1) * pl] for j in range(3)], 1).contiguous()
 
             def write(buf, nm=nm, gi=gi):
                 getattr(dst_model, nm)[gi, slot].copy_(buf)
-            out.append((shape, ref.dtype, read, write))
+            out.append((shape, dtype, read, write))
     return out
 
 
 def hand_off(stage: Optional[CpStage], engine, n_ctx: int, stage_ranks: Sequence[int], decode_ranks: Sequence[int],
-             cfg, rank: int, compact: bool = True, group=None, slot: int = 0) -> float:
+             cfg, rank: int, compact: bool = True, group=None, slot: int = 0, mode: str = "dcp") -> float:
     """Move a prefilled sequence from the prefill group to the decode group.  Every rank of either group calls
     this with the same arguments (``stage``: this rank's CpStage or None, ``engine``: this rank's decode engine
     or None).  Transfers run in one global order (stage by stage, decode rank by decode rank); a rank sends,
-    receives, copies locally (it is both ends) or skips each of them.  Returns this rank's wall time."""
-    n_stages, n_dcp = len(stage_ranks), len(decode_ranks)
+    receives, copies locally (it is both ends) or skips each of them.  ``mode``: "dcp" - the decode ranks hold
+    whole models and split the latent pages; "tp" - the decode ranks are a tensor-parallel group (every rank gets
+    all pages and its own heads of the recurrent states).  Returns this rank's wall time."""
+    n_stages = len(stage_ranks)
+    n_dcp = len(decode_ranks) if mode == "dcp" else 1
     ps = cfg.dsa.page_size
     t0 = time.perf_counter()
     dev = (stage.model if stage is not None else engine.model).dev
@@ -205,10 +223,11 @@ def hand_off(stage: Optional[CpStage], engine, n_ctx: int, stage_ranks: Sequence
         for d, dr in enumerate(decode_ranks):
             if rank != sr and rank != dr:
                 continue
-            plan = TransferPlan(n_ctx, ps, n_dcp, d)
+            plan = TransferPlan(n_ctx, ps, n_dcp, d if mode == "dcp" else 0)
             src_m = stage.model if rank == sr else None
             dst_m = engine.model if rank == dr else None
-            parts = _parts(src_m, dst_m, plan, fams, gidx, compact, slot)
+            parts = _parts(src_m, dst_m, plan, fams, gidx, compact, slot,
+                           tp=(d, len(decode_ranks)) if mode == "tp" else (0, 1))
             last = s == n_stages - 1
             if rank == sr and rank == dr:
                 for _, _, read, write in parts:

@@ -70,6 +70,38 @@ def main():
         dist.barrier()
         if merge is not None:
             merge.close()
+    # the same prefill group handing off to a TENSOR-PARALLEL decode group: every decode rank gets all cache pages
+    # and its own heads of the recurrent states (2 ranks: both groups are {0, 1})
+    if world == 2:
+        from ferrite_b200.parallel.collective import make_allreduce
+        ar = make_allreduce(dev, rank, world, max_elems=64 * cfg.hidden_size, kind="p2p")
+        for mtp_n in (1, 3):
+            ecfg1 = EngineConfig(max_ctx=256, mtp_n=mtp_n, kv_dtype="f32")
+            ecfg2 = EngineConfig(max_ctx=256, mtp_n=mtp_n, kv_dtype="f32", tp=world)
+            stage = CpStage(cfg, ecfg1, DictSource(w, dev), rank, 2, [0, 1], dev, prefill_rows=16)
+            eng = GlmEngine(cfg, ecfg2, DictSource(w, dev), rank=rank, world=world, device=dev, allreduce=ar, prefill_rows=16)
+            first = torch.zeros(1, dtype=torch.int64, device=dev)
+            t = stage.prefill(prompt)
+            if t is not None:
+                first[0] = t
+            hand_off(stage, eng, len(prompt), [0, 1], [0, 1], cfg, rank, mode="tp")
+            dist.broadcast(first, 1)
+            out = [int(first.item())]
+            eng.build_graphs(mtp_n > 1)
+            while len(out) < 14:
+                out += eng.spec_step() if mtp_n > 1 else [eng.step_plain()]
+            ar.check()
+            ref = GlmEngine(cfg, ecfg1, DictSource(w, dev), device=dev, prefill_rows=16)
+            want, _ = ref.generate(prompt, 14)
+            same = sum(a == b for a, b in zip(out[:14], want))
+            assert same >= 12, (mtp_n, rank, out, want)      # shards quantise their own fp8 blocks
+            tt = torch.tensor(out[:14], device=dev)
+            t0 = tt.clone()
+            dist.broadcast(t0, 0)
+            assert torch.equal(tt, t0), "TP ranks emitted different tokens"
+            if rank == 0:
+                print(f"cp2 -> tp2 mtp_n={mtp_n}: {out[:14]} ({same}/14 equal to one rank)")
+            dist.barrier()
     dist.destroy_process_group()
     if rank == decode_ranks[-1]:
         print("CP_WORKER_OK")
