@@ -1,17 +1,16 @@
 // One-shot all-reduce over NVLink peer memory, with bounded waits and a status word.
 //
-// Every rank owns a symmetric region: staging[2 parity][world][max_elems] f32 and
+// Every rank owns a symmetric region: staging[2 parity][world][max_elems] (value, epoch) pairs and
 // flags[2][world][kMaxChunks] u32, mapped into every peer through CUDA IPC.  One launch does
 // the whole collective for payloads of a few rows of the hidden size (16-48 KB):
-//   1. push: each CTA owns a 4096-element chunk and stores its part of the local vector
-//      into slot `rank` of EVERY peer's staging (16-byte peer stores over NVLink);
-//   2. publish: bar.sync, then one thread fences at system scope and release-stores the
-//      epoch stamp of that chunk into every peer's flag word;
-//   3. wait: the CTA polls its OWN flag words (peers write them into local memory, so a
-//      poll never crosses NVLink) until all peers carry the epoch -- at most `max_spins`
-//      polls, after which the kernel records {TIMEOUT, peer, epoch, chunk} in the status
-//      buffer and leaves the vector unreduced instead of spinning, trapping or parking;
-//   4. reduce: slots are summed in rank order, so every rank gets bit-identical sums.
+//   1. push: each CTA owns a 4096-element chunk and stores its part of the local vector into slot `rank` of
+//      EVERY peer's staging as 8-byte (value, epoch) pairs, two per 16-byte peer store over NVLink.  A pair that
+//      carries the launch's epoch IS the data: no fence and no flag follow the stores (with tile stores + a
+//      system-scope fence + a flag per chunk the 3 x 4096 case took 18 us on 4 GPUs);
+//   2. wait: each thread polls its OWN four pairs of every peer's slot in local staging (a poll never crosses
+//      NVLink) -- at most `max_spins` polls, after which the kernel records {TIMEOUT, peer, epoch, chunk} in the
+//      status buffer and leaves the vector unreduced instead of spinning, trapping or parking;
+//   3. reduce: slots are summed in rank order, so every rank gets bit-identical sums.
 // Epochs advance only inside this kernel, chunk by chunk, so warm-up, capture and replay
 // keep all ranks in lockstep; staging is double-buffered by epoch parity, which is enough
 // because a rank publishes epoch e+1 only after it finished reducing epoch e.
@@ -41,62 +40,70 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+
+// One chunk of the all-reduce: push `v`, wait, and return the rank-ordered sum of the four chunk elements owned by
+// this thread.  Low-latency exchange: every value travels as an 8-byte (value, epoch) pair (two pairs per 16-byte
+// peer store); a pair that carries the launch's epoch IS the data, so no fence and no flag stand between the peer
+// stores and the peers' reduction, and a thread polls only its own pairs in LOCAL staging.  Staging is double-buffered
+// by epoch parity (a peer can be at most one launch ahead: it needs this rank's pairs to finish one).  `ok` is false
+// after a timeout (v is then returned unchanged).
+__device__ __forceinline__ float2 ld_relaxed_sys_f2(const float2* p) {
+    float2 v;
+    asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
     return v;
 }
-
-// Shared by the stand-alone all-reduce and the fused epilogues: push `v`, publish, wait,
-// and return the rank-ordered sum of the chunk element owned by this thread.  `ok` is false
-// after a timeout (v is then returned unchanged).
 __device__ __forceinline__ float4 ar_chunk(const ArTables& t, uint32_t* epoch, int* status, int rank, int world,
                                            int max_elems, int max_spins, int chunk, float4 v, bool valid, bool* ok) {
     __shared__ int s_fail;
     const uint32_t e = epoch[chunk] + 1u;
     const int par = e & 1u;
+    const float ef = __uint_as_float(e);
     const size_t off = (size_t)chunk * kChunk + threadIdx.x * 4;
     if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    float4 acc = v;
     if (valid) {
         for (int p = 0; p < world; ++p) {
-            float* dst = t.staging[p] + ((size_t)par * world + rank) * max_elems + off;
-            *reinterpret_cast<float4*>(dst) = v;
+            if (p == rank) continue;
+            float2* dst = reinterpret_cast<float2*>(t.staging[p]) + ((size_t)par * world + rank) * max_elems + off;
+            reinterpret_cast<float4*>(dst)[0] = make_float4(v.x, ef, v.y, ef);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(v.z, ef, v.w, ef);
         }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        for (int p = 0; p < world; ++p) st_release_sys(t.flags[p] + ((size_t)par * world + rank) * kMaxChunks + chunk, e);
-    }
-    if (threadIdx.x < world) {
-        const uint32_t* f = t.flags[rank] + ((size_t)par * world + threadIdx.x) * kMaxChunks + chunk;
-        int spins = 0;
         const int budget = fb_spin_budget(status, max_spins);
-        // stamps only grow; a stamp ahead of e cannot occur (see the parity argument above)
-        while (ld_acquire_sys(f) < e) {
-            if (++spins > budget) {
-                if (atomicCAS(&s_fail, 0, 1) == 0) {
-                    status[0] = FB_TIMEOUT; status[1] = threadIdx.x; status[2] = (int)e; status[3] = chunk;
-                }
-                break;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float mine[4] = {v.x, v.y, v.z, v.w};
+        bool failed = false;
+        for (int src = 0; src < world && !failed; ++src) {      // rank order: identical bits on every rank
+            if (src == rank) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s4[j] += mine[j];
+                continue;
             }
-            __nanosleep(32);
+            const float2* f = reinterpret_cast<const float2*>(t.staging[rank]) + ((size_t)par * world + src) * max_elems + off;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 pr = ld_relaxed_sys_f2(f + j);
+                int spins = 0;
+                while (__float_as_uint(pr.y) != e) {
+                    if (++spins > budget) {
+                        if (atomicCAS(&s_fail, 0, 1) == 0) {
+                            status[0] = FB_TIMEOUT; status[1] = src; status[2] = (int)e; status[3] = chunk;
+                        }
+                        failed = true;
+                        break;
+                    }
+                    pr = ld_relaxed_sys_f2(f + j);
+                }
+                s4[j] += pr.x;
+            }
         }
+        acc = make_float4(s4[0], s4[1], s4[2], s4[3]);
     }
     __syncthreads();
     const bool good = (s_fail == 0);
     *ok = good;
-    float4 acc = v;
-    if (good && valid) {
-        acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int src = 0; src < world; ++src) {
-            const float4 a = ld_cg_f4(t.staging[rank] + ((size_t)par * world + src) * max_elems + off);
-            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
-        }
-    }
-    __syncthreads();
     if (threadIdx.x == 0) epoch[chunk] = e;  // stay in step with the peers even after a timeout
-    return acc;
+    return good ? acc : v;
 }
 
 __global__ void __launch_bounds__(1024)

@@ -92,7 +92,7 @@ class P2PAllReduce(_Checked):
         self.K.lib.fb_ar_limits(ctypes.byref(mc), ctypes.byref(ce))
         self.max_chunks, self.chunk = mc.value, ce.value
         self.max_elems = min((max_elems + self.chunk - 1) // self.chunk, self.max_chunks) * self.chunk
-        self.staging = SymmetricRegion(2 * world * self.max_elems * 4, rank, world, group)
+        self.staging = SymmetricRegion(2 * world * self.max_elems * 8, rank, world, group)   # (value, epoch) pairs
         self.flags = SymmetricRegion(2 * world * self.max_chunks * 4, rank, world, group)
         self.epoch = self.arena.take(self.max_chunks, "allreduce.epoch")
         self.status = self.arena.status("allreduce")
