@@ -133,6 +133,7 @@ class GlmDeviceModel:
             self.K.lib.fb_set_l2_ahead(sw.l2_ahead)
         self.K.lib.fb_set_pdl(1 if sw.pdl else 0)
         self._tc_part = self._tc_ticket = None
+        self._dense_tc, self._dense_act = {}, None     # per-row-count tile lists / f16 staging of the dense FFN's tcgen05 path
         self.fused_rows = 8      # forwards of up to this many rows use the fused epilogue; above 8 rows the kernel
                                  # would stream the weights once per 8-row window, where the tcgen05 GEMM streams them once
         self._fold_next = None   # (fn_next, front) while a hyper-connection site's sublayer runs; front = (scale,
@@ -665,22 +666,26 @@ class GlmDeviceModel:
                     n, ds.index_kpool, ds.select_pools)
         self.gemv(L["wk_abs"], qq, ws["dsa_qabs"], n, hl * DL, dk, group_rows=DL)
         d_, n_ = (self.dcp[0], self.dcp[1]) if self.dcp is not None else (0, 1)
+        # key splits: decode rows need them to fill the GPU; a prefill chunk has a CTA per row already, and every
+        # split re-reads the row's 64 x 512 query and adds a partial to merge (1024 rows x 32 splits: 3.3 ms + 0.7 ms
+        # per layer against a fraction of that unsplit)
+        ns = self.nsplit if n <= 64 else (2 if n < 256 else 1)
         if DL == 512 and not self.kv_f32:   # tensor-core form (bf16 latents)
             self.K.call("fb_dsa_attn_partial_tc", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, ns, d_, n_,
                         float(dk ** -0.5))
         else:
             self.K.call("fb_dsa_attn_partial", ws["dsa_qabs"], self.lat_cache[f], ws["dsa_idx"], ldi, ws["dsa_cnt"],
-                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, self.nsplit, d_, n_,
+                        ws["dsa_opart"], ws["dsa_ml"], rs.meta, lt, mp, ps, n, hl, DL, ns, d_, n_,
                         float(dk ** -0.5), int(self.kv_f32))
         if self.dcp is None:
-            self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, self.nsplit, 1,
+            self.K.call("fb_dsa_attn_merge", ws["dsa_opart"], ws["dsa_ml"], ctx.f, None, n, hl, DL, ns, 1,
                         *ctx.sp(1))
         else:
             # decode context parallel: this rank attends over its own pages (page % n_dcp == d) of the
             # global top-k list; the merge kernel exchanges the partials with the peers and finishes
             merge = self.dcp[2]
-            merge(ws["dsa_opart"], ws["dsa_ml"], ctx.f, n, hl, DL, self.nsplit, ctx.sp(1))
+            merge(ws["dsa_opart"], ws["dsa_ml"], ctx.f, n, hl, DL, ns, ctx.sp(1))
         self.gemv(L["wv_abs"], ctx, ov, n, hl * dv, DL, group_rows=dv, omask=1)
         self._out_gemv(L["o_proj"], ov, n, H, hl * dv)
 
@@ -689,6 +694,32 @@ class GlmDeviceModel:
         H, I = cfg.hidden_size, L["I_dense"]
         ldg = ws["gu"].shape[1]
         act = ws["act"]
+        if (L.get("d13s") is not None and 0 < self.moe_tc_rows <= n and H % 128 == 0 and I % 128 == 0 and "tc_x" in ws
+                and ws["y"].shape[1] % 4 == 0):
+            # prefill rows: the e4m3 dense FFN as a one-expert case of the grouped W8A16 tcgen05 GEMM
+            K = self.K
+            self._fold_next = None
+            t = self._dense_tc.get(n)
+            if t is None:
+                bn = 32 if n <= 32 else 64 if n <= 64 else 128
+                mt = (n + bn - 1) // bn + 1
+                i32 = lambda *a: torch.zeros(*a, dtype=torch.int32, device=self.dev)
+                t = {"tiles": i32(mt, 4), "nt": i32(1), "off": i32(2), "bn": bn, "mt": mt,
+                     "cnt": torch.tensor([n], dtype=torch.int32, device=self.dev),
+                     "iota": torch.arange(n, dtype=torch.int32, device=self.dev), "ones": torch.ones(n, device=self.dev)}
+                K.call("fb_mx_tiles", t["cnt"], 1, bn, t["tiles"], t["nt"], t["off"], mt)
+                self._dense_tc[n] = t
+            if self._dense_act is None or self._dense_act.shape[1] < max(I, H):
+                self._dense_act = torch.zeros(self.max_rows, max(I, H), dtype=torch.float16, device=self.dev)
+            xh = self._dense_act
+            K.call("fb_scatter_rows_f16", ws["x"].f, ws["x"].ld, t["iota"], 1, n, H, xh)
+            K.call("fb_fp8w_gemm_grouped", L["d13"], L["d13s"], xh, t["tiles"], t["nt"], t["mt"], ws["gu"], ldg, n, 1,
+                   2 * I, H, t["bn"], self.tc_status)
+            K.call("fb_swiglu_rows_f16", ws["gu"], ldg, t["ones"], t["cnt"], n, I, float(cfg.swiglu_limit), xh)
+            K.call("fb_fp8w_gemm_grouped", L["d2"], L["d2s"], xh, t["tiles"], t["nt"], t["mt"], ws["y"], ws["y"].shape[1],
+                   n, 1, H, I, t["bn"], self.tc_status)
+            self._reduce(ws["y"], n)
+            return
         self.gemv(L["d13"], ws["x"], ws["gu"], n, 2 * I, H, ldo=ldg, scales=L.get("d13s"))
         # SwiGLU rides in the down projection's activation load (or runs as its own kernel, rows packed with stride I)
         self._out_gemv(L["d2"], act, n, H, I, ldx=I, scales=L.get("d2s"), swiglu=(ws["gu"], ldg, I))
