@@ -129,12 +129,14 @@ constexpr int kPmThreads = 128; // one float4 column of R per thread -> 512 colu
 // grid = (ceil(H/512), n, kMixGroups); every z recomputes R' for its columns (cheap), z == 0
 // writes it and owns the sum of squares.  With a mix (several z) Rout must not alias Rin:
 // the other z blocks still read Rin.
+template <int G>
 __global__ void __launch_bounds__(kPmThreads)
 hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, const float* __restrict__ post,
                    const float* __restrict__ comb, const float* __restrict__ fn, float* __restrict__ acc,
                    int H, int mix) {
     PDL_PROLOGUE();
-    __shared__ float red[kPmThreads / 32][8];
+    constexpr int PER = (kMaxMix + G - 1) / G;     // mix rows per z block: 6 with four groups, 24 with one
+    __shared__ float red[kPmThreads / 32][PER + 1];
     const int r = blockIdx.y, z = blockIdx.z;
     const int j = (blockIdx.x * kPmThreads + threadIdx.x) * 4;
     const bool act = j < H;
@@ -167,14 +169,14 @@ hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, c
         }
     }
     if (!fn) return;
-    const int per = (mix + kMixGroups - 1) / kMixGroups;  // <= 6
+    const int per = (mix + G - 1) / G;  // <= PER
     const int m0 = z * per;
-    float part[7];
+    float part[PER + 1];
 #pragma unroll
-    for (int q = 0; q < 7; ++q) part[q] = 0.f;
+    for (int q = 0; q < PER + 1; ++q) part[q] = 0.f;
     if (act) {
 #pragma unroll
-        for (int q = 0; q < 6; ++q) {
+        for (int q = 0; q < PER; ++q) {
             const int m = m0 + q;
             if (q < per && m < mix) {
 #pragma unroll
@@ -186,22 +188,22 @@ hc_post_mix_kernel(const float* Rin, float* Rout, const float* __restrict__ y, c
         }
         if (z == 0) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) part[6] += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+            for (int i = 0; i < 4; ++i) part[PER] += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
         }
     }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int q = 0; q < 7; ++q) {
+    for (int q = 0; q < PER + 1; ++q) {
         const float s = warp_sum(part[q]);
         if (lane == 0) red[wid][q] = s;
     }
     __syncthreads();
-    if (threadIdx.x < 7) {
+    if (threadIdx.x < PER + 1) {
         const int q = threadIdx.x;
         float s = 0.f;
         for (int w = 0; w < kPmThreads / 32; ++w) s += red[w][q];
         float* a = acc + (size_t)r * (kMaxMix + 1);
-        if (q == 6) { if (z == 0) atomicAdd(a + kMaxMix, s); }
+        if (q == PER) { if (z == 0) atomicAdd(a + kMaxMix, s); }
         else if (q < per && m0 + q < mix) atomicAdd(a + m0 + q, s);
     }
 }
@@ -502,8 +504,12 @@ FB_API int fb_mtp_prep(const int* ids, const void* emb, const float* h_prev, con
 FB_API int fb_hc_post_mix(const float* Rin, float* Rout, const float* y, const float* post, const float* comb,
                           const float* fn, float* acc, int64_t n, int64_t H, int64_t mix, cudaStream_t st) {
     if (mix > kMaxMix || (H % 4) || (y && fn && Rin == Rout)) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned)((H / 4 + kPmThreads - 1) / kPmThreads), (unsigned)n, fn ? kMixGroups : 1);
-    FB_LAUNCH((hc_post_mix_kernel), grid, kPmThreads, 0, st, Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
+    // few rows: the mix rows go over four z blocks (each re-reads the row: latency matters, traffic does not);
+    // prefill-sized row counts: one block per (columns, row) does all of them and the row is read once
+    const bool wide = fn && n < 64;
+    dim3 grid((unsigned)((H / 4 + kPmThreads - 1) / kPmThreads), (unsigned)n, wide ? kMixGroups : 1);
+    if (wide) FB_LAUNCH((hc_post_mix_kernel<kMixGroups>), grid, kPmThreads, 0, st, Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
+    else FB_LAUNCH((hc_post_mix_kernel<1>), grid, kPmThreads, 0, st, Rin, Rout, y, post, comb, fn, acc, (int)H, (int)mix);
     return FB_LAUNCH_CHECK();
 }
 
