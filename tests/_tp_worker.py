@@ -232,6 +232,28 @@ def main():
             print(f"dsv41 tiny: tp{world} tokens {outs[False]} (tp1 agreement {same}/12)")
     dist.barrier()
     ar.close()
+    # A peer that does not join a launch (it left between steps, with nothing of its own in flight): the waiting
+    # rank's bounded poll runs out after a few milliseconds, the kernel returns, the status word names the peer,
+    # and the engine-level check raises.  No kernel is made to spin, trap or fault.
+    from ferrite_b200.parallel.status import CollectiveTimeout
+    ar2 = P2PAllReduce(dev, rank, world, max_elems=4 * 4096, max_spins=20000)
+    buf = torch.ones(1, 4096, device=dev)
+    ar2(buf)
+    torch.cuda.synchronize()
+    ar2.arena.verify()
+    assert float(buf[0, 0]) == world
+    dist.barrier()
+    if rank == 0:
+        ar2(buf)                      # nobody else launches this one
+        torch.cuda.synchronize()
+        try:
+            ar2.arena.verify()
+            raise AssertionError("the missing peers went unnoticed")
+        except CollectiveTimeout as e:
+            assert e.peer == 1 and e.name.startswith("allreduce"), (e.peer, e.name)
+            print(f"missing peer detected: {e}")
+    dist.barrier()
+    ar2.close()
     dist.destroy_process_group()
     if rank == 0:
         print("TP_WORKER_OK")
