@@ -4,11 +4,12 @@
 //   route (local)  ->  fb_ep_dispatch  ->  expert gate/up + down over the gathered rows (local experts
 //   only: the grouped tensor-core kernels skip slots whose expert lives elsewhere)  ->  fb_ep_combine.
 //
-// fb_ep_dispatch   each CTA pushes one local row - its split activation planes and its routing
-//                  (expert ids, weights) - into this rank's row block of EVERY rank's gather buffers
-//                  (16-byte peer stores), the grid publishes one epoch stamp per peer (GPU-scope fence
-//                  + ticket, a single system-scope fence), and waits, bounded, until all ranks' rows
-//                  have arrived.
+// fb_ep_dispatch   each CTA handles one local row: its routing (expert ids, weights: a few bytes) goes into this
+//                  rank's row block of every rank's gather buffers, its split activation planes ONLY to the ranks
+//                  that own one of its top-k experts (16-byte peer stores): NVLink carries a row once per distinct
+//                  owner, not once per rank.  The grid publishes one epoch stamp per peer (GPU-scope fence + ticket,
+//                  a single system-scope fence) and waits, bounded, until all ranks' rows have arrived.  A row block
+//                  entry whose ids name no local expert keeps stale planes; the expert kernels never read them.
 // fb_ep_combine    each CTA pushes one gathered row's partial output (the sum over this rank's experts,
 //                  already scaled by the routing weights) back to the rank that owns the token, into
 //                  slot `rank` of its staging; publish, bounded wait; the first n_loc CTAs then sum the
@@ -84,9 +85,9 @@ __device__ __forceinline__ bool publish_and_wait(const EpPtrs& t, int phase, uin
 // grid = n_loc CTAs (>= 1), 256 threads.  xs_local: [planes][n_loc_ld rows][H] planes of the local rows.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint16_t* __restrict__ xs_local, int local_plane, const int* __restrict__ ids,
-                   const float* __restrict__ wts, int n_loc, int n_max, int H, int topk, int planes, EpPtrs t,
-                   uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status, int rank,
-                   int world, int max_spins) {
+                   const float* __restrict__ wts, int n_loc, int n_max, int H, int topk, int planes, int e_per_rank,
+                   EpPtrs t, uint32_t* __restrict__ epoch, unsigned* __restrict__ ticket, int* __restrict__ status,
+                   int rank, int world, int max_spins) {
     PDL_PROLOGUE();
     __shared__ int s_fail;
     if (threadIdx.x == 0) s_fail = 0;
@@ -94,8 +95,16 @@ ep_dispatch_kernel(const uint16_t* __restrict__ xs_local, int local_plane, const
     const uint32_t e = epoch[0] + 1u;
     const size_t gather_plane = (size_t)world * n_max * H;
     const int grow = rank * n_max + r;   // this row's place in every rank's gather buffers
+    unsigned owners = 0xffffffffu;          // bit p: rank p owns one of this row's experts
+    if (e_per_rank > 0 && r < n_loc) {
+        owners = 0u;
+        for (int k = 0; k < topk; ++k) {
+            const int e = ids[(size_t)r * topk + k];
+            if (e >= 0) owners |= 1u << min(e / e_per_rank, 31);
+        }
+    }
     for (int p = 0; p < world; ++p) {
-        if (r < n_loc) {
+        if (r < n_loc && ((owners >> p) & 1u)) {
             for (int pl = 0; pl < planes; ++pl) {
                 const uint4* src = reinterpret_cast<const uint4*>(xs_local + (size_t)pl * local_plane + (size_t)r * H);
                 uint4* dst = reinterpret_cast<uint4*>(t.xs[p] + (size_t)pl * gather_plane + (size_t)grow * H);
@@ -156,15 +165,17 @@ static void fill_ptrs(EpPtrs& t, const void* const* ptrs, int world) {
     }
 }
 
+// e_per_rank > 0: experts [p * e_per_rank, (p + 1) * e_per_rank) live on rank p and a row's planes go to its owners
+// only; 0: every row goes to every rank.
 FB_API int fb_ep_dispatch(const void* xs_local, int64_t local_plane, const int* ids, const float* wts, int64_t n_loc,
-                          int64_t n_max, int64_t H, int64_t topk, int64_t planes, const void* const* ptrs, void* epoch,
+                          int64_t n_max, int64_t H, int64_t topk, int64_t planes, int64_t e_per_rank, const void* const* ptrs, void* epoch,
                           void* ticket, int* status, int64_t rank, int64_t world, int64_t max_spins, cudaStream_t st) {
     if ((H % 8) || world > kMaxWorld || n_loc > n_max || topk > 32 || n_max > 148) return (int)cudaErrorInvalidValue;
     EpPtrs t = {};
     fill_ptrs(t, ptrs, (int)world);
     FB_LAUNCH((ep_dispatch_kernel), n_max, 256, 0, st, (const uint16_t*)xs_local, (int)local_plane, ids, wts, (int)n_loc,
-              (int)n_max, (int)H, (int)topk, (int)planes, t, (uint32_t*)epoch, (unsigned*)ticket, status, (int)rank,
-              (int)world, (int)max_spins);
+              (int)n_max, (int)H, (int)topk, (int)planes, (int)e_per_rank, t, (uint32_t*)epoch, (unsigned*)ticket, status,
+              (int)rank, (int)world, (int)max_spins);
     return FB_LAUNCH_CHECK();
 }
 

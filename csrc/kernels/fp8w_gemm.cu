@@ -375,6 +375,21 @@ scatter_rows_f16_kernel(const float* __restrict__ src, int ld, const int* __rest
     }
 }
 
+// dst[pos[r * topk + k]] = src[r] for rows that are 16-bit already (one plane of a split activation buffer).
+__global__ void __launch_bounds__(256)
+scatter_rows_16_kernel(const uint16_t* __restrict__ src, int ld, const int* __restrict__ pos, int topk, int K,
+                       uint16_t* __restrict__ dst) {
+    PDL_PROLOGUE();
+    const int r = blockIdx.y;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= K) return;
+    const uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
+    for (int k = 0; k < topk; ++k) {
+        const int p = pos[r * topk + k];
+        if (p >= 0) *reinterpret_cast<uint4*>(dst + (size_t)p * K + c) = v;
+    }
+}
+
 // h [m, ldh] = [gate (I) | up (I)] of sorted row p -> act[p] = f16(wts[p] * silu(min(g, L)) * clamp(u, -L, L)).
 __global__ void __launch_bounds__(256)
 swiglu_rows_f16_kernel(const float* __restrict__ h, int ldh, const float* __restrict__ wts, const int* __restrict__ m_ptr,
@@ -425,6 +440,14 @@ FB_API int fb_scatter_rows_f16(const float* src, int64_t ld, const int* pos, int
     if ((K % 8) || (ld % 4)) return (int)cudaErrorInvalidValue;
     FB_LAUNCH((scatter_rows_f16_kernel), dim3((unsigned)((K / 8 + 255) / 256), (unsigned)n), 256, 0, st, src,
               (int)ld, pos, (int)topk, (int)K, (__half*)dst);
+    return FB_LAUNCH_CHECK();
+}
+
+FB_API int fb_scatter_rows_16(const void* src, int64_t ld, const int* pos, int64_t topk, int64_t n, int64_t K, void* dst,
+                              cudaStream_t st) {
+    if ((K % 8) || (ld % 8)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((scatter_rows_16_kernel), dim3((unsigned)((K / 8 + 255) / 256), (unsigned)n), 256, 0, st, (const uint16_t*)src,
+              (int)ld, pos, (int)topk, (int)K, (uint16_t*)dst);
     return FB_LAUNCH_CHECK();
 }
 

@@ -135,7 +135,7 @@ def main():
     # 1d. expert-parallel MoE (all-to-all dispatch / combine) == all experts applied to this rank's own rows
     from ferrite_b200.ops import reference as R
     from ferrite_b200.parallel.ep import EpMoE
-    H_, I_, E_, topk_, n_max_ = 256, 128, 4 * world, 2, 4
+    H_, I_, E_, topk_ = 256, 128, 4 * world, 2
     gw = torch.Generator().manual_seed(21)
     w13f = torch.randn(E_, 2 * I_, H_, generator=gw) * 0.05
     w2f = torch.randn(E_, H_, I_, generator=gw) * 0.05
@@ -147,30 +147,34 @@ def main():
     s13 = torch.stack([q13[e][1] for e in mine]).to(dev)
     w2 = torch.stack([q2[e][0] for e in mine]).to(dev)
     s2 = torch.stack([q2[e][1] for e in mine]).to(dev)
-    ep = EpMoE(dev, rank, world, n_max_, H_, topk_, I_)
-    for it, n_loc in enumerate((3, 4, 1)):
-        gx = torch.Generator().manual_seed(100 * it + rank)
-        xa = Act(dev, n_max_, H_)
-        xa.f[:n_loc].copy_(torch.randn(n_loc, H_, generator=gx))
-        K.call("fb_split_rows", xa.f, H_, *xa.sp(3), n_max_, H_)
-        ids = torch.stack([torch.randperm(E_, generator=gx)[:topk_] for _ in range(n_loc)]).to(torch.int32).to(dev)
-        wts = torch.rand(n_loc, topk_, generator=gx).to(dev)
-        add = torch.randn(n_max_, H_, generator=gx).to(dev)
-        y = torch.zeros(n_max_, H_, device=dev)
-        ep.forward(xa.s, xa.plane, ids, wts, n_loc, w13, s13, w2, s2, el, 7.0, y, add)
-        torch.cuda.synchronize()
-        ep.check()
-        want = add[:n_loc].cpu().clone()
-        xc = xa.f[:n_loc].cpu()
-        for r in range(n_loc):
-            for s_ in range(topk_):
-                e = int(ids[r, s_])
-                gu = xc[r] @ R.dequant_fp8_block(*q13[e]).t()
-                h = R.swiglu_limited(gu[:I_], gu[I_:], 7.0) * float(wts[r, s_])
-                want[r] += h @ R.dequant_fp8_block(*q2[e]).t()
-        err = (y[:n_loc].cpu() - want).abs().max().item()
-        assert err < 3e-2 * max(1.0, want.abs().max().item()), (it, n_loc, err)
-    ep.close()
+    # few rows: per-pair tensor-core kernels between dispatch and combine; 40 rows per rank: the gathered pairs are
+    # sorted by local expert and run through the grouped tcgen05 GEMM
+    for n_max_, cases in ((4, (3, 4, 1)), (40, (40, 17))):
+        ep = EpMoE(dev, rank, world, n_max_, H_, topk_, I_)
+        assert (world * n_max_ * topk_ >= ep.tc_pairs) == (n_max_ == 40)
+        for it, n_loc in enumerate(cases):
+            gx = torch.Generator().manual_seed(100 * it + rank)
+            xa = Act(dev, n_max_, H_)
+            xa.f[:n_loc].copy_(torch.randn(n_loc, H_, generator=gx))
+            K.call("fb_split_rows", xa.f, H_, *xa.sp(3), n_max_, H_)
+            ids = torch.stack([torch.randperm(E_, generator=gx)[:topk_] for _ in range(n_loc)]).to(torch.int32).to(dev)
+            wts = torch.rand(n_loc, topk_, generator=gx).to(dev)
+            add = torch.randn(n_max_, H_, generator=gx).to(dev)
+            y = torch.zeros(n_max_, H_, device=dev)
+            ep.forward(xa.s, xa.plane, ids, wts, n_loc, w13, s13, w2, s2, el, 7.0, y, add)
+            torch.cuda.synchronize()
+            ep.check()
+            want = add[:n_loc].cpu().clone()
+            xc = xa.f[:n_loc].cpu()
+            for r in range(n_loc):
+                for s_ in range(topk_):
+                    e = int(ids[r, s_])
+                    gu = xc[r] @ R.dequant_fp8_block(*q13[e]).t()
+                    h = R.swiglu_limited(gu[:I_], gu[I_:], 7.0) * float(wts[r, s_])
+                    want[r] += h @ R.dequant_fp8_block(*q2[e]).t()
+            err = (y[:n_loc].cpu() - want).abs().max().item()
+            assert err < 3e-2 * max(1.0, want.abs().max().item()), (it, n_loc, err)
+        ep.close()
     # 2. tensor-parallel engine == single-rank engine, token for token (greedy and MTP)
     for name in ("tiny", "golden4"):
         cfg = getattr(GlmConfig, name)()
