@@ -30,10 +30,15 @@ struct Cfg {
     static constexpr int kABytes = kTileW * kBK * 2;
     static constexpr int kBBytes = BN * kBK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+    static constexpr int kAccCols = BN < 32 ? 32 : BN;
+    static constexpr int kTmemCols = 2 * kAccCols;           // two accumulators: the epilogue of a tile overlaps the next tile's MMAs
     static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// Persistent: CTA c walks the tiles c, c + grid, c + 2 grid, ...; tile t = (weight tile t / MT, row tile t % MT), so the
+// CTAs that run side by side share a weight tile (read from HBM once, then from L2) and the activations stay in L2.
+// The shared-memory ring and both accumulators run across tile boundaries: while the epilogue warps drain tile i out
+// of one accumulator, the MMA warp is already filling the other with tile i + 1.
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -42,23 +47,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;  // SW128 tiles need 1024-byte alignment
-    const uint32_t bars = base + C::kStages * C::kStageBytes;         // full[S], empty[S], accum, tmem slot
+    const uint32_t bars = base + C::kStages * C::kStageBytes;         // full[S], empty[S], acc_full[2], acc_empty[2], slot
     auto full = [&](int s) { return bars + 8u * s; };
     auto empty = [&](int s) { return bars + 8u * (C::kStages + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * C::kStages);
-    const uint32_t tmem_slot = accum_bar + 8u;
+    auto acc_full = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
+    auto acc_empty = [&](int s) { return bars + 8u * (2 * C::kStages + 2 + s); };
+    const uint32_t tmem_slot = bars + 8u * (2 * C::kStages + 4);
     __shared__ int s_fail;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTileW;
-    const int m0 = blockIdx.y * BN;
     const int nkb = (K + kBK - 1) / kBK;
-    const int xk0 = group_rows > 0 ? (n0 / group_rows) * K : 0;   // block-diagonal: group g reads x columns [g K, (g + 1) K)
+    const int MT = (M + BN - 1) / BN, NT = (N + kTileW - 1) / kTileW;
+    const int total = MT * NT;
 
     if (threadIdx.x == 0) {
         s_fail = 0;
         for (int s = 0; s < C::kStages; ++s) { tc::mbar_init(full(s), 1); tc::mbar_init(empty(s), 1); }
-        tc::mbar_init(accum_bar, 1);
+        for (int s = 0; s < 2; ++s) { tc::mbar_init(acc_full(s), 1); tc::mbar_init(acc_empty(s), 4); }
         tc::mbar_fence_init();
         tc::prefetch_tmap(&tmap_w);
         tc::prefetch_tmap(&tmap_x);
@@ -74,43 +79,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
     if (warp == 0 && lane == 0) {
         // ---- producer ----
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % C::kStages;
-            if (kb >= C::kStages && !tc::mbar_wait(empty(s), ((kb / C::kStages) - 1) & 1)) { atomicExch(&s_fail, 1); break; }
-            const uint32_t a = base + s * C::kStageBytes, b = a + C::kABytes;
-            tc::mbar_expect_tx(full(s), C::kStageBytes);
-            tc::tma_load_2d(a, &tmap_w, kb * kBK, n0, full(s));
-            tc::tma_load_2d(b, &tmap_x, xk0 + kb * kBK, m0, full(s));
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+            const int n0 = (t / MT) * kTileW, m0 = (t % MT) * BN;
+            const int xk0 = group_rows > 0 ? (n0 / group_rows) * K : 0;   // block-diagonal: group g reads x columns [g K, (g + 1) K)
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % C::kStages;
+                if (it >= C::kStages && !tc::mbar_wait(empty(s), ((it / C::kStages) - 1) & 1)) { atomicExch(&s_fail, 1); ok = false; break; }
+                const uint32_t a = base + s * C::kStageBytes, b = a + C::kABytes;
+                tc::mbar_expect_tx(full(s), C::kStageBytes);
+                tc::tma_load_2d(a, &tmap_w, kb * kBK, n0, full(s));
+                tc::tma_load_2d(b, &tmap_x, xk0 + kb * kBK, m0, full(s));
+            }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
+        // ---- MMA issuer: tile i of this CTA accumulates into accumulator i & 1 ----
         constexpr uint32_t idesc = tc::umma_idesc_bf16(kTileW, BN < 16 ? 16 : BN);
+        int it = 0, ti = 0;
         bool ok = true;
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-            const int s = kb % C::kStages;
-            if (!tc::mbar_wait(full(s), (kb / C::kStages) & 1)) { atomicExch(&s_fail, 1); ok = false; break; }
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++ti) {
+            const int slot = ti & 1;
+            if (ti >= 2 && !tc::mbar_wait(acc_empty(slot), ((ti >> 1) - 1) & 1)) { atomicExch(&s_fail, 1); break; }
             tc::tc_fence_after();
-            const uint32_t a = base + s * C::kStageBytes, b = a + C::kABytes;
-            const uint64_t ad = tc::umma_desc_sw128(a), bd = tc::umma_desc_sw128(b);
+            const uint32_t d = tmem_base + (uint32_t)(slot * C::kAccCols);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % C::kStages;
+                if (!tc::mbar_wait(full(s), (it / C::kStages) & 1)) { atomicExch(&s_fail, 1); ok = false; break; }
+                tc::tc_fence_after();
+                const uint32_t a = base + s * C::kStageBytes, b = a + C::kABytes;
+                const uint64_t ad = tc::umma_desc_sw128(a), bd = tc::umma_desc_sw128(b);
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k)  // 32 bytes (two 16-byte units) per K = 16 step inside the swizzle atom
-                tc::umma_bf16(tmem_base, ad + 2u * k, bd + 2u * k, idesc, (kb | k) ? 1u : 0u);
-            tc::umma_commit(empty(s));
+                for (int k = 0; k < kBK / 16; ++k)  // 32 bytes (two 16-byte units) per K = 16 step inside the swizzle atom
+                    tc::umma_bf16(d, ad + 2u * k, bd + 2u * k, idesc, (kb | k) ? 1u : 0u);
+                tc::umma_commit(empty(s));
+            }
+            if (ok) tc::umma_commit(acc_full(slot));
         }
-        tc::umma_commit(accum_bar);
     } else if (warp >= 2) {
         // ---- epilogue: warp w may touch TMEM lanes 32*(w % 4) .. +31 ----
         const int q = warp & 3;
-        const bool ok = tc::mbar_wait(accum_bar, 0, 4000000000ll);
-        tc::tc_fence_after();
-        if (!ok) atomicExch(&s_fail, 1);
-        const bool go = __shfl_sync(0xffffffffu, (ok && s_fail == 0) ? 1 : 0, 0) != 0;  // warp-uniform
-        if (go) {
+        int ti = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++ti) {
+            const int slot = ti & 1;
+            const int n0 = (t / MT) * kTileW, m0 = (t % MT) * BN;
+            bool ok = tc::mbar_wait(acc_full(slot), (ti >> 1) & 1, 4000000000ll);
+            ok = __shfl_sync(0xffffffffu, (ok && s_fail == 0) ? 1 : 0, 0) != 0;  // warp-uniform
+            if (!ok) { atomicExch(&s_fail, 1); break; }
+            tc::tc_fence_after();
             const int n = n0 + q * 32 + lane;
+            const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * C::kAccCols);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 8) {
+                if (m0 + c >= M) break;
                 float v[8];
-                tc::tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                tc::tmem_ld8(ta + (uint32_t)c, v);
                 if (n < N) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -122,11 +145,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     }
                 }
             }
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(slot)) : "memory");
+            }
         }
     }
     tc::tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && s_fail) { status[0] = FB_TIMEOUT; status[1] = blockIdx.x; status[2] = blockIdx.y; status[3] = nkb; }
+    if (threadIdx.x == 0 && s_fail) { status[0] = FB_TIMEOUT; status[1] = blockIdx.x; status[2] = total; status[3] = nkb; }
     if (warp == 1) {
         tc::tc_fence_after();
         tc::tmem_dealloc(tmem_base, C::kTmemCols);
@@ -138,12 +166,17 @@ int launch_tc(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int ldo,
               int group_rows, int* status, cudaStream_t st) {
     auto k = gemm_tc_kernel<BN>;
     static bool attr_done = false;
+    static int sms = 0;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmem);
         if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return (int)cudaErrorInvalidValue;
         attr_done = true;
     }
-    dim3 grid((N + kTileW - 1) / kTileW, (M + BN - 1) / BN);
+    const long long tiles = (long long)((N + kTileW - 1) / kTileW) * ((M + BN - 1) / BN);
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     FB_LAUNCH((k), grid, kThreads, Cfg<BN>::kSmem, st, tw, tx, out, ldo, M, N, K, accumulate, group_rows, status);
     return FB_LAUNCH_CHECK();
 }
