@@ -240,8 +240,10 @@ def main():
     # rank's bounded poll runs out after a few milliseconds, the kernel returns, the status word names the peer,
     # and the engine-level check raises.  No kernel is made to spin, trap or fault.
     from ferrite_b200.parallel.status import CollectiveTimeout
-    ar2 = P2PAllReduce(dev, rank, world, max_elems=4 * 4096, max_spins=20000)
+    ar2 = P2PAllReduce(dev, rank, world, max_elems=4 * 4096, max_spins=400000)   # a wait budget of a few hundred ms
     buf = torch.ones(1, 4096, device=dev)
+    torch.cuda.synchronize()
+    dist.barrier()                    # the joint launch below must not pay for start-up skew out of that budget
     ar2(buf)
     torch.cuda.synchronize()
     ar2.arena.verify()
