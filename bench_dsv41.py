@@ -39,6 +39,12 @@ def main():
     ap.add_argument("--experts", type=int, default=384)
     ap.add_argument("--max-rows", type=int, default=64,
                     help="rows per prefill chunk (>= 16: routed experts run as block-scaled tcgen05 grouped GEMMs)")
+    ap.add_argument("--kernel-times", default=None, metavar="FILE",
+                    help="after the timed loop: 5 more steps under torch.profiler on rank 0 (every rank steps), per-kernel "
+                         "device times of one step written to FILE")
+    ap.add_argument("--engram", action="store_true",
+                    help="with --layers 0: keep the two engram layers and their hash tables (197 G e4m3 parameters, "
+                         "row-sharded: 49 GB per rank at TP=4)")
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
     ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     ap.add_argument("--emulate-tp", type=int, default=0,
@@ -78,7 +84,8 @@ def main():
         base = Dsv41Config()
         L = base.n_layers
         cfg = replace(base, n_mtp_layers=n_mtp, compress_ratios=tuple(base.compress_ratios[:L]) + (0,) * n_mtp,
-                      engram_layer_ids=(), engram_num_embeddings=(),
+                      engram_layer_ids=base.engram_layer_ids if args.engram else (),
+                      engram_num_embeddings=base.engram_num_embeddings if args.engram else (),
                       dspark_target_layer_ids=base.dspark_target_layer_ids if args.spec else (),
                       dspark_block_size=base.dspark_block_size if args.spec else 0,
                       n_routed_experts=args.experts).validate()
@@ -119,6 +126,35 @@ def main():
     if args.profiler_range:
         torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
+    if args.kernel_times:
+        from torch.profiler import ProfilerActivity, profile
+        import torch.distributed as dist
+        sync = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+        sync()
+        if rank == 0:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                sync()                       # the profiler's start-up is over before the peers' bounded waits begin
+                for _ in range(5):
+                    step()
+                torch.cuda.synchronize()
+            rows = {}
+            for ev in prof.events():
+                if ev.device_type is not None and "cuda" in str(ev.device_type).lower() and ev.name:
+                    r = rows.setdefault(ev.name, [0, 0.0])
+                    r[0] += 1
+                    r[1] += float(ev.time_range.elapsed_us())
+            tot = sum(v[1] for v in rows.values())
+            with open(args.kernel_times, "w") as f:
+                f.write(f"# per-kernel device time, 5 decode steps, rank 0; total {tot / 5:.1f} us of kernel time per step\n")
+                f.write("# us_per_step  launches_per_step  avg_us  kernel\n")
+                for name, (n, us) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+                    f.write(f"{us / 5:10.1f} {n / 5:8.1f} {us / max(n, 1):8.2f}  {name[:110]}\n")
+        else:
+            sync()
+            for _ in range(5):
+                step()
+            torch.cuda.synchronize()
+        sync()
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms], device=dev)
@@ -131,12 +167,14 @@ def main():
         print(json.dumps({"metric": name, "value": round(ms, 4), "unit": "ms",
                           "higher_is_better": False, "n_gpus": world, "steps": args.steps, "layers": L,
                           "ms_per_layer": round(ms / L, 4),
-                          "estimate_40_layers_ms": round(ms / L * 40, 3), "estimate_note": "extrapolated, not measured",
+                          "estimate_40_layers_ms": round(ms / L * 40, 3),
+                          "estimate_note": "all 40 layers ran: measured" if full else "extrapolated, not measured",
                           "tokens_per_step": round(toks / args.steps, 3), "dtype": "bf16 dense / e2m1 experts",
                           "data": "synthetic", "config": {"dim": cfg.dim, "heads": cfg.n_heads, "experts": cfg.n_routed_experts,
                                                           "topk": cfg.n_activated_experts, "context": args.prompt_len,
                                                           "parallelism": f"tp{world}", "spec": bool(args.spec), "pdl": bool(args.pdl),
-                                                          "emulated_tp": args.emulate_tp, "engram": "left out",
+                                                          "emulated_tp": args.emulate_tp,
+                                                          "engram": "2 layers, tables resident" if (args.engram and full) else "left out",
                                                           "prefill_rows_per_chunk": args.max_rows,
                                                           "prefill_ms": round(prefill_ms, 2),
                                                           "prefill_ms_per_token": round(prefill_ms / args.prompt_len, 4),

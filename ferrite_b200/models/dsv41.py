@@ -211,14 +211,17 @@ class Dsv41DeviceModel:
             L = self._pack_block(src, p, l)
             ei = cfg.engram_index(l)
             if ei >= 0:
-                tab = self._sh(src, p + "engram.embed.weight").float()
                 rows = cfg.engram_num_embeddings[ei]
                 per = (rows + self.world - 1) // self.world
-                q, sc = Q.fp8_act_quant(tab, cfg.fp8_block)
                 L["e_idx"] = ei
                 L["e_lo"], L["e_hi"] = self.rank * per, min(rows, (self.rank + 1) * per)
-                L["e_table"] = q.to(torch.float8_e4m3fn).view(torch.uint8).to(self.dev).contiguous()
-                L["e_scale"] = sc.to(self.dev).contiguous()
+                if hasattr(src, "engram_pack"):     # a source that hands the shard over in its device form
+                    L["e_table"], L["e_scale"] = src.engram_pack(p, L["e_lo"], L["e_hi"], self.dev)
+                else:
+                    tab = self._sh(src, p + "engram.embed.weight").float()
+                    q, sc = Q.fp8_act_quant(tab, cfg.fp8_block)
+                    L["e_table"] = q.to(torch.float8_e4m3fn).view(torch.uint8).to(self.dev).contiguous()
+                    L["e_scale"] = sc.to(self.dev).contiguous()
                 L["e_wkv"] = self._bf(src.get(p + "engram.wkv.weight"))
                 L["e_qk"] = self._f(src.get(p + "engram.q_weight").float() * src.get(p + "engram.k_weight").float())
             self.layers.append(L)

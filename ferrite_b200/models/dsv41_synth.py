@@ -54,6 +54,23 @@ class SyntheticDsv41Source:
         return w13, s13, w2, s2
 
 
+    def engram_pack(self, prefix: str, lo: int, hi: int, dev):
+        """Rows [lo, hi) of an engram table in its device form: e4m3 bytes [rows, head_dim] (no NaN codes) and one
+        ue8m0 scale byte per 32 values, generated in slabs so that a 25 GB shard never needs a second copy."""
+        hd = self.cfg.engram_head_dim
+        n = max(0, hi - lo)
+        g = self._gen(prefix + f"engram@{lo}")
+        tab = torch.empty(n, hd, dtype=torch.uint8, device=dev)
+        step = 1 << 22
+        for r0 in range(0, n, step):
+            r1 = min(n, r0 + step)
+            mag = torch.randint(0, 0x70, (r1 - r0, hd), dtype=torch.uint8, device=dev, generator=g)     # |v| <= 224
+            sgn = torch.randint(0, 2, (r1 - r0, hd), dtype=torch.uint8, device=dev, generator=g) << 7
+            tab[r0:r1] = mag | sgn
+        scale = torch.full((n, hd // self.cfg.fp8_block), 118, dtype=torch.uint8, device=dev)              # 2^-9
+        return tab, scale
+
+
 def tensor_specs_lazy(cfg: Dsv41Config):
     """Specs without the per-expert entries (the synthetic source packs experts in bulk)."""
-    return {k: v for k, v in tensor_specs(cfg).items() if ".experts." not in k}
+    return {k: v for k, v in tensor_specs(cfg).items() if ".experts." not in k and not k.endswith("engram.embed.weight")}
