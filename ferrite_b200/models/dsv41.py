@@ -373,7 +373,9 @@ class Dsv41DeviceModel:
     # ---- forward ---------------------------------------------------------------------------------
     def _reduce(self, t, n):
         if self.world > 1:
-            self.allreduce(t[:n])
+            step = max(1, getattr(self.allreduce, "max_elems", t[:n].numel()) // t.shape[1])
+            for r0 in range(0, n, step):   # the one-shot all-reduce takes a bounded payload per launch
+                self.allreduce(t[r0:min(n, r0 + step)])
 
     def _argmax(self, logits, out_ids, n):
         """Greedy ids of `n` rows of logits [n, Vl] (this rank's vocab slice when the head is sliced: the
