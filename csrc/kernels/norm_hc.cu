@@ -327,6 +327,17 @@ hc_pre_apply_kernel(const float* __restrict__ R, float* __restrict__ acc, const 
 //   CTA (nx, r)         : post and comb of row r (softmax + Sinkhorn), which only the next fold reads, side by side
 //                         with the x CTAs.
 // No CTA waits for another one, and the serial part (Sinkhorn) is off the path to x.
+// e4m3-per-32 round trip with a power-of-two scale (the DSV41 activation quantiser, csrc/kernels/dsv41.cu)
+__device__ __forceinline__ float wide_e4m3_rt(float v, float amax) {
+    const float t = fmaxf(amax, 1e-4f) * (1.f / 448.f);
+    const uint32_t b = __float_as_uint(t);
+    const int e = (int)((b >> 23) & 0xff) + ((b & 0x7fffffu) ? 1 : 0);
+    const float s = __uint_as_float((uint32_t)min(max(e, 0), 254) << 23);
+    const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(v / s, __NV_SATFINITE, __NV_E4M3);
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(q, __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&h)) * s;
+}
+
 constexpr int kWideCols = 512;
 constexpr int kGramPairs = 10;
 
@@ -345,7 +356,11 @@ hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, 
                    const int* __restrict__ part_n, int part_ld, const float* __restrict__ scale,
                    const float* __restrict__ base, const float* __restrict__ ln_w, float* __restrict__ xn_out,
                    float* __restrict__ post_out, float* __restrict__ comb_out, int H, int mix, float rms_eps,
-                   float hc_eps, int iters, SplitBuf osp) {
+                   float hc_eps, int iters, SplitBuf osp, const float* __restrict__ pre_in, float* __restrict__ pre_out,
+                   float* __restrict__ xq_out, SplitBuf qsp) {
+    // pre_in / pre_out: the offset form of the hyper-connections (the contraction uses the PREVIOUS site's `pre`, given
+    // in pre_in; this site's `pre` is only stored for the next one).  xq_out / qsp: also the e4m3-per-32 round trip of
+    // the normed row (a warp's 32 columns are one quantisation block).
     PDL_PROLOGUE();
     __shared__ float s_sum[kMaxMix + 1 + kGramPairs];
     const int r = blockIdx.y, nx = gridDim.x - 1;
@@ -364,6 +379,7 @@ hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, 
         if (warp != 0) return;
         const float rr = rsqrtf(s_sum[kMaxMix] / (float)(4 * H) + rms_eps);
         if (lane < 4) post_out[(size_t)r * 4 + lane] = 2.f * sigmoidf_(s_sum[4 + lane] * rr * scale[1] + base[4 + lane]);
+        if (pre_out && lane < 4) pre_out[(size_t)r * 4 + lane] = sigmoidf_(s_sum[lane] * rr * scale[0] + base[lane]) + hc_eps;
         float c = 0.f;
         const bool on = lane < 16;
         if (on) c = s_sum[8 + lane] * rr * scale[2] + base[8 + lane];
@@ -408,7 +424,7 @@ hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, 
     const float rr = rsqrtf(s_sum[kMaxMix] / (float)(4 * H) + rms_eps);
     float pw[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(s_sum[i] * rr * scale[0] + base[i]) + hc_eps;
+    for (int i = 0; i < 4; ++i) pw[i] = pre_in ? pre_in[(size_t)r * 4 + i] : sigmoidf_(s_sum[i] * rr * scale[0] + base[i]) + hc_eps;
     float xss = 0.f;
     int p = 0;
 #pragma unroll
@@ -416,10 +432,17 @@ hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, 
 #pragma unroll
         for (int k = i; k < 4; ++k, ++p) xss += (i == k ? 1.f : 2.f) * pw[i] * pw[k] * s_sum[kMaxMix + 1 + p];
     const float inv = rsqrtf(fmaxf(xss, 0.f) / (float)H + rms_eps);
+    const float o = act ? (pw[0] * rv[0] + pw[1] * rv[1] + pw[2] * rv[2] + pw[3] * rv[3]) * inv * lw : 0.f;
     if (act) {
-        const float o = (pw[0] * rv[0] + pw[1] * rv[1] + pw[2] * rv[2] + pw[3] * rv[3]) * inv * lw;
         xn_out[(size_t)r * H + j] = o;
         split_store(osp, r, j, o);
+    }
+    if (xq_out || qsp.base) {
+        const float q = wide_e4m3_rt(o, warp_max(fabsf(o)));      // whole warps: H is a multiple of 32
+        if (act) {
+            if (xq_out) xq_out[(size_t)r * H + j] = q;
+            split_store(qsp, r, j, q);
+        }
     }
 }
 
@@ -541,7 +564,28 @@ FB_API int fb_hc_pre_wide(const float* R, const float* part, const float* gram, 
     if (n < 1 || n > 8 || mix > kMaxMix || mix < 24 || !part || !gram || !part_n) return (int)cudaErrorInvalidValue;
     const unsigned nx = (unsigned)((H + kWideCols - 1) / kWideCols);
     FB_LAUNCH((hc_pre_wide_kernel), dim3(nx + 1, (unsigned)n), kWideCols, 0, st, R, part, gram, part_n, (int)part_ld, scale,
-              base, ln_w, xn_out, post_out, comb_out, (int)H, (int)mix, rms_eps, hc_eps, (int)iters, osp);
+              base, ln_w, xn_out, post_out, comb_out, (int)H, (int)mix, rms_eps, hc_eps, (int)iters, osp,
+              (const float*)nullptr, (float*)nullptr, (float*)nullptr, SplitBuf{nullptr, 0, 0, 0});
+    return FB_LAUNCH_CHECK();
+}
+
+// The same front for the offset form (DSV41): x = rmsnorm(sum_i pre_in[r][i] R_i) * ln_w with the PREVIOUS site's
+// coefficients, this site's (pre, post, comb) stored for later; optionally the e4m3-per-32 round trip of x as well
+// (xq_out f32 and / or its split planes).  H % 32 == 0.
+FB_API int fb_hc_pre_wide_offset(const float* R, const float* part, const float* gram, const int* part_n, int64_t part_ld,
+                                 const float* scale, const float* base, const float* ln_w, const float* pre_in,
+                                 float* pre_out, float* xn_out, float* post_out, float* comb_out, int64_t n, int64_t H,
+                                 int64_t mix, float rms_eps, float hc_eps, int64_t iters, void* s_base, int64_t s_ld,
+                                 int64_t s_plane, int64_t s_mask, float* xq_out, void* q_base, int64_t q_ld, int64_t q_plane,
+                                 int64_t q_mask, cudaStream_t st) {
+    SplitBuf osp{(uint16_t*)s_base, (int)s_ld, (int)s_plane, (int)s_mask};
+    SplitBuf qsp{(uint16_t*)q_base, (int)q_ld, (int)q_plane, (int)q_mask};
+    if (n < 1 || n > 8 || mix > kMaxMix || mix < 24 || !part || !gram || !part_n || !pre_in || !pre_out || (H % 32))
+        return (int)cudaErrorInvalidValue;
+    const unsigned nx = (unsigned)((H + kWideCols - 1) / kWideCols);
+    FB_LAUNCH((hc_pre_wide_kernel), dim3(nx + 1, (unsigned)n), kWideCols, 0, st, R, part, gram, part_n, (int)part_ld, scale,
+              base, ln_w, xn_out, post_out, comb_out, (int)H, (int)mix, rms_eps, hc_eps, (int)iters, osp, pre_in, pre_out,
+              xq_out, qsp);
     return FB_LAUNCH_CHECK();
 }
 

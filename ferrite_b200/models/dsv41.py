@@ -95,6 +95,8 @@ class Dsv41DeviceModel:
             self.fused = FusedGemvAllReduce(self.dev, 0, 1, arena=self.arena)
         self._fold_next = None
         self._folded = False
+        self._wide_ready = False   # the closing GEMV left mix-dot AND Gram partials: the column-parallel front can run
+        self._part_stale = False   # the partial tile counts were consumed by a kernel that does not clear them
         self.debug_hook = None
         self.win_cap = cfg.window_size + max_rows
         # compressor ring: positions that one forward may look back over (ratio + rows of the forward)
@@ -424,18 +426,25 @@ class Dsv41DeviceModel:
             self._reduce(ws["y"], n)
             return
         f = None
+        want_gram = False
         if fold is not None:
             rin = ws["R"]
             rout = ws["R1"] if rin is ws["R0"] else ws["R0"]
             f = (rin, rout, ws["post"], ws["comb"], fold[0], ws["hc_acc"], (2 + self.cfg.hc_mult) * self.cfg.hc_mult)
             ws["R"] = rout
             self._folded = True
-        self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f)
+            self._part_stale = False   # this launch rewrites the tile counts
+            if fold[0] is not None and self.hc_wide and N == self.cfg.dim and N // 16 <= 512 and N % 32 == 0:
+                self._wide_ready = want_gram = True
+        self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f,
+                   gram=want_gram)
 
     # hc_pre can also emit the e4m3 round trip of its output (two launches fewer per layer).  Off by default: measured
     # 1 % SLOWER at TP1 and on the TP8 shard (2.175 vs 2.161 ms, 5.94 vs 5.88 ms): hc_pre is a one-CTA latency chain
     # on the critical path, the separate quantiser spreads over many CTAs
     fuse_quant = property(lambda self: switches().d4_fuse_quant)
+    # decode rows: the front as a column-parallel kernel fed by the closing GEMV's Gram partials (it also quantises)
+    hc_wide = property(lambda self: switches().hc_pre_wide and self.cfg.hc_mult == 4)
 
     def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
         quant = quant and self.fuse_quant
@@ -444,6 +453,22 @@ class Dsv41DeviceModel:
         cfg, ws = self.cfg, self.ws
         x = ws["x"]
         pin, pout = ws["pre_cur"], ws["pre_nxt"]
+        if self._wide_ready:
+            self._wide_ready = False
+            assert coeffs and n <= 8
+            part, gram, part_n, ld = self.fused.wide_partials()
+            xq = ws["xq"]
+            self.K.call("fb_hc_pre_wide_offset", ws["R"], part, gram, part_n, ld, L[f"hc_{site}_scale"],
+                        L[f"hc_{site}_base"], ln, pin, pout, x.f, ws["post"], ws["comb"], n, cfg.dim,
+                        (2 + cfg.hc_mult) * cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps), cfg.hc_sinkhorn_iters,
+                        *x.sp(1), xq.f, *xq.sp(3))
+            self._xq_ready = True
+            self._part_stale = True
+            ws["pre_cur"], ws["pre_nxt"] = pout, pin
+            return
+        if self._part_stale:   # no launch rewrote the tile counts since the column-parallel front read them
+            self._part_stale = False
+            self.fused.part_n.zero_()
         self.K.call("fb_d4_hc_pre", ws["R"], ws["hc_acc"] if coeffs else None,
                     L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
                     ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),

@@ -181,3 +181,49 @@ def test_sparse_attention_with_sink_matches_rows_statement(K):
         kv = torch.stack(keys)                                        # [keys, hd]
         want = G.sparse_attn_rows(q[r].view(Hl, hd), kv, sink, scale)  # [Hl, hd]
         close(f"sparse attention row {r}", out[r].view(Hl, hd), want, 3e-3)
+
+
+def test_hc_front_column_parallel_offset_form(K):
+    """fb_hc_pre_wide_offset (partial tiles of the mix dots, the sum of squares and the Gram of R in; x, its e4m3 round
+    trip and this site's coefficients out) against the fp32 statement of the offset hyper-connection front."""
+    from ferrite_b200.ops import reference as R
+    n, H, m, tiles, ld = 3, 1536, 4, 5, 8
+    Rm = torch.randn(n, m, H, generator=gen(60)) * torch.tensor([0.5, 1.0, 3.0]).view(n, 1, 1)
+    fn = torch.randn(24, m * H, generator=gen(61)) * 0.05
+    scale = torch.tensor([0.7, 1.3, 0.9])
+    base = torch.randn(24, generator=gen(62)) * 0.3
+    ln_w = 1 + 0.1 * torch.randn(H, generator=gen(63))
+    pre_in = torch.rand(n, m, generator=gen(64)) + 0.1
+    rms_eps, hc_eps, iters = 1e-6, 1e-6, 20
+    flat = Rm.reshape(n, -1)
+    # per-tile partials: column tiles of unequal width, each tile's share of every sum
+    edges = [0, 100, 612, 613, 1400, H]
+    part = torch.zeros(8, 25, ld)
+    gram = torch.zeros(8, 10, ld)
+    for t in range(tiles):
+        sl = Rm[:, :, edges[t]:edges[t + 1]]                                   # [n, m, w]
+        fl = fn.view(24, m, H)[:, :, edges[t]:edges[t + 1]]
+        part[:n, :24, t] = torch.einsum("nmw,qmw->nq", sl, fl)
+        part[:n, 24, t] = sl.square().sum((1, 2))
+        p = 0
+        for i in range(m):
+            for k in range(i, m):
+                gram[:n, p, t] = (sl[:, i] * sl[:, k]).sum(-1)
+                p += 1
+    part[:, :, tiles:] = 7.0                                                   # beyond the tile count: never read
+    part_n = torch.full((8,), tiles, dtype=torch.int32)
+    x_out, xq_out = torch.zeros(n, H, device="cuda"), torch.zeros(n, H, device="cuda")
+    pre_out, post, comb = torch.zeros(n, m, device="cuda"), torch.zeros(n, m, device="cuda"), torch.zeros(n, m * m, device="cuda")
+    K.call("fb_hc_pre_wide_offset", Rm.cuda(), part.cuda(), gram.cuda(), part_n.cuda(), ld, scale.cuda(), base.cuda(),
+           ln_w.cuda(), pre_in.cuda(), pre_out, x_out, post, comb, n, H, 24, rms_eps, hc_eps, iters, None, 0, 0, 0,
+           xq_out, None, 0, 0, 0)
+    r = torch.rsqrt(flat.square().mean(-1, keepdim=True) + rms_eps)
+    wpre, wpost, wcomb = R.hc_coeffs((flat @ fn.t()) * r, scale, base, m, hc_eps, iters)
+    close("pre", pre_out, wpre, 1e-5)
+    close("post", post, wpost, 1e-5)
+    close("comb", comb, wcomb.reshape(n, -1), 1e-5)
+    want = G.rmsnorm((pre_in.unsqueeze(-1) * Rm).sum(1), ln_w, rms_eps)
+    close("x", x_out, want, 2e-5 * want.abs().max().item())
+    wq = Q.fp8_act_roundtrip(want, 32)
+    diff = (xq_out.cpu() - wq).abs()
+    assert (diff > 1e-6).float().mean().item() < 0.005 and (diff <= 0.126 * want.abs() + 1e-6).all()
