@@ -665,33 +665,55 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
         const int cnt = min(kAttnStage, k_hi - base);
         const int cnt8 = (cnt + kAttnTile - 1) / kAttnTile * kAttnTile;
         __syncthreads();
-        for (int t = warp; t < cnt8; t += 8) {
-            const int i = base + t;
-            const __nv_bfloat16* src = nullptr;
-            const float* srcf = nullptr;
-            if (t >= cnt) {
-                // padding of the last tile
-            } else if (i < nw) {
-                const int p = wpos - nw + 1 + i;
-                src = ring + ((size_t)m.slot * cap + (p % cap)) * HD;
-            } else if (i < nw + ktop) {
-                const int c = idx[(size_t)r * ldi + (i - nw)];
-                if (c >= 0 && c < ccap) src = comp + ((size_t)m.slot * ccap + c) * HD;
-            } else {
-                srcf = extra + (size_t)(i - nw - ktop) * HD;
+        // Lane u < KPW resolves the source of key (warp + 8u) of this pass (the index loads of a warp's keys go out
+        // together); the warp then issues the 16-byte loads of ALL its keys before the first store, so a pass costs
+        // one index latency plus one key latency however many keys a warp stages.
+        constexpr int KPW = kAttnStage / 8;            // keys per warp and pass
+        constexpr int VW = (HD / 8 + 31) / 32;         // 16-byte words per lane and key
+        const __nv_bfloat16* my_src = nullptr;
+        const float* my_srcf = nullptr;
+        {
+            const int t = warp + 8 * lane, i = base + t;
+            if (lane < KPW && t < cnt) {
+                if (i < nw) {
+                    const int p = wpos - nw + 1 + i;
+                    my_src = ring + ((size_t)m.slot * cap + (p % cap)) * HD;
+                } else if (i < nw + ktop) {
+                    const int c = idx[(size_t)r * ldi + (i - nw)];
+                    if (c >= 0 && c < ccap) my_src = comp + ((size_t)m.slot * ccap + c) * HD;
+                } else {
+                    my_srcf = extra + (size_t)(i - nw - ktop) * HD;
+                }
             }
+        }
+        uint4 kv[KPW][VW];
+        unsigned long long sp[KPW];
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) {
+            sp[u] = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_src, u);
+#pragma unroll
+            for (int w = 0; w < VW; ++w) {
+                kv[u][w] = make_uint4(0u, 0u, 0u, 0u);   // a masked key must not feed NaN into 0 * k
+                if (sp[u] && lane + 32 * w < HD / 8) kv[u][w] = __ldg(reinterpret_cast<const uint4*>(sp[u]) + lane + 32 * w);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KPW; ++u) {
+            const int t = warp + 8 * u;
+            const unsigned long long sf = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)my_srcf, u);
+            if (t >= cnt8) continue;
             uint32_t* dst = ktile + (size_t)t * (HD / 2);
-            if (lane == 0) kvalid[t] = (src || srcf) ? 1 : 0;
-            if (src) {
-                const uint4* s16 = reinterpret_cast<const uint4*>(src);
-                for (int v = lane; v < HD / 8; v += 32) reinterpret_cast<uint4*>(dst)[v] = __ldg(s16 + v);
-            } else if (srcf) {
+            if (lane == 0) kvalid[t] = (sp[u] || sf) ? 1 : 0;
+            if (sf) {   // a draft block's own row, kept in f32
+                const float* srcf = reinterpret_cast<const float*>(sf);
                 for (int e = lane; e < HD / 2; e += 32) {
                     const __nv_bfloat162 v = __floats2bfloat162_rn(srcf[2 * e], srcf[2 * e + 1]);
                     dst[e] = *reinterpret_cast<const uint32_t*>(&v);
                 }
             } else {
-                for (int e = lane; e < HD / 2; e += 32) dst[e] = 0u;  // a masked key must not feed NaN into 0 * k
+#pragma unroll
+                for (int w = 0; w < VW; ++w)
+                    if (lane + 32 * w < HD / 8) reinterpret_cast<uint4*>(dst)[lane + 32 * w] = kv[u][w];
             }
         }
         __syncthreads();
@@ -760,20 +782,34 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
     __syncthreads();
     if (!s_last || !hv) return;
     __threadfence();
-    float M = -1e30f;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(ml_part + (p0 + s) * 2));
-    float dsum = __expf(sink[h] - M);
+    // lane s holds split s's (max, denominator): one round trip for all of them; the partial outputs then come in
+    // groups of four splits whose loads are all issued before the first is used (a split per iteration would pay one
+    // L2 latency per split)
+    float2 mlv = make_float2(-1e30f, 0.f);
+    if (lane < nsplit) mlv = __ldcg(reinterpret_cast<const float2*>(ml_part + (p0 + lane) * 2));
+    const float M = warp_max(mlv.x);
+    const float wl = lane < nsplit ? __expf(mlv.x - M) : 0.f;
+    const float dsum = __expf(sink[h] - M) + warp_sum(mlv.y * wl);
     float a[NJ], b[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; ++j) a[j] = b[j] = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float w = __expf(__ldcg(ml_part + (p0 + s) * 2) - M);
-        dsum = fmaf(__ldcg(ml_part + (p0 + s) * 2 + 1), w, dsum);
+    for (int s0 = 0; s0 < nsplit; s0 += 4) {
+        float2 o[4][NJ];
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            const float2 o = __ldcg(reinterpret_cast<const float2*>(o_part + (p0 + s) * HD + 2 * lane + 64 * j));
-            a[j] = fmaf(o.x, w, a[j]);
-            b[j] = fmaf(o.y, w, b[j]);
+        for (int u = 0; u < 4; ++u) {
+            const int s = min(s0 + u, nsplit - 1);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j)
+                o[u][j] = __ldcg(reinterpret_cast<const float2*>(o_part + (p0 + s) * HD + 2 * lane + 64 * j));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float w = s0 + u < nsplit ? __shfl_sync(0xffffffffu, wl, (s0 + u) & 31) : 0.f;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                a[j] = fmaf(o[u][j].x, w, a[j]);
+                b[j] = fmaf(o[u][j].y, w, b[j]);
+            }
         }
     }
     const float inv = 1.f / dsum;
@@ -1372,7 +1408,7 @@ FB_API int fb_d4_sparse_attn(const float* q, int64_t ldq, const void* ring, int6
     const SplitBuf osp = mk_split(s_base, s_ld, s_plane, s_mask);
     if (!idx) ktop = 0;
     if (!extra) n_extra = 0;
-    if (nsplit < 1 || !o_part || !ml_part) return (int)cudaErrorInvalidValue;
+    if (nsplit < 1 || !o_part || !ml_part || (ticket && nsplit > 32)) return (int)cudaErrorInvalidValue;   // the merging warp keeps one split per lane
     int rc;
 #define D4_ATTN(NJ) launch_attn<NJ>(q, (int)ldq, ring, (int)cap, (int)window, comp, (int)ccap, idx, (int)ldi, (int)ktop, extra, \
                                     (int)n_extra, sink, freqs, (int)rd, meta, (int)pos_off, (int)win_mode, scale, (int)heads, \

@@ -273,8 +273,11 @@ class Dsv41DeviceModel:
         # split-K attention: keys of a row are spread over up to 16 CTAs per head tile
         lmax = cfg.window_size + cfg.index_topk + max(cfg.dspark_block_size, 1)
         self.at_split = max(1, min(16, (lmax + 31) // 32))
-        ws["at_o"] = self._z(M * self.Hl * self.at_split * hd)
-        ws["at_ml"] = self._z(M * self.Hl * self.at_split * 2)
+        # a few decode rows on few heads (a tensor-parallel shard): 32 splits, or the grid is a fraction of the SMs
+        self.at_split_few = 32
+        at_parts = max(M * self.Hl * self.at_split, 32 * self.at_split_few)
+        ws["at_o"] = self._z(at_parts * hd)
+        ws["at_ml"] = self._z(at_parts * 2)
         ws["at_ticket"] = self._z(M * ((self.Hl + 7) // 8), dtype=torch.int32)   # split-merge tickets (left at zero)
         ws["y"] = self._z(M, d)
         ws["ckv"] = self._z(M, 2 * hd)
@@ -547,7 +550,8 @@ class Dsv41DeviceModel:
         else:
             self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
                         cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
-                        self.Hl, hd, o.f, self.Hl * hd, n, self.at_split, ws["at_o"], ws["at_ml"], *o.sp(1), ws["at_ticket"])
+                        self.Hl, hd, o.f, self.Hl * hd, n, self.at_split_few if n * self.Hl <= 32 else self.at_split,
+                        ws["at_o"], ws["at_ml"], *o.sp(1), ws["at_ticket"])
         low = ws["low"]
         R_ = cfg.o_lora_rank
         self.gemv(L["wo_a"], o, low, n, self.Gl * R_, cfg.heads_per_group * hd, ldx=self.Hl * hd, group_rows=R_)

@@ -155,8 +155,10 @@ def test_gemv_f32_weights(K):
     close("gemv f32w", out, x[:, :Kd].double() @ W.double().t(), 1e-3)
 
 
-def test_sparse_attention_with_sink_matches_rows_statement(K):
-    """Window ring + compressed rows + sink against models/dsv41_ref.py::sparse_attn_rows on the gathered keys."""
+@pytest.mark.parametrize("nsplit,own_merge", [(4, False), (4, True), (7, True), (32, True)])
+def test_sparse_attention_with_sink_matches_rows_statement(K, nsplit, own_merge):
+    """Window ring + compressed rows + sink against models/dsv41_ref.py::sparse_attn_rows on the gathered keys; the
+    split partials merged by a second kernel or by the last CTA of each (row, head tile)."""
     n, Hl, hd, W, cap, ccap, ktop = 2, 4, 128, 16, 24, 64, 8
     pos = [40, 9]                                       # row 1: fewer positions than the window holds
     ring = (torch.randn(1, cap, hd, generator=gen(40)) * 0.5).to(torch.bfloat16)
@@ -168,13 +170,15 @@ def test_sparse_attention_with_sink_matches_rows_statement(K):
     freqs = torch.zeros(32)                             # no output rotation: rd = 64 dims with zero angles
     meta = meta_for(pos)
     out = torch.zeros(n, Hl * hd, device="cuda")
-    nsplit = 4
+    ticket = torch.zeros(n, dtype=torch.int32, device="cuda") if own_merge else None
     o_part = torch.zeros(n * Hl * nsplit * hd, device="cuda")
     ml_part = torch.zeros(n * Hl * nsplit * 2, device="cuda")
     scale = hd ** -0.5
     K.call("fb_d4_sparse_attn", q.cuda(), Hl * hd, ring.cuda(), cap, W, comp.cuda(), ccap, idx.cuda(), ktop, ktop, None, 0,
            sink.cuda(), freqs.cuda(), 64, meta, 0, 0, float(scale), Hl, hd, out, Hl * hd, n, nsplit, o_part, ml_part,
-           None, 0, 0, 0, None)
+           None, 0, 0, 0, ticket)
+    if own_merge:
+        assert int(ticket.abs().sum()) == 0        # left at zero for the next launch
     for r in range(n):
         win = [p % cap for p in G.window_positions(pos[r], W)]
         keys = [ring[0, p].float() for p in win] + [comp[0, int(j)].float() for j in idx[r] if j >= 0]
