@@ -16,6 +16,8 @@
 // ref_inference/model.py and ref_inference/kernel.py.
 #include <cuda_fp4.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "mma_gemv.cuh"
 
@@ -615,7 +617,12 @@ cand_mask_kernel(const int* __restrict__ blk, int ldb, int kb, int bs, uint8_t* 
 // joins the denominator at the end, a row without keys yields zeros.
 constexpr int kAttnTile = 8;
 constexpr int kAttnStage = 48;   // keys staged per pass (48 KB of shared memory at head_dim 512)
-template <int NJ>  // head_dim / 64
+// CL: launched as clusters of kAttnCluster CTAs along the split axis.  The CTAs of a cluster exchange their partials
+// through distributed shared memory (CTA c merges head c of the tile: the merge of a cluster runs on eight SMs side by
+// side) and global memory only sees one partial per cluster; one CTA merging all splits of eight heads is bound by one
+// SM's L2 bandwidth (32 splits x 8 heads x 2 KB).
+constexpr int kAttnCluster = 8;
+template <int NJ, bool CL>  // NJ = head_dim / 64
 __global__ void __launch_bounds__(256)
 sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ ring, int cap, int window,
                    const __nv_bfloat16* __restrict__ comp, int ccap, const int* __restrict__ idx, int ldi, int ktop,
@@ -758,8 +765,57 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
         }
     }
     // un-normalised partial of this split: o (already rotated keys), running max and denominator
+    if constexpr (CL) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        constexpr int PS = HD + 8;                            // floats per staged partial: o, max, denominator
+        float* ps = reinterpret_cast<float*>(ktile);          // [8 heads][PS]: this CTA's partials
+        float* ps2 = ps + 8 * PS;                             // [8 CTAs][PS]: the cluster's partials of MY head
+        __syncthreads();                                      // the key tile is no longer read
+#pragma unroll
+        for (int j = 0; j < NJ; ++j)
+            *reinterpret_cast<float2*>(ps + warp * PS + 2 * lane + 64 * j) = make_float2(ov[j][0], ov[j][1]);
+        if (lane == 0) { ps[warp * PS + HD] = mx; ps[warp * PS + HD + 1] = den; }
+        cluster.sync();
+        const int cr = (int)cluster.block_rank();             // head of the tile that this CTA merges
+        {
+            const float* rp = cluster.map_shared_rank(ps, warp) + cr * PS;   // CTA `warp`'s partial of head cr
+            float2 po[NJ];
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) po[j] = *reinterpret_cast<const float2*>(rp + 2 * lane + 64 * j);
+            const float pm = rp[HD], pd = rp[HD + 1];
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) *reinterpret_cast<float2*>(ps2 + warp * PS + 2 * lane + 64 * j) = po[j];
+            if (lane == 0) { ps2[warp * PS + HD] = pm; ps2[warp * PS + HD + 1] = pd; }
+        }
+        __syncthreads();
+        const int hc = blockIdx.x * 8 + cr;
+        const int nparts = nsplit / kAttnCluster;
+        if (hc < heads) {
+            float Mc = -1e30f;
+#pragma unroll
+            for (int w = 0; w < kAttnCluster; ++w) Mc = fmaxf(Mc, ps2[w * PS + HD]);
+            float wgt[kAttnCluster], dc = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAttnCluster; ++w) { wgt[w] = __expf(ps2[w * PS + HD] - Mc); dc = fmaf(ps2[w * PS + HD + 1], wgt[w], dc); }
+            const size_t pi = ((size_t)r * heads + hc) * nparts + sp / kAttnCluster;
+            for (int e2 = threadIdx.x; e2 < HD / 2; e2 += 256) {
+                float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < kAttnCluster; ++w) {
+                    const float2 v = *reinterpret_cast<const float2*>(ps2 + w * PS + 2 * e2);
+                    acc.x = fmaf(v.x, wgt[w], acc.x);
+                    acc.y = fmaf(v.y, wgt[w], acc.y);
+                }
+                *reinterpret_cast<float2*>(o_part + pi * HD + 2 * e2) = acc;
+            }
+            if (threadIdx.x == 0) { ml_part[pi * 2] = Mc; ml_part[pi * 2 + 1] = dc; }
+        }
+        cluster.sync();                                       // nobody leaves while its partials may still be read
+        nsplit = nparts;                                      // what the final merge below sees
+    }
     const size_t p0 = ((size_t)r * heads + h) * nsplit;
-    if (hv) {
+    if (!CL && hv) {
         const size_t pi = p0 + sp;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -776,7 +832,7 @@ sparse_attn_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __
     if (threadIdx.x == 0) {
         unsigned* tk = ticket + (size_t)r * gridDim.x + blockIdx.x;
         const unsigned t = atomicAdd(tk, 1u);
-        s_last = (t == (unsigned)nsplit - 1u) ? 1 : 0;
+        s_last = (t == gridDim.z - 1u) ? 1 : 0;
         if (s_last) *tk = 0u;   // every CTA of the group has taken its ticket
     }
     __syncthreads();
@@ -1384,13 +1440,37 @@ static int launch_attn(const float* q, int ldq, const void* ring, int cap, int w
                        int nsplit, float* o_part, float* ml_part, int n, unsigned* ticket, float* out, int ldo, SplitBuf osp,
                        cudaStream_t st) {
     constexpr int kSm = kAttnStage * NJ * 64 * 2;
+    static_assert(2 * 8 * (NJ * 64 + 8) * 4 <= kSm, "the cluster merge stages its partials in the key tile");
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(sparse_attn_kernel<NJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSm);
+        cudaError_t e = cudaFuncSetAttribute(sparse_attn_kernel<NJ, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSm);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(sparse_attn_kernel<NJ, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSm);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    FB_LAUNCH((sparse_attn_kernel<NJ>), dim3((unsigned)((heads + 7) / 8), (unsigned)n, (unsigned)nsplit), 256, kSm, st, q, ldq,
+    const dim3 grid((unsigned)((heads + 7) / 8), (unsigned)n, (unsigned)nsplit);
+    if (ticket && nsplit % kAttnCluster == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = kSm;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = kAttnCluster;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_fb_pdl ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, sparse_attn_kernel<NJ, true>, q, ldq, (const __nv_bfloat16*)ring, cap, window,
+                                       (const __nv_bfloat16*)comp, ccap, idx, ldi, ktop, extra, n_extra, sink, freqs, rd,
+                                       (const RowMeta*)meta, pos_off, win_mode, scale, heads, nsplit, o_part, ml_part, ticket,
+                                       out, ldo, osp);
+    }
+    FB_LAUNCH((sparse_attn_kernel<NJ, false>), grid, 256, kSm, st, q, ldq,
               (const __nv_bfloat16*)ring, cap, window, (const __nv_bfloat16*)comp, ccap, idx, ldi, ktop, extra, n_extra, sink,
               freqs, rd, (const RowMeta*)meta, pos_off, win_mode, scale, heads, nsplit, o_part, ml_part, ticket, out, ldo, osp);
     return FB_LAUNCH_CHECK();

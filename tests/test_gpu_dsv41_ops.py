@@ -155,7 +155,7 @@ def test_gemv_f32_weights(K):
     close("gemv f32w", out, x[:, :Kd].double() @ W.double().t(), 1e-3)
 
 
-@pytest.mark.parametrize("nsplit,own_merge", [(4, False), (4, True), (7, True), (32, True)])
+@pytest.mark.parametrize("nsplit,own_merge", [(4, False), (4, True), (7, True), (8, True), (16, True), (32, True)])
 def test_sparse_attention_with_sink_matches_rows_statement(K, nsplit, own_merge):
     """Window ring + compressed rows + sink against models/dsv41_ref.py::sparse_attn_rows on the gathered keys; the
     split partials merged by a second kernel or by the last CTA of each (row, head tile)."""
