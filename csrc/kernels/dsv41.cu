@@ -236,12 +236,10 @@ rope_heads_kernel(float* __restrict__ x, int ld, int heads, int hd, int rd, cons
 }
 
 // ---- KV row: rmsnorm -> rope -> e4m3/32 round trip -> ring (bf16) and/or plain rows --------------
-__global__ void __launch_bounds__(128)
-kv_append_kernel(const float* __restrict__ kv, int ld, const float* __restrict__ norm_w, const float* __restrict__ freqs,
-                 const RowMeta* __restrict__ meta, __nv_bfloat16* __restrict__ ring, int cap, float* __restrict__ rows_out,
-                 int hd, int rd, float eps, int pos_off) {
-    PDL_PROLOGUE();
-    extern __shared__ float sh[];
+__device__ __forceinline__ void kv_append_body(float* sh, const float* __restrict__ kv, int ld, const float* __restrict__ norm_w,
+                                               const float* __restrict__ freqs, const RowMeta* __restrict__ meta,
+                                               __nv_bfloat16* __restrict__ ring, int cap, float* __restrict__ rows_out,
+                                               int hd, int rd, float eps, int pos_off) {
     float* red = sh;
     float* v = sh + 32;
     const int r = blockIdx.x;
@@ -274,6 +272,15 @@ kv_append_kernel(const float* __restrict__ kv, int ld, const float* __restrict__
         if (ring) ring[((size_t)m.slot * cap + (p % cap)) * hd + b * 32 + lane] = __float2bfloat16_rn(q);
         if (rows_out) rows_out[(size_t)r * hd + b * 32 + lane] = q;
     }
+}
+
+__global__ void __launch_bounds__(128)
+kv_append_kernel(const float* __restrict__ kv, int ld, const float* __restrict__ norm_w, const float* __restrict__ freqs,
+                 const RowMeta* __restrict__ meta, __nv_bfloat16* __restrict__ ring, int cap, float* __restrict__ rows_out,
+                 int hd, int rd, float eps, int pos_off) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    kv_append_body(sh, kv, ld, norm_w, freqs, meta, ring, cap, rows_out, hd, rd, eps, pos_off);
 }
 
 // ---- compressor ------------------------------------------------------------------------------------
@@ -1125,11 +1132,8 @@ swiglu_clamp_kernel(const float* __restrict__ gu, int ld, float* __restrict__ ou
 
 // RMSNorm of a row slice followed by the e4m3-per-32 round trip (the q-lora vector on its way to wq_b):
 // out = rt(x * rsqrt(mean x^2 + eps) * w).  One CTA per row, a warp per 32-value block.
-__global__ void __launch_bounds__(256)
-rmsnorm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ out, int ldo,
-                     int K, float eps, SplitBuf osp) {
-    PDL_PROLOGUE();
-    __shared__ float red[32];
+__device__ __forceinline__ void rmsnorm_quant_body(float* red, const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                                   float* __restrict__ out, int ldo, int K, float eps, SplitBuf osp) {
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* row = x + (size_t)r * ldx;
     float ss = 0.f;
@@ -1144,6 +1148,28 @@ rmsnorm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restri
         out[(size_t)r * ldo + k] = q;
         split_store(osp, r, k, q);
     }
+}
+
+__global__ void __launch_bounds__(256)
+rmsnorm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, float* __restrict__ out, int ldo,
+                     int K, float eps, SplitBuf osp) {
+    PDL_PROLOGUE();
+    __shared__ float red[32];
+    rmsnorm_quant_body(red, x, ldx, w, out, ldo, K, eps, osp);
+}
+
+// The two consumers of the fused q-lora | kv projection in one launch, grid (rows, 2): CTA (r, 0) normalises and
+// quantises the q-lora slice of row r (rmsnorm_quant), CTA (r, 1) normalises, rotates, quantises and stores its kv
+// slice (kv_append).  Neither depends on the other; apart they cost a launch each on the decode critical path.
+__global__ void __launch_bounds__(256)
+qnorm_kv_append_kernel(const float* __restrict__ qa, int ld, int ql, const float* __restrict__ q_w, float* __restrict__ q_out,
+                       int ldo, float eps, SplitBuf osp, const float* __restrict__ kv_w, const float* __restrict__ freqs,
+                       const RowMeta* __restrict__ meta, __nv_bfloat16* __restrict__ ring, int cap,
+                       float* __restrict__ rows_out, int hd, int rd, int pos_off) {
+    PDL_PROLOGUE();
+    extern __shared__ float sh[];
+    if (blockIdx.y == 0) rmsnorm_quant_body(sh, qa, ld, q_w, q_out, ldo, ql, eps, osp);
+    else kv_append_body(sh, qa + ql, ld, kv_w, freqs, meta, ring, cap, rows_out, hd, rd, eps, pos_off);
 }
 
 // Shared expert: SwiGLU with clamps, then the e4m3-per-32 round trip of the result (f32 + split planes).
@@ -1547,6 +1573,19 @@ FB_API int fb_d4_rmsnorm_quant(const float* x, int64_t ldx, const float* w, floa
     if (K % 32) return (int)cudaErrorInvalidValue;
     FB_LAUNCH((rmsnorm_quant_kernel), n, 256, 0, st, x, (int)ldx, w, out, (int)ldo, (int)K, eps,
               mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+// qa [n][ld]: columns [0, ql) the q-lora vector, [ql, ql + hd) the raw kv row.  q_out / split planes as
+// fb_d4_rmsnorm_quant, ring / rows_out as fb_d4_kv_append.
+FB_API int fb_d4_qnorm_kv_append(const float* qa, int64_t ld, int64_t ql, const float* q_w, float* q_out, int64_t ldo,
+                                 float eps, void* s_base, int64_t s_ld, int64_t s_plane, int64_t s_mask, const float* kv_w,
+                                 const float* freqs, const void* meta, void* ring, int64_t cap, float* rows_out, int64_t n,
+                                 int64_t hd, int64_t rd, int64_t pos_off, cudaStream_t st) {
+    if ((ql % 32) || (hd % 32)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((qnorm_kv_append_kernel), dim3((unsigned)n, 2u), 256, (32 + hd) * sizeof(float), st, qa, (int)ld, (int)ql, q_w,
+              q_out, (int)ldo, eps, mk_split(s_base, s_ld, s_plane, s_mask), kv_w, freqs, (const RowMeta*)meta,
+              (__nv_bfloat16*)ring, (int)cap, rows_out, (int)hd, (int)rd, (int)pos_off);
     return FB_LAUNCH_CHECK();
 }
 

@@ -62,6 +62,39 @@ __device__ __forceinline__ void load_x_fp4(uint4 (&x)[4], const uint16_t* __rest
     }
 }
 
+// The same fragment from f32 rows that are not quantised yet: the e4m3-per-32 round trip (power-of-two block scale)
+// happens here.  The 32 values of scale block b sit in the four column-0 lanes (lanes 0..3, 8 values each), so the
+// block maximum is two shuffles; the round-tripped values are exact in f16.  All lanes of the warp must call.
+__device__ __forceinline__ void load_x_f32_quant(uint4 (&x)[4], const float* __restrict__ xr, int k0, int g, int tq, int nb = 4) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+        if (g == 0 && b < nb) {
+            const float4* p = reinterpret_cast<const float4*>(xr + k0 + b * 32 + tq * 8);
+            lo = __ldg(p);
+            hi = __ldg(p + 1);
+        }
+        float am = fmaxf(fmaxf(fmaxf(fabsf(lo.x), fabsf(lo.y)), fmaxf(fabsf(lo.z), fabsf(lo.w))),
+                         fmaxf(fmaxf(fabsf(hi.x), fabsf(hi.y)), fmaxf(fabsf(hi.z), fabsf(hi.w))));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        // 2^ceil(log2(amax / 448)), amax clamped from below as in the stand-alone quantiser
+        const float tt = fmaxf(am, 1e-4f) * (1.f / 448.f);
+        const uint32_t tb = __float_as_uint(tt);
+        const int ex = (int)((tb >> 23) & 0xff) + ((tb & 0x7fffffu) ? 1 : 0);
+        const float sc = __uint_as_float((uint32_t)min(max(ex, 0), 254) << 23);
+        const float inv = 1.f / sc;   // a power of two: exact
+        auto rt2 = [&](float a, float c) -> uint32_t {
+            // e4m3 (saturating) and back: two values per conversion
+            const __nv_fp8x2_storage_t q = __nv_cvt_float2_to_fp8x2(make_float2(a * inv, c * inv), __NV_SATFINITE, __NV_E4M3);
+            const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(q, __NV_E4M3);
+            const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&h), __float2half2_rn(sc));
+            return *reinterpret_cast<const uint32_t*>(&r);
+        };
+        x[b] = make_uint4(rt2(lo.x, lo.y), rt2(lo.z, lo.w), rt2(hi.x, hi.y), rt2(hi.z, hi.w));
+    }
+}
+
 struct Fp4Frag { uint4 wa, wb; uint32_t sa, sb; };
 __device__ __forceinline__ Fp4Frag load_fp4(const uint8_t* __restrict__ wa, const uint8_t* __restrict__ wb,
                                             const uint8_t* __restrict__ sa, const uint8_t* __restrict__ sb, int kb, int tq) {
@@ -143,8 +176,10 @@ expert_gate_up_mma_kernel(const uint16_t* __restrict__ xh, int ldx, const int* _
     }
 }
 
+// QF: `hh` holds f32 rows that are quantised on load (no separate quantiser launch before this kernel).
+template <bool QF>
 __global__ void __launch_bounds__(kNW * 32)
-expert_down_mma_kernel(const uint16_t* __restrict__ hh, const int* __restrict__ idx, const uint8_t* __restrict__ w2,
+expert_down_mma_kernel(const void* __restrict__ hh, const int* __restrict__ idx, const uint8_t* __restrict__ w2,
                        const uint8_t* __restrict__ s2, float* __restrict__ y, int ldy, int topk, int I, int D, int accumulate) {
     pdl_launch();
     __shared__ float red[kNW][16];
@@ -170,7 +205,8 @@ expert_down_mma_kernel(const uint16_t* __restrict__ hh, const int* __restrict__ 
     auto compute = [&](const Item& q, const Fp4Frag& f) {
         const int nb = q.kb < nfull ? 4 : 2;
         uint4 x[4];
-        load_x_fp4(x, hh + ((size_t)r * topk + q.s) * I, q.kb * 128, g, tq, nb);
+        if constexpr (QF) load_x_f32_quant(x, static_cast<const float*>(hh) + ((size_t)r * topk + q.s) * I, q.kb * 128, g, tq, nb);
+        else load_x_fp4(x, static_cast<const uint16_t*>(hh) + ((size_t)r * topk + q.s) * I, q.kb * 128, g, tq, nb);
         mma_block_fp4(acc, f.wa, f.wb, f.sa, f.sb, x, nb);
     };
     Fp4Frag fa, fb;
@@ -254,7 +290,17 @@ FB_API int fb_d4_expert_gate_up_mma(const void* xh, int64_t ldx, const int* idx,
 FB_API int fb_d4_expert_down_mma(const void* hh, const int* idx, const void* w2, const void* s2, float* y, int64_t ldy,
                                  int64_t n, int64_t topk, int64_t I, int64_t D, int64_t accumulate, cudaStream_t st) {
     if ((I % 64) || ((uintptr_t)hh & 15)) return (int)cudaErrorInvalidValue;
-    FB_LAUNCH((expert_down_mma_kernel), dim3((unsigned)((D + 15) / 16), (unsigned)n), kNW * 32, 0, st, (const uint16_t*)hh, idx,
+    FB_LAUNCH((expert_down_mma_kernel<false>), dim3((unsigned)((D + 15) / 16), (unsigned)n), kNW * 32, 0, st, hh, idx,
+              (const uint8_t*)w2, (const uint8_t*)s2, y, (int)ldy, (int)topk, (int)I, (int)D, (int)accumulate);
+    return FB_LAUNCH_CHECK();
+}
+
+// The same with h [rows][topk][I] in f32, NOT yet quantised: every CTA applies the e4m3-per-32 round trip to the
+// blocks it loads (the result equals fb_d4_quant_rows followed by fb_d4_expert_down_mma, one launch fewer).
+FB_API int fb_d4_expert_down_mma_f32(const float* h, const int* idx, const void* w2, const void* s2, float* y, int64_t ldy,
+                                     int64_t n, int64_t topk, int64_t I, int64_t D, int64_t accumulate, cudaStream_t st) {
+    if ((I % 64) || ((uintptr_t)h & 15)) return (int)cudaErrorInvalidValue;
+    FB_LAUNCH((expert_down_mma_kernel<true>), dim3((unsigned)((D + 15) / 16), (unsigned)n), kNW * 32, 0, st, (const void*)h, idx,
               (const uint8_t*)w2, (const uint8_t*)s2, y, (int)ldy, (int)topk, (int)I, (int)D, (int)accumulate);
     return FB_LAUNCH_CHECK();
 }

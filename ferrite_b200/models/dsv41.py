@@ -492,15 +492,11 @@ class Dsv41DeviceModel:
             self._quant(x.f, xq, n, d)
         self._xq_ready = False
         self.gemv(L["w_qkv_a"], xq, ws["qa"], n, ql + hd, d)
-        self.K.call("fb_d4_rmsnorm_quant", ws["qa"], ql + hd, L["q_norm"], qr.f, ql, n, ql, float(cfg.norm_eps), *qr.sp(1))
+        # one launch for both consumers of the q-lora | kv row: q-lora norm + quantiser, kv norm + rope + quantiser + store
+        # (a draft block's own KV rows stay out of the ring: they go to `extra`)
+        self.K.call("fb_d4_qnorm_kv_append", ws["qa"], ql + hd, ql, L["q_norm"], qr.f, ql, float(cfg.norm_eps), *qr.sp(1),
+                    L["kv_norm"], freqs, rs.meta, ring if extra is None else None, self.win_cap, extra, n, hd, rd, 0)
         self.gemv(L["wq_b"], qr, ws["q"], n, self.Hl * hd, ql)
-        kv_raw = View(ws["qa"], ql)
-        if extra is None:
-            self.K.call("fb_d4_kv_append", kv_raw, ql + hd, L["kv_norm"], freqs, rs.meta, ring, self.win_cap, None, n, hd,
-                        rd, float(cfg.norm_eps), 0)
-        else:   # a draft block: its own KV rows stay out of the ring
-            self.K.call("fb_d4_kv_append", kv_raw, ql + hd, L["kv_norm"], freqs, rs.meta, None, self.win_cap, extra, n, hd,
-                        rd, float(cfg.norm_eps), 0)
         comp, idx, ktop, ccap = None, None, 0, 0
         if r > 0:
             src = cfg.kv_source_of(layer)
@@ -615,6 +611,8 @@ class Dsv41DeviceModel:
             f16 = lambda a: _lib.ctypes.c_void_p(a.s.data_ptr() + 4 * a.plane)   # plane 2 of the int16 planes
             self.K.call("fb_d4_expert_gate_up_mma", f16(xq), xq.ld, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk,
                         self.Il, d, float(cfg.swiglu_limit))
+            # (fb_d4_expert_down_mma_f32 quantises h while loading it and saves this launch, but every one of its
+            # D / 16 CTAs then repeats the quantiser: 10.6 us against 1.7 + 7.2 us measured on the TP=4 shard)
             self.K.call("fb_d4_quant_rows", h.f, self.Il, h.f, self.Il, n * topk, self.Il, *h.sp(2))
             self.K.call("fb_d4_expert_down_mma", f16(h), ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
         else:

@@ -258,6 +258,11 @@ def test_fp4_expert_mma_kernels_match_simt(K, n, topk, E, I, D):
     K.call("fb_d4_expert_down_mma", f16(h), idx, w2p, s2, y, D, n, topk, I, D, 1)
     torch.cuda.synchronize()
     assert torch.allclose(y, 2 * y_ref, atol=2e-5 * max(1.0, y_ref.abs().max().item()), rtol=1e-4)
+    # quantise-on-load form: f32 rows that are not round-tripped yet give the same sums
+    y_q = torch.zeros(n, D, device=dev)
+    K.call("fb_d4_expert_down_mma_f32", h_raw, idx, w2p, s2, y_q, D, n, topk, I, D, 0)
+    torch.cuda.synchronize()
+    assert torch.allclose(y_q, y_ref, atol=1e-5 * max(1.0, y_ref.abs().max().item()), rtol=1e-4), (y_q - y_ref).abs().max().item()
     for t, orig in ((w13p, w13), (w2p, w2)):
         K.call("fb_d4_fp4_repack", t, t.numel() // t.shape[-1], t.shape[-1], 1)
         assert torch.equal(t, orig)

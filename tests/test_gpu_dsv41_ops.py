@@ -231,3 +231,34 @@ def test_hc_front_column_parallel_offset_form(K):
     wq = Q.fp8_act_roundtrip(want, 32)
     diff = (xq_out.cpu() - wq).abs()
     assert (diff > 1e-6).float().mean().item() < 0.005 and (diff <= 0.126 * want.abs() + 1e-6).all()
+
+
+def test_qnorm_and_kv_append_in_one_launch_match_the_two_kernels(K):
+    n, ql, hd, rd, cap = 3, 192, 128, 64, 16
+    qa = torch.randn(n, ql + hd, generator=gen(70)).cuda()
+    q_w = (1 + 0.1 * torch.randn(ql, generator=gen(71))).cuda()
+    kv_w = (1 + 0.1 * torch.randn(hd, generator=gen(72))).cuda()
+    freqs = (torch.rand(rd // 2, generator=gen(73)) * 0.1).cuda()
+    meta = meta_for([5, 77, 1000])
+    outs = []
+    for fused in (False, True):
+        q_out = torch.zeros(n, ql, device="cuda")
+        ring = torch.zeros(1, cap, hd, dtype=torch.bfloat16, device="cuda")
+        rows = torch.zeros(n, hd, device="cuda")
+        if fused:
+            K.call("fb_d4_qnorm_kv_append", qa, ql + hd, ql, q_w, q_out, ql, 1e-6, None, 0, 0, 0, kv_w, freqs, meta, ring, cap,
+                   rows, n, hd, rd, 0)
+        else:
+            K.call("fb_d4_rmsnorm_quant", qa, ql + hd, q_w, q_out, ql, n, ql, 1e-6, None, 0, 0, 0)
+            K.call("fb_d4_kv_append", _lib_view(qa, ql), ql + hd, kv_w, freqs, meta, ring, cap, rows, n, hd, rd, 1e-6, 0)
+        outs.append((q_out.cpu(), ring.float().cpu(), rows.cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    want = Q.fp8_act_roundtrip(G.rmsnorm(qa[:, :ql].cpu(), q_w.cpu(), 1e-6), 32)
+    diff = (outs[1][0] - want).abs()
+    assert (diff > 1e-6).float().mean().item() < 0.005
+
+
+def _lib_view(t, elems):
+    import ctypes
+    return ctypes.c_void_p(t.data_ptr() + elems * t.element_size())
