@@ -1174,13 +1174,11 @@ qnorm_kv_append_kernel(const float* __restrict__ qa, int ld, int ql, const float
 
 // Shared expert: SwiGLU with clamps, then the e4m3-per-32 round trip of the result (f32 + split planes).
 // One warp per 32-value block.
-__global__ void __launch_bounds__(256)
-swiglu_clamp_quant_kernel(const float* __restrict__ gu, int ld, float* __restrict__ out, int ldo, int n, int I, float lim,
-                          SplitBuf osp) {
-    PDL_PROLOGUE();
+__device__ __forceinline__ void swiglu_clamp_quant_body(const float* __restrict__ gu, int ld, float* __restrict__ out, int ldo,
+                                                        int n, int I, float lim, SplitBuf osp, int block) {
     const int lane = threadIdx.x & 31;
     const int nb = I / 32;
-    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int w = block * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (w >= n * nb) return;
     const int r = w / nb, i = (w % nb) * 32 + lane;
     float g = gu[(size_t)r * ld + i], u = gu[(size_t)r * ld + I + i];
@@ -1190,6 +1188,100 @@ swiglu_clamp_quant_kernel(const float* __restrict__ gu, int ld, float* __restric
     const float q = e4m3_rt(v / s) * s;
     out[(size_t)r * ldo + i] = q;
     split_store(osp, r, i, q);
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_clamp_quant_kernel(const float* __restrict__ gu, int ld, float* __restrict__ out, int ldo, int n, int I, float lim,
+                          SplitBuf osp) {
+    PDL_PROLOGUE();
+    swiglu_clamp_quant_body(gu, ld, out, ldo, n, I, lim, osp, (int)blockIdx.x);
+}
+
+// ---- MoE route without block-wide barriers in the pick loop ---------------------------------------
+// The same selection as route_kernel (sqrt(softplus) scores, bias only for the selection, ties to the lower
+// expert, weights of the picks normalised in pick order).  The whole block computes the scores (shared memory),
+// then ONE warp picks: lane l holds experts l, l + 32, ... (E <= 32 * kRouteSlots) as order-preserving 32-bit
+// keys; a pick is a register scan, a warp-wide integer maximum, and a warp-wide minimum over the indices that
+// hold it (two redux instructions).  The block-wide form takes six barriers per pick.
+constexpr int kRouteSlots = 12;
+__device__ __forceinline__ void route_row_block_d4(const float* __restrict__ lrow, const float* __restrict__ b, int E, int topk,
+                                                   float route_scale, int* __restrict__ idx_row, float* __restrict__ wts_row,
+                                                   uint32_t* u_s, float* sc_s) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const float x = lrow[e];
+        const float sp = x > 20.f ? x : log1pf(expf(x));
+        const float v = sqrtf(sp);
+        const float sv = v + b[e];
+        uint32_t u = __float_as_uint(sv);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // order-preserving map of finite and infinite floats
+        if (sv != sv) u = 1u;                             // NaN: below every number; 0 = not (or no longer) a candidate
+        sc_s[e] = v;
+        u_s[e] = u;
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const int lane = threadIdx.x;
+    float sc[kRouteSlots];
+    uint32_t u[kRouteSlots];
+#pragma unroll
+    for (int j = 0; j < kRouteSlots; ++j) {
+        const int e = lane + 32 * j;
+        sc[j] = e < E ? sc_s[e] : 0.f;
+        u[j] = e < E ? u_s[e] : 0u;
+    }
+    float wsum = 0.f, my_w = 0.f;
+    int my_e = 0;
+    for (int k = 0; k < topk; ++k) {
+        uint32_t m[kRouteSlots / 2];
+#pragma unroll
+        for (int j = 0; j < kRouteSlots / 2; ++j) m[j] = max(u[2 * j], u[2 * j + 1]);
+        const uint32_t lm = max(max(max(m[0], m[1]), max(m[2], m[3])), max(m[4], m[5]));
+        const uint32_t gm = __reduce_max_sync(0xffffffffu, lm);
+        uint32_t ce = 0xffffffffu;
+#pragma unroll
+        for (int j = kRouteSlots - 1; j >= 0; --j) ce = (u[j] == gm) ? (uint32_t)(lane + 32 * j) : ce;   // lowest j last
+        const int e = (int)__reduce_min_sync(0xffffffffu, ce);
+        const int jw = e >> 5, lw = e & 31;
+        float mine = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRouteSlots; ++j) {
+            if (j == jw) {
+                mine = sc[j];
+                if (lane == lw) u[j] = 0u;
+            }
+        }
+        const float s_e = __shfl_sync(0xffffffffu, mine, lw);
+        if (lane == k) { my_e = e; my_w = s_e; }
+        wsum += s_e;
+    }
+    if (lane < topk) {
+        float w = my_w;
+        if (topk > 1) w = w / (wsum + 1e-20f);
+        idx_row[lane] = my_e;
+        wts_row[lane] = w * route_scale;
+    }
+}
+
+// Routing of the rows and the shared expert's SwiGLU + quantiser in ONE launch: the two belong to independent
+// chains (router logits / shared gate | up, themselves one two-problem GEMV launch) that meet again only at the
+// down projections.  Blocks [0, n) route (a block per row), the others run swiglu_clamp_quant.
+__global__ void __launch_bounds__(256)
+route_swiglu_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, const float* __restrict__ bias_vl,
+                    const uint8_t* __restrict__ is_image, int n, int E, int topk, float route_scale, int* __restrict__ idx,
+                    float* __restrict__ wts, const float* __restrict__ gu, int ldgu, float* __restrict__ out, int ldo, int I,
+                    float lim, SplitBuf osp) {
+    PDL_PROLOGUE();
+    __shared__ uint32_t u_s[32 * kRouteSlots];
+    __shared__ float sc_s[32 * kRouteSlots];
+    const int rb = n;
+    if ((int)blockIdx.x < rb) {
+        const int r = blockIdx.x;
+        const float* b = (bias_vl && is_image && is_image[r]) ? bias_vl : bias;
+        route_row_block_d4(logits + (size_t)r * ld, b, E, topk, route_scale, idx + (size_t)r * topk, wts + (size_t)r * topk,
+                           u_s, sc_s);
+        return;
+    }
+    if (gu) swiglu_clamp_quant_body(gu, ldgu, out, ldo, n, I, lim, osp, (int)blockIdx.x - rb);
 }
 
 // ---- engram --------------------------------------------------------------------------------------
@@ -1595,6 +1687,18 @@ FB_API int fb_d4_swiglu_clamp_quant(const float* gu, int64_t ld, float* out, int
     const int64_t warps = n * (I / 32);
     FB_LAUNCH((swiglu_clamp_quant_kernel), (warps + 7) / 8, 256, 0, st, gu, (int)ld, out, (int)ldo, (int)n, (int)I, lim,
               mk_split(s_base, s_ld, s_plane, s_mask));
+    return FB_LAUNCH_CHECK();
+}
+
+// fb_d4_route and fb_d4_swiglu_clamp_quant (gu may be null: routing only) in one launch; E <= 384, topk <= 32.
+FB_API int fb_d4_route_swiglu(const float* logits, int64_t ld, const float* bias, const float* bias_vl, const uint8_t* is_image,
+                              int64_t n, int64_t E, int64_t topk, float route_scale, int* idx, float* wts, const float* gu,
+                              int64_t ldgu, float* out, int64_t ldo, int64_t I, float lim, void* s_base, int64_t s_ld,
+                              int64_t s_plane, int64_t s_mask, cudaStream_t st) {
+    if (topk > 32 || topk > E || E > 32 * kRouteSlots || (gu && (I % 32))) return (int)cudaErrorInvalidValue;
+    const int64_t rb = n, sb = gu ? (n * (I / 32) + 7) / 8 : 0;
+    FB_LAUNCH((route_swiglu_kernel), (unsigned)(rb + sb), 256, 0, st, logits, (int)ld, bias, bias_vl, is_image, (int)n, (int)E,
+              (int)topk, route_scale, idx, wts, gu, (int)ldgu, out, (int)ldo, (int)I, lim, mk_split(s_base, s_ld, s_plane, s_mask));
     return FB_LAUNCH_CHECK();
 }
 

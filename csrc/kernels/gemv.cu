@@ -289,19 +289,19 @@ __device__ __noinline__ void route_row_warp(const float* __restrict__ logits, co
 // A CTA owns 16*RT weight rows; its NW warps take interleaved k-blocks (64 bf16 / 128 e4m3
 // elements) with the next block's weight loads in flight while the current block is
 // multiplied; partial D tiles are summed across warps through shared memory.
+// tile_x: the CTA's row tile (blockIdx.x of a one-problem launch).
 template <int RT, int NW, bool FP8>
-__global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
-gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
-                const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
-                float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,
-                SplitBuf osplit, int l2_ahead, RouteTail rt) {
+__device__ __forceinline__ void gemv_mma_body(const uint8_t* __restrict__ W, const float* __restrict__ scales,
+                                              const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
+                                              float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows,
+                                              int accumulate, SplitBuf osplit, int l2_ahead, RouteTail rt, int tile_x) {
     pdl_launch();  // weights are constant: the first k-block is fetched before pdl_wait()
     constexpr int KB = FP8 ? 128 : 64;
     constexpr int XW = FP8 ? 16 : 8;
     __shared__ float red[NW][RT][32][4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16 * RT;
+    const int n0 = tile_x * 16 * RT;
     const int nkb = K / KB;
     const int kblocks = (K + 127) >> 7;
     // blockIdx.y walks 8-row windows of the activations: prefill-sized row counts take one launch, every
@@ -397,6 +397,36 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
     }
 }
 
+template <int RT, int NW, bool FP8>
+__global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : (RT >= 2 ? 2 : 4)))
+gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ scales,
+                const uint16_t* __restrict__ xhi, const uint16_t* __restrict__ xlo, int ldx,
+                float* __restrict__ out, int ldo, int mrows, int N, int K, int group_rows, int accumulate,
+                SplitBuf osplit, int l2_ahead, RouteTail rt) {
+    gemv_mma_body<RT, NW, FP8>(W, scales, xhi, xlo, ldx, out, ldo, mrows, N, K, group_rows, accumulate, osplit, l2_ahead, rt,
+                               (int)blockIdx.x);
+}
+
+// Two independent bf16 problems over the same rows in ONE launch (e.g. router logits from the un-quantised input and
+// the shared expert's gate | up from the quantised one): CTAs [0, tiles_a) work on problem a, the rest on problem b.
+// Apart, the smaller problem is a launch of a few dozen CTAs on the decode critical path.
+struct GemvProb {
+    const uint8_t* W;
+    const uint16_t* xhi;
+    const uint16_t* xlo;
+    int ldx;
+    float* out;
+    int ldo, N, K;
+};
+template <int NW>
+__global__ void __launch_bounds__(NW * 32, (NW >= 16 ? 2 : 4))
+gemv_mma_dual_kernel(GemvProb a, GemvProb b, int tiles_a, int mrows, int l2_ahead) {
+    const bool second = (int)blockIdx.x >= tiles_a;
+    const GemvProb p = second ? b : a;
+    gemv_mma_body<1, NW, false>(p.W, nullptr, p.xhi, p.xlo, p.ldx, p.out, p.ldo, mrows, p.N, p.K, 0, 0,
+                                SplitBuf{nullptr, 0, 0, 0}, l2_ahead, RouteTail{}, (int)blockIdx.x - (second ? tiles_a : 0));
+}
+
 template <bool FP8>
 int launch_mma(const void* W, const float* scales, const uint16_t* xs, int ldx, int plane, float* out, int ldo,
                int mrows, int N, int K, int group_rows, int accumulate, SplitBuf osplit, cudaStream_t st,
@@ -482,6 +512,27 @@ FB_API int fb_gemv_mma_bf16(const void* W, const void* xs, int64_t xs_ld, int64_
     SplitBuf os{(uint16_t*)os_base, (int)os_ld, (int)os_plane, (int)os_mask};
     return launch_mma<false>(W, nullptr, (const uint16_t*)xs, (int)xs_ld, (int)xs_plane, out, (int)ldo, (int)m, (int)N,
                              (int)K, (int)group_rows, (int)accumulate, os, st);
+}
+
+// out_a[m][N_a] = x_a . W_a^T and out_b[m][N_b] = x_b . W_b^T in one launch (bf16 weights, split-plane activations as
+// in fb_gemv_mma_bf16; plain stores, no groups).  K_a, K_b multiples of 64.
+FB_API int fb_gemv_mma_bf16_dual(const void* Wa, const void* xa, int64_t xa_ld, int64_t xa_plane, float* out_a, int64_t ldo_a,
+                                 int64_t Na, int64_t Ka, const void* Wb, const void* xb, int64_t xb_ld, int64_t xb_plane,
+                                 float* out_b, int64_t ldo_b, int64_t Nb, int64_t Kb, int64_t m, cudaStream_t st) {
+    if (m < 1 || m > 8 * 65535 || (Ka % 64) || (Kb % 64) || (xa_ld % 8) || (xb_ld % 8) || Na < 1 || Nb < 1)
+        return (int)cudaErrorInvalidValue;
+    const uint16_t* ha = (const uint16_t*)xa;
+    const uint16_t* hb = (const uint16_t*)xb;
+    GemvProb a{(const uint8_t*)Wa, ha, ha + xa_plane, (int)xa_ld, out_a, (int)ldo_a, (int)Na, (int)Ka};
+    GemvProb b{(const uint8_t*)Wb, hb, hb + xb_plane, (int)xb_ld, out_b, (int)ldo_b, (int)Nb, (int)Kb};
+    const int ta = (int)((Na + 15) / 16), tb = (int)((Nb + 15) / 16);
+    const dim3 grid((unsigned)(ta + tb), (unsigned)((m + 7) / 8));
+    if (Ka / 64 >= 64 && Kb / 64 >= 64) {
+        FB_LAUNCH((gemv_mma_dual_kernel<16>), grid, 512, 0, st, a, b, ta, (int)m, g_fb_l2_ahead);
+    } else {
+        FB_LAUNCH((gemv_mma_dual_kernel<8>), grid, 256, 0, st, a, b, ta, (int)m, g_fb_l2_ahead);
+    }
+    return FB_LAUNCH_CHECK();
 }
 
 // fb_gemv_mma_bf16 for the MoE router matrix [E router rows | shared gate | shared up]: the launch also routes the

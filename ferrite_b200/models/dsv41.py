@@ -446,6 +446,7 @@ class Dsv41DeviceModel:
     # 1 % SLOWER at TP1 and on the TP8 shard (2.175 vs 2.161 ms, 5.94 vs 5.88 ms): hc_pre is a one-CTA latency chain
     # on the critical path, the separate quantiser spreads over many CTAs
     fuse_quant = property(lambda self: switches().d4_fuse_quant)
+    moe_paired = True   # decode rows: router and shared-expert chains share their launches
     # decode rows: the front as a column-parallel kernel fed by the closing GEMV's Gram partials (it also quantises)
     hc_wide = property(lambda self: switches().hc_pre_wide and self.cfg.hc_mult == 4)
 
@@ -593,6 +594,33 @@ class Dsv41DeviceModel:
         d, x, xq = cfg.dim, ws["x"], ws["xq"]
         E, topk = L["E"], L["topk"]
         ldl = ws["rlogit"].shape[1]
+        if (L["fp4_mma"] and n <= self.fp4_mma_rows and not (L.get("mx") and n >= self.mx_min_rows) and E <= 384
+                and topk <= 32 and d % 64 == 0 and x.s is not None and xq.s is not None and self.moe_paired):
+            # Decode rows.  The router chain (logits -> route) and the shared expert's chain (gate | up -> SwiGLU) do
+            # not depend on each other: they share their launches (one two-problem GEMV, one route + SwiGLU kernel)
+            if not self._xq_ready:
+                self._quant(x.f, xq, n, d, mask=3)
+            self._xq_ready = False
+            hs, gu = ws["hs"], ws["gu"]
+            self.K.call("fb_gemv_mma_bf16_dual", L["gate_w"], x.s, x.ld, x.plane, ws["rlogit"], ldl, E, d,
+                        L["sh_w13"], xq.s, xq.ld, xq.plane, gu, gu.shape[1], 2 * self.Is, d, n)
+            self.K.call("fb_d4_route_swiglu", ws["rlogit"], ldl, L["gate_b"], L["gate_bvl"],
+                        ws["is_image"] if L["gate_bvl"] is not None else None, n, E, topk, float(cfg.route_scale),
+                        ws["ridx"], ws["rw"], gu, gu.shape[1], hs.f, self.Is, self.Is, float(cfg.swiglu_limit), *hs.sp(1))
+            h = ws["h"]
+            f16 = lambda a: _lib.ctypes.c_void_p(a.s.data_ptr() + 4 * a.plane)   # plane 2 of the int16 planes
+            self.K.call("fb_d4_expert_gate_up_mma", f16(xq), xq.ld, ws["ridx"], ws["rw"], L["w13"], L["s13"], h.f, n, topk,
+                        self.Il, d, float(cfg.swiglu_limit))
+            self.K.call("fb_d4_quant_rows", h.f, self.Il, h.f, self.Il, n * topk, self.Il, *h.sp(2))
+            self.K.call("fb_d4_expert_down_mma", f16(h), ws["ridx"], L["w2"], L["s2"], ws["y"], d, n, topk, self.Il, d, 0)
+            if not self.shared_tp:
+                self._reduce(ws["y"], n)
+            if self.shared_tp or self.world == 1:
+                self._out_gemv(L["sh_w2"], hs, n, d, self.Is, accumulate=True)
+            else:
+                self._fold_next = None
+                self.gemv(L["sh_w2"], hs, ws["y"], n, d, self.Is, accumulate=True)
+            return
         self.gemv(L["gate_w"], x, ws["rlogit"], n, E, d, ldo=ldl)
         self.K.call("fb_d4_route", ws["rlogit"], ldl, L["gate_b"], L["gate_bvl"], ws["is_image"] if L["gate_bvl"] is not None else None,
                     n, E, topk, float(cfg.route_scale), ws["ridx"], ws["rw"])

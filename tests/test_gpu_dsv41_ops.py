@@ -262,3 +262,42 @@ def test_qnorm_and_kv_append_in_one_launch_match_the_two_kernels(K):
 def _lib_view(t, elems):
     import ctypes
     return ctypes.c_void_p(t.data_ptr() + elems * t.element_size())
+
+
+@pytest.mark.parametrize("E,topk,n", [(384, 6, 1), (256, 8, 11), (40, 1, 3)])
+def test_route_and_swiglu_in_one_launch_match_the_two_kernels(K, E, topk, n):
+    I = 96
+    logits = torch.randn(n, E, generator=gen(80)) * 3
+    logits[0, 3] = logits[0, 9]                       # a tie: the lower index wins
+    logits[n - 1, :5] = float("-inf")
+    bias = (torch.randn(E, generator=gen(81)) * 0.1).cuda()
+    bias_vl = (torch.randn(E, generator=gen(82)) * 0.1).cuda()
+    is_img = (torch.arange(n) % 2).to(torch.uint8).cuda()
+    gu = (torch.randn(n, 2 * I, generator=gen(83)) * 4).cuda()
+    lg = logits.cuda()
+    idx0, w0 = torch.zeros(n, topk, dtype=torch.int32, device="cuda"), torch.zeros(n, topk, device="cuda")
+    out0 = torch.zeros(n, I, device="cuda")
+    K.call("fb_d4_route", lg, E, bias, bias_vl, is_img, n, E, topk, 2.5, idx0, w0)
+    K.call("fb_d4_swiglu_clamp_quant", gu, 2 * I, out0, I, n, I, 7.0, None, 0, 0, 0)
+    idx1, w1, out1 = torch.zeros_like(idx0), torch.zeros_like(w0), torch.zeros_like(out0)
+    K.call("fb_d4_route_swiglu", lg, E, bias, bias_vl, is_img, n, E, topk, 2.5, idx1, w1, gu, 2 * I, out1, I, I, 7.0,
+           None, 0, 0, 0)
+    assert torch.equal(idx0, idx1) and torch.equal(w0, w1) and torch.equal(out0, out1)
+
+
+def test_two_problem_gemv_matches_two_launches(K):
+    from ferrite_b200.models.glm import Act
+    m, Kd, Na, Nb = 3, 1024, 40, 200
+    dev = torch.device("cuda")
+    xa, xb = Act(dev, m, Kd), Act(dev, m, Kd)
+    xa.f.copy_(torch.randn(m, Kd, generator=gen(90)))
+    xb.f.copy_(torch.randn(m, Kd, generator=gen(91)))
+    for a in (xa, xb):
+        K.call("fb_split_rows", a.f, Kd, *a.sp(1), m, Kd)
+    Wa = torch.randn(Na, Kd, generator=gen(92)).to(torch.bfloat16).cuda()
+    Wb = torch.randn(Nb, Kd, generator=gen(93)).to(torch.bfloat16).cuda()
+    oa, ob = torch.zeros(m, Na + 8, device="cuda"), torch.zeros(m, Nb, device="cuda")
+    K.call("fb_gemv_mma_bf16_dual", Wa, xa.s, xa.ld, xa.plane, oa, Na + 8, Na, Kd, Wb, xb.s, xb.ld, xb.plane, ob, Nb, Nb, Kd, m)
+    close("problem a", oa[:, :Na], xa.f.cpu().double() @ Wa.float().cpu().double().t(), 2e-3)
+    close("problem b", ob, xb.f.cpu().double() @ Wb.float().cpu().double().t(), 2e-3)
+    assert float(oa[:, Na:].abs().sum()) == 0.0
