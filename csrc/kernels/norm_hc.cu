@@ -370,10 +370,27 @@ hc_pre_wide_kernel(const float* __restrict__ R, const float* __restrict__ part, 
     const float* grow = gram + (size_t)r * kGramPairs * part_ld;
     if ((int)blockIdx.x == nx) {
         // ---- coefficient CTA: all 24 mix dots + the sum of squares, then post / comb ----
-        for (int q = warp; q <= mix; q += kWideCols / 32) {
-            const int qi = q < mix ? q : kMaxMix;
-            const float v = tile_sum(prow + (size_t)qi * part_ld, nt, lane);
-            if (lane == 0) s_sum[qi] = v;
+        // 16 warps, 25 sums: a warp issues the loads of both of its sums before it reduces either (one L2 round trip)
+        for (int q = warp; q <= mix; q += 2 * (kWideCols / 32)) {
+            const int q2 = q + kWideCols / 32;
+            const int qi = q < mix ? q : kMaxMix, qi2 = q2 < mix ? q2 : kMaxMix;
+            const float* s1 = prow + (size_t)qi * part_ld;
+            const float* s2 = prow + (size_t)qi2 * part_ld;
+            const int nt2 = q2 <= mix ? nt : 0;
+            float v1[16], v2[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v1[j] = (lane + 32 * j < nt) ? __ldcg(s1 + lane + 32 * j) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v2[j] = (lane + 32 * j < nt2) ? __ldcg(s2 + lane + 32 * j) : 0.f;
+            float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { a1 += v1[j]; a2 += v2[j]; }
+            a1 = warp_sum(a1);
+            a2 = warp_sum(a2);
+            if (lane == 0) {
+                s_sum[qi] = a1;
+                if (q2 <= mix) s_sum[qi2] = a2;
+            }
         }
         __syncthreads();
         if (warp != 0) return;
