@@ -20,6 +20,63 @@ __device__ __forceinline__ uint32_t okey(float f) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// E <= 384: the block computes the sigmoids and the order-preserving selection keys into shared memory, then ONE warp
+// picks: lane l holds experts l, l + 32, ... in registers, a pick is a register scan, a warp-wide integer maximum and a
+// warp-wide minimum over the indices that hold it (two redux instructions) instead of three block barriers and a serial
+// scan by thread 0.  Same picks, same pick order, same sums as the general form below.
+constexpr int kFastSlots = 12;
+__device__ __forceinline__ void moe_route_row_fast(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                                   int* __restrict__ ids, float* __restrict__ wts, int E, int topk,
+                                                   float scaling, int r) {
+    __shared__ uint32_t u_s[32 * kFastSlots];
+    __shared__ float sig_s[32 * kFastSlots];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const float s = 1.f / (1.f + expf(-logits[(size_t)r * ld + e]));
+        sig_s[e] = s;
+        u_s[e] = okey(s + bias[e]);   // > 0 for every number; 0 marks "not (or no longer) a candidate"
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    const int lane = threadIdx.x;
+    uint32_t u[kFastSlots];
+    float sg[kFastSlots];
+#pragma unroll
+    for (int j = 0; j < kFastSlots; ++j) {
+        const int e = lane + 32 * j;
+        u[j] = e < E ? u_s[e] : 0u;
+        sg[j] = e < E ? sig_s[e] : 0.f;
+    }
+    float sum = 0.f, my_s = 0.f;
+    int my_e = 0;
+    for (int k = 0; k < topk; ++k) {
+        uint32_t m[kFastSlots / 2];
+#pragma unroll
+        for (int j = 0; j < kFastSlots / 2; ++j) m[j] = max(u[2 * j], u[2 * j + 1]);
+        const uint32_t gm = __reduce_max_sync(0xffffffffu, max(max(max(m[0], m[1]), max(m[2], m[3])), max(m[4], m[5])));
+        uint32_t ce = 0xffffffffu;
+#pragma unroll
+        for (int j = kFastSlots - 1; j >= 0; --j) ce = (u[j] == gm) ? (uint32_t)(lane + 32 * j) : ce;   // lowest index last
+        const int e = (int)__reduce_min_sync(0xffffffffu, ce);
+        const int jw = e >> 5, lw = e & 31;
+        float mine = 0.f;
+#pragma unroll
+        for (int j = 0; j < kFastSlots; ++j) {
+            if (j == jw) {
+                mine = sg[j];
+                if (lane == lw) u[j] = 0u;
+            }
+        }
+        const float sv = __shfl_sync(0xffffffffu, mine, lw);
+        if (lane == k) { my_s = sv; my_e = e; }
+        sum += sv;
+    }
+    if (lane < topk) {
+        const float inv = scaling / (sum + 1.1920929e-07f);
+        ids[(size_t)r * topk + lane] = my_e;
+        wts[(size_t)r * topk + lane] = my_s * inv;
+    }
+}
+
 // One block (256 threads) per row; E <= 1024.
 __device__ __forceinline__ void moe_route_row(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
                                               int* __restrict__ ids, float* __restrict__ wts, int E, int topk, float scaling, int r) {
@@ -76,7 +133,8 @@ __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int* __restrict__ ids,
                  float* __restrict__ wts, int E, int topk, float scaling) {
     PDL_PROLOGUE();
-    moe_route_row(logits, ld, bias, ids, wts, E, topk, scaling, blockIdx.x);
+    if (E <= 32 * kFastSlots && topk <= E) moe_route_row_fast(logits, ld, bias, ids, wts, E, topk, scaling, blockIdx.x);
+    else moe_route_row(logits, ld, bias, ids, wts, E, topk, scaling, blockIdx.x);
 }
 
 
@@ -390,7 +448,8 @@ moe_route_swiglu_kernel(const float* __restrict__ lg, int ld, const float* __res
                         SplitBuf asplit) {
     PDL_PROLOGUE();
     if (blockIdx.x == 0) {
-        moe_route_row(lg, ld, bias, ids, wts, E, topk, scaling, blockIdx.y);
+        if (E <= 32 * kFastSlots && topk <= E) moe_route_row_fast(lg, ld, bias, ids, wts, E, topk, scaling, blockIdx.y);
+        else moe_route_row(lg, ld, bias, ids, wts, E, topk, scaling, blockIdx.y);
         return;
     }
     const int r = blockIdx.y;
