@@ -301,3 +301,107 @@ def test_two_problem_gemv_matches_two_launches(K):
     close("problem a", oa[:, :Na], xa.f.cpu().double() @ Wa.float().cpu().double().t(), 2e-3)
     close("problem b", ob, xb.f.cpu().double() @ Wb.float().cpu().double().t(), 2e-3)
     assert float(oa[:, Na:].abs().sum()) == 0.0
+
+
+def test_index_score_relu_weighted_heads(K):
+    """score[r][j] = sum_h relu(q_h . k_j) w_h over the visible compressed rows, -inf beyond."""
+    n, IH, ID, ratio, cap, lds = 3, 8, 64, 2, 40, 48
+    pos = [9, 40, 79]                                  # visible rows: 5, 20, 40 (= cap)
+    q = torch.randn(n, IH * ID, generator=gen(100))
+    w = torch.randn(n, IH, generator=gen(101))
+    kc = torch.randn(1, cap, ID, generator=gen(102)).to(torch.bfloat16)
+    score = torch.full((n, lds), 7.0, device="cuda")
+    K.call("fb_d4_index_score", q.cuda(), IH * ID, w.cuda(), IH, kc.cuda(), cap, meta_for(pos), score, lds, n, IH, ID, ratio, 0.25)
+    want = (torch.einsum("shd,td->sht", q.view(n, IH, ID), kc[0].float()).relu() * (w * 0.25).unsqueeze(-1)).sum(1)
+    got = score.cpu()
+    for r in range(n):
+        clen = (pos[r] + 1) // ratio
+        close(f"index score row {r}", got[r, :clen], want[r, :clen], 2e-4 * max(1.0, want[r].abs().max().item()))
+        assert torch.isinf(got[r, clen:cap]).all() and (got[r, clen:cap] < 0).all()
+
+
+@pytest.mark.parametrize("ratio", [1, 4])
+def test_compressor_pools_groups_with_channel_softmax(K, ratio):
+    """A row whose position completes a group pools the group's positions with a per-channel softmax over the scores
+    and RMS-normalises (ratio 1: plain RMSNorm); other rows only store into the ring."""
+    hd, depth, n = 64, 16, 6
+    pos = list(range(5, 5 + n))                        # positions 5..10: groups complete at 7 (ratio 4) / everywhere (1)
+    kv = torch.randn(n, 2 * hd, generator=gen(110))    # [kv | score] per row
+    w = 1 + 0.1 * torch.randn(hd, generator=gen(111))
+    ring_kv = torch.zeros(1, depth, hd, device="cuda")
+    ring_sc = torch.zeros(1, depth, hd, device="cuda")
+    hist_kv = torch.randn(5, hd, generator=gen(112))   # positions 0..4, already in the ring
+    hist_sc = torch.randn(5, hd, generator=gen(113))
+    ring_kv[0, :5] = hist_kv.cuda()
+    ring_sc[0, :5] = hist_sc.cuda()
+    lat = torch.zeros(n, hd, device="cuda")
+    flag = torch.full((n,), -1, dtype=torch.int32, device="cuda")
+    kvd = kv.cuda()
+    import ctypes
+    K.call("fb_d4_compress", kvd, ctypes.c_void_p(kvd.data_ptr() + 4 * hd), 2 * hd, meta_for(pos),
+           ring_kv if ratio > 1 else None, ring_sc if ratio > 1 else None, depth, w.cuda(), lat, flag, n, hd, ratio, 1e-6)
+    all_kv = torch.cat([hist_kv, kv[:, :hd]])
+    all_sc = torch.cat([hist_sc, kv[:, hd:]])
+    for r, p in enumerate(pos):
+        done = (p + 1) % ratio == 0
+        assert int(flag[r]) == int(done)
+        if not done:
+            continue
+        if ratio == 1:
+            pooled = kv[r, :hd]
+        else:
+            g = slice(p - ratio + 1, p + 1)
+            pooled = (all_kv[g] * all_sc[g].softmax(0)).sum(0)
+        close(f"latent of position {p}", lat[r], G.rmsnorm(pooled, w, 1e-6), 1e-4)
+
+
+def test_engram_apply_gates_the_value_into_every_stream(K):
+    n, hc, D = 3, 4, 256
+    Rm = torch.randn(n, hc, D, generator=gen(120))
+    kv = torch.randn(n, (hc + 1) * D, generator=gen(121))
+    qk = torch.randn(hc, D, generator=gen(122))
+    dead = torch.tensor([0, 1, 0], dtype=torch.uint8)
+    Rd = Rm.clone().cuda()
+    K.call("fb_d4_engram_apply", Rd, kv.cuda(), qk.cuda(), dead.cuda(), n, hc, D, 1e-6)
+    key, value = kv[:, :hc * D].view(n, hc, D), kv[:, hc * D:]
+    rstd = torch.rsqrt(Rm.square().mean(-1) + 1e-6) * torch.rsqrt(key.square().mean(-1) + 1e-6)
+    dot = (Rm * qk * key).sum(-1) * rstd * D ** -0.5
+    gate = torch.sigmoid(torch.copysign(dot.abs().clamp_min(1e-6).sqrt(), dot))
+    gate = gate.masked_fill(dead.bool().unsqueeze(-1), 0)
+    close("engram", Rd, Rm + gate.unsqueeze(-1) * value.unsqueeze(-2), 1e-4)
+
+
+def test_hc_front_one_cta_per_row_and_post_mix(K):
+    """fb_hc_post_mix (R' = post y + comb^T R, mix dots of R' into acc) followed by fb_d4_hc_pre (coefficients of the
+    site from acc, contraction with the previous site's pre) against the fp32 statement."""
+    from ferrite_b200.ops import reference as R
+    n, m, H = 2, 4, 512
+    Rm = torch.randn(n, m, H, generator=gen(130))
+    y = torch.randn(n, H, generator=gen(131))
+    post = torch.rand(n, m, generator=gen(132)) * 2
+    comb = torch.rand(n, m, m, generator=gen(133))
+    fn = torch.randn(24, m * H, generator=gen(134)) * 0.05
+    scale = torch.tensor([0.7, 1.3, 0.9])
+    base = torch.randn(24, generator=gen(135)) * 0.3
+    ln_w = 1 + 0.1 * torch.randn(H, generator=gen(136))
+    pre_in = torch.rand(n, m, generator=gen(137)) + 0.1
+    Rout = torch.zeros(n, m, H, device="cuda")
+    acc = torch.zeros(n, 25, device="cuda")
+    K.call("fb_hc_post_mix", Rm.cuda(), Rout, y.cuda(), post.cuda(), comb.reshape(n, -1).cuda(), fn.cuda(), acc, n, H, 24)
+    want_R = R.hc_post(y, Rm, post, comb)
+    close("hc_post", Rout, want_R, 1e-4)
+    flat = want_R.reshape(n, -1)
+    close("mix dots", acc[:, :24], flat @ fn.t(), 2e-3)
+    close("sum of squares", acc[:, 24], flat.square().sum(-1), 1e-2)
+    x = torch.zeros(n, H, device="cuda")
+    pre_out, post_o, comb_o = torch.zeros(n, m, device="cuda"), torch.zeros(n, m, device="cuda"), torch.zeros(n, 16, device="cuda")
+    K.call("fb_d4_hc_pre", Rout, acc, scale.cuda(), base.cuda(), ln_w.cuda(), pre_in.cuda(), pre_out, post_o, comb_o, x, None,
+           n, H, m, 1e-6, 1e-6, 20, None, 0, 0, 0, None, None, 0, None, None, 0, 0, 0)
+    r = torch.rsqrt(flat.square().mean(-1, keepdim=True) + 1e-6)
+    wpre, wpost, wcomb = R.hc_coeffs((flat @ fn.t()) * r, scale, base, m, 1e-6, 20)
+    close("pre", pre_out, wpre, 2e-5)
+    close("post", post_o, wpost, 2e-5)
+    close("comb", comb_o, wcomb.reshape(n, -1), 2e-5)
+    want = G.rmsnorm((pre_in.unsqueeze(-1) * want_R).sum(1), ln_w, 1e-6)
+    close("x", x, want, 2e-5 * want.abs().max().item())
+    assert float(acc.abs().sum()) == 0.0               # cleared for the next site
