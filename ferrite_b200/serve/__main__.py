@@ -119,8 +119,13 @@ def _build_dsv41(args, tok):
         verdict = self_test(allreduce, dev, rank, world)   # a fused kernel that fails its check is detached
         if rank == 0:
             print(f"collective self-test: {verdict}", flush=True)
-    eng = Dsv41Engine(cfg, src, rank, world, dev, allreduce, max_ctx=args.max_ctx)
-    serve_eng = SingleFlight(Dsv41StepEngine(eng, spec=args.mtp > 1))
+    if args.max_seqs > 1:   # continuous batching, greedy: one row per live sequence in one forward per tick
+        from ..engine.dsv41_batch import Dsv41BatchEngine
+        serve_eng = Dsv41BatchEngine(cfg, src, rank, world, dev, allreduce, max_ctx=args.max_ctx, max_seqs=args.max_seqs,
+                                     prefill_rows=min(64, getattr(args, "prefill_rows", 64)))
+    else:
+        eng = Dsv41Engine(cfg, src, rank, world, dev, allreduce, max_ctx=args.max_ctx)
+        serve_eng = SingleFlight(Dsv41StepEngine(eng, spec=args.mtp > 1))
     if world > 1:
         from .tp_pool import ReplicatedEngine, make_control_group
         serve_eng = ReplicatedEngine(serve_eng, rank, world, make_control_group())

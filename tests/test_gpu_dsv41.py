@@ -126,6 +126,45 @@ def test_engine_plain_and_spec_generation():
     assert outs[("spec", True)] == outs[("plain", False)], outs
 
 
+def test_batched_engine_matches_single_sequence_engine():
+    """Continuous batching (several sequences of different lengths, more requests than slots, prefill chunks between
+    decode ticks, graph per bucket) emits for every request the tokens of the single-sequence engine."""
+    from ferrite_b200.engine.dsv41_batch import Dsv41BatchEngine
+    from ferrite_b200.engine.dsv41_engine import Dsv41Engine
+    from ferrite_b200.models.dsv41 import DictWeights
+    from ferrite_b200.serve.engine import RequestSpec
+    cfg, w, _ = _pair(seed=2)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (11, 3, 27, 1, 19)]
+    n_new = [9, 12, 6, 10, 8]
+    single = Dsv41Engine(cfg, DictWeights(w), max_ctx=128)
+    want = [single.generate(p, k) for p, k in zip(prompts, n_new)]
+    for graphs in (False, True):
+        eng = Dsv41BatchEngine(cfg, DictWeights(w), max_ctx=128, max_seqs=3, prefill_rows=8, prefill_budget=12,
+                               use_graphs=graphs)
+        got = eng.run_all([RequestSpec(p, k) for p, k in zip(prompts, n_new)])
+        assert eng.idle() and sorted(eng.free) == [0, 1, 2]
+        for rid, (p, k) in enumerate(zip(prompts, n_new), start=1):
+            assert got[rid] == want[rid - 1], (graphs, rid, got[rid], want[rid - 1])
+            assert eng.usage[rid].prompt_tokens == len(p) and eng.usage[rid].completion_tokens == k
+    # a stop id ends a sequence without emitting it; a cancelled request frees its slot
+    eng = Dsv41BatchEngine(cfg, DictWeights(w), max_ctx=128, max_seqs=2, prefill_rows=8)
+    stop_at = want[0][4]
+    cut = want[0].index(stop_at)
+    a = eng.submit(RequestSpec(prompts[0], 9, stop_ids=(stop_at,)))
+    b = eng.submit(RequestSpec(prompts[2], 50))
+    toks = {a: [], b: []}
+    for t in range(200):
+        if t == 3:
+            eng.cancel(b)
+        for rid, ev in eng.tick():
+            if ev.kind == "tokens":
+                toks[rid] += ev.ids
+        if eng.idle():
+            break
+    assert toks[a] == want[0][:cut] and eng.idle() and len(eng.free) == 2
+
+
 def test_draft_block_matches_golden():
     from ferrite_b200.models.dsv41 import DictWeights, Dsv41DeviceModel
     cfg, w, ref = _pair(seed=4)
