@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import time
 import os
 from dataclasses import replace
 
@@ -45,6 +46,7 @@ def main():
     ap.add_argument("--engram", action="store_true",
                     help="with --layers 0: keep the two engram layers and their hash tables (197 G e4m3 parameters, "
                          "row-sharded: 49 GB per rank at TP=4)")
+    ap.add_argument("--seqs", type=int, default=1, help="N > 1: N sequences through the continuous-batching engine")
     ap.add_argument("--spec", action="store_true", help="DSpark draft/verify steps instead of plain decode")
     ap.add_argument("--pdl", action="store_true", help="launch with programmatic dependent launch")
     ap.add_argument("--emulate-tp", type=int, default=0,
@@ -98,6 +100,8 @@ def main():
                       candidate_source_layer=2, engram_layer_ids=(), engram_num_embeddings=(),
                       dspark_target_layer_ids=tuple(range(max(0, L - 3), L)) if args.spec else (),
                       dspark_block_size=5 if args.spec else 0, n_routed_experts=args.experts).validate()
+    if args.seqs > 1:
+        return bench_batched(args, cfg, dev, model_rank, model_world, rank, world, allreduce, L)
     eng = Dsv41Engine(cfg, SyntheticDsv41Source(cfg, dev), model_rank, model_world, dev, allreduce,
                       max_ctx=args.prompt_len + 1024, max_rows=args.max_rows)
     g = torch.Generator().manual_seed(0)
@@ -179,6 +183,59 @@ def main():
                                                           "prefill_ms": round(prefill_ms, 2),
                                                           "prefill_ms_per_token": round(prefill_ms / args.prompt_len, 4),
                                                           }}))
+    if world > 1 or args.emulate_tp > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def bench_batched(args, cfg, dev, model_rank, model_world, rank, world, allreduce, L):
+    """--seqs N: N sequences through the continuous-batching engine (engine/dsv41_batch.py): prompts of --prompt-len
+    tokens are admitted and prefilled, then --steps decode ticks (one graph replay of N rows each, one token per
+    sequence, token read-back included) are timed with CUDA events.  Greedy, no speculation."""
+    from ferrite_b200.engine.dsv41_batch import Dsv41BatchEngine
+    from ferrite_b200.models.dsv41_synth import SyntheticDsv41Source
+    from ferrite_b200.serve.engine import RequestSpec
+    N = args.seqs
+    eng = Dsv41BatchEngine(cfg, SyntheticDsv41Source(cfg, dev), model_rank, model_world, dev, allreduce,
+                           max_ctx=args.prompt_len + args.steps + 64, max_seqs=N, prefill_rows=args.max_rows,
+                           prefill_budget=N * args.prompt_len)
+    g = torch.Generator().manual_seed(0)
+    budget = args.steps + max(args.warmup, 3) + 8
+    for _ in range(N):
+        eng.submit(RequestSpec(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), budget))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while sum(s.decoding for s in eng.live.values()) < N:
+        eng.tick()
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    for _ in range(max(args.warmup, 3)):
+        eng.tick()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    toks = 0
+    e0.record()
+    for _ in range(args.steps):
+        toks += sum(len(ev.ids) for _, ev in eng.tick() if ev.kind == "tokens")
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "dsv41_batched_decode_tok_s" + (f"_rank0_of_tp{args.emulate_tp}_emulated" if args.emulate_tp > 1 else ""),
+                          "value": round(toks / args.steps / ms * 1e3, 1), "unit": "tok/s", "higher_is_better": True,
+                          "n_gpus": world, "steps": args.steps, "ms_per_tick": round(ms, 3), "seqs": N, "layers": L,
+                          "tokens_per_tick": round(toks / args.steps, 2), "launches_per_tick": eng.launches,
+                          "dtype": "bf16 dense / e2m1 experts", "data": "synthetic",
+                          "config": {"dim": cfg.dim, "experts": cfg.n_routed_experts, "topk": cfg.n_activated_experts,
+                                     "context": args.prompt_len, "parallelism": f"tp{world}", "emulated_tp": args.emulate_tp,
+                                     "speculation": "none (greedy)", "prefill_all_s": round(prefill_s, 3),
+                                     "routed_experts": "block-scaled tcgen05 grouped GEMM" if 0 < eng.model.mx_min_rows <= N else "per-pair mma kernels"}}))
     if world > 1 or args.emulate_tp > 1:
         import torch.distributed as dist
         dist.barrier()

@@ -68,7 +68,8 @@ class Dsv41DeviceModel:
         self.shared_tp = world > 1 and per * world == cfg.moe_inter_dim
         self.Is_real = per if self.shared_tp else cfg.moe_inter_dim      # columns of the shared expert this rank owns
         self.Is = (self.Is_real + 63) // 64 * 64                        # zero-padded to the tensor-core GEMV's k-block
-        self.tc_min_rows = 16
+        self.tc_min_rows = switches().d4_tc_min_rows
+        self.fused_rows = switches().d4_fused_rows
         from ..parallel.status import StatusArena
         self.arena = getattr(allreduce, "arena", None) or StatusArena(self.dev, 2048)
         self.tc_status = self.arena.status("tcgen05")
@@ -416,7 +417,7 @@ class Dsv41DeviceModel:
         the fused kernel also applies hc_post and leaves the next site's mix-dot partials."""
         ws = self.ws
         fold, self._fold_next = self._fold_next, None
-        ok = (self.fused is not None and x.s is not None and n <= 8 and K % 64 == 0 and x.ld % 8 == 0 and N % 32 == 0
+        ok = (self.fused is not None and x.s is not None and n <= self.fused_rows and K % 64 == 0 and x.ld % 8 == 0 and N % 32 == 0
               and (self.world == 1 or n * N <= self.fused.max_elems) and (self.world > 1 or fold is not None))
         if not ok:
             gar = getattr(self.allreduce, "gemm_fused", None) if self.world > 1 else None
@@ -437,7 +438,7 @@ class Dsv41DeviceModel:
             ws["R"] = rout
             self._folded = True
             self._part_stale = False   # this launch rewrites the tile counts
-            if fold[0] is not None and self.hc_wide and N == self.cfg.dim and N // 16 <= 512 and N % 32 == 0:
+            if fold[0] is not None and self.hc_wide and n <= 8 and N == self.cfg.dim and N // 16 <= 512 and N % 32 == 0:
                 self._wide_ready = want_gram = True
         self.fused(w, None, x.s, x.ld, x.plane, ws["y"], N, n, N, K, accumulate, fold is None or self.debug is not None, f,
                    gram=want_gram)
@@ -477,7 +478,7 @@ class Dsv41DeviceModel:
                     L[f"hc_{site}_scale"] if coeffs else None, L[f"hc_{site}_base"] if coeffs else None, ln, pin, pout,
                     ws["post"], ws["comb"], x.f, None, n, cfg.dim, cfg.hc_mult, float(cfg.norm_eps), float(cfg.hc_eps),
                     cfg.hc_sinkhorn_iters, *x.sp(1),
-                    *(self.fused.partials() if self.fused is not None and coeffs and n <= 8 else (None, None, 0)),
+                    *(self.fused.partials() if self.fused is not None and coeffs and n <= self.fused_rows else (None, None, 0)),
                     *((ws["xq"].f, *ws["xq"].sp(3)) if quant else (None, None, 0, 0, 0)))
         self._xq_ready = quant   # the sublayer's first quantisation of x is already done
         if coeffs:

@@ -42,7 +42,11 @@ class Switches:
     l2_ahead: int = -1              # read-ahead distance of the weight-streaming kernels (-1 = library default)
     gdn_chunk_rows: int = 16        # GatedDeltaNet: groups of at least this many rows use the WY-chunked scan (0 = never)
     moe_tc_rows: int = 64           # GLM routed experts: rows from which the tcgen05 grouped GEMM runs (0 = never)
-    d4_mx_min_rows: int = 16        # DSV41 routed experts: rows from which the block-scaled tcgen05 grouped GEMM runs (0 = never)
+    d4_mx_min_rows: int = 32        # DSV41 routed experts: rows from which the block-scaled tcgen05 grouped GEMM runs (0 = never);
+                                    # 16 rows x 6 experts of 384 are nearly all distinct: grouping them buys no reuse (22.2 vs 16.2 ms per tick)
+    d4_tc_min_rows: int = 32        # DSV41 dense projections: rows from which the tcgen05 GEMM replaces 8-row GEMV windows
+                                    # (16 rows: two windows, the second from L2, 15.5 vs 16.2 ms per tick)
+    d4_fused_rows: int = 8          # DSV41: forwards of up to this many rows close their sublayers with the fused GEMV + all-reduce
     d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores
     d4_attn_tc: bool = False        # DSV41 tensor-core sparse attention (slower than the SIMT kernel at decode sizes)
     d4_fuse_quant: bool = False     # DSV41 activation quantiser fused into hc_pre (a one-CTA latency chain; slower)

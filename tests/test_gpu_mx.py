@@ -146,9 +146,12 @@ def test_dsv41_prefill_through_block_scaled_experts_matches_decode_kernels():
     logits = {}
     try:
         for mx_rows in (0, 16):
-            set_switches(Switches(d4_mx_min_rows=mx_rows))
+            set_switches(Switches(d4_mx_min_rows=mx_rows, d4_tc_min_rows=16))
             dev = Dsv41DeviceModel(cfg, DictWeights(w), max_rows=16, max_ctx=128)
             assert any(L.get("mx") for L in dev.layers) == (mx_rows > 0)
+            # the same router GEMM in both runs (the paired decode launches read the activations' hi + lo planes, the
+            # tcgen05 GEMM the hi plane: a router logit that moves in its last bits can pick another expert)
+            dev.moe_paired = False
             out = []
             for i in range(0, len(ids), 16):
                 c = ids[i:i + 16]
