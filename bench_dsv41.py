@@ -131,34 +131,7 @@ def main():
         torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / args.steps
     if args.kernel_times:
-        from torch.profiler import ProfilerActivity, profile
-        import torch.distributed as dist
-        sync = (lambda: dist.barrier()) if world > 1 else (lambda: None)
-        sync()
-        if rank == 0:
-            with profile(activities=[ProfilerActivity.CUDA]) as prof:
-                sync()                       # the profiler's start-up is over before the peers' bounded waits begin
-                for _ in range(5):
-                    step()
-                torch.cuda.synchronize()
-            rows = {}
-            for ev in prof.events():
-                if ev.device_type is not None and "cuda" in str(ev.device_type).lower() and ev.name:
-                    r = rows.setdefault(ev.name, [0, 0.0])
-                    r[0] += 1
-                    r[1] += float(ev.time_range.elapsed_us())
-            tot = sum(v[1] for v in rows.values())
-            with open(args.kernel_times, "w") as f:
-                f.write(f"# per-kernel device time, 5 decode steps, rank 0; total {tot / 5:.1f} us of kernel time per step\n")
-                f.write("# us_per_step  launches_per_step  avg_us  kernel\n")
-                for name, (n, us) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
-                    f.write(f"{us / 5:10.1f} {n / 5:8.1f} {us / max(n, 1):8.2f}  {name[:110]}\n")
-        else:
-            sync()
-            for _ in range(5):
-                step()
-            torch.cuda.synchronize()
-        sync()
+        kernel_times(args.kernel_times, step, rank, world, "decode steps")
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms], device=dev)
@@ -187,6 +160,38 @@ def main():
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+
+
+def kernel_times(path, step, rank, world, what):
+    """5 more calls of `step` under torch.profiler on rank 0 (every rank steps): per-kernel device times to `path`."""
+    from torch.profiler import ProfilerActivity, profile
+    import torch.distributed as dist
+    sync = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    sync()
+    if rank == 0:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            sync()                       # the profiler's start-up is over before the peers' bounded waits begin
+            for _ in range(5):
+                step()
+            torch.cuda.synchronize()
+        rows = {}
+        for ev in prof.events():
+            if ev.device_type is not None and "cuda" in str(ev.device_type).lower() and ev.name:
+                r = rows.setdefault(ev.name, [0, 0.0])
+                r[0] += 1
+                r[1] += float(ev.time_range.elapsed_us())
+        tot = sum(v[1] for v in rows.values())
+        with open(path, "w") as f:
+            f.write(f"# per-kernel device time, 5 {what}, rank 0; total {tot / 5:.1f} us of kernel time per step\n")
+            f.write("# us_per_step  launches_per_step  avg_us  kernel\n")
+            for name, (n, us) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+                f.write(f"{us / 5:10.1f} {n / 5:8.1f} {us / max(n, 1):8.2f}  {name[:110]}\n")
+    else:
+        sync()
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+    sync()
 
 
 def bench_batched(args, cfg, dev, model_rank, model_world, rank, world, allreduce, L):
@@ -221,6 +226,8 @@ def bench_batched(args, cfg, dev, model_rank, model_world, rank, world, allreduc
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
+    if args.kernel_times:
+        kernel_times(args.kernel_times, eng.tick, rank, world, "decode ticks")
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms], device=dev)
