@@ -363,7 +363,8 @@ def make_cases(K, only):
         cases.append(Case("d4_sparse_attn_tc.tp8.m1", (W + ktop) * hd * 2, d4attc, "tensor-core form, 10 splits of 64 keys + merge kernel"))
         for ns in (32, 40, 80):
             bo, bm = torch.zeros(n * Hl * ns * hd, device=dev), torch.zeros(n * Hl * ns * 2, device=dev)
-            for tk, tag in ((None, "2k"), (at_tk, "1k")):
+            # one-kernel form: the merging warp keeps a split per lane (<= 32 splits); multiples of 8 merge by clusters
+            for tk, tag in ((None, "2k"), (at_tk, "1k")) if ns <= 32 else ((None, "2k"),):
                 def f(ns=ns, bo=bo, bm=bm, tk=tk):
                     K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta,
                            0, 0, float(hd ** -0.5), Hl, hd, out, Hl * hd, n, ns, bo, bm, None, 0, 0, 0, tk)
