@@ -452,9 +452,11 @@ class Dsv41DeviceModel:
     hc_wide = property(lambda self: switches().hc_pre_wide and self.cfg.hc_mult == 4)
 
     def _hc_pre(self, L, site, ln, n, coeffs=True, quant=True):
-        quant = quant and self.fuse_quant
         """Coefficients of this site (stored for the next one) and the contraction with the previous
-        site's `pre`; leaves the normed input in ws['x'] (f32 + bf16 planes)."""
+        site's `pre`; leaves the normed input in ws['x'] (f32 + bf16 planes).  When the closing GEMV of the previous
+        sublayer left mix-dot and Gram partials (decode rows), the column-parallel kernel runs and also leaves the
+        e4m3 round trip of x in ws['xq']."""
+        quant = quant and self.fuse_quant
         cfg, ws = self.cfg, self.ws
         x = ws["x"]
         pin, pout = ws["pre_cur"], ws["pre_nxt"]
