@@ -5,9 +5,10 @@ ring and engram history are all indexed by slot and position), so a decode tick 
 live slots, replayed as a CUDA graph per bucket of the ladder: batch membership only changes the device tables of
 the bucket's row set (slot of every row), never the graph.  Prompts are admitted FIFO into free slots and prefilled
 in chunks of ``prefill_rows`` rows between decode ticks, at most ``prefill_budget`` prompt tokens per tick, so a
-long prompt does not stall the sequences that are already decoding.  Routed experts of a decode tick with 16 rows or
+long prompt does not stall the sequences that are already decoding.  Routed experts of a decode tick with 32 rows or
 more run as the block-scaled tcgen05 grouped GEMMs (every expert's weights stream once per tick, however many rows
-routed to it); below that the per-pair tensor-core kernels run.
+routed to it); below that the per-pair tensor-core kernels run (16 rows x 6 picks of 384 experts are nearly all
+distinct experts: grouping them buys no reuse).
 
 Counterpart of the reference's batched DSV41 arm (``scripts/batched_400_v2.sh``; serving seam
 ``crates/ferrite-dsv41/src/serve.rs``) behind the same ``ServeEngine`` protocol as the GLM batched engine
@@ -52,20 +53,25 @@ def bucket_for(buckets: Sequence[int], n: int) -> int:
 class Dsv41BatchEngine:
     def __init__(self, cfg: Dsv41Config, src, rank: int = 0, world: int = 1, device="cuda", allreduce=None,
                  max_ctx: int = 1024, max_seqs: int = 8, prefill_rows: int = 64, prefill_budget: int = 256,
-                 buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64), use_graphs: bool = True):
+                 buckets: Sequence[int] = (1, 2, 4, 8, 16, 32, 64), use_graphs: bool = True, model=None):
         self.cfg = cfg
         self.max_seqs, self.prefill_rows, self.prefill_budget = max_seqs, prefill_rows, max(prefill_budget, 1)
-        self.model = m = Dsv41DeviceModel(cfg, src, rank, world, device, allreduce, max_rows=max(prefill_rows, max_seqs),
-                                          max_ctx=max_ctx, n_slots=max_seqs + 1)
+        # `model`: a ready device model (tests drive the scheduling with a host stand-in of the same interface)
+        self.model = m = model if model is not None else Dsv41DeviceModel(
+            cfg, src, rank, world, device, allreduce, max_rows=max(prefill_rows, max_seqs), max_ctx=max_ctx,
+            n_slots=max_seqs + 1)
         self.dev = dev = m.dev
-        self.use_graphs = use_graphs
+        self.on_gpu = dev.type == "cuda"
+        self.use_graphs = use_graphs and self.on_gpu
         self.buckets = [b for b in buckets if b < max_seqs] + [max_seqs]
         self.dummy_slot = max_seqs                                    # padding rows of a bucket run on this slot
         self.rowsets = {b: m.make_rows(list(range(b)), [1] * b) for b in self.buckets}
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.ids = torch.zeros(max_seqs, dtype=torch.int32, device=dev)          # input token of every graph row
         self.tok_slot = torch.zeros(max_seqs + 1, dtype=torch.int32, device=dev)  # next input token of every slot
-        self.pin_out = torch.zeros(max_seqs, dtype=torch.int32).pin_memory()
+        self.pin_out = torch.zeros(max_seqs, dtype=torch.int32)
+        if self.on_gpu:
+            self.pin_out = self.pin_out.pin_memory()
         self.free: List[int] = list(range(max_seqs - 1, -1, -1))
         self.waiting: Deque[_Seq] = deque()
         self.live: Dict[int, _Seq] = {}                                # by request id, admission order
@@ -73,8 +79,9 @@ class Dsv41BatchEngine:
         self.next_id = 1
         self.ticks = self.tokens = 0
         self.launches = 0
-        from ..parallel.collective import startup_barrier
-        startup_barrier(world, getattr(allreduce, "group", None))
+        if model is None:
+            from ..parallel.collective import startup_barrier
+            startup_barrier(world, getattr(allreduce, "group", None))
 
     # ------------------------------------------------------------------ ServeEngine
     def max_prompt(self) -> int:
@@ -173,7 +180,8 @@ class Dsv41BatchEngine:
             self.tok_slot[idx] = self.ids[:bucket]
             self.pin_out.copy_(self.ids, non_blocking=True)
             m.arena.snapshot_async()
-            torch.cuda.current_stream().synchronize()
+            if self.on_gpu:
+                torch.cuda.current_stream().synchronize()
             m.arena.verify()
             for i, s in enumerate(dec):
                 self._emit(s, int(self.pin_out[i]), out)
