@@ -48,6 +48,38 @@ def main():
         out = [None] * world
         dist.all_gather_object(out, (s["ticks"], s["tokens_committed"]))
         assert len(set(out)) == 1, out
+    elif mode == "dsv41batch":
+        # the batched DSV41 engine (host stand-in model) under replicated control: rank 0 submits and cancels, every
+        # rank plans the same ticks and commits the same tokens
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from test_dsv41_batch_sched import FakeModel, expected
+        from ferrite_b200.engine.dsv41_batch import Dsv41BatchEngine
+        inner = Dsv41BatchEngine(None, None, max_ctx=64, max_seqs=2, prefill_rows=4, prefill_budget=6,
+                                 model=FakeModel(3, 64, 4))
+        eng = ReplicatedEngine(inner, rank, world)
+        if rank == 0:
+            prompts = [[7, 8, 9], list(range(20, 31)), [5], [40, 41]]
+            ids = [eng.submit(RequestSpec(p, 5)) for p in prompts]
+            toks = {i: [] for i in ids}
+            n = 0
+            while not eng.idle():
+                n += 1
+                if n == 2:
+                    eng.cancel(ids[3])
+                for rid, ev in eng.tick():
+                    if ev.kind == "tokens":
+                        toks[rid] += ev.ids
+            eng.stop()
+            for i, p in zip(ids[:3], prompts):
+                assert toks[i] == expected(p, 5), (i, toks[i])
+            assert toks[ids[3]] == []
+            print("POOL_OK", sorted(toks.items()))
+        else:
+            eng.follow()
+        s = eng.stats()["engine"]
+        out = [None] * world
+        dist.all_gather_object(out, (s["ticks"], s["tokens_committed"], s["free_slots"]))
+        assert len(set(out)) == 1 and out[0][2] == 2, out
     elif mode == "fault":
         eng = ReplicatedEngine(Flaky(bad_rank=1, bad_tick=3, rank=rank), rank, world)
         try:

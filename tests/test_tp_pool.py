@@ -19,6 +19,11 @@ def test_replicated_engine_keeps_ranks_in_step():
     assert r.returncode == 0 and "POOL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def test_batched_dsv41_engine_under_replicated_control():
+    r = _run("dsv41batch", 2, 29614)
+    assert r.returncode == 0 and "POOL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_failing_rank_is_reported_by_every_rank():
     r = _run("fault", 3, 29612)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
