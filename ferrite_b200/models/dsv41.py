@@ -418,7 +418,8 @@ class Dsv41DeviceModel:
         ws = self.ws
         fold, self._fold_next = self._fold_next, None
         ok = (self.fused is not None and x.s is not None and n <= self.fused_rows and K % 64 == 0 and x.ld % 8 == 0 and N % 32 == 0
-              and (self.world == 1 or n * N <= self.fused.max_elems) and (self.world > 1 or fold is not None))
+              and (self.world == 1 or min(n, 8) * N <= self.fused.max_elems)   # the launcher walks 8-row windows
+              and (self.world > 1 or fold is not None))
         if not ok:
             gar = getattr(self.allreduce, "gemm_fused", None) if self.world > 1 else None
             if (gar is not None and x.s is not None and n >= self.tc_min_rows and K % 8 == 0 and x.ld % 8 == 0

@@ -47,6 +47,7 @@ class Switches:
     d4_tc_min_rows: int = 32        # DSV41 dense projections: rows from which the tcgen05 GEMM replaces 8-row GEMV windows
                                     # (16 rows: two windows, the second from L2, 15.5 vs 16.2 ms per tick)
     d4_fused_rows: int = 8          # DSV41: forwards of up to this many rows close their sublayers with the fused GEMV + all-reduce
+                                    # (16: two 8-row windows per launch site, 80 launches fewer per 16-row tick but 15.9 vs 15.5 ms)
     d4_fp4_mma: bool = True         # DSV41 routed experts of decode rows on the tensor cores
     d4_attn_tc: bool = False        # DSV41 tensor-core sparse attention (slower than the SIMT kernel at decode sizes)
     d4_fuse_quant: bool = False     # DSV41 activation quantiser fused into hc_pre (a one-CTA latency chain; slower)

@@ -147,6 +147,20 @@ def test_batched_engine_matches_single_sequence_engine():
         for rid, (p, k) in enumerate(zip(prompts, n_new), start=1):
             assert got[rid] == want[rid - 1], (graphs, rid, got[rid], want[rid - 1])
             assert eng.usage[rid].prompt_tokens == len(p) and eng.usage[rid].completion_tokens == k
+    # more than 8 decode rows, with the sublayers closed by the fused GEMV + fold kernel in two 8-row windows
+    from ferrite_b200.utils.switches import Switches, set_switches
+    try:
+        set_switches(Switches(d4_fused_rows=16))
+        many = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (4, 9, 2, 6, 12, 3, 7, 5, 10, 8, 1)]
+        want_many = [single.generate(p, 6) for p in many]
+        eng = Dsv41BatchEngine(cfg, DictWeights(w), max_ctx=128, max_seqs=11, prefill_rows=16, prefill_budget=200)
+        assert eng.model.fused_rows == 16
+        got = eng.run_all([RequestSpec(p, 6) for p in many])
+        assert max(rows for rows in eng.graphs) == 11                # one tick decoded all eleven sequences
+        for rid, wnt in enumerate(want_many, start=1):
+            assert got[rid] == wnt, (rid, got[rid], wnt)
+    finally:
+        set_switches(None)
     # a stop id ends a sequence without emitting it; a cancelled request frees its slot
     eng = Dsv41BatchEngine(cfg, DictWeights(w), max_ctx=128, max_seqs=2, prefill_rows=8)
     stop_at = want[0][4]
