@@ -274,9 +274,8 @@ class Dsv41DeviceModel:
         # split-K attention: keys of a row are spread over up to 16 CTAs per head tile
         lmax = cfg.window_size + cfg.index_topk + max(cfg.dspark_block_size, 1)
         self.at_split = max(1, min(16, (lmax + 31) // 32))
-        # a few decode rows on few heads (a tensor-parallel shard): 32 splits, or the grid is a fraction of the SMs
-        self.at_split_few = 32
-        at_parts = max(M * self.Hl * self.at_split, 32 * self.at_split_few)
+        # the split count follows the row count (`_attn_splits`): about one CTA per SM, at most 32 splits
+        at_parts = max(M * self.Hl * self.at_split, 1536)
         ws["at_o"] = self._z(at_parts * hd)
         ws["at_ml"] = self._z(at_parts * 2)
         ws["at_ticket"] = self._z(M * ((self.Hl + 7) // 8), dtype=torch.int32)   # split-merge tickets (left at zero)
@@ -487,6 +486,16 @@ class Dsv41DeviceModel:
         if coeffs:
             ws["pre_cur"], ws["pre_nxt"] = pout, pin
 
+    def _attn_splits(self, n: int) -> int:
+        """Key splits of the sparse attention for n rows: about one CTA per SM over (head tiles x rows x splits).  One
+        decode row on a tensor-parallel shard takes 32 splits (4 clusters of 8 per head tile), 16 batched rows 4, a
+        prefill chunk 1: a CTA holds 233 registers per thread, so only one is resident per SM and every further wave
+        of CTAs costs a whole pass (16 rows at 16 splits: 60.7 us in 3.5 waves)."""
+        want = max(1, 148 // (((self.Hl + 7) // 8) * n))
+        if want >= 32:
+            return 32
+        return want // 8 * 8 if want >= 8 else want   # multiples of 8 merge by clusters
+
     def _attention(self, L, rs: RowSet, shared: dict, ring, extra=None, n_extra=0, win_mode=0):
         cfg, ws, n = self.cfg, self.ws, rs.n
         d, hd, ql, rd = cfg.dim, cfg.head_dim, cfg.q_lora_rank, cfg.rope_head_dim
@@ -551,7 +560,7 @@ class Dsv41DeviceModel:
         else:
             self.K.call("fb_d4_sparse_attn", ws["q"], self.Hl * hd, ring, self.win_cap, cfg.window_size, comp, ccap, idx,
                         cfg.index_topk, ktop, extra, n_extra, L["sink"], freqs, rd, rs.meta, 0, win_mode, float(hd ** -0.5),
-                        self.Hl, hd, o.f, self.Hl * hd, n, self.at_split_few if n * self.Hl <= 32 else self.at_split,
+                        self.Hl, hd, o.f, self.Hl * hd, n, self._attn_splits(n),
                         ws["at_o"], ws["at_ml"], *o.sp(1), ws["at_ticket"])
         low = ws["low"]
         R_ = cfg.o_lora_rank
