@@ -369,6 +369,50 @@ def make_cases(K, only):
                     K.call("fb_d4_sparse_attn", q, Hl * hd, ring, cap, W, comp, ccap, idx, ktop, ktop, None, 0, sink, freqs, 64, meta,
                            0, 0, float(hd ** -0.5), Hl, hd, out, Hl * hd, n, ns, bo, bm, None, 0, 0, 0, tk)
                 cases.append(Case(f"d4_sparse_attn_{tag}.split{ns}.tp8.m1", (W + ktop) * hd * 2, f, f"{ns} splits"))
+    if want("d4_route_swiglu"):
+        # DSV41 decode, one row: routing over 384 experts (block-parallel scores, one-warp picks) and the shared
+        # expert's SwiGLU + quantiser as two roles of one launch
+        n, E, topk, I = 1, 384, 6, 512
+        lg = torch.randn(n, E, device=dev) * 3
+        bias = torch.randn(E, device=dev) * 0.1
+        gu = torch.randn(n, 2 * I, device=dev) * 4
+        ridx = torch.zeros(n, topk, dtype=torch.int32, device=dev)
+        rw = torch.zeros(n, topk, device=dev)
+        hs = torch.zeros(n, I, device=dev)
+
+        def d4rs():
+            K.call("fb_d4_route_swiglu", lg, E, bias, None, None, n, E, topk, 2.5, ridx, rw, gu, 2 * I, hs, I, I, 7.0, None, 0, 0, 0)
+
+        def d4r():
+            K.call("fb_d4_route", lg, E, bias, None, None, n, E, topk, 2.5, ridx, rw)
+        cases.append(Case("d4_route_swiglu.m1", E * 8 + 3 * I * 4, d4rs, "one launch: route (384 experts, top 6) + SwiGLU/quantiser of 512 channels"))
+        cases.append(Case("d4_route_block.m1", E * 8, d4r, "the block-wide router alone (six barriers per pick)"))
+    if want("hc_pre_wide_offset"):
+        # DSV41 decode, one row: the column-parallel hyper-connection front fed by 320 tiles of partials
+        n, H, tiles, ld = 1, 5120, 320, 512
+        Rm = torch.randn(n, 4, H, device=dev)
+        part = torch.randn(8, 25, ld, device=dev) * 0.1
+        part[:, 24] = part[:, 24].abs() * 50 + 1.0          # sums of squares
+        gram = torch.randn(8, 10, ld, device=dev).abs() + 0.5
+        part_n = torch.full((8,), tiles, dtype=torch.int32, device=dev)
+        scale, base = torch.ones(3, device=dev), torch.zeros(24, device=dev)
+        ln_w = torch.ones(H, device=dev)
+        pre_in, pre_out = torch.rand(n, 4, device=dev) + 0.1, torch.zeros(n, 4, device=dev)
+        post, comb = torch.zeros(n, 4, device=dev), torch.zeros(n, 16, device=dev)
+        xo, xq = torch.zeros(n, H, device=dev), torch.zeros(n, H, device=dev)
+        acc = torch.zeros(n, 25, device=dev)
+
+        def hcw():
+            K.call("fb_hc_pre_wide_offset", Rm, part, gram, part_n, ld, scale, base, ln_w, pre_in, pre_out, xo, post, comb, n, H,
+                   24, 1e-6, 1e-6, 20, None, 0, 0, 0, xq, None, 0, 0, 0)
+
+        def hc1():
+            acc.copy_(part[:1, :, 0])
+            K.call("fb_d4_hc_pre", Rm, acc, scale, base, ln_w, pre_in, pre_out, post, comb, xo, None, n, H, 4, 1e-6, 1e-6, 20,
+                   None, 0, 0, 0, None, None, 0, None, None, 0, 0, 0)
+        cases.append(Case("hc_pre_wide_offset.m1", 4 * H * 4 + 2 * H * 4 + 35 * tiles * 4, hcw,
+                          "11 CTAs per row: contraction + RMSNorm + e4m3 round trip per 512 columns, coefficients in their own CTA"))
+        cases.append(Case("hc_pre_offset_one_cta.m1", 4 * H * 4 + H * 4, hc1, "one CTA per row (plus a 100-byte copy that refills its accumulator)"))
     if want("d4_index_score"):
         n, IHl, ID, ccap = 1, 4, 128, 65536
         kc = torch.randn(1, ccap, ID, device=dev).to(torch.bfloat16)
