@@ -57,12 +57,63 @@ def finish_reason(reason: str) -> str:
     return reason if reason in ("stop", "length") else ("stop" if reason == "cancelled" else reason)
 
 
+class ServerMetrics:
+    """Counters of the HTTP layer in the Prometheus text exposition format (``GET /metrics``), next to the JSON of
+    ``/v1/stats`` (the reference exposes only the latter, ``crates/ferrite-http/src/driver.rs``): requests, prompt and
+    completion tokens, finish reasons, a time-to-first-token histogram, and the engine's gauges."""
+
+    BUCKETS = (0.01, 0.025, 0.05, 0.1, 0.25, 0.5, 1.0, 2.5, 5.0, 10.0, 30.0)
+
+    def __init__(self):
+        self.requests = self.prompt_tokens = self.completion_tokens = 0
+        self.reasons: dict = {}
+        self.ttft_counts = [0] * (len(self.BUCKETS) + 1)
+        self.ttft_sum = 0.0
+
+    def first_token(self, seconds: float) -> None:
+        self.ttft_sum += seconds
+        for i, b in enumerate(self.BUCKETS):
+            if seconds <= b:
+                self.ttft_counts[i] += 1
+                return
+        self.ttft_counts[-1] += 1
+
+    def finished(self, reason: str) -> None:
+        key = reason.split(":", 1)[0] or "stop"
+        self.reasons[key] = self.reasons.get(key, 0) + 1
+
+    def render(self, stats: dict, poisoned: bool) -> str:
+        e = stats.get("engine", {})
+        out = ["# TYPE ferrite_requests_total counter", f"ferrite_requests_total {self.requests}",
+               "# TYPE ferrite_prompt_tokens_total counter", f"ferrite_prompt_tokens_total {self.prompt_tokens}",
+               "# TYPE ferrite_completion_tokens_total counter", f"ferrite_completion_tokens_total {self.completion_tokens}",
+               "# TYPE ferrite_requests_finished_total counter"]
+        for k in sorted(self.reasons):
+            out.append(f'ferrite_requests_finished_total{{reason="{k}"}} {self.reasons[k]}')
+        out.append("# TYPE ferrite_time_to_first_token_seconds histogram")
+        cum = 0
+        for b, c in zip(self.BUCKETS, self.ttft_counts):
+            cum += c
+            out.append(f'ferrite_time_to_first_token_seconds_bucket{{le="{b}"}} {cum}')
+        cum += self.ttft_counts[-1]
+        out += [f'ferrite_time_to_first_token_seconds_bucket{{le="+Inf"}} {cum}',
+                f"ferrite_time_to_first_token_seconds_sum {self.ttft_sum:.6f}",
+                f"ferrite_time_to_first_token_seconds_count {cum}"]
+        for name, key in (("ticks_total", "ticks"), ("engine_tokens_committed_total", "tokens_committed")):
+            out += [f"# TYPE ferrite_{name} counter", f"ferrite_{name} {int(e.get(key, 0))}"]
+        for name, key in (("live_rows", "live_rows"), ("queued_requests", "queued")):
+            out += [f"# TYPE ferrite_{name} gauge", f"ferrite_{name} {int(e.get(key, 0))}"]
+        out += ["# TYPE ferrite_engine_failed gauge", f"ferrite_engine_failed {int(poisoned)}"]
+        return "\n".join(out) + "\n"
+
+
 def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str = "glm-5.3-flash",
                on_shutdown=None):
     from fastapi import FastAPI, Request
     from fastapi.responses import JSONResponse, StreamingResponse
 
     app = FastAPI(title="ferrite_b200")
+    metrics = ServerMetrics()
 
     async def _next_event(sink):
         return await sink.get()
@@ -96,6 +147,9 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
             return _err(f"engine failed: {e}", 503, "server_error")
         cid = "chatcmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())
+        t_submit = time.perf_counter()
+        metrics.requests += 1
+        metrics.prompt_tokens += len(prompt)
 
         if not stream:
             ids: List[int] = []
@@ -103,9 +157,13 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
             while True:
                 ev = await _next_event(sink)
                 if ev.kind == "tokens":
+                    if not ids:
+                        metrics.first_token(time.perf_counter() - t_submit)
                     ids.extend(ev.ids)
+                    metrics.completion_tokens += len(ev.ids)
                 elif ev.kind == "finished":
                     usage, reason = ev.usage, ev.reason
+                    metrics.finished(reason)
                     break
             return JSONResponse({
                 "id": cid, "object": "chat.completion", "created": created, "model": model,
@@ -123,12 +181,17 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
         async def gen():
             held = b""
             done = False
+            first = True
             try:
                 while True:
                     ev = await _next_event(sink)
                     if ev.kind == "admitted":
                         yield f": ferrite: admitted prefix_hit={str(ev.prefix_hit).lower()} prompt_tokens={ev.prompt_tokens}\n\n"
                     elif ev.kind == "tokens":
+                        if first:
+                            metrics.first_token(time.perf_counter() - t_submit)
+                            first = False
+                        metrics.completion_tokens += len(ev.ids)
                         data = held + tokenizer.decode_bytes(ev.ids)
                         hb = utf8_holdback(data)
                         held = data[len(data) - hb:] if hb else b""
@@ -141,10 +204,12 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
                                     usage=_usage(ev.usage) if include_usage else None)
                         yield "data: [DONE]\n\n"
                         done = True
+                        metrics.finished(ev.reason)
                         return
             finally:
                 if not done:  # the client went away: stop generating for it
                     driver.cancel(rid)
+                    metrics.finished("client_gone")
 
         return StreamingResponse(gen(), media_type="text/event-stream",
                                  headers={"Cache-Control": "no-cache", "Connection": "keep-alive"})
@@ -163,6 +228,11 @@ def create_app(driver: EngineDriver, tokenizer: ChatTokenizer, model_name: str =
     @app.get("/v1/stats")
     async def stats():
         return driver.stats()
+
+    @app.get("/metrics")
+    async def prometheus():
+        from fastapi.responses import PlainTextResponse
+        return PlainTextResponse(metrics.render(driver.stats(), bool(driver.poisoned)), media_type="text/plain; version=0.0.4")
 
     @app.post("/shutdown")
     async def shutdown():

@@ -106,6 +106,13 @@ def test_http_routes_and_streaming():
         assert frames[-1]["choices"][0]["finish_reason"] == "length" and frames[-1]["usage"]["completion_tokens"] == 9
         st = c.get("/v1/stats").json()
         assert set(st) == {"engine", "radix", "hicache"} and st["engine"]["tokens_committed"] >= 18
+        m = c.get("/metrics")
+        assert m.status_code == 200 and m.headers["content-type"].startswith("text/plain")
+        vals = {l.split(" ")[0]: float(l.split(" ")[1]) for l in m.text.splitlines() if l and not l.startswith("#")}
+        assert vals["ferrite_requests_total"] == 2 and vals["ferrite_completion_tokens_total"] == 18
+        assert vals['ferrite_requests_finished_total{reason="length"}'] == 2
+        assert vals["ferrite_time_to_first_token_seconds_count"] == 2 and vals['ferrite_time_to_first_token_seconds_bucket{le="+Inf"}'] == 2
+        assert vals["ferrite_engine_tokens_committed_total"] >= 18 and vals["ferrite_engine_failed"] == 0
         assert c.post("/shutdown").json() == {"status": "shutting_down"}
     driver.shutdown()
 
