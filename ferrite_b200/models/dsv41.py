@@ -49,6 +49,21 @@ class DictWeights:
         return name in self.w
 
 
+ATTN_MIN_PARTS = 1536   # (row, head, split) partials that the attention workspace always holds
+
+
+def attn_splits(heads_local: int, n: int, sms: int = 148) -> int:
+    """Key splits of the sparse attention for n rows: about one CTA per SM over (head tiles x rows x splits).  One
+    decode row on a tensor-parallel shard takes 32 splits (4 clusters of 8 per head tile), 16 batched rows 4, a
+    prefill chunk 1: a CTA holds 233 registers per thread, so only one is resident per SM and every further wave
+    of CTAs costs a whole pass (16 rows at 16 splits: 60.7 us in 3.5 waves).  n * heads_local * splits never exceeds
+    max(n * heads_local, ATTN_MIN_PARTS): the partial buffers are sized for that."""
+    want = max(1, sms // (((heads_local + 7) // 8) * n))
+    if want >= 32:
+        return 32
+    return want // 8 * 8 if want >= 8 else want   # multiples of 8 merge by clusters
+
+
 class Dsv41DeviceModel:
     def __init__(self, cfg: Dsv41Config, src, rank: int = 0, world: int = 1, device="cuda", allreduce=None,
                  max_rows: int = 8, max_ctx: int = 1024, n_slots: int = 1, token_map=None):
@@ -275,7 +290,7 @@ class Dsv41DeviceModel:
         lmax = cfg.window_size + cfg.index_topk + max(cfg.dspark_block_size, 1)
         self.at_split = max(1, min(16, (lmax + 31) // 32))
         # the split count follows the row count (`_attn_splits`): about one CTA per SM, at most 32 splits
-        at_parts = max(M * self.Hl * self.at_split, 1536)
+        at_parts = max(M * self.Hl * self.at_split, ATTN_MIN_PARTS)
         ws["at_o"] = self._z(at_parts * hd)
         ws["at_ml"] = self._z(at_parts * 2)
         ws["at_ticket"] = self._z(M * ((self.Hl + 7) // 8), dtype=torch.int32)   # split-merge tickets (left at zero)
@@ -487,14 +502,7 @@ class Dsv41DeviceModel:
             ws["pre_cur"], ws["pre_nxt"] = pout, pin
 
     def _attn_splits(self, n: int) -> int:
-        """Key splits of the sparse attention for n rows: about one CTA per SM over (head tiles x rows x splits).  One
-        decode row on a tensor-parallel shard takes 32 splits (4 clusters of 8 per head tile), 16 batched rows 4, a
-        prefill chunk 1: a CTA holds 233 registers per thread, so only one is resident per SM and every further wave
-        of CTAs costs a whole pass (16 rows at 16 splits: 60.7 us in 3.5 waves)."""
-        want = max(1, 148 // (((self.Hl + 7) // 8) * n))
-        if want >= 32:
-            return 32
-        return want // 8 * 8 if want >= 8 else want   # multiples of 8 merge by clusters
+        return attn_splits(self.Hl, n)
 
     def _attention(self, L, rs: RowSet, shared: dict, ring, extra=None, n_extra=0, win_mode=0):
         cfg, ws, n = self.cfg, self.ws, rs.n

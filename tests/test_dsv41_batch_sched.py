@@ -145,3 +145,14 @@ def test_prompt_beyond_the_context_limit_is_refused_and_buckets_pad():
     except ContextOverflow:
         pass
     assert eng.buckets == [1, 2, 4, 5] and bucket_for(eng.buckets, 3) == 4 and bucket_for(eng.buckets, 5) == 5
+
+
+def test_attention_split_count_fits_its_workspace_and_the_kernel_limits():
+    from ferrite_b200.models.dsv41 import ATTN_MIN_PARTS, attn_splits
+    for heads in (1, 4, 8, 16, 32, 64):
+        for n in range(1, 300):
+            s = attn_splits(heads, n)
+            assert 1 <= s <= 32                                   # the merging warp keeps one split per lane
+            assert s < 8 or s % 8 == 0                            # 8 and more: whole clusters of 8
+            assert n * heads * s <= max(n * heads, ATTN_MIN_PARTS), (heads, n, s)
+    assert attn_splits(16, 1) == 32 and attn_splits(16, 16) == 4 and attn_splits(16, 64) == 1 and attn_splits(64, 1) == 16
