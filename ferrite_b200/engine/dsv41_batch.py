@@ -105,8 +105,13 @@ class Dsv41BatchEngine:
         return not self.waiting and not self.live
 
     def stats(self) -> dict:
+        # the shape of the GLM engines' stats (this engine keeps no prefix cache and no tiered snapshots)
         return {"engine": {"ticks": self.ticks, "tokens_committed": self.tokens, "live_rows": len(self.live),
-                           "queued": len(self.waiting), "free_slots": len(self.free)}}
+                           "queued": len(self.waiting), "free_slots": len(self.free)},
+                "radix": {"tree_nodes": 0, "tree_blocks": 0, "evictable_tokens": 0, "protected_tokens": 0,
+                          "hits": 0, "misses": 0},
+                "hicache": {"tiers": {"device": 0, "host": 0, "disk": 0}, "pages_in_use": len(self.live),
+                            "pages_free": len(self.free)}}
 
     # ------------------------------------------------------------------ one tick
     def _finish(self, s: _Seq, reason: str, out: List[Tuple[int, ReqEvent]]):
