@@ -27,7 +27,8 @@ class FakeRows:
 class FakeModel:
     """out_ids[row] = nxt(input token, position of the row); rows of one group take consecutive positions."""
 
-    def __init__(self, n_slots, max_ctx, max_rows):
+    def __init__(self, n_slots, max_ctx, max_rows, fn=None):
+        self.fn = fn or nxt
         self.dev = torch.device("cpu")
         self.max_ctx, self.max_rows = max_ctx, max_rows
         self.seq_len = torch.zeros(n_slots, dtype=torch.int32)
@@ -50,7 +51,7 @@ class FakeModel:
             pos = int(self.seq_len[s]) + seen.get(s, 0)
             assert pos < self.max_ctx, "a row beyond the context limit reached the model"
             seen[s] = seen.get(s, 0) + 1
-            self.ws["out_ids"][r] = nxt(int(ids[r]), pos)
+            self.ws["out_ids"][r] = self.fn(int(ids[r]), pos)
         if advance:
             for s, k in seen.items():
                 self.seq_len[s] += k
@@ -156,3 +157,43 @@ def test_attention_split_count_fits_its_workspace_and_the_kernel_limits():
             assert s < 8 or s % 8 == 0                            # 8 and more: whole clusters of 8
             assert n * heads * s <= max(n * heads, ATTN_MIN_PARTS), (heads, n, s)
     assert attn_splits(16, 1) == 32 and attn_splits(16, 16) == 4 and attn_splits(16, 64) == 1 and attn_splits(64, 1) == 16
+
+
+def test_batched_engine_behind_the_http_server_streams_two_concurrent_requests():
+    """EngineDriver + the OpenAI-style API over the batched engine (host stand-in model that emits printable bytes):
+    two streamed requests run in the same decode ticks and both get their own greedy text."""
+    import json
+    import threading
+
+    from fastapi.testclient import TestClient
+
+    from ferrite_b200.serve.api import create_app
+    from ferrite_b200.serve.engine import EngineDriver
+    from ferrite_b200.serve.tokenizer import ByteTokenizer, ChatTokenizer
+    printable = lambda tok, pos: 97 + (tok * 7 + pos) % 26
+    model = FakeModel(3, 512, 8, fn=printable)
+    eng = Dsv41BatchEngine(None, None, max_ctx=512, max_seqs=2, prefill_rows=8, prefill_budget=64, model=model)
+    tok = ChatTokenizer(ByteTokenizer())
+    driver = EngineDriver(eng)
+    app = create_app(driver, tok, "dsv41-batch", on_shutdown=lambda: None)
+    texts = {}
+
+    def ask(c, name, content):
+        body = {"messages": [{"role": "user", "content": content}], "max_tokens": 12, "stream": True}
+        with c.stream("POST", "/v1/chat/completions", json=body) as s:
+            frames = [json.loads(l[6:]) for l in s.iter_lines() if l.startswith("data: {")]
+        texts[name] = "".join(f["choices"][0]["delta"].get("content", "") for f in frames)
+        assert frames[-1]["choices"][0]["finish_reason"] == "length"
+
+    with TestClient(app) as c:
+        th = [threading.Thread(target=ask, args=(c, n, t)) for n, t in (("a", "first prompt"), ("b", "another, longer prompt"))]
+        for t in th:
+            t.start()
+        for t in th:
+            t.join(timeout=60)
+        assert set(texts) == {"a", "b"} and all(len(v) == 12 and v.isalpha() for v in texts.values())
+        assert texts["a"] != texts["b"]
+        st = c.get("/v1/stats").json()
+        assert st["engine"]["tokens_committed"] == 24 and st["engine"]["free_slots"] == 2
+    driver.shutdown()
+    assert any(slots == 2 for _, slots in model.forwards)            # the two requests shared decode forwards
