@@ -125,3 +125,19 @@ def test_cli_dsv41_cpu_backend_generates(capsys):
         assert main(["--model", "dsv41-tiny", "--backend", "cpu", "--prompt", "hi", "--max-tokens", "6", "--mtp", mtp]) == 0
         outs.append(capsys.readouterr().out)
     assert outs[0] == outs[1] and len(outs[0]) > 0       # speculation does not change the text
+
+
+def test_serving_workload_bench_on_the_mock_engine(capsys):
+    """bench_serving.py end to end on the host engine: ragged prompts, more requests than rows, every request gets
+    its tokens and a first-token time."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench_serving.py")
+    spec = importlib.util.spec_from_file_location("bench_serving", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.main(["--model", "mock", "--requests", "20", "--max-seqs", "4", "--prompt-min", "5", "--prompt-max", "90",
+                     "--new-tokens", "12"]) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["metric"] == "serving_output_tok_s" and line["output_tokens"] == 20 * 12 and line["value"] > 0
+    assert line["finish_reasons"] == {"length": 20} and line["p50_ttft_ms"] is not None and line["p95_ttft_ms"] >= line["p50_ttft_ms"]
