@@ -155,6 +155,20 @@ def tensor_specs_cached(cfg: Dsv41Config) -> Dict[str, Spec]:
     return tensor_specs(cfg)
 
 
+def estimate_device_bytes(cfg: Dsv41Config, world: int = 1) -> int:
+    """Weight bytes one rank of a `world`-way tensor-parallel device model holds: e2m1 experts with their ue8m0 scales
+    (17 / 32 byte per value), engram tables as e4m3 bytes, dense and bf16 tensors as bf16 (dense e4m3 weights are
+    expanded at load), f32 vectors; sharded tensors count 1 / world.  Caches and workspaces come on top (a few GB)."""
+    import math
+    per = {"expert": (17 / 32) if cfg.expert_dtype == "fp4" else 2.0, "table": 1.0, "dense": 2.0, "bf16": 2.0, "f32": 4.0,
+           "fp4": 17 / 32, "fp8": 2.0}
+    total = 0.0
+    for spec in tensor_specs_cached(cfg).values():
+        n = math.prod(spec.shape) * per.get(spec.kind, 4.0)
+        total += n / world if spec.shard is not None else n
+    return int(total)
+
+
 # ---------------------------------------------------------------------------------------------
 # random weights (values already on their storage grid, returned as f32)
 # ---------------------------------------------------------------------------------------------

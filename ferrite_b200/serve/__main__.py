@@ -100,9 +100,11 @@ def _build_dsv41(args, tok):
     if args.model_dir and not args.synthetic:
         from ..models.dsv41_checkpoint import Dsv41CheckpointSource
         src = Dsv41CheckpointSource(args.model_dir, cfg)
-    else:
+    elif args.backend == "cpu" or args.model == "dsv41-tiny":
         from ..models.dsv41_weights import random_weights
         src = DictWeights(random_weights(cfg, 0))
+    else:
+        src = None   # production shapes: synthetic weights are generated on the device, shard by shard (below)
     if args.backend == "cpu":
         from ..models.dsv41_ref import Dsv41Reference
         from ..models.dsv41_weights import tensor_specs
@@ -110,6 +112,15 @@ def _build_dsv41(args, tok):
         return SingleFlight(_Dsv41RefStep(Dsv41Reference(cfg, w), spec=args.mtp > 1)), tok, 0, 1
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # refuse a model that cannot fit before anything is allocated (475 GiB at production shapes: TP >= 4 on 180 GB parts)
+    from ..models.dsv41_weights import estimate_device_bytes
+    need, have = estimate_device_bytes(cfg, world), torch.cuda.get_device_properties(dev).total_memory
+    if need > 0.92 * have:
+        raise SystemExit(f"--model {args.model} at --tp {world} needs about {need / 2**30:.0f} GiB of weights per GPU, "
+                         f"this GPU has {have / 2**30:.0f} GiB: use more ranks")
+    if src is None:
+        from ..models.dsv41_synth import SyntheticDsv41Source
+        src = SyntheticDsv41Source(cfg, dev)
     allreduce = None
     if world > 1:
         import torch.distributed as dist

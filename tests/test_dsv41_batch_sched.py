@@ -197,3 +197,14 @@ def test_batched_engine_behind_the_http_server_streams_two_concurrent_requests()
         assert st["engine"]["tokens_committed"] == 24 and st["engine"]["free_slots"] == 2
     driver.shutdown()
     assert any(slots == 2 for _, slots in model.forwards)            # the two requests shared decode forwards
+
+
+def test_weight_bytes_estimate_matches_the_checkpoint_size_and_shrinks_with_ranks():
+    from ferrite_b200.models.dsv41_config import Dsv41Config
+    from ferrite_b200.models.dsv41_weights import estimate_device_bytes
+    cfg = Dsv41Config()
+    gib = [estimate_device_bytes(cfg, w) / 2 ** 30 for w in (1, 2, 4, 8)]
+    assert 470 < gib[0] < 480                                  # the production checkpoint is 475 GiB
+    assert gib[2] < 0.92 * 180e9 / 2 ** 30 < gib[1]            # fits a 180 GB part from four ranks on, not on two
+    assert all(a > b for a, b in zip(gib, gib[1:]))
+    assert gib[3] > gib[0] / 8                                 # replicated tensors do not shrink
