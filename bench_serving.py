@@ -11,7 +11,8 @@ over the run (first submit to last finish, wall clock), p50 / p95 time to first 
     python bench_serving.py --model glm53 --requests 64 --max-seqs 32       # one GPU (128 of 288 experts resident)
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench_serving.py --model glm53 --tp 8 \\
         --requests 64 --max-seqs 32
-    python bench_serving.py --model dsv41 --requests 32 --max-seqs 32 --prompt-min 2048 --prompt-max 2048 --new-tokens 256
+    python -m torch.distributed.run --nproc-per-node 4 --master-addr 127.0.0.1 bench_serving.py --model dsv41 --tp 4 \\
+        --requests 32 --max-seqs 32 --prompt-min 2048 --prompt-max 2048 --new-tokens 256
 
 Weights are random-init, prompts synthetic.  Rank 0 prints one JSON line; the other ranks follow its commands.
 """
