@@ -240,7 +240,24 @@ def main(argv=None):
     ap.add_argument("--prefill-rows", type=int, default=1024,
                     help="rows per prefill chunk of the single-sequence engine (the tensor-core expert GEMM and the "
                          "chunked GatedDeltaNet scan take over from 64 rows)")
+    ap.add_argument("--cpu-profile", default=None, metavar="FILE",
+                    help="host CPU profile (cProfile) of the one-shot run, written as pstats to FILE with the 25 heaviest "
+                         "functions on stderr: the counterpart of the reference's pprof switch (crates/ferrite-serve/src/main.rs)")
     args = ap.parse_args(argv)
+    if args.cpu_profile and not args.serve:
+        import cProfile
+        import pstats
+        prof = cProfile.Profile()
+        args_file, args.cpu_profile = args.cpu_profile, None
+        try:
+            return prof.runcall(_run, args)
+        finally:
+            prof.dump_stats(args_file)
+            pstats.Stats(prof, stream=sys.stderr).sort_stats("cumulative").print_stats(25)
+    return _run(args)
+
+
+def _run(args):
     eng, tok, rank, world = build_engine(args)
     if rank != 0:
         eng.follow()

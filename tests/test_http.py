@@ -141,3 +141,12 @@ def test_serving_workload_bench_on_the_mock_engine(capsys):
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert line["metric"] == "serving_output_tok_s" and line["output_tokens"] == 20 * 12 and line["value"] > 0
     assert line["finish_reasons"] == {"length": 20} and line["p50_ttft_ms"] is not None and line["p95_ttft_ms"] >= line["p50_ttft_ms"]
+
+
+def test_cli_host_cpu_profile(tmp_path, capsys):
+    from ferrite_b200.serve.__main__ import main
+    out = tmp_path / "run.pstats"
+    assert main(["--model", "mock", "--prompt", "hello", "--max-tokens", "4", "--cpu-profile", str(out)]) == 0
+    import pstats
+    st = pstats.Stats(str(out))
+    assert st.total_calls > 0 and "cumulative" in capsys.readouterr().err
