@@ -211,7 +211,7 @@ def bench_batched(args, cfg, dev, model_rank, model_world, rank, world, allreduc
         eng.submit(RequestSpec(torch.randint(0, cfg.vocab_size, (args.prompt_len,), generator=g).tolist(), budget))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    while sum(s.decoding for s in eng.live.values()) < N:
+    while eng.n_decoding() < N:
         eng.tick()
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0

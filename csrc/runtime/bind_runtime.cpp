@@ -6,6 +6,7 @@
 #include <pybind11/numpy.h>
 
 #include "safetensors_file.h"
+#include "slot_scheduler.h"
 #include "tick_planner.h"
 
 namespace py = pybind11;
@@ -154,6 +155,61 @@ PYBIND11_MODULE(_runtime, m) {
         .def_readonly("cached_tokens", &Request::cached_tokens).def_readonly("generated", &Request::generated)
         .def_readonly("pages", &Request::pages).def_readonly("finish_reason", &Request::finish_reason)
         .def_readonly("max_new", &Request::max_new);
+    py::class_<SlotSchedConfig>(m, "SlotSchedConfig")
+        .def(py::init<>())
+        .def_readwrite("max_seqs", &SlotSchedConfig::max_seqs)
+        .def_readwrite("prefill_rows", &SlotSchedConfig::prefill_rows)
+        .def_readwrite("prefill_budget", &SlotSchedConfig::prefill_budget)
+        .def_readwrite("max_ctx", &SlotSchedConfig::max_ctx)
+        .def_readwrite("buckets", &SlotSchedConfig::buckets);
+    py::class_<SlotEvent>(m, "SlotEvent")
+        .def_readonly("req", &SlotEvent::req)
+        .def_readonly("kind", &SlotEvent::kind)
+        .def_readonly("token", &SlotEvent::token)
+        .def_readonly("reason", &SlotEvent::reason)
+        .def_readonly("prompt_tokens", &SlotEvent::prompt_tokens)
+        .def_readonly("completion_tokens", &SlotEvent::completion_tokens);
+    m.attr("SLOT_EV_ADMITTED") = (int)SlotEvent::ADMITTED;
+    m.attr("SLOT_EV_TOKEN") = (int)SlotEvent::TOKEN;
+    m.attr("SLOT_EV_FINISHED") = (int)SlotEvent::FINISHED;
+    py::class_<SlotChunk>(m, "SlotChunk")
+        .def_readonly("req", &SlotChunk::req)
+        .def_readonly("slot", &SlotChunk::slot)
+        .def_readonly("start", &SlotChunk::start)
+        .def_readonly("len", &SlotChunk::len)
+        .def_readonly("last", &SlotChunk::last);
+    py::class_<SlotDecodePlan>(m, "SlotDecodePlan")
+        .def_readonly("slots", &SlotDecodePlan::slots)
+        .def_readonly("reqs", &SlotDecodePlan::reqs)
+        .def_readonly("bucket", &SlotDecodePlan::bucket);
+    py::class_<SlotPrefillPlan>(m, "SlotPrefillPlan")
+        .def_readonly("events", &SlotPrefillPlan::events)
+        .def_readonly("reset_slots", &SlotPrefillPlan::reset_slots)
+        .def_readonly("chunks", &SlotPrefillPlan::chunks);
+    py::class_<SlotStats>(m, "SlotStats")
+        .def_readonly("ticks", &SlotStats::ticks)
+        .def_readonly("tokens_committed", &SlotStats::tokens_committed)
+        .def_readonly("live", &SlotStats::live)
+        .def_readonly("queued", &SlotStats::queued)
+        .def_readonly("free_slots", &SlotStats::free_slots);
+    // the three ingest / begin calls return (events, released slots)
+    py::class_<SlotScheduler>(m, "SlotScheduler")
+        .def(py::init<const SlotSchedConfig&>())
+        .def("buckets", &SlotScheduler::buckets)
+        .def("max_prompt", &SlotScheduler::max_prompt)
+        .def("submit", &SlotScheduler::submit, py::arg("prompt"), py::arg("max_new"), py::arg("stop_ids") = std::vector<int32_t>())
+        .def("cancel", &SlotScheduler::cancel)
+        .def("idle", &SlotScheduler::idle)
+        .def("free_slots", &SlotScheduler::free_slots)
+        .def("begin_tick", [](SlotScheduler& s) { std::vector<int> rel; auto ev = s.begin_tick(&rel); return py::make_tuple(ev, rel); })
+        .def("plan_decode", &SlotScheduler::plan_decode)
+        .def("ingest_decode", [](SlotScheduler& s, const std::vector<int32_t>& toks) {
+            std::vector<int> rel; auto ev = s.ingest_decode(toks, &rel); return py::make_tuple(ev, rel); })
+        .def("plan_prefill", &SlotScheduler::plan_prefill)
+        .def("ingest_first", [](SlotScheduler& s, int64_t rid, int32_t tok) {
+            std::vector<int> rel; auto ev = s.ingest_first(rid, tok, &rel); return py::make_tuple(ev, rel); })
+        .def("stats", &SlotScheduler::stats);
+
     py::class_<BatchScheduler>(m, "BatchScheduler")
         .def(py::init<const SchedConfig&>())
         .def("max_prompt", &BatchScheduler::max_prompt)

@@ -17,30 +17,13 @@ Counterpart of the reference's batched DSV41 arm (``scripts/batched_400_v2.sh``;
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..models.dsv41 import Dsv41DeviceModel
 from ..models.dsv41_config import Dsv41Config
 from ..serve.engine import ContextOverflow, ReqEvent, RequestSpec, Usage
-
-
-@dataclass
-class _Seq:
-    rid: int
-    prompt: List[int]
-    max_new: int
-    stop: Tuple[int, ...]
-    slot: int = -1
-    filled: int = 0                 # prompt tokens already in the caches
-    out: List[int] = field(default_factory=list)
-
-    @property
-    def decoding(self) -> bool:
-        return self.slot >= 0 and self.filled == len(self.prompt)
 
 
 def bucket_for(buckets: Sequence[int], n: int) -> int:
@@ -63,7 +46,16 @@ class Dsv41BatchEngine:
         self.dev = dev = m.dev
         self.on_gpu = dev.type == "cuda"
         self.use_graphs = use_graphs and self.on_gpu
-        self.buckets = [b for b in buckets if b < max_seqs] + [max_seqs]
+        # the planner is native (csrc/runtime/slot_scheduler.h): admission, prefill chunks, decode rows, finish rules
+        from .. import build
+        build.build_runtime()
+        from .. import _runtime as rt
+        self.rt = rt
+        sc = rt.SlotSchedConfig()
+        sc.max_seqs, sc.prefill_rows, sc.prefill_budget, sc.max_ctx = max_seqs, prefill_rows, self.prefill_budget, m.max_ctx
+        sc.buckets = [int(b) for b in buckets]
+        self.sched = rt.SlotScheduler(sc)
+        self.buckets = list(self.sched.buckets())
         self.dummy_slot = max_seqs                                    # padding rows of a bucket run on this slot
         self.rowsets = {b: m.make_rows(list(range(b)), [1] * b) for b in self.buckets}
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
@@ -72,12 +64,7 @@ class Dsv41BatchEngine:
         self.pin_out = torch.zeros(max_seqs, dtype=torch.int32)
         if self.on_gpu:
             self.pin_out = self.pin_out.pin_memory()
-        self.free: List[int] = list(range(max_seqs - 1, -1, -1))
-        self.waiting: Deque[_Seq] = deque()
-        self.live: Dict[int, _Seq] = {}                                # by request id, admission order
-        self.cancelled: set = set()
-        self.next_id = 1
-        self.ticks = self.tokens = 0
+        self.prompts: Dict[int, List[int]] = {}                        # token ids of the live and waiting requests
         self.launches = 0
         if model is None:
             from ..parallel.collective import startup_barrier
@@ -85,7 +72,7 @@ class Dsv41BatchEngine:
 
     # ------------------------------------------------------------------ ServeEngine
     def max_prompt(self) -> int:
-        return self.model.max_ctx - 4
+        return self.sched.max_prompt()
 
     def validate(self, spec: RequestSpec) -> None:
         if not spec.prompt_ids or len(spec.prompt_ids) > self.max_prompt():
@@ -94,45 +81,52 @@ class Dsv41BatchEngine:
 
     def submit(self, spec: RequestSpec) -> int:
         self.validate(spec)
-        rid, self.next_id = self.next_id, self.next_id + 1
-        self.waiting.append(_Seq(rid, list(spec.prompt_ids), max(1, spec.max_new_tokens), tuple(spec.stop_ids)))
+        prompt = [int(t) for t in spec.prompt_ids]
+        rid = self.sched.submit(prompt, int(spec.max_new_tokens), [int(t) for t in spec.stop_ids])
+        assert rid > 0
+        self.prompts[rid] = prompt
         return rid
 
     def cancel(self, req: int) -> None:
-        self.cancelled.add(req)
+        self.sched.cancel(req)
 
     def idle(self) -> bool:
-        return not self.waiting and not self.live
+        return self.sched.idle()
+
+    @property
+    def free(self) -> List[int]:
+        return list(self.sched.free_slots())
+
+    def n_decoding(self) -> int:
+        """Sequences whose prompt is in the caches (the rows of the next decode tick)."""
+        return len(self.sched.plan_decode().slots)
 
     def stats(self) -> dict:
+        st = self.sched.stats()
         # the shape of the GLM engines' stats (this engine keeps no prefix cache and no tiered snapshots)
-        return {"engine": {"ticks": self.ticks, "tokens_committed": self.tokens, "live_rows": len(self.live),
-                           "queued": len(self.waiting), "free_slots": len(self.free)},
+        return {"engine": {"ticks": st.ticks, "tokens_committed": st.tokens_committed, "live_rows": st.live,
+                           "queued": st.queued, "free_slots": st.free_slots},
                 "radix": {"tree_nodes": 0, "tree_blocks": 0, "evictable_tokens": 0, "protected_tokens": 0,
                           "hits": 0, "misses": 0},
-                "hicache": {"tiers": {"device": 0, "host": 0, "disk": 0}, "pages_in_use": len(self.live),
-                            "pages_free": len(self.free)}}
+                "hicache": {"tiers": {"device": 0, "host": 0, "disk": 0}, "pages_in_use": st.live,
+                            "pages_free": st.free_slots}}
 
     # ------------------------------------------------------------------ one tick
-    def _finish(self, s: _Seq, reason: str, out: List[Tuple[int, ReqEvent]]):
-        out.append((s.rid, ReqEvent("finished", reason=reason, usage=Usage(len(s.prompt), len(s.out), 0))))
-        if s.slot >= 0:
-            self.model.reset_slot(s.slot)
-            self.free.append(s.slot)
-        self.live.pop(s.rid, None)
-
-    def _emit(self, s: _Seq, tok: int, out: List[Tuple[int, ReqEvent]]):
-        """Commit one token of a sequence; ends the sequence at a stop id, its budget or the context limit."""
-        self.tokens += 1
-        if tok in s.stop:
-            self._finish(s, "stop", out)
-            return
-        s.out.append(tok)
-        out.append((s.rid, ReqEvent("tokens", ids=[tok])))
-        if len(s.out) >= s.max_new:
-            self._finish(s, "length", out)
-        elif len(s.prompt) + len(s.out) + 2 >= self.model.max_ctx:
-            self._finish(s, "context", out)
+    def _convert(self, res, out: List[Tuple[int, ReqEvent]]):
+        """(events, released slots) of a planner call -> ReqEvents; released slots get their lengths cleared."""
+        evs, released = res
+        rt = self.rt
+        for e in evs:
+            if e.kind == rt.SLOT_EV_ADMITTED:
+                out.append((e.req, ReqEvent("admitted", prefix_hit=False, prompt_tokens=e.prompt_tokens)))
+            elif e.kind == rt.SLOT_EV_TOKEN:
+                out.append((e.req, ReqEvent("tokens", ids=[e.token])))
+            else:
+                out.append((e.req, ReqEvent("finished", reason=e.reason,
+                                            usage=Usage(e.prompt_tokens, e.completion_tokens, 0))))
+                self.prompts.pop(e.req, None)
+        for slot in released:
+            self.model.reset_slot(slot)
 
     def _decode_body(self, bucket: int):
         m = self.model
@@ -162,18 +156,12 @@ class Dsv41BatchEngine:
     def tick(self) -> List[Tuple[int, ReqEvent]]:
         m = self.model
         out: List[Tuple[int, ReqEvent]] = []
-        self.ticks += 1
-        # cancellations: waiting requests are dropped, live ones free their slot
-        if self.cancelled:
-            self.waiting = deque(s for s in self.waiting if s.rid not in self.cancelled)
-            for s in [s for s in self.live.values() if s.rid in self.cancelled]:
-                self._finish(s, "cancelled", out)
-            self.cancelled.clear()
+        self._convert(self.sched.begin_tick(), out)      # cancellations: waiting requests are dropped, live ones free their slot
         # decode: every sequence whose prompt is in the caches advances by one token
-        dec = [s for s in self.live.values() if s.decoding]
-        if dec:
-            bucket = bucket_for(self.buckets, len(dec))
-            slots = [s.slot for s in dec] + [self.dummy_slot] * (bucket - len(dec))
+        dp = self.sched.plan_decode()
+        if dp.bucket:
+            bucket, live = dp.bucket, len(dp.slots)
+            slots = list(dp.slots) + [self.dummy_slot] * (bucket - live)
             slot_t = torch.tensor(slots, dtype=torch.int32)
             rs = self.rowsets[bucket]
             rs.row_slot.copy_(slot_t)
@@ -188,31 +176,21 @@ class Dsv41BatchEngine:
             if self.on_gpu:
                 torch.cuda.current_stream().synchronize()
             m.arena.verify()
-            for i, s in enumerate(dec):
-                self._emit(s, int(self.pin_out[i]), out)
+            self._convert(self.sched.ingest_decode([int(t) for t in self.pin_out[:live]]), out)
         # admission, then chunked prefill within the tick's token budget (oldest admitted first)
-        while self.waiting and self.free:
-            s = self.waiting.popleft()
-            s.slot = self.free.pop()
-            m.reset_slot(s.slot)
-            self.live[s.rid] = s
-            out.append((s.rid, ReqEvent("admitted", prefix_hit=False, prompt_tokens=len(s.prompt))))
-        budget = self.prefill_budget
-        for s in [s for s in self.live.values() if not s.decoding]:
-            while budget > 0 and s.filled < len(s.prompt):
-                n = min(self.prefill_rows, len(s.prompt) - s.filled, budget)
-                ids = torch.tensor(s.prompt[s.filled:s.filled + n], dtype=torch.int32, device=self.dev)
-                last = s.filled + n == len(s.prompt)
-                m.forward(m.make_rows([s.slot], [n]), ids, advance=True, want_logits=last)
-                s.filled += n
-                budget -= n
-                if last:
-                    first = int(m.ws["out_ids"][n - 1].item())
-                    m.arena.verify(snapshot=False)
-                    self.tok_slot[s.slot] = first
-                    self._emit(s, first, out)
-            if budget <= 0:
-                break
+        pp = self.sched.plan_prefill()
+        for slot in pp.reset_slots:
+            m.reset_slot(slot)
+        self._convert((pp.events, []), out)
+        for ch in pp.chunks:
+            prompt = self.prompts[ch.req]
+            ids = torch.tensor(prompt[ch.start:ch.start + ch.len], dtype=torch.int32, device=self.dev)
+            m.forward(m.make_rows([ch.slot], [ch.len]), ids, advance=True, want_logits=ch.last)
+            if ch.last:
+                first = int(m.ws["out_ids"][ch.len - 1].item())
+                m.arena.verify(snapshot=False)
+                self.tok_slot[ch.slot] = first
+                self._convert(self.sched.ingest_first(ch.req, first), out)
         return out
 
     def run_all(self, specs: List[RequestSpec], max_ticks: int = 100000) -> Dict[int, List[int]]:

@@ -234,3 +234,65 @@ def test_pdaf_transfer_plan_page_mask():
     assert p0.src_pages == [0, 4] and p0.dst_slots == [0, 1]   # page p lands at slot p // n_dcp
     assert TransferPlan(70, 16).src_pages == [0, 1, 2, 3, 4]
     assert p0.bytes_moved(100, 7) == 207
+
+
+def test_slot_scheduler_plans_admission_budgeted_prefill_and_finish_rules():
+    """csrc/runtime/slot_scheduler.h driven directly: FIFO admission into free slots, the per-tick prefill budget cut
+    into chunks, decode rows in admission order with a padded bucket, stop / length / context / cancel finishes."""
+    from ferrite_b200 import build
+    build.build_runtime()
+    from ferrite_b200 import _runtime as rt
+    c = rt.SlotSchedConfig()
+    c.max_seqs, c.prefill_rows, c.prefill_budget, c.max_ctx, c.buckets = 2, 4, 6, 16, [1, 2, 4, 8]
+    s = rt.SlotScheduler(c)
+    assert s.buckets() == [1, 2] and s.max_prompt() == 12 and s.free_slots() == [1, 0]
+    assert s.submit([], 1, []) == -1 and s.submit(list(range(13)), 1, []) == -1
+    a = s.submit([1, 2, 3, 4, 5, 6, 7], 3, [99])
+    b = s.submit([1], 50, [])
+    d = s.submit([5, 5], 2, [])
+    assert s.begin_tick() == ([], []) and s.plan_decode().bucket == 0
+    pp = s.plan_prefill()
+    assert [(e.req, e.kind, e.prompt_tokens) for e in pp.events] == [(a, rt.SLOT_EV_ADMITTED, 7), (b, rt.SLOT_EV_ADMITTED, 1)]
+    assert pp.reset_slots == [0, 1]
+    assert [(ch.req, ch.slot, ch.start, ch.len, ch.last) for ch in pp.chunks] == [(a, 0, 0, 4, False), (a, 0, 4, 2, False)]
+    # tick 2: nobody decodes yet; a's last token and b's prompt fit the budget
+    s.begin_tick()
+    assert s.plan_decode().bucket == 0
+    pp = s.plan_prefill()
+    assert [(ch.req, ch.start, ch.len, ch.last) for ch in pp.chunks] == [(a, 6, 1, True), (b, 0, 1, True)]
+    ev, rel = s.ingest_first(a, 40)
+    assert [(e.req, e.kind, e.token) for e in ev] == [(a, rt.SLOT_EV_TOKEN, 40)] and rel == []
+    s.ingest_first(b, 41)
+    # tick 3: both decode in one bucket of 2; a hits its stop id (not emitted), its slot goes to d in the same tick
+    s.begin_tick()
+    dp = s.plan_decode()
+    assert (dp.bucket, dp.slots, dp.reqs) == (2, [0, 1], [a, b])
+    ev, rel = s.ingest_decode([99, 7])
+    assert [(e.req, e.kind, e.reason) for e in ev] == [(a, rt.SLOT_EV_FINISHED, "stop"), (b, rt.SLOT_EV_TOKEN, "")]
+    assert ev[0].completion_tokens == 1 and rel == [0]
+    pp = s.plan_prefill()
+    assert [e.req for e in pp.events] == [d] and pp.reset_slots == [0] and [(ch.req, ch.len, ch.last) for ch in pp.chunks] == [(d, 2, True)]
+    ev, _ = s.ingest_first(d, 8)
+    # b runs into the context limit: 1 prompt token + n outputs + 2 >= 16
+    reasons = {}
+    for _ in range(40):
+        s.begin_tick()
+        dp = s.plan_decode()
+        if not dp.bucket:
+            break
+        ev, rel = s.ingest_decode([3] * len(dp.slots))
+        for e in ev:
+            if e.kind == rt.SLOT_EV_FINISHED:
+                reasons[e.req] = (e.reason, e.completion_tokens)
+        s.plan_prefill()
+    assert reasons[d] == ("length", 2) and reasons[b] == ("context", 13)
+    # cancellation of a queued and of a live request
+    x = s.submit([1, 2], 5, [])
+    y = s.submit([3], 5, [])
+    z = s.submit([4], 5, [])
+    s.begin_tick(); s.plan_decode(); s.plan_prefill()
+    s.cancel(x); s.cancel(z)
+    ev, rel = s.begin_tick()
+    assert [(e.req, e.reason) for e in ev] == [(x, "cancelled")] and len(rel) == 1
+    st = s.stats()
+    assert (st.live, st.queued, st.free_slots) == (1, 0, 1) and not s.idle()
